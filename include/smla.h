@@ -1,0 +1,178 @@
+/*
+ * C ABI of the B200 sparse-MLA kernel library (libsmla_b200.so).
+ *
+ * Every entry point takes plain device pointers, sizes and a CUDA stream (cudaStream_t passed
+ * as void*; NULL = the legacy default stream).  Nothing here allocates, synchronises with the
+ * host or reads device memory on the host unless its comment says so, so the calls can be
+ * recorded into CUDA graphs.  All functions return 0 on success, a negative SMLA_E_* code for
+ * an argument error (nothing was launched) or a positive cudaError_t value when a launch
+ * failed.  smla_last_error() returns the message of the last failure on the calling thread.
+ *
+ * Each declaration names the interface of the reference project (path:line in that project)
+ * that it stands in for.
+ */
+#ifndef SMLA_H_
+#define SMLA_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define SMLA_D_NOPE 512
+#define SMLA_D_ROPE 64
+#define SMLA_D_QK 576
+#define SMLA_D_V 512
+#define SMLA_ROW_BYTES 656   /* 512 e4m3 | 4 fp32 scales | 64 bf16 */
+#define SMLA_BLOCK_N 64      /* tokens per scheduling block */
+#define SMLA_SCHED_META_INTS 8
+
+enum {
+    SMLA_OK = 0,
+    SMLA_E_NULL = -1,        /* a required pointer is NULL */
+    SMLA_E_SHAPE = -2,       /* unsupported size (heads, topk, d_qk, ...) */
+    SMLA_E_ALIGN = -3,       /* pointer or stride not 16-byte aligned */
+    SMLA_E_UNSUPPORTED = -4, /* feature of the reference interface that is not built */
+    SMLA_E_WORKSPACE = -5,   /* scratch too small for the request */
+    SMLA_E_DEVICE = -6       /* the kernel reported a device-side status (see smla_device_status) */
+};
+
+/* Kernel selection for the attention entry points. */
+enum {
+    SMLA_IMPL_AUTO = 0,    /* tcgen05 kernel */
+    SMLA_IMPL_SCALAR = 1,  /* fp32 CUDA-core kernel: slow, exact; a second opinion in tests */
+    SMLA_IMPL_TC = 2       /* tcgen05/TMEM kernel, FP8 QK^T and PV */
+};
+
+const char* smla_last_error(void);
+int smla_version(void);
+
+/* Number of SMs of the current device (cached per device).  Host query only. */
+int smla_num_sms(void);
+
+/*
+ * Split-KV scheduler.  Replaces get_decode_metadata (csrc/binding.cpp:281-286,
+ * csrc/kernel/sched/get_sched_meta.cu:148-165).  Writes num_sm_parts records of 8 int32
+ * {begin_req, end_req, begin_block, end_block, begin_split_idx, first_is_split, last_is_split, 0}
+ * (layout of csrc/kernel/sched/sched_params.h:8-18) and the prefix sum num_splits[b+1].
+ * topk_length / extra_topk_length may be NULL.  One 32-thread CTA; b <= 8192.
+ */
+int smla_sched_meta(int b, int topk, int extra_topk, int num_sm_parts, int fixed_overhead,
+                    const int32_t* topk_length, const int32_t* extra_topk_length,
+                    int32_t* sched_meta, int32_t* num_splits, void* stream);
+
+/*
+ * Scheduler-driven split-KV decode.  Replaces sparse_mla_splitkv_v2_fwd
+ * (csrc/binding.cpp:96-164, kernel csrc/kernel/decode/decode_v2_kernel.cuh:54-657).
+ *   q          [num_tokens, num_heads, 576] bf16, contiguous
+ *   kv         packed rows of 656 bytes; row r lives at
+ *              kv + (r / page_block_size) * kv_block_stride_bytes + (r % page_block_size) * 656
+ *   indices    [num_tokens, topk] int32, physical row numbers, -1 = no entry
+ *   o_accum    [>= num_tokens + num_sm_parts, 1, num_heads, 512] fp32 partial outputs
+ *   lse_accum  [>= num_tokens + num_sm_parts, 1, num_heads]      fp32 base-2 partial LSE
+ *   out        [num_tokens, num_heads, 512] bf16 (written directly for unsplit requests)
+ *   out_lse    [num_tokens, num_heads] fp32, base-2 LSE of the scaled logits, -1e30 when empty
+ *   attn_sink  [num_heads] fp32 natural-log sink logit or NULL; topk_length [num_tokens] or NULL
+ * num_heads in 1..128; topk a multiple of 64.  status (device int32[4], may be NULL) receives a
+ * non-zero code when a bounded wait inside the tcgen05 kernel gave up.
+ */
+int smla_decode_splitkv(const void* q, const void* kv, const int32_t* indices,
+                        float* o_accum, float* lse_accum, void* out, float* out_lse,
+                        const int32_t* sched_meta, const int32_t* num_splits,
+                        int num_tokens, int num_heads, int topk, float sm_scale,
+                        int page_block_size, int64_t kv_block_stride_bytes, int num_sm_parts,
+                        const float* attn_sink, const int32_t* topk_length,
+                        int impl, int32_t* status, void* stream);
+
+/*
+ * LSE-weighted merge of the split partials.  Replaces sparse_mla_combine_v2_fwd
+ * (csrc/binding.cpp:166-183, kernel csrc/kernel/combine/combine_kernel.cu:39-159).
+ * Requests with <= 1 split are left untouched.  max_nsplits <= 1024.
+ */
+int smla_combine(const float* o_accum, const float* lse_accum, void* out, float* out_lse,
+                 const int32_t* num_splits, int batch, int num_heads, int max_nsplits,
+                 const float* attn_sink, void* stream);
+
+/*
+ * Single-pass sparse attention for many query tokens.  Replaces sparse_mla_prefill_fwd
+ * (csrc/binding.cpp:185-247, kernels csrc/kernel/prefill/prefill_kernel.cuh:48-553,570-1134).
+ * out_max_logits [num_tokens, num_heads] fp32 (running maximum of the scaled base-2 logits)
+ * may be NULL.
+ */
+int smla_prefill(const void* q, const void* kv, const int32_t* indices,
+                 void* out, float* out_lse, float* out_max_logits,
+                 int num_tokens, int num_heads, int topk, float sm_scale,
+                 int page_block_size, int64_t kv_block_stride_bytes,
+                 const float* attn_sink, const int32_t* topk_length,
+                 int impl, int32_t* status, void* stream);
+
+/*
+ * bf16 -> packed 656-byte rows (the writer of the cache format).  No kernel of the reference
+ * does this; the format is specified by tests/test_decode.py:33-57 (quantize_kv_v32).
+ *   kv_bf16 [num_rows, 576] bf16, packed [num_rows, 656] uint8.
+ */
+int smla_pack_kv(const void* kv_bf16, void* packed, int64_t num_rows, void* stream);
+
+/*
+ * FP8 MQA-logits indexer.  No counterpart in the reference (the indices it consumes come from
+ * an external indexer, flash_mla_sm120/interface.py:39-58).
+ *   logits[i, j] = k_scale[j] * sum_h weights[i, h] * relu(q[i, h, :] . k[j, :]),
+ *   -inf for j outside [ks[i], ke[i]).
+ *   q [s_q, num_heads, 128] e4m3, k [s_k, 128] e4m3, k_scale [s_k] fp32,
+ *   weights [s_q, num_heads] fp32, ks/ke [s_q] int32, logits [s_q, logits_stride] fp32.
+ */
+int smla_mqa_logits(const void* q, const void* k, const float* k_scale, const float* weights,
+                    const int32_t* ks, const int32_t* ke, float* logits,
+                    int s_q, int num_heads, int s_k, int64_t logits_stride,
+                    int impl, int32_t* status, void* stream);
+
+/*
+ * Per-row top-k selection over logits[row, ks[row]:ke[row]) (ks/ke may be NULL = whole row).
+ * Writes k int32 indices per row, unordered, padded with -1 when fewer than k candidates are
+ * finite.  Ties at the threshold are broken towards the lower index.  No counterpart in the
+ * reference.
+ */
+int smla_topk(const float* logits, const int32_t* ks, const int32_t* ke, int32_t* out_indices,
+              int num_rows, int num_cols, int64_t logits_stride, int k, void* stream);
+
+/*
+ * Context-parallel index partition: keeps, in order, the entries of each row that fall in
+ * [lo, hi), rebases them to lo, pads with -1 and writes the count to local_length.  No
+ * counterpart in the reference (it has no multi-GPU path).
+ */
+int smla_cp_partition_indices(const int32_t* indices, int32_t* local_indices, int32_t* local_length,
+                              int num_tokens, int topk, int lo, int hi, void* stream);
+
+/*
+ * Context-parallel local step: split-KV decode over this GPU's shard followed by the local
+ * merge, giving ONE fp32 partial per token (normalised by its own sum) and its base-2 LSE, ready
+ * to be exchanged.  Same arguments as smla_decode_splitkv; o_part [num_tokens, num_heads, 512]
+ * fp32 and lse_part [num_tokens, num_heads] fp32 replace out / out_lse, and no sink is applied
+ * (the sink belongs to the final merge).  No counterpart in the reference.
+ */
+int smla_decode_partial(const void* q, const void* kv, const int32_t* indices,
+                        float* o_accum, float* lse_accum, float* o_part, float* lse_part,
+                        const int32_t* sched_meta, const int32_t* num_splits,
+                        int num_tokens, int num_heads, int topk, float sm_scale,
+                        int page_block_size, int64_t kv_block_stride_bytes, int num_sm_parts,
+                        const int32_t* topk_length, int impl, int32_t* status, void* stream);
+
+/*
+ * Final merge of the context-parallel exchange: o_parts [parts, num_tokens, num_heads, 512] fp32
+ * and lse_parts [parts, num_tokens, num_heads] fp32 (the layout an all-gather of the per-GPU
+ * partials produces) -> out bf16 and base-2 LSE, sink applied if given.  Same arithmetic as
+ * smla_combine (csrc/kernel/combine/combine_kernel.cu:39-159); the strided layout has no
+ * counterpart in the reference.
+ */
+int smla_combine_parts(const float* o_parts, const float* lse_parts, void* out, float* out_lse,
+                       int parts, int num_tokens, int num_heads, const float* attn_sink, void* stream);
+
+/* Bytes of o_accum + lse_accum scratch that smla_decode_splitkv needs. */
+size_t smla_workspace_bytes(int num_tokens, int num_heads, int num_sm_parts);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* SMLA_H_ */

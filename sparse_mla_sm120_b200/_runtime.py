@@ -1,0 +1,127 @@
+"""Host-side glue shared by the op modules: pointers, streams, cached scratch, split policy."""
+from __future__ import annotations
+
+from typing import Dict, Optional, Tuple
+
+import torch
+
+from . import _lib
+
+HEADS_PER_TILE = 128     # one CTA covers every head of a query token
+CTAS_PER_PART = 2        # two CTAs (one per half of d_v) share a partition
+FIXED_OVERHEAD = 5       # scheduler cost of starting a request, in 64-token blocks
+BLOCK_N = 64
+
+_scratch: Dict[Tuple, Dict[str, torch.Tensor]] = {}
+_num_sms: Dict[int, int] = {}
+
+
+def ptr(t: Optional[torch.Tensor]) -> Optional[int]:
+    return None if t is None else t.data_ptr()
+
+
+def stream_ptr(device: torch.device) -> int:
+    return torch.cuda.current_stream(device).cuda_stream
+
+
+def num_sms(device: torch.device) -> int:
+    idx = device.index if device.index is not None else torch.cuda.current_device()
+    if idx not in _num_sms:
+        _num_sms[idx] = torch.cuda.get_device_properties(idx).multi_processor_count
+    return _num_sms[idx]
+
+
+def require_cuda(*tensors: Optional[torch.Tensor]) -> None:
+    for t in tensors:
+        if t is not None and not t.is_cuda:
+            raise ValueError("sparse_mla_sm120_b200 runs on CUDA tensors only (there is no CPU path)")
+
+
+def kv_geometry(kv_cache: torch.Tensor) -> Tuple[int, int]:
+    """(page_block_size, bytes between pages) of a packed cache tensor.
+
+    Accepts [num_blocks, block, 1, 656], the legacy flat [pool, 1, 656] and [pool, 656].  A page
+    stride larger than block*656 (a padded allocation) is honoured; the reference computes the
+    same quantity in flash_mla_sm120/ops.py:23-45 but its V32 gather then ignores it."""
+    if kv_cache.dtype not in (torch.uint8, torch.int8, torch.float8_e4m3fn):
+        raise ValueError(f"kv_cache must be a byte tensor, got {kv_cache.dtype}")
+    if kv_cache.shape[-1] != 656:
+        if kv_cache.shape[-1] == 584:
+            raise NotImplementedError("the 584-byte (MODEL1) cache layout is not built")
+        raise ValueError(f"kv_cache rows must be 656 bytes, got {kv_cache.shape[-1]}")
+    if kv_cache.stride(-1) != 1:
+        raise ValueError("kv_cache rows must be contiguous")
+    if kv_cache.dim() == 4:
+        block = kv_cache.shape[1]
+        if kv_cache.shape[2] != 1 or kv_cache.stride(1) != 656:
+            raise ValueError("kv_cache must be [num_blocks, block, 1, 656] with 656-byte rows")
+        return block, kv_cache.stride(0)
+    if kv_cache.dim() == 3:
+        if kv_cache.shape[1] != 1 or kv_cache.stride(0) != 656:
+            raise ValueError("kv_cache must be [pool, 1, 656] with 656-byte rows")
+        pool = max(kv_cache.shape[0], 1)
+        return pool, pool * 656
+    if kv_cache.dim() == 2:
+        if kv_cache.stride(0) != 656:
+            raise ValueError("kv_cache must be [pool, 656] with 656-byte rows")
+        pool = max(kv_cache.shape[0], 1)
+        return pool, pool * 656
+    raise ValueError(f"unsupported kv_cache rank {kv_cache.dim()}")
+
+
+def pick_num_sm_parts(num_tokens: int, sms: int) -> int:
+    """Partitions for the split-KV scheduler.
+
+    A partition is served by two CTAs, so at most sms // 2 partitions run at once.  When whole
+    requests already fill the machine to >= 80 % in full waves they are left unsplit (one
+    partition per token: no partial outputs, no combine traffic); otherwise the work is cut into
+    sms // 2 equal partitions."""
+    max_parts = max(sms // CTAS_PER_PART, 1)
+    ctas = num_tokens * CTAS_PER_PART
+    waves = -(-ctas // sms)
+    if ctas / (waves * sms) >= 0.8:
+        return num_tokens
+    return max_parts
+
+
+def scratch(device: torch.device, total_splits: int, num_heads: int, num_tokens: int, num_parts: int):
+    """Cached scratch for one decode call shape (the reference allocates these on every call,
+    flash_mla_sm120/ops.py:78-99)."""
+    key = (device.index, total_splits, num_heads, num_tokens, num_parts)
+    ws = _scratch.get(key)
+    if ws is None:
+        ws = {
+            "o_accum": torch.empty((total_splits, 1, num_heads, 512), dtype=torch.float32, device=device),
+            "lse_accum": torch.empty((total_splits, 1, num_heads), dtype=torch.float32, device=device),
+            "sched_meta": torch.empty(num_parts * 8, dtype=torch.int32, device=device),
+            "num_splits": torch.empty(num_tokens + 1, dtype=torch.int32, device=device),
+            "status": torch.zeros(4, dtype=torch.int32, device=device),
+        }
+        if len(_scratch) > 64:
+            _scratch.clear()
+        _scratch[key] = ws
+    return ws
+
+
+_status: Dict[int, torch.Tensor] = {}
+
+
+def status_buffer(device: torch.device) -> torch.Tensor:
+    idx = device.index if device.index is not None else torch.cuda.current_device()
+    if idx not in _status:
+        _status[idx] = torch.zeros(4, dtype=torch.int32, device=device)
+    return _status[idx]
+
+
+def check_status(device: Optional[torch.device] = None) -> None:
+    """Synchronises and raises if a kernel recorded a bounded wait that gave up.  Not called on
+    the hot path (it reads device memory); tests and the benchmark call it."""
+    if device is None:
+        device = torch.device("cuda", torch.cuda.current_device())
+    st = status_buffer(device)
+    vals = st.tolist()
+    if vals[0] != 0:
+        st.zero_()
+        names = {1: "empty", 2: "full", 3: "s_ready", 4: "p_ready", 5: "pv_done", 6: "q_ready"}
+        raise _lib.SmlaError(f"kernel wait gave up: barrier={names.get(vals[0], vals[0])} "
+                             f"ctas={vals[1]} last_cta={vals[2]}")

@@ -1,0 +1,115 @@
+"""Multi-GPU paths: one process per GPU, torch.distributed (NCCL over NVLink) for the exchange.
+
+The reference has no multi-GPU code.  Two shardings are offered:
+
+* decode batches shard by sequence: every rank calls ``flash_ops.sparse_mla_decode_fwd`` on its
+  own requests, nothing is exchanged (``shard_requests`` gives the slice of a rank);
+* long-context decode shards the KV context: rank g holds rows [g*L/G, (g+1)*L/G) of every
+  sequence.  Each rank keeps the entries of the global index list that fall into its shard
+  (``partition_indices``), runs split-KV decode over them to one fp32 partial + base-2 LSE per
+  token, the partials are all-gathered and merged with the same LSE-weighted combine that merges
+  split-KV partials (``sparse_mla_decode_cp_fwd``).  A token with no entry on a rank contributes
+  LSE = -1e30 and drops out of the merge exactly.
+"""
+from __future__ import annotations
+
+from typing import Dict, Optional, Tuple
+
+import torch
+
+from . import _lib
+from ._lib import IMPL_AUTO, check
+from ._runtime import (FIXED_OVERHEAD, kv_geometry, num_sms, pick_num_sm_parts, ptr, require_cuda, scratch,
+                       status_buffer, stream_ptr)
+
+
+def shard_requests(num_requests: int, rank: int, world: int) -> Tuple[int, int]:
+    """[begin, end) of the requests rank serves when a decode batch is sharded by sequence."""
+    per, rem = divmod(num_requests, world)
+    begin = rank * per + min(rank, rem)
+    return begin, begin + per + (1 if rank < rem else 0)
+
+
+def shard_context(context_len: int, rank: int, world: int, align: int = 64) -> Tuple[int, int]:
+    """[lo, hi) of the token positions rank holds; shards are contiguous and page aligned."""
+    per = -(-context_len // world)
+    per = -(-per // align) * align
+    lo = min(rank * per, context_len)
+    return lo, min(lo + per, context_len)
+
+
+def partition_indices(indices: torch.Tensor, lo: int, hi: int) -> Tuple[torch.Tensor, torch.Tensor]:
+    """Stable compaction of the entries of each row inside [lo, hi), rebased to lo, -1 padded.
+    Returns (local_indices [T, topk] int32, local_length [T] int32)."""
+    require_cuda(indices)
+    assert indices.dim() == 2 and indices.dtype == torch.int32 and indices.is_contiguous()
+    T, topk = indices.shape
+    local = torch.empty_like(indices)
+    length = torch.empty(T, dtype=torch.int32, device=indices.device)
+    check(_lib.load().smla_cp_partition_indices(ptr(indices), ptr(local), ptr(length), T, topk, lo, hi,
+                                                stream_ptr(indices.device)))
+    return local, length
+
+
+_gather_bufs: Dict[Tuple, Tuple[torch.Tensor, torch.Tensor]] = {}
+
+
+def _gather_buffers(device, world, T, H):
+    key = (device.index, world, T, H)
+    if key not in _gather_bufs:
+        _gather_bufs[key] = (torch.empty((world, T, H, 512), dtype=torch.float32, device=device),
+                             torch.empty((world, T, H), dtype=torch.float32, device=device))
+    return _gather_bufs[key]
+
+
+def decode_partial(q, kv_local, local_indices, local_length, sm_scale, o_part=None, lse_part=None,
+                   impl: int = IMPL_AUTO, num_sm_parts: Optional[int] = None):
+    """Local step: fp32 partial [T, H, 512] and base-2 LSE [T, H] over this rank's entries."""
+    require_cuda(q, kv_local, local_indices, local_length)
+    T, H, _ = q.shape
+    topk = local_indices.shape[-1]
+    pbs, stride = kv_geometry(kv_local)
+    if num_sm_parts is None:
+        num_sm_parts = pick_num_sm_parts(T, num_sms(q.device))
+    ws = scratch(q.device, T + num_sm_parts, H, T, num_sm_parts)
+    if o_part is None:
+        o_part = torch.empty((T, H, 512), dtype=torch.float32, device=q.device)
+        lse_part = torch.empty((T, H), dtype=torch.float32, device=q.device)
+    lib, stream = _lib.load(), stream_ptr(q.device)
+    check(lib.smla_sched_meta(T, topk, 0, num_sm_parts, FIXED_OVERHEAD, ptr(local_length), None,
+                              ptr(ws["sched_meta"]), ptr(ws["num_splits"]), stream))
+    check(lib.smla_decode_partial(ptr(q), ptr(kv_local), ptr(local_indices), ptr(ws["o_accum"]),
+                                  ptr(ws["lse_accum"]), ptr(o_part), ptr(lse_part), ptr(ws["sched_meta"]),
+                                  ptr(ws["num_splits"]), T, H, topk, float(sm_scale), pbs, stride, num_sm_parts,
+                                  ptr(local_length), impl, ptr(status_buffer(q.device)), stream))
+    return o_part, lse_part
+
+
+def combine_parts(o_parts, lse_parts, attn_sink=None, out=None):
+    """Merge [G, T, H, 512] fp32 partials and [G, T, H] base-2 LSEs -> (out bf16, lse)."""
+    require_cuda(o_parts, lse_parts)
+    G, T, H, _ = o_parts.shape
+    if out is None:
+        out = torch.empty((T, H, 512), dtype=torch.bfloat16, device=o_parts.device)
+    lse = torch.empty((T, H), dtype=torch.float32, device=o_parts.device)
+    check(_lib.load().smla_combine_parts(ptr(o_parts), ptr(lse_parts), ptr(out), ptr(lse), G, T, H,
+                                         ptr(attn_sink), stream_ptr(o_parts.device)))
+    return out, lse
+
+
+def sparse_mla_decode_cp_fwd(q, kv_local, indices, sm_scale, shard_lo: int, shard_hi: int, group=None,
+                             attn_sink=None, impl: int = IMPL_AUTO):
+    """Context-parallel decode.  ``indices`` [T, topk] are global row numbers of the full context
+    (identical on every rank), ``kv_local`` holds rows [shard_lo, shard_hi) of it.
+    Returns (out [T, H, 512] bf16, lse [T, H] fp32 base-2), identical on every rank."""
+    import torch.distributed as dist
+    world = dist.get_world_size(group) if dist.is_initialized() else 1
+    rank = dist.get_rank(group) if dist.is_initialized() else 0
+    T, H, _ = q.shape
+    local_idx, local_len = partition_indices(indices, shard_lo, shard_hi)
+    o_all, lse_all = _gather_buffers(q.device, world, T, H)
+    decode_partial(q, kv_local, local_idx, local_len, sm_scale, o_all[rank], lse_all[rank], impl=impl)
+    if world > 1:
+        dist.all_gather_into_tensor(o_all, o_all[rank], group=group)
+        dist.all_gather_into_tensor(lse_all, lse_all[rank], group=group)
+    return combine_parts(o_all, lse_all, attn_sink)

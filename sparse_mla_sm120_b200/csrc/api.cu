@@ -1,0 +1,221 @@
+// extern "C" entry points of libsmla_b200.so: argument checks, error strings, dispatch.
+// No torch types, no allocation, no host synchronisation.
+#include <cstdarg>
+#include <cstdio>
+
+#include "common.cuh"
+
+namespace smla {
+
+static thread_local char g_err[512] = "";
+
+int set_error(int code, const char* fmt, ...) {
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(g_err, sizeof(g_err), fmt, ap);
+    va_end(ap);
+    return code;
+}
+
+int check_launch(const char* what) {
+    const cudaError_t e = cudaGetLastError();
+    if (e == cudaSuccess) return 0;
+    return set_error((int)e, "%s: launch failed: %s", what, cudaGetErrorString(e));
+}
+
+static bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+static int check_attn_common(const char* fn, const void* q, const void* kv, const int32_t* indices,
+                             const void* out, const float* out_lse, int num_tokens, int num_heads, int topk,
+                             int page_block_size, int64_t stride, int impl) {
+    if (!q || !kv || !indices || !out || !out_lse) return set_error(SMLA_E_NULL, "%s: null pointer argument", fn);
+    if (num_tokens < 0) return set_error(SMLA_E_SHAPE, "%s: num_tokens=%d", fn, num_tokens);
+    if (num_heads < 1 || num_heads > 128)
+        return set_error(SMLA_E_SHAPE, "%s: num_heads=%d, supported 1..128", fn, num_heads);
+    if (topk < 1) return set_error(SMLA_E_SHAPE, "%s: topk=%d", fn, topk);
+    if (page_block_size < 1) return set_error(SMLA_E_SHAPE, "%s: page_block_size=%d", fn, page_block_size);
+    if (!aligned16(q) || !aligned16(kv) || !aligned16(out) || (stride & 15))
+        return set_error(SMLA_E_ALIGN, "%s: q, kv, out and the page stride must be 16-byte aligned", fn);
+    if (stride < (int64_t)page_block_size * ROW_BYTES)
+        return set_error(SMLA_E_SHAPE, "%s: page stride %lld smaller than %d rows of %d bytes", fn,
+                         (long long)stride, page_block_size, ROW_BYTES);
+    if (impl != SMLA_IMPL_AUTO && impl != SMLA_IMPL_SCALAR && impl != SMLA_IMPL_TC)
+        return set_error(SMLA_E_SHAPE, "%s: unknown impl %d", fn, impl);
+    return 0;
+}
+
+}  // namespace smla
+
+using namespace smla;
+
+extern "C" {
+
+const char* smla_last_error(void) { return g_err; }
+int smla_version(void) { return 100; }
+
+int smla_num_sms(void) {
+    static int cache[64] = {};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess) return set_error(SMLA_E_DEVICE, "smla_num_sms: no CUDA device");
+    if (dev < 64 && cache[dev]) return cache[dev];
+    int n = 0;
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess)
+        return set_error(SMLA_E_DEVICE, "smla_num_sms: attribute query failed");
+    if (dev < 64) cache[dev] = n;
+    return n;
+}
+
+size_t smla_workspace_bytes(int num_tokens, int num_heads, int num_sm_parts) {
+    const size_t splits = (size_t)num_tokens + (size_t)num_sm_parts;
+    return splits * num_heads * (D_V + 1) * sizeof(float);
+}
+
+int smla_sched_meta(int b, int topk, int extra_topk, int num_sm_parts, int fixed_overhead,
+                    const int32_t* topk_length, const int32_t* extra_topk_length,
+                    int32_t* sched_meta, int32_t* num_splits, void* stream) {
+    if (!sched_meta || !num_splits) return set_error(SMLA_E_NULL, "smla_sched_meta: null output");
+    if (b < 1 || b > 8192) return set_error(SMLA_E_SHAPE, "smla_sched_meta: b=%d, supported 1..8192", b);
+    if (num_sm_parts < 1) return set_error(SMLA_E_SHAPE, "smla_sched_meta: num_sm_parts=%d", num_sm_parts);
+    if (topk < 0 || extra_topk < 0 || fixed_overhead < 0)
+        return set_error(SMLA_E_SHAPE, "smla_sched_meta: negative size");
+    return launch_sched_meta(b, topk, extra_topk, num_sm_parts, fixed_overhead, topk_length,
+                             extra_topk_length, sched_meta, num_splits, (cudaStream_t)stream);
+}
+
+int smla_decode_splitkv(const void* q, const void* kv, const int32_t* indices,
+                        float* o_accum, float* lse_accum, void* out, float* out_lse,
+                        const int32_t* sched_meta, const int32_t* num_splits,
+                        int num_tokens, int num_heads, int topk, float sm_scale,
+                        int page_block_size, int64_t kv_block_stride_bytes, int num_sm_parts,
+                        const float* attn_sink, const int32_t* topk_length,
+                        int impl, int32_t* status, void* stream) {
+    if (int e = check_attn_common("smla_decode_splitkv", q, kv, indices, out, out_lse, num_tokens, num_heads,
+                                  topk, page_block_size, kv_block_stride_bytes, impl)) return e;
+    if (!o_accum || !lse_accum || !sched_meta || !num_splits)
+        return set_error(SMLA_E_NULL, "smla_decode_splitkv: null scratch or scheduler pointer");
+    if (!aligned16(o_accum)) return set_error(SMLA_E_ALIGN, "smla_decode_splitkv: o_accum not 16-byte aligned");
+    if (num_sm_parts < 1) return set_error(SMLA_E_SHAPE, "smla_decode_splitkv: num_sm_parts=%d", num_sm_parts);
+    AttnParams p{};
+    p.q = (const __nv_bfloat16*)q; p.kv = (const uint8_t*)kv; p.indices = indices;
+    p.o_accum = o_accum; p.lse_accum = lse_accum; p.out = (__nv_bfloat16*)out; p.out_lse = out_lse;
+    p.out_max_logits = nullptr; p.sched = (const SchedMeta*)sched_meta; p.num_splits = num_splits;
+    p.attn_sink = attn_sink; p.topk_length = topk_length; p.status = status;
+    p.num_tokens = num_tokens; p.num_heads = num_heads; p.topk = topk; p.num_parts = num_sm_parts;
+    p.page_block_size = page_block_size; p.block_stride = kv_block_stride_bytes; p.sm_scale = sm_scale;
+    if (impl == SMLA_IMPL_SCALAR) return launch_attn_scalar(p, (cudaStream_t)stream);
+    return launch_attn_tc(p, (cudaStream_t)stream);
+}
+
+int smla_combine(const float* o_accum, const float* lse_accum, void* out, float* out_lse,
+                 const int32_t* num_splits, int batch, int num_heads, int max_nsplits,
+                 const float* attn_sink, void* stream) {
+    if (!o_accum || !lse_accum || !out || !out_lse || !num_splits)
+        return set_error(SMLA_E_NULL, "smla_combine: null pointer argument");
+    if (batch < 0 || num_heads < 1) return set_error(SMLA_E_SHAPE, "smla_combine: batch=%d heads=%d", batch, num_heads);
+    if (max_nsplits > 1024) return set_error(SMLA_E_SHAPE, "smla_combine: max_nsplits=%d exceeds 1024", max_nsplits);
+    if (!aligned16(o_accum) || !aligned16(out)) return set_error(SMLA_E_ALIGN, "smla_combine: unaligned buffer");
+    return launch_combine(o_accum, lse_accum, (__nv_bfloat16*)out, out_lse, num_splits, batch, num_heads,
+                          max_nsplits, attn_sink, (cudaStream_t)stream);
+}
+
+int smla_decode_partial(const void* q, const void* kv, const int32_t* indices,
+                        float* o_accum, float* lse_accum, float* o_part, float* lse_part,
+                        const int32_t* sched_meta, const int32_t* num_splits,
+                        int num_tokens, int num_heads, int topk, float sm_scale,
+                        int page_block_size, int64_t kv_block_stride_bytes, int num_sm_parts,
+                        const int32_t* topk_length, int impl, int32_t* status, void* stream) {
+    if (int e = check_attn_common("smla_decode_partial", q, kv, indices, o_part, lse_part, num_tokens, num_heads,
+                                  topk, page_block_size, kv_block_stride_bytes, impl)) return e;
+    if (!o_accum || !lse_accum || !sched_meta || !num_splits)
+        return set_error(SMLA_E_NULL, "smla_decode_partial: null scratch or scheduler pointer");
+    if (!aligned16(o_accum)) return set_error(SMLA_E_ALIGN, "smla_decode_partial: o_accum not 16-byte aligned");
+    if (num_sm_parts < 1) return set_error(SMLA_E_SHAPE, "smla_decode_partial: num_sm_parts=%d", num_sm_parts);
+    AttnParams p{};
+    p.q = (const __nv_bfloat16*)q; p.kv = (const uint8_t*)kv; p.indices = indices;
+    p.o_accum = o_accum; p.lse_accum = lse_accum; p.out = nullptr; p.out_lse = nullptr;
+    p.sched = (const SchedMeta*)sched_meta; p.num_splits = num_splits;
+    p.topk_length = topk_length; p.status = status;
+    p.num_tokens = num_tokens; p.num_heads = num_heads; p.topk = topk; p.num_parts = num_sm_parts;
+    p.force_partial = 1;
+    p.page_block_size = page_block_size; p.block_stride = kv_block_stride_bytes; p.sm_scale = sm_scale;
+    const int e = (impl == SMLA_IMPL_SCALAR) ? launch_attn_scalar(p, (cudaStream_t)stream)
+                                             : launch_attn_tc(p, (cudaStream_t)stream);
+    if (e) return e;
+    return launch_combine_f32(o_accum, lse_accum, o_part, lse_part, num_splits, num_tokens, num_heads,
+                              (cudaStream_t)stream);
+}
+
+int smla_combine_parts(const float* o_parts, const float* lse_parts, void* out, float* out_lse,
+                       int parts, int num_tokens, int num_heads, const float* attn_sink, void* stream) {
+    if (!o_parts || !lse_parts || !out || !out_lse)
+        return set_error(SMLA_E_NULL, "smla_combine_parts: null pointer argument");
+    if (parts < 1 || num_tokens < 0 || num_heads < 1)
+        return set_error(SMLA_E_SHAPE, "smla_combine_parts: parts=%d tokens=%d heads=%d", parts, num_tokens, num_heads);
+    if (!aligned16(o_parts) || !aligned16(out)) return set_error(SMLA_E_ALIGN, "smla_combine_parts: unaligned buffer");
+    return launch_combine_parts(o_parts, lse_parts, (__nv_bfloat16*)out, out_lse, parts, num_tokens, num_heads,
+                                attn_sink, (cudaStream_t)stream);
+}
+
+int smla_prefill(const void* q, const void* kv, const int32_t* indices,
+                 void* out, float* out_lse, float* out_max_logits,
+                 int num_tokens, int num_heads, int topk, float sm_scale,
+                 int page_block_size, int64_t kv_block_stride_bytes,
+                 const float* attn_sink, const int32_t* topk_length,
+                 int impl, int32_t* status, void* stream) {
+    if (int e = check_attn_common("smla_prefill", q, kv, indices, out, out_lse, num_tokens, num_heads, topk,
+                                  page_block_size, kv_block_stride_bytes, impl)) return e;
+    AttnParams p{};
+    p.q = (const __nv_bfloat16*)q; p.kv = (const uint8_t*)kv; p.indices = indices;
+    p.out = (__nv_bfloat16*)out; p.out_lse = out_lse; p.out_max_logits = out_max_logits;
+    p.attn_sink = attn_sink; p.topk_length = topk_length; p.status = status;
+    p.num_tokens = num_tokens; p.num_heads = num_heads; p.topk = topk; p.num_parts = num_tokens;
+    p.page_block_size = page_block_size; p.block_stride = kv_block_stride_bytes; p.sm_scale = sm_scale;
+    if (impl == SMLA_IMPL_SCALAR) return launch_attn_scalar(p, (cudaStream_t)stream);
+    return launch_attn_tc(p, (cudaStream_t)stream);
+}
+
+int smla_pack_kv(const void* kv_bf16, void* packed, int64_t num_rows, void* stream) {
+    if (!kv_bf16 || !packed) return set_error(SMLA_E_NULL, "smla_pack_kv: null pointer argument");
+    if (num_rows < 0) return set_error(SMLA_E_SHAPE, "smla_pack_kv: num_rows=%lld", (long long)num_rows);
+    if (!aligned16(kv_bf16) || !aligned16(packed)) return set_error(SMLA_E_ALIGN, "smla_pack_kv: unaligned buffer");
+    return launch_pack_kv((const __nv_bfloat16*)kv_bf16, (uint8_t*)packed, num_rows, (cudaStream_t)stream);
+}
+
+int smla_mqa_logits(const void* q, const void* k, const float* k_scale, const float* weights,
+                    const int32_t* ks, const int32_t* ke, float* logits,
+                    int s_q, int num_heads, int s_k, int64_t logits_stride,
+                    int impl, int32_t* status, void* stream) {
+    if (!q || !k || !k_scale || !weights || !ks || !ke || !logits)
+        return set_error(SMLA_E_NULL, "smla_mqa_logits: null pointer argument");
+    if (s_q < 0 || s_k < 0 || num_heads < 1 || num_heads > 64)
+        return set_error(SMLA_E_SHAPE, "smla_mqa_logits: s_q=%d s_k=%d heads=%d (heads 1..64)", s_q, s_k, num_heads);
+    if (logits_stride < s_k) return set_error(SMLA_E_SHAPE, "smla_mqa_logits: logits_stride < s_k");
+    if (!aligned16(q) || !aligned16(k)) return set_error(SMLA_E_ALIGN, "smla_mqa_logits: q and k must be 16-byte aligned");
+    if (impl == SMLA_IMPL_SCALAR)
+        return launch_mqa_logits_scalar((const uint8_t*)q, (const uint8_t*)k, k_scale, weights, ks, ke, logits,
+                                        s_q, num_heads, s_k, logits_stride, (cudaStream_t)stream);
+    return launch_mqa_logits_tc((const uint8_t*)q, (const uint8_t*)k, k_scale, weights, ks, ke, logits, s_q,
+                                num_heads, s_k, logits_stride, status, (cudaStream_t)stream);
+}
+
+int smla_topk(const float* logits, const int32_t* ks, const int32_t* ke, int32_t* out_indices,
+              int num_rows, int num_cols, int64_t logits_stride, int k, void* stream) {
+    if (!logits || !out_indices) return set_error(SMLA_E_NULL, "smla_topk: null pointer argument");
+    if (num_rows < 0 || num_cols < 0 || k < 0 || logits_stride < num_cols)
+        return set_error(SMLA_E_SHAPE, "smla_topk: rows=%d cols=%d k=%d stride=%lld", num_rows, num_cols, k,
+                         (long long)logits_stride);
+    return launch_topk(logits, ks, ke, out_indices, num_rows, num_cols, logits_stride, k, (cudaStream_t)stream);
+}
+
+int smla_cp_partition_indices(const int32_t* indices, int32_t* local_indices, int32_t* local_length,
+                              int num_tokens, int topk, int lo, int hi, void* stream) {
+    if (!indices || !local_indices || !local_length)
+        return set_error(SMLA_E_NULL, "smla_cp_partition_indices: null pointer argument");
+    if (num_tokens < 0 || topk < 0 || hi < lo)
+        return set_error(SMLA_E_SHAPE, "smla_cp_partition_indices: tokens=%d topk=%d range=[%d,%d)", num_tokens,
+                         topk, lo, hi);
+    return launch_cp_partition(indices, local_indices, local_length, num_tokens, topk, lo, hi,
+                               (cudaStream_t)stream);
+}
+
+}  // extern "C"

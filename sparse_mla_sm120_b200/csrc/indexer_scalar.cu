@@ -1,0 +1,212 @@
+// MQA-logits indexer, CUDA-core version, top-k selection and context-parallel index partition.
+//
+// None of the three has a counterpart in the reference project (its indices come from an
+// external indexer and it has no multi-GPU path); they implement
+//   logits[i, j] = k_scale[j] * sum_h w[i, h] * relu(q[i, h, :] . k[j, :]),  -inf outside [ks_i, ke_i)
+// followed by a per-row top-k, and the split of a global index list into one GPU's shard.
+#include "common.cuh"
+
+namespace smla {
+
+namespace {
+
+// ---------------------------------------------------------------- logits, fp32 CUDA cores
+// One CTA = (128 keys, one query).  Two threads per key, each holding half of the key's 128
+// values in registers; q of the query sits in shared memory as fp32.
+constexpr int LK = 128;   // keys per CTA
+constexpr int LD = 128;   // head dim of the indexer
+
+__global__ void __launch_bounds__(256)
+mqa_logits_scalar_kernel(const uint8_t* __restrict__ q, const uint8_t* __restrict__ k,
+                         const float* __restrict__ k_scale, const float* __restrict__ weights,
+                         const int32_t* __restrict__ ks, const int32_t* __restrict__ ke,
+                         float* __restrict__ logits, int num_heads, int s_k, int64_t logits_stride) {
+    extern __shared__ float qs[];  // [num_heads][LD]
+    const int i = blockIdx.y;
+    const int j = blockIdx.x * LK + (threadIdx.x >> 1);
+    const int half = threadIdx.x & 1;
+    for (int e = threadIdx.x; e < num_heads * LD; e += blockDim.x)
+        qs[e] = e4m3_to_float(q[(size_t)i * num_heads * LD + e]);
+    float kr[LD / 2];
+    if (j < s_k) {
+#pragma unroll
+        for (int d = 0; d < LD / 2; ++d) kr[d] = e4m3_to_float(k[(size_t)j * LD + half * (LD / 2) + d]);
+    } else {
+#pragma unroll
+        for (int d = 0; d < LD / 2; ++d) kr[d] = 0.f;
+    }
+    __syncthreads();
+    float acc = 0.f;
+    for (int h = 0; h < num_heads; ++h) {
+        const float* qh = qs + h * LD + half * (LD / 2);
+        float s = 0.f;
+#pragma unroll
+        for (int d = 0; d < LD / 2; ++d) s += qh[d] * kr[d];
+        s += __shfl_xor_sync(0xffffffffu, s, 1);
+        acc += weights[(size_t)i * num_heads + h] * fmaxf(s, 0.f);
+    }
+    if (half == 0 && j < s_k) {
+        const bool in = (j >= ks[i]) && (j < ke[i]);
+        logits[(size_t)i * logits_stride + j] = in ? acc * k_scale[j] : -INFINITY;
+    }
+}
+
+// ---------------------------------------------------------------- top-k: radix select per row
+constexpr int TK_THREADS = 512;
+
+__device__ __forceinline__ uint32_t order_key(float f) {   // larger float <=> larger key
+    const uint32_t b = __float_as_uint(f);
+    return (b & 0x80000000u) ? ~b : (b | 0x80000000u);
+}
+
+__global__ void __launch_bounds__(TK_THREADS)
+topk_kernel(const float* __restrict__ logits, const int32_t* __restrict__ ks,
+            const int32_t* __restrict__ ke, int32_t* __restrict__ out, int num_cols,
+            int64_t logits_stride, int k) {
+    __shared__ int hist[256];
+    __shared__ int sel_bin, sel_need;
+    __shared__ int warp_gt[TK_THREADS / 32], warp_eq[TK_THREADS / 32];
+    __shared__ int base_gt, base_eq;
+
+    const int row = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const float* x = logits + (size_t)row * logits_stride;
+    int lo = ks ? max(ks[row], 0) : 0;
+    int hi = ke ? min(ke[row], num_cols) : num_cols;
+    if (hi < lo) hi = lo;
+    int32_t* o = out + (size_t)row * k;
+    const uint32_t NEG_INF_KEY = order_key(-INFINITY);
+
+    // Pass 0..3: find the key of the k-th largest candidate (candidates: finite-or-+inf, > -inf).
+    uint32_t prefix = 0, prefix_mask = 0;
+    int need = k;           // how many still to take among keys matching the prefix
+    bool take_all = false;
+    for (int pass = 0; pass < 4; ++pass) {
+        const int shift = 24 - 8 * pass;
+        for (int b = tid; b < 256; b += TK_THREADS) hist[b] = 0;
+        __syncthreads();
+        for (int j = lo + tid; j < hi; j += TK_THREADS) {
+            const uint32_t key = order_key(x[j]);
+            if (key > NEG_INF_KEY && (key & prefix_mask) == prefix) atomicAdd(&hist[(key >> shift) & 255], 1);
+        }
+        __syncthreads();
+        if (tid == 0) {
+            int cum = 0, b = 255;
+            for (; b >= 0; --b) {
+                if (cum + hist[b] >= need) break;
+                cum += hist[b];
+            }
+            sel_bin = b;            // -1: fewer candidates than needed
+            sel_need = need - cum;
+        }
+        __syncthreads();
+        if (sel_bin < 0) { take_all = true; break; }
+        prefix |= (uint32_t)sel_bin << shift;
+        prefix_mask |= 255u << shift;
+        need = sel_need;
+        __syncthreads();
+    }
+    const uint32_t thr = take_all ? NEG_INF_KEY : prefix;   // take keys > thr, plus `need` keys == thr
+    const int need_eq = take_all ? 0 : need;
+
+    // Ordered compaction: output positions follow the column order, ties go to lower columns.
+    if (tid == 0) { base_gt = 0; base_eq = 0; }
+    __syncthreads();
+    // First count how many are strictly greater, so that the ties can be placed after them
+    // without a second scan: positions [0, n_gt) hold the greater ones, [n_gt, n_gt+need_eq) the ties.
+    if (tid == 0) hist[0] = 0;
+    __syncthreads();
+    int n_gt_local = 0;
+    for (int j = lo + tid; j < hi; j += TK_THREADS) n_gt_local += (order_key(x[j]) > thr);
+    n_gt_local = __reduce_add_sync(0xffffffffu, n_gt_local);
+    if (lane == 0) atomicAdd(&hist[0], n_gt_local);
+    __syncthreads();
+    const int n_gt = hist[0];
+
+    for (int j0 = lo; j0 < hi; j0 += TK_THREADS) {
+        const int j = j0 + tid;
+        uint32_t key = NEG_INF_KEY;
+        if (j < hi) key = order_key(x[j]);
+        const bool gt = key > thr;
+        const bool eq = (!take_all) && key == thr;
+        const uint32_t mg = __ballot_sync(0xffffffffu, gt), me = __ballot_sync(0xffffffffu, eq);
+        if (lane == 0) { warp_gt[warp] = __popc(mg); warp_eq[warp] = __popc(me); }
+        __syncthreads();
+        int off_gt = base_gt, off_eq = base_eq;
+        for (int w = 0; w < warp; ++w) { off_gt += warp_gt[w]; off_eq += warp_eq[w]; }
+        const uint32_t below = (1u << lane) - 1u;
+        if (gt) o[off_gt + __popc(mg & below)] = j;
+        if (eq) {
+            const int r = off_eq + __popc(me & below);
+            if (r < need_eq) o[n_gt + r] = j;
+        }
+        __syncthreads();
+        if (tid == 0) {
+            int tg = 0, te = 0;
+            for (int w = 0; w < TK_THREADS / 32; ++w) { tg += warp_gt[w]; te += warp_eq[w]; }
+            base_gt += tg; base_eq += te;
+        }
+        __syncthreads();
+    }
+    const int filled = n_gt + (take_all ? 0 : min(need_eq, base_eq));
+    for (int r = filled + tid; r < k; r += TK_THREADS) o[r] = -1;
+}
+
+// ---------------------------------------------------------------- context-parallel partition
+// One warp per row: stable compaction of the entries inside [lo, hi), rebased to lo.
+__global__ void __launch_bounds__(256)
+cp_partition_kernel(const int32_t* __restrict__ indices, int32_t* __restrict__ local_indices,
+                    int32_t* __restrict__ local_length, int num_tokens, int topk, int lo, int hi) {
+    const int lane = threadIdx.x & 31;
+    const int row = blockIdx.x * 8 + (threadIdx.x >> 5);
+    if (row >= num_tokens) return;
+    const int32_t* in = indices + (size_t)row * topk;
+    int32_t* o = local_indices + (size_t)row * topk;
+    int n = 0;
+    for (int j0 = 0; j0 < topk; j0 += 32) {
+        const int j = j0 + lane;
+        const int v = (j < topk) ? in[j] : -1;
+        const bool keep = (v >= lo) && (v < hi);
+        const uint32_t m = __ballot_sync(0xffffffffu, keep);
+        if (keep) o[n + __popc(m & ((1u << lane) - 1u))] = v - lo;
+        n += __popc(m);
+    }
+    for (int j = n + lane; j < topk; j += 32) o[j] = -1;
+    if (lane == 0) local_length[row] = n;
+}
+
+}  // namespace
+
+int launch_mqa_logits_scalar(const uint8_t* q, const uint8_t* k, const float* k_scale, const float* weights,
+                             const int32_t* ks, const int32_t* ke, float* logits, int s_q, int num_heads,
+                             int s_k, int64_t logits_stride, cudaStream_t stream) {
+    if (s_q == 0 || s_k == 0) return 0;
+    const size_t smem = (size_t)num_heads * LD * sizeof(float);
+    static bool attr_set[64] = {};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (smem > 48 * 1024 && dev < 64 && !attr_set[dev]) {
+        cudaFuncSetAttribute(mqa_logits_scalar_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 128 * 1024);
+        attr_set[dev] = true;
+    }
+    dim3 grid((s_k + LK - 1) / LK, s_q);
+    mqa_logits_scalar_kernel<<<grid, 256, smem, stream>>>(q, k, k_scale, weights, ks, ke, logits, num_heads,
+                                                        s_k, logits_stride);
+    return check_launch("mqa_logits_scalar_kernel");
+}
+
+int launch_topk(const float* logits, const int32_t* ks, const int32_t* ke, int32_t* out, int num_rows,
+                int num_cols, int64_t logits_stride, int k, cudaStream_t stream) {
+    if (num_rows == 0 || k == 0) return 0;
+    topk_kernel<<<num_rows, TK_THREADS, 0, stream>>>(logits, ks, ke, out, num_cols, logits_stride, k);
+    return check_launch("topk_kernel");
+}
+
+int launch_cp_partition(const int32_t* indices, int32_t* local_indices, int32_t* local_length,
+                        int num_tokens, int topk, int lo, int hi, cudaStream_t stream) {
+    if (num_tokens == 0) return 0;
+    cp_partition_kernel<<<(num_tokens + 7) / 8, 256, 0, stream>>>(indices, local_indices, local_length,
+                                                                  num_tokens, topk, lo, hi);
+    return check_launch("cp_partition_kernel");
+}
+
+}  // namespace smla

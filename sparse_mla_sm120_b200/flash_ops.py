@@ -1,0 +1,207 @@
+"""The current op surface of the reference (flash_mla_sm120/ops.py:48-165), on B200 kernels.
+
+Same names, argument order, argument meaning and return tuples; the raw entry points that the
+reference exposes as ``flash_mla_sm120.cuda`` (csrc/binding.cpp:250-292) are the functions
+``get_decode_metadata``, ``sparse_mla_splitkv_v2_fwd``, ``sparse_mla_combine_v2_fwd`` and
+``sparse_mla_prefill_raw`` below.  Arguments that belong to the 584-byte MODEL1 layout or to the
+second ("extra") cache raise NotImplementedError.
+"""
+from __future__ import annotations
+
+from typing import Optional, Tuple
+
+import torch
+
+from . import _lib
+from ._lib import IMPL_AUTO, check
+from ._runtime import (BLOCK_N, FIXED_OVERHEAD, kv_geometry, num_sms, pick_num_sm_parts, ptr, require_cuda,
+                       scratch, status_buffer, stream_ptr)
+
+
+def _effective_stride_kv_row(kv_cache: torch.Tensor) -> int:
+    """Per-token byte stride such that block * stride == the page stride.
+
+    Mirrors flash_mla_sm120/ops.py:23-45 for callers that use it; the kernels here take the
+    page stride itself (see _runtime.kv_geometry)."""
+    if kv_cache.dim() < 3:
+        return kv_cache.stride(-2) * kv_cache.element_size()
+    page_block_size = kv_cache.shape[-3]
+    natural = kv_cache.stride(-2) * kv_cache.element_size()
+    block_stride = kv_cache.stride(0) * kv_cache.element_size()
+    if block_stride == page_block_size * natural:
+        return natural
+    assert block_stride % page_block_size == 0, (
+        f"kv_cache block stride {block_stride} not divisible by page_block_size {page_block_size}")
+    return block_stride // page_block_size
+
+
+def _reject_extra(extra_k_cache, extra_indices, extra_topk_length, extra_topk):
+    if extra_k_cache is not None or extra_indices is not None or extra_topk_length is not None or extra_topk:
+        raise NotImplementedError("the second (extra) KV cache of the MODEL1 layout is not built")
+
+
+def _check_q(q: torch.Tensor):
+    if q.dim() != 3:
+        raise ValueError(f"q must be [num_tokens, num_heads, d_qk], got {tuple(q.shape)}")
+    if q.dtype != torch.bfloat16:
+        raise ValueError(f"q must be bf16, got {q.dtype}")
+    if q.shape[-1] == 512:
+        raise NotImplementedError("d_qk=512 (MODEL1) is not built; only d_qk=576 (V32)")
+    if q.shape[-1] != 576:
+        raise ValueError(f"Unsupported d_qk={q.shape[-1]}; expected 576")
+    assert q.is_contiguous()
+
+
+# ------------------------------------------------------------------ raw entry points
+def get_decode_metadata(b, topk, extra_topk, num_sm_parts, fixed_overhead, topk_length, extra_topk_length,
+                        sched_meta, num_splits):
+    """csrc/binding.cpp:281-286."""
+    require_cuda(sched_meta, num_splits, topk_length, extra_topk_length)
+    check(_lib.load().smla_sched_meta(b, topk, extra_topk, num_sm_parts, fixed_overhead, ptr(topk_length),
+                                      ptr(extra_topk_length), ptr(sched_meta), ptr(num_splits),
+                                      stream_ptr(sched_meta.device)))
+
+
+def sparse_mla_splitkv_v2_fwd(Q, KV_cache, indices, o_accum, lse_accum, output, out_lse, sched_meta, num_splits,
+                              sm_scale, topk, stride_kv_row, page_block_size, num_sm_parts, attn_sink=None,
+                              extra_k_cache=None, extra_indices=None, topk_length=None, extra_topk=0,
+                              extra_topk_length=None, bf16_qk=True, impl=IMPL_AUTO):
+    """csrc/binding.cpp:96-164.  ``stride_kv_row * page_block_size`` is the page stride."""
+    _reject_extra(extra_k_cache, extra_indices, extra_topk_length, extra_topk)
+    _check_q(Q)
+    require_cuda(Q, KV_cache, indices, o_accum, lse_accum, output, out_lse, sched_meta, num_splits)
+    if attn_sink is not None and attn_sink.dtype != torch.float32:
+        raise ValueError("attn_sink must be float32")
+    num_tokens, num_heads, _ = Q.shape
+    st = status_buffer(Q.device)
+    check(_lib.load().smla_decode_splitkv(
+        ptr(Q), ptr(KV_cache), ptr(indices), ptr(o_accum), ptr(lse_accum), ptr(output), ptr(out_lse),
+        ptr(sched_meta), ptr(num_splits), num_tokens, num_heads, topk, float(sm_scale), page_block_size,
+        int(stride_kv_row) * int(page_block_size), num_sm_parts, ptr(attn_sink), ptr(topk_length), impl,
+        ptr(st), stream_ptr(Q.device)))
+
+
+def sparse_mla_combine_v2_fwd(o_accum, lse_accum, output, out_lse, num_splits_ptr, batch, max_nsplits,
+                              attn_sink=None):
+    """csrc/binding.cpp:166-183."""
+    require_cuda(o_accum, lse_accum, output, out_lse, num_splits_ptr)
+    num_heads = o_accum.shape[2]
+    check(_lib.load().smla_combine(ptr(o_accum), ptr(lse_accum), ptr(output), ptr(out_lse), ptr(num_splits_ptr),
+                                   batch, num_heads, max_nsplits, ptr(attn_sink), stream_ptr(o_accum.device)))
+
+
+def sparse_mla_prefill_raw(Q, KV_cache, indices, output, out_lse, sm_scale, topk, stride_kv_row, page_block_size,
+                           attn_sink=None, topk_length=None, bf16_qk=True, out_max_logits=None,
+                           extra_k_cache=None, extra_indices=None, extra_topk=0, impl=IMPL_AUTO):
+    """csrc/binding.cpp:185-247 (there named sparse_mla_prefill_fwd)."""
+    _reject_extra(extra_k_cache, extra_indices, None, extra_topk)
+    _check_q(Q)
+    require_cuda(Q, KV_cache, indices, output, out_lse)
+    if output.dtype != torch.bfloat16:
+        raise ValueError("output must be bf16")
+    if out_lse.dtype != torch.float32:
+        raise ValueError("out_lse must be float32")
+    num_tokens, num_heads, _ = Q.shape
+    st = status_buffer(Q.device)
+    check(_lib.load().smla_prefill(
+        ptr(Q), ptr(KV_cache), ptr(indices), ptr(output), ptr(out_lse), ptr(out_max_logits), num_tokens,
+        num_heads, topk, float(sm_scale), page_block_size, int(stride_kv_row) * int(page_block_size),
+        ptr(attn_sink), ptr(topk_length), impl, ptr(st), stream_ptr(Q.device)))
+
+
+# ------------------------------------------------------------------ op surface
+def sparse_mla_decode_fwd(
+    q: torch.Tensor,
+    kv_cache: torch.Tensor,
+    indices: torch.Tensor,
+    sm_scale: float,
+    d_v: int = 512,
+    attn_sink: Optional[torch.Tensor] = None,
+    bf16_qk: bool = True,
+    extra_k_cache: Optional[torch.Tensor] = None,
+    extra_indices: Optional[torch.Tensor] = None,
+    topk_length: Optional[torch.Tensor] = None,
+    extra_topk_length: Optional[torch.Tensor] = None,
+    extra_topk: int = 0,
+    out: Optional[torch.Tensor] = None,
+    impl: int = IMPL_AUTO,
+    num_sm_parts: Optional[int] = None,
+) -> Tuple[torch.Tensor, torch.Tensor]:
+    """Split-KV sparse-MLA decode: scheduler -> attention -> combine.
+
+    q [T, H, 576] bf16, kv_cache packed 656-byte rows, indices [T, topk] int32 (-1 = no entry).
+    Returns (out [T, H, 512] bf16, lse [T, H] fp32, base-2 LSE of the scaled logits).
+    Signature and results follow flash_mla_sm120/ops.py:48-119."""
+    _reject_extra(extra_k_cache, extra_indices, extra_topk_length, extra_topk)
+    _check_q(q)
+    page_block_size, page_stride = kv_geometry(kv_cache)
+    require_cuda(q, kv_cache, indices)
+    if d_v != 512:
+        raise ValueError(f"d_v must be 512, got {d_v}")
+    num_tokens, num_heads, _ = q.shape
+    topk = indices.shape[-1]
+    assert indices.dtype == torch.int32 and indices.is_contiguous()
+
+    if num_sm_parts is None:
+        num_sm_parts = pick_num_sm_parts(num_tokens, num_sms(q.device))
+    total_splits = num_tokens + num_sm_parts
+    ws = scratch(q.device, total_splits, num_heads, num_tokens, num_sm_parts)
+    lib = _lib.load()
+    stream = stream_ptr(q.device)
+    check(lib.smla_sched_meta(num_tokens, topk, 0, num_sm_parts, FIXED_OVERHEAD, ptr(topk_length), None,
+                              ptr(ws["sched_meta"]), ptr(ws["num_splits"]), stream))
+    if out is not None:
+        output = out.view(num_tokens, num_heads, d_v)
+    else:
+        output = torch.empty((num_tokens, num_heads, d_v), dtype=torch.bfloat16, device=q.device)
+    out_lse = torch.empty((num_tokens, num_heads), dtype=torch.float32, device=q.device)
+    check(lib.smla_decode_splitkv(
+        ptr(q), ptr(kv_cache), ptr(indices), ptr(ws["o_accum"]), ptr(ws["lse_accum"]), ptr(output), ptr(out_lse),
+        ptr(ws["sched_meta"]), ptr(ws["num_splits"]), num_tokens, num_heads, topk, float(sm_scale),
+        page_block_size, page_stride, num_sm_parts, ptr(attn_sink), ptr(topk_length), impl,
+        ptr(status_buffer(q.device)), stream))
+    max_nsplits = min(max(-(-topk // BLOCK_N), 1), num_sm_parts)
+    check(lib.smla_combine(ptr(ws["o_accum"]), ptr(ws["lse_accum"]), ptr(output), ptr(out_lse),
+                           ptr(ws["num_splits"]), num_tokens, num_heads, max_nsplits, ptr(attn_sink), stream))
+    return output, out_lse
+
+
+def sparse_mla_prefill_fwd(
+    q: torch.Tensor,
+    kv_cache: torch.Tensor,
+    indices: torch.Tensor,
+    sm_scale: float,
+    d_v: int = 512,
+    attn_sink: Optional[torch.Tensor] = None,
+    topk_length: Optional[torch.Tensor] = None,
+    bf16_qk: bool = True,
+    out: Optional[torch.Tensor] = None,
+    extra_k_cache: Optional[torch.Tensor] = None,
+    extra_indices: Optional[torch.Tensor] = None,
+    extra_topk: int = 0,
+    impl: int = IMPL_AUTO,
+) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
+    """Single-pass sparse-MLA attention for many query tokens.
+
+    Returns (out [T, H, 512] bf16, max_logits [T, H] fp32, lse [T, H] fp32), as
+    flash_mla_sm120/ops.py:122-165."""
+    _reject_extra(extra_k_cache, extra_indices, None, extra_topk)
+    _check_q(q)
+    page_block_size, page_stride = kv_geometry(kv_cache)
+    require_cuda(q, kv_cache, indices)
+    if d_v != 512:
+        raise ValueError(f"d_v must be 512, got {d_v}")
+    num_tokens, num_heads, _ = q.shape
+    topk = indices.shape[-1]
+    assert indices.dtype == torch.int32 and indices.is_contiguous()
+    if out is not None:
+        output = out.view(num_tokens, num_heads, d_v)
+    else:
+        output = torch.empty((num_tokens, num_heads, d_v), dtype=torch.bfloat16, device=q.device)
+    lse = torch.empty((num_tokens, num_heads), dtype=torch.float32, device=q.device)
+    max_logits = torch.empty((num_tokens, num_heads), dtype=torch.float32, device=q.device)
+    check(_lib.load().smla_prefill(
+        ptr(q), ptr(kv_cache), ptr(indices), ptr(output), ptr(lse), ptr(max_logits), num_tokens, num_heads,
+        topk, float(sm_scale), page_block_size, page_stride, ptr(attn_sink), ptr(topk_length), impl,
+        ptr(status_buffer(q.device)), stream_ptr(q.device)))
+    return output, max_logits, lse

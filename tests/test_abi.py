@@ -1,0 +1,78 @@
+"""The C-ABI library: it loads, exports every function include/smla.h declares, and rejects bad
+arguments with an error code and a message before touching the device (no GPU needed)."""
+import ctypes
+import os
+import re
+
+import pytest
+
+from helpers import ROOT
+from sparse_mla_sm120_b200 import _lib, build
+
+
+@pytest.fixture(scope="module")
+def lib():
+    build.build()
+    return _lib.load()
+
+
+def _declared():
+    text = open(os.path.join(ROOT, "include", "smla.h")).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(smla_[a-z0-9_]+)\s*\(", text)))
+
+
+def test_every_declared_symbol_is_exported(lib):
+    names = _declared()
+    assert len(names) >= 12
+    raw = ctypes.CDLL(build.LIB_PATH)
+    for n in names:
+        assert hasattr(raw, n), f"{n} declared in include/smla.h but not exported"
+    assert set(names) == set(_lib.EXPORTS), "python prototypes out of sync with the header"
+
+
+def test_argument_errors_do_not_launch(lib):
+    assert lib.smla_version() >= 100
+    rc = lib.smla_decode_splitkv(None, None, None, None, None, None, None, None, None, 1, 128, 2048, 1.0, 64,
+                                 64 * 656, 1, None, None, 0, None, None)
+    assert rc == -1 and b"null" in lib.smla_last_error()
+    fake = 4096  # a non-null, 16-byte aligned address that is never dereferenced on the host
+    rc = lib.smla_prefill(fake, fake, fake, fake, fake, None, 1, 129, 2048, 1.0, 64, 64 * 656, None, None, 0,
+                          None, None)
+    assert rc == -2 and b"num_heads" in lib.smla_last_error()
+    rc = lib.smla_prefill(fake + 4, fake, fake, fake, fake, None, 1, 128, 2048, 1.0, 64, 64 * 656, None, None, 0,
+                          None, None)
+    assert rc == -3
+    rc = lib.smla_prefill(fake, fake, fake, fake, fake, None, 1, 128, 2048, 1.0, 64, 64 * 600, None, None, 0,
+                          None, None)
+    assert rc == -2 and b"stride" in lib.smla_last_error()
+    assert lib.smla_combine(fake, fake, fake, fake, fake, 1, 128, 4096, None, None) == -2
+    assert lib.smla_sched_meta(0, 2048, 0, 4, 5, None, None, fake, fake, None) == -2
+    assert lib.smla_topk(None, None, None, None, 1, 1, 1, 1, None) == -1
+    assert lib.smla_workspace_bytes(64, 128, 74) == (64 + 74) * 128 * 513 * 4
+    with pytest.raises(ValueError):
+        _lib.check(-2)
+
+
+def test_python_surface_rejects_cpu_tensors_and_unbuilt_features():
+    import torch
+    import sparse_mla_sm120_b200 as smla
+    q = torch.zeros(1, 128, 576, dtype=torch.bfloat16)
+    kv = torch.zeros(4, 64, 1, 656, dtype=torch.uint8)
+    idx = torch.zeros(1, 64, dtype=torch.int32)
+    with pytest.raises(ValueError, match="CUDA"):
+        smla.flash_ops.sparse_mla_decode_fwd(q, kv, idx, 1.0)
+    with pytest.raises(NotImplementedError):
+        smla.flash_ops.sparse_mla_decode_fwd(q[..., :512].contiguous(), kv, idx, 1.0)
+    with pytest.raises(NotImplementedError):
+        smla.flash_ops.sparse_mla_decode_fwd(q, kv, idx, 1.0, extra_k_cache=kv, extra_indices=idx, extra_topk=64)
+    with pytest.raises(NotImplementedError):
+        smla.flash_ops.sparse_mla_prefill_fwd(q, torch.zeros(4, 64, 1, 584, dtype=torch.uint8), idx, 1.0)
+
+
+def test_split_policy():
+    from sparse_mla_sm120_b200._runtime import pick_num_sm_parts
+    assert pick_num_sm_parts(64, 148) == 64      # 128 CTAs on 148 SMs: unsplit
+    assert pick_num_sm_parts(128, 148) == 128    # two nearly full waves: unsplit
+    assert pick_num_sm_parts(1, 148) == 74       # small batch: cut into sms/2 partitions
+    assert pick_num_sm_parts(80, 148) == 74

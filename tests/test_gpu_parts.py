@@ -1,0 +1,169 @@
+"""Parity of the scheduler, combine, cache writer, indexer, top-k and index partition kernels."""
+import numpy as np
+import pytest
+import torch
+
+import helpers as H
+from helpers import bf16_from_bits, orc
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+
+
+# ------------------------------------------------------------------ scheduler: integer-exact
+@pytest.mark.parametrize("b,topk,parts", [(1, 512, 4), (1, 2048, 32), (4, 1024, 16), (8, 2048, 32), (16, 512, 4),
+                                          (32, 512, 64), (64, 2048, 74), (64, 2048, 64), (128, 2048, 74),
+                                          (5, 2048, 148), (4096, 2048, 74)])
+def test_scheduler_matches_oracle(b, topk, parts):
+    from sparse_mla_sm120_b200 import flash_ops
+    meta = torch.empty(parts * 8, dtype=torch.int32, device=DEV)
+    ns = torch.empty(b + 1, dtype=torch.int32, device=DEV)
+    flash_ops.get_decode_metadata(b, topk, 0, parts, 5, None, None, meta, ns)
+    ref_meta, ref_ns = orc.sched_meta_ref(b, topk, 0, parts, 5)
+    got = meta.view(parts, 8).cpu().tolist()
+    assert got == ref_meta
+    assert ns.cpu().tolist() == ref_ns
+    orc.verify_schedule(got, ns.cpu().tolist(), orc.expected_blocks(b, topk, 0, None, None), b)
+
+
+def test_scheduler_lengths_and_extra():
+    from sparse_mla_sm120_b200 import flash_ops
+    for tl, etl, topk, extra, parts in [([256, 512, 128, 512], None, 512, 0, 8), ([0, 512], None, 512, 0, 4),
+                                        ([100, 200, 300], None, 512, 0, 4),
+                                        ([256, 512, 128, 512], [128, 64, 256, 0], 512, 256, 8)]:
+        b = len(tl)
+        meta = torch.empty(parts * 8, dtype=torch.int32, device=DEV)
+        ns = torch.empty(b + 1, dtype=torch.int32, device=DEV)
+        tl_d = torch.tensor(tl, dtype=torch.int32, device=DEV)
+        etl_d = None if etl is None else torch.tensor(etl, dtype=torch.int32, device=DEV)
+        flash_ops.get_decode_metadata(b, topk, extra, parts, 5, tl_d, etl_d, meta, ns)
+        ref_meta, ref_ns = orc.sched_meta_ref(b, topk, extra, parts, 5, tl, etl)
+        assert meta.view(parts, 8).cpu().tolist() == ref_meta and ns.cpu().tolist() == ref_ns
+
+
+# ------------------------------------------------------------------ combine
+def _combine(o_accum, lse_accum, num_splits, batch, h, sink=None):
+    from sparse_mla_sm120_b200 import flash_ops
+    out = torch.zeros(batch, h, 512, dtype=torch.bfloat16, device=DEV)
+    lse = torch.zeros(batch, h, dtype=torch.float32, device=DEV)
+    ns = torch.as_tensor(num_splits, dtype=torch.int32).to(DEV)
+    mx = int(max(num_splits[i + 1] - num_splits[i] for i in range(batch)))
+    flash_ops.sparse_mla_combine_v2_fwd(o_accum.to(DEV), lse_accum.to(DEV), out, lse, ns, batch, mx,
+                                        None if sink is None else sink.to(DEV))
+    torch.cuda.synchronize()
+    return out.cpu(), lse.cpu()
+
+
+def test_combine_golden(golden_dir):
+    g = np.load(f"{golden_dir}/combine.npz")
+    ns = g["num_splits"].tolist()
+    b = len(ns) - 1
+    out, lse = _combine(torch.from_numpy(g["o_accum"]), torch.from_numpy(g["lse_accum"]), ns, b, 16)
+    ref_out, ref_lse = bf16_from_bits(g["out_bf16"]), torch.from_numpy(g["lse"])
+    multi = [i for i in range(b) if ns[i + 1] - ns[i] > 1]   # single-split requests are not touched
+    assert float((out[multi].float() - ref_out[multi].float()).abs().max()) < 2e-3
+    assert float((lse[multi] - ref_lse[multi]).abs().max()) < 1e-4
+    single = [i for i in range(b) if ns[i + 1] - ns[i] <= 1]
+    assert not out[single].any()
+
+
+@pytest.mark.parametrize("nsplits", [2, 4, 8, 16, 32, 74])
+@pytest.mark.parametrize("num_heads", [8, 64, 128])
+def test_combine_grid(nsplits, num_heads):
+    """tests/test_combine.py:60-93: bounds 1e-2 on output and LSE (ours: 2e-3 / 1e-4)."""
+    torch.manual_seed(42)
+    batch = 4
+    o = torch.randn(batch * nsplits, 1, num_heads, 512) * 0.1
+    l = torch.randn(batch * nsplits, 1, num_heads) * 3.0
+    l[0, 0, :] = 100.0
+    l[1:nsplits, 0, :] = -100.0
+    ns = [i * nsplits for i in range(batch + 1)]
+    out, lse = _combine(o, l, ns, batch, num_heads)
+    ref_out, ref_lse = orc.combine_ref(o, l, ns, batch)
+    assert float((out.float() - ref_out.float()).abs().max()) < 2e-3
+    assert float((lse - ref_lse).abs().max()) < 1e-4
+    assert torch.isfinite(out.float()).all()
+
+
+# ------------------------------------------------------------------ cache writer: byte-exact
+def test_pack_kv_bytes(golden_dir):
+    from sparse_mla_sm120_b200 import indexer
+    g = np.load(f"{golden_dir}/kv_format.npz")
+    kv = bf16_from_bits(g["kv_bf16"])
+    packed = indexer.pack_kv_cache(kv.to(DEV)).cpu()
+    assert np.array_equal(packed.numpy(), g["packed"])
+    torch.manual_seed(1)
+    kv = (torch.randn(1000, 576) * torch.logspace(-6, 4, 1000).unsqueeze(1)).to(torch.bfloat16)
+    kv[17] = 0
+    ref = orc.quantize_kv_v32(kv.view(1000, 1, 1, 576)).view(1000, 656)
+    got = indexer.pack_kv_cache(kv.to(DEV)).cpu()
+    assert torch.equal(got, ref)
+
+
+# ------------------------------------------------------------------ indexer + top-k + partition
+def _indexer_case(seed, s_q, h, s_k):
+    g = torch.Generator().manual_seed(seed)
+    q = torch.randn(s_q, h, 128, generator=g).to(torch.float8_e4m3fn)
+    kf = torch.randn(s_k, 128, generator=g)
+    k_scale = kf.abs().amax(dim=1) / 448.0
+    k = (kf / k_scale.unsqueeze(1)).to(torch.float8_e4m3fn)
+    w = torch.randn(s_q, h, generator=g) * 0.1
+    ks = torch.zeros(s_q, dtype=torch.int32)
+    ke = (s_k - s_q + torch.arange(s_q)).to(torch.int32).clamp(min=1)
+    return q, k, k_scale, w, ks, ke
+
+
+@pytest.mark.parametrize("impl", [1, 2])
+@pytest.mark.parametrize("s_q,h,s_k", [(8, 64, 1000), (130, 64, 4096), (5, 32, 257)])
+def test_mqa_logits(s_q, h, s_k, impl):
+    from sparse_mla_sm120_b200 import indexer
+    q, k, k_scale, w, ks, ke = _indexer_case(3, s_q, h, s_k)
+    ks[1 % s_q] = 7
+    ref = orc.mqa_logits_ref(q, k, k_scale, w, ks, ke)
+    got = indexer.fp8_mqa_logits(q.to(DEV), k.to(DEV), k_scale.to(DEV), w.to(DEV), ks.to(DEV), ke.to(DEV),
+                                 impl=impl).cpu()
+    assert torch.equal(torch.isinf(got), torch.isinf(ref)), "range mask differs"
+    fin = ~torch.isinf(ref)
+    # products of e4m3 values are exact in fp32; only the summation order differs
+    assert float((got[fin] - ref[fin]).abs().max()) <= 1e-4 * float(ref[fin].abs().max())
+
+
+def test_topk_sets():
+    from sparse_mla_sm120_b200 import indexer
+    torch.manual_seed(5)
+    rows, cols, k = 6, 5000, 512
+    logits = torch.randn(rows, cols)
+    logits[2, 100:400] = 1.0            # a run of ties across the threshold
+    ks = torch.tensor([0, 10, 0, 0, 4000, 0], dtype=torch.int32)
+    ke = torch.tensor([cols, 4000, cols, 300, cols, 0], dtype=torch.int32)
+    masked = logits.clone()
+    j = torch.arange(cols).unsqueeze(0)
+    masked[(j < ks.view(-1, 1)) | (j >= ke.view(-1, 1))] = float("-inf")
+    got = indexer.topk_indices(masked.to(DEV), ks.to(DEV), ke.to(DEV), k).cpu()
+    for r in range(rows):
+        g = got[r][got[r] >= 0]
+        n = int(min(k, max(int(ke[r]) - int(ks[r]), 0)))
+        assert g.numel() == n and torch.all(got[r][n:] == -1)
+        assert torch.all(g[1:] > g[:-1]) if n > 1 else True      # ascending, no duplicates
+        if n:
+            thr = torch.topk(masked[r], n).values[-1]
+            vals = masked[r][g.long()]
+            assert float(vals.min()) >= float(thr)
+            assert int((masked[r] > thr).sum()) == int((vals > thr).sum())   # every strictly-greater one taken
+    # ties go to the lower column
+    r = 2
+    thr = torch.topk(masked[r], k).values[-1]
+    if float(thr) == 1.0:
+        tied = got[r][(masked[r][got[r].long()] == 1.0)]
+        assert int(tied.max()) - int(tied.min()) + 1 == tied.numel() and int(tied.min()) == 100
+
+
+def test_cp_partition():
+    from sparse_mla_sm120_b200 import cp
+    torch.manual_seed(8)
+    idx = torch.stack([torch.randperm(4096)[:300] for _ in range(9)]).to(torch.int32)
+    idx[:, -20:] = -1
+    for lo, hi in [(0, 1024), (1024, 2048), (3072, 4096), (100, 100)]:
+        ref_local, ref_len = orc.cp_partition_ref(idx, lo, hi)
+        local, length = cp.partition_indices(idx.to(DEV), lo, hi)
+        assert torch.equal(local.cpu(), ref_local) and torch.equal(length.cpu(), ref_len)

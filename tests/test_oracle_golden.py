@@ -1,0 +1,62 @@
+"""The CPU oracle against the fixtures that the reference's own helpers produced
+(tests/golden/make_golden.py).  These pin the oracle; no GPU involved."""
+import numpy as np
+import torch
+
+from helpers import bf16_from_bits, orc
+
+
+def _load(golden_dir, name):
+    return np.load(f"{golden_dir}/{name}.npz")
+
+
+def test_kv_format_roundtrip(golden_dir):
+    g = _load(golden_dir, "kv_format")
+    kv = bf16_from_bits(g["kv_bf16"])
+    packed = orc.quantize_kv_v32(kv)
+    assert np.array_equal(packed.numpy(), g["packed"]), "packed bytes differ from the reference writer"
+    deq = orc.dequantize_kv_v32(torch.from_numpy(g["packed"]))
+    assert np.array_equal(deq.view(torch.uint16).numpy(), g["dequant_bf16"]), "dequantised bf16 differs"
+    # every stored scale is a power of two (the kernels rely on it)
+    scales = torch.from_numpy(g["packed"]).reshape(-1, 656)[:, 512:528].contiguous().view(torch.float32)
+    m, _ = torch.frexp(scales)
+    assert torch.all(m == 0.5)
+
+
+def test_attention_matches_reference(golden_dir):
+    for name in ("attn_h16", "attn_h128", "attn_h64_lonely"):
+        g = _load(golden_dir, name)
+        packed = torch.from_numpy(g["packed"])
+        q = bf16_from_bits(g["q_bf16"])
+        idx = torch.from_numpy(g["indices"])
+        out, lse = orc.ref_sparse_attn(q, orc.dequantize_kv_v32(packed), idx, float(g["sm_scale"]), 512)
+        ref_out = bf16_from_bits(g["out_bf16"])
+        assert torch.equal(out.view(torch.uint16), ref_out.view(torch.uint16)), name
+        ref_lse = torch.from_numpy(g["lse"])
+        assert torch.equal(torch.isinf(lse), torch.isinf(ref_lse)), name
+        fin = ~torch.isinf(ref_lse)
+        assert torch.allclose(lse[fin], ref_lse[fin], rtol=0, atol=1e-6), name
+    # the lonely request: output exactly zero, LSE -inf
+    g = _load(golden_dir, "attn_h64_lonely")
+    assert not bf16_from_bits(g["out_bf16"])[1].any()
+    assert np.all(np.isneginf(g["lse"][1]))
+
+
+def test_combine_matches_reference(golden_dir):
+    g = _load(golden_dir, "combine")
+    out, lse = orc.combine_ref(torch.from_numpy(g["o_accum"]), torch.from_numpy(g["lse_accum"]),
+                               g["num_splits"].tolist(), len(g["num_splits"]) - 1)
+    assert torch.equal(out.view(torch.uint16), bf16_from_bits(g["out_bf16"]).view(torch.uint16))
+    assert torch.equal(lse, torch.from_numpy(g["lse"]))
+
+
+def test_topk_length_masks_tail():
+    from helpers import make_case
+    c = make_case(3, 2, 8, 128, 4, invalid_tail=0.0)
+    tl = torch.tensor([40, 128], dtype=torch.int32)
+    deq = orc.dequantize_kv_v32(c["packed"])
+    out, lse = orc.ref_sparse_attn(c["q"].unsqueeze(1), deq, c["indices"].unsqueeze(1), c["sm_scale"], 512, tl)
+    idx2 = c["indices"].clone()
+    idx2[0, 40:] = -1
+    out2, lse2 = orc.ref_sparse_attn(c["q"].unsqueeze(1), deq, idx2.unsqueeze(1), c["sm_scale"], 512)
+    assert torch.equal(out, out2) and torch.equal(lse, lse2)
