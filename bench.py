@@ -1,0 +1,384 @@
+#!/usr/bin/env python
+"""Benchmark of the sparse-MLA hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference] [--no-extras]
+
+One step = one split-KV decode call (scheduler -> attention -> combine) over one batch of the
+DeepSeek-V3.2-shape decode configuration: 64 requests per GPU, 128 query heads, top-k 2048,
+per-request KV length uniform in [4096, 32768] in a paged (block 64) pool of packed 656-byte
+FP8 rows.  All inputs are synthetic and seeded.  With N > 1 every rank serves its own 64
+requests (decode batches shard by sequence, nothing is exchanged), so scaling is weak.
+
+Printed line: ``value`` is the algorithmic HBM traffic of the whole job divided by the step time
+with inputs resident on the device (CUDA-graph replay of the public op); ``e2e`` is the same
+through the public op with q / indices coming from pinned host memory and the output copied back
+every step (the paged KV cache is device-resident state, as in any serving engine).
+``--impl reference`` times the reference's CPU PyTorch path (restated in oracle/) on the host cores.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+import torch
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+B_PER_GPU, HEADS, TOPK, D_QK, D_V, ROW = 64, 128, 2048, 576, 512, 656
+LEN_LO, LEN_HI, BLOCK = 4096, 32768, 64
+NSETS = 8   # rotating (q, indices) sets so that consecutive steps gather different rows
+SM_SCALE = D_QK ** -0.5
+WORKLOAD = ("V3.2-shape sparse-MLA decode: b=64/GPU, s_q=1, h_q=128, topk=2048, d_qk=576, d_v=512, "
+            "KV len U[4096,32768], paged block 64, packed FP8 656 B rows")
+# DRAM bytes per launch of the attention kernel from the ncu capture summarised in
+# profiles/attn_tc_decode_b64.md (None until a capture exists).
+NCU_TRAFFIC_BYTES = None
+
+
+def algorithmic_bytes(num_tokens: int, n_valid: int) -> int:
+    """Bytes one decode step must move: gathered rows + q + output + indices + LSE."""
+    return num_tokens * (n_valid * ROW + HEADS * D_QK * 2 + HEADS * D_V * 2 + TOPK * 4 + HEADS * 4)
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            d = json.load(f)
+        return float(d["hbm_gbs"]), float(d.get("bf16_tflops", 1679.4)), "measured"
+    return 6650.0, 1590.0, "fallback"
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+    Q = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index, self.samples, self.proc = index, [], None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.Q}",
+                                          "--format=csv,noheader,nounits", "-lms", "100"],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.samples.append(line.strip())
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=2)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, mx, reasons = [], None, set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for s in self.samples:
+            parts = [x.strip() for x in s.split(",")]
+            if len(parts) < 6:
+                continue
+            try:
+                sm.append(float(parts[0])); mx = float(parts[1])
+            except ValueError:
+                continue
+            for n, v in zip(names, parts[2:6]):
+                if v.lower().startswith("active"):
+                    reasons.add(n)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": mx, "reasons": sorted(reasons),
+                "samples": len(sm)}
+
+
+def build_workload(device, seed: int, batch: int):
+    """Paged pool + NSETS rotating (q, indices) sets, all on the device."""
+    from sparse_mla_sm120_b200 import indexer
+    g = torch.Generator(device="cpu").manual_seed(seed)
+    lens = torch.randint(LEN_LO, LEN_HI + 1, (batch,), generator=g)
+    nblk = (lens + BLOCK - 1) // BLOCK
+    total_blocks = int(nblk.sum())
+    perm = torch.randperm(total_blocks, generator=g)          # shuffled block table
+    tables, off = [], 0
+    for n in nblk.tolist():
+        tables.append(perm[off:off + n]); off += n
+    gd = torch.Generator(device=device).manual_seed(seed)
+    pool = torch.empty((total_blocks, BLOCK, 1, ROW), dtype=torch.uint8, device=device)
+    chunk = 2048  # blocks per packing chunk (bounds the bf16 temporary)
+    for b0 in range(0, total_blocks, chunk):
+        b1 = min(b0 + chunk, total_blocks)
+        kv = torch.randn(((b1 - b0) * BLOCK, D_QK), device=device, generator=gd).to(torch.bfloat16)
+        pool[b0:b1] = indexer.pack_kv_cache(kv).view(b1 - b0, BLOCK, 1, ROW)
+    sets = []
+    for s in range(NSETS):
+        q = (torch.randn((batch, HEADS, D_QK), device=device, generator=gd) * 0.5).to(torch.bfloat16)
+        idx = torch.empty((batch, TOPK), dtype=torch.int32)
+        for i, (L, tab) in enumerate(zip(lens.tolist(), tables)):
+            pos = torch.randperm(L, generator=g)[:TOPK]
+            idx[i] = (tab[pos // BLOCK] * BLOCK + pos % BLOCK).to(torch.int32)
+        sets.append((q, idx.to(device)))
+    return pool, sets, lens
+
+
+def time_events(fn, steps, warmup, sync):
+    for i in range(warmup):
+        fn(i)
+    sync()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for i in range(steps):
+        fn(warmup + i)
+    e1.record()
+    sync()
+    return e0.elapsed_time(e1) / 1e3
+
+
+def run_ours(args):
+    import torch.distributed as dist
+    from sparse_mla_sm120_b200 import _lib, flash_ops
+    from sparse_mla_sm120_b200._runtime import (FIXED_OVERHEAD, check_status, kv_geometry, pick_num_sm_parts, ptr,
+                                                 scratch, status_buffer, stream_ptr)
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    device = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=device)
+    hbm_peak, bf16_peak, peak_kind = measured_peaks()
+
+    pool, sets, lens = build_workload(device, 1234 + rank, B_PER_GPU)
+    bytes_step = algorithmic_bytes(B_PER_GPU, TOPK)
+
+    def barrier_sync():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    # ---- device-resident: CUDA-graph replay of the public op, one graph per input set ----------
+    outs, graphs = [], []
+    side = torch.cuda.Stream()
+    with torch.cuda.stream(side):
+        for q, idx in sets:
+            for _ in range(2):
+                o = flash_ops.sparse_mla_decode_fwd(q, pool, idx, SM_SCALE)
+            side.synchronize()
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g, stream=side):
+                o = flash_ops.sparse_mla_decode_fwd(q, pool, idx, SM_SCALE)
+            graphs.append(g); outs.append(o)
+    torch.cuda.synchronize()
+    check_status(device)
+
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    barrier_sync()
+    secs = time_events(lambda i: graphs[i % NSETS].replay(), args.steps, args.warmup, barrier_sync)
+    t = torch.tensor([secs], device=device)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    secs = float(t.item())
+    check_status(device)
+
+    # ---- end to end: pinned host q / indices in, output out, through the public op -------------
+    host_sets = [(q.cpu().pin_memory(), idx.cpu().pin_memory()) for q, idx in sets]
+    host_out = torch.empty((B_PER_GPU, HEADS, D_V), dtype=torch.bfloat16).pin_memory()
+    host_lse = torch.empty((B_PER_GPU, HEADS), dtype=torch.float32).pin_memory()
+    dq = torch.empty_like(sets[0][0]); didx = torch.empty_like(sets[0][1])
+
+    def e2e_step(i):
+        hq, hidx = host_sets[i % NSETS]
+        dq.copy_(hq, non_blocking=True)
+        didx.copy_(hidx, non_blocking=True)
+        o, lse = flash_ops.sparse_mla_decode_fwd(dq, pool, didx, SM_SCALE)
+        host_out.copy_(o, non_blocking=True)
+        host_lse.copy_(lse, non_blocking=True)
+
+    barrier_sync()
+    e2e_secs = time_events(e2e_step, args.steps, args.warmup, barrier_sync)
+    t = torch.tensor([e2e_secs], device=device)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    e2e_secs = float(t.item())
+    clocks = sampler.stop() if rank == 0 else None
+
+    # ---- the dominant kernel alone (attention), events around each launch ----------------------
+    T = B_PER_GPU
+    parts = pick_num_sm_parts(T, torch.cuda.get_device_properties(device).multi_processor_count)
+    ws = scratch(device, T + parts, HEADS, T, parts)
+    lib, stream = _lib.load(), stream_ptr(device)
+    pbs, pstride = kv_geometry(pool)
+    lib.smla_sched_meta(T, TOPK, 0, parts, FIXED_OVERHEAD, None, None, ptr(ws["sched_meta"]), ptr(ws["num_splits"]), stream)
+    out = torch.empty((T, HEADS, D_V), dtype=torch.bfloat16, device=device)
+    lse = torch.empty((T, HEADS), dtype=torch.float32, device=device)
+    st = status_buffer(device)
+    kt = []
+    for i in range(args.warmup + min(args.steps, 50)):
+        q, idx = sets[i % NSETS]
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        lib.smla_decode_splitkv(ptr(q), ptr(pool), ptr(idx), ptr(ws["o_accum"]), ptr(ws["lse_accum"]), ptr(out),
+                                ptr(lse), ptr(ws["sched_meta"]), ptr(ws["num_splits"]), T, HEADS, TOPK, SM_SCALE,
+                                pbs, pstride, parts, None, None, 0, ptr(st), stream)
+        e1.record()
+        torch.cuda.synchronize()
+        if i >= args.warmup:
+            kt.append(e0.elapsed_time(e1) * 1e-3)
+    k_secs = statistics.mean(kt)
+
+    extras = {}
+    if rank == 0 and not args.no_extras:
+        try:
+            extras = run_extras(device, bf16_peak)
+        except Exception as e:  # the headline line must still print
+            extras = {"error": repr(e)}
+    cpu = cpu_baseline(pool, sets) if rank == 0 else None
+
+    if rank == 0:
+        total_bytes = bytes_step * world
+        ms = secs / args.steps * 1e3
+        line = {
+            "metric": "sparse_mla_decode_algorithmic_hbm_throughput",
+            "value": total_bytes * args.steps / secs / 1e9, "unit": "GB/s",
+            "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms,
+            "decode_us_per_step": ms * 1e3,
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "fp8_e4m3",
+            "data": "synthetic",
+            "config": {"workload": WORKLOAD, "requests_per_gpu": B_PER_GPU, "sharding": "requests across GPUs, no collective",
+                       "l2": f"inputs larger than L2: {NSETS} rotating (q, indices) sets gathering from a "
+                             f"{pool.numel() / 1e9:.2f} GB pool", "timed": "scheduler + attention + combine, CUDA graph replay",
+                       "num_sm_parts": parts},
+            "e2e": {"value": total_bytes * args.steps / e2e_secs / 1e9, "unit": "GB/s",
+                    "us_per_step": e2e_secs / args.steps * 1e6,
+                    "h2d_bytes_per_step": int(dq.numel() * 2 + didx.numel() * 4),
+                    "d2h_bytes_per_step": int(host_out.numel() * 2 + host_lse.numel() * 4),
+                    "note": "paged KV cache is device-resident state; q and indices come from pinned host memory, output and LSE go back"},
+            "gpu_launches": 3 * args.steps,
+            "roofline": {"bound": "hbm", "kernel": "attn_tc_kernel", "achieved": bytes_step / k_secs / 1e9, "peak": hbm_peak,
+                         "unit": "GB/s", "frac": bytes_step / k_secs / 1e9 / hbm_peak, "peak_kind": f"of {peak_kind}",
+                         "kernel_us": k_secs * 1e6, "traffic": NCU_TRAFFIC_BYTES,
+                         "frac_of_8TBs_nominal": bytes_step / k_secs / 8e12},
+            "cpu_baseline": cpu, "clocks": clocks, "extras": extras,
+        }
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+def run_extras(device, bf16_peak):
+    """Secondary measurements of the other kernels on the path (not part of the timed step)."""
+    from sparse_mla_sm120_b200 import flash_ops, indexer
+    out = {}
+    g = torch.Generator(device=device).manual_seed(7)
+    # prefill: s_q 4096, H 128, topk 2048 over 8192 rows, causal top-k
+    s_q, rows = 4096, 8192
+    kv = indexer.pack_kv_cache(torch.randn((rows, D_QK), device=device, generator=g).to(torch.bfloat16)).view(rows // 64, 64, 1, ROW)
+    q = torch.randn((s_q, HEADS, D_QK), device=device, generator=g).to(torch.bfloat16)
+    idx = torch.stack([torch.randperm(4096 + i, device=device, generator=g)[:TOPK] for i in range(s_q)]).to(torch.int32)
+    for _ in range(2):
+        flash_ops.sparse_mla_prefill_fwd(q, kv, idx, SM_SCALE)
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    n = 5
+    e0.record()
+    for _ in range(n):
+        flash_ops.sparse_mla_prefill_fwd(q, kv, idx, SM_SCALE)
+    e1.record(); torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / n
+    flops = 2.0 * s_q * HEADS * TOPK * (D_QK + D_V)
+    out["prefill"] = {"workload": "s_q=4096, h=128, topk=2048, KV 8192 rows", "ms": ms,
+                      "tflops": flops / ms / 1e9, "frac_of_bf16_peak": flops / ms / 1e9 / bf16_peak}
+    del q, idx
+    return out
+
+
+def cpu_baseline(pool, sets, n_req: int = 16):
+    """The reference's CPU PyTorch path (oracle port) on a bounded sample: n_req of the 64
+    requests of one step, all host threads."""
+    from oracle import sparse_mla_oracle as orc
+    q, idx = sets[0]
+    rows = pool.view(-1, ROW)[idx[:n_req].reshape(-1).long()].cpu()
+    qc = q[:n_req].cpu().unsqueeze(1)
+    local_idx = torch.arange(n_req * TOPK, dtype=torch.int32).view(n_req, 1, TOPK)
+    torch.set_num_threads(os.cpu_count())
+    best = None
+    for _ in range(5):
+        t0 = time.perf_counter()
+        deq = orc.dequantize_kv_v32(rows.view(-1, 64, 1, ROW))
+        orc.ref_sparse_attn(qc, deq, local_idx, SM_SCALE, D_V)
+        dt = time.perf_counter() - t0
+        best = dt if best is None else min(best, dt)
+    return {"value": algorithmic_bytes(n_req, TOPK) / best / 1e9, "unit": "GB/s", "cores": os.cpu_count(),
+            "kind": "port", "sample": f"{n_req} of {B_PER_GPU} requests of one step (dequantise gathered rows + fp32 attention), best of 5",
+            "seconds": best}
+
+
+def run_reference(args):
+    """The reference's own CPU implementation of the path (its PyTorch reference functions,
+    restated in oracle/), timed on the host cores on a bounded sample per step."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    from oracle import sparse_mla_oracle as orc
+    torch.set_num_threads(os.cpu_count())
+    n_req = 16
+    g = torch.Generator().manual_seed(1234)
+    kv = torch.randn(n_req * TOPK // 64, 64, 1, D_QK, generator=g).to(torch.bfloat16)
+    packed = orc.quantize_kv_v32(kv)
+    q = (torch.randn(n_req, 1, HEADS, D_QK, generator=g) * 0.5).to(torch.bfloat16)
+    idx = torch.stack([torch.randperm(n_req * TOPK, generator=g)[:TOPK] for _ in range(n_req)]).view(n_req, 1, TOPK).int()
+
+    def step():
+        deq = orc.dequantize_kv_v32(packed)
+        orc.ref_sparse_attn(q, deq, idx, SM_SCALE, D_V)
+
+    for _ in range(args.warmup):
+        step()
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        step()
+    secs = time.perf_counter() - t0
+    value = algorithmic_bytes(n_req, TOPK) * args.steps / secs / 1e9
+    sample = f"{n_req} of {B_PER_GPU} requests per step on the CPU (the step's unit work scales linearly with requests)"
+    print(json.dumps({
+        "impl": "reference", "metric": "sparse_mla_decode_algorithmic_hbm_throughput", "value": value, "unit": "GB/s",
+        "n_gpus": int(os.environ.get("WORLD_SIZE", "1")), "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": secs / args.steps * 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "f32", "data": "synthetic", "config": {"workload": WORKLOAD, "sample": sample},
+        "cpu_baseline": {"value": value, "unit": "GB/s", "cores": os.cpu_count(), "kind": "port", "sample": sample},
+        "e2e": {"value": value, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=200)
+    ap.add_argument("--warmup", type=int, default=20)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-extras", action="store_true")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3)
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -53,6 +53,13 @@ extern "C" {
 const char* smla_last_error(void) { return g_err; }
 int smla_version(void) { return 100; }
 
+// Debugging aid, not part of the public header: registers a device buffer of 1 + 2*capacity
+// int64 (zeroed by the caller) that CTA 0 of the tcgen05 attention kernel fills with a timeline.
+int smla_debug_set_trace(void* buf, int capacity) {
+    set_attn_trace((long long*)buf, capacity);
+    return 0;
+}
+
 int smla_num_sms(void) {
     static int cache[64] = {};
     int dev = 0;

@@ -75,6 +75,24 @@ constexpr uint32_t IDESC_PV_F8 = instr_desc(FMT_E4M3, FMT_E4M3, false, true, 128
 // give-up codes reported through status[0]
 enum { W_EMPTY = 1, W_FULL = 2, W_SREADY = 3, W_PREADY = 4, W_PVDONE = 5, W_QREADY = 6 };
 
+// Optional timeline of CTA 0 (debugging aid): records (tag, tile, clock) triples when a trace
+// buffer has been registered with smla_debug_set_trace.
+struct Trace {
+    long long* buf;
+    int cap;
+};
+__device__ __forceinline__ void trace(const Trace& t, int tag, int tile) {
+    if (t.buf != nullptr && blockIdx.x == 0 && (threadIdx.x & 31) == 0) {
+        const int slot = atomicAdd(reinterpret_cast<int*>(t.buf), 1);
+        if (slot < t.cap) {
+            long long c;
+            asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(c));
+            t.buf[1 + 2 * slot] = ((long long)tag << 32) | (unsigned)tile;
+            t.buf[2 + 2 * slot] = c;
+        }
+    }
+}
+
 struct Work {   // one request's share of a partition
     int req, blk0, nblk, len, split_idx;
     bool no_split;
@@ -143,7 +161,7 @@ __device__ __forceinline__ uint32_t mul_bf16x2(uint32_t w, __nv_bfloat162 f) {
 }
 
 // ---------------------------------------------------------------------------------------------
-__global__ void __launch_bounds__(TC_THREADS, 1) attn_tc_kernel(const AttnParams p) {
+__global__ void __launch_bounds__(TC_THREADS, 1) attn_tc_kernel(const AttnParams p, const Trace tr) {
     extern __shared__ uint8_t smem_raw[];
     const uint32_t raw = smem_u32(smem_raw);
     const uint32_t base = (raw + 1023u) & ~1023u;
@@ -245,6 +263,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) attn_tc_kernel(const AttnParams
                 const uint32_t b = it & 1u, st = it % NSTAGE;
                 ok = __all_sync(0xffffffffu, mbar_wait(bar(BAR_SREADY + b), (it >> 1) & 1u, abort_flag, W_SREADY));
                 if (!ok) break;
+                trace(tr, 10 + warp, it);
                 // the per-token scale arrays of this stage were published with the tile itself
                 ok = __all_sync(0xffffffffu, mbar_wait(bar(BAR_FULL + st), (it / NSTAGE) & 1u, abort_flag, W_FULL));
                 if (!ok) break;
@@ -273,6 +292,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) attn_tc_kernel(const AttnParams
                         x_max = fmaxf(x_max, fmaxf(fmaxf(z[t] - g4.x, z[t + 1] - g4.y), fmaxf(z[t + 2] - g4.z, z[t + 3] - g4.w)));
                     }
                 }
+                trace(tr, 15 + warp, it);
                 const bool grow = mx > m_run + RESCALE_TAU;   // false while the row has seen no valid entry
                 if (__any_sync(0xffffffffu, grow)) {
                     if (j > 0) {   // the accumulator holds earlier tiles: wait for the last P.V, then scale it
@@ -332,6 +352,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) attn_tc_kernel(const AttnParams
                 fence_proxy_async();
                 tc_fence_before();
                 mbar_arrive(bar(BAR_PREADY + b));
+                trace(tr, 20 + warp, it);
             }
             if (!ok) break;
             // ---- epilogue ---------------------------------------------------------------------
@@ -418,54 +439,14 @@ __global__ void __launch_bounds__(TC_THREADS, 1) attn_tc_kernel(const AttnParams
             int idx_next = fetch_idx(0);
 #pragma unroll 1
             for (int k = 0; k < w.nblk + PREFETCH && ok; ++k) {
-                if (k < w.nblk) {
-                    // -------- issue tile k
-                    const uint32_t t_it = it + k, st = t_it % NSTAGE;
-                    const int idx = idx_next;
-                    idx_next = fetch_idx(k + 1);
-                    if (t_it >= NSTAGE) {
-                        ok = __all_sync(0xffffffffu,
-                                        mbar_wait(bar(BAR_EMPTY + st), ((t_it / NSTAGE) - 1) & 1u, abort_flag, W_EMPTY));
-                        if (!ok) break;
-                    }
-                    const uint32_t sbase = base + ST_OFF + st * ST_BYTES;
-                    float4 sc = make_float4(0.f, 0.f, 0.f, 0.f);
-                    if (idx >= 0) {
-                        const uint8_t* src = kv_row_ptr(p.kv, idx, p.page_block_size, p.block_stride);
-#pragma unroll
-                        for (int c = 0; c < 16; ++c) {
-                            const int ch = hf * 16 + c;        // 16-byte chunk of the 512 no-PE bytes
-                            cp_async16(sbase + (ch >> 3) * KV_CHUNK + r * 128 + ((((uint32_t)ch & 7u) ^ sw) << 4), src + ch * 16);
-                        }
-#pragma unroll
-                        for (int c = 0; c < 4; ++c) {
-                            const int ch = hf * 4 + c;
-                            cp_async16(sbase + ST_ROPE + r * 128 + (((uint32_t)ch ^ sw) << 4), src + ROPE_OFF + ch * 16);
-                        }
-                        sc = __ldg(reinterpret_cast<const float4*>(src + SCALE_OFF));
-                    } else {
-                        uint8_t* sp = sm + ST_OFF + st * ST_BYTES;
-                        const uint4 zero = make_uint4(0, 0, 0, 0);
-#pragma unroll
-                        for (int c = 0; c < 16; ++c) {
-                            const int ch = hf * 16 + c;
-                            *reinterpret_cast<uint4*>(sp + (ch >> 3) * KV_CHUNK + r * 128 + ((((uint32_t)ch & 7u) ^ sw) << 4)) = zero;
-                        }
-#pragma unroll
-                        for (int c = 0; c < 4; ++c) {
-                            const int ch = hf * 4 + c;
-                            *reinterpret_cast<uint4*>(sp + ST_ROPE + r * 128 + (((uint32_t)ch ^ sw) << 4)) = zero;
-                        }
-                    }
-                    sc_c = sc;
-                    idx_c = idx;
-                }
-                cp_async_commit();
+                // Finishing tile k-2 comes first: the MMA warp needs it (score MMA of tile k-2) before it
+                // can retire the P.V of tile k-3, which is what frees the stage tile k goes into.
                 if (k >= PREFETCH) {
                     // -------- finish tile k - PREFETCH
                     const int kk = k - PREFETCH;
-                    cp_async_wait<PREFETCH>();
+                    cp_async_wait<PREFETCH - 1>();
                     const uint32_t t_it = it + kk, st = t_it % NSTAGE;
+                    trace(tr, 30 + warp, t_it);
                     uint8_t* sp = sm + ST_OFF + st * ST_BYTES;
                     float* tok = reinterpret_cast<float*>(sm + TOK_OFF + st * TOK_BYTES);
                     const float4 sc = sc_a;
@@ -506,7 +487,53 @@ __global__ void __launch_bounds__(TC_THREADS, 1) attn_tc_kernel(const AttnParams
                     }
                     fence_proxy_async();
                     mbar_arrive(bar(BAR_FULL + st));
+                    trace(tr, 40 + warp, t_it);
                 }
+                if (k < w.nblk) {
+                    // -------- issue tile k
+                    const uint32_t t_it = it + k, st = t_it % NSTAGE;
+                    const int idx = idx_next;
+                    idx_next = fetch_idx(k + 1);
+                    if (t_it >= NSTAGE) {
+                        ok = __all_sync(0xffffffffu,
+                                        mbar_wait(bar(BAR_EMPTY + st), ((t_it / NSTAGE) - 1) & 1u, abort_flag, W_EMPTY));
+                        if (!ok) break;
+                    }
+                    trace(tr, 50 + warp, t_it);
+                    const uint32_t sbase = base + ST_OFF + st * ST_BYTES;
+                    float4 sc = make_float4(0.f, 0.f, 0.f, 0.f);
+                    if (idx >= 0) {
+                        const uint8_t* src = kv_row_ptr(p.kv, idx, p.page_block_size, p.block_stride);
+#pragma unroll
+                        for (int c = 0; c < 16; ++c) {
+                            const int ch = hf * 16 + c;        // 16-byte chunk of the 512 no-PE bytes
+                            cp_async16(sbase + (ch >> 3) * KV_CHUNK + r * 128 + ((((uint32_t)ch & 7u) ^ sw) << 4), src + ch * 16);
+                        }
+#pragma unroll
+                        for (int c = 0; c < 4; ++c) {
+                            const int ch = hf * 4 + c;
+                            cp_async16(sbase + ST_ROPE + r * 128 + (((uint32_t)ch ^ sw) << 4), src + ROPE_OFF + ch * 16);
+                        }
+                        sc = __ldg(reinterpret_cast<const float4*>(src + SCALE_OFF));
+                    } else {
+                        uint8_t* sp = sm + ST_OFF + st * ST_BYTES;
+                        const uint4 zero = make_uint4(0, 0, 0, 0);
+#pragma unroll
+                        for (int c = 0; c < 16; ++c) {
+                            const int ch = hf * 16 + c;
+                            *reinterpret_cast<uint4*>(sp + (ch >> 3) * KV_CHUNK + r * 128 + ((((uint32_t)ch & 7u) ^ sw) << 4)) = zero;
+                        }
+#pragma unroll
+                        for (int c = 0; c < 4; ++c) {
+                            const int ch = hf * 4 + c;
+                            *reinterpret_cast<uint4*>(sp + ST_ROPE + r * 128 + (((uint32_t)ch ^ sw) << 4)) = zero;
+                        }
+                    }
+                    sc_c = sc;
+                    idx_c = idx;
+                    trace(tr, 60 + warp, t_it);
+                }
+                cp_async_commit();
                 sc_a = sc_b; idx_a = idx_b;
                 sc_b = sc_c; idx_b = idx_c;
             }
@@ -554,13 +581,16 @@ __global__ void __launch_bounds__(TC_THREADS, 1) attn_tc_kernel(const AttnParams
                     ok = __all_sync(0xffffffffu, mbar_wait(bar(BAR_FULL + nx % NSTAGE), (nx / NSTAGE) & 1u, abort_flag, W_FULL));
                     if (!ok) break;
                     tc_fence_after();
+                    trace(tr, 70, nx);
                     if (lane == 0) issue_qk(nx);
                     __syncwarp();
+                    trace(tr, 71, nx);
                 }
                 const uint32_t b = it & 1u, st = it % NSTAGE;
                 ok = __all_sync(0xffffffffu, mbar_wait(bar(BAR_PREADY + b), (it >> 1) & 1u, abort_flag, W_PREADY));
                 if (!ok) break;
                 tc_fence_after();
+                trace(tr, 72, it);
                 if (lane == 0) {
                     const uint32_t pb = base + P_OFF + b * P_BYTES;
                     const uint32_t vb = base + ST_OFF + st * ST_BYTES + (uint32_t)half * 2 * KV_CHUNK;
@@ -573,6 +603,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) attn_tc_kernel(const AttnParams
                     tc_commit(bar(BAR_PVDONE + b));
                 }
                 __syncwarp();
+                trace(tr, 73, it);
             }
         }
     }
@@ -593,6 +624,9 @@ __global__ void __launch_bounds__(TC_THREADS, 1) attn_tc_kernel(const AttnParams
 
 }  // namespace
 
+static Trace g_trace = {nullptr, 0};
+void set_attn_trace(long long* buf, int cap) { g_trace.buf = buf; g_trace.cap = cap; }
+
 int launch_attn_tc(const AttnParams& p, cudaStream_t stream) {
     if (p.num_tokens == 0) return 0;
     static bool attr_set[64] = {};
@@ -605,7 +639,7 @@ int launch_attn_tc(const AttnParams& p, cudaStream_t stream) {
         attr_set[dev] = true;
     }
     const int parts = p.sched ? p.num_parts : p.num_tokens;
-    attn_tc_kernel<<<2 * parts, TC_THREADS, SMEM_ALLOC, stream>>>(p);
+    attn_tc_kernel<<<2 * parts, TC_THREADS, SMEM_ALLOC, stream>>>(p, g_trace);
     return check_launch("attn_tc_kernel");
 }
 
