@@ -43,11 +43,12 @@ def load():
     global _lib
     if _lib is not None:
         return _lib
-    if not os.path.exists(LIB_PATH):
+    path = os.environ.get("SMLA_LIBRARY", LIB_PATH)   # an alternative build of the same library
+    if not os.path.exists(path):
         raise ImportError(
-            f"{LIB_PATH} is missing: build it with `python -m sparse_mla_sm120_b200.build` "
+            f"{path} is missing: build it with `python -m sparse_mla_sm120_b200.build` "
             "(needs nvcc); this library has no CPU fallback")
-    lib = ctypes.CDLL(LIB_PATH)
+    lib = ctypes.CDLL(path)
     for name, (res, args) in _SIGS.items():
         fn = getattr(lib, name)
         fn.restype = res

@@ -3,19 +3,23 @@
 // Work unit.  One CTA owns one scheduler partition (a run of 64-token blocks of consecutive
 // requests, see sched.cu; for prefill: one query token) and ONE HALF of the 512 output
 // dimensions, for all (<= 128) query heads at once: heads are the M = 128 rows of every MMA.
-// The fp32 output accumulator for 128 heads x 256 dims takes 256 of the 512 tensor-memory
-// columns; two 64-column score buffers take 128 more.  The two CTAs of a partition both compute
-// the scores (the score MMA is the cheaper part once everything is FP8) and are launched next
-// to each other so that the second gather of a row is served by L2.
+// Tensor memory (512 columns) holds everything that is reused: the fp32 output accumulator
+// (128 heads x 256 dims, 256 columns), two 64-column score buffers, and the quantised Q no-PE
+// operand (128 rows x 512 e4m3 = 128 columns).  The softmax weights P' are written back over the
+// score buffer they came from, so both Q and P' reach the tensor core as TMEM A operands and
+// shared memory only carries the gathered KV tiles (four 64-token stages) and Q RoPE.
+// The two CTAs of a partition both compute the scores and are launched next to each other so
+// that the second gather of a row is served by L2.
 //
 // Numerics (the FP8 class of the reference's V32 kernels, which quantise Q and P to e4m3:
 // csrc/kernel/common/fp8_quant.cuh:44-103, csrc/kernel/decode/decode_v2_kernel.cuh:414-493):
-//   * Q no-PE is quantised to e4m3 with one power-of-two scale per head; Q RoPE stays bf16 and
-//     is pre-divided by that scale.
+//   * Q no-PE is quantised to e4m3 with one power-of-two scale sq_h per head; Q RoPE stays bf16
+//     and is pre-divided by that scale.
 //   * K/V bytes are consumed as stored.  A row whose four 128-value tiles carry different
-//     scales is re-expressed against its largest scale (a power-of-two shift, exact until the
-//     e4m3 subnormal range); K RoPE is pre-divided by the row scale s_t.  One accumulator then
-//     holds  S = (q . k) / (sq_h * s_t)  for no-PE (FP8 MMA) and RoPE (BF16 MMA) together.
+//     scales is re-expressed against its largest scale s_t (a power-of-two shift, exact until the
+//     e4m3 subnormal range); K RoPE is pre-divided by s_t.  One accumulator then holds
+//     S = (q . k) / (sq_h * s_t) for no-PE (FP8 MMA) and RoPE (BF16 MMA) together.
+//     The row scales must be powers of two, as the cache format defines them.
 //   * The row scale of V is folded into the exponent: z = S*sq_h*s_t*sm_scale*log2e + log2(s_t),
 //     P' = 2^(z - m) with m the (lazily updated) running maximum of z, so that
 //     O_acc = sum_t P'_t * Vfp8_t needs no per-tile scale; the denominator is tracked apart as
@@ -25,12 +29,18 @@
 //   * Invalid entries (index < 0, position >= topk_length) are never loaded: their shared-memory
 //     rows are zero-filled and their weight is exactly 0 (NaN-safe, decode_v2_kernel.cuh:262-278).
 //
-// Warp roles (288 threads): warps 0-3 softmax + epilogue (thread = head row = TMEM lane),
-// warps 4-7 gather producers (cp.async 16 B into 128B-swizzled tiles, three stages),
-// warp 8 MMA issue (one lane) and TMEM allocation.  Every wait is bounded; a wait that gives up
-// records a code in status[] and the CTA drains and exits.
+// Warp roles (768 threads; the first five warpgroups trade registers with setmaxnreg): warps 0-7
+// softmax + epilogue (thread = head row = TMEM lane; warps w and w+4 share a lane quarter and
+// split the 64 score columns / the output columns), warps 8-11 gather issuers (coalesced 16-byte
+// cp.async into 128B-swizzled tiles, never waiting for data), warps 12-19 tile fix-up (scale
+// arrays, RoPE pre-division), warp 20 MMA issue (one lane) and TMEM allocation, warps 21-23 idle.  Every wait is bounded; a wait that gives up records a code in status[] and
+// the CTA drains and exits.
 #include "common.cuh"
 #include "sm100_ptx.cuh"
+
+#ifndef SMLA_DBG
+#define SMLA_DBG 0   // debugging switches for timing experiments: 1 skip softmax math, 2 skip fix-up work, 4 skip copies
+#endif
 
 namespace smla {
 
@@ -38,58 +48,75 @@ namespace {
 
 using namespace ptx;
 
-constexpr int TC_THREADS = 288;
-constexpr int NSTAGE = 3;
-constexpr int PREFETCH = 2;            // tiles in flight per producer thread
+constexpr int N_SM_WARPS = 8, N_PR_WARPS = 4, N_FX_WARPS = 8;
+constexpr int FX_ROWS = 8;    // rows of a tile per fix-up warp
+constexpr int FX_WARP0 = N_SM_WARPS + N_PR_WARPS;
+constexpr int MMA_WARP = FX_WARP0 + N_FX_WARPS;
+constexpr int TC_THREADS = (MMA_WARP + 4) * 32;   // the MMA warp's warpgroup is completed by three idle warps
+// Per-thread register budgets after the warpgroups trade registers.  The MMA warp's warpgroup
+// keeps its launch-time allocation (its single issuing thread must not spill).  setmaxnreg.inc
+// can only draw on what the CTA was launched with (TC_THREADS x REGS_LAUNCH), so the budgets
+// must fit it or the increase would block for ever; the launcher checks the compiled register
+// count against REGS_LAUNCH before it launches.
+constexpr int REGS_LAUNCH = 80, REGS_SOFTMAX = 128, REGS_OTHER = 48;
+static_assert(N_SM_WARPS * 32 * REGS_SOFTMAX + (N_PR_WARPS + N_FX_WARPS) * 32 * REGS_OTHER + 128 * REGS_LAUNCH
+                  <= TC_THREADS * REGS_LAUNCH, "register budgets exceed what the CTA owns");
+static_assert((N_SM_WARPS % 4) == 0 && (N_PR_WARPS % 4) == 0 && (N_FX_WARPS % 4) == 0, "setmaxnreg acts on whole warpgroups");
+static_assert(65536 / TC_THREADS / 8 * 8 == REGS_LAUNCH, "launch-time registers per thread");
+constexpr int NSTAGE = 4;
 constexpr int P_SHIFT = 5;             // P' is stored as e4m3(P' * 2^P_SHIFT)
 constexpr float RESCALE_TAU = 3.0f;    // lazy-rescale threshold (log2 units); P' <= 2^TAU
 
 // shared-memory map (bytes from a 1024-aligned base)
-constexpr uint32_t QN_OFF = 0;                       // Q no-PE e4m3: 4 k-chunks x [128 rows x 128 B]
-constexpr uint32_t QN_CHUNK = 128 * 128;
-constexpr uint32_t QR_OFF = QN_OFF + 4 * QN_CHUNK;   // Q RoPE bf16: [128 rows x 128 B]
+constexpr uint32_t QR_OFF = 0;                       // Q RoPE bf16, K-major 128B swizzle: [128 rows x 128 B]
 constexpr uint32_t ST_OFF = QR_OFF + 128 * 128;      // KV stages
 constexpr uint32_t KV_CHUNK = 64 * 128;              // one 128-dim chunk of a 64-token tile
-constexpr uint32_t ST_ROPE = 4 * KV_CHUNK;           // offset of the RoPE tile inside a stage
-constexpr uint32_t ST_BYTES = ST_ROPE + 64 * 128;
-constexpr uint32_t P_OFF = ST_OFF + NSTAGE * ST_BYTES;   // P' e4m3: 2 buffers x [4 k-chunks x 16 groups x 128 B]
-constexpr uint32_t P_BYTES = 128 * 64;
-constexpr uint32_t TOK_OFF = P_OFF + 2 * P_BYTES;    // per stage: s_t[64], log2 s_t[64], 1/s_t[64]
+constexpr uint32_t ST_ROPE = 4 * KV_CHUNK;           // RoPE tile inside a stage
+constexpr uint32_t ST_SCALE = ST_ROPE + 64 * 128;    // the rows' 4 fp32 scales, [64 x 16 B]
+constexpr uint32_t ST_BYTES = ST_SCALE + 64 * 16;    // 41984 = 41 * 1024
+constexpr uint32_t QSTG_OFF = ST_OFF + NSTAGE * ST_BYTES;   // Q staging, per softmax warp [32 rows x 144 B]
+constexpr uint32_t QSTG_ROW = 144;
+constexpr uint32_t QSTG_WARP = 32 * QSTG_ROW;
+constexpr uint32_t TOK_OFF = QSTG_OFF + N_SM_WARPS * QSTG_WARP;   // per stage: s_t[64], log2 s_t[64], 1/s_t[64]
 constexpr uint32_t TOK_BYTES = 3 * 64 * 4;
-constexpr uint32_t SQC_OFF = TOK_OFF + NSTAGE * TOK_BYTES;  // sq_h * sm_scale * log2e, [128]
-constexpr uint32_t BAR_OFF = SQC_OFF + 128 * 4;
-// barriers (8 B each): full[3] empty[3] s_ready[2] p_ready[2] pv_done[2] q_ready
-constexpr int BAR_FULL = 0, BAR_EMPTY = 3, BAR_SREADY = 6, BAR_PREADY = 8, BAR_PVDONE = 10, BAR_QREADY = 12, NBAR = 13;
+constexpr uint32_t XCH_OFF = TOK_OFF + NSTAGE * TOK_BYTES;   // pair exchange: [2 buffers][2 halves][128 rows] fp32
+constexpr uint32_t BAR_OFF = XCH_OFF + 2 * 2 * 128 * 4;
+// barriers (8 B each): full[4] empty[4] loaded[4] s_ready[2] p_ready[2] pv_done[2] q_ready
+constexpr int BAR_FULL = 0, BAR_EMPTY = NSTAGE, BAR_LOADED = 2 * NSTAGE, BAR_SREADY = 3 * NSTAGE,
+              BAR_PREADY = BAR_SREADY + 2, BAR_PVDONE = BAR_PREADY + 2, BAR_QREADY = BAR_PVDONE + 2, NBAR = BAR_QREADY + 1;
 constexpr uint32_t MISC_OFF = BAR_OFF + NBAR * 8;    // tmem base (4 B), abort flag (4 B)
 constexpr uint32_t SMEM_BYTES = MISC_OFF + 16;
 constexpr uint32_t SMEM_ALLOC = SMEM_BYTES + 1024;   // slack for the 1024-byte alignment
 static_assert(SMEM_ALLOC <= 227 * 1024, "shared memory budget");
+static_assert(ST_BYTES % 1024 == 0 && ST_OFF % 1024 == 0, "swizzled tiles need 1024-byte alignment");
 
 constexpr uint32_t TMEM_COLS = 512;
-constexpr uint32_t TM_O = 0, TM_S = 256;             // O: 256 columns; S buffer b at 256 + 64 b
+constexpr uint32_t TM_O = 0, TM_S = 256, TM_Q = 384;   // O 256 cols; S buffer b at 256 + 64 b; Q 128 cols
 
 constexpr uint32_t IDESC_QK_F8 = instr_desc(FMT_E4M3, FMT_E4M3, false, false, 128, 64);
 constexpr uint32_t IDESC_QK_BF16 = instr_desc(FMT_BF16, FMT_BF16, false, false, 128, 64);
 constexpr uint32_t IDESC_PV_F8 = instr_desc(FMT_E4M3, FMT_E4M3, false, true, 128, 256);
+constexpr uint32_t DESC_HI_SW128 = desc_hi(1024, (uint32_t)SWIZZLE_128B);
 
 // give-up codes reported through status[0]
-enum { W_EMPTY = 1, W_FULL = 2, W_SREADY = 3, W_PREADY = 4, W_PVDONE = 5, W_QREADY = 6 };
+enum { W_EMPTY = 1, W_FULL = 2, W_SREADY = 3, W_PREADY = 4, W_PVDONE = 5, W_QREADY = 6, W_LOADED = 7 };
 
-// Optional timeline of CTA 0 (debugging aid): records (tag, tile, clock) triples when a trace
-// buffer has been registered with smla_debug_set_trace.
+// Optional timeline of CTA 0 (debugging aid): when a trace buffer has been registered with
+// smla_debug_set_trace, lane 0 of every warp appends (tag, tile, SM clock) records to its own
+// region of the buffer with plain stores (no atomics, so that tracing does not stall the warp).
 struct Trace {
-    long long* buf;
+    long long* buf;   // [warps][cap][2]
     int cap;
 };
-__device__ __forceinline__ void trace(const Trace& t, int tag, int tile) {
-    if (t.buf != nullptr && blockIdx.x == 0 && (threadIdx.x & 31) == 0) {
-        const int slot = atomicAdd(reinterpret_cast<int*>(t.buf), 1);
-        if (slot < t.cap) {
-            long long c;
-            asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(c));
-            t.buf[1 + 2 * slot] = ((long long)tag << 32) | (unsigned)tile;
-            t.buf[2 + 2 * slot] = c;
-        }
+struct TraceCursor {
+    int n = 0;
+};
+__device__ __forceinline__ void trace(const Trace& t, TraceCursor& c, int tag, int tile) {
+    if (t.buf != nullptr && blockIdx.x == 0 && (threadIdx.x & 31) == 0 && c.n < t.cap) {
+        long long* slot = t.buf + ((size_t)(threadIdx.x >> 5) * t.cap + c.n) * 2;
+        slot[0] = ((long long)tag << 32) | (unsigned)tile;
+        slot[1] = clock64();
+        ++c.n;
     }
 }
 
@@ -160,31 +187,39 @@ __device__ __forceinline__ uint32_t mul_bf16x2(uint32_t w, __nv_bfloat162 f) {
     return *reinterpret_cast<uint32_t*>(&r);
 }
 
+__device__ __forceinline__ float bf16lo(uint32_t w) { return __uint_as_float(w << 16); }
+__device__ __forceinline__ float bf16hi(uint32_t w) { return __uint_as_float(w & 0xffff0000u); }
+
 // ---------------------------------------------------------------------------------------------
 __global__ void __launch_bounds__(TC_THREADS, 1) attn_tc_kernel(const AttnParams p, const Trace tr) {
     extern __shared__ uint8_t smem_raw[];
     const uint32_t raw = smem_u32(smem_raw);
     const uint32_t base = (raw + 1023u) & ~1023u;
     uint8_t* sm = smem_raw + (base - raw);
-    float* sqc = reinterpret_cast<float*>(sm + SQC_OFF);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(sm + MISC_OFF + 4);
     volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(sm + MISC_OFF);
     auto bar = [&](int i) -> uint32_t { return base + BAR_OFF + 8u * i; };
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int part = blockIdx.x >> 1, half = blockIdx.x & 1;
+    TraceCursor tc;
     const SchedMeta meta = load_meta(p, part);
 
     if (tid == 0) {
-        for (int s = 0; s < NSTAGE; ++s) { mbar_init(bar(BAR_FULL + s), 128); mbar_init(bar(BAR_EMPTY + s), 1); }
-        for (int b = 0; b < 2; ++b) {
-            mbar_init(bar(BAR_SREADY + b), 1); mbar_init(bar(BAR_PREADY + b), 128); mbar_init(bar(BAR_PVDONE + b), 1);
+        for (int s = 0; s < NSTAGE; ++s) {
+            mbar_init(bar(BAR_FULL + s), N_FX_WARPS * 32);
+            mbar_init(bar(BAR_EMPTY + s), 1);
+            mbar_init(bar(BAR_LOADED + s), N_PR_WARPS * 32);       // one arrive per issuer thread, when its copies have landed
         }
-        mbar_init(bar(BAR_QREADY), 128);
+        for (int b = 0; b < 2; ++b) {
+            mbar_init(bar(BAR_SREADY + b), 1); mbar_init(bar(BAR_PREADY + b), N_SM_WARPS * 32);
+            mbar_init(bar(BAR_PVDONE + b), 1);
+        }
+        mbar_init(bar(BAR_QREADY), N_SM_WARPS * 32);
         *abort_flag = 0;
         mbar_init_fence();
     }
-    if (warp == 8) {
+    if (warp == MMA_WARP) {
         tmem_alloc(base + MISC_OFF, TMEM_COLS);
         tmem_relinquish();
     }
@@ -195,188 +230,202 @@ __global__ void __launch_bounds__(TC_THREADS, 1) attn_tc_kernel(const AttnParams
 
     const int last_req = min(meta.end_req, p.num_tokens - 1);
 
-    if (warp < 4) {
+    if (!(SMLA_DBG & 32)) {
+        if (warp < N_SM_WARPS) setmaxnreg_inc<REGS_SOFTMAX>();
+        else if (warp < MMA_WARP) setmaxnreg_dec<REGS_OTHER>();
+    }
+
+    if ((SMLA_DBG & 8) && warp != MMA_WARP) {
+        // timing experiment: only the MMA warp runs
+    } else if (warp < N_SM_WARPS) {
         // =================================================================== softmax + epilogue
-        const int row = tid;                      // head index == TMEM lane
-        const uint32_t lane_addr = tmem + ((uint32_t)(warp * 32) << 16);
-        uint32_t it = 0, rq = 0;                  // running tile / request counters of this CTA
+        const int quarter = warp & 3, hh = warp >> 2;     // TMEM lane quarter, column half
+        const int row = quarter * 32 + lane;              // head index == TMEM lane
+        const uint32_t lane_addr = tmem + ((uint32_t)(quarter * 32) << 16);
+        float* xch = reinterpret_cast<float*>(sm + XCH_OFF);   // [2][2][128]
+        uint8_t* qstg = sm + QSTG_OFF + warp * QSTG_WARP;
+        const bool live = row < p.num_heads;
+        uint32_t it = 0;                          // running tile counter of this CTA
         bool ok = true;
         for (int req = meta.begin_req; req <= last_req && ok; ++req) {
             Work w;
             if (!get_work(p, meta, req, w)) continue;
-            // ---- Q: load, quantise, store in the 128B-swizzled K-major layout ----------------
-            for (int r0 = warp * 32; r0 < warp * 32 + 32; r0 += 4) {
-                uint4 a[4], b[4], c[4];
+            // ---- Q: this warp owns rows [32*quarter, +32) x no-PE dims [256*hh, +256) -----------
+            const __nv_bfloat16* qbase = p.q + ((size_t)req * p.num_heads + quarter * 32) * D_QK + hh * 256;
+            const int rows_here = min(max(p.num_heads - quarter * 32, 0), 32);
+            float amax_mine = 0.f;                // lane r ends up with the amax of row r (this half)
+#pragma unroll 1
+            for (int r0 = 0; r0 < 32; r0 += 8) {
+                float am[8];
 #pragma unroll
-                for (int u = 0; u < 4; ++u) {
-                    const int h = r0 + u;
-                    a[u] = b[u] = c[u] = make_uint4(0, 0, 0, 0);
-                    if (h < p.num_heads) {
-                        const __nv_bfloat16* src = p.q + ((size_t)req * p.num_heads + h) * D_QK;
-                        a[u] = __ldg(reinterpret_cast<const uint4*>(src + lane * 16));
-                        b[u] = __ldg(reinterpret_cast<const uint4*>(src + lane * 16 + 8));
-                        if (lane < 8) c[u] = __ldg(reinterpret_cast<const uint4*>(src + D_NOPE + lane * 8));
-                    }
+                for (int u = 0; u < 8; ++u) {
+                    uint4 a = make_uint4(0, 0, 0, 0);
+                    if (r0 + u < rows_here) a = __ldg(reinterpret_cast<const uint4*>(qbase + (size_t)(r0 + u) * D_QK + lane * 8));
+                    am[u] = fmaxf(fmaxf(fmaxf(fabsf(bf16lo(a.x)), fabsf(bf16hi(a.x))), fmaxf(fabsf(bf16lo(a.y)), fabsf(bf16hi(a.y)))),
+                                  fmaxf(fmaxf(fabsf(bf16lo(a.z)), fabsf(bf16hi(a.z))), fmaxf(fabsf(bf16lo(a.w)), fabsf(bf16hi(a.w)))));
                 }
 #pragma unroll
-                for (int u = 0; u < 4; ++u) {
-                    const int h = r0 + u;
-                    const uint32_t wd[8] = {a[u].x, a[u].y, a[u].z, a[u].w, b[u].x, b[u].y, b[u].z, b[u].w};
-                    float v[16];
-                    float amax = 0.f;
+                for (int o = 16; o >= 1; o >>= 1) {
 #pragma unroll
-                    for (int i = 0; i < 8; ++i) {
-                        v[2 * i] = __uint_as_float(wd[i] << 16);
-                        v[2 * i + 1] = __uint_as_float(wd[i] & 0xffff0000u);
-                        amax = fmaxf(amax, fmaxf(fabsf(v[2 * i]), fabsf(v[2 * i + 1])));
-                    }
-                    amax = warp_max(amax);
-                    const float sq = pow2_ceil(fmaxf(amax, 1e-4f) * (1.f / 448.f));
-                    const float inv = 1.f / sq;
-                    uint4 o;
-                    o.x = pack_e4m3x4(v[0] * inv, v[1] * inv, v[2] * inv, v[3] * inv);
-                    o.y = pack_e4m3x4(v[4] * inv, v[5] * inv, v[6] * inv, v[7] * inv);
-                    o.z = pack_e4m3x4(v[8] * inv, v[9] * inv, v[10] * inv, v[11] * inv);
-                    o.w = pack_e4m3x4(v[12] * inv, v[13] * inv, v[14] * inv, v[15] * inv);
-                    const uint32_t sw = (uint32_t)(h & 7);
-                    *reinterpret_cast<uint4*>(sm + QN_OFF + (lane >> 3) * QN_CHUNK + h * 128 + (((lane & 7) ^ sw) << 4)) = o;
-                    if (lane < 8) {
-                        const __nv_bfloat162 f = __float2bfloat162_rn(inv);
-                        uint4 r;
-                        r.x = mul_bf16x2(c[u].x, f); r.y = mul_bf16x2(c[u].y, f);
-                        r.z = mul_bf16x2(c[u].z, f); r.w = mul_bf16x2(c[u].w, f);
-                        *reinterpret_cast<uint4*>(sm + QR_OFF + h * 128 + ((lane ^ sw) << 4)) = r;
-                    }
-                    if (lane == 0) sqc[h] = (h < p.num_heads) ? sq * p.sm_scale * LOG2E : 0.f;
+                    for (int u = 0; u < 8; ++u) am[u] = fmaxf(am[u], __shfl_xor_sync(0xffffffffu, am[u], o));
                 }
+#pragma unroll
+                for (int u = 0; u < 8; ++u) if (lane == r0 + u) amax_mine = am[u];
             }
+            // both halves of a row agree on one scale
+            xch[hh * 128 + row] = amax_mine;
+            named_bar_sync(1 + quarter, 64);
+            const float amax = fmaxf(amax_mine, xch[(1 - hh) * 128 + row]);
+            const float sq = pow2_ceil(fmaxf(amax, 1e-4f) * (1.f / 448.f));
+            const float inv_sq = __uint_as_float(0x7f000000u - __float_as_uint(sq));   // 1/sq, sq a power of two
+            const float my_sqc = live ? sq * p.sm_scale * LOG2E : 0.f;
+            named_bar_sync(1 + quarter, 64);   // xch may be reused
+            // quantise, transpose through the warp's staging slab, store to tensor memory
+#pragma unroll 1
+            for (int qq = 0; qq < 2; ++qq) {
+#pragma unroll 8
+                for (int r = 0; r < 32; ++r) {
+                    uint2 a = make_uint2(0, 0);
+                    if (r < rows_here) a = __ldg(reinterpret_cast<const uint2*>(qbase + (size_t)r * D_QK + qq * 128 + lane * 4));
+                    const float s = __shfl_sync(0xffffffffu, inv_sq, r);
+                    *reinterpret_cast<uint32_t*>(qstg + r * QSTG_ROW + lane * 4) =
+                        pack_e4m3x4(bf16lo(a.x) * s, bf16hi(a.x) * s, bf16lo(a.y) * s, bf16hi(a.y) * s);
+                }
+                __syncwarp();
+                uint32_t wq[32];
+#pragma unroll
+                for (int c = 0; c < 8; ++c) {
+                    const uint4 v = *reinterpret_cast<const uint4*>(qstg + lane * QSTG_ROW + c * 16);
+                    wq[4 * c] = v.x; wq[4 * c + 1] = v.y; wq[4 * c + 2] = v.z; wq[4 * c + 3] = v.w;
+                }
+                tmem_st32(lane_addr + TM_Q + hh * 64 + qq * 32, wq);
+                __syncwarp();
+            }
+            // Q RoPE: warp (quarter, hh) stores rows [16*hh, +16) of its quarter, pre-divided by sq
+#pragma unroll
+            for (int g = 0; g < 4; ++g) {
+                const int rl = hh * 16 + g * 4 + (lane >> 3);          // row inside the quarter
+                const int h = quarter * 32 + rl;
+                uint4 c = make_uint4(0, 0, 0, 0);
+                if (h < p.num_heads)
+                    c = __ldg(reinterpret_cast<const uint4*>(p.q + ((size_t)req * p.num_heads + h) * D_QK + D_NOPE + (lane & 7) * 8));
+                const __nv_bfloat162 f = __float2bfloat162_rn(__shfl_sync(0xffffffffu, inv_sq, rl));
+                c.x = mul_bf16x2(c.x, f); c.y = mul_bf16x2(c.y, f); c.z = mul_bf16x2(c.z, f); c.w = mul_bf16x2(c.w, f);
+                *reinterpret_cast<uint4*>(sm + QR_OFF + h * 128 + ((((uint32_t)lane & 7u) ^ ((uint32_t)h & 7u)) << 4)) = c;
+            }
+            tmem_wait_st();
             fence_proxy_async();
-            tc_fence_before();     // orders the previous epilogue's TMEM reads before the next MMAs
+            tc_fence_before();     // also orders the previous epilogue's TMEM reads before the next MMAs
             mbar_arrive(bar(BAR_QREADY));
-            __syncwarp();
-            const float my_sqc = sqc[row];
 
             float m_run = -INFINITY;   // running maximum of z (lags by at most RESCALE_TAU)
-            float l_run = 0.f;         // sum of P'/s_t
-            float x_max = -INFINITY;   // running maximum of the scaled logits (max_logits output)
+            float l_run = 0.f;         // this half's sum of P'/s_t (scaled by 2^P_SHIFT)
+            float x_max = -INFINITY;   // this half's maximum of the scaled logits (max_logits output)
             for (int j = 0; j < w.nblk && ok; ++j, ++it) {
                 const uint32_t b = it & 1u, st = it % NSTAGE;
-                ok = __all_sync(0xffffffffu, mbar_wait(bar(BAR_SREADY + b), (it >> 1) & 1u, abort_flag, W_SREADY));
+                ok = (mbar_wait(bar(BAR_SREADY + b), (it >> 1) & 1u, abort_flag, W_SREADY));
                 if (!ok) break;
-                trace(tr, 10 + warp, it);
                 // the per-token scale arrays of this stage were published with the tile itself
-                ok = __all_sync(0xffffffffu, mbar_wait(bar(BAR_FULL + st), (it / NSTAGE) & 1u, abort_flag, W_FULL));
+                ok = (mbar_wait(bar(BAR_FULL + st), (it / NSTAGE) & 1u, abort_flag, W_FULL));
                 if (!ok) break;
                 tc_fence_after();
-                uint32_t sv[2][32];
-                tmem_ld32(lane_addr + TM_S + 64 * b, sv[0]);
-                tmem_ld32(lane_addr + TM_S + 64 * b + 32, sv[1]);
+                trace(tr, tc, 10 + warp, it);
+                if (SMLA_DBG & 1) { tc_fence_before(); mbar_arrive(bar(BAR_PREADY + b)); continue; }
+                uint32_t sv[32];
+                tmem_ld32(lane_addr + TM_S + 64 * b + 32 * hh, sv);
+                const float* tok = reinterpret_cast<const float*>(sm + TOK_OFF + st * TOK_BYTES) + 32 * hh;
                 tmem_wait_ld();
-                const float* tok = reinterpret_cast<const float*>(sm + TOK_OFF + st * TOK_BYTES);
-                float z[64];
-                float mx = -INFINITY;
+                float z[32];
+                float mx0 = -INFINITY, mx1 = -INFINITY;
 #pragma unroll
-                for (int t = 0; t < 64; t += 4) {
+                for (int t = 0; t < 32; t += 4) {
                     const float4 s4 = *reinterpret_cast<const float4*>(tok + t);
                     const float4 g4 = *reinterpret_cast<const float4*>(tok + 64 + t);
-                    z[t + 0] = fmaf(__uint_as_float(sv[t >> 5][(t + 0) & 31]) * s4.x, my_sqc, g4.x);
-                    z[t + 1] = fmaf(__uint_as_float(sv[t >> 5][(t + 1) & 31]) * s4.y, my_sqc, g4.y);
-                    z[t + 2] = fmaf(__uint_as_float(sv[t >> 5][(t + 2) & 31]) * s4.z, my_sqc, g4.z);
-                    z[t + 3] = fmaf(__uint_as_float(sv[t >> 5][(t + 3) & 31]) * s4.w, my_sqc, g4.w);
-                    mx = fmaxf(mx, fmaxf(fmaxf(z[t], z[t + 1]), fmaxf(z[t + 2], z[t + 3])));
-                }
-                if (p.out_max_logits != nullptr) {
-#pragma unroll
-                    for (int t = 0; t < 64; t += 4) {
-                        const float4 g4 = *reinterpret_cast<const float4*>(tok + 64 + t);
+                    z[t + 0] = fmaf(__uint_as_float(sv[t + 0]) * s4.x, my_sqc, g4.x);
+                    z[t + 1] = fmaf(__uint_as_float(sv[t + 1]) * s4.y, my_sqc, g4.y);
+                    z[t + 2] = fmaf(__uint_as_float(sv[t + 2]) * s4.z, my_sqc, g4.z);
+                    z[t + 3] = fmaf(__uint_as_float(sv[t + 3]) * s4.w, my_sqc, g4.w);
+                    mx0 = fmaxf(mx0, fmaxf(z[t], z[t + 1]));
+                    mx1 = fmaxf(mx1, fmaxf(z[t + 2], z[t + 3]));
+                    if (p.out_max_logits != nullptr)   // z - log2(s_t) is the scaled logit itself (NaN for masked entries is ignored by fmaxf)
                         x_max = fmaxf(x_max, fmaxf(fmaxf(z[t] - g4.x, z[t + 1] - g4.y), fmaxf(z[t + 2] - g4.z, z[t + 3] - g4.w)));
-                    }
                 }
-                trace(tr, 15 + warp, it);
+                // row maximum over both column halves
+                xch[b * 256 + hh * 128 + row] = fmaxf(mx0, mx1);
+                named_bar_sync(1 + quarter, 64);   // also: both warps have finished reading S[b]
+                const float mx = fmaxf(fmaxf(mx0, mx1), xch[b * 256 + (1 - hh) * 128 + row]);
+                trace(tr, tc, 20 + warp, it);
                 const bool grow = mx > m_run + RESCALE_TAU;   // false while the row has seen no valid entry
                 if (__any_sync(0xffffffffu, grow)) {
                     if (j > 0) {   // the accumulator holds earlier tiles: wait for the last P.V, then scale it
-                        ok = __all_sync(0xffffffffu,
-                                        mbar_wait(bar(BAR_PVDONE + ((it - 1) & 1u)), ((it - 1) >> 1) & 1u, abort_flag, W_PVDONE));
+                        ok = (mbar_wait(bar(BAR_PVDONE + ((it - 1) & 1u)), ((it - 1) >> 1) & 1u, abort_flag, W_PVDONE));
                         if (!ok) break;
                         tc_fence_after();
                     }
-                    const float alpha = grow ? exp2f(m_run - mx) : 1.f;   // exp2(-inf) = 0 for the first tile
+                    const float alpha = grow ? ex2(m_run - mx) : 1.f;   // 2^-inf = 0 for the first tile
                     if (grow) { m_run = mx; l_run *= alpha; }
                     if (j > 0) {
 #pragma unroll 1
-                        for (int c = 0; c < 256; c += 32) {
+                        for (int c = 0; c < 128; c += 32) {
                             uint32_t o[32];
-                            tmem_ld32(lane_addr + TM_O + c, o);
+                            tmem_ld32(lane_addr + TM_O + 128 * hh + c, o);
                             tmem_wait_ld();
 #pragma unroll
                             for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
-                            tmem_st32(lane_addr + TM_O + c, o);
+                            tmem_st32(lane_addr + TM_O + 128 * hh + c, o);
                         }
                         tmem_wait_st();
                     }
                 }
-                const float m_use = (m_run == -INFINITY) ? 0.f : m_run;
-                // the P' buffer of tile it was last read by the P.V of tile it-2
-                if (it >= 2) {
-                    ok = __all_sync(0xffffffffu,
-                                    mbar_wait(bar(BAR_PVDONE + b), ((it - 2) >> 1) & 1u, abort_flag, W_PVDONE));
-                    if (!ok) break;
-                }
-                uint8_t* pbuf = sm + P_OFF + b * P_BYTES + (row >> 3) * 128 + (row & 7) * 16;
-                float lsum = 0.f;
+                const float m_off = ((m_run == -INFINITY) ? 0.f : m_run) - (float)P_SHIFT;
+                uint32_t pw[8];
+                float l0 = 0.f, l1 = 0.f;
 #pragma unroll
-                for (int t = 0; t < 64; t += 16) {
-                    float pv[16];
-#pragma unroll
-                    for (int i = 0; i < 16; i += 4) {
-                        const float4 i4 = *reinterpret_cast<const float4*>(tok + 128 + t + i);
-                        pv[i + 0] = ex2(z[t + i + 0] - m_use);
-                        pv[i + 1] = ex2(z[t + i + 1] - m_use);
-                        pv[i + 2] = ex2(z[t + i + 2] - m_use);
-                        pv[i + 3] = ex2(z[t + i + 3] - m_use);
-                        lsum = fmaf(pv[i + 0], i4.x, lsum);
-                        lsum = fmaf(pv[i + 1], i4.y, lsum);
-                        lsum = fmaf(pv[i + 2], i4.z, lsum);
-                        lsum = fmaf(pv[i + 3], i4.w, lsum);
-                    }
-                    constexpr float PS = (float)(1 << P_SHIFT);
-                    uint4 o;
-                    o.x = pack_e4m3x4(pv[0] * PS, pv[1] * PS, pv[2] * PS, pv[3] * PS);
-                    o.y = pack_e4m3x4(pv[4] * PS, pv[5] * PS, pv[6] * PS, pv[7] * PS);
-                    o.z = pack_e4m3x4(pv[8] * PS, pv[9] * PS, pv[10] * PS, pv[11] * PS);
-                    o.w = pack_e4m3x4(pv[12] * PS, pv[13] * PS, pv[14] * PS, pv[15] * PS);
-                    *reinterpret_cast<uint4*>(pbuf + (t >> 4) * 2048) = o;   // k-chunk t/16, 16 tokens = 16 B
+                for (int t = 0; t < 32; t += 4) {
+                    const float4 i4 = *reinterpret_cast<const float4*>(tok + 128 + t);
+                    const float p0 = ex2(z[t + 0] - m_off), p1 = ex2(z[t + 1] - m_off);
+                    const float p2 = ex2(z[t + 2] - m_off), p3 = ex2(z[t + 3] - m_off);
+                    l0 = fmaf(p0, i4.x, l0); l1 = fmaf(p1, i4.y, l1);
+                    l0 = fmaf(p2, i4.z, l0); l1 = fmaf(p3, i4.w, l1);
+                    pw[t >> 2] = pack_e4m3x4(p0, p1, p2, p3);
                 }
-                l_run += lsum;
-                fence_proxy_async();
+                l_run += l0 + l1;
+                // P' of tokens [32*hh, +32) goes over the first 16 columns of the score buffer
+                tmem_st8(lane_addr + TM_S + 64 * b + 8 * hh, pw);
+                tmem_wait_st();
                 tc_fence_before();
                 mbar_arrive(bar(BAR_PREADY + b));
-                trace(tr, 20 + warp, it);
+                trace(tr, tc, 30 + warp, it);
             }
             if (!ok) break;
             // ---- epilogue ---------------------------------------------------------------------
             {
                 const uint32_t last = it - 1;
-                ok = __all_sync(0xffffffffu, mbar_wait(bar(BAR_PVDONE + (last & 1u)), (last >> 1) & 1u, abort_flag, W_PVDONE));
+                ok = (mbar_wait(bar(BAR_PVDONE + (last & 1u)), (last >> 1) & 1u, abort_flag, W_PVDONE));
                 if (!ok) break;
                 tc_fence_after();
-                const bool live = row < p.num_heads;
-                float lse = (l_run > 0.f) ? (log2f(l_run) + m_run) : NEG_BIG;
-                float denom = l_run;
+                named_bar_sync(1 + quarter, 64);   // the partner has read the last tile's row maximum
+                xch[hh * 128 + row] = l_run;
+                xch[256 + hh * 128 + row] = x_max;
+                named_bar_sync(1 + quarter, 64);
+                const float l_all = l_run + xch[(1 - hh) * 128 + row];
+                const float xm = fmaxf(x_max, xch[256 + (1 - hh) * 128 + row]);
+                float lse = (l_all > 0.f) ? (log2f(l_all) - (float)P_SHIFT + m_run) : NEG_BIG;
+                float denom = l_all;
                 if (w.no_split && p.attn_sink != nullptr && live) {
                     const float sink2 = p.attn_sink[row] * LOG2E;
-                    denom = l_run + ((m_run == -INFINITY) ? INFINITY : exp2f(sink2 - m_run));
+                    denom = l_all + ((m_run == -INFINITY) ? INFINITY : exp2f(sink2 - m_run + (float)P_SHIFT));
                     if (lse != NEG_BIG) lse += log2f(1.f + exp2f(sink2 - lse));
                     else lse = sink2;
                 }
-                const float inv = (denom > 0.f) ? 1.f / (denom * (float)(1 << P_SHIFT)) : 0.f;
+                const float inv = (denom > 0.f) ? 1.f / denom : 0.f;
+                const int col0 = half * 256 + hh * 128;
                 if (w.no_split) {
-                    __nv_bfloat16* dst = p.out + ((size_t)req * p.num_heads + row) * D_V + half * 256;
+                    __nv_bfloat16* dst = p.out + ((size_t)req * p.num_heads + row) * D_V + col0;
 #pragma unroll 1
-                    for (int c = 0; c < 256; c += 32) {
+                    for (int c = 0; c < 128; c += 32) {
                         uint32_t o[32];
-                        tmem_ld32(lane_addr + TM_O + c, o);
+                        tmem_ld32(lane_addr + TM_O + 128 * hh + c, o);
                         tmem_wait_ld();
                         if (live) {
 #pragma unroll
@@ -392,16 +441,16 @@ __global__ void __launch_bounds__(TC_THREADS, 1) attn_tc_kernel(const AttnParams
                             }
                         }
                     }
-                    if (live && half == 0) {
+                    if (live && half == 0 && hh == 0) {
                         p.out_lse[(size_t)req * p.num_heads + row] = lse;
-                        if (p.out_max_logits) p.out_max_logits[(size_t)req * p.num_heads + row] = (x_max == -INFINITY) ? NEG_BIG : x_max;
+                        if (p.out_max_logits) p.out_max_logits[(size_t)req * p.num_heads + row] = (xm == -INFINITY) ? NEG_BIG : xm;
                     }
                 } else {
-                    float* dst = p.o_accum + ((size_t)w.split_idx * p.num_heads + row) * D_V + half * 256;
+                    float* dst = p.o_accum + ((size_t)w.split_idx * p.num_heads + row) * D_V + col0;
 #pragma unroll 1
-                    for (int c = 0; c < 256; c += 32) {
+                    for (int c = 0; c < 128; c += 32) {
                         uint32_t o[32];
-                        tmem_ld32(lane_addr + TM_O + c, o);
+                        tmem_ld32(lane_addr + TM_O + 128 * hh + c, o);
                         tmem_wait_ld();
                         if (live) {
 #pragma unroll
@@ -412,198 +461,231 @@ __global__ void __launch_bounds__(TC_THREADS, 1) attn_tc_kernel(const AttnParams
                             }
                         }
                     }
-                    if (live && half == 0) p.lse_accum[(size_t)w.split_idx * p.num_heads + row] = lse;
+                    if (live && half == 0 && hh == 0) p.lse_accum[(size_t)w.split_idx * p.num_heads + row] = lse;
                 }
+                named_bar_sync(1 + quarter, 64);   // xch is free again
             }
-            ++rq;
         }
-        (void)rq;
-    } else if (warp < 8) {
-        // =================================================================== gather producers
-        const int ptid = tid - 128;
-        const int r = ptid >> 1, hf = ptid & 1;    // token row inside the tile, half of the row
-        const uint32_t sw = (uint32_t)(r & 7);
+    } else if (warp < FX_WARP0) {
+        // =================================================================== gather issuers
+        // Warp pw gathers rows [16*pw, +16) of every tile and never waits for data.  Lane l copies
+        // 16-byte chunk l of the 512 no-PE bytes of each of those rows (one 512-byte coalesced
+        // request per row), chunk l%8 of the RoPE bytes of rows 4g + l/8, and lanes 0-15 the rows'
+        // scale words.  Rows without an entry are zero-filled here.  Completion reaches the fix-up
+        // warps through the LOADED barrier: one plain arrive per thread (releases the zero fills)
+        // plus one arrive that fires when the thread's copies have landed.
+        const int pw = warp - N_SM_WARPS;
+        const int row0 = pw * 16;
+        const int my_row = row0 + (lane & 15);
+        const int pbs_shift = (p.page_block_size & (p.page_block_size - 1)) == 0 ? __ffs(p.page_block_size) - 1 : -1;
         uint32_t it = 0;
         bool ok = true;
         for (int req = meta.begin_req; req <= last_req && ok; ++req) {
             Work w;
             if (!get_work(p, meta, req, w)) continue;
             const int32_t* idx_row = p.indices + (size_t)req * p.topk;
-            static_assert(PREFETCH == 2, "the in-flight bookkeeping below is written for two tiles");
-            float4 sc_a = make_float4(0.f, 0.f, 0.f, 0.f), sc_b = sc_a, sc_c = sc_a;   // scales of tiles k-2, k-1, k
-            int idx_a = -1, idx_b = -1, idx_c = -1;
             auto fetch_idx = [&](int j) -> int {
-                const int pos = (w.blk0 + j) * BLOCK_N + r;
+                const int pos = (w.blk0 + j) * BLOCK_N + my_row;
                 return (j < w.nblk && pos < w.len) ? __ldg(idx_row + pos) : -1;
             };
-            int idx_next = fetch_idx(0);
+            int idx_next = fetch_idx(0), idx_next2 = fetch_idx(1);
 #pragma unroll 1
-            for (int k = 0; k < w.nblk + PREFETCH && ok; ++k) {
-                // Finishing tile k-2 comes first: the MMA warp needs it (score MMA of tile k-2) before it
-                // can retire the P.V of tile k-3, which is what frees the stage tile k goes into.
-                if (k >= PREFETCH) {
-                    // -------- finish tile k - PREFETCH
-                    const int kk = k - PREFETCH;
-                    cp_async_wait<PREFETCH - 1>();
-                    const uint32_t t_it = it + kk, st = t_it % NSTAGE;
-                    trace(tr, 30 + warp, t_it);
-                    uint8_t* sp = sm + ST_OFF + st * ST_BYTES;
-                    float* tok = reinterpret_cast<float*>(sm + TOK_OFF + st * TOK_BYTES);
-                    const float4 sc = sc_a;
-                    const bool valid = idx_a >= 0;
-                    const float smax = fmaxf(fmaxf(sc.x, sc.y), fmaxf(sc.z, sc.w));
-                    if (valid) {
-                        const float inv_s = 1.f / smax;
-                        // no-PE tiles whose scale is below the row scale: shift them onto the row scale
-                        const float mine[2] = {hf ? sc.z : sc.x, hf ? sc.w : sc.y};
-#pragma unroll
-                        for (int q = 0; q < 2; ++q) {
-                            if (mine[q] != smax) {
-                                const __half2 ratio = __float2half2_rn(mine[q] * inv_s);
-                                uint8_t* rowp = sp + (hf * 2 + q) * KV_CHUNK + r * 128;
-#pragma unroll
-                                for (int c = 0; c < 8; ++c) {
-                                    uint4 v = *reinterpret_cast<uint4*>(rowp + c * 16);
-                                    v.x = rescale_e4m3x4(v.x, ratio); v.y = rescale_e4m3x4(v.y, ratio);
-                                    v.z = rescale_e4m3x4(v.z, ratio); v.w = rescale_e4m3x4(v.w, ratio);
-                                    *reinterpret_cast<uint4*>(rowp + c * 16) = v;
-                                }
-                            }
-                        }
-                        // RoPE part of K, pre-divided by the row scale
-                        const __nv_bfloat162 f = __float2bfloat162_rn(inv_s);
-#pragma unroll
-                        for (int c = 0; c < 4; ++c) {
-                            const int ch = hf * 4 + c;
-                            uint4* q4 = reinterpret_cast<uint4*>(sp + ST_ROPE + r * 128 + (((uint32_t)ch ^ sw) << 4));
-                            uint4 v = *q4;
-                            v.x = mul_bf16x2(v.x, f); v.y = mul_bf16x2(v.y, f);
-                            v.z = mul_bf16x2(v.z, f); v.w = mul_bf16x2(v.w, f);
-                            *q4 = v;
-                        }
-                        if (hf == 0) { tok[r] = smax; tok[64 + r] = log2f(smax); tok[128 + r] = inv_s; }
-                    } else if (hf == 0) {
-                        tok[r] = 0.f; tok[64 + r] = -INFINITY; tok[128 + r] = 0.f;
-                    }
-                    fence_proxy_async();
-                    mbar_arrive(bar(BAR_FULL + st));
-                    trace(tr, 40 + warp, t_it);
+            for (int k = 0; k < w.nblk && ok; ++k) {
+                const uint32_t t_it = it + k, st = t_it % NSTAGE;
+                const int idx = idx_next;
+                idx_next = idx_next2;
+                idx_next2 = fetch_idx(k + 2);
+                // rows without an entry travel as a null source: their copies zero-fill (size 0, nothing is read)
+                unsigned long long my_src_u = 0ull;
+                if (idx >= 0) {
+                    const unsigned u = (unsigned)idx;
+                    const uint8_t* src = (pbs_shift >= 0)
+                        ? p.kv + (int64_t)(u >> pbs_shift) * p.block_stride + (int64_t)(u & (unsigned)(p.page_block_size - 1)) * ROW_BYTES
+                        : kv_row_ptr(p.kv, idx, p.page_block_size, p.block_stride);
+                    my_src_u = reinterpret_cast<unsigned long long>(src);
                 }
-                if (k < w.nblk) {
-                    // -------- issue tile k
-                    const uint32_t t_it = it + k, st = t_it % NSTAGE;
-                    const int idx = idx_next;
-                    idx_next = fetch_idx(k + 1);
-                    if (t_it >= NSTAGE) {
-                        ok = __all_sync(0xffffffffu,
-                                        mbar_wait(bar(BAR_EMPTY + st), ((t_it / NSTAGE) - 1) & 1u, abort_flag, W_EMPTY));
-                        if (!ok) break;
-                    }
-                    trace(tr, 50 + warp, t_it);
-                    const uint32_t sbase = base + ST_OFF + st * ST_BYTES;
-                    float4 sc = make_float4(0.f, 0.f, 0.f, 0.f);
-                    if (idx >= 0) {
-                        const uint8_t* src = kv_row_ptr(p.kv, idx, p.page_block_size, p.block_stride);
-#pragma unroll
-                        for (int c = 0; c < 16; ++c) {
-                            const int ch = hf * 16 + c;        // 16-byte chunk of the 512 no-PE bytes
-                            cp_async16(sbase + (ch >> 3) * KV_CHUNK + r * 128 + ((((uint32_t)ch & 7u) ^ sw) << 4), src + ch * 16);
-                        }
-#pragma unroll
-                        for (int c = 0; c < 4; ++c) {
-                            const int ch = hf * 4 + c;
-                            cp_async16(sbase + ST_ROPE + r * 128 + (((uint32_t)ch ^ sw) << 4), src + ROPE_OFF + ch * 16);
-                        }
-                        sc = __ldg(reinterpret_cast<const float4*>(src + SCALE_OFF));
-                    } else {
-                        uint8_t* sp = sm + ST_OFF + st * ST_BYTES;
-                        const uint4 zero = make_uint4(0, 0, 0, 0);
-#pragma unroll
-                        for (int c = 0; c < 16; ++c) {
-                            const int ch = hf * 16 + c;
-                            *reinterpret_cast<uint4*>(sp + (ch >> 3) * KV_CHUNK + r * 128 + ((((uint32_t)ch & 7u) ^ sw) << 4)) = zero;
-                        }
-#pragma unroll
-                        for (int c = 0; c < 4; ++c) {
-                            const int ch = hf * 4 + c;
-                            *reinterpret_cast<uint4*>(sp + ST_ROPE + r * 128 + (((uint32_t)ch ^ sw) << 4)) = zero;
-                        }
-                    }
-                    sc_c = sc;
-                    idx_c = idx;
-                    trace(tr, 60 + warp, t_it);
+                if (t_it >= NSTAGE) {
+                    ok = (mbar_wait(bar(BAR_EMPTY + st), ((t_it / NSTAGE) - 1) & 1u, abort_flag, W_EMPTY));
+                    if (!ok) break;
                 }
-                cp_async_commit();
-                sc_a = sc_b; idx_a = idx_b;
-                sc_b = sc_c; idx_b = idx_c;
+                trace(tr, tc, 60 + pw, t_it);
+                if (SMLA_DBG & 4) { mbar_arrive(bar(BAR_LOADED + st)); continue; }
+                const uint32_t sbase = base + ST_OFF + st * ST_BYTES;
+                const unsigned long long kv_u = reinterpret_cast<unsigned long long>(p.kv);
+#pragma unroll
+                for (int hb = 0; hb < 2; ++hb) {       // two batches of 8 rows keep the register count low
+                    unsigned long long srcs[8];
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) srcs[i] = __shfl_sync(0xffffffffu, my_src_u, hb * 8 + i);
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) {
+                        const int r = row0 + hb * 8 + i;
+                        const uint32_t off = (lane >> 3) * KV_CHUNK + r * 128 + ((((uint32_t)lane & 7u) ^ ((uint32_t)r & 7u)) << 4);
+                        const bool v = srcs[i] != 0ull;
+                        cp_async16_zfill(sbase + off, reinterpret_cast<const uint8_t*>(v ? srcs[i] + lane * 16 : kv_u), v ? 16u : 0u);
+                    }
+                }
+#pragma unroll
+                for (int g = 0; g < 4; ++g) {
+                    const unsigned long long rs = __shfl_sync(0xffffffffu, my_src_u, g * 4 + (lane >> 3));
+                    const int r = row0 + g * 4 + (lane >> 3);
+                    const uint32_t off = ST_ROPE + r * 128 + ((((uint32_t)lane & 7u) ^ ((uint32_t)r & 7u)) << 4);
+                    const bool v = rs != 0ull;
+                    cp_async16_zfill(sbase + off, reinterpret_cast<const uint8_t*>(v ? rs + ROPE_OFF + (lane & 7) * 16 : kv_u), v ? 16u : 0u);
+                }
+                if (lane < 16) {
+                    const bool v = my_src_u != 0ull;
+                    cp_async16_zfill(sbase + ST_SCALE + my_row * 16, reinterpret_cast<const uint8_t*>(v ? my_src_u + SCALE_OFF : kv_u), v ? 16u : 0u);
+                }
+                cp_async_arrive_noinc(bar(BAR_LOADED + st));
+                trace(tr, tc, 70 + pw, t_it);
             }
             it += w.nblk;
         }
-        cp_async_wait<0>();
-    } else {
+        cp_async_wait_all();
+    } else if (warp < MMA_WARP) {
+        // =================================================================== tile fix-up
+        // Warp fw owns rows [8*fw, +8) of every tile: publishes the per-token scale arrays,
+        // re-expresses no-PE tiles that carry a smaller scale than their row, and pre-divides the
+        // RoPE part of K by the row scale.  Lane l holds the scales of row l % 8.
+        const int fw = warp - FX_WARP0;
+        const int row0 = fw * FX_ROWS;
+        const int my_row = row0 + (lane & 7);
+        const int blk = lane >> 3;
+        uint32_t it = 0;
+        bool ok = true;
+        for (int req = meta.begin_req; req <= last_req && ok; ++req) {
+            Work w;
+            if (!get_work(p, meta, req, w)) continue;
+#pragma unroll 1
+            for (int k = 0; k < w.nblk && ok; ++k, ++it) {
+                const uint32_t st = it % NSTAGE;
+                ok = (mbar_wait(bar(BAR_LOADED + st), (it / NSTAGE) & 1u, abort_flag, W_LOADED));
+                if (!ok) break;
+                trace(tr, tc, 40, it);
+                if (SMLA_DBG & 2) { mbar_arrive(bar(BAR_FULL + st)); continue; }
+                uint8_t* sp = sm + ST_OFF + st * ST_BYTES;
+                // RoPE chunks of this lane: 2 passes of 4 rows x 8 chunks
+                uint4 rv[2];
+#pragma unroll
+                for (int g = 0; g < 2; ++g) {
+                    const int r = row0 + g * 4 + (lane >> 3);
+                    rv[g] = *reinterpret_cast<const uint4*>(sp + ST_ROPE + r * 128 + ((((uint32_t)lane & 7u) ^ ((uint32_t)r & 7u)) << 4));
+                }
+                // row scale, validity (a zero-filled scale word marks a row that was not loaded)
+                const float4 sc = *reinterpret_cast<const float4*>(sp + ST_SCALE + my_row * 16);
+                const float smax = fmaxf(fmaxf(sc.x, sc.y), fmaxf(sc.z, sc.w));
+                const bool uneven = (sc.x != smax) | (sc.y != smax) | (sc.z != smax) | (sc.w != smax);
+                const float inv_s = (smax > 0.f) ? __uint_as_float(0x7f000000u - __float_as_uint(smax)) : 0.f;
+                // ratio of (row lane % 8, block lane / 8) to its row scale: a power of two <= 1
+                const float my_ratio = (blk == 0 ? sc.x : (blk == 1 ? sc.y : (blk == 2 ? sc.z : sc.w))) * inv_s;
+                if (lane < 8) {
+                    float* tok = reinterpret_cast<float*>(sm + TOK_OFF + st * TOK_BYTES);
+                    tok[my_row] = smax;
+                    tok[64 + my_row] = (smax > 0.f) ? (float)((int)(__float_as_uint(smax) >> 23) - 127) : -INFINITY;
+                    tok[128 + my_row] = inv_s;
+                }
+#pragma unroll
+                for (int g = 0; g < 2; ++g) {
+                    const int rl = g * 4 + (lane >> 3);
+                    const int r = row0 + rl;
+                    const __nv_bfloat162 f = __float2bfloat162_rn(__shfl_sync(0xffffffffu, inv_s, rl));
+                    uint4 v = rv[g];
+                    v.x = mul_bf16x2(v.x, f); v.y = mul_bf16x2(v.y, f);
+                    v.z = mul_bf16x2(v.z, f); v.w = mul_bf16x2(v.w, f);
+                    *reinterpret_cast<uint4*>(sp + ST_ROPE + r * 128 + ((((uint32_t)lane & 7u) ^ ((uint32_t)r & 7u)) << 4)) = v;
+                }
+                trace(tr, tc, 43, it);
+                // no-PE tiles whose scale is below the row scale: shift them onto the row scale.
+                // Lane l rewrites 16-byte chunk l of a flagged row (block l / 8).
+                uint32_t fix = __ballot_sync(0xffffffffu, uneven && smax > 0.f) & 0xffu;
+                while (fix) {
+                    const int i = __ffs(fix) - 1;
+                    fix &= fix - 1;
+                    const int r = row0 + i;
+                    const float ratio_f = __shfl_sync(0xffffffffu, my_ratio, (lane & 24) + i);   // (row i, my block)
+                    if (ratio_f != 1.f) {
+                        uint4* q4 = reinterpret_cast<uint4*>(sp + blk * KV_CHUNK + r * 128 + ((((uint32_t)lane & 7u) ^ ((uint32_t)r & 7u)) << 4));
+                        const __half2 ratio = __float2half2_rn(ratio_f);
+                        uint4 v = *q4;
+                        v.x = rescale_e4m3x4(v.x, ratio); v.y = rescale_e4m3x4(v.y, ratio);
+                        v.z = rescale_e4m3x4(v.z, ratio); v.w = rescale_e4m3x4(v.w, ratio);
+                        *q4 = v;
+                    }
+                }
+                trace(tr, tc, 46, it);
+                fence_proxy_async();
+                mbar_arrive(bar(BAR_FULL + st));
+                trace(tr, tc, 50, it);
+            }
+        }
+    } else if (warp == MMA_WARP && lane == 0) {
         // =================================================================== MMA issue
+        // One thread runs this role from start to end: the tensor pipe only stays busy while its
+        // issuing thread keeps feeding it, so nothing warp-wide sits between two MMAs.
         uint32_t it = 0, rq = 0;
         bool ok = true;
-        const uint32_t qn = base + QN_OFF, qr = base + QR_OFF;
+        const uint32_t qr_lo = desc_lo(base + QR_OFF, 16);
+        auto wait = [&](int b, uint32_t parity, int code) -> bool {
+            return (SMLA_DBG & 8) ? true : mbar_wait_thread(bar(b), parity, abort_flag, code);
+        };
         auto issue_qk = [&](uint32_t t_it) {
             const uint32_t st = t_it % NSTAGE, b = t_it & 1u;
-            const uint32_t kb = base + ST_OFF + st * ST_BYTES;
+            const uint32_t kb_lo = desc_lo(base + ST_OFF + st * ST_BYTES, 16);
             const uint32_t d = tmem + TM_S + 64 * b;
 #pragma unroll
             for (int kc = 0; kc < 4; ++kc) {
 #pragma unroll
                 for (int ks = 0; ks < 4; ++ks) {
-                    mma_f8(d, smem_desc(qn + kc * QN_CHUNK + ks * 32, 16, 1024, SWIZZLE_128B),
-                           smem_desc(kb + kc * KV_CHUNK + ks * 32, 16, 1024, SWIZZLE_128B), IDESC_QK_F8, (kc | ks) != 0);
+                    mma_f8_ts(d, tmem + TM_Q + 32 * kc + 8 * ks,
+                              make_desc(kb_lo + ((kc * KV_CHUNK + ks * 32) >> 4), DESC_HI_SW128), IDESC_QK_F8, (kc | ks) != 0);
+                    if ((SMLA_DBG & 16) && t_it == 8) trace(tr, tc, 100 + kc * 4 + ks, t_it);
                 }
             }
 #pragma unroll
             for (int ks = 0; ks < 4; ++ks) {
-                mma_f16(d, smem_desc(qr + ks * 32, 16, 1024, SWIZZLE_128B),
-                        smem_desc(kb + ST_ROPE + ks * 32, 16, 1024, SWIZZLE_128B), IDESC_QK_BF16, true);
+                mma_f16(d, make_desc(qr_lo + ((ks * 32) >> 4), DESC_HI_SW128),
+                        make_desc(kb_lo + ((ST_ROPE + ks * 32) >> 4), DESC_HI_SW128), IDESC_QK_BF16, true);
+                if ((SMLA_DBG & 16) && t_it == 8) trace(tr, tc, 116 + ks, t_it);
             }
             tc_commit(bar(BAR_SREADY + b));
         };
         for (int req = meta.begin_req; req <= last_req && ok; ++req) {
             Work w;
             if (!get_work(p, meta, req, w)) continue;
-            ok = __all_sync(0xffffffffu, mbar_wait(bar(BAR_QREADY), rq & 1u, abort_flag, W_QREADY));
+            ok = wait(BAR_QREADY, rq & 1u, W_QREADY);
             if (!ok) break;
             ++rq;
-            ok = __all_sync(0xffffffffu, mbar_wait(bar(BAR_FULL + it % NSTAGE), (it / NSTAGE) & 1u, abort_flag, W_FULL));
+            ok = wait(BAR_FULL + it % NSTAGE, (it / NSTAGE) & 1u, W_FULL);
             if (!ok) break;
             tc_fence_after();
-            if (lane == 0) issue_qk(it);
-            __syncwarp();
-            for (int j = 0; j < w.nblk && ok; ++j, ++it) {
+            issue_qk(it);
+            for (int j = 0; j < w.nblk; ++j, ++it) {
                 if (j + 1 < w.nblk) {
                     const uint32_t nx = it + 1;
-                    ok = __all_sync(0xffffffffu, mbar_wait(bar(BAR_FULL + nx % NSTAGE), (nx / NSTAGE) & 1u, abort_flag, W_FULL));
+                    ok = wait(BAR_FULL + nx % NSTAGE, (nx / NSTAGE) & 1u, W_FULL);
                     if (!ok) break;
                     tc_fence_after();
-                    trace(tr, 70, nx);
-                    if (lane == 0) issue_qk(nx);
-                    __syncwarp();
-                    trace(tr, 71, nx);
+                    trace(tr, tc, 80, nx);
+                    issue_qk(nx);
+                    trace(tr, tc, 81, nx);
                 }
                 const uint32_t b = it & 1u, st = it % NSTAGE;
-                ok = __all_sync(0xffffffffu, mbar_wait(bar(BAR_PREADY + b), (it >> 1) & 1u, abort_flag, W_PREADY));
+                ok = wait(BAR_PREADY + b, (it >> 1) & 1u, W_PREADY);
                 if (!ok) break;
                 tc_fence_after();
-                trace(tr, 72, it);
-                if (lane == 0) {
-                    const uint32_t pb = base + P_OFF + b * P_BYTES;
-                    const uint32_t vb = base + ST_OFF + st * ST_BYTES + (uint32_t)half * 2 * KV_CHUNK;
+                trace(tr, tc, 82, it);
+                // V = the no-PE bytes of the same stage, read MN-major: 128-dim chunks 8192 B apart,
+                // 8-token groups 1024 B apart; this CTA's half of the output dims is two chunks.
+                const uint32_t vb_lo = desc_lo(base + ST_OFF + st * ST_BYTES + (uint32_t)half * 2 * KV_CHUNK, KV_CHUNK);
 #pragma unroll
-                    for (int ks = 0; ks < 2; ++ks) {
-                        mma_f8(tmem + TM_O, smem_desc(pb + ks * 4096, 2048, 128, SWIZZLE_NONE),
-                               smem_desc(vb + ks * 4096, KV_CHUNK, 1024, SWIZZLE_128B), IDESC_PV_F8, (j | ks) != 0);
-                    }
-                    tc_commit(bar(BAR_EMPTY + st));
-                    tc_commit(bar(BAR_PVDONE + b));
+                for (int ks = 0; ks < 2; ++ks) {
+                    mma_f8_ts(tmem + TM_O, tmem + TM_S + 64 * b + 8 * ks,
+                              make_desc(vb_lo + ((ks * 4096) >> 4), DESC_HI_SW128), IDESC_PV_F8, (j | ks) != 0);
                 }
-                __syncwarp();
-                trace(tr, 73, it);
+                tc_commit(bar(BAR_EMPTY + st));
+                tc_commit(bar(BAR_PVDONE + b));
+                trace(tr, tc, 83, it);
             }
         }
     }
@@ -616,7 +698,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) attn_tc_kernel(const AttnParams
         atomicAdd(p.status + 1, 1);
         p.status[2] = blockIdx.x;
     }
-    if (warp == 8) {
+    if (warp == MMA_WARP) {
         tc_fence_after();
         tmem_dealloc(tmem, TMEM_COLS);
     }
@@ -633,6 +715,10 @@ int launch_attn_tc(const AttnParams& p, cudaStream_t stream) {
     int dev = 0;
     cudaGetDevice(&dev);
     if (dev < 64 && !attr_set[dev]) {
+        cudaFuncAttributes fa;
+        if (cudaFuncGetAttributes(&fa, attn_tc_kernel) != cudaSuccess || fa.numRegs != REGS_LAUNCH)
+            return set_error(SMLA_E_DEVICE, "attn_tc_kernel: compiled with %d registers per thread, the warpgroup budgets assume %d",
+                             fa.numRegs, REGS_LAUNCH);
         const cudaError_t e = cudaFuncSetAttribute(attn_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_ALLOC);
         if (e != cudaSuccess) return set_error((int)e, "attn_tc_kernel: cannot reserve %u bytes of shared memory: %s",
                                                SMEM_ALLOC, cudaGetErrorString(e));

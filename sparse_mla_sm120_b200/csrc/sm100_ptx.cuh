@@ -23,27 +23,47 @@ __device__ __forceinline__ void mbar_init_fence() {
 __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
 }
-__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+// One poll; the hardware may suspend the thread for up to `hint_ns` while the phase is incomplete.
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity, uint32_t hint_ns) {
     uint32_t ok;
     asm volatile(
         "{\n\t.reg .pred p;\n\t"
         "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
         "selp.u32 %0, 1, 0, p;\n\t}"
         : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+    (void)hint_ns;
     return ok != 0;
 }
 
-// Waits for the phase with the given parity, giving up after a bounded number of polls or as
-// soon as another thread of the CTA has given up (*abort != 0).  Returns false on give-up and
-// records `code` in *abort so that the kernel can report where it stopped.
-constexpr uint32_t WAIT_SPINS = 1u << 22;
+// Warp-wide wait for the phase with the given parity.  Lane 0 polls (32 lanes polling one
+// mbarrier only add shared-memory traffic), the warp reconverges on the result.  The wait gives
+// up after a bounded number of polls (about half a second) or as soon as another thread of the
+// CTA has given up (*abort != 0); it then returns false and records `code` in *abort so that the
+// kernel can report where it stopped.  Must be called by all 32 lanes.
+constexpr uint32_t WAIT_POLLS = 1u << 22;
+constexpr uint32_t WAIT_HINT_NS = 2000;
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort, int code) {
-    for (uint32_t i = 0; i < WAIT_SPINS; ++i) {
-        if (mbar_try_wait(bar, parity)) return true;
-        if (i > 64) {
-            __nanosleep(64);
-            if ((i & 255u) == 0 && *abort != 0) return false;
+    uint32_t ok = 1;
+    if ((threadIdx.x & 31) == 0) {
+        ok = 0;
+        for (uint32_t i = 0; i < WAIT_POLLS; ++i) {
+            if (mbar_try_wait(bar, parity, WAIT_HINT_NS)) { ok = 1; break; }
+            __nanosleep(32);   // a spinning poller would take issue slots from the working warps of its scheduler
+            if ((i & 255u) == 255u && *abort != 0) break;
         }
+        if (!ok) atomicCAS(const_cast<int*>(abort), 0, code);
+    }
+    ok = __shfl_sync(0xffffffffu, ok, 0);
+    __syncwarp();
+    return ok != 0;
+}
+
+// Single-thread variant of mbar_wait (same bounds and give-up protocol), for a role that is run
+// by one lane only.
+__device__ __forceinline__ bool mbar_wait_thread(uint32_t bar, uint32_t parity, volatile int* abort, int code) {
+    for (uint32_t i = 0; i < WAIT_POLLS; ++i) {
+        if (mbar_try_wait(bar, parity, WAIT_HINT_NS)) return true;
+        if ((i & 255u) == 255u && *abort != 0) return false;
     }
     atomicCAS(const_cast<int*>(abort), 0, code);
     return false;
@@ -53,11 +73,21 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
 __device__ __forceinline__ void cp_async16(uint32_t dst, const void* src) {
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
 }
+// Copies src_bytes (0 or 16) bytes and zero-fills the rest of the 16-byte destination.
+__device__ __forceinline__ void cp_async16_zfill(uint32_t dst, const void* src, uint32_t src_bytes) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(src_bytes) : "memory");
+}
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
 template <int N>
 __device__ __forceinline__ void cp_async_wait() {
     asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
 }
+// Arrives on the mbarrier (without adding to its pending count) once every cp.async issued so
+// far by this thread has landed.
+__device__ __forceinline__ void cp_async_arrive_noinc(uint32_t bar) {
+    asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_all;" ::: "memory"); }
 // Makes generic-proxy writes to shared memory visible to the async proxy (tcgen05.mma operands).
 __device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 
@@ -110,6 +140,22 @@ __device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[32
         : "memory");
 }
 
+// 32 lanes x 8 columns: thread i of the warp writes 8 consecutive columns of its lane.
+__device__ __forceinline__ void tmem_st8(uint32_t taddr, const uint32_t (&r)[8]) {
+    asm volatile("tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};"
+                 ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7])
+                 : "memory");
+}
+
+// Register reallocation between warpgroups (all four warps of a warpgroup execute it together).
+template <int N> __device__ __forceinline__ void setmaxnreg_inc() { asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(N)); }
+template <int N> __device__ __forceinline__ void setmaxnreg_dec() { asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(N)); }
+
+// Named barrier among `threads` threads (ids 1..15; id 0 is __syncthreads).
+__device__ __forceinline__ void named_bar_sync(uint32_t id, uint32_t threads) {
+    asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
+}
+
 // ------------------------------------------------------------------ descriptors
 // Shared-memory matrix descriptor of tcgen05.mma: start address, leading / stride byte offsets
 // (all in 16-byte units), descriptor version 1 (bits 46-47) and the swizzle mode (bits 61-63).
@@ -140,6 +186,24 @@ __device__ __forceinline__ void mma_f16(uint32_t d_tmem, uint64_t a_desc, uint64
         "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
         ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"((uint32_t)accumulate) : "memory");
 }
+
+// Same with the A operand read from tensor memory (lane = row, K packed along the columns).
+__device__ __forceinline__ void mma_f8_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc, bool accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], [%1], %2, %3, p;\n\t}"
+        ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"((uint32_t)accumulate) : "memory");
+}
+
+// Descriptor halves for operands whose address changes while everything else stays fixed:
+// desc = (hi << 32) | (lo(addr) ), lo(addr + off) = lo(addr) + (off >> 4).
+__device__ __forceinline__ uint32_t desc_lo(uint32_t addr, uint32_t lbo_bytes) {
+    return ((addr >> 4) & 0x3fffu) | (((lbo_bytes >> 4) & 0x3fffu) << 16);
+}
+__host__ __device__ constexpr uint32_t desc_hi(uint32_t sbo_bytes, uint32_t swizzle) {
+    return ((sbo_bytes >> 4) & 0x3fffu) | (1u << 14) | (swizzle << 29);
+}
+__device__ __forceinline__ uint64_t make_desc(uint32_t lo, uint32_t hi) { return ((uint64_t)hi << 32) | lo; }
 
 }  // namespace ptx
 }  // namespace smla

@@ -184,7 +184,7 @@ def test_attn_sink(impl):
     for parts in (None, 3):
         out, lse = _decode(case, impl, num_sm_parts=parts, attn_sink=sink)
         a, r, c, l = _tols(impl)
-        H.compare_out(out, s_out, a, r, None)
+        H.compare_out(out, s_out, a, r, c)
         k = lse.double() * H.LN2
         fin = torch.isfinite(s_lse)
         assert float((k[fin] - s_lse.double()[fin]).abs().max()) <= max(l, 1e-3)
@@ -216,7 +216,7 @@ def test_out_argument_is_written_in_place():
     case = make_case(2, 3, 16, 128, 4)
     out = torch.zeros(3, 16, 512, dtype=torch.bfloat16, device=dev)
     res, _ = flash_ops.sparse_mla_decode_fwd(case["q"].to(dev), case["packed"].to(dev), case["indices"].to(dev),
-                                             case["sm_scale"], out=out)
+                                             case["sm_scale"], out=out, num_sm_parts=3)   # one whole request per partition
     assert res.data_ptr() == out.data_ptr() and out.any()
     out2 = torch.zeros_like(out)
     res2, _, _ = flash_ops.sparse_mla_prefill_fwd(case["q"].to(dev), case["packed"].to(dev),
