@@ -38,8 +38,8 @@ SM_SCALE = D_QK ** -0.5
 WORKLOAD = ("V3.2-shape sparse-MLA decode: b=64/GPU, s_q=1, h_q=128, topk=2048, d_qk=576, d_v=512, "
             "KV len U[4096,32768], paged block 64, packed FP8 656 B rows")
 # DRAM bytes per launch of the attention kernel from the ncu capture summarised in
-# profiles/attn_tc_decode_b64.md (None until a capture exists).
-NCU_TRAFFIC_BYTES = None
+# profiles/attn_tc_decode_b64.md (dram__bytes_read.sum + dram__bytes_write.sum of one launch).
+NCU_TRAFFIC_BYTES = 112_157_440
 
 
 def algorithmic_bytes(num_tokens: int, n_valid: int) -> int:
@@ -368,8 +368,8 @@ def run_reference(args):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=200)
-    ap.add_argument("--warmup", type=int, default=20)
+    ap.add_argument("--steps", type=int, default=3000)
+    ap.add_argument("--warmup", type=int, default=50)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-extras", action="store_true")
     args = ap.parse_args()

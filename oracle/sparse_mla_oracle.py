@@ -126,9 +126,10 @@ def apply_attn_sink(out: torch.Tensor, lse: torch.Tensor, attn_sink: torch.Tenso
     lse' = lse + log(1+exp(sink-lse)) follows decode_v2_kernel.cuh:582-595 (there in base 2)."""
     sink = attn_sink.view(*([1] * (lse.dim() - 1)), -1).float()
     lse_f = lse.float()
-    scale = 1.0 / (1.0 + torch.exp(sink - lse_f))
+    empty = torch.isinf(lse_f) & (lse_f < 0)          # no valid entry: the output is 0 whatever the sink
+    scale = torch.where(empty, torch.zeros_like(lse_f), 1.0 / (1.0 + torch.exp(sink - lse_f.masked_fill(empty, 0.0))))
     out2 = (out.float() * scale.unsqueeze(-1)).to(torch.bfloat16)
-    lse2 = torch.where(torch.isinf(lse_f) & (lse_f < 0), sink.expand_as(lse_f),
+    lse2 = torch.where(empty, sink.expand_as(lse_f),
                        lse_f + torch.log1p(torch.exp(sink - lse_f)))
     return out2, lse2
 

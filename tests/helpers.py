@@ -90,11 +90,12 @@ def compare_lse(lse2_kernel: torch.Tensor, lse_ref: torch.Tensor, tol: float):
     return err
 
 
-def compare_out(out_kernel: torch.Tensor, out_ref: torch.Tensor, abs_tol, rel_tol, cos_tol=None):
+def compare_out(out_kernel: torch.Tensor, out_ref: torch.Tensor, abs_tol, rel_tol, cos_tol=None, noise=1.0):
     """|d| <= abs_tol + rel_tol*max(|a|,|b|) elementwise; when cos_tol is given (FP8 kernel) the
     absolute term grows by TC_NOISE * rms(reference) and 1 - cos must stay below cos_tol."""
     if cos_tol is not None:
-        abs_tol = abs_tol + TC_NOISE * float(out_ref.float().pow(2).mean().sqrt())
+        abs_tol = abs_tol + noise * TC_NOISE * float(out_ref.float().pow(2).mean().sqrt())
+        cos_tol = cos_tol * noise * noise
     ok, max_diff, nbad = orc.allclose_report(out_kernel.cpu(), out_ref, abs_tol, rel_tol)
     assert ok, f"{nbad} elements outside |d| <= {abs_tol} + {rel_tol}*max(|a|,|b|); max diff {max_diff}"
     if cos_tol is not None:
