@@ -240,11 +240,20 @@ def run_ours(args):
     k_secs = statistics.mean(kt)
 
     extras = {}
+    if world > 1 and not args.no_extras:
+        try:
+            cp_extra = run_cp_extra(device, rank, world)
+        except Exception as e:
+            cp_extra = {"error": repr(e)}
+    else:
+        cp_extra = None
     if rank == 0 and not args.no_extras:
         try:
             extras = run_extras(device, bf16_peak)
         except Exception as e:  # the headline line must still print
             extras = {"error": repr(e)}
+    if cp_extra is not None:
+        extras["cp_decode"] = cp_extra
     cpu = cpu_baseline(pool, sets) if rank == 0 else None
 
     if rank == 0:
@@ -277,6 +286,53 @@ def run_ours(args):
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()
+
+
+def run_cp_extra(device, rank, world):
+    """Context-parallel long-context decode: 16 requests, 131072-token context sharded across the
+    ranks, top-k 2048 uniform over the whole context.  Timed per step on the device, max over ranks:
+    index partition + scheduler + local split-KV decode + local merge + NCCL all-gather + final merge.
+    (The indexer that would produce the indices is not part of this timing.)"""
+    import torch.distributed as dist
+    from sparse_mla_sm120_b200 import cp, indexer
+    b, ctx = 16, 131072
+    lo, hi = cp.shard_context(ctx, rank, world)
+    rows = hi - lo
+    g = torch.Generator(device=device).manual_seed(99 + rank)
+    pools = []
+    for _ in range(b):   # one contiguous shard per request; rows of request i live at [i*rows, (i+1)*rows)
+        pools.append(indexer.pack_kv_cache(torch.randn((rows, D_QK), device=device, generator=g).to(torch.bfloat16)))
+    kv_local = torch.cat(pools).view(-1, BLOCK, 1, ROW)
+    gi = torch.Generator(device=device).manual_seed(7)      # same indices on every rank
+    q = (torch.randn((b, HEADS, D_QK), device=device, generator=gi) * 0.5).to(torch.bfloat16)
+    pos = torch.stack([torch.randperm(ctx, device=device, generator=gi)[:TOPK] for _ in range(b)])
+    # global row number = request * ctx + position; the local pool stores request i's shard at i*rows
+    in_shard = (pos >= lo) & (pos < hi)
+    local = torch.where(in_shard, pos - lo + torch.arange(b, device=device).view(-1, 1) * rows, torch.full_like(pos, -1)).to(torch.int32)
+
+    def step():
+        # entries outside the shard are already -1; compaction and the local length come from the partition kernel
+        li, ln = cp.partition_indices(local, 0, b * rows)
+        o_all, l_all = cp._gather_buffers(device, world, b, HEADS)
+        cp.decode_partial(q, kv_local, li, ln, SM_SCALE, o_all[rank], l_all[rank])
+        dist.all_gather_into_tensor(o_all, o_all[rank])
+        dist.all_gather_into_tensor(l_all, l_all[rank])
+        return cp.combine_parts(o_all, l_all)
+
+    for _ in range(5):
+        step()
+    dist.barrier(); torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    n = 50
+    e0.record()
+    for _ in range(n):
+        step()
+    e1.record(); torch.cuda.synchronize()
+    t = torch.tensor([e0.elapsed_time(e1) / n * 1e3], device=device)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return {"workload": "b=16, h=128, topk=2048, 131072-token context sharded over the ranks", "us_per_step": float(t.item()),
+            "timed": "partition + scheduler + local decode + local merge + 2 NCCL all-gathers + final merge (eager launches)",
+            "exchange_bytes_per_rank": b * HEADS * (D_V + 1) * 4}
 
 
 def run_extras(device, bf16_peak):
