@@ -169,6 +169,28 @@ int smla_decode_partial(const void* q, const void* kv, const int32_t* indices,
 int smla_combine_parts(const float* o_parts, const float* lse_parts, void* out, float* out_lse,
                        int parts, int num_tokens, int num_heads, const float* attn_sink, void* stream);
 
+/*
+ * Split-KV decode (scheduler + attention + combine in one call) that allocates nothing and takes
+ * no scratch from the caller.  It has no counterpart in the reference.  It is for hosts that
+ * cannot give this library device memory at call time: a process whose own pool already owns the
+ * whole device, or a call site that must stay out of the CUDA allocator because cudaMalloc can
+ * synchronise the device.  The scratch is an array of SMLA_NOALLOC_SCRATCH_BYTES built into the
+ * library (held on every GPU that loads it until the process exits), so requests are limited to
+ * smla_noalloc_scratch_need(num_tokens, num_heads, num_sm_parts) <= SMLA_NOALLOC_SCRATCH_BYTES
+ * (at 128 heads: num_tokens + num_sm_parts <= 63); larger ones return SMLA_E_WORKSPACE and a
+ * message.  The first call on a device looks up the array's device address and should be made
+ * before any stream capture.  All calls share the array: calls that overlap on the GPU race.
+ * Arguments as smla_decode_splitkv, fixed_overhead of the scheduler is 5.
+ */
+#define SMLA_NOALLOC_SCRATCH_BYTES (16u << 20)
+size_t smla_noalloc_scratch_need(int num_tokens, int num_heads, int num_sm_parts);
+int smla_decode_splitkv_noalloc(const void* q, const void* kv, const int32_t* indices,
+                                void* out, float* out_lse,
+                                int num_tokens, int num_heads, int topk, float sm_scale,
+                                int page_block_size, int64_t kv_block_stride_bytes, int num_sm_parts,
+                                const float* attn_sink, const int32_t* topk_length,
+                                int impl, int32_t* status, void* stream);
+
 /* Bytes of o_accum + lse_accum scratch that smla_decode_splitkv needs. */
 size_t smla_workspace_bytes(int num_tokens, int num_heads, int num_sm_parts);
 
