@@ -358,7 +358,32 @@ def run_extras(device, bf16_peak):
     flops = 2.0 * s_q * HEADS * TOPK * (D_QK + D_V)
     out["prefill"] = {"workload": "s_q=4096, h=128, topk=2048, KV 8192 rows", "ms": ms,
                       "tflops": flops / ms / 1e9, "frac_of_bf16_peak": flops / ms / 1e9 / bf16_peak}
-    del q, idx
+    del q, idx, kv
+    # indexer: q e4m3 [4096, 64, 128], k e4m3 [65536, 128], ke = 61440 + i, then top-2048 per row
+    s_q, s_k, hh = 4096, 65536, 64
+    qi = torch.randn((s_q, hh, 128), device=device, generator=g).to(torch.float8_e4m3fn)
+    kf = torch.randn((s_k, 128), device=device, generator=g)
+    k_scale = kf.abs().amax(dim=1) / 448.0
+    ki = (kf / k_scale.unsqueeze(1)).to(torch.float8_e4m3fn)
+    w = torch.randn((s_q, hh), device=device, generator=g) * 0.1
+    ks = torch.zeros(s_q, dtype=torch.int32, device=device)
+    ke = (61440 + torch.arange(s_q, device=device)).to(torch.int32)
+    logits = torch.empty((s_q, s_k), dtype=torch.float32, device=device)
+    for name, fn in (("mqa_logits", lambda: indexer.fp8_mqa_logits(qi, ki, k_scale, w, ks, ke, out=logits)),
+                     ("topk", lambda: indexer.topk_indices(logits, ks, ke, TOPK))):
+        fn(); fn()
+        torch.cuda.synchronize()
+        e0.record()
+        for _ in range(3):
+            fn()
+        e1.record(); torch.cuda.synchronize()
+        out[name] = {"ms": e0.elapsed_time(e1) / 3}
+    pairs = float(ke.double().sum())
+    fl = 2.0 * hh * 128 * pairs
+    out["mqa_logits"].update({"workload": "s_q=4096, 64 heads, d=128, s_k=65536, ke=61440+i", "tflops": fl / out["mqa_logits"]["ms"] / 1e9,
+                              "frac_of_fp8_peak(2x measured bf16)": fl / out["mqa_logits"]["ms"] / 1e9 / (2 * bf16_peak),
+                              "write_gbs": s_q * s_k * 4 / out["mqa_logits"]["ms"] / 1e6})
+    out["topk"].update({"workload": "top-2048 of each of 4096 rows of 65536 fp32", "read_gbs": s_q * s_k * 4 / out["topk"]["ms"] / 1e6})
     return out
 
 

@@ -729,11 +729,4 @@ int launch_attn_tc(const AttnParams& p, cudaStream_t stream) {
     return check_launch("attn_tc_kernel");
 }
 
-int launch_mqa_logits_tc(const uint8_t* q, const uint8_t* k, const float* k_scale, const float* weights,
-                         const int32_t* ks, const int32_t* ke, float* logits, int s_q, int num_heads,
-                         int s_k, int64_t logits_stride, int32_t* status, cudaStream_t stream) {
-    (void)status;
-    return launch_mqa_logits_scalar(q, k, k_scale, weights, ks, ke, logits, s_q, num_heads, s_k, logits_stride, stream);
-}
-
 }  // namespace smla

@@ -1,0 +1,282 @@
+// FP8 MQA-logits indexer on tcgen05 tensor cores (sm_100a).
+//
+//   logits[i, j] = k_scale[j] * sum_h w[i, h] * relu(q[i, h, :] . k[j, :]),   -inf outside [ks_i, ke_i)
+//
+// No counterpart in the reference project (its indices come from an external indexer).  The
+// contraction is run transposed: a tile of 128 keys is the M side, the (query, head) pairs of
+// four queries are the N side (N = 4 * heads <= 256), K = 128 e4m3 values, so that one thread of
+// the epilogue owns one key (one TMEM lane) and the ReLU / head-weighted sum runs along the
+// columns it holds, with no cross-thread reduction.  Two accumulators (2 x 256 TMEM columns) let
+// the MMAs of the next key tile run under the epilogue of the current one.
+//
+// One CTA walks query groups (4 queries) round-robin and, per group, the key tiles up to the
+// largest ke of the group.  Warps: 0-7 epilogue (warp w: TMEM lane quarter w % 4, queries
+// 2 * (w / 4) and +1 of the group), 8 loader (16-byte cp.async into 128B-swizzled K-major tiles;
+// q group and key tiles are contiguous in global memory), 9 MMA issue (one thread).
+// The kernel is tensor-bound at the benchmark shape (4.26 TFLOP) with the logits write
+// (1.07 GB) as the second term.  Every wait is bounded.
+#include "common.cuh"
+#include "sm100_ptx.cuh"
+
+namespace smla {
+
+namespace {
+
+using namespace ptx;
+
+constexpr int LX_D = 128;            // head dim of the indexer (bytes per row)
+constexpr int LX_KT = 128;           // keys per tile
+constexpr int LX_QG = 4;             // queries per group
+constexpr int LX_EPI_WARPS = 8;
+constexpr int LX_LOAD_WARP = 8, LX_MMA_WARP = 9;
+constexpr int LX_THREADS = 10 * 32;
+constexpr int LX_KSTAGE = 4;
+
+constexpr uint32_t LX_Q_OFF = 0;                              // q group: [<=256 rows x 128 B] K-major 128B swizzle
+constexpr uint32_t LX_K_OFF = 256 * 128;                      // key tiles: LX_KSTAGE x [128 rows x 128 B]
+constexpr uint32_t LX_W_OFF = LX_K_OFF + LX_KSTAGE * LX_KT * 128;   // weights: 4 rotating buffers of [4 queries][64] fp32
+constexpr uint32_t LX_W_BYTES = LX_QG * 64 * 4;
+constexpr uint32_t LX_BAR_OFF = LX_W_OFF + 4 * LX_W_BYTES;
+// barriers: kfull[4] kempty[4] dfull[2] dempty[2] qfull qempty
+constexpr int LXB_KFULL = 0, LXB_KEMPTY = LX_KSTAGE, LXB_DFULL = 2 * LX_KSTAGE, LXB_DEMPTY = LXB_DFULL + 2,
+              LXB_QFULL = LXB_DEMPTY + 2, LXB_QEMPTY = LXB_QFULL + 1, LXB_N = LXB_QEMPTY + 1;
+constexpr uint32_t LX_MISC_OFF = LX_BAR_OFF + LXB_N * 8;
+constexpr uint32_t LX_SMEM_NEED = LX_MISC_OFF + 16 + 1024;
+// one CTA per SM (each allocates all 512 TMEM columns): ask for more than half of the SM's shared memory
+constexpr uint32_t LX_SMEM = LX_SMEM_NEED > 118 * 1024 ? LX_SMEM_NEED : 118 * 1024;
+
+struct LogitsParams {
+    const uint8_t* q; const uint8_t* k; const float* k_scale; const float* w;
+    const int32_t* ks; const int32_t* ke; float* logits; int32_t* status;
+    int s_q, heads, s_k; int64_t stride;
+};
+
+__global__ void __launch_bounds__(LX_THREADS, 1) mqa_logits_tc_kernel(const LogitsParams p) {
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t raw = smem_u32(smem_raw);
+    const uint32_t base = (raw + 1023u) & ~1023u;
+    uint8_t* sm = smem_raw + (base - raw);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(sm + LX_MISC_OFF + 4);
+    volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(sm + LX_MISC_OFF);
+    auto bar = [&](int i) -> uint32_t { return base + LX_BAR_OFF + 8u * i; };
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int H = p.heads, N = LX_QG * H;
+
+    if (tid == 0) {
+        for (int s = 0; s < LX_KSTAGE; ++s) { mbar_init(bar(LXB_KFULL + s), 32); mbar_init(bar(LXB_KEMPTY + s), 1); }
+        for (int b = 0; b < 2; ++b) { mbar_init(bar(LXB_DFULL + b), 1); mbar_init(bar(LXB_DEMPTY + b), LX_EPI_WARPS * 32); }
+        mbar_init(bar(LXB_QFULL), 32);
+        mbar_init(bar(LXB_QEMPTY), 1);
+        *abort_flag = 0;
+        mbar_init_fence();
+    }
+    if (warp == LX_MMA_WARP) { tmem_alloc(base + LX_MISC_OFF, 512); tmem_relinquish(); }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = *tmem_slot;
+
+    const int num_groups = (p.s_q + LX_QG - 1) / LX_QG;
+    // key tiles a group needs: up to the largest ke of its queries (and from the smallest ks)
+    auto group_range = [&](int g, int& t0, int& t1) {
+        int lo = p.s_k, hi = 0;
+        for (int i = 0; i < LX_QG; ++i) {
+            const int qi = g * LX_QG + i;
+            if (qi < p.s_q) { lo = min(lo, max(p.ks[qi], 0)); hi = max(hi, min(p.ke[qi], p.s_k)); }
+        }
+        t0 = (hi > lo) ? lo / LX_KT : 0;
+        t1 = (hi > lo) ? (hi + LX_KT - 1) / LX_KT : 0;
+    };
+
+    if (warp < LX_EPI_WARPS) {
+        // =================================================================== epilogue
+        const int quarter = warp & 3, qp = warp >> 2;
+        const uint32_t lane_addr = tmem + ((uint32_t)(quarter * 32) << 16);
+        uint32_t it = 0, qn = 0;   // tiles and non-empty groups seen by this CTA
+        bool ok = true;
+        for (int g = blockIdx.x; g < num_groups && ok; g += gridDim.x) {
+            int t0, t1;
+            group_range(g, t0, t1);
+            const float* wsm = reinterpret_cast<const float*>(sm + LX_W_OFF + (qn & 3u) * LX_W_BYTES);
+            const int q0 = g * LX_QG + 2 * qp, q1 = q0 + 1;
+            const int ks0 = q0 < p.s_q ? p.ks[q0] : 0, ke0 = q0 < p.s_q ? p.ke[q0] : 0;
+            const int ks1 = q1 < p.s_q ? p.ks[q1] : 0, ke1 = q1 < p.s_q ? p.ke[q1] : 0;
+            // columns outside every tile of the group are -inf: written here, 128 keys per pass
+            for (int qq = 0; qq < 2; ++qq) {
+                const int qi = q0 + qq;
+                if (qi >= p.s_q) continue;
+                float* row = p.logits + (size_t)qi * p.stride;
+                for (int j = quarter * 32 + lane; j < p.s_k; j += 128)
+                    if (j < t0 * LX_KT || j >= t1 * LX_KT) row[j] = -INFINITY;
+            }
+            if (t1 > t0) {
+                ok = mbar_wait(bar(LXB_QFULL), qn & 1u, abort_flag, 11);   // weights of the group are in shared memory
+                if (!ok) break;
+                ++qn;
+            }
+            for (int t = t0; t < t1 && ok; ++t, ++it) {
+                const uint32_t b = it & 1u;
+                ok = mbar_wait(bar(LXB_DFULL + b), (it >> 1) & 1u, abort_flag, 12);
+                if (!ok) break;
+                tc_fence_after();
+                const int key = t * LX_KT + quarter * 32 + lane;
+                const float sc = key < p.s_k ? __ldg(p.k_scale + key) : 0.f;
+                float acc[2] = {0.f, 0.f};
+#pragma unroll
+                for (int qq = 0; qq < 2; ++qq) {
+                    const float* wq = wsm + (2 * qp + qq) * 64;
+                    for (int c = 0; c < H; c += 32) {
+                        uint32_t d[32];
+                        tmem_ld32(lane_addr + 256 * b + (2 * qp + qq) * H + c, d);
+                        tmem_wait_ld();
+                        float a0 = 0.f, a1 = 0.f;
+#pragma unroll
+                        for (int i = 0; i < 32; i += 4) {
+                            const float4 w4 = *reinterpret_cast<const float4*>(wq + c + i);
+                            a0 = fmaf(fmaxf(__uint_as_float(d[i + 0]), 0.f), w4.x, a0);
+                            a1 = fmaf(fmaxf(__uint_as_float(d[i + 1]), 0.f), w4.y, a1);
+                            a0 = fmaf(fmaxf(__uint_as_float(d[i + 2]), 0.f), w4.z, a0);
+                            a1 = fmaf(fmaxf(__uint_as_float(d[i + 3]), 0.f), w4.w, a1);
+                        }
+                        acc[qq] += a0 + a1;
+                    }
+                }
+                tc_fence_before();
+                mbar_arrive(bar(LXB_DEMPTY + b));
+                if (key < p.s_k) {
+                    if (q0 < p.s_q) p.logits[(size_t)q0 * p.stride + key] = (key >= ks0 && key < ke0) ? acc[0] * sc : -INFINITY;
+                    if (q1 < p.s_q) p.logits[(size_t)q1 * p.stride + key] = (key >= ks1 && key < ke1) ? acc[1] * sc : -INFINITY;
+                }
+            }
+        }
+    } else if (warp == LX_LOAD_WARP) {
+        // =================================================================== loader
+        uint32_t it = 0, qn = 0;
+        bool ok = true;
+        for (int g = blockIdx.x; g < num_groups && ok; g += gridDim.x) {
+            int t0, t1;
+            group_range(g, t0, t1);
+            if (t1 <= t0) continue;
+            if (qn > 0) {   // the MMAs of the previous group have finished reading q
+                ok = mbar_wait(bar(LXB_QEMPTY), (qn - 1) & 1u, abort_flag, 13);
+                if (!ok) break;
+            }
+            // q group: N rows of 128 B, contiguous in global memory; rows past s_q are zero-filled
+            const int rows_valid = min(LX_QG, p.s_q - g * LX_QG) * H;
+            const uint8_t* qsrc = p.q + (size_t)g * LX_QG * H * LX_D;
+            for (int c = lane; c < N * 8; c += 32) {
+                const int r = c >> 3, ch = c & 7;
+                const bool v = r < rows_valid;
+                cp_async16_zfill(base + LX_Q_OFF + r * 128 + (((uint32_t)ch ^ ((uint32_t)r & 7u)) << 4),
+                                 v ? qsrc + (size_t)r * LX_D + ch * 16 : p.q, v ? 16u : 0u);
+            }
+            for (int c = lane; c < LX_QG * 64; c += 32) {
+                const int qi = g * LX_QG + (c >> 6), h = c & 63;
+                reinterpret_cast<float*>(sm + LX_W_OFF + (qn & 3u) * LX_W_BYTES)[c] = (qi < p.s_q && h < H) ? p.w[(size_t)qi * H + h] : 0.f;
+            }
+            cp_async_wait_all();
+            fence_proxy_async();
+            mbar_arrive(bar(LXB_QFULL));
+            ++qn;
+            for (int t = t0; t < t1 && ok; ++t, ++it) {
+                const uint32_t st = it % LX_KSTAGE;
+                if (it >= LX_KSTAGE) {
+                    ok = mbar_wait(bar(LXB_KEMPTY + st), ((it / LX_KSTAGE) - 1) & 1u, abort_flag, 14);
+                    if (!ok) break;
+                }
+                const int key0 = t * LX_KT;
+                const int valid = min(LX_KT, p.s_k - key0);
+                const uint8_t* ksrc = p.k + (size_t)key0 * LX_D;
+                const uint32_t dst = base + LX_K_OFF + st * (LX_KT * 128);
+#pragma unroll 4
+                for (int c = lane; c < LX_KT * 8; c += 32) {
+                    const int r = c >> 3, ch = c & 7;
+                    const bool v = r < valid;
+                    cp_async16_zfill(dst + r * 128 + (((uint32_t)ch ^ ((uint32_t)r & 7u)) << 4),
+                                     v ? ksrc + (size_t)r * LX_D + ch * 16 : p.k, v ? 16u : 0u);
+                }
+                cp_async_commit();
+                // complete the tile issued two iterations ago (keeps two tiles in flight)
+                if (t - t0 >= 2) {
+                    cp_async_wait<2>();
+                    fence_proxy_async();
+                    mbar_arrive(bar(LXB_KFULL + (it - 2) % LX_KSTAGE));
+                }
+            }
+            // drain: the last (up to two) tiles of the group
+            cp_async_wait_all();
+            fence_proxy_async();
+            const int n = t1 - t0;
+            for (int d = min(n, 2); d >= 1 && ok; --d) mbar_arrive(bar(LXB_KFULL + (it - d) % LX_KSTAGE));
+        }
+    } else if (warp == LX_MMA_WARP && lane == 0) {
+        // =================================================================== MMA issue (one thread)
+        constexpr uint32_t HI = desc_hi(1024, (uint32_t)SWIZZLE_128B);
+        const uint32_t idesc = instr_desc(FMT_E4M3, FMT_E4M3, false, false, 128, (uint32_t)N);
+        const uint32_t q_lo = desc_lo(base + LX_Q_OFF, 16);
+        uint32_t it = 0, qn = 0;
+        bool ok = true;
+        for (int g = blockIdx.x; g < num_groups && ok; g += gridDim.x) {
+            int t0, t1;
+            group_range(g, t0, t1);
+            if (t1 <= t0) continue;
+            ok = mbar_wait_thread(bar(LXB_QFULL), qn & 1u, abort_flag, 15);
+            if (!ok) break;
+            ++qn;
+            for (int t = t0; t < t1; ++t, ++it) {
+                const uint32_t st = it % LX_KSTAGE, b = it & 1u;
+                ok = mbar_wait_thread(bar(LXB_KFULL + st), (it / LX_KSTAGE) & 1u, abort_flag, 16);
+                if (!ok) break;
+                if (it >= 2) {
+                    ok = mbar_wait_thread(bar(LXB_DEMPTY + b), ((it >> 1) - 1) & 1u, abort_flag, 17);
+                    if (!ok) break;
+                }
+                tc_fence_after();
+                const uint32_t k_lo = desc_lo(base + LX_K_OFF + st * (LX_KT * 128), 16);
+#pragma unroll
+                for (int ks = 0; ks < 4; ++ks)
+                    mma_f8(tmem + 256 * b, make_desc(k_lo + ks * 2, HI), make_desc(q_lo + ks * 2, HI), idesc, ks != 0);
+                tc_commit(bar(LXB_KEMPTY + st));
+                tc_commit(bar(LXB_DFULL + b));
+            }
+            if (ok) tc_commit(bar(LXB_QEMPTY));
+        }
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    if (tid == 0 && *abort_flag != 0 && p.status != nullptr) {
+        atomicCAS(p.status, 0, *abort_flag);
+        atomicAdd(p.status + 1, 1);
+        p.status[2] = blockIdx.x;
+    }
+    if (warp == LX_MMA_WARP) { tc_fence_after(); tmem_dealloc(tmem, 512); }
+}
+
+}  // namespace
+
+int launch_mqa_logits_tc(const uint8_t* q, const uint8_t* k, const float* k_scale, const float* weights,
+                         const int32_t* ks, const int32_t* ke, float* logits, int s_q, int num_heads,
+                         int s_k, int64_t logits_stride, int32_t* status, cudaStream_t stream) {
+    if (s_q == 0 || s_k == 0) return 0;
+    // the tensor-core kernel reads its accumulator 32 columns at a time: 32 or 64 heads
+    if (num_heads % 32 != 0 || num_heads > 64)
+        return launch_mqa_logits_scalar(q, k, k_scale, weights, ks, ke, logits, s_q, num_heads, s_k, logits_stride, stream);
+    static bool attr_set[64] = {};
+    static int sms[64] = {};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev < 64 && !attr_set[dev]) {
+        const cudaError_t e = cudaFuncSetAttribute(mqa_logits_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)LX_SMEM);
+        if (e != cudaSuccess) return set_error((int)e, "mqa_logits_tc_kernel: shared memory: %s", cudaGetErrorString(e));
+        cudaDeviceGetAttribute(&sms[dev], cudaDevAttrMultiProcessorCount, dev);
+        attr_set[dev] = true;
+    }
+    LogitsParams p{q, k, k_scale, weights, ks, ke, logits, status, s_q, num_heads, s_k, logits_stride};
+    const int groups = (s_q + LX_QG - 1) / LX_QG;
+    const int grid = groups < sms[dev < 64 ? dev : 0] ? groups : sms[dev < 64 ? dev : 0];
+    mqa_logits_tc_kernel<<<grid, LX_THREADS, LX_SMEM, stream>>>(p);
+    return check_launch("mqa_logits_tc_kernel");
+}
+
+}  // namespace smla
