@@ -64,6 +64,13 @@ static_assert(N_SM_WARPS * 32 * REGS_SOFTMAX + (N_PR_WARPS + N_FX_WARPS) * 32 * 
 static_assert((N_SM_WARPS % 4) == 0 && (N_PR_WARPS % 4) == 0 && (N_FX_WARPS % 4) == 0, "setmaxnreg acts on whole warpgroups");
 static_assert(65536 / TC_THREADS / 8 * 8 == REGS_LAUNCH, "launch-time registers per thread");
 constexpr int NSTAGE = 4;
+#ifndef SMLA_PF
+#define SMLA_PF 0
+#endif
+#ifndef SMLA_HOT
+#define SMLA_HOT 15    // which waits block in the barrier instead of sleeping between polls: 1 scores, 2 loaded, 4 empty, 8 P.V done
+#endif
+constexpr int PF_DIST = SMLA_PF;       // rows are requested into L2 this many tiles before they are gathered
 constexpr int P_SHIFT = 5;             // P' is stored as e4m3(P' * 2^P_SHIFT)
 constexpr float RESCALE_TAU = 3.0f;    // lazy-rescale threshold (log2 units); P' <= 2^TAU
 
@@ -235,9 +242,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) attn_tc_kernel(const AttnParams
         else if (warp < MMA_WARP) setmaxnreg_dec<REGS_OTHER>();
     }
 
-    if ((SMLA_DBG & 8) && warp != MMA_WARP) {
-        // timing experiment: only the MMA warp runs
-    } else if (warp < N_SM_WARPS) {
+    if (warp < N_SM_WARPS) {
         // =================================================================== softmax + epilogue
         const int quarter = warp & 3, hh = warp >> 2;     // TMEM lane quarter, column half
         const int row = quarter * 32 + lane;              // head index == TMEM lane
@@ -323,7 +328,8 @@ __global__ void __launch_bounds__(TC_THREADS, 1) attn_tc_kernel(const AttnParams
             float x_max = -INFINITY;   // this half's maximum of the scaled logits (max_logits output)
             for (int j = 0; j < w.nblk && ok; ++j, ++it) {
                 const uint32_t b = it & 1u, st = it % NSTAGE;
-                ok = (mbar_wait(bar(BAR_SREADY + b), (it >> 1) & 1u, abort_flag, W_SREADY));
+                ok = (SMLA_HOT & 1) ? mbar_wait_hot(bar(BAR_SREADY + b), (it >> 1) & 1u, abort_flag, W_SREADY)
+                                    : mbar_wait(bar(BAR_SREADY + b), (it >> 1) & 1u, abort_flag, W_SREADY);
                 if (!ok) break;
                 // the per-token scale arrays of this stage were published with the tile itself
                 ok = (mbar_wait(bar(BAR_FULL + st), (it / NSTAGE) & 1u, abort_flag, W_FULL));
@@ -358,7 +364,8 @@ __global__ void __launch_bounds__(TC_THREADS, 1) attn_tc_kernel(const AttnParams
                 const bool grow = mx > m_run + RESCALE_TAU;   // false while the row has seen no valid entry
                 if (__any_sync(0xffffffffu, grow)) {
                     if (j > 0) {   // the accumulator holds earlier tiles: wait for the last P.V, then scale it
-                        ok = (mbar_wait(bar(BAR_PVDONE + ((it - 1) & 1u)), ((it - 1) >> 1) & 1u, abort_flag, W_PVDONE));
+                        ok = (SMLA_HOT & 8) ? mbar_wait_hot(bar(BAR_PVDONE + ((it - 1) & 1u)), ((it - 1) >> 1) & 1u, abort_flag, W_PVDONE)
+                                            : mbar_wait(bar(BAR_PVDONE + ((it - 1) & 1u)), ((it - 1) >> 1) & 1u, abort_flag, W_PVDONE);
                         if (!ok) break;
                         tc_fence_after();
                     }
@@ -401,7 +408,8 @@ __global__ void __launch_bounds__(TC_THREADS, 1) attn_tc_kernel(const AttnParams
             // ---- epilogue ---------------------------------------------------------------------
             {
                 const uint32_t last = it - 1;
-                ok = (mbar_wait(bar(BAR_PVDONE + (last & 1u)), (last >> 1) & 1u, abort_flag, W_PVDONE));
+                ok = (SMLA_HOT & 8) ? mbar_wait_hot(bar(BAR_PVDONE + (last & 1u)), (last >> 1) & 1u, abort_flag, W_PVDONE)
+                                    : mbar_wait(bar(BAR_PVDONE + (last & 1u)), (last >> 1) & 1u, abort_flag, W_PVDONE);
                 if (!ok) break;
                 tc_fence_after();
                 named_bar_sync(1 + quarter, 64);   // the partner has read the last tile's row maximum
@@ -488,24 +496,39 @@ __global__ void __launch_bounds__(TC_THREADS, 1) attn_tc_kernel(const AttnParams
                 const int pos = (w.blk0 + j) * BLOCK_N + my_row;
                 return (j < w.nblk && pos < w.len) ? __ldg(idx_row + pos) : -1;
             };
+            // A shared-memory stage is held from the moment its copies are issued, so the DRAM
+            // latency is taken off that path: lanes 0-15 ask L2 for their row PF_DIST tiles ahead.
+            auto row_ptr = [&](int idx) -> const uint8_t* {
+                const unsigned u = (unsigned)idx;
+                return (pbs_shift >= 0)
+                    ? p.kv + (int64_t)(u >> pbs_shift) * p.block_stride + (int64_t)(u & (unsigned)(p.page_block_size - 1)) * ROW_BYTES
+                    : kv_row_ptr(p.kv, idx, p.page_block_size, p.block_stride);
+            };
+            if (PF_DIST > 0 && lane < 16) {
+#pragma unroll 1
+                for (int j = 0; j < PF_DIST && j < w.nblk; ++j) {
+                    const int i = fetch_idx(j);
+                    if (i >= 0) prefetch_l2_bulk(row_ptr(i), ROW_BYTES);
+                }
+            }
             int idx_next = fetch_idx(0), idx_next2 = fetch_idx(1);
+            int idx_pf = (PF_DIST > 0) ? fetch_idx(PF_DIST) : -1;
 #pragma unroll 1
             for (int k = 0; k < w.nblk && ok; ++k) {
                 const uint32_t t_it = it + k, st = t_it % NSTAGE;
                 const int idx = idx_next;
                 idx_next = idx_next2;
                 idx_next2 = fetch_idx(k + 2);
+                if (PF_DIST > 0) {
+                    if (lane < 16 && idx_pf >= 0) prefetch_l2_bulk(row_ptr(idx_pf), ROW_BYTES);
+                    idx_pf = fetch_idx(k + 1 + PF_DIST);
+                }
                 // rows without an entry travel as a null source: their copies zero-fill (size 0, nothing is read)
                 unsigned long long my_src_u = 0ull;
-                if (idx >= 0) {
-                    const unsigned u = (unsigned)idx;
-                    const uint8_t* src = (pbs_shift >= 0)
-                        ? p.kv + (int64_t)(u >> pbs_shift) * p.block_stride + (int64_t)(u & (unsigned)(p.page_block_size - 1)) * ROW_BYTES
-                        : kv_row_ptr(p.kv, idx, p.page_block_size, p.block_stride);
-                    my_src_u = reinterpret_cast<unsigned long long>(src);
-                }
+                if (idx >= 0) my_src_u = reinterpret_cast<unsigned long long>(row_ptr(idx));
                 if (t_it >= NSTAGE) {
-                    ok = (mbar_wait(bar(BAR_EMPTY + st), ((t_it / NSTAGE) - 1) & 1u, abort_flag, W_EMPTY));
+                    ok = (SMLA_HOT & 4) ? mbar_wait_hot(bar(BAR_EMPTY + st), ((t_it / NSTAGE) - 1) & 1u, abort_flag, W_EMPTY)
+                                        : mbar_wait(bar(BAR_EMPTY + st), ((t_it / NSTAGE) - 1) & 1u, abort_flag, W_EMPTY);
                     if (!ok) break;
                 }
                 trace(tr, tc, 60 + pw, t_it);
@@ -560,7 +583,8 @@ __global__ void __launch_bounds__(TC_THREADS, 1) attn_tc_kernel(const AttnParams
 #pragma unroll 1
             for (int k = 0; k < w.nblk && ok; ++k, ++it) {
                 const uint32_t st = it % NSTAGE;
-                ok = (mbar_wait(bar(BAR_LOADED + st), (it / NSTAGE) & 1u, abort_flag, W_LOADED));
+                ok = (SMLA_HOT & 2) ? mbar_wait_hot(bar(BAR_LOADED + st), (it / NSTAGE) & 1u, abort_flag, W_LOADED)
+                                    : mbar_wait(bar(BAR_LOADED + st), (it / NSTAGE) & 1u, abort_flag, W_LOADED);
                 if (!ok) break;
                 trace(tr, tc, 40, it);
                 if (SMLA_DBG & 2) { mbar_arrive(bar(BAR_FULL + st)); continue; }
@@ -620,58 +644,61 @@ __global__ void __launch_bounds__(TC_THREADS, 1) attn_tc_kernel(const AttnParams
             }
         }
     } else if (warp == MMA_WARP && lane == 0) {
-        // =================================================================== MMA issue
+        // =================================================================== score MMA issue
         // One thread runs this role from start to end: the tensor pipe only stays busy while its
-        // issuing thread keeps feeding it, so nothing warp-wide sits between two MMAs.
+        // issuing thread keeps feeding it, so nothing warp-wide sits between two MMAs.  The P.V
+        // products are issued by a second thread (below), so that a P' that becomes ready while
+        // this thread is blocked on the pipe's queue does not wait for it.  MMAs of different
+        // threads are not ordered against each other: score buffer b is rewritten only after the
+        // P.V that read P' from it has completed (PVDONE), not merely been issued.
         uint32_t it = 0, rq = 0;
         bool ok = true;
         const uint32_t qr_lo = desc_lo(base + QR_OFF, 16);
-        auto wait = [&](int b, uint32_t parity, int code) -> bool {
-            return (SMLA_DBG & 8) ? true : mbar_wait_thread(bar(b), parity, abort_flag, code);
-        };
-        auto issue_qk = [&](uint32_t t_it) {
-            const uint32_t st = t_it % NSTAGE, b = t_it & 1u;
-            const uint32_t kb_lo = desc_lo(base + ST_OFF + st * ST_BYTES, 16);
-            const uint32_t d = tmem + TM_S + 64 * b;
-#pragma unroll
-            for (int kc = 0; kc < 4; ++kc) {
-#pragma unroll
-                for (int ks = 0; ks < 4; ++ks) {
-                    mma_f8_ts(d, tmem + TM_Q + 32 * kc + 8 * ks,
-                              make_desc(kb_lo + ((kc * KV_CHUNK + ks * 32) >> 4), DESC_HI_SW128), IDESC_QK_F8, (kc | ks) != 0);
-                    if ((SMLA_DBG & 16) && t_it == 8) trace(tr, tc, 100 + kc * 4 + ks, t_it);
-                }
-            }
-#pragma unroll
-            for (int ks = 0; ks < 4; ++ks) {
-                mma_f16(d, make_desc(qr_lo + ((ks * 32) >> 4), DESC_HI_SW128),
-                        make_desc(kb_lo + ((ST_ROPE + ks * 32) >> 4), DESC_HI_SW128), IDESC_QK_BF16, true);
-                if ((SMLA_DBG & 16) && t_it == 8) trace(tr, tc, 116 + ks, t_it);
-            }
-            tc_commit(bar(BAR_SREADY + b));
-        };
         for (int req = meta.begin_req; req <= last_req && ok; ++req) {
             Work w;
             if (!get_work(p, meta, req, w)) continue;
-            ok = wait(BAR_QREADY, rq & 1u, W_QREADY);
+            ok = mbar_wait_thread(bar(BAR_QREADY), rq & 1u, abort_flag, W_QREADY);
             if (!ok) break;
             ++rq;
-            ok = wait(BAR_FULL + it % NSTAGE, (it / NSTAGE) & 1u, W_FULL);
-            if (!ok) break;
-            tc_fence_after();
-            issue_qk(it);
-            for (int j = 0; j < w.nblk; ++j, ++it) {
-                if (j + 1 < w.nblk) {
-                    const uint32_t nx = it + 1;
-                    ok = wait(BAR_FULL + nx % NSTAGE, (nx / NSTAGE) & 1u, W_FULL);
+            for (int j = 0; j < w.nblk && ok; ++j, ++it) {
+                const uint32_t st = it % NSTAGE, b = it & 1u;
+                if (it >= 2) {
+                    ok = mbar_wait_thread(bar(BAR_PVDONE + b), ((it - 2) >> 1) & 1u, abort_flag, W_PVDONE);
                     if (!ok) break;
-                    tc_fence_after();
-                    trace(tr, tc, 80, nx);
-                    issue_qk(nx);
-                    trace(tr, tc, 81, nx);
                 }
-                const uint32_t b = it & 1u, st = it % NSTAGE;
-                ok = wait(BAR_PREADY + b, (it >> 1) & 1u, W_PREADY);
+                ok = mbar_wait_thread(bar(BAR_FULL + st), (it / NSTAGE) & 1u, abort_flag, W_FULL);
+                if (!ok) break;
+                tc_fence_after();
+                trace(tr, tc, 80, it);
+                const uint32_t kb_lo = desc_lo(base + ST_OFF + st * ST_BYTES, 16);
+                const uint32_t d = tmem + TM_S + 64 * b;
+#pragma unroll
+                for (int kc = 0; kc < 4; ++kc) {
+#pragma unroll
+                    for (int ks = 0; ks < 4; ++ks) {
+                        mma_f8_ts(d, tmem + TM_Q + 32 * kc + 8 * ks,
+                                  make_desc(kb_lo + ((kc * KV_CHUNK + ks * 32) >> 4), DESC_HI_SW128), IDESC_QK_F8, (kc | ks) != 0);
+                    }
+                }
+#pragma unroll
+                for (int ks = 0; ks < 4; ++ks) {
+                    mma_f16(d, make_desc(qr_lo + ((ks * 32) >> 4), DESC_HI_SW128),
+                            make_desc(kb_lo + ((ST_ROPE + ks * 32) >> 4), DESC_HI_SW128), IDESC_QK_BF16, true);
+                }
+                tc_commit(bar(BAR_SREADY + b));
+                trace(tr, tc, 81, it);
+            }
+        }
+    } else if (warp == MMA_WARP + 1 && lane == 0) {
+        // =================================================================== P.V MMA issue
+        uint32_t it = 0;
+        bool ok = true;
+        for (int req = meta.begin_req; req <= last_req && ok; ++req) {
+            Work w;
+            if (!get_work(p, meta, req, w)) continue;
+            for (int j = 0; j < w.nblk && ok; ++j, ++it) {
+                const uint32_t st = it % NSTAGE, b = it & 1u;
+                ok = mbar_wait_thread(bar(BAR_PREADY + b), (it >> 1) & 1u, abort_flag, W_PREADY);
                 if (!ok) break;
                 tc_fence_after();
                 trace(tr, tc, 82, it);

@@ -34,6 +34,16 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity, uin
     (void)hint_ns;
     return ok != 0;
 }
+// One non-blocking poll.
+__device__ __forceinline__ bool mbar_test(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+    return ok != 0;
+}
 
 // Warp-wide wait for the phase with the given parity.  Lane 0 polls (32 lanes polling one
 // mbarrier only add shared-memory traffic), the warp reconverges on the result.  The wait gives
@@ -58,6 +68,20 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
     return ok != 0;
 }
 
+// Variant for waits on the critical path: every lane blocks in mbarrier.try_wait itself (the
+// hardware parks the thread until the phase completes or its own time limit passes), so the warp
+// resumes as soon as the barrier flips instead of after a sleep interval.  Same bounds and
+// give-up protocol as mbar_wait.
+__device__ __forceinline__ bool mbar_wait_hot(uint32_t bar, uint32_t parity, volatile int* abort, int code) {
+    uint32_t ok = 0;
+    for (uint32_t i = 0; i < WAIT_POLLS; ++i) {
+        if (mbar_try_wait(bar, parity, WAIT_HINT_NS)) { ok = 1; break; }
+        if ((i & 255u) == 255u && *abort != 0) break;
+    }
+    if (!ok) atomicCAS(const_cast<int*>(abort), 0, code);
+    return __all_sync(0xffffffffu, ok != 0);
+}
+
 // Single-thread variant of mbar_wait (same bounds and give-up protocol), for a role that is run
 // by one lane only.
 __device__ __forceinline__ bool mbar_wait_thread(uint32_t bar, uint32_t parity, volatile int* abort, int code) {
@@ -76,6 +100,10 @@ __device__ __forceinline__ void cp_async16(uint32_t dst, const void* src) {
 // Copies src_bytes (0 or 16) bytes and zero-fills the rest of the 16-byte destination.
 __device__ __forceinline__ void cp_async16_zfill(uint32_t dst, const void* src, uint32_t src_bytes) {
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(src_bytes) : "memory");
+}
+// Asks L2 to fetch [src, src + bytes) from DRAM; src 16-byte aligned, bytes a multiple of 16.
+__device__ __forceinline__ void prefetch_l2_bulk(const void* src, uint32_t bytes) {
+    asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(src), "r"(bytes) : "memory");
 }
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
 template <int N>
