@@ -4,7 +4,8 @@
 // every request costs its block count plus a fixed overhead, each partition receives
 // ceil(total / parts) + overhead units, and a request that straddles a partition boundary
 // becomes one more split.  One warp: lanes count blocks in parallel, lane 0 walks the
-// partitions (the walk is inherently sequential and a few hundred steps long).
+// partitions (the walk is inherently sequential and a few hundred steps long) entirely in
+// shared memory, then all lanes copy the records out.
 #include "common.cuh"
 
 namespace smla {
@@ -23,6 +24,7 @@ __global__ void __launch_bounds__(32) sched_meta_kernel(const SchedArgs a) {
     extern __shared__ int sh[];
     int* nblk = sh;               // [b]   blocks of request i
     int* splits = sh + a.b;       // [b+1] prefix sum of splits
+    int* meta_sh = sh + 2 * a.b + 1;   // [parts][8] records, copied out at the end
     const int lane = threadIdx.x;
 
     int cost = 0;
@@ -69,10 +71,13 @@ __global__ void __launch_bounds__(32) sched_meta_kernel(const SchedArgs a) {
             m.last_split = (m.end_req >= 0 && m.end_req < a.b && m.end_block != nblk[m.end_req]);
             if (m.begin_req == m.end_req) m.first_split = m.last_split = (m.first_split | m.last_split);
             m.pad = 0;
-            a.meta[p] = m;
+            *reinterpret_cast<SchedMeta*>(meta_sh + 8 * p) = m;
         }
     }
     __syncwarp();
+    static_assert(sizeof(SchedMeta) == 32, "scheduler records are eight 32-bit words");
+    int* meta_out = reinterpret_cast<int*>(a.meta);
+    for (int i = lane; i < 8 * a.parts; i += 32) meta_out[i] = meta_sh[i];
     for (int i = lane; i <= a.b; i += 32) a.num_splits[i] = splits[i];
 }
 
@@ -83,7 +88,7 @@ int launch_sched_meta(int b, int topk, int extra_topk, int num_sm_parts, int fix
                       int32_t* sched_meta, int32_t* num_splits, cudaStream_t stream) {
     SchedArgs a{b, topk, extra_topk, num_sm_parts, fixed_overhead, topk_length, extra_topk_length,
                 reinterpret_cast<SchedMeta*>(sched_meta), num_splits};
-    const size_t smem = sizeof(int) * (2 * (size_t)b + 1);
+    const size_t smem = sizeof(int) * (2 * (size_t)b + 1 + 8 * (size_t)num_sm_parts + 8);
     static bool big_smem[64] = {};
     if (smem > 48 * 1024) {
         int dev = 0;

@@ -127,7 +127,8 @@ def sparse_mla_decode_fwd(
     impl: int = IMPL_AUTO,
     num_sm_parts: Optional[int] = None,
 ) -> Tuple[torch.Tensor, torch.Tensor]:
-    """Split-KV sparse-MLA decode: scheduler -> attention -> combine.
+    """Split-KV sparse-MLA decode: scheduler -> attention -> combine (attention alone when the
+    partition count equals the number of requests, i.e. when nothing is split).
 
     q [T, H, 576] bf16, kv_cache packed 656-byte rows, indices [T, topk] int32 (-1 = no entry).
     Returns (out [T, H, 512] bf16, lse [T, H] fp32, base-2 LSE of the scaled logits).
@@ -144,17 +145,25 @@ def sparse_mla_decode_fwd(
 
     if num_sm_parts is None:
         num_sm_parts = pick_num_sm_parts(num_tokens, num_sms(q.device))
-    total_splits = num_tokens + num_sm_parts
-    ws = scratch(q.device, total_splits, num_heads, num_tokens, num_sm_parts)
     lib = _lib.load()
     stream = stream_ptr(q.device)
-    check(lib.smla_sched_meta(num_tokens, topk, 0, num_sm_parts, FIXED_OVERHEAD, ptr(topk_length), None,
-                              ptr(ws["sched_meta"]), ptr(ws["num_splits"]), stream))
     if out is not None:
         output = out.view(num_tokens, num_heads, d_v)
     else:
         output = torch.empty((num_tokens, num_heads, d_v), dtype=torch.bfloat16, device=q.device)
     out_lse = torch.empty((num_tokens, num_heads), dtype=torch.float32, device=q.device)
+    if num_sm_parts == num_tokens:
+        # One partition per request: nothing is split, so neither the scheduler nor the combine
+        # has anything to decide; the attention kernel derives the trivial schedule itself.
+        check(lib.smla_prefill(
+            ptr(q), ptr(kv_cache), ptr(indices), ptr(output), ptr(out_lse), None, num_tokens, num_heads,
+            topk, float(sm_scale), page_block_size, page_stride, ptr(attn_sink), ptr(topk_length), impl,
+            ptr(status_buffer(q.device)), stream))
+        return output, out_lse
+    total_splits = num_tokens + num_sm_parts
+    ws = scratch(q.device, total_splits, num_heads, num_tokens, num_sm_parts)
+    check(lib.smla_sched_meta(num_tokens, topk, 0, num_sm_parts, FIXED_OVERHEAD, ptr(topk_length), None,
+                              ptr(ws["sched_meta"]), ptr(ws["num_splits"]), stream))
     check(lib.smla_decode_splitkv(
         ptr(q), ptr(kv_cache), ptr(indices), ptr(ws["o_accum"]), ptr(ws["lse_accum"]), ptr(output), ptr(out_lse),
         ptr(ws["sched_meta"]), ptr(ws["num_splits"]), num_tokens, num_heads, topk, float(sm_scale),
