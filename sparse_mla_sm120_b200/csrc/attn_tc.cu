@@ -63,7 +63,7 @@ static_assert(N_SM_WARPS * 32 * REGS_SOFTMAX + (N_PR_WARPS + N_FX_WARPS) * 32 * 
                   <= TC_THREADS * REGS_LAUNCH, "register budgets exceed what the CTA owns");
 static_assert((N_SM_WARPS % 4) == 0 && (N_PR_WARPS % 4) == 0 && (N_FX_WARPS % 4) == 0, "setmaxnreg acts on whole warpgroups");
 static_assert(65536 / TC_THREADS / 8 * 8 == REGS_LAUNCH, "launch-time registers per thread");
-constexpr int NSTAGE = 4;
+constexpr int NSTAGE = 5;
 #ifndef SMLA_PF
 #define SMLA_PF 0
 #endif
@@ -79,16 +79,18 @@ constexpr uint32_t QR_OFF = 0;                       // Q RoPE bf16, K-major 128
 constexpr uint32_t ST_OFF = QR_OFF + 128 * 128;      // KV stages
 constexpr uint32_t KV_CHUNK = 64 * 128;              // one 128-dim chunk of a 64-token tile
 constexpr uint32_t ST_ROPE = 4 * KV_CHUNK;           // RoPE tile inside a stage
-constexpr uint32_t ST_SCALE = ST_ROPE + 64 * 128;    // the rows' 4 fp32 scales, [64 x 16 B]
+constexpr uint32_t ST_SCALE = ST_ROPE + 64 * 128;    // [64 x 16 B]: the rows' 4 fp32 scales as gathered; the fix-up replaces
+                                                     // them in place by (s_t, log2 s_t, 1/s_t, 0)
 constexpr uint32_t ST_BYTES = ST_SCALE + 64 * 16;    // 41984 = 41 * 1024
-constexpr uint32_t QSTG_OFF = ST_OFF + NSTAGE * ST_BYTES;   // Q staging, per softmax warp [32 rows x 144 B]
-constexpr uint32_t QSTG_ROW = 144;
-constexpr uint32_t QSTG_WARP = 32 * QSTG_ROW;
-constexpr uint32_t TOK_OFF = QSTG_OFF + N_SM_WARPS * QSTG_WARP;   // per stage: s_t[64], log2 s_t[64], 1/s_t[64]
-constexpr uint32_t TOK_BYTES = 3 * 64 * 4;
-constexpr uint32_t XCH_OFF = TOK_OFF + NSTAGE * TOK_BYTES;   // pair exchange: [2 buffers][2 halves][128 rows] fp32
-constexpr uint32_t BAR_OFF = XCH_OFF + 2 * 2 * 128 * 4;
-// barriers (8 B each): full[4] empty[4] loaded[4] s_ready[2] p_ready[2] pv_done[2] q_ready
+// Pair exchange [2 buffers][2 halves][128 rows] fp32 (2 KB); the same region doubles as the
+// Q staging slabs of the softmax warps (8 x 512 B) while a request's Q is being quantised.
+constexpr uint32_t XCH_OFF = ST_OFF + NSTAGE * ST_BYTES;
+constexpr uint32_t QSTG_OFF = XCH_OFF;
+constexpr uint32_t QSTG_WARP = 32 * 16;              // 32 rows x 16 e4m3 values
+constexpr uint32_t XCH_BYTES = N_SM_WARPS * QSTG_WARP;
+static_assert(XCH_BYTES >= 2 * 2 * 128 * 4, "exchange buffers must fit the region");
+constexpr uint32_t BAR_OFF = XCH_OFF + XCH_BYTES;
+// barriers (8 B each): full[NSTAGE] empty[NSTAGE] loaded[NSTAGE] s_ready[2] p_ready[2] pv_done[2] q_ready
 constexpr int BAR_FULL = 0, BAR_EMPTY = NSTAGE, BAR_LOADED = 2 * NSTAGE, BAR_SREADY = 3 * NSTAGE,
               BAR_PREADY = BAR_SREADY + 2, BAR_PVDONE = BAR_PREADY + 2, BAR_QREADY = BAR_PVDONE + 2, NBAR = BAR_QREADY + 1;
 constexpr uint32_t MISC_OFF = BAR_OFF + NBAR * 8;    // tmem base (4 B), abort flag (4 B)
@@ -284,27 +286,42 @@ __global__ void __launch_bounds__(TC_THREADS, 1) attn_tc_kernel(const AttnParams
             const float sq = pow2_ceil(fmaxf(amax, 1e-4f) * (1.f / 448.f));
             const float inv_sq = __uint_as_float(0x7f000000u - __float_as_uint(sq));   // 1/sq, sq a power of two
             const float my_sqc = live ? sq * p.sm_scale * LOG2E : 0.f;
-            named_bar_sync(1 + quarter, 64);   // xch may be reused
-            // quantise, transpose through the warp's staging slab, store to tensor memory
+            // the exchange region now turns into the staging slabs of all eight warps
+            named_bar_sync(5, N_SM_WARPS * 32);
+            // quantise, transpose through the warp's staging slab, store to tensor memory.  One round
+            // handles 16 dims of all 32 rows: lane l loads 8 values of row l/2 (and of row 16 + l/2),
+            // the slab then holds 16 bytes per row and lane r reads its own row back.
+            {
+                const int lrow = lane >> 1, lhalf = lane & 1;
+                const float s_lo = __shfl_sync(0xffffffffu, inv_sq, lrow), s_hi = __shfl_sync(0xffffffffu, inv_sq, 16 + lrow);
+                const __nv_bfloat16* src_lo = qbase + (size_t)lrow * D_QK + lhalf * 8;
+                const __nv_bfloat16* src_hi = src_lo + (size_t)16 * D_QK;
+                const bool v_lo = lrow < rows_here, v_hi = 16 + lrow < rows_here;
 #pragma unroll 1
-            for (int qq = 0; qq < 2; ++qq) {
-#pragma unroll 8
-                for (int r = 0; r < 32; ++r) {
-                    uint2 a = make_uint2(0, 0);
-                    if (r < rows_here) a = __ldg(reinterpret_cast<const uint2*>(qbase + (size_t)r * D_QK + qq * 128 + lane * 4));
-                    const float s = __shfl_sync(0xffffffffu, inv_sq, r);
-                    *reinterpret_cast<uint32_t*>(qstg + r * QSTG_ROW + lane * 4) =
-                        pack_e4m3x4(bf16lo(a.x) * s, bf16hi(a.x) * s, bf16lo(a.y) * s, bf16hi(a.y) * s);
-                }
-                __syncwarp();
-                uint32_t wq[32];
+                for (int qq = 0; qq < 2; ++qq) {
+                    uint4 a_lo[8], a_hi[8];
 #pragma unroll
-                for (int c = 0; c < 8; ++c) {
-                    const uint4 v = *reinterpret_cast<const uint4*>(qstg + lane * QSTG_ROW + c * 16);
-                    wq[4 * c] = v.x; wq[4 * c + 1] = v.y; wq[4 * c + 2] = v.z; wq[4 * c + 3] = v.w;
+                    for (int rd = 0; rd < 8; ++rd) {
+                        a_lo[rd] = v_lo ? __ldg(reinterpret_cast<const uint4*>(src_lo + qq * 128 + rd * 16)) : make_uint4(0, 0, 0, 0);
+                        a_hi[rd] = v_hi ? __ldg(reinterpret_cast<const uint4*>(src_hi + qq * 128 + rd * 16)) : make_uint4(0, 0, 0, 0);
+                    }
+                    uint32_t wq[32];
+#pragma unroll
+                    for (int rd = 0; rd < 8; ++rd) {
+                        const uint4 a = a_lo[rd], b4 = a_hi[rd];
+                        *reinterpret_cast<uint2*>(qstg + lrow * 16 + lhalf * 8) =
+                            make_uint2(pack_e4m3x4(bf16lo(a.x) * s_lo, bf16hi(a.x) * s_lo, bf16lo(a.y) * s_lo, bf16hi(a.y) * s_lo),
+                                       pack_e4m3x4(bf16lo(a.z) * s_lo, bf16hi(a.z) * s_lo, bf16lo(a.w) * s_lo, bf16hi(a.w) * s_lo));
+                        *reinterpret_cast<uint2*>(qstg + (16 + lrow) * 16 + lhalf * 8) =
+                            make_uint2(pack_e4m3x4(bf16lo(b4.x) * s_hi, bf16hi(b4.x) * s_hi, bf16lo(b4.y) * s_hi, bf16hi(b4.y) * s_hi),
+                                       pack_e4m3x4(bf16lo(b4.z) * s_hi, bf16hi(b4.z) * s_hi, bf16lo(b4.w) * s_hi, bf16hi(b4.w) * s_hi));
+                        __syncwarp();
+                        const uint4 v = *reinterpret_cast<const uint4*>(qstg + lane * 16);
+                        wq[4 * rd] = v.x; wq[4 * rd + 1] = v.y; wq[4 * rd + 2] = v.z; wq[4 * rd + 3] = v.w;
+                        __syncwarp();
+                    }
+                    tmem_st32(lane_addr + TM_Q + hh * 64 + qq * 32, wq);
                 }
-                tmem_st32(lane_addr + TM_Q + hh * 64 + qq * 32, wq);
-                __syncwarp();
             }
             // Q RoPE: warp (quarter, hh) stores rows [16*hh, +16) of its quarter, pre-divided by sq
 #pragma unroll
@@ -339,22 +356,23 @@ __global__ void __launch_bounds__(TC_THREADS, 1) attn_tc_kernel(const AttnParams
                 if (SMLA_DBG & 1) { tc_fence_before(); mbar_arrive(bar(BAR_PREADY + b)); continue; }
                 uint32_t sv[32];
                 tmem_ld32(lane_addr + TM_S + 64 * b + 32 * hh, sv);
-                const float* tok = reinterpret_cast<const float*>(sm + TOK_OFF + st * TOK_BYTES) + 32 * hh;
+                // per token (s_t, log2 s_t, 1/s_t, 0), published with the tile by the fix-up warps
+                const float4* tok = reinterpret_cast<const float4*>(sm + ST_OFF + st * ST_BYTES + ST_SCALE) + 32 * hh;
                 tmem_wait_ld();
                 float z[32];
                 float mx0 = -INFINITY, mx1 = -INFINITY;
 #pragma unroll
                 for (int t = 0; t < 32; t += 4) {
-                    const float4 s4 = *reinterpret_cast<const float4*>(tok + t);
-                    const float4 g4 = *reinterpret_cast<const float4*>(tok + 64 + t);
-                    z[t + 0] = fmaf(__uint_as_float(sv[t + 0]) * s4.x, my_sqc, g4.x);
-                    z[t + 1] = fmaf(__uint_as_float(sv[t + 1]) * s4.y, my_sqc, g4.y);
-                    z[t + 2] = fmaf(__uint_as_float(sv[t + 2]) * s4.z, my_sqc, g4.z);
-                    z[t + 3] = fmaf(__uint_as_float(sv[t + 3]) * s4.w, my_sqc, g4.w);
+                    const float2 a0 = *reinterpret_cast<const float2*>(tok + t), a1 = *reinterpret_cast<const float2*>(tok + t + 1);
+                    const float2 a2 = *reinterpret_cast<const float2*>(tok + t + 2), a3 = *reinterpret_cast<const float2*>(tok + t + 3);
+                    z[t + 0] = fmaf(__uint_as_float(sv[t + 0]) * a0.x, my_sqc, a0.y);
+                    z[t + 1] = fmaf(__uint_as_float(sv[t + 1]) * a1.x, my_sqc, a1.y);
+                    z[t + 2] = fmaf(__uint_as_float(sv[t + 2]) * a2.x, my_sqc, a2.y);
+                    z[t + 3] = fmaf(__uint_as_float(sv[t + 3]) * a3.x, my_sqc, a3.y);
                     mx0 = fmaxf(mx0, fmaxf(z[t], z[t + 1]));
                     mx1 = fmaxf(mx1, fmaxf(z[t + 2], z[t + 3]));
                     if (p.out_max_logits != nullptr)   // z - log2(s_t) is the scaled logit itself (NaN for masked entries is ignored by fmaxf)
-                        x_max = fmaxf(x_max, fmaxf(fmaxf(z[t] - g4.x, z[t + 1] - g4.y), fmaxf(z[t + 2] - g4.z, z[t + 3] - g4.w)));
+                        x_max = fmaxf(x_max, fmaxf(fmaxf(z[t] - a0.y, z[t + 1] - a1.y), fmaxf(z[t + 2] - a2.y, z[t + 3] - a3.y)));
                 }
                 // row maximum over both column halves
                 xch[b * 256 + hh * 128 + row] = fmaxf(mx0, mx1);
@@ -389,11 +407,10 @@ __global__ void __launch_bounds__(TC_THREADS, 1) attn_tc_kernel(const AttnParams
                 float l0 = 0.f, l1 = 0.f;
 #pragma unroll
                 for (int t = 0; t < 32; t += 4) {
-                    const float4 i4 = *reinterpret_cast<const float4*>(tok + 128 + t);
                     const float p0 = ex2(z[t + 0] - m_off), p1 = ex2(z[t + 1] - m_off);
                     const float p2 = ex2(z[t + 2] - m_off), p3 = ex2(z[t + 3] - m_off);
-                    l0 = fmaf(p0, i4.x, l0); l1 = fmaf(p1, i4.y, l1);
-                    l0 = fmaf(p2, i4.z, l0); l1 = fmaf(p3, i4.w, l1);
+                    l0 = fmaf(p0, tok[t].z, l0); l1 = fmaf(p1, tok[t + 1].z, l1);
+                    l0 = fmaf(p2, tok[t + 2].z, l0); l1 = fmaf(p3, tok[t + 3].z, l1);
                     pw[t >> 2] = pack_e4m3x4(p0, p1, p2, p3);
                 }
                 l_run += l0 + l1;
@@ -603,12 +620,10 @@ __global__ void __launch_bounds__(TC_THREADS, 1) attn_tc_kernel(const AttnParams
                 const float inv_s = (smax > 0.f) ? __uint_as_float(0x7f000000u - __float_as_uint(smax)) : 0.f;
                 // ratio of (row lane % 8, block lane / 8) to its row scale: a power of two <= 1
                 const float my_ratio = (blk == 0 ? sc.x : (blk == 1 ? sc.y : (blk == 2 ? sc.z : sc.w))) * inv_s;
-                if (lane < 8) {
-                    float* tok = reinterpret_cast<float*>(sm + TOK_OFF + st * TOK_BYTES);
-                    tok[my_row] = smax;
-                    tok[64 + my_row] = (smax > 0.f) ? (float)((int)(__float_as_uint(smax) >> 23) - 127) : -INFINITY;
-                    tok[128 + my_row] = inv_s;
-                }
+                __syncwarp();   // every lane has read its row's scales before they are replaced
+                if (lane < 8)
+                    *reinterpret_cast<float4*>(sp + ST_SCALE + my_row * 16) =
+                        make_float4(smax, (smax > 0.f) ? (float)((int)(__float_as_uint(smax) >> 23) - 127) : -INFINITY, inv_s, 0.f);
 #pragma unroll
                 for (int g = 0; g < 2; ++g) {
                     const int rl = g * 4 + (lane >> 3);
