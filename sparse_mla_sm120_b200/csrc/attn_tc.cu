@@ -82,13 +82,9 @@ constexpr uint32_t ST_ROPE = 4 * KV_CHUNK;           // RoPE tile inside a stage
 constexpr uint32_t ST_SCALE = ST_ROPE + 64 * 128;    // [64 x 16 B]: the rows' 4 fp32 scales as gathered; the fix-up replaces
                                                      // them in place by (s_t, log2 s_t, 1/s_t, 0)
 constexpr uint32_t ST_BYTES = ST_SCALE + 64 * 16;    // 41984 = 41 * 1024
-// Pair exchange [2 buffers][2 halves][128 rows] fp32 (2 KB); the same region doubles as the
-// Q staging slabs of the softmax warps (8 x 512 B) while a request's Q is being quantised.
+// Pair exchange [2 buffers][2 halves][128 rows] fp32
 constexpr uint32_t XCH_OFF = ST_OFF + NSTAGE * ST_BYTES;
-constexpr uint32_t QSTG_OFF = XCH_OFF;
-constexpr uint32_t QSTG_WARP = 32 * 16;              // 32 rows x 16 e4m3 values
-constexpr uint32_t XCH_BYTES = N_SM_WARPS * QSTG_WARP;
-static_assert(XCH_BYTES >= 2 * 2 * 128 * 4, "exchange buffers must fit the region");
+constexpr uint32_t XCH_BYTES = 2 * 2 * 128 * 4;
 constexpr uint32_t BAR_OFF = XCH_OFF + XCH_BYTES;
 // barriers (8 B each): full[NSTAGE] empty[NSTAGE] loaded[NSTAGE] s_ready[2] p_ready[2] pv_done[2] q_ready
 constexpr int BAR_FULL = 0, BAR_EMPTY = NSTAGE, BAR_LOADED = 2 * NSTAGE, BAR_SREADY = 3 * NSTAGE,
@@ -250,79 +246,67 @@ __global__ void __launch_bounds__(TC_THREADS, 1) attn_tc_kernel(const AttnParams
         const int row = quarter * 32 + lane;              // head index == TMEM lane
         const uint32_t lane_addr = tmem + ((uint32_t)(quarter * 32) << 16);
         float* xch = reinterpret_cast<float*>(sm + XCH_OFF);   // [2][2][128]
-        uint8_t* qstg = sm + QSTG_OFF + warp * QSTG_WARP;
         const bool live = row < p.num_heads;
         uint32_t it = 0;                          // running tile counter of this CTA
         bool ok = true;
         for (int req = meta.begin_req; req <= last_req && ok; ++req) {
             Work w;
             if (!get_work(p, meta, req, w)) continue;
-            // ---- Q: this warp owns rows [32*quarter, +32) x no-PE dims [256*hh, +256) -----------
-            const __nv_bfloat16* qbase = p.q + ((size_t)req * p.num_heads + quarter * 32) * D_QK + hh * 256;
-            const int rows_here = min(max(p.num_heads - quarter * 32, 0), 32);
-            float amax_mine = 0.f;                // lane r ends up with the amax of row r (this half)
-#pragma unroll 1
-            for (int r0 = 0; r0 < 32; r0 += 8) {
-                float am[8];
-#pragma unroll
-                for (int u = 0; u < 8; ++u) {
-                    uint4 a = make_uint4(0, 0, 0, 0);
-                    if (r0 + u < rows_here) a = __ldg(reinterpret_cast<const uint4*>(qbase + (size_t)(r0 + u) * D_QK + lane * 8));
-                    am[u] = fmaxf(fmaxf(fmaxf(fabsf(bf16lo(a.x)), fabsf(bf16hi(a.x))), fmaxf(fabsf(bf16lo(a.y)), fabsf(bf16hi(a.y)))),
-                                  fmaxf(fmaxf(fabsf(bf16lo(a.z)), fabsf(bf16hi(a.z))), fmaxf(fabsf(bf16lo(a.w)), fabsf(bf16hi(a.w)))));
-                }
-#pragma unroll
-                for (int o = 16; o >= 1; o >>= 1) {
-#pragma unroll
-                    for (int u = 0; u < 8; ++u) am[u] = fmaxf(am[u], __shfl_xor_sync(0xffffffffu, am[u], o));
-                }
-#pragma unroll
-                for (int u = 0; u < 8; ++u) if (lane == r0 + u) amax_mine = am[u];
-            }
-            // both halves of a row agree on one scale
-            xch[hh * 128 + row] = amax_mine;
-            named_bar_sync(1 + quarter, 64);
-            const float amax = fmaxf(amax_mine, xch[(1 - hh) * 128 + row]);
-            const float sq = pow2_ceil(fmaxf(amax, 1e-4f) * (1.f / 448.f));
-            const float inv_sq = __uint_as_float(0x7f000000u - __float_as_uint(sq));   // 1/sq, sq a power of two
-            const float my_sqc = live ? sq * p.sm_scale * LOG2E : 0.f;
-            // the exchange region now turns into the staging slabs of all eight warps
-            named_bar_sync(5, N_SM_WARPS * 32);
-            // quantise, transpose through the warp's staging slab, store to tensor memory.  One round
-            // handles 16 dims of all 32 rows: lane l loads 8 values of row l/2 (and of row 16 + l/2),
-            // the slab then holds 16 bytes per row and lane r reads its own row back.
+            // ---- Q: this warp owns rows [32*quarter, +32) x no-PE dims [256*hh, +256), read once ----
+            // The 16x256b store shape takes a row from four lanes: lane (g = lane/4, c = lane%4) holds,
+            // for every block i of 32 dims, dims [32i + 8c, +8) of rows g and g + 8 of a 16-row group,
+            // which is also how it loads them (16 bytes of bf16 per row and block).  A group is kept
+            // in registers between finding its rows' maxima and quantising them.
             {
-                const int lrow = lane >> 1, lhalf = lane & 1;
-                const float s_lo = __shfl_sync(0xffffffffu, inv_sq, lrow), s_hi = __shfl_sync(0xffffffffu, inv_sq, 16 + lrow);
-                const __nv_bfloat16* src_lo = qbase + (size_t)lrow * D_QK + lhalf * 8;
-                const __nv_bfloat16* src_hi = src_lo + (size_t)16 * D_QK;
-                const bool v_lo = lrow < rows_here, v_hi = 16 + lrow < rows_here;
+                const int g = lane >> 2, c4 = lane & 3;
 #pragma unroll 1
-                for (int qq = 0; qq < 2; ++qq) {
-                    uint4 a_lo[8], a_hi[8];
+                for (int hf = 0; hf < 2; ++hf) {
+                    const int r_a = quarter * 32 + 16 * hf + g, r_b = r_a + 8;
+                    const __nv_bfloat16* src_a = p.q + ((size_t)req * p.num_heads + r_a) * D_QK + hh * 256 + c4 * 8;
+                    const __nv_bfloat16* src_b = src_a + (size_t)8 * D_QK;
+                    const bool v_a = r_a < p.num_heads, v_b = r_b < p.num_heads;
+                    uint4 xa[8], xb[8];
 #pragma unroll
-                    for (int rd = 0; rd < 8; ++rd) {
-                        a_lo[rd] = v_lo ? __ldg(reinterpret_cast<const uint4*>(src_lo + qq * 128 + rd * 16)) : make_uint4(0, 0, 0, 0);
-                        a_hi[rd] = v_hi ? __ldg(reinterpret_cast<const uint4*>(src_hi + qq * 128 + rd * 16)) : make_uint4(0, 0, 0, 0);
+                    for (int i = 0; i < 8; ++i) {
+                        xa[i] = v_a ? __ldg(reinterpret_cast<const uint4*>(src_a + 32 * i)) : make_uint4(0, 0, 0, 0);
+                        xb[i] = v_b ? __ldg(reinterpret_cast<const uint4*>(src_b + 32 * i)) : make_uint4(0, 0, 0, 0);
                     }
-                    uint32_t wq[32];
+                    auto absmax8 = [](const uint4& a) {
+                        return fmaxf(fmaxf(fmaxf(fabsf(bf16lo(a.x)), fabsf(bf16hi(a.x))), fmaxf(fabsf(bf16lo(a.y)), fabsf(bf16hi(a.y)))),
+                                     fmaxf(fmaxf(fabsf(bf16lo(a.z)), fabsf(bf16hi(a.z))), fmaxf(fabsf(bf16lo(a.w)), fabsf(bf16hi(a.w)))));
+                    };
+                    float am_a = 0.f, am_b = 0.f;
 #pragma unroll
-                    for (int rd = 0; rd < 8; ++rd) {
-                        const uint4 a = a_lo[rd], b4 = a_hi[rd];
-                        *reinterpret_cast<uint2*>(qstg + lrow * 16 + lhalf * 8) =
-                            make_uint2(pack_e4m3x4(bf16lo(a.x) * s_lo, bf16hi(a.x) * s_lo, bf16lo(a.y) * s_lo, bf16hi(a.y) * s_lo),
-                                       pack_e4m3x4(bf16lo(a.z) * s_lo, bf16hi(a.z) * s_lo, bf16lo(a.w) * s_lo, bf16hi(a.w) * s_lo));
-                        *reinterpret_cast<uint2*>(qstg + (16 + lrow) * 16 + lhalf * 8) =
-                            make_uint2(pack_e4m3x4(bf16lo(b4.x) * s_hi, bf16hi(b4.x) * s_hi, bf16lo(b4.y) * s_hi, bf16hi(b4.y) * s_hi),
-                                       pack_e4m3x4(bf16lo(b4.z) * s_hi, bf16hi(b4.z) * s_hi, bf16lo(b4.w) * s_hi, bf16hi(b4.w) * s_hi));
-                        __syncwarp();
-                        const uint4 v = *reinterpret_cast<const uint4*>(qstg + lane * 16);
-                        wq[4 * rd] = v.x; wq[4 * rd + 1] = v.y; wq[4 * rd + 2] = v.z; wq[4 * rd + 3] = v.w;
-                        __syncwarp();
+                    for (int i = 0; i < 8; ++i) { am_a = fmaxf(am_a, absmax8(xa[i])); am_b = fmaxf(am_b, absmax8(xb[i])); }
+                    am_a = fmaxf(am_a, __shfl_xor_sync(0xffffffffu, am_a, 1)); am_b = fmaxf(am_b, __shfl_xor_sync(0xffffffffu, am_b, 1));
+                    am_a = fmaxf(am_a, __shfl_xor_sync(0xffffffffu, am_a, 2)); am_b = fmaxf(am_b, __shfl_xor_sync(0xffffffffu, am_b, 2));
+                    // both halves of a row agree on one scale
+                    if (c4 == 0) { xch[hh * 128 + r_a] = am_a; xch[hh * 128 + r_b] = am_b; }
+                    named_bar_sync(1 + quarter, 64);
+                    am_a = fmaxf(am_a, xch[(1 - hh) * 128 + r_a]);
+                    am_b = fmaxf(am_b, xch[(1 - hh) * 128 + r_b]);
+                    const float sq_a = pow2_ceil(fmaxf(am_a, 1e-4f) * (1.f / 448.f)), sq_b = pow2_ceil(fmaxf(am_b, 1e-4f) * (1.f / 448.f));
+                    const float ia = __uint_as_float(0x7f000000u - __float_as_uint(sq_a));   // 1/sq, sq a power of two
+                    const float ib = __uint_as_float(0x7f000000u - __float_as_uint(sq_b));
+                    if (c4 == 0) { xch[256 + r_a] = sq_a; xch[256 + r_b] = sq_b; }   // the partner warp writes the same values
+#pragma unroll
+                    for (int h4 = 0; h4 < 2; ++h4) {
+                        uint32_t wq[16];
+#pragma unroll
+                        for (int k = 0; k < 4; ++k) {
+                            const uint4 a = xa[4 * h4 + k], b4 = xb[4 * h4 + k];
+                            wq[4 * k + 0] = pack_e4m3x4(bf16lo(a.x) * ia, bf16hi(a.x) * ia, bf16lo(a.y) * ia, bf16hi(a.y) * ia);
+                            wq[4 * k + 1] = pack_e4m3x4(bf16lo(a.z) * ia, bf16hi(a.z) * ia, bf16lo(a.w) * ia, bf16hi(a.w) * ia);
+                            wq[4 * k + 2] = pack_e4m3x4(bf16lo(b4.x) * ib, bf16hi(b4.x) * ib, bf16lo(b4.y) * ib, bf16hi(b4.y) * ib);
+                            wq[4 * k + 3] = pack_e4m3x4(bf16lo(b4.z) * ib, bf16hi(b4.z) * ib, bf16lo(b4.w) * ib, bf16hi(b4.w) * ib);
+                        }
+                        tmem_st_16x256b_x4(tmem + ((uint32_t)(quarter * 32 + 16 * hf) << 16) + TM_Q + hh * 64 + h4 * 32, wq);
                     }
-                    tmem_st32(lane_addr + TM_Q + hh * 64 + qq * 32, wq);
                 }
+                __syncwarp();   // this warp has written the scales of all 32 rows of its quarter
             }
+            const float sq = xch[256 + row];
+            const float my_sqc = live ? sq * p.sm_scale * LOG2E : 0.f;
             // Q RoPE: warp (quarter, hh) stores rows [16*hh, +16) of its quarter, pre-divided by sq
 #pragma unroll
             for (int g = 0; g < 4; ++g) {
@@ -331,7 +315,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) attn_tc_kernel(const AttnParams
                 uint4 c = make_uint4(0, 0, 0, 0);
                 if (h < p.num_heads)
                     c = __ldg(reinterpret_cast<const uint4*>(p.q + ((size_t)req * p.num_heads + h) * D_QK + D_NOPE + (lane & 7) * 8));
-                const __nv_bfloat162 f = __float2bfloat162_rn(__shfl_sync(0xffffffffu, inv_sq, rl));
+                const __nv_bfloat162 f = __float2bfloat162_rn(__uint_as_float(0x7f000000u - __float_as_uint(xch[256 + h])));   // 1/sq
                 c.x = mul_bf16x2(c.x, f); c.y = mul_bf16x2(c.y, f); c.z = mul_bf16x2(c.z, f); c.w = mul_bf16x2(c.w, f);
                 *reinterpret_cast<uint4*>(sm + QR_OFF + h * 128 + ((((uint32_t)lane & 7u) ^ ((uint32_t)h & 7u)) << 4)) = c;
             }
