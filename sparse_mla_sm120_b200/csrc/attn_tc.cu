@@ -7,7 +7,7 @@
 // (128 heads x 256 dims, 256 columns), two 64-column score buffers, and the quantised Q no-PE
 // operand (128 rows x 512 e4m3 = 128 columns).  The softmax weights P' are written back over the
 // score buffer they came from, so both Q and P' reach the tensor core as TMEM A operands and
-// shared memory only carries the gathered KV tiles (four 64-token stages) and Q RoPE.
+// shared memory only carries the gathered KV tiles (five 64-token stages) and Q RoPE.
 // The two CTAs of a partition both compute the scores and are launched next to each other so
 // that the second gather of a row is served by L2.
 //
@@ -31,15 +31,19 @@
 //
 // Warp roles (768 threads; the first five warpgroups trade registers with setmaxnreg): warps 0-7
 // softmax + epilogue (thread = head row = TMEM lane; warps w and w+4 share a lane quarter and
-// split the 64 score columns / the output columns), warps 8-11 gather issuers (coalesced 16-byte
-// cp.async into 128B-swizzled tiles, never waiting for data), warps 12-19 tile fix-up (scale
-// arrays, RoPE pre-division), warp 20 MMA issue (one lane) and TMEM allocation, warps 21-23 idle.  Every wait is bounded; a wait that gives up records a code in status[] and
-// the CTA drains and exits.
+// split the 64 score columns / the output columns; they also quantise Q, read once, into tensor
+// memory at the start of a request), warps 8-11 gather issuers (coalesced 16-byte cp.async into
+// 128B-swizzled tiles, never waiting for data), warps 12-19 tile fix-up (per-token scale triples,
+// RoPE pre-division, uneven-scale rewrite), warp 20 issues the score MMAs and owns the TMEM
+// allocation, warp 21 issues the P.V MMAs (one lane each), warps 22-23 idle.  Waits on the
+// per-tile critical path block inside mbarrier.try_wait instead of sleeping between polls.
+// Every wait is bounded; a wait that gives up records a code in status[] and the CTA drains and
+// exits.
 #include "common.cuh"
 #include "sm100_ptx.cuh"
 
 #ifndef SMLA_DBG
-#define SMLA_DBG 0   // debugging switches for timing experiments: 1 skip softmax math, 2 skip fix-up work, 4 skip copies
+#define SMLA_DBG 0   // debugging switches for timing experiments: 1 skip softmax math, 2 skip fix-up work, 4 skip copies, 32 no register trading
 #endif
 
 namespace smla {
@@ -52,9 +56,9 @@ constexpr int N_SM_WARPS = 8, N_PR_WARPS = 4, N_FX_WARPS = 8;
 constexpr int FX_ROWS = 8;    // rows of a tile per fix-up warp
 constexpr int FX_WARP0 = N_SM_WARPS + N_PR_WARPS;
 constexpr int MMA_WARP = FX_WARP0 + N_FX_WARPS;
-constexpr int TC_THREADS = (MMA_WARP + 4) * 32;   // the MMA warp's warpgroup is completed by three idle warps
-// Per-thread register budgets after the warpgroups trade registers.  The MMA warp's warpgroup
-// keeps its launch-time allocation (its single issuing thread must not spill).  setmaxnreg.inc
+constexpr int TC_THREADS = (MMA_WARP + 4) * 32;   // the two MMA-issuing warps share a warpgroup with two idle warps
+// Per-thread register budgets after the warpgroups trade registers.  The MMA warps' warpgroup
+// keeps its launch-time allocation (the issuing threads must not spill).  setmaxnreg.inc
 // can only draw on what the CTA was launched with (TC_THREADS x REGS_LAUNCH), so the budgets
 // must fit it or the increase would block for ever; the launcher checks the compiled register
 // count against REGS_LAUNCH before it launches.
@@ -64,13 +68,9 @@ static_assert(N_SM_WARPS * 32 * REGS_SOFTMAX + (N_PR_WARPS + N_FX_WARPS) * 32 * 
 static_assert((N_SM_WARPS % 4) == 0 && (N_PR_WARPS % 4) == 0 && (N_FX_WARPS % 4) == 0, "setmaxnreg acts on whole warpgroups");
 static_assert(65536 / TC_THREADS / 8 * 8 == REGS_LAUNCH, "launch-time registers per thread");
 constexpr int NSTAGE = 5;
-#ifndef SMLA_PF
-#define SMLA_PF 0
-#endif
 #ifndef SMLA_HOT
 #define SMLA_HOT 15    // which waits block in the barrier instead of sleeping between polls: 1 scores, 2 loaded, 4 empty, 8 P.V done
 #endif
-constexpr int PF_DIST = SMLA_PF;       // rows are requested into L2 this many tiles before they are gathered
 constexpr int P_SHIFT = 5;             // P' is stored as e4m3(P' * 2^P_SHIFT)
 constexpr float RESCALE_TAU = 3.0f;    // lazy-rescale threshold (log2 units); P' <= 2^TAU
 
@@ -208,6 +208,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) attn_tc_kernel(const AttnParams
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int part = blockIdx.x >> 1, half = blockIdx.x & 1;
     TraceCursor tc;
+    trace(tr, tc, 1, 0);
     const SchedMeta meta = load_meta(p, part);
 
     if (tid == 0) {
@@ -473,6 +474,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) attn_tc_kernel(const AttnParams
                     if (live && half == 0 && hh == 0) p.lse_accum[(size_t)w.split_idx * p.num_heads + row] = lse;
                 }
                 named_bar_sync(1 + quarter, 64);   // xch is free again
+                trace(tr, tc, 2, it);
             }
         }
     } else if (warp < FX_WARP0) {
@@ -497,33 +499,19 @@ __global__ void __launch_bounds__(TC_THREADS, 1) attn_tc_kernel(const AttnParams
                 const int pos = (w.blk0 + j) * BLOCK_N + my_row;
                 return (j < w.nblk && pos < w.len) ? __ldg(idx_row + pos) : -1;
             };
-            // A shared-memory stage is held from the moment its copies are issued, so the DRAM
-            // latency is taken off that path: lanes 0-15 ask L2 for their row PF_DIST tiles ahead.
             auto row_ptr = [&](int idx) -> const uint8_t* {
                 const unsigned u = (unsigned)idx;
                 return (pbs_shift >= 0)
                     ? p.kv + (int64_t)(u >> pbs_shift) * p.block_stride + (int64_t)(u & (unsigned)(p.page_block_size - 1)) * ROW_BYTES
                     : kv_row_ptr(p.kv, idx, p.page_block_size, p.block_stride);
             };
-            if (PF_DIST > 0 && lane < 16) {
-#pragma unroll 1
-                for (int j = 0; j < PF_DIST && j < w.nblk; ++j) {
-                    const int i = fetch_idx(j);
-                    if (i >= 0) prefetch_l2_bulk(row_ptr(i), ROW_BYTES);
-                }
-            }
             int idx_next = fetch_idx(0), idx_next2 = fetch_idx(1);
-            int idx_pf = (PF_DIST > 0) ? fetch_idx(PF_DIST) : -1;
 #pragma unroll 1
             for (int k = 0; k < w.nblk && ok; ++k) {
                 const uint32_t t_it = it + k, st = t_it % NSTAGE;
                 const int idx = idx_next;
                 idx_next = idx_next2;
                 idx_next2 = fetch_idx(k + 2);
-                if (PF_DIST > 0) {
-                    if (lane < 16 && idx_pf >= 0) prefetch_l2_bulk(row_ptr(idx_pf), ROW_BYTES);
-                    idx_pf = fetch_idx(k + 1 + PF_DIST);
-                }
                 // rows without an entry travel as a null source: their copies zero-fill (size 0, nothing is read)
                 unsigned long long my_src_u = 0ull;
                 if (idx >= 0) my_src_u = reinterpret_cast<unsigned long long>(row_ptr(idx));
@@ -728,6 +716,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) attn_tc_kernel(const AttnParams
         tc_fence_after();
         tmem_dealloc(tmem, TMEM_COLS);
     }
+    trace(tr, tc, 3, 0);
 }
 
 }  // namespace
