@@ -39,7 +39,7 @@ WORKLOAD = ("V3.2-shape sparse-MLA decode: b=64/GPU, s_q=1, h_q=128, topk=2048, 
             "KV len U[4096,32768], paged block 64, packed FP8 656 B rows")
 # DRAM bytes per launch of the attention kernel from the ncu capture summarised in
 # profiles/attn_tc_decode_b64.md (dram__bytes_read.sum + dram__bytes_write.sum of one launch).
-NCU_TRAFFIC_BYTES = 112_157_440
+NCU_TRAFFIC_BYTES = 113_699_328
 
 
 def algorithmic_bytes(num_tokens: int, n_valid: int) -> int:

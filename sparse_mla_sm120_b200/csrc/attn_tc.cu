@@ -1,7 +1,7 @@
 // Sparse-MLA attention on tcgen05 tensor cores (sm_100a): split-KV decode and prefill.
 //
 // Work unit.  One CTA owns one scheduler partition (a run of 64-token blocks of consecutive
-// requests, see sched.cu; for prefill: one query token) and ONE HALF of the 512 output
+// requests, see sched.cu; without a scheduler: a contiguous share of the requests) and ONE HALF of the 512 output
 // dimensions, for all (<= 128) query heads at once: heads are the M = 128 rows of every MMA.
 // Tensor memory (512 columns) holds everything that is reused: the fp32 output accumulator
 // (128 heads x 256 dims, 256 columns), two 64-column score buffers, and the quantised Q no-PE
@@ -135,7 +135,11 @@ __device__ __forceinline__ SchedMeta load_meta(const AttnParams& p, int part) {
     if (p.sched != nullptr) {
         m = p.sched[part];
     } else {
-        m.begin_req = m.end_req = part;
+        // no scheduler: the CTA pairs of the grid share the requests as contiguous, whole ranges
+        // (one request each when there are at least as many pairs as requests)
+        const long long pairs = gridDim.x >> 1;
+        m.begin_req = (int)((long long)part * p.num_tokens / pairs);
+        m.end_req = (int)((long long)(part + 1) * p.num_tokens / pairs) - 1;
         m.begin_block = 0; m.end_block = 0x7fffffff;
         m.begin_split = 0; m.first_split = m.last_split = 0; m.pad = 0;
     }
@@ -739,7 +743,11 @@ int launch_attn_tc(const AttnParams& p, cudaStream_t stream) {
                                                SMEM_ALLOC, cudaGetErrorString(e));
         attr_set[dev] = true;
     }
-    const int parts = p.sched ? p.num_parts : p.num_tokens;
+    static int sm_count[64] = {};
+    if (dev < 64 && sm_count[dev] == 0) cudaDeviceGetAttribute(&sm_count[dev], cudaDevAttrMultiProcessorCount, dev);
+    // Without a scheduler the grid is persistent: at most one CTA per SM, each pair walks its share of the requests.
+    const int max_pairs = (dev < 64 && sm_count[dev] >= 2) ? sm_count[dev] / 2 : 1;
+    const int parts = p.sched ? p.num_parts : (p.num_tokens < max_pairs ? p.num_tokens : max_pairs);
     attn_tc_kernel<<<2 * parts, TC_THREADS, SMEM_ALLOC, stream>>>(p, g_trace);
     return check_launch("attn_tc_kernel");
 }
