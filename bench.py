@@ -491,6 +491,49 @@ def run_reference(args):
     }), flush=True)
 
 
+def run_small_case(name):
+    """Small instances of the secondary kernels, sized for a profiler capture (a few hundred MB on the
+    device, kernels of well under a millisecond); prints one informative JSON line, no headline metric."""
+    from sparse_mla_sm120_b200 import flash_ops, indexer
+    device = torch.device("cuda", 0)
+    torch.cuda.set_device(0)
+    g = torch.Generator(device=device).manual_seed(11)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    if name == "prefill":
+        s_q, rows = 512, 8192
+        kv = indexer.pack_kv_cache(torch.randn((rows, D_QK), device=device, generator=g).to(torch.bfloat16)).view(rows // 64, 64, 1, ROW)
+        q = torch.randn((s_q, HEADS, D_QK), device=device, generator=g).to(torch.bfloat16)
+        idx = torch.stack([torch.randperm(4096 + i, device=device, generator=g)[:TOPK] for i in range(s_q)]).to(torch.int32)
+        fn = lambda: flash_ops.sparse_mla_prefill_fwd(q, kv, idx, SM_SCALE)
+        work = {"flop": 2.0 * s_q * HEADS * TOPK * (D_QK + D_V)}
+        desc = f"prefill s_q={s_q}, h=128, topk=2048, KV {rows} rows"
+    else:
+        s_q, s_k, hh = 512, 65536, 64
+        qi = torch.randn((s_q, hh, 128), device=device, generator=g).to(torch.float8_e4m3fn)
+        kf = torch.randn((s_k, 128), device=device, generator=g)
+        k_scale = kf.abs().amax(dim=1) / 448.0
+        ki = (kf / k_scale.unsqueeze(1)).to(torch.float8_e4m3fn)
+        w = torch.randn((s_q, hh), device=device, generator=g) * 0.1
+        ks = torch.zeros(s_q, dtype=torch.int32, device=device)
+        ke = (61440 + torch.arange(s_q, device=device)).to(torch.int32)
+        logits = torch.empty((s_q, s_k), dtype=torch.float32, device=device)
+
+        def fn():
+            indexer.fp8_mqa_logits(qi, ki, k_scale, w, ks, ke, out=logits)
+            indexer.topk_indices(logits, ks, ke, TOPK)
+        work = {"flop": 2.0 * s_q * hh * 128 * s_k}
+        desc = f"indexer s_q={s_q}, 64 heads, d=128, s_k={s_k}, then top-2048"
+    for _ in range(3):
+        fn()
+    torch.cuda.synchronize()
+    e0.record()
+    for _ in range(3):
+        fn()
+    e1.record(); torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / 3
+    print(json.dumps({"case": name, "workload": desc, "ms": ms, "tflops": work["flop"] / ms / 1e9}), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -498,9 +541,13 @@ def main():
     ap.add_argument("--warmup", type=int, default=50)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-extras", action="store_true")
+    ap.add_argument("--case", default=None, choices=["prefill", "indexer"],
+                    help="run a small instance of a secondary kernel (for profiler captures) instead of the benchmark")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
-    if args.impl == "reference":
+    if args.case is not None:
+        run_small_case(args.case)
+    elif args.impl == "reference":
         run_reference(args)
     else:
         run_ours(args)
