@@ -52,21 +52,51 @@ mqa_logits_scalar_kernel(const uint8_t* __restrict__ q, const uint8_t* __restric
 }
 
 // ---------------------------------------------------------------- top-k: radix select per row
-constexpr int TK_THREADS = 512;
+constexpr int TK_THREADS = 1024;
+constexpr int TK_WARPS = TK_THREADS / 32;
 
 __device__ __forceinline__ uint32_t order_key(float f) {   // larger float <=> larger key
     const uint32_t b = __float_as_uint(f);
     return (b & 0x80000000u) ? ~b : (b | 0x80000000u);
 }
 
-__global__ void __launch_bounds__(TK_THREADS)
+// Applies fn(column, key) to every column of [lo, hi): 16-byte loads over the aligned middle part,
+// four of them in flight per thread, scalar loads at the ragged ends.
+template <typename F>
+__device__ __forceinline__ void for_each_key(const float* __restrict__ x, int lo, int hi, int tid, int nthreads, F fn) {
+    const int a0 = min(hi, (int)(((size_t)lo + 3) & ~(size_t)3));                 // first multiple of 4 >= lo (x is 16-byte aligned)
+    const int a1 = max(a0, hi & ~3);
+    for (int j = lo + tid; j < a0; j += nthreads) fn(j, order_key(x[j]));
+    const float4* x4 = reinterpret_cast<const float4*>(x);
+    const int v0 = a0 >> 2, v1 = a1 >> 2;
+    int v = v0 + tid;
+    for (; v + 3 * nthreads < v1; v += 4 * nthreads) {
+        const float4 f0 = x4[v], f1 = x4[v + nthreads], f2 = x4[v + 2 * nthreads], f3 = x4[v + 3 * nthreads];
+        const float4 ff[4] = {f0, f1, f2, f3};
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            const int j = (v + u * nthreads) << 2;
+            fn(j, order_key(ff[u].x)); fn(j + 1, order_key(ff[u].y)); fn(j + 2, order_key(ff[u].z)); fn(j + 3, order_key(ff[u].w));
+        }
+    }
+    for (; v < v1; v += nthreads) {
+        const float4 f = x4[v];
+        const int j = v << 2;
+        fn(j, order_key(f.x)); fn(j + 1, order_key(f.y)); fn(j + 2, order_key(f.z)); fn(j + 3, order_key(f.w));
+    }
+    for (int j = a1 + tid; j < hi; j += nthreads) fn(j, order_key(x[j]));
+}
+
+// One CTA of 1024 threads per row, so at most two rows per SM are in flight: a row of 65536
+// logits is 256 KB, the rows in flight (76 MB on 148 SMs) fit the L2 and only the first of the
+// passes over a row reaches DRAM.
+__global__ void __launch_bounds__(TK_THREADS, 1)
 topk_kernel(const float* __restrict__ logits, const int32_t* __restrict__ ks,
             const int32_t* __restrict__ ke, int32_t* __restrict__ out, int num_cols,
             int64_t logits_stride, int k) {
     __shared__ int hist[256];
     __shared__ int sel_bin, sel_need;
-    __shared__ int warp_gt[TK_THREADS / 32], warp_eq[TK_THREADS / 32];
-    __shared__ int base_gt, base_eq;
+    __shared__ int seg_gt[TK_WARPS], seg_eq[TK_WARPS];
 
     const int row = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const float* x = logits + (size_t)row * logits_stride;
@@ -75,8 +105,10 @@ topk_kernel(const float* __restrict__ logits, const int32_t* __restrict__ ks,
     if (hi < lo) hi = lo;
     int32_t* o = out + (size_t)row * k;
     const uint32_t NEG_INF_KEY = order_key(-INFINITY);
+    const bool vec_ok = ((reinterpret_cast<size_t>(x) & 15) == 0);
+    // (rows that are not 16-byte aligned are read with scalar loads only)
 
-    // Pass 0..3: find the key of the k-th largest candidate (candidates: finite-or-+inf, > -inf).
+    // Pass 0..3: find the key of the k-th largest candidate (candidates: keys above -inf).
     uint32_t prefix = 0, prefix_mask = 0;
     int need = k;           // how many still to take among keys matching the prefix
     bool take_all = false;
@@ -84,10 +116,11 @@ topk_kernel(const float* __restrict__ logits, const int32_t* __restrict__ ks,
         const int shift = 24 - 8 * pass;
         for (int b = tid; b < 256; b += TK_THREADS) hist[b] = 0;
         __syncthreads();
-        for (int j = lo + tid; j < hi; j += TK_THREADS) {
-            const uint32_t key = order_key(x[j]);
+        auto count = [&](int, uint32_t key) {
             if (key > NEG_INF_KEY && (key & prefix_mask) == prefix) atomicAdd(&hist[(key >> shift) & 255], 1);
-        }
+        };
+        if (vec_ok) for_each_key(x, lo, hi, tid, TK_THREADS, count);
+        else for (int j = lo + tid; j < hi; j += TK_THREADS) count(j, order_key(x[j]));
         __syncthreads();
         if (tid == 0) {
             int cum = 0, b = 255;
@@ -108,46 +141,43 @@ topk_kernel(const float* __restrict__ logits, const int32_t* __restrict__ ks,
     const uint32_t thr = take_all ? NEG_INF_KEY : prefix;   // take keys > thr, plus `need` keys == thr
     const int need_eq = take_all ? 0 : need;
 
-    // Ordered compaction: output positions follow the column order, ties go to lower columns.
-    if (tid == 0) { base_gt = 0; base_eq = 0; }
+    // Ordered compaction: every warp owns a contiguous run of columns, counts its keys above and
+    // at the threshold, and after a scan over the warps writes them in column order: positions
+    // [0, n_gt) hold the greater ones, [n_gt, n_gt + need_eq) the first need_eq ties.
+    const int span = hi - lo;
+    const int seg = ((span + TK_WARPS - 1) / TK_WARPS + 31) & ~31;
+    const int s0 = min(lo + warp * seg, hi), s1 = min(s0 + seg, hi);
+    int c_gt = 0, c_eq = 0;
+    for (int j = s0 + lane; j < s1; j += 32) {
+        const uint32_t key = order_key(x[j]);
+        c_gt += (key > thr);
+        c_eq += (!take_all && key == thr);
+    }
+    c_gt = __reduce_add_sync(0xffffffffu, c_gt);
+    c_eq = __reduce_add_sync(0xffffffffu, c_eq);
+    if (lane == 0) { seg_gt[warp] = c_gt; seg_eq[warp] = c_eq; }
     __syncthreads();
-    // First count how many are strictly greater, so that the ties can be placed after them
-    // without a second scan: positions [0, n_gt) hold the greater ones, [n_gt, n_gt+need_eq) the ties.
-    if (tid == 0) hist[0] = 0;
-    __syncthreads();
-    int n_gt_local = 0;
-    for (int j = lo + tid; j < hi; j += TK_THREADS) n_gt_local += (order_key(x[j]) > thr);
-    n_gt_local = __reduce_add_sync(0xffffffffu, n_gt_local);
-    if (lane == 0) atomicAdd(&hist[0], n_gt_local);
-    __syncthreads();
-    const int n_gt = hist[0];
-
-    for (int j0 = lo; j0 < hi; j0 += TK_THREADS) {
-        const int j = j0 + tid;
+    int off_gt = 0, off_eq = 0, n_gt = 0, n_eq = 0;
+    for (int w = 0; w < TK_WARPS; ++w) {
+        if (w < warp) { off_gt += seg_gt[w]; off_eq += seg_eq[w]; }
+        n_gt += seg_gt[w]; n_eq += seg_eq[w];
+    }
+    const uint32_t below = (1u << lane) - 1u;
+    for (int j0 = s0; j0 < s1; j0 += 32) {
+        const int j = j0 + lane;
         uint32_t key = NEG_INF_KEY;
-        if (j < hi) key = order_key(x[j]);
+        if (j < s1) key = order_key(x[j]);
         const bool gt = key > thr;
-        const bool eq = (!take_all) && key == thr;
+        const bool eq = (!take_all) && key == thr && j < s1;
         const uint32_t mg = __ballot_sync(0xffffffffu, gt), me = __ballot_sync(0xffffffffu, eq);
-        if (lane == 0) { warp_gt[warp] = __popc(mg); warp_eq[warp] = __popc(me); }
-        __syncthreads();
-        int off_gt = base_gt, off_eq = base_eq;
-        for (int w = 0; w < warp; ++w) { off_gt += warp_gt[w]; off_eq += warp_eq[w]; }
-        const uint32_t below = (1u << lane) - 1u;
         if (gt) o[off_gt + __popc(mg & below)] = j;
         if (eq) {
             const int r = off_eq + __popc(me & below);
             if (r < need_eq) o[n_gt + r] = j;
         }
-        __syncthreads();
-        if (tid == 0) {
-            int tg = 0, te = 0;
-            for (int w = 0; w < TK_THREADS / 32; ++w) { tg += warp_gt[w]; te += warp_eq[w]; }
-            base_gt += tg; base_eq += te;
-        }
-        __syncthreads();
+        off_gt += __popc(mg); off_eq += __popc(me);
     }
-    const int filled = n_gt + (take_all ? 0 : min(need_eq, base_eq));
+    const int filled = n_gt + (take_all ? 0 : min(need_eq, n_eq));
     for (int r = filled + tid; r < k; r += TK_THREADS) o[r] = -1;
 }
 

@@ -10,11 +10,15 @@
 // the MMAs of the next key tile run under the epilogue of the current one.
 //
 // One CTA walks query groups (4 queries) round-robin and, per group, the key tiles up to the
-// largest ke of the group.  Warps: 0-7 epilogue (warp w: TMEM lane quarter w % 4, queries
-// 2 * (w / 4) and +1 of the group), 8 loader (16-byte cp.async into 128B-swizzled K-major tiles;
-// q group and key tiles are contiguous in global memory), 9 MMA issue (one thread).
+// largest ke of the group.  Warps: 0-15 epilogue (warp w: TMEM lane quarter w % 4, query w / 4
+// of the group; the epilogue is bound by instruction issue, so it gets four warps per scheduler),
+// 16 loader (one TMA tile load per key tile and per q group: both are contiguous rows of 128
+// bytes in global memory and land 128B-swizzled, K-major; rows past the end arrive as zeros),
+// 17 MMA issue (one thread).
 // The kernel is tensor-bound at the benchmark shape (4.26 TFLOP) with the logits write
 // (1.07 GB) as the second term.  Every wait is bounded.
+#include <cuda.h>
+
 #include "common.cuh"
 #include "sm100_ptx.cuh"
 
@@ -27,9 +31,9 @@ using namespace ptx;
 constexpr int LX_D = 128;            // head dim of the indexer (bytes per row)
 constexpr int LX_KT = 128;           // keys per tile
 constexpr int LX_QG = 4;             // queries per group
-constexpr int LX_EPI_WARPS = 8;
-constexpr int LX_LOAD_WARP = 8, LX_MMA_WARP = 9;
-constexpr int LX_THREADS = 10 * 32;
+constexpr int LX_EPI_WARPS = 16;
+constexpr int LX_LOAD_WARP = 16, LX_MMA_WARP = 17;
+constexpr int LX_THREADS = 18 * 32;
 constexpr int LX_KSTAGE = 4;
 
 constexpr uint32_t LX_Q_OFF = 0;                              // q group: [<=256 rows x 128 B] K-major 128B swizzle
@@ -51,7 +55,8 @@ struct LogitsParams {
     int s_q, heads, s_k; int64_t stride;
 };
 
-__global__ void __launch_bounds__(LX_THREADS, 1) mqa_logits_tc_kernel(const LogitsParams p) {
+__global__ void __launch_bounds__(LX_THREADS, 1) mqa_logits_tc_kernel(const LogitsParams p, const __grid_constant__ CUtensorMap qmap,
+                                                                      const __grid_constant__ CUtensorMap kmap) {
     extern __shared__ uint8_t smem_raw[];
     const uint32_t raw = smem_u32(smem_raw);
     const uint32_t base = (raw + 1023u) & ~1023u;
@@ -63,7 +68,7 @@ __global__ void __launch_bounds__(LX_THREADS, 1) mqa_logits_tc_kernel(const Logi
     const int H = p.heads, N = LX_QG * H;
 
     if (tid == 0) {
-        for (int s = 0; s < LX_KSTAGE; ++s) { mbar_init(bar(LXB_KFULL + s), 32); mbar_init(bar(LXB_KEMPTY + s), 1); }
+        for (int s = 0; s < LX_KSTAGE; ++s) { mbar_init(bar(LXB_KFULL + s), 1); mbar_init(bar(LXB_KEMPTY + s), 1); }
         for (int b = 0; b < 2; ++b) { mbar_init(bar(LXB_DFULL + b), 1); mbar_init(bar(LXB_DEMPTY + b), LX_EPI_WARPS * 32); }
         mbar_init(bar(LXB_QFULL), 32);
         mbar_init(bar(LXB_QEMPTY), 1);
@@ -98,14 +103,11 @@ __global__ void __launch_bounds__(LX_THREADS, 1) mqa_logits_tc_kernel(const Logi
             int t0, t1;
             group_range(g, t0, t1);
             const float* wsm = reinterpret_cast<const float*>(sm + LX_W_OFF + (qn & 3u) * LX_W_BYTES);
-            const int q0 = g * LX_QG + 2 * qp, q1 = q0 + 1;
+            const int q0 = g * LX_QG + qp;
             const int ks0 = q0 < p.s_q ? p.ks[q0] : 0, ke0 = q0 < p.s_q ? p.ke[q0] : 0;
-            const int ks1 = q1 < p.s_q ? p.ks[q1] : 0, ke1 = q1 < p.s_q ? p.ke[q1] : 0;
             // columns outside every tile of the group are -inf: written here, 128 keys per pass
-            for (int qq = 0; qq < 2; ++qq) {
-                const int qi = q0 + qq;
-                if (qi >= p.s_q) continue;
-                float* row = p.logits + (size_t)qi * p.stride;
+            if (q0 < p.s_q) {
+                float* row = p.logits + (size_t)q0 * p.stride;
                 for (int j = quarter * 32 + lane; j < p.s_k; j += 128)
                     if (j < t0 * LX_KT || j >= t1 * LX_KT) row[j] = -INFINITY;
             }
@@ -116,37 +118,40 @@ __global__ void __launch_bounds__(LX_THREADS, 1) mqa_logits_tc_kernel(const Logi
             }
             for (int t = t0; t < t1 && ok; ++t, ++it) {
                 const uint32_t b = it & 1u;
-                ok = mbar_wait(bar(LXB_DFULL + b), (it >> 1) & 1u, abort_flag, 12);
+                ok = mbar_wait_hot(bar(LXB_DFULL + b), (it >> 1) & 1u, abort_flag, 12);
                 if (!ok) break;
                 tc_fence_after();
                 const int key = t * LX_KT + quarter * 32 + lane;
                 const float sc = key < p.s_k ? __ldg(p.k_scale + key) : 0.f;
-                float acc[2] = {0.f, 0.f};
+                // Chunks of 32 score columns of this warp's query (heads [0,32), [32,64)); the
+                // tensor-memory load of the next chunk is in flight while the current one is reduced,
+                // and four partial sums per chunk keep the FMA chains short.
+                float acc = 0.f;
+                const int nch = H >> 5;                          // 1 or 2 chunks
+                const uint32_t col0 = lane_addr + 256 * b + qp * H;
+                const float* wq = wsm + qp * 64;
+                uint32_t d0[32], d1[32];
+                tmem_ld32(col0, d0);
+                auto reduce = [&](const uint32_t (&d)[32], int c) {
+                    float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
 #pragma unroll
-                for (int qq = 0; qq < 2; ++qq) {
-                    const float* wq = wsm + (2 * qp + qq) * 64;
-                    for (int c = 0; c < H; c += 32) {
-                        uint32_t d[32];
-                        tmem_ld32(lane_addr + 256 * b + (2 * qp + qq) * H + c, d);
-                        tmem_wait_ld();
-                        float a0 = 0.f, a1 = 0.f;
-#pragma unroll
-                        for (int i = 0; i < 32; i += 4) {
-                            const float4 w4 = *reinterpret_cast<const float4*>(wq + c + i);
-                            a0 = fmaf(fmaxf(__uint_as_float(d[i + 0]), 0.f), w4.x, a0);
-                            a1 = fmaf(fmaxf(__uint_as_float(d[i + 1]), 0.f), w4.y, a1);
-                            a0 = fmaf(fmaxf(__uint_as_float(d[i + 2]), 0.f), w4.z, a0);
-                            a1 = fmaf(fmaxf(__uint_as_float(d[i + 3]), 0.f), w4.w, a1);
-                        }
-                        acc[qq] += a0 + a1;
+                    for (int i = 0; i < 32; i += 4) {
+                        const float4 w4 = *reinterpret_cast<const float4*>(wq + c + i);
+                        a0 = fmaf(fmaxf(__uint_as_float(d[i + 0]), 0.f), w4.x, a0);
+                        a1 = fmaf(fmaxf(__uint_as_float(d[i + 1]), 0.f), w4.y, a1);
+                        a2 = fmaf(fmaxf(__uint_as_float(d[i + 2]), 0.f), w4.z, a2);
+                        a3 = fmaf(fmaxf(__uint_as_float(d[i + 3]), 0.f), w4.w, a3);
                     }
-                }
+                    acc += (a0 + a1) + (a2 + a3);
+                };
+                tmem_wait_ld();
+                if (nch > 1) tmem_ld32(col0 + 32, d1);
+                reduce(d0, 0);
+                if (nch > 1) { tmem_wait_ld(); reduce(d1, 32); }
                 tc_fence_before();
                 mbar_arrive(bar(LXB_DEMPTY + b));
-                if (key < p.s_k) {
-                    if (q0 < p.s_q) p.logits[(size_t)q0 * p.stride + key] = (key >= ks0 && key < ke0) ? acc[0] * sc : -INFINITY;
-                    if (q1 < p.s_q) p.logits[(size_t)q1 * p.stride + key] = (key >= ks1 && key < ke1) ? acc[1] * sc : -INFINITY;
-                }
+                if (key < p.s_k && q0 < p.s_q)
+                    p.logits[(size_t)q0 * p.stride + key] = (key >= ks0 && key < ke0) ? acc * sc : -INFINITY;
             }
         }
     } else if (warp == LX_LOAD_WARP) {
@@ -161,53 +166,30 @@ __global__ void __launch_bounds__(LX_THREADS, 1) mqa_logits_tc_kernel(const Logi
                 ok = mbar_wait(bar(LXB_QEMPTY), (qn - 1) & 1u, abort_flag, 13);
                 if (!ok) break;
             }
-            // q group: N rows of 128 B, contiguous in global memory; rows past s_q are zero-filled
-            const int rows_valid = min(LX_QG, p.s_q - g * LX_QG) * H;
-            const uint8_t* qsrc = p.q + (size_t)g * LX_QG * H * LX_D;
-            for (int c = lane; c < N * 8; c += 32) {
-                const int r = c >> 3, ch = c & 7;
-                const bool v = r < rows_valid;
-                cp_async16_zfill(base + LX_Q_OFF + r * 128 + (((uint32_t)ch ^ ((uint32_t)r & 7u)) << 4),
-                                 v ? qsrc + (size_t)r * LX_D + ch * 16 : p.q, v ? 16u : 0u);
-            }
+            // q group: N rows of 128 B, one tile load (rows past s_q * H arrive as zeros); the head
+            // weights go to shared memory with plain stores, every lane arrives once
             for (int c = lane; c < LX_QG * 64; c += 32) {
                 const int qi = g * LX_QG + (c >> 6), h = c & 63;
                 reinterpret_cast<float*>(sm + LX_W_OFF + (qn & 3u) * LX_W_BYTES)[c] = (qi < p.s_q && h < H) ? p.w[(size_t)qi * H + h] : 0.f;
             }
-            cp_async_wait_all();
-            fence_proxy_async();
-            mbar_arrive(bar(LXB_QFULL));
+            if (lane == 0) {
+                mbar_arrive_expect_tx(bar(LXB_QFULL), (uint32_t)N * LX_D);
+                tma_load_2d(base + LX_Q_OFF, &qmap, 0, g * LX_QG * H, bar(LXB_QFULL));
+            } else {
+                mbar_arrive(bar(LXB_QFULL));
+            }
             ++qn;
             for (int t = t0; t < t1 && ok; ++t, ++it) {
                 const uint32_t st = it % LX_KSTAGE;
                 if (it >= LX_KSTAGE) {
-                    ok = mbar_wait(bar(LXB_KEMPTY + st), ((it / LX_KSTAGE) - 1) & 1u, abort_flag, 14);
+                    ok = mbar_wait_hot(bar(LXB_KEMPTY + st), ((it / LX_KSTAGE) - 1) & 1u, abort_flag, 14);
                     if (!ok) break;
                 }
-                const int key0 = t * LX_KT;
-                const int valid = min(LX_KT, p.s_k - key0);
-                const uint8_t* ksrc = p.k + (size_t)key0 * LX_D;
-                const uint32_t dst = base + LX_K_OFF + st * (LX_KT * 128);
-#pragma unroll 4
-                for (int c = lane; c < LX_KT * 8; c += 32) {
-                    const int r = c >> 3, ch = c & 7;
-                    const bool v = r < valid;
-                    cp_async16_zfill(dst + r * 128 + (((uint32_t)ch ^ ((uint32_t)r & 7u)) << 4),
-                                     v ? ksrc + (size_t)r * LX_D + ch * 16 : p.k, v ? 16u : 0u);
-                }
-                cp_async_commit();
-                // complete the tile issued two iterations ago (keeps two tiles in flight)
-                if (t - t0 >= 2) {
-                    cp_async_wait<2>();
-                    fence_proxy_async();
-                    mbar_arrive(bar(LXB_KFULL + (it - 2) % LX_KSTAGE));
+                if (lane == 0) {
+                    mbar_arrive_expect_tx(bar(LXB_KFULL + st), LX_KT * LX_D);
+                    tma_load_2d(base + LX_K_OFF + st * (LX_KT * 128), &kmap, 0, t * LX_KT, bar(LXB_KFULL + st));
                 }
             }
-            // drain: the last (up to two) tiles of the group
-            cp_async_wait_all();
-            fence_proxy_async();
-            const int n = t1 - t0;
-            for (int d = min(n, 2); d >= 1 && ok; --d) mbar_arrive(bar(LXB_KFULL + (it - d) % LX_KSTAGE));
         }
     } else if (warp == LX_MMA_WARP && lane == 0) {
         // =================================================================== MMA issue (one thread)
@@ -272,10 +254,37 @@ int launch_mqa_logits_tc(const uint8_t* q, const uint8_t* k, const float* k_scal
         cudaDeviceGetAttribute(&sms[dev], cudaDevAttrMultiProcessorCount, dev);
         attr_set[dev] = true;
     }
+    // tensor maps of q ([s_q * heads rows] x 128 B, box of one query group) and k ([s_k rows] x 128 B, box of one key tile)
+    typedef CUresult (*EncodeFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                 const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                 CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+    static EncodeFn encode = nullptr;
+    if (encode == nullptr) {
+        cudaDriverEntryPointQueryResult qres;
+        void* fn = nullptr;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres) != cudaSuccess || fn == nullptr)
+            return set_error(SMLA_E_DEVICE, "mqa_logits_tc_kernel: the driver has no cuTensorMapEncodeTiled");
+        encode = (EncodeFn)fn;
+    }
+    CUtensorMap qmap, kmap;
+    {
+        const cuuint64_t qdims[2] = {(cuuint64_t)LX_D, (cuuint64_t)s_q * num_heads}, kdims[2] = {(cuuint64_t)LX_D, (cuuint64_t)s_k};
+        const cuuint64_t strides[1] = {(cuuint64_t)LX_D};
+        const cuuint32_t qbox[2] = {(cuuint32_t)LX_D, (cuuint32_t)(LX_QG * num_heads)}, kbox[2] = {(cuuint32_t)LX_D, (cuuint32_t)LX_KT};
+        const cuuint32_t estr[2] = {1, 1};
+        const CUresult r1 = encode(&qmap, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<uint8_t*>(q), qdims, strides, qbox, estr,
+                                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE,
+                                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        const CUresult r2 = encode(&kmap, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<uint8_t*>(k), kdims, strides, kbox, estr,
+                                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE,
+                                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        if (r1 != CUDA_SUCCESS || r2 != CUDA_SUCCESS)
+            return set_error(SMLA_E_DEVICE, "mqa_logits_tc_kernel: cuTensorMapEncodeTiled failed (%d, %d)", (int)r1, (int)r2);
+    }
     LogitsParams p{q, k, k_scale, weights, ks, ke, logits, status, s_q, num_heads, s_k, logits_stride};
     const int groups = (s_q + LX_QG - 1) / LX_QG;
     const int grid = groups < sms[dev < 64 ? dev : 0] ? groups : sms[dev < 64 ? dev : 0];
-    mqa_logits_tc_kernel<<<grid, LX_THREADS, LX_SMEM, stream>>>(p);
+    mqa_logits_tc_kernel<<<grid, LX_THREADS, LX_SMEM, stream>>>(p, qmap, kmap);
     return check_launch("mqa_logits_tc_kernel");
 }
 
