@@ -727,6 +727,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) attn_tc_kernel(const AttnParams
 
 static Trace g_trace = {nullptr, 0};
 void set_attn_trace(long long* buf, int cap) { g_trace.buf = buf; g_trace.cap = cap; }
+void get_attn_trace(long long** buf, int* cap) { *buf = g_trace.buf; *cap = g_trace.cap; }
 
 int launch_attn_tc(const AttnParams& p, cudaStream_t stream) {
     if (p.num_tokens == 0) return 0;

@@ -82,6 +82,71 @@ __device__ __forceinline__ bool mbar_wait_hot(uint32_t bar, uint32_t parity, vol
     return __all_sync(0xffffffffu, ok != 0);
 }
 
+// ------------------------------------------------------------------ thread-block cluster
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+// Address of the same shared-memory location in CTA `rank` of the cluster (shared::cluster window).
+__device__ __forceinline__ uint32_t mapa_shared(uint32_t addr, uint32_t rank) {
+    uint32_t r;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(addr), "r"(rank));
+    return r;
+}
+// Cluster-wide barrier; executed by every thread of every CTA of the cluster.
+__device__ __forceinline__ void cluster_sync_all() {
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void st_cluster_v4(uint32_t addr, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
+    asm volatile("st.shared::cluster.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
+}
+__device__ __forceinline__ void st_cluster_f32(uint32_t addr, float v) {
+    asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(addr), "f"(v) : "memory");
+}
+// Arrive on a barrier of another CTA of the cluster; releases this thread's earlier writes to it.
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t remote_bar) {
+    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(remote_bar) : "memory");
+}
+// Arrive on a barrier of another CTA and add `bytes` to its pending transaction count.
+__device__ __forceinline__ void mbar_arrive_expect_tx_cluster(uint32_t remote_bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.release.cluster.shared::cluster.b64 _, [%0], %1;" ::"r"(remote_bar), "r"(bytes) : "memory");
+}
+// Bulk copy from this CTA's shared memory into another CTA's (both 16-byte aligned, size a
+// multiple of 16); the destination CTA's barrier receives the byte count when the data has landed.
+__device__ __forceinline__ void bulk_copy_to_cluster(uint32_t remote_dst, uint32_t local_src, uint32_t bytes, uint32_t remote_bar) {
+    asm volatile("cp.async.bulk.shared::cluster.shared::cta.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                 ::"r"(remote_dst), "r"(local_src), "r"(bytes), "r"(remote_bar) : "memory");
+}
+// One poll with cluster-scope acquire: for barriers that another CTA arrives on after writing here.
+__device__ __forceinline__ bool mbar_try_wait_cluster(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+    return ok != 0;
+}
+// mbar_wait_hot with cluster-scope acquire.
+__device__ __forceinline__ bool mbar_wait_hot_cluster(uint32_t bar, uint32_t parity, volatile int* abort, int code) {
+    uint32_t ok = 0;
+    for (uint32_t i = 0; i < WAIT_POLLS; ++i) {
+        if (mbar_try_wait_cluster(bar, parity)) { ok = 1; break; }
+        if ((i & 255u) == 255u && *abort != 0) break;
+    }
+    if (!ok) atomicCAS(const_cast<int*>(abort), 0, code);
+    return __all_sync(0xffffffffu, ok != 0);
+}
+__device__ __forceinline__ bool mbar_wait_thread_cluster(uint32_t bar, uint32_t parity, volatile int* abort, int code) {
+    for (uint32_t i = 0; i < WAIT_POLLS; ++i) {
+        if (mbar_try_wait_cluster(bar, parity)) return true;
+        if ((i & 255u) == 255u && *abort != 0) return false;
+    }
+    atomicCAS(const_cast<int*>(abort), 0, code);
+    return false;
+}
+
 // Single-thread variant of mbar_wait (same bounds and give-up protocol), for a role that is run
 // by one lane only.
 __device__ __forceinline__ bool mbar_wait_thread(uint32_t bar, uint32_t parity, volatile int* abort, int code) {

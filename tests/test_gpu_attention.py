@@ -1,7 +1,8 @@
 """Parity of the CUDA attention kernels (through the C-ABI) with the CPU oracle.
 
 Each case builds seeded inputs on the CPU, runs the oracle there and the kernels on cuda:0.
-``impl`` 1 is the exact fp32 kernel, 2 the tcgen05 kernel (FP8 class; tolerances in helpers.py).
+``impl`` 1 is the exact fp32 kernel, 2 the tcgen05 kernel (FP8 class; tolerances in helpers.py),
+3 the tcgen05 kernel that shares the score work inside a two-CTA cluster (same class).
 """
 import numpy as np
 import pytest
@@ -12,7 +13,7 @@ from helpers import bf16_from_bits, make_case, oracle_attn, orc
 
 pytestmark = pytest.mark.gpu
 
-SCALAR, TC = 1, 2
+SCALAR, TC, TC_PAIR = 1, 2, 3
 
 
 def _tols(impl, prefill=False):
@@ -58,7 +59,7 @@ def _check(out, lse2, ref_out, ref_lse, impl, prefill=False, noise=1.0):
 
 
 # ------------------------------------------------------------------ golden fixtures
-@pytest.mark.parametrize("impl", [SCALAR, TC])
+@pytest.mark.parametrize("impl", [SCALAR, TC, TC_PAIR])
 @pytest.mark.parametrize("name", ["attn_h16", "attn_h128", "attn_h64_lonely"])
 def test_golden_fixtures(golden_dir, name, impl):
     g = np.load(f"{golden_dir}/{name}.npz")
@@ -79,7 +80,7 @@ def test_golden_fixtures(golden_dir, name, impl):
 
 
 # ------------------------------------------------------------------ reference test grid (tests/test_decode.py:223-234)
-@pytest.mark.parametrize("impl", [SCALAR, TC])
+@pytest.mark.parametrize("impl", [SCALAR, TC, TC_PAIR])
 @pytest.mark.parametrize("num_heads,batch", [(128, 1), (128, 4), (16, 1), (16, 4), (64, 1), (64, 4), (8, 1), (8, 4)])
 def test_decode_reference_grid(num_heads, batch, impl):
     """topk 2048, data randn/10 clamped, last 10 indices -1, bound max|dO| < 1e-3 as the reference."""
@@ -92,7 +93,7 @@ def test_decode_reference_grid(num_heads, batch, impl):
     _check(out, lse, ref_out, ref_lse, impl)
 
 
-@pytest.mark.parametrize("impl", [SCALAR, TC])
+@pytest.mark.parametrize("impl", [SCALAR, TC, TC_PAIR])
 def test_decode_v32_shape_values(impl):
     """Benchmark-like value distribution (kv randn, q randn*0.5), mixed per-tile scales."""
     case = make_case(7, 6, 128, 2048, 96, kv_std=1.0, q_std=0.5, invalid_tail=0.1)
@@ -102,7 +103,7 @@ def test_decode_v32_shape_values(impl):
         _check(out, lse, ref_out, ref_lse, impl)
 
 
-@pytest.mark.parametrize("impl", [SCALAR, TC])
+@pytest.mark.parametrize("impl", [SCALAR, TC, TC_PAIR])
 def test_scale_spread_rows(impl):
     """Rows whose four tiles carry very different scales exercise the re-expression against the
     largest scale."""
@@ -117,7 +118,7 @@ def test_scale_spread_rows(impl):
     _check(out, lse, ref_out, ref_lse, impl, noise=1.5)   # values span 2^9 between tiles: single outliers at 1.2x the bound
 
 
-@pytest.mark.parametrize("impl", [SCALAR, TC])
+@pytest.mark.parametrize("impl", [SCALAR, TC, TC_PAIR])
 def test_peaked_attention_and_rescale(impl):
     """Logits that keep growing along the index list force accumulator rescales; a few dominant
     keys make the distribution peaked.  With logits of +-6 the e4m3 rounding of Q alone moves
@@ -133,7 +134,7 @@ def test_peaked_attention_and_rescale(impl):
     _check(out, lse, ref_out, ref_lse, impl, noise=2.0)
 
 
-@pytest.mark.parametrize("impl", [SCALAR, TC])
+@pytest.mark.parametrize("impl", [SCALAR, TC, TC_PAIR])
 def test_topk_length_and_ragged(impl):
     case = make_case(9, 5, 32, 512, 16, invalid_tail=0.0)
     tl = torch.tensor([512, 100, 0, 64, 333], dtype=torch.int32)
@@ -146,7 +147,7 @@ def test_topk_length_and_ragged(impl):
     assert not out[2].any()
 
 
-@pytest.mark.parametrize("impl", [SCALAR, TC])
+@pytest.mark.parametrize("impl", [SCALAR, TC, TC_PAIR])
 def test_minus_one_handling_is_exact(impl):
     """Moving the -1 entries around, or poisoning the row that -1 would be clamped to with NaN,
     must not change a single bit (tests/test_nan_safe.py:13-32 poisons slot 0 the same way)."""
@@ -175,7 +176,7 @@ def test_minus_one_handling_is_exact(impl):
     _check(out2, lse2, o_ref, l_ref, impl)
 
 
-@pytest.mark.parametrize("impl", [SCALAR, TC])
+@pytest.mark.parametrize("impl", [SCALAR, TC, TC_PAIR])
 def test_attn_sink(impl):
     case = make_case(21, 4, 64, 512, 16, invalid_tail=0.1)
     case["indices"][3] = -1
@@ -192,7 +193,7 @@ def test_attn_sink(impl):
         assert torch.all(k[~fin] < -1e20)
 
 
-@pytest.mark.parametrize("impl", [SCALAR, TC])
+@pytest.mark.parametrize("impl", [SCALAR, TC, TC_PAIR])
 @pytest.mark.parametrize("num_heads,num_tokens", [(128, 65), (64, 65), (16, 100)])
 def test_prefill_reference_grid(num_heads, num_tokens, impl):
     """tests/test_prefill.py:56-71: topk 2048, randn/10 data, bound 1e-3; plus max_logits."""
@@ -208,7 +209,7 @@ def test_prefill_reference_grid(num_heads, num_tokens, impl):
     t = 0
     valid = case["indices"][t] >= 0
     s = (case["q"][t].float() @ deq[case["indices"][t][valid].long()].T) * case["sm_scale"] * 1.4426950408889634
-    assert float((mx[t] - s.max(dim=1).values).abs().max()) < (2e-2 if impl == TC else 1e-4)
+    assert float((mx[t] - s.max(dim=1).values).abs().max()) < (2e-2 if impl != SCALAR else 1e-4)
 
 
 def test_out_argument_is_written_in_place():
