@@ -24,6 +24,8 @@
 // Numerics, tensor-memory map, the per-tile pipeline inside a CTA and the bounded-wait protocol
 // are those of attn_tc.cu (see its header).  Nothing here loads with cluster multicast; the only
 // cross-CTA traffic is plain st.shared::cluster stores and mbarrier arrives.
+#include <cstdlib>
+
 #include "common.cuh"
 #include "sm100_ptx.cuh"
 
@@ -36,7 +38,7 @@ using namespace ptx;
 constexpr int N_SM_WARPS = 8, N_PR_WARPS = 4, N_FX_WARPS = 8;
 constexpr int FX_ROWS = 8;
 constexpr int FX_WARP0 = N_SM_WARPS + N_PR_WARPS;
-constexpr int MMA_WARP = FX_WARP0 + N_FX_WARPS;       // score MMAs; +1: P.V MMAs; +2: credit relay; +3: receipt relay
+constexpr int MMA_WARP = FX_WARP0 + N_FX_WARPS;       // score MMAs; +1: P.V MMAs (and slot credits); +2: P' sender; +3: receipt relay
 constexpr int TC_THREADS = (MMA_WARP + 4) * 32;
 constexpr int REGS_LAUNCH = 80, REGS_SOFTMAX = 128, REGS_OTHER = 48;
 static_assert(N_SM_WARPS * 32 * REGS_SOFTMAX + (N_PR_WARPS + N_FX_WARPS) * 32 * REGS_OTHER + 128 * REGS_LAUNCH
@@ -70,7 +72,7 @@ constexpr uint32_t BAR_OFF = EPI_OFF + 2 * 3 * 128 * 4;
 constexpr int BAR_FULL = 0, BAR_EMPTY = NS, BAR_LOADED = 2 * NS, BAR_HLOADED = 3 * NS, BAR_HFULL = 4 * NS, BAR_HEMPTY = 5 * NS,
               BAR_SREADY = 6 * NS, BAR_PREADY = BAR_SREADY + 2, BAR_PVOWN = BAR_PREADY + 2, BAR_QREADY = BAR_PVOWN + 2,
               BAR_PFULL = BAR_QREADY + 1, BAR_PFREE = BAR_PFULL + NP, BAR_PDONE = BAR_PFREE + NP, BAR_ADOPTED = BAR_PDONE + NP,
-              BAR_DONE = BAR_ADOPTED + NP, BAR_EPI = BAR_DONE + NDONE, NBAR = BAR_EPI + 2;
+              BAR_DONE = BAR_ADOPTED + NP, BAR_EPI = BAR_DONE + NDONE, BAR_STAGED = BAR_EPI + 2, NBAR = BAR_STAGED + NS;
 constexpr uint32_t MISC_OFF = BAR_OFF + NBAR * 8;
 constexpr uint32_t SMEM_BYTES = MISC_OFF + 16;
 constexpr uint32_t SMEM_ALLOC = SMEM_BYTES + 1024;
@@ -99,12 +101,13 @@ struct Work {
 struct Trace {
     long long* buf;
     int cap;
+    int block;    // the CTA that records
 };
 struct TraceCursor {
     int n = 0;
 };
 __device__ __forceinline__ void trace(const Trace& t, TraceCursor& c, int tag, int tile) {
-    if (t.buf != nullptr && blockIdx.x == 0 && (threadIdx.x & 31) == 0 && c.n < t.cap) {
+    if (t.buf != nullptr && blockIdx.x == t.block && (threadIdx.x & 31) == 0 && c.n < t.cap) {
         long long* slot = t.buf + ((size_t)(threadIdx.x >> 5) * t.cap + c.n) * 2;
         slot[0] = ((long long)tag << 32) | (unsigned)tile;
         slot[1] = clock64();
@@ -173,6 +176,55 @@ __device__ __forceinline__ uint32_t mul_bf16x2(uint32_t w, __nv_bfloat162 f) {
 __device__ __forceinline__ float bf16lo(uint32_t w) { return __uint_as_float(w << 16); }
 __device__ __forceinline__ float bf16hi(uint32_t w) { return __uint_as_float(w & 0xffff0000u); }
 
+// Order in which a CTA consumes the n tiles of a request that starts at running tile t0: its own
+// tiles in order, and each tile of the other CTA three tiles after the own tile that precedes it
+// (so that the other CTA's P' has normally arrived, and neither softmax waits for the other).
+// Gathers, fix-up, softmax and P.V issue all walk this order; fo(t) / fp(t) return false to stop.
+template <typename FO, typename FP>
+__device__ __forceinline__ bool run_sequence(uint32_t t0, uint32_t n, uint32_t rank, FO fo, FP fp) {
+    const uint32_t first_own = ((t0 & 1u) == rank) ? 0u : 1u, first_oth = 1u - first_own;
+    const uint32_t n_own = (n > first_own) ? (n - first_own + 1) / 2 : 0, n_oth = (n > first_oth) ? (n - first_oth + 1) / 2 : 0;
+    const uint32_t lead = (first_own == 0u) ? 2u : 1u;      // how many own tiles the own side runs ahead
+    uint32_t io = 0, ip = 0;
+#pragma unroll 1
+    while (io < n_own || ip < n_oth) {
+        if (io < n_own && (ip >= n_oth || io <= ip + lead)) { if (!fo(t0 + first_own + 2 * io)) return false; ++io; }
+        else { if (!fp(t0 + first_oth + 2 * ip)) return false; ++ip; }
+    }
+    return true;
+}
+
+// The same walk for callers that want to look one tile ahead: f(tile, is_own, next_tile), with
+// next_tile = 0xffffffff after the last one.  `first` receives the first tile of the order.
+template <typename F>
+__device__ __forceinline__ bool run_sequence_ahead(uint32_t t0, uint32_t n, uint32_t rank, F f) {
+    const uint32_t first_own = ((t0 & 1u) == rank) ? 0u : 1u, first_oth = 1u - first_own;
+    const uint32_t n_own = (n > first_own) ? (n - first_own + 1) / 2 : 0, n_oth = (n > first_oth) ? (n - first_oth + 1) / 2 : 0;
+    const uint32_t lead = (first_own == 0u) ? 2u : 1u;
+    uint32_t io = 0, ip = 0;
+    auto pick = [&](uint32_t a, uint32_t b, bool& own) -> uint32_t {
+        if (a >= n_own && b >= n_oth) { own = false; return 0xffffffffu; }
+        own = a < n_own && (b >= n_oth || a <= b + lead);
+        return own ? t0 + first_own + 2 * a : t0 + first_oth + 2 * b;
+    };
+    bool own;
+    uint32_t cur = pick(io, ip, own);
+#pragma unroll 1
+    while (cur != 0xffffffffu) {
+        if (own) ++io; else ++ip;
+        bool own_next;
+        const uint32_t nxt = pick(io, ip, own_next);
+        if (!f(cur, own, nxt)) return false;
+        cur = nxt; own = own_next;
+    }
+    return true;
+}
+__device__ __forceinline__ uint32_t first_in_sequence(uint32_t t0, uint32_t n, uint32_t rank) {
+    // an owned tile comes first whenever the request has one; otherwise its only tile is the other CTA's
+    const uint32_t first_own = ((t0 & 1u) == rank) ? 0u : 1u;
+    return (n > first_own) ? t0 + first_own : t0;
+}
+
 // ---------------------------------------------------------------------------------------------
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(TC_THREADS, 1) attn_tc2_kernel(const AttnParams p, const Trace tr) {
     extern __shared__ uint8_t smem_raw[];
@@ -200,6 +252,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(TC_THREADS, 1) attn_
             mbar_init(bar(BAR_HLOADED + s), N_PR_WARPS * 32);
             mbar_init(bar(BAR_HFULL + s), N_FX_WARPS * 32);
             mbar_init(bar(BAR_HEMPTY + s), 1);
+            mbar_init(bar(BAR_STAGED + s), N_SM_WARPS * 32);     // P' image of the owned tile in this stage is complete
         }
         for (int b = 0; b < 2; ++b) {
             mbar_init(bar(BAR_SREADY + b), 1);
@@ -208,7 +261,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(TC_THREADS, 1) attn_
             mbar_init(bar(BAR_EPI + b), N_SM_WARPS * 16);        // the hh = 0 threads of the other CTA
         }
         for (int s = 0; s < NP; ++s) {
-            mbar_init(bar(BAR_PFULL + s), 1);                    // armed and filled by the other CTA (bulk copies of P' and references)
+            mbar_init(bar(BAR_PFULL + s), 1);                    // armed by this CTA, filled by the other CTA's bulk copies of P' and references
             mbar_init(bar(BAR_PFREE + s), 1);                    // arrived by the other CTA's relay thread
             mbar_init(bar(BAR_PDONE + s), 1);
             mbar_init(bar(BAR_ADOPTED + s), N_SM_WARPS * 32);
@@ -217,6 +270,8 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(TC_THREADS, 1) attn_
         mbar_init(bar(BAR_QREADY), N_SM_WARPS * 32);
         *abort_flag = 0;
         mbar_init_fence();
+        // every use of a P' slot is armed here, by the receiver: the sender only copies
+        for (int s = 0; s < NP; ++s) mbar_arrive_expect_tx(bar(BAR_PFULL + s), PS_BYTES + 128 * 4);
     }
     if (warp == MMA_WARP) {
         tmem_alloc(base + MISC_OFF, TMEM_COLS);
@@ -348,7 +403,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(TC_THREADS, 1) attn_
 
             // ---- an owned tile: scores -> P', to this CTA's tensor memory and to the other CTA ----
             auto own_tile = [&](uint32_t t) -> bool {
-                const uint32_t r = t >> 1, b = r & 1u, st = r % NS, ps = r % NP;
+                const uint32_t r = t >> 1, b = r & 1u, st = r % NS;
                 trace(tr, tc, 5, t);
                 if (!mbar_wait_hot(bar(BAR_SREADY + b), (r >> 1) & 1u, abort_flag, W_SREADY)) return false;
                 if (!mbar_wait(bar(BAR_FULL + st), (r / NS) & 1u, abort_flag, W_FULL)) return false;
@@ -397,36 +452,22 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(TC_THREADS, 1) attn_
                     pw[u >> 2] = pack_e4m3x4(p0, p1, p2, p3);
                 }
                 l_run += l0 + l1;
-                // the other CTA's slot for this tile is free once its P.V of the tile NP ring positions back is done
-                trace(tr, tc, 110 + warp, t);
-                if (r >= (uint32_t)NP) {
-                    if (!mbar_wait_hot_cluster(bar(BAR_PFREE + (int)ps), ((r / NP) - 1) & 1u, abort_flag, W_PFREE)) return false;
-                }
-                trace(tr, tc, 120 + warp, t);
                 {
-                    // image of the slot in the (dead) RoPE region of this tile's stage, the references in
-                    // the first bytes of a no-PE chunk of the other CTA's dims (dead as well)
+                    // image of the other CTA's P' slot in the (dead) RoPE region of this tile's stage, the
+                    // references in the first bytes of a no-PE chunk of the other CTA's dims (dead as well);
+                    // the sender thread copies both once every softmax thread has arrived on PREADY
                     uint8_t* stg = sm + FS_OFF + st * ST_BYTES + ST_ROPE + row * 64;
                     const uint32_t sw = ((uint32_t)row >> 1) & 3u;
                     *reinterpret_cast<uint4*>(stg + (((2u * (uint32_t)hh) ^ sw) << 4)) = make_uint4(pw[0], pw[1], pw[2], pw[3]);
                     *reinterpret_cast<uint4*>(stg + (((2u * (uint32_t)hh + 1u) ^ sw) << 4)) = make_uint4(pw[4], pw[5], pw[6], pw[7]);
-                    const uint32_t mst_off = FS_OFF + st * ST_BYTES + 2u * (1u - (uint32_t)half) * KV_CHUNK;
-                    if (hh == 0) reinterpret_cast<float*>(sm + mst_off)[row] = m_run;
+                    if (hh == 0) reinterpret_cast<float*>(sm + FS_OFF + st * ST_BYTES + 2u * (1u - (uint32_t)half) * KV_CHUNK)[row] = m_run;
                     fence_proxy_async();
-                    trace(tr, tc, 7, t);
-                    named_bar_sync(6, N_SM_WARPS * 32);
-                    trace(tr, tc, 8, t);
-                    if (warp == 0 && lane == 0) {
-                        const uint32_t rbar = remote(bar(BAR_PFULL + (int)ps));
-                        mbar_arrive_expect_tx_cluster(rbar, PS_BYTES + 128 * 4);
-                        bulk_copy_to_cluster(remote(base + PS_OFF + ps * PS_BYTES), base + FS_OFF + st * ST_BYTES + ST_ROPE, PS_BYTES, rbar);
-                        bulk_copy_to_cluster(remote(base + PM_OFF + ps * 128 * 4), base + mst_off, 128 * 4, rbar);
-                    }
                 }
                 tmem_st8(lane_addr + TM_S + 64 * b + 8 * hh, pw);
                 tmem_wait_st();
                 tc_fence_before();
                 mbar_arrive(bar(BAR_PREADY + b));
+                mbar_arrive(bar(BAR_STAGED + (int)st));
                 trace(tr, tc, 30 + warp, t);
                 ++n_rel; ++rel_req;
                 return true;
@@ -477,18 +518,16 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(TC_THREADS, 1) attn_
                 return true;
             };
 
-            // Order: owned tiles run one ahead of the other CTA's tiles, so that neither CTA's
-            // softmax waits for the other's in the steady state (the order is fixed, every warp
-            // takes the same path).
-            {
+            {   // the order of run_sequence, written out (head of own tiles, then rounds)
                 const uint32_t t0 = it, n = (uint32_t)w.nblk;
                 const uint32_t first_own = owned(t0) ? 0u : 1u, first_oth = 1u - first_own;
                 const uint32_t n_own = (n > first_own) ? (n - first_own + 1) / 2 : 0, n_oth = (n > first_oth) ? (n - first_oth + 1) / 2 : 0;
-                if (n_own > 0) ok = own_tile(t0 + first_own);
-                const uint32_t steps = max(n_own > 0 ? n_own - 1 : 0u, n_oth);
-                for (uint32_t k = 0; k < steps && ok; ++k) {
-                    if (k + 1 < n_own) ok = own_tile(t0 + first_own + 2 * (k + 1));
-                    if (ok && k < n_oth) ok = other_tile(t0 + first_oth + 2 * k);
+                const uint32_t head = min((first_own == 0u ? 2u : 1u) + 1u, n_own);
+                for (uint32_t i = 0; i < head && ok; ++i) ok = own_tile(t0 + first_own + 2 * i);
+                const uint32_t rounds = max(n_own - head, n_oth);
+                for (uint32_t k = 0; k < rounds && ok; ++k) {
+                    if (k < n_oth) ok = other_tile(t0 + first_oth + 2 * k);
+                    if (ok && head + k < n_own) ok = own_tile(t0 + first_own + 2 * (head + k));
                 }
                 it += n;
             }
@@ -604,76 +643,86 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(TC_THREADS, 1) attn_
                     ? p.kv + (int64_t)(u >> pbs_shift) * p.block_stride + (int64_t)(u & (unsigned)(p.page_block_size - 1)) * ROW_BYTES
                     : kv_row_ptr(p.kv, idx, p.page_block_size, p.block_stride);
             };
-            int idx_next = fetch_idx(0), idx_next2 = fetch_idx(1);
-#pragma unroll 1
-            for (int k = 0; k < w.nblk && ok; ++k) {
-                const uint32_t t = it + k, r = t >> 1, st = r % NS;
-                const int idx = idx_next;
-                idx_next = idx_next2;
-                idx_next2 = fetch_idx(k + 2);
-                unsigned long long my_src_u = 0ull;
-                if (idx >= 0) my_src_u = reinterpret_cast<unsigned long long>(row_ptr(idx));
-                const unsigned long long kv_u = reinterpret_cast<unsigned long long>(p.kv);
-                if (owned(t)) {
-                    if (r >= (uint32_t)NS) {
-                        ok = mbar_wait_hot(bar(BAR_EMPTY + (int)st), ((r / NS) - 1) & 1u, abort_flag, W_EMPTY);
-                        if (!ok) break;
-                    }
-                    const uint32_t sbase = base + FS_OFF + st * ST_BYTES;
-                    trace(tr, tc, 60 + pw, t);
+            const uint32_t t0 = it;
+            const unsigned long long kv_u = reinterpret_cast<unsigned long long>(p.kv);
+            // the index of this lane's row in the next tile of the order is fetched one tile ahead
+            int idx_pref = fetch_idx((int)(first_in_sequence(t0, (uint32_t)w.nblk, rank) - t0));
+            uint32_t t_next = 0xffffffffu;
+            auto src_of = [&](uint32_t) -> unsigned long long {
+                const int idx = idx_pref;
+                if (t_next != 0xffffffffu) idx_pref = fetch_idx((int)(t_next - t0));
+                return idx >= 0 ? reinterpret_cast<unsigned long long>(row_ptr(idx)) : 0ull;
+            };
+            auto gather_full = [&](uint32_t t) -> bool {
+                const uint32_t r = t >> 1, st = r % NS;
+                const unsigned long long my_src_u = src_of(t);      // issued before the wait for the stage
+                if (r >= (uint32_t)NS) {
+                    ok = mbar_wait_hot(bar(BAR_EMPTY + (int)st), ((r / NS) - 1) & 1u, abort_flag, W_EMPTY);
+                    if (!ok) return false;
+                }
+                const uint32_t sbase = base + FS_OFF + st * ST_BYTES;
+                trace(tr, tc, 60 + pw, t);
 #pragma unroll
-                    for (int hb = 0; hb < 2; ++hb) {
-                        unsigned long long srcs[8];
+                for (int hb = 0; hb < 2; ++hb) {
+                    unsigned long long srcs[8];
 #pragma unroll
-                        for (int i = 0; i < 8; ++i) srcs[i] = __shfl_sync(0xffffffffu, my_src_u, hb * 8 + i);
-#pragma unroll
-                        for (int i = 0; i < 8; ++i) {
-                            const int rr = row0 + hb * 8 + i;
-                            const uint32_t off = (lane >> 3) * KV_CHUNK + rr * 128 + ((((uint32_t)lane & 7u) ^ ((uint32_t)rr & 7u)) << 4);
-                            const bool v = srcs[i] != 0ull;
-                            cp_async16_zfill(sbase + off, reinterpret_cast<const uint8_t*>(v ? srcs[i] + lane * 16 : kv_u), v ? 16u : 0u);
-                        }
-                    }
-#pragma unroll
-                    for (int g = 0; g < 4; ++g) {
-                        const unsigned long long rs = __shfl_sync(0xffffffffu, my_src_u, g * 4 + (lane >> 3));
-                        const int rr = row0 + g * 4 + (lane >> 3);
-                        const uint32_t off = ST_ROPE + rr * 128 + ((((uint32_t)lane & 7u) ^ ((uint32_t)rr & 7u)) << 4);
-                        const bool v = rs != 0ull;
-                        cp_async16_zfill(sbase + off, reinterpret_cast<const uint8_t*>(v ? rs + ROPE_OFF + (lane & 7) * 16 : kv_u), v ? 16u : 0u);
-                    }
-                    if (lane < 16) {
-                        const bool v = my_src_u != 0ull;
-                        cp_async16_zfill(sbase + ST_SCALE + my_row * 16, reinterpret_cast<const uint8_t*>(v ? my_src_u + SCALE_OFF : kv_u), v ? 16u : 0u);
-                    }
-                    cp_async_arrive_noinc(bar(BAR_LOADED + (int)st));
-                    trace(tr, tc, 70 + pw, t);
-                } else {
-                    if (r >= (uint32_t)NS) {
-                        ok = mbar_wait_hot(bar(BAR_HEMPTY + (int)st), ((r / NS) - 1) & 1u, abort_flag, W_HEMPTY);
-                        if (!ok) break;
-                    }
-                    const uint32_t sbase = base + HS_OFF + st * HS_BYTES;
-                    trace(tr, tc, 64 + pw, t);
-                    // lanes 0-15 / 16-31: the 16 chunks (256 bytes) of two rows per pass
+                    for (int i = 0; i < 8; ++i) srcs[i] = __shfl_sync(0xffffffffu, my_src_u, hb * 8 + i);
 #pragma unroll
                     for (int i = 0; i < 8; ++i) {
-                        const int rl = 2 * i + (lane >> 4);
-                        const unsigned long long rs = __shfl_sync(0xffffffffu, my_src_u, rl);
-                        const int rr = row0 + rl;
-                        const uint32_t ch = (uint32_t)lane & 15u;      // chunk inside this CTA's 256 bytes
-                        const uint32_t off = (ch >> 3) * KV_CHUNK + rr * 128 + (((ch & 7u) ^ ((uint32_t)rr & 7u)) << 4);
-                        const bool v = rs != 0ull;
-                        cp_async16_zfill(sbase + off, reinterpret_cast<const uint8_t*>(v ? rs + half * 256 + ch * 16 : kv_u), v ? 16u : 0u);
+                        const int rr = row0 + hb * 8 + i;
+                        const uint32_t off = (lane >> 3) * KV_CHUNK + rr * 128 + ((((uint32_t)lane & 7u) ^ ((uint32_t)rr & 7u)) << 4);
+                        const bool v = srcs[i] != 0ull;
+                        cp_async16_zfill(sbase + off, reinterpret_cast<const uint8_t*>(v ? srcs[i] + lane * 16 : kv_u), v ? 16u : 0u);
                     }
-                    if (lane < 16) {
-                        const bool v = my_src_u != 0ull;
-                        cp_async16_zfill(sbase + HS_SCALE + my_row * 16, reinterpret_cast<const uint8_t*>(v ? my_src_u + SCALE_OFF : kv_u), v ? 16u : 0u);
-                    }
-                    cp_async_arrive_noinc(bar(BAR_HLOADED + (int)st));
-                    trace(tr, tc, 74 + pw, t);
                 }
-            }
+#pragma unroll
+                for (int g = 0; g < 4; ++g) {
+                    const unsigned long long rs = __shfl_sync(0xffffffffu, my_src_u, g * 4 + (lane >> 3));
+                    const int rr = row0 + g * 4 + (lane >> 3);
+                    const uint32_t off = ST_ROPE + rr * 128 + ((((uint32_t)lane & 7u) ^ ((uint32_t)rr & 7u)) << 4);
+                    const bool v = rs != 0ull;
+                    cp_async16_zfill(sbase + off, reinterpret_cast<const uint8_t*>(v ? rs + ROPE_OFF + (lane & 7) * 16 : kv_u), v ? 16u : 0u);
+                }
+                if (lane < 16) {
+                    const bool v = my_src_u != 0ull;
+                    cp_async16_zfill(sbase + ST_SCALE + my_row * 16, reinterpret_cast<const uint8_t*>(v ? my_src_u + SCALE_OFF : kv_u), v ? 16u : 0u);
+                }
+                cp_async_arrive_noinc(bar(BAR_LOADED + (int)st));
+                trace(tr, tc, 70 + pw, t);
+                return true;
+            };
+            auto gather_half = [&](uint32_t t) -> bool {
+                const uint32_t r = t >> 1, st = r % NS;
+                const unsigned long long my_src_u = src_of(t);
+                if (r >= (uint32_t)NS) {
+                    ok = mbar_wait_hot(bar(BAR_HEMPTY + (int)st), ((r / NS) - 1) & 1u, abort_flag, W_HEMPTY);
+                    if (!ok) return false;
+                }
+                const uint32_t sbase = base + HS_OFF + st * HS_BYTES;
+                trace(tr, tc, 64 + pw, t);
+                // lanes 0-15 / 16-31: the 16 chunks (256 bytes) of two rows per pass
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                    const int rl = 2 * i + (lane >> 4);
+                    const unsigned long long rs = __shfl_sync(0xffffffffu, my_src_u, rl);
+                    const int rr = row0 + rl;
+                    const uint32_t ch = (uint32_t)lane & 15u;      // chunk inside this CTA's 256 bytes
+                    const uint32_t off = (ch >> 3) * KV_CHUNK + rr * 128 + (((ch & 7u) ^ ((uint32_t)rr & 7u)) << 4);
+                    const bool v = rs != 0ull;
+                    cp_async16_zfill(sbase + off, reinterpret_cast<const uint8_t*>(v ? rs + half * 256 + ch * 16 : kv_u), v ? 16u : 0u);
+                }
+                if (lane < 16) {
+                    const bool v = my_src_u != 0ull;
+                    cp_async16_zfill(sbase + HS_SCALE + my_row * 16, reinterpret_cast<const uint8_t*>(v ? my_src_u + SCALE_OFF : kv_u), v ? 16u : 0u);
+                }
+                cp_async_arrive_noinc(bar(BAR_HLOADED + (int)st));
+                trace(tr, tc, 74 + pw, t);
+                return true;
+            };
+            ok = run_sequence_ahead(t0, (uint32_t)w.nblk, rank, [&](uint32_t t, bool own, uint32_t tn) -> bool {
+                t_next = tn;
+                return own ? gather_full(t) : gather_half(t);
+            });
             it += w.nblk;
         }
         cp_async_wait_all();
@@ -688,89 +737,92 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(TC_THREADS, 1) attn_
         for (int req = meta.begin_req; req <= last_req && ok; ++req) {
             Work w;
             if (!get_work(p, meta, req, w)) continue;
-#pragma unroll 1
-            for (int k = 0; k < w.nblk && ok; ++k, ++it) {
-                const uint32_t r = it >> 1, st = r % NS;
-                if (owned(it)) {
-                    ok = mbar_wait_hot(bar(BAR_LOADED + (int)st), (r / NS) & 1u, abort_flag, W_LOADED);
-                    if (!ok) break;
-                    uint8_t* sp = sm + FS_OFF + st * ST_BYTES;
-                    uint4 rv[2];
+            auto fix_full = [&](uint32_t t) -> bool {
+                const uint32_t r = t >> 1, st = r % NS;
+                ok = mbar_wait_hot(bar(BAR_LOADED + (int)st), (r / NS) & 1u, abort_flag, W_LOADED);
+                if (!ok) return false;
+                uint8_t* sp = sm + FS_OFF + st * ST_BYTES;
+                uint4 rv[2];
 #pragma unroll
-                    for (int g = 0; g < 2; ++g) {
-                        const int rr = row0 + g * 4 + (lane >> 3);
-                        rv[g] = *reinterpret_cast<const uint4*>(sp + ST_ROPE + rr * 128 + ((((uint32_t)lane & 7u) ^ ((uint32_t)rr & 7u)) << 4));
-                    }
-                    const float4 sc = *reinterpret_cast<const float4*>(sp + ST_SCALE + my_row * 16);
-                    const float smax = fmaxf(fmaxf(sc.x, sc.y), fmaxf(sc.z, sc.w));
-                    const bool uneven = (sc.x != smax) | (sc.y != smax) | (sc.z != smax) | (sc.w != smax);
-                    const float inv_s = (smax > 0.f) ? __uint_as_float(0x7f000000u - __float_as_uint(smax)) : 0.f;
-                    const float my_ratio = (blk == 0 ? sc.x : (blk == 1 ? sc.y : (blk == 2 ? sc.z : sc.w))) * inv_s;
-                    __syncwarp();
-                    if (lane < 8)
-                        *reinterpret_cast<float4*>(sp + ST_SCALE + my_row * 16) =
-                            make_float4(smax, (smax > 0.f) ? (float)((int)(__float_as_uint(smax) >> 23) - 127) : -INFINITY, inv_s, 0.f);
-#pragma unroll
-                    for (int g = 0; g < 2; ++g) {
-                        const int rl = g * 4 + (lane >> 3);
-                        const int rr = row0 + rl;
-                        const __nv_bfloat162 f = __float2bfloat162_rn(__shfl_sync(0xffffffffu, inv_s, rl));
-                        uint4 v = rv[g];
-                        v.x = mul_bf16x2(v.x, f); v.y = mul_bf16x2(v.y, f);
-                        v.z = mul_bf16x2(v.z, f); v.w = mul_bf16x2(v.w, f);
-                        *reinterpret_cast<uint4*>(sp + ST_ROPE + rr * 128 + ((((uint32_t)lane & 7u) ^ ((uint32_t)rr & 7u)) << 4)) = v;
-                    }
-                    uint32_t fix = __ballot_sync(0xffffffffu, uneven && smax > 0.f) & 0xffu;
-                    while (fix) {
-                        const int i = __ffs(fix) - 1;
-                        fix &= fix - 1;
-                        const int rr = row0 + i;
-                        const float ratio_f = __shfl_sync(0xffffffffu, my_ratio, (lane & 24) + i);
-                        if (ratio_f != 1.f) {
-                            uint4* q4 = reinterpret_cast<uint4*>(sp + blk * KV_CHUNK + rr * 128 + ((((uint32_t)lane & 7u) ^ ((uint32_t)rr & 7u)) << 4));
-                            const __half2 ratio = __float2half2_rn(ratio_f);
-                            uint4 v = *q4;
-                            v.x = rescale_e4m3x4(v.x, ratio); v.y = rescale_e4m3x4(v.y, ratio);
-                            v.z = rescale_e4m3x4(v.z, ratio); v.w = rescale_e4m3x4(v.w, ratio);
-                            *q4 = v;
-                        }
-                    }
-                    fence_proxy_async();
-                    mbar_arrive(bar(BAR_FULL + (int)st));
-                    trace(tr, tc, 50, it);
-                } else {
-                    // the other CTA's tile: only this CTA's two no-PE chunks are here; bring them to the row scale
-                    ok = mbar_wait_hot(bar(BAR_HLOADED + (int)st), (r / NS) & 1u, abort_flag, W_HLOADED);
-                    if (!ok) break;
-                    uint8_t* sp = sm + HS_OFF + st * HS_BYTES;
-                    const float4 sc = *reinterpret_cast<const float4*>(sp + HS_SCALE + my_row * 16);
-                    const float smax = fmaxf(fmaxf(sc.x, sc.y), fmaxf(sc.z, sc.w));
-                    const float inv_s = (smax > 0.f) ? __uint_as_float(0x7f000000u - __float_as_uint(smax)) : 0.f;
-                    // lane = (row lane % 8, local chunk block (lane / 8) % 2); lanes 16-31 mirror lanes 0-15
-                    const int lb = (lane >> 3) & 1, gb = 2 * half + lb;
-                    const float my_ratio = (gb == 0 ? sc.x : (gb == 1 ? sc.y : (gb == 2 ? sc.z : sc.w))) * inv_s;
-                    uint32_t fix = __ballot_sync(0xffffffffu, smax > 0.f && my_ratio != 1.f && lane < 16);
-                    fix = (fix | (fix >> 8)) & 0xffu;      // rows with at least one of the two chunks to rewrite
-                    while (fix) {
-                        const int i = __ffs(fix) - 1;
-                        fix &= fix - 1;
-                        const int rr = row0 + i;
-                        // 16 chunks of 16 bytes per row: lane l < 16 rewrites chunk l (block l / 8)
-                        const float ratio_f = __shfl_sync(0xffffffffu, my_ratio, ((lane >> 3) & 1) * 8 + i);
-                        if (lane < 16 && ratio_f != 1.f) {
-                            uint4* q4 = reinterpret_cast<uint4*>(sp + (lane >> 3) * KV_CHUNK + rr * 128 + ((((uint32_t)lane & 7u) ^ ((uint32_t)rr & 7u)) << 4));
-                            const __half2 ratio = __float2half2_rn(ratio_f);
-                            uint4 v = *q4;
-                            v.x = rescale_e4m3x4(v.x, ratio); v.y = rescale_e4m3x4(v.y, ratio);
-                            v.z = rescale_e4m3x4(v.z, ratio); v.w = rescale_e4m3x4(v.w, ratio);
-                            *q4 = v;
-                        }
-                    }
-                    fence_proxy_async();
-                    mbar_arrive(bar(BAR_HFULL + (int)st));
-                    trace(tr, tc, 54, it);
+                for (int g = 0; g < 2; ++g) {
+                    const int rr = row0 + g * 4 + (lane >> 3);
+                    rv[g] = *reinterpret_cast<const uint4*>(sp + ST_ROPE + rr * 128 + ((((uint32_t)lane & 7u) ^ ((uint32_t)rr & 7u)) << 4));
                 }
-            }
+                const float4 sc = *reinterpret_cast<const float4*>(sp + ST_SCALE + my_row * 16);
+                const float smax = fmaxf(fmaxf(sc.x, sc.y), fmaxf(sc.z, sc.w));
+                const bool uneven = (sc.x != smax) | (sc.y != smax) | (sc.z != smax) | (sc.w != smax);
+                const float inv_s = (smax > 0.f) ? __uint_as_float(0x7f000000u - __float_as_uint(smax)) : 0.f;
+                const float my_ratio = (blk == 0 ? sc.x : (blk == 1 ? sc.y : (blk == 2 ? sc.z : sc.w))) * inv_s;
+                __syncwarp();
+                if (lane < 8)
+                    *reinterpret_cast<float4*>(sp + ST_SCALE + my_row * 16) =
+                        make_float4(smax, (smax > 0.f) ? (float)((int)(__float_as_uint(smax) >> 23) - 127) : -INFINITY, inv_s, 0.f);
+#pragma unroll
+                for (int g = 0; g < 2; ++g) {
+                    const int rl = g * 4 + (lane >> 3);
+                    const int rr = row0 + rl;
+                    const __nv_bfloat162 f = __float2bfloat162_rn(__shfl_sync(0xffffffffu, inv_s, rl));
+                    uint4 v = rv[g];
+                    v.x = mul_bf16x2(v.x, f); v.y = mul_bf16x2(v.y, f);
+                    v.z = mul_bf16x2(v.z, f); v.w = mul_bf16x2(v.w, f);
+                    *reinterpret_cast<uint4*>(sp + ST_ROPE + rr * 128 + ((((uint32_t)lane & 7u) ^ ((uint32_t)rr & 7u)) << 4)) = v;
+                }
+                uint32_t fix = __ballot_sync(0xffffffffu, uneven && smax > 0.f) & 0xffu;
+                while (fix) {
+                    const int i = __ffs(fix) - 1;
+                    fix &= fix - 1;
+                    const int rr = row0 + i;
+                    const float ratio_f = __shfl_sync(0xffffffffu, my_ratio, (lane & 24) + i);
+                    if (ratio_f != 1.f) {
+                        uint4* q4 = reinterpret_cast<uint4*>(sp + blk * KV_CHUNK + rr * 128 + ((((uint32_t)lane & 7u) ^ ((uint32_t)rr & 7u)) << 4));
+                        const __half2 ratio = __float2half2_rn(ratio_f);
+                        uint4 v = *q4;
+                        v.x = rescale_e4m3x4(v.x, ratio); v.y = rescale_e4m3x4(v.y, ratio);
+                        v.z = rescale_e4m3x4(v.z, ratio); v.w = rescale_e4m3x4(v.w, ratio);
+                        *q4 = v;
+                    }
+                }
+                fence_proxy_async();
+                mbar_arrive(bar(BAR_FULL + (int)st));
+                trace(tr, tc, 50, t);
+                return true;
+            };
+            auto fix_half = [&](uint32_t t) -> bool {
+                const uint32_t r = t >> 1, st = r % NS;
+                // the other CTA's tile: only this CTA's two no-PE chunks are here; bring them to the row scale
+                ok = mbar_wait_hot(bar(BAR_HLOADED + (int)st), (r / NS) & 1u, abort_flag, W_HLOADED);
+                if (!ok) return false;
+                uint8_t* sp = sm + HS_OFF + st * HS_BYTES;
+                const float4 sc = *reinterpret_cast<const float4*>(sp + HS_SCALE + my_row * 16);
+                const float smax = fmaxf(fmaxf(sc.x, sc.y), fmaxf(sc.z, sc.w));
+                const float inv_s = (smax > 0.f) ? __uint_as_float(0x7f000000u - __float_as_uint(smax)) : 0.f;
+                // lane = (row lane % 8, local chunk block (lane / 8) % 2); lanes 16-31 mirror lanes 0-15
+                const int lb = (lane >> 3) & 1, gb = 2 * half + lb;
+                const float my_ratio = (gb == 0 ? sc.x : (gb == 1 ? sc.y : (gb == 2 ? sc.z : sc.w))) * inv_s;
+                uint32_t fix = __ballot_sync(0xffffffffu, smax > 0.f && my_ratio != 1.f && lane < 16);
+                fix = (fix | (fix >> 8)) & 0xffu;      // rows with at least one of the two chunks to rewrite
+                while (fix) {
+                    const int i = __ffs(fix) - 1;
+                    fix &= fix - 1;
+                    const int rr = row0 + i;
+                    // 16 chunks of 16 bytes per row: lane l < 16 rewrites chunk l (block l / 8)
+                    const float ratio_f = __shfl_sync(0xffffffffu, my_ratio, ((lane >> 3) & 1) * 8 + i);
+                    if (lane < 16 && ratio_f != 1.f) {
+                        uint4* q4 = reinterpret_cast<uint4*>(sp + (lane >> 3) * KV_CHUNK + rr * 128 + ((((uint32_t)lane & 7u) ^ ((uint32_t)rr & 7u)) << 4));
+                        const __half2 ratio = __float2half2_rn(ratio_f);
+                        uint4 v = *q4;
+                        v.x = rescale_e4m3x4(v.x, ratio); v.y = rescale_e4m3x4(v.y, ratio);
+                        v.z = rescale_e4m3x4(v.z, ratio); v.w = rescale_e4m3x4(v.w, ratio);
+                        *q4 = v;
+                    }
+                }
+                fence_proxy_async();
+                mbar_arrive(bar(BAR_HFULL + (int)st));
+                trace(tr, tc, 54, t);
+                return true;
+            };
+            ok = run_sequence(it, (uint32_t)w.nblk, rank, fix_full, fix_half);
+            it += (uint32_t)w.nblk;
         }
     } else if (warp == MMA_WARP && lane == 0) {
         // =================================================================== score MMA issue (owned tiles)
@@ -825,9 +877,6 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(TC_THREADS, 1) attn_
         for (int req = meta.begin_req; req <= last_req && ok; ++req) {
             Work w;
             if (!get_work(p, meta, req, w)) continue;
-            const uint32_t t0 = it, n = (uint32_t)w.nblk;
-            const uint32_t first_own = owned(t0) ? 0u : 1u, first_oth = 1u - first_own;
-            const uint32_t n_own = (n > first_own) ? (n - first_own + 1) / 2 : 0, n_oth = (n > first_oth) ? (n - first_oth + 1) / 2 : 0;
             bool first = true;        // the first product of a request overwrites the accumulator
             auto pv_own = [&](uint32_t t) -> bool {
                 const uint32_t r = t >> 1, b = r & 1u, st = r % NS;
@@ -852,6 +901,8 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(TC_THREADS, 1) attn_
                 if (!mbar_wait_thread(bar(BAR_HFULL + (int)st), (r / NS) & 1u, abort_flag, W_HFULL)) return false;
                 if (!mbar_wait_thread(bar(BAR_ADOPTED + (int)ps), (r / NP) & 1u, abort_flag, W_ADOPTED)) return false;
                 tc_fence_after();
+                // every softmax thread has seen this use of the slot: arm the next one
+                mbar_arrive_expect_tx(bar(BAR_PFULL + (int)ps), PS_BYTES + 128 * 4);
                 const uint32_t vb_lo = desc_lo(base + HS_OFF + st * HS_BYTES, KV_CHUNK);
                 const uint32_t pa_lo = desc_lo(base + PS_OFF + ps * PS_BYTES, 16);
 #pragma unroll
@@ -861,35 +912,41 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(TC_THREADS, 1) attn_
                 }
                 first = false;
                 tc_commit(bar(BAR_HEMPTY + (int)st));
-                tc_commit(bar(BAR_PDONE + (int)ps));
+                tc_commit(remote(bar(BAR_PFREE + (int)ps)));      // the owner may fill the slot again once this product has read it
                 tc_commit(bar(BAR_DONE + (int)(n_issued % NDONE)));
                 trace(tr, tc, 85, t);
                 ++n_issued;
                 return true;
             };
-            if (n_own > 0) ok = pv_own(t0 + first_own);
-            const uint32_t steps = max(n_own > 0 ? n_own - 1 : 0u, n_oth);
-            for (uint32_t k = 0; k < steps && ok; ++k) {
-                if (k + 1 < n_own) ok = pv_own(t0 + first_own + 2 * (k + 1));
-                if (ok && k < n_oth) ok = pv_other(t0 + first_oth + 2 * k);
-            }
-            it += n;
+            ok = run_sequence(it, (uint32_t)w.nblk, rank, pv_own, pv_other);
+            it += (uint32_t)w.nblk;
         }
     } else if (warp == MMA_WARP + 2 && lane == 0) {
-        // =================================================================== credit relay
-        // When the P.V of one of the other CTA's tiles has completed here, its P' slot is free
-        // again: tell the other CTA (it writes the slot from its softmax warps).
+        // =================================================================== sender
+        // When the softmax warps have released an owned tile (P' staged in the tile's stage), copies
+        // the P' image and the references into the other CTA's slot for that tile, once the slot is
+        // free (the other CTA's P.V of the tile NP ring positions back has completed).
         uint32_t it = 0;
         bool ok = true;
         for (int req = meta.begin_req; req <= last_req && ok; ++req) {
             Work w;
             if (!get_work(p, meta, req, w)) continue;
             for (int j = 0; j < w.nblk && ok; ++j, ++it) {
-                if (owned(it)) continue;
-                const uint32_t r = it >> 1, ps = r % NP;
-                ok = mbar_wait_thread(bar(BAR_PDONE + (int)ps), (r / NP) & 1u, abort_flag, W_PDONE);
+                if (!owned(it)) continue;
+                const uint32_t r = it >> 1, st = r % NS, ps = r % NP;
+                ok = mbar_wait_thread(bar(BAR_STAGED + (int)st), (r / NS) & 1u, abort_flag, W_PREADY);
                 if (!ok) break;
-                mbar_arrive_cluster(remote(bar(BAR_PFREE + (int)ps)));
+                trace(tr, tc, 90, it);
+                if (r >= (uint32_t)NP) {
+                    ok = mbar_wait_thread_cluster(bar(BAR_PFREE + (int)ps), ((r / NP) - 1) & 1u, abort_flag, W_PFREE);
+                    if (!ok) break;
+                }
+                trace(tr, tc, 91, it);
+                const uint32_t rbar = remote(bar(BAR_PFULL + (int)ps));
+                const uint32_t stage = base + FS_OFF + st * ST_BYTES;
+                bulk_copy_to_cluster(remote(base + PS_OFF + ps * PS_BYTES), stage + ST_ROPE, PS_BYTES, rbar);
+                bulk_copy_to_cluster(remote(base + PM_OFF + ps * 128 * 4), stage + 2u * (1u - (uint32_t)half) * KV_CHUNK, 128 * 4, rbar);
+                trace(tr, tc, 92, it);
             }
         }
     } else if (warp == MMA_WARP + 3 && lane == 0) {
@@ -906,6 +963,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(TC_THREADS, 1) attn_
                 const uint32_t r = it >> 1, ps = r % NP;
                 ok = mbar_wait_thread_cluster(bar(BAR_PFULL + (int)ps), (r / NP) & 1u, abort_flag, W_PFULL);
                 if (!ok) break;
+                trace(tr, tc, 93, it);
                 mbar_arrive_cluster(remote(bar(BAR_EMPTY + (int)(r % NS))));
             }
         }
@@ -947,8 +1005,12 @@ int launch_attn_tc2(const AttnParams& p, cudaStream_t stream) {
     }
     const int max_pairs = (dev < 64 && sm_count[dev] >= 2) ? sm_count[dev] / 2 : 1;
     const int parts = p.sched ? p.num_parts : (p.num_tokens < max_pairs ? p.num_tokens : max_pairs);
-    Trace tr{nullptr, 0};
+    Trace tr{nullptr, 0, 0};
     get_attn_trace(&tr.buf, &tr.cap);
+    if (tr.buf != nullptr) {
+        const char* e = getenv("SMLA_TRACE_BLOCK");      // debugging aid: which CTA records the timeline
+        tr.block = e ? atoi(e) : 0;
+    }
     attn_tc2_kernel<<<2 * parts, TC_THREADS, SMEM_ALLOC, stream>>>(p, tr);
     return check_launch("attn_tc2_kernel");
 }
