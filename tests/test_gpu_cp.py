@@ -71,8 +71,12 @@ def test_cp_two_nccl_ranks(tmp_path):
     script = tmp_path / "rank.py"
     script.write_text(_RANK_SCRIPT)
     env = dict(os.environ, SMLA_ROOT=ROOT, NCCL_NVLS_ENABLE="0")
-    res = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2",
-                          "--master-addr", "127.0.0.1", "--master-port", "29631", str(script)],
-                         env=env, capture_output=True, text=True, timeout=300)
+    # a rendezvous port may still be held by an earlier job on the same box: one retry on another port
+    for port in ("29631", "29747"):
+        res = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2",
+                              "--master-addr", "127.0.0.1", "--master-port", port, str(script)],
+                             env=env, capture_output=True, text=True, timeout=300)
+        if res.returncode == 0:
+            break
     assert res.returncode == 0, res.stdout[-2000:] + res.stderr[-2000:]
     assert "rank 0 ok" in res.stdout and "rank 1 ok" in res.stdout
