@@ -4,6 +4,8 @@
 // external indexer and it has no multi-GPU path); they implement
 //   logits[i, j] = k_scale[j] * sum_h w[i, h] * relu(q[i, h, :] . k[j, :]),  -inf outside [ks_i, ke_i)
 // followed by a per-row top-k, and the split of a global index list into one GPU's shard.
+#include <cstdint>
+
 #include "common.cuh"
 
 namespace smla {
@@ -54,6 +56,8 @@ mqa_logits_scalar_kernel(const uint8_t* __restrict__ q, const uint8_t* __restric
 // ---------------------------------------------------------------- top-k: radix select per row
 constexpr int TK_THREADS = 1024;
 constexpr int TK_WARPS = TK_THREADS / 32;
+constexpr int TK_CAND = 1024;              // candidates (entries of the threshold's 16-bit bin) topk16_kernel resolves itself
+constexpr int32_t TK_REDO = INT32_MIN;     // first output of a row that has more: the multi-pass kernel redoes the row
 
 __device__ __forceinline__ uint32_t order_key(float f) {   // larger float <=> larger key
     const uint32_t b = __float_as_uint(f);
@@ -93,7 +97,9 @@ __device__ __forceinline__ void for_each_key(const float* __restrict__ x, int lo
 __global__ void __launch_bounds__(TK_THREADS, 1)
 topk_kernel(const float* __restrict__ logits, const int32_t* __restrict__ ks,
             const int32_t* __restrict__ ke, int32_t* __restrict__ out, int num_cols,
-            int64_t logits_stride, int k) {
+            int64_t logits_stride, int k, int only_flagged) {
+    // only_flagged: redo the rows that topk16_kernel marked as beyond its candidate list
+    if (only_flagged && out[(size_t)blockIdx.x * k] != TK_REDO) return;
     __shared__ int hist[256];
     __shared__ int sel_bin, sel_need;
     __shared__ int seg_gt[TK_WARPS], seg_eq[TK_WARPS];
@@ -181,6 +187,139 @@ topk_kernel(const float* __restrict__ logits, const int32_t* __restrict__ ks,
     for (int r = filled + tid; r < k; r += TK_THREADS) o[r] = -1;
 }
 
+// Two-read variant for rows of at most 65536 columns.  The first read of the row leaves the top
+// 16 bits of every key in shared memory (128 KB) and a histogram of the top 8; the second 8 bits
+// are resolved from shared memory, which fixes the threshold's 16-bit bin.  Entries above the bin
+// are written in column order; the entries inside it (a few dozen for real logits) are the only
+// ones whose full keys are read again, and the needed number of them is chosen by rank (key
+// descending, lower column first) and written after the others, again in column order.  A row
+// with more than TK_CAND entries in its bin is marked for the multi-pass kernel.
+__global__ void __launch_bounds__(TK_THREADS, 1)
+topk16_kernel(const float* __restrict__ logits, const int32_t* __restrict__ ks,
+              const int32_t* __restrict__ ke, int32_t* __restrict__ out, int num_cols,
+              int64_t logits_stride, int k) {
+    extern __shared__ uint16_t k16[];          // top 16 key bits of columns [lo, hi)
+    __shared__ int hist[256];
+    __shared__ int sel_bin, sel_need;
+    __shared__ int seg_gt[TK_WARPS], seg_eq[TK_WARPS];
+    __shared__ uint32_t cand_key[TK_CAND];
+    __shared__ int cand_col[TK_CAND];
+
+    const int row = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const float* x = logits + (size_t)row * logits_stride;
+    int lo = ks ? max(ks[row], 0) : 0;
+    int hi = ke ? min(ke[row], num_cols) : num_cols;
+    if (hi < lo) hi = lo;
+    int32_t* o = out + (size_t)row * k;
+    constexpr uint32_t VALID16 = 0x007fu;      // key16 of -inf (and of negative NaNs): candidates lie strictly above
+    const bool vec_ok = ((reinterpret_cast<size_t>(x) & 15) == 0);
+
+    // ---- read 1: 16-bit keys to shared memory, histogram of the top 8 bits
+    for (int b = tid; b < 256; b += TK_THREADS) hist[b] = 0;
+    __syncthreads();
+    auto first = [&](int j, uint32_t key) {
+        const uint32_t h = key >> 16;
+        k16[j - lo] = (uint16_t)h;
+        if (h > VALID16) atomicAdd(&hist[h >> 8], 1);
+    };
+    if (vec_ok) for_each_key(x, lo, hi, tid, TK_THREADS, first);
+    else for (int j = lo + tid; j < hi; j += TK_THREADS) first(j, order_key(x[j]));
+    __syncthreads();
+    auto pick = [&](int need) {        // thread 0: highest bin at which the cumulated count reaches `need`
+        int cum = 0, b = 255;
+        for (; b >= 0; --b) {
+            if (cum + hist[b] >= need) break;
+            cum += hist[b];
+        }
+        sel_bin = b; sel_need = need - cum;
+    };
+    if (tid == 0) pick(k);
+    __syncthreads();
+    bool take_all = sel_bin < 0;               // fewer candidates than k: every one is taken
+    uint32_t t16 = VALID16;                    // entries with key16 > t16 are taken outright
+    int need = 0;                              // and `need` of those with key16 == t16
+    if (!take_all) {
+        const uint32_t b1 = (uint32_t)sel_bin;
+        const int need1 = sel_need;
+        __syncthreads();
+        // ---- second 8 bits, from shared memory
+        for (int b = tid; b < 256; b += TK_THREADS) hist[b] = 0;
+        __syncthreads();
+        for (int i = tid; i < hi - lo; i += TK_THREADS) {
+            const uint32_t h = k16[i];
+            if (h > VALID16 && (h >> 8) == b1) atomicAdd(&hist[h & 255u], 1);
+        }
+        __syncthreads();
+        if (tid == 0) pick(need1);
+        __syncthreads();
+        t16 = (b1 << 8) | (uint32_t)sel_bin;   // sel_bin >= 0: the bin b1 holds at least need1 entries
+        need = sel_need;
+    }
+
+    // ---- ordered write of the entries above the bin; the bin's entries go to the candidate list
+    const int span = hi - lo;
+    const int seg = ((span + TK_WARPS - 1) / TK_WARPS + 31) & ~31;
+    const int s0 = min(warp * seg, span), s1 = min(s0 + seg, span);
+    int c_gt = 0, c_eq = 0;
+    for (int i = s0 + lane; i < s1; i += 32) {
+        const uint32_t h = k16[i];
+        c_gt += (h > t16);
+        c_eq += (!take_all && h == t16);
+    }
+    c_gt = __reduce_add_sync(0xffffffffu, c_gt);
+    c_eq = __reduce_add_sync(0xffffffffu, c_eq);
+    if (lane == 0) { seg_gt[warp] = c_gt; seg_eq[warp] = c_eq; }
+    __syncthreads();
+    int off_gt = 0, off_eq = 0, n_gt = 0, n_eq = 0;
+    for (int w = 0; w < TK_WARPS; ++w) {
+        if (w < warp) { off_gt += seg_gt[w]; off_eq += seg_eq[w]; }
+        n_gt += seg_gt[w]; n_eq += seg_eq[w];
+    }
+    if (n_eq > TK_CAND) {                       // (uniform) too many for the list: leave the row to the multi-pass kernel
+        if (tid == 0) o[0] = TK_REDO;
+        return;
+    }
+    const uint32_t below = (1u << lane) - 1u;
+    for (int i0 = s0; i0 < s1; i0 += 32) {
+        const int i = i0 + lane;
+        const uint32_t h = (i < s1) ? k16[i] : 0u;
+        const bool gt = (i < s1) && h > t16;
+        const bool eq = (i < s1) && !take_all && h == t16;
+        const uint32_t mg = __ballot_sync(0xffffffffu, gt), me = __ballot_sync(0xffffffffu, eq);
+        if (gt) o[off_gt + __popc(mg & below)] = lo + i;
+        if (eq) cand_col[off_eq + __popc(me & below)] = lo + i;
+        off_gt += __popc(mg); off_eq += __popc(me);
+    }
+    __syncthreads();
+    // ---- the bin's entries: full keys (second read, these few only), rank, ordered write of the chosen ones
+    int taken = 0;
+    if (n_eq > 0) {
+        if (tid < n_eq) cand_key[tid] = order_key(x[cand_col[tid]]);
+        __syncthreads();
+        bool chosen = false;
+        if (tid < n_eq) {
+            if (need >= n_eq) chosen = true;
+            else {
+                const uint32_t mine = cand_key[tid];
+                int rank = 0;                   // entries that go before this one: larger key, or equal key and lower column
+                for (int j = 0; j < n_eq; ++j) {
+                    const uint32_t kj = cand_key[j];
+                    rank += (kj > mine) || (kj == mine && j < tid);
+                }
+                chosen = rank < need;
+            }
+        }
+        const uint32_t mc = __ballot_sync(0xffffffffu, chosen);
+        if (lane == 0) seg_eq[warp] = __popc(mc);
+        __syncthreads();
+        int off = 0;
+        for (int w = 0; w < warp; ++w) off += seg_eq[w];
+        if (chosen) o[n_gt + off + __popc(mc & below)] = cand_col[tid];
+        taken = min(need, n_eq);
+    }
+    for (int r = n_gt + taken + tid; r < k; r += TK_THREADS) o[r] = -1;
+}
+
 // ---------------------------------------------------------------- context-parallel partition
 // One warp per row: stable compaction of the entries inside [lo, hi), rebased to lo.
 __global__ void __launch_bounds__(256)
@@ -227,7 +366,23 @@ int launch_mqa_logits_scalar(const uint8_t* q, const uint8_t* k, const float* k_
 int launch_topk(const float* logits, const int32_t* ks, const int32_t* ke, int32_t* out, int num_rows,
                 int num_cols, int64_t logits_stride, int k, cudaStream_t stream) {
     if (num_rows == 0 || k == 0) return 0;
-    topk_kernel<<<num_rows, TK_THREADS, 0, stream>>>(logits, ks, ke, out, num_cols, logits_stride, k);
+    if (num_cols > 65536) {
+        topk_kernel<<<num_rows, TK_THREADS, 0, stream>>>(logits, ks, ke, out, num_cols, logits_stride, k, 0);
+        return check_launch("topk_kernel");
+    }
+    static bool attr_set[64] = {};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    const int smem = 65536 * (int)sizeof(uint16_t);
+    if (dev < 64 && !attr_set[dev]) {
+        const cudaError_t e = cudaFuncSetAttribute(topk16_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+        if (e != cudaSuccess) return set_error((int)e, "topk16_kernel: shared memory: %s", cudaGetErrorString(e));
+        attr_set[dev] = true;
+    }
+    topk16_kernel<<<num_rows, TK_THREADS, smem, stream>>>(logits, ks, ke, out, num_cols, logits_stride, k);
+    if (int e = check_launch("topk16_kernel")) return e;
+    // rows whose threshold bin was larger than the candidate list (marked in their first output) are redone
+    topk_kernel<<<num_rows, TK_THREADS, 0, stream>>>(logits, ks, ke, out, num_cols, logits_stride, k, 1);
     return check_launch("topk_kernel");
 }
 

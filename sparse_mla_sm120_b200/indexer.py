@@ -41,9 +41,9 @@ def fp8_mqa_logits(q: torch.Tensor, k: torch.Tensor, k_scale: torch.Tensor, weig
 
 def topk_indices(logits: torch.Tensor, ks: Optional[torch.Tensor], ke: Optional[torch.Tensor],
                  k: int = 2048) -> torch.Tensor:
-    """Per row, the column numbers of the k largest logits inside [ks, ke) as int32 [rows, k]:
-    first the entries above the k-th value, then the ties at it (lowest columns first), each run
-    in ascending column order; padded with -1 when fewer than k candidates exist."""
+    """Per row, the column numbers of the k largest logits inside [ks, ke) as int32 [rows, k],
+    padded with -1 when fewer than k candidates exist.  Ties at the k-th value go to the lowest
+    columns.  The order inside a row is not part of the contract (two ascending runs)."""
     require_cuda(logits, ks, ke)
     assert logits.dim() == 2 and logits.dtype == torch.float32 and logits.stride(1) == 1
     rows, cols = logits.shape

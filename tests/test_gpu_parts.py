@@ -158,6 +158,28 @@ def test_topk_sets():
     assert int(tied.max()) - int(tied.min()) + 1 == tied.numel() and int(tied.min()) == 100
 
 
+def test_topk_many_ties_and_wide_rows():
+    """More ties at the threshold than the two-read kernel keeps as candidates (the row is redone
+    by the multi-pass kernel), and rows wider than its 65536-column limit."""
+    from sparse_mla_sm120_b200 import indexer
+    torch.manual_seed(6)
+    for rows, cols, k, tie_lo, tie_hi in [(3, 9000, 1024, 2000, 6000), (2, 70000, 2048, 100, 400)]:
+        logits = torch.randn(rows, cols)
+        logits[1, tie_lo:tie_hi] = 0.75
+        got = indexer.topk_indices(logits.to(DEV), None, None, k).cpu()
+        for r in range(rows):
+            g = got[r]
+            assert int((g < 0).sum()) == 0 and torch.unique(g).numel() == k
+            thr = torch.topk(logits[r], k).values[-1]
+            vals = logits[r][g.long()]
+            assert float(vals.min()) >= float(thr)
+            assert int((logits[r] > thr).sum()) == int((vals > thr).sum())
+            tied = g[vals == thr]
+            if tied.numel() > 1 and r == 1 and float(thr) == 0.75:      # ties go to the lowest columns
+                all_tied = torch.nonzero(logits[r] == thr).flatten()
+                assert torch.equal(torch.sort(tied).values, all_tied[:tied.numel()].to(torch.int32))
+
+
 def test_cp_partition():
     from sparse_mla_sm120_b200 import cp
     torch.manual_seed(8)
