@@ -254,3 +254,19 @@ def test_padded_page_stride():
     ref_out, ref_lse = oracle_attn(case)
     out, lse = flash_ops.sparse_mla_decode_fwd(case["q"].to(dev), kv, case["indices"].to(dev), case["sm_scale"])
     H.compare_out(out.cpu(), ref_out, H.TC_ABS, H.TC_REL, H.TC_COS)
+
+
+@pytest.mark.parametrize("impl", [TC, TC_PAIR])
+def test_many_tokens_per_cta(impl):
+    """More query tokens than CTA pairs: without a scheduler every pair walks a run of tokens
+    (Q reloaded, accumulator restarted, rings and barrier phases carried over between them)."""
+    case = make_case(21, 200, 128, 192, 8, kv_std=1.0, q_std=0.5, invalid_tail=0.05)
+    tl = torch.full((200,), 192, dtype=torch.int32)
+    tl[::7] = 64          # some tokens with one tile, so that tile ownership flips between tokens
+    tl[3::11] = 0         # and some with none
+    ref_out, ref_lse = oracle_attn(case, topk_length=tl)
+    # 13 M outputs, many of them averages over 64 tokens only: the noise term of the bound (a 6-sigma figure) gets 1.5x
+    out, mx, lse = _prefill(case, impl, topk_length=tl)
+    _check(out, lse, ref_out, ref_lse, impl, prefill=True, noise=1.5)
+    out, lse = _decode(case, impl, num_sm_parts=200, topk_length=tl)     # the unsplit decode path takes the same route
+    _check(out, lse, ref_out, ref_lse, impl, noise=1.5)
