@@ -76,3 +76,25 @@ def test_split_policy():
     assert pick_num_sm_parts(128, 148) == 128    # two nearly full waves: unsplit
     assert pick_num_sm_parts(1, 148) == 74       # small batch: cut into sms/2 partitions
     assert pick_num_sm_parts(80, 148) == 74
+
+
+def test_flashmla_surface_argument_checks():
+    """The FlashMLA-shaped wrappers refuse what the reference refuses, before any device work."""
+    import pytest
+    import torch
+    from sparse_mla_sm120_b200 import interface
+    meta, none = interface.get_mla_metadata()
+    assert none is None and isinstance(meta, interface.FlashMLASchedMeta) and not meta.have_initialized
+    q = torch.zeros(1, 1, 128, 576, dtype=torch.bfloat16)
+    kv = torch.zeros(2, 64, 1, 656, dtype=torch.uint8)
+    idx = torch.zeros(1, 1, 64, dtype=torch.int32)
+    with pytest.raises(TypeError):
+        interface.flash_mla_with_kvcache(q, kv, None, None, 512, object(), None, None, False, True, indices=idx)
+    with pytest.raises(ValueError):
+        interface.flash_mla_with_kvcache(q, kv, None, None, 512, meta, None, None, False, True, indices=None)
+    with pytest.raises(ValueError):
+        interface.flash_mla_with_kvcache(q, kv, None, None, 512, meta, None, None, False, False, indices=idx)
+    with pytest.raises(NotImplementedError):
+        interface.flash_mla_with_kvcache(q, kv, None, None, 512, meta, None, None, False, True, indices=idx,
+                                         extra_k_cache=kv)
+    assert not meta.have_initialized
