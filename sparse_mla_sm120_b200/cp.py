@@ -113,3 +113,72 @@ def sparse_mla_decode_cp_fwd(q, kv_local, indices, sm_scale, shard_lo: int, shar
         dist.all_gather_into_tensor(o_all, o_all[rank], group=group)
         dist.all_gather_into_tensor(lse_all, lse_all[rank], group=group)
     return combine_parts(o_all, lse_all, attn_sink)
+
+
+# ----------------------------------------------------------------------------------------------
+# Indexer under context parallelism: every rank scores its own shard of the context, keeps its k
+# best candidates per query, and the ranks merge the G*k candidates to the global k best.  The
+# global k best of a row are a subset of the union of the per-shard k best, so the merge is exact
+# (up to the choice among equal logits at the k-th value).
+# ----------------------------------------------------------------------------------------------
+
+def local_window(ks: torch.Tensor, ke: torch.Tensor, shard_lo: int, shard_hi: int):
+    """The part of each query's window [ks, ke) (global positions) that falls into the shard, in
+    shard-local positions; empty windows come out as ks == ke."""
+    n_local = shard_hi - shard_lo
+    return ((ks - shard_lo).clamp(0, n_local).to(torch.int32), (ke - shard_lo).clamp(0, n_local).to(torch.int32))
+
+
+def local_candidates(qi, ki_local, k_scale_local, weights, ks, ke, shard_lo: int, shard_hi: int, k: int):
+    """Score the shard's keys and keep the k best per query.
+
+    ``qi`` [T, H_i, 128] e4m3 and ``weights`` [T, H_i] are the indexer queries (identical on every
+    rank), ``ki_local`` [shard_hi - shard_lo, 128] e4m3 with ``k_scale_local`` the shard's keys,
+    ``ks`` / ``ke`` [T] int32 the visible window of each query in GLOBAL positions.
+    Returns (values [T, k] fp32 with -inf padding, positions [T, k] int32 global with -1 padding)."""
+    from . import indexer
+    ks_l, ke_l = local_window(ks, ke, shard_lo, shard_hi)
+    logits = indexer.fp8_mqa_logits(qi, ki_local, k_scale_local, weights, ks_l, ke_l)
+    local = indexer.topk_indices(logits, ks_l, ke_l, k)
+    valid = local >= 0
+    vals = torch.gather(logits, 1, local.clamp(min=0).long())
+    vals = torch.where(valid, vals, torch.full_like(vals, float("-inf")))
+    return vals, torch.where(valid, local + shard_lo, local)
+
+
+def merge_candidates(vals: torch.Tensor, pos: torch.Tensor, k: int) -> torch.Tensor:
+    """``vals`` / ``pos`` [T, G*k]: the candidates of all shards side by side.  Returns the global
+    positions of the k best per row as int32 [T, k], -1 padded."""
+    from . import indexer
+    pick = indexer.topk_indices(vals.contiguous(), None, None, k)        # columns of the candidate list
+    got = torch.gather(pos, 1, pick.clamp(min=0).long())
+    return torch.where(pick >= 0, got, pick).to(torch.int32)
+
+
+def select_indices_cp(qi, ki_local, k_scale_local, weights, ks, ke, shard_lo: int, shard_hi: int, k: int = 2048,
+                      group=None) -> torch.Tensor:
+    """Distributed top-k of the indexer logits over a context sharded across the ranks of
+    ``group``.  Returns the same [T, k] int32 global positions on every rank.  Exchanged per
+    query token: G * k * 8 bytes."""
+    import torch.distributed as dist
+    world = dist.get_world_size(group) if dist.is_initialized() else 1
+    vals, pos = local_candidates(qi, ki_local, k_scale_local, weights, ks, ke, shard_lo, shard_hi, k)
+    if world == 1:
+        return pos
+    T = vals.shape[0]
+    v_all = torch.empty((world, T, k), dtype=torch.float32, device=vals.device)
+    p_all = torch.empty((world, T, k), dtype=torch.int32, device=vals.device)
+    dist.all_gather_into_tensor(v_all, vals.contiguous(), group=group)
+    dist.all_gather_into_tensor(p_all, pos.contiguous(), group=group)
+    return merge_candidates(v_all.permute(1, 0, 2).reshape(T, world * k), p_all.permute(1, 0, 2).reshape(T, world * k), k)
+
+
+def sparse_mla_indexed_decode_cp_fwd(q, kv_local, qi, ki_local, k_scale_local, weights, ks, ke, sm_scale,
+                                     shard_lo: int, shard_hi: int, topk: int = 2048, group=None, attn_sink=None,
+                                     impl: int = IMPL_AUTO):
+    """One decode step of a long sequence whose context (attention cache and indexer keys alike)
+    is sharded across the ranks: indexer logits -> distributed top-k -> context-parallel sparse
+    attention.  Positions are rows of the flat cache.  Returns (out, lse, indices)."""
+    indices = select_indices_cp(qi, ki_local, k_scale_local, weights, ks, ke, shard_lo, shard_hi, topk, group)
+    out, lse = sparse_mla_decode_cp_fwd(q, kv_local, indices, sm_scale, shard_lo, shard_hi, group, attn_sink, impl)
+    return out, lse, indices

@@ -6,6 +6,7 @@
 // followed by a per-row top-k, and the split of a global index list into one GPU's shard.
 #include <cstdint>
 
+#include <cstdio>
 #include "common.cuh"
 
 namespace smla {
@@ -56,7 +57,6 @@ mqa_logits_scalar_kernel(const uint8_t* __restrict__ q, const uint8_t* __restric
 // ---------------------------------------------------------------- top-k: radix select per row
 constexpr int TK_THREADS = 1024;
 constexpr int TK_WARPS = TK_THREADS / 32;
-constexpr int TK_CAND = 1024;              // candidates (entries of the threshold's 16-bit bin) topk16_kernel resolves itself
 constexpr int32_t TK_REDO = INT32_MIN;     // first output of a row that has more: the multi-pass kernel redoes the row
 
 __device__ __forceinline__ uint32_t order_key(float f) {   // larger float <=> larger key
@@ -98,7 +98,7 @@ __global__ void __launch_bounds__(TK_THREADS, 1)
 topk_kernel(const float* __restrict__ logits, const int32_t* __restrict__ ks,
             const int32_t* __restrict__ ke, int32_t* __restrict__ out, int num_cols,
             int64_t logits_stride, int k, int only_flagged) {
-    // only_flagged: redo the rows that topk16_kernel marked as beyond its candidate list
+    // only_flagged: redo the rows that topk_select_kernel gave up on
     if (only_flagged && out[(size_t)blockIdx.x * k] != TK_REDO) return;
     __shared__ int hist[256];
     __shared__ int sel_bin, sel_need;
@@ -187,23 +187,95 @@ topk_kernel(const float* __restrict__ logits, const int32_t* __restrict__ ks,
     for (int r = filled + tid; r < k; r += TK_THREADS) o[r] = -1;
 }
 
-// Two-read variant for rows of at most 65536 columns.  The first read of the row leaves the top
-// 16 bits of every key in shared memory (128 KB) and a histogram of the top 8; the second 8 bits
-// are resolved from shared memory, which fixes the threshold's 16-bit bin.  Entries above the bin
-// are written in column order; the entries inside it (a few dozen for real logits) are the only
-// ones whose full keys are read again, and the needed number of them is chosen by rank (key
-// descending, lower column first) and written after the others, again in column order.  A row
-// with more than TK_CAND entries in its bin is marked for the multi-pass kernel.
-__global__ void __launch_bounds__(TK_THREADS, 1)
-topk16_kernel(const float* __restrict__ logits, const int32_t* __restrict__ ks,
-              const int32_t* __restrict__ ke, int32_t* __restrict__ out, int num_cols,
-              int64_t logits_stride, int k) {
-    extern __shared__ uint16_t k16[];          // top 16 key bits of columns [lo, hi)
-    __shared__ int hist[256];
-    __shared__ int sel_bin, sel_need;
-    __shared__ int seg_gt[TK_WARPS], seg_eq[TK_WARPS];
-    __shared__ uint32_t cand_key[TK_CAND];
-    __shared__ int cand_col[TK_CAND];
+// Warp 0: the highest of 256 bins at which the count cumulated from the top reaches `need`
+// (bin -1 when the whole histogram holds less), and how many entries of that bin are needed.
+__device__ __forceinline__ void pick_bin(const int* hist, int need, int lane, int* sel_bin, int* sel_need) {
+    int h[8], s = 0;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) { h[i] = hist[8 * lane + i]; s += h[i]; }
+    int suf = s;                                   // sum over lanes >= this one
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+        const int t = __shfl_down_sync(0xffffffffu, suf, o);
+        if (lane + o < 32) suf += t;
+    }
+    const int above = suf - s;
+    const bool here = (above < need) && (suf >= need);
+    const uint32_t m = __ballot_sync(0xffffffffu, here);
+    if (here) {
+        int cum = above, b = 7;
+        for (; b > 0; --b) {
+            if (cum + h[b] >= need) break;
+            cum += h[b];
+        }
+        *sel_bin = 8 * lane + b; *sel_need = need - cum;
+    }
+    if (m == 0 && lane == 0) { *sel_bin = -1; *sel_need = need - suf; }
+}
+
+// One-read selection.  A sample of the row (512 runs of 8 neighbouring logits, one 32-byte sector
+// each, evenly spread) gives a threshold that, with a margin of four standard deviations of the
+// estimate, lets through somewhat more than k entries (about 1.4 k for k = 2048 out of 65536).
+// The single pass over the row then appends the column of every entry at or above the threshold
+// to a candidate list in shared memory, and the exact k best are chosen among the few thousand
+// candidates (their logits are read again, into registers): radix select on the full 32-bit keys,
+// ties at the k-th key by lowest column.  Rows whose window has at most TS_DIRECT columns skip the
+// sample and list every column.  Any width of row is served (nothing but the candidates is kept
+// on chip), and several CTAs fit an SM, so the read of one row overlaps the selection of another.
+// When the guess fails -- fewer than k candidates, a list overflows (heavy ties, logits that
+// cluster far more than the sample saw) -- the row is marked for the multi-pass kernel.
+// The pass over the row is bound by instruction issue: it compares the logits as floats (one
+// instruction per entry; NaNs never become candidates) and runs one round of warp votes per 256
+// entries.
+//
+// Order of the output: every warp owns the 128-column blocks warp, warp + 16, ... of the row and
+// appends to its own list in block order, lane order, column order; the lists are written out one
+// after the other.  The order is therefore a fixed function of the input (no atomics decide it),
+// though not ascending.
+constexpr int TS_THREADS = 512;
+constexpr int TS_WARPS = TS_THREADS / 32;
+constexpr int TS_LIST = 512;               // candidates per warp
+constexpr int TS_PER_LANE = TS_LIST / 32;
+constexpr int TS_SAMPLE = 4096;            // sampled logits: 512 runs of 8
+constexpr int TS_EQ = 1024;                // entries equal to the k-th key that are ranked by column
+constexpr int TS_DIRECT = TS_WARPS * TS_LIST - 128;   // windows up to this size need no threshold
+constexpr int TS_KMAX = 4096;              // largest k (the lists hold 8192)
+
+__device__ __forceinline__ float4 load_row4(const float* __restrict__ x, int j, int num_cols, bool vec_ok) {
+    if (vec_ok && j + 3 < num_cols) return *reinterpret_cast<const float4*>(x + j);
+    float4 f;
+    f.x = (j + 0 < num_cols) ? x[j + 0] : -INFINITY;
+    f.y = (j + 1 < num_cols) ? x[j + 1] : -INFINITY;
+    f.z = (j + 2 < num_cols) ? x[j + 2] : -INFINITY;
+    f.w = (j + 3 < num_cols) ? x[j + 3] : -INFINITY;
+    return f;
+}
+
+__device__ __forceinline__ float key_to_float(uint32_t key) {      // inverse of order_key
+    return __uint_as_float((key & 0x80000000u) ? (key ^ 0x80000000u) : ~key);
+}
+
+// Adds one to hist[bin] for every lane with `on`; the lanes that share the bin of the first such
+// lane (nearly all of them while the radix select is at its leading digits) share one atomic.
+__device__ __forceinline__ void hist_add(int* hist, bool on, uint32_t bin, int lane) {
+    const uint32_t mm = __ballot_sync(0xffffffffu, on);
+    if (mm == 0) return;
+    const int first = __ffs(mm) - 1;
+    const uint32_t lead = __shfl_sync(0xffffffffu, bin, first);
+    const uint32_t same = __ballot_sync(0xffffffffu, on && bin == lead);
+    if (lane == first) atomicAdd(&hist[lead], __popc(same));
+    if (on && bin != lead) atomicAdd(&hist[bin], 1);
+}
+
+__global__ void __launch_bounds__(TS_THREADS, 2)
+topk_select_kernel(const float* __restrict__ logits, const int32_t* __restrict__ ks,
+                   const int32_t* __restrict__ ke, int32_t* __restrict__ out, int num_cols,
+                   int64_t logits_stride, int k) {
+    __shared__ __align__(16) int lists[TS_WARPS * TS_LIST];   // candidate columns
+    __shared__ int hist[2][256];
+    __shared__ int sel_bin, sel_need, n_eq_s;
+    __shared__ int cw[TS_WARPS], cc[TS_WARPS];
+    __shared__ int eq_col[TS_EQ];
 
     const int row = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const float* x = logits + (size_t)row * logits_stride;
@@ -211,113 +283,210 @@ topk16_kernel(const float* __restrict__ logits, const int32_t* __restrict__ ks,
     int hi = ke ? min(ke[row], num_cols) : num_cols;
     if (hi < lo) hi = lo;
     int32_t* o = out + (size_t)row * k;
-    constexpr uint32_t VALID16 = 0x007fu;      // key16 of -inf (and of negative NaNs): candidates lie strictly above
+    const uint32_t NEG_INF_KEY = order_key(-INFINITY);
+    constexpr uint32_t VALID16 = 0x007fu;      // key >> 16 of -inf: candidates lie strictly above
     const bool vec_ok = ((reinterpret_cast<size_t>(x) & 15) == 0);
-
-    // ---- read 1: 16-bit keys to shared memory, histogram of the top 8 bits
-    for (int b = tid; b < 256; b += TK_THREADS) hist[b] = 0;
-    __syncthreads();
-    auto first = [&](int j, uint32_t key) {
-        const uint32_t h = key >> 16;
-        k16[j - lo] = (uint16_t)h;
-        if (h > VALID16) atomicAdd(&hist[h >> 8], 1);
-    };
-    if (vec_ok) for_each_key(x, lo, hi, tid, TK_THREADS, first);
-    else for (int j = lo + tid; j < hi; j += TK_THREADS) first(j, order_key(x[j]));
-    __syncthreads();
-    auto pick = [&](int need) {        // thread 0: highest bin at which the cumulated count reaches `need`
-        int cum = 0, b = 255;
-        for (; b >= 0; --b) {
-            if (cum + hist[b] >= need) break;
-            cum += hist[b];
-        }
-        sel_bin = b; sel_need = need - cum;
-    };
-    if (tid == 0) pick(k);
-    __syncthreads();
-    bool take_all = sel_bin < 0;               // fewer candidates than k: every one is taken
-    uint32_t t16 = VALID16;                    // entries with key16 > t16 are taken outright
-    int need = 0;                              // and `need` of those with key16 == t16
-    if (!take_all) {
-        const uint32_t b1 = (uint32_t)sel_bin;
-        const int need1 = sel_need;
-        __syncthreads();
-        // ---- second 8 bits, from shared memory
-        for (int b = tid; b < 256; b += TK_THREADS) hist[b] = 0;
-        __syncthreads();
-        for (int i = tid; i < hi - lo; i += TK_THREADS) {
-            const uint32_t h = k16[i];
-            if (h > VALID16 && (h >> 8) == b1) atomicAdd(&hist[h & 255u], 1);
-        }
-        __syncthreads();
-        if (tid == 0) pick(need1);
-        __syncthreads();
-        t16 = (b1 << 8) | (uint32_t)sel_bin;   // sel_bin >= 0: the bin b1 holds at least need1 entries
-        need = sel_need;
-    }
-
-    // ---- ordered write of the entries above the bin; the bin's entries go to the candidate list
+    const int base = lo & ~3;
     const int span = hi - lo;
-    const int seg = ((span + TK_WARPS - 1) / TK_WARPS + 31) & ~31;
-    const int s0 = min(warp * seg, span), s1 = min(s0 + seg, span);
-    int c_gt = 0, c_eq = 0;
-    for (int i = s0 + lane; i < s1; i += 32) {
-        const uint32_t h = k16[i];
-        c_gt += (h > t16);
-        c_eq += (!take_all && h == t16);
+    const uint32_t below = (1u << lane) - 1u;
+
+#ifdef SMLA_TK_TRACE
+    long long tk_t[16]; int tk_n = 0;
+#define TK_MARK() do { __syncthreads(); tk_t[tk_n++] = clock64(); } while (0)
+#else
+#define TK_MARK() do {} while (0)
+#endif
+    TK_MARK();
+    // ---- threshold from a sample
+    uint32_t t_lo = NEG_INF_KEY + 1u;          // entries with key >= t_lo become candidates
+    const bool sampled = (hi - base) > TS_DIRECT;
+    for (int b = tid; b < 512; b += TS_THREADS) (&hist[0][0])[b] = 0;
+    if (tid == 0) n_eq_s = 0;
+    if (sampled) {
+        __syncthreads();
+        const int run_stride = span / (TS_SAMPLE / 8);   // >= 15: the runs of 8 do not overlap
+        uint32_t h[TS_SAMPLE / TS_THREADS];
+#pragma unroll
+        for (int r = 0; r < TS_SAMPLE / TS_THREADS; ++r) {
+            const int i = tid + TS_THREADS * r;
+            h[r] = order_key(x[lo + (i >> 3) * run_stride + (i & 7)]) >> 16;
+        }
+#pragma unroll
+        for (int r = 0; r < TS_SAMPLE / TS_THREADS; ++r) hist_add(hist[0], h[r] > VALID16, h[r] >> 8, lane);
+        __syncthreads();
+        // expected rank of the row's k-th entry inside the sample, plus four standard deviations
+        const float m = (float)k * (float)TS_SAMPLE / (float)span;
+        const int need_s = (int)(m + 4.f * sqrtf(m)) + 4;
+        if (warp == 0) pick_bin(hist[0], need_s, lane, &sel_bin, &sel_need);
+        __syncthreads();
+        if (sel_bin >= 0) {
+            const uint32_t b1 = (uint32_t)sel_bin;
+            const int need1 = sel_need;
+#pragma unroll
+            for (int r = 0; r < TS_SAMPLE / TS_THREADS; ++r)
+                if (h[r] > VALID16 && (h[r] >> 8) == b1) atomicAdd(&hist[1][h[r] & 255u], 1);
+            __syncthreads();
+            if (warp == 0) pick_bin(hist[1], need1, lane, &sel_bin, &sel_need);
+            __syncthreads();
+            t_lo = max(((b1 << 8) | (uint32_t)sel_bin) << 16, NEG_INF_KEY + 1u);
+        }
     }
-    c_gt = __reduce_add_sync(0xffffffffu, c_gt);
-    c_eq = __reduce_add_sync(0xffffffffu, c_eq);
-    if (lane == 0) { seg_gt[warp] = c_gt; seg_eq[warp] = c_eq; }
+    const float t_f = key_to_float(t_lo);
+
+    TK_MARK();
+    // ---- the one pass over the row: candidate columns to the warp's list.  Two blocks (256
+    // entries, eight per lane) per round of votes; the loads of the next four blocks are issued
+    // before the current four are looked at.
+    const int nblk = (hi - base + 127) >> 7;
+    int* mine = lists + warp * TS_LIST;
+    int cnt = 0;                               // entries this warp has met (beyond TS_LIST they are only counted)
+    const float4 none = make_float4(-INFINITY, -INFINITY, -INFINITY, -INFINITY);
+    auto load_blk = [&](int blk) -> float4 {
+        return (blk < nblk) ? load_row4(x, base + blk * 128 + 4 * lane, num_cols, vec_ok) : none;
+    };
+    float4 f[4], g[4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) f[u] = load_blk(warp + u * TS_WARPS);
+    for (int blk0 = warp; blk0 < nblk; blk0 += 4 * TS_WARPS) {
+#pragma unroll
+        for (int u = 0; u < 4; ++u) g[u] = load_blk(blk0 + (4 + u) * TS_WARPS);
+#pragma unroll
+        for (int u = 0; u < 4; u += 2) {
+            const int blk_a = blk0 + u * TS_WARPS, blk_b = blk_a + TS_WARPS;     // blocks past the end hold -inf
+            const int ja = base + blk_a * 128 + 4 * lane, jb = ja + TS_WARPS * 128;
+            const float v[8] = {f[u].x, f[u].y, f[u].z, f[u].w, f[u + 1].x, f[u + 1].y, f[u + 1].z, f[u + 1].w};
+            uint32_t m = 0;
+#pragma unroll
+            for (int e = 0; e < 8; ++e) m |= (uint32_t)(v[e] >= t_f) << e;
+            if (blk_a == 0 || blk_b >= nblk - 1) {                               // (uniform) the window's edges
+#pragma unroll
+                for (int e = 0; e < 8; ++e) {
+                    const int j = (e < 4 ? ja : jb) + (e & 3);
+                    if (j < lo || j >= hi) m &= ~(1u << e);
+                }
+            }
+            if (__ballot_sync(0xffffffffu, m != 0) == 0) continue;
+            const int c = __popc(m);
+            const uint32_t b0 = __ballot_sync(0xffffffffu, c & 1), b1 = __ballot_sync(0xffffffffu, c & 2),
+                           b2 = __ballot_sync(0xffffffffu, c & 4), b3 = __ballot_sync(0xffffffffu, c & 8);
+            int at = cnt + __popc(b0 & below) + 2 * __popc(b1 & below) + 4 * __popc(b2 & below) + 8 * __popc(b3 & below);
+#pragma unroll
+            for (int e = 0; e < 8; ++e) {
+                if ((m >> e) & 1u) {
+                    if (at < TS_LIST) mine[at] = (e < 4 ? ja : jb) + (e & 3);
+                    ++at;
+                }
+            }
+            cnt += __popc(b0) + 2 * __popc(b1) + 4 * __popc(b2) + 8 * __popc(b3);
+        }
+#pragma unroll
+        for (int u = 0; u < 4; ++u) f[u] = g[u];
+    }
+    TK_MARK();
+    if (lane == 0) cw[warp] = cnt;
     __syncthreads();
-    int off_gt = 0, off_eq = 0, n_gt = 0, n_eq = 0;
-    for (int w = 0; w < TK_WARPS; ++w) {
-        if (w < warp) { off_gt += seg_gt[w]; off_eq += seg_eq[w]; }
-        n_gt += seg_gt[w]; n_eq += seg_eq[w];
-    }
-    if (n_eq > TK_CAND) {                       // (uniform) too many for the list: leave the row to the multi-pass kernel
+    int total = 0;
+    bool overflow = false;
+#pragma unroll
+    for (int w = 0; w < TS_WARPS; ++w) { total += cw[w]; overflow |= cw[w] > TS_LIST; }
+    if (overflow || (sampled && total < k)) {  // (uniform) the guess failed: the multi-pass kernel redoes the row
         if (tid == 0) o[0] = TK_REDO;
         return;
     }
-    const uint32_t below = (1u << lane) - 1u;
-    for (int i0 = s0; i0 < s1; i0 += 32) {
-        const int i = i0 + lane;
-        const uint32_t h = (i < s1) ? k16[i] : 0u;
-        const bool gt = (i < s1) && h > t16;
-        const bool eq = (i < s1) && !take_all && h == t16;
-        const uint32_t mg = __ballot_sync(0xffffffffu, gt), me = __ballot_sync(0xffffffffu, eq);
-        if (gt) o[off_gt + __popc(mg & below)] = lo + i;
-        if (eq) cand_col[off_eq + __popc(me & below)] = lo + i;
-        off_gt += __popc(mg); off_eq += __popc(me);
+
+    // ---- the candidates of this warp's list, TS_PER_LANE per lane, into registers
+    const int mycount = cnt;
+    const int nr = (mycount + 31) >> 5;        // rounds in use (uniform in the warp)
+    int col[TS_PER_LANE];
+    uint32_t key[TS_PER_LANE];
+#pragma unroll
+    for (int r = 0; r < TS_PER_LANE; ++r) {
+        const bool in = lane + 32 * r < mycount;
+        col[r] = in ? mine[lane + 32 * r] : -1;
+        key[r] = in ? order_key(x[col[r]]) : 0u;
     }
-    __syncthreads();
-    // ---- the bin's entries: full keys (second read, these few only), rank, ordered write of the chosen ones
-    int taken = 0;
-    if (n_eq > 0) {
-        if (tid < n_eq) cand_key[tid] = order_key(x[cand_col[tid]]);
-        __syncthreads();
-        bool chosen = false;
-        if (tid < n_eq) {
-            if (need >= n_eq) chosen = true;
-            else {
-                const uint32_t mine = cand_key[tid];
-                int rank = 0;                   // entries that go before this one: larger key, or equal key and lower column
-                for (int j = 0; j < n_eq; ++j) {
-                    const uint32_t kj = cand_key[j];
-                    rank += (kj > mine) || (kj == mine && j < tid);
-                }
-                chosen = rank < need;
+
+    // ---- the k-th largest key among the candidates (radix select, 8 bits per pass)
+    uint32_t kth = 0;                          // chosen: key > kth, and need_eq of the entries with key == kth
+    int need_eq = 0;
+    const bool take_all = total <= k;
+    if (!take_all) {
+        uint32_t prefix = 0, prefix_mask = 0;
+        int need = k;
+#pragma unroll
+        for (int pass = 0; pass < 4; ++pass) {
+            const int shift = 24 - 8 * pass;
+            int* hp = hist[pass & 1];
+            if (pass >= 2 || sampled) {        // used two passes ago, or by the sample (both were cleared at the start)
+                for (int b = tid; b < 256; b += TS_THREADS) hp[b] = 0;
+                __syncthreads();
+            }
+#pragma unroll
+            for (int r = 0; r < TS_PER_LANE; ++r) {
+                if (r < nr) hist_add(hp, col[r] >= 0 && (key[r] & prefix_mask) == prefix, (key[r] >> shift) & 255u, lane);
+            }
+            __syncthreads();
+            if (warp == 0) pick_bin(hp, need, lane, &sel_bin, &sel_need);
+            __syncthreads();
+            prefix |= (uint32_t)sel_bin << shift;      // sel_bin >= 0: at least `need` entries match the prefix
+            prefix_mask |= 255u << shift;
+            need = sel_need;
+        }
+        kth = prefix;
+        need_eq = need;
+        // the entries equal to the k-th key, to be ranked by column
+#pragma unroll
+        for (int r = 0; r < TS_PER_LANE; ++r) {
+            if (col[r] >= 0 && key[r] == kth) {
+                const int at = atomicAdd(&n_eq_s, 1);
+                if (at < TS_EQ) eq_col[at] = col[r];
             }
         }
-        const uint32_t mc = __ballot_sync(0xffffffffu, chosen);
-        if (lane == 0) seg_eq[warp] = __popc(mc);
         __syncthreads();
-        int off = 0;
-        for (int w = 0; w < warp; ++w) off += seg_eq[w];
-        if (chosen) o[n_gt + off + __popc(mc & below)] = cand_col[tid];
-        taken = min(need, n_eq);
+        if (n_eq_s > TS_EQ) {                  // (uniform)
+            if (tid == 0) o[0] = TK_REDO;
+            return;
+        }
     }
-    for (int r = n_gt + taken + tid; r < k; r += TK_THREADS) o[r] = -1;
+    TK_MARK();
+    const int n_eq = take_all ? 0 : n_eq_s;
+    // ---- write: every warp its own list, in list order
+    uint32_t votes[TS_PER_LANE];
+    int nsel = 0;
+#pragma unroll
+    for (int r = 0; r < TS_PER_LANE; ++r) {
+        bool ch = false;
+        if (col[r] >= 0) {
+            if (take_all || key[r] > kth) ch = true;
+            else if (key[r] == kth) {
+                if (need_eq >= n_eq) ch = true;
+                else {
+                    int rank = 0;              // equal entries in lower columns
+                    for (int i = 0; i < n_eq; ++i) rank += eq_col[i] < col[r];
+                    ch = rank < need_eq;
+                }
+            }
+        }
+        votes[r] = (r < nr) ? __ballot_sync(0xffffffffu, ch) : 0u;
+        nsel += __popc(votes[r]);
+    }
+    if (lane == 0) cc[warp] = nsel;
+    __syncthreads();
+    int off = 0, filled = 0;
+#pragma unroll
+    for (int w = 0; w < TS_WARPS; ++w) { if (w < warp) off += cc[w]; filled += cc[w]; }
+#pragma unroll
+    for (int r = 0; r < TS_PER_LANE; ++r) {
+        if ((votes[r] >> lane) & 1u) o[off + __popc(votes[r] & below)] = col[r];
+        off += __popc(votes[r]);
+    }
+    for (int r = filled + tid; r < k; r += TS_THREADS) o[r] = -1;
+#ifdef SMLA_TK_TRACE
+    TK_MARK();
+    if (tid == 0 && row == 0)
+        printf("select: sample %lld pass %lld select %lld write %lld (cand %d, eq %d)\n", tk_t[1] - tk_t[0], tk_t[2] - tk_t[1],
+               tk_t[3] - tk_t[2], tk_t[4] - tk_t[3], total, n_eq);
+#endif
 }
 
 // ---------------------------------------------------------------- context-parallel partition
@@ -366,22 +535,16 @@ int launch_mqa_logits_scalar(const uint8_t* q, const uint8_t* k, const float* k_
 int launch_topk(const float* logits, const int32_t* ks, const int32_t* ke, int32_t* out, int num_rows,
                 int num_cols, int64_t logits_stride, int k, cudaStream_t stream) {
     if (num_rows == 0 || k == 0) return 0;
-    if (num_cols > 65536) {
+    if (k > TS_KMAX) {
         topk_kernel<<<num_rows, TK_THREADS, 0, stream>>>(logits, ks, ke, out, num_cols, logits_stride, k, 0);
         return check_launch("topk_kernel");
     }
     static bool attr_set[64] = {};
     int dev = 0;
     cudaGetDevice(&dev);
-    const int smem = 65536 * (int)sizeof(uint16_t);
-    if (dev < 64 && !attr_set[dev]) {
-        const cudaError_t e = cudaFuncSetAttribute(topk16_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
-        if (e != cudaSuccess) return set_error((int)e, "topk16_kernel: shared memory: %s", cudaGetErrorString(e));
-        attr_set[dev] = true;
-    }
-    topk16_kernel<<<num_rows, TK_THREADS, smem, stream>>>(logits, ks, ke, out, num_cols, logits_stride, k);
-    if (int e = check_launch("topk16_kernel")) return e;
-    // rows whose threshold bin was larger than the candidate list (marked in their first output) are redone
+    topk_select_kernel<<<num_rows, TS_THREADS, 0, stream>>>(logits, ks, ke, out, num_cols, logits_stride, k);
+    if (const int rc = check_launch("topk_select_kernel")) return rc;
+    // rows the one-read kernel gave up on (it marks them) are redone by the multi-pass kernel
     topk_kernel<<<num_rows, TK_THREADS, 0, stream>>>(logits, ks, ke, out, num_cols, logits_stride, k, 1);
     return check_launch("topk_kernel");
 }

@@ -53,6 +53,7 @@ struct LogitsParams {
     const uint8_t* q; const uint8_t* k; const float* k_scale; const float* w;
     const int32_t* ks; const int32_t* ke; float* logits; int32_t* status;
     int s_q, heads, s_k; int64_t stride;
+    int chunk_tiles;   // key tiles per work item (a work item: one query group x one run of key tiles)
 };
 
 __global__ void __launch_bounds__(LX_THREADS, 1) mqa_logits_tc_kernel(const LogitsParams p, const __grid_constant__ CUtensorMap qmap,
@@ -92,6 +93,22 @@ __global__ void __launch_bounds__(LX_THREADS, 1) mqa_logits_tc_kernel(const Logi
         t0 = (hi > lo) ? lo / LX_KT : 0;
         t1 = (hi > lo) ? (hi + LX_KT - 1) / LX_KT : 0;
     };
+    // Work items: item w is query group w % num_groups over the key tiles [c * chunk_tiles, (c + 1) *
+    // chunk_tiles) with c = w / num_groups, so that a few decode tokens over a long context still
+    // fill the machine and neighbouring CTAs read the same keys.  [t0, t1) are the tiles of the item
+    // that the group needs, [j0, j1) the logits columns the item is responsible for.
+    const int num_chunks = ((p.s_k + LX_KT - 1) / LX_KT + p.chunk_tiles - 1) / p.chunk_tiles;
+    const int num_items = num_groups * num_chunks;
+    auto item_range = [&](int w, int& g, int& t0, int& t1, int& j0, int& j1) {
+        g = w % num_groups;
+        const int c = w / num_groups;
+        group_range(g, t0, t1);
+        t0 = max(t0, c * p.chunk_tiles);
+        t1 = min(t1, (c + 1) * p.chunk_tiles);
+        if (t1 < t0) t1 = t0;
+        j0 = c * p.chunk_tiles * LX_KT;
+        j1 = min(p.s_k, (c + 1) * p.chunk_tiles * LX_KT);
+    };
 
     if (warp < LX_EPI_WARPS) {
         // =================================================================== epilogue
@@ -99,16 +116,16 @@ __global__ void __launch_bounds__(LX_THREADS, 1) mqa_logits_tc_kernel(const Logi
         const uint32_t lane_addr = tmem + ((uint32_t)(quarter * 32) << 16);
         uint32_t it = 0, qn = 0;   // tiles and non-empty groups seen by this CTA
         bool ok = true;
-        for (int g = blockIdx.x; g < num_groups && ok; g += gridDim.x) {
-            int t0, t1;
-            group_range(g, t0, t1);
+        for (int w = blockIdx.x; w < num_items && ok; w += gridDim.x) {
+            int g, t0, t1, j0, j1;
+            item_range(w, g, t0, t1, j0, j1);
             const float* wsm = reinterpret_cast<const float*>(sm + LX_W_OFF + (qn & 3u) * LX_W_BYTES);
             const int q0 = g * LX_QG + qp;
             const int ks0 = q0 < p.s_q ? p.ks[q0] : 0, ke0 = q0 < p.s_q ? p.ke[q0] : 0;
-            // columns outside every tile of the group are -inf: written here, 128 keys per pass
+            // columns of the item outside every tile the group needs are -inf: written here, 128 keys per pass
             if (q0 < p.s_q) {
                 float* row = p.logits + (size_t)q0 * p.stride;
-                for (int j = quarter * 32 + lane; j < p.s_k; j += 128)
+                for (int j = j0 + quarter * 32 + lane; j < j1; j += 128)
                     if (j < t0 * LX_KT || j >= t1 * LX_KT) row[j] = -INFINITY;
             }
             if (t1 > t0) {
@@ -158,9 +175,9 @@ __global__ void __launch_bounds__(LX_THREADS, 1) mqa_logits_tc_kernel(const Logi
         // =================================================================== loader
         uint32_t it = 0, qn = 0;
         bool ok = true;
-        for (int g = blockIdx.x; g < num_groups && ok; g += gridDim.x) {
-            int t0, t1;
-            group_range(g, t0, t1);
+        for (int w = blockIdx.x; w < num_items && ok; w += gridDim.x) {
+            int g, t0, t1, j0, j1;
+            item_range(w, g, t0, t1, j0, j1);
             if (t1 <= t0) continue;
             if (qn > 0) {   // the MMAs of the previous group have finished reading q
                 ok = mbar_wait(bar(LXB_QEMPTY), (qn - 1) & 1u, abort_flag, 13);
@@ -198,9 +215,9 @@ __global__ void __launch_bounds__(LX_THREADS, 1) mqa_logits_tc_kernel(const Logi
         const uint32_t q_lo = desc_lo(base + LX_Q_OFF, 16);
         uint32_t it = 0, qn = 0;
         bool ok = true;
-        for (int g = blockIdx.x; g < num_groups && ok; g += gridDim.x) {
-            int t0, t1;
-            group_range(g, t0, t1);
+        for (int w = blockIdx.x; w < num_items && ok; w += gridDim.x) {
+            int g, t0, t1, j0, j1;
+            item_range(w, g, t0, t1, j0, j1);
             if (t1 <= t0) continue;
             ok = mbar_wait_thread(bar(LXB_QFULL), qn & 1u, abort_flag, 15);
             if (!ok) break;
@@ -281,9 +298,19 @@ int launch_mqa_logits_tc(const uint8_t* q, const uint8_t* k, const float* k_scal
         if (r1 != CUDA_SUCCESS || r2 != CUDA_SUCCESS)
             return set_error(SMLA_E_DEVICE, "mqa_logits_tc_kernel: cuTensorMapEncodeTiled failed (%d, %d)", (int)r1, (int)r2);
     }
-    LogitsParams p{q, k, k_scale, weights, ks, ke, logits, status, s_q, num_heads, s_k, logits_stride};
     const int groups = (s_q + LX_QG - 1) / LX_QG;
-    const int grid = groups < sms[dev < 64 ? dev : 0] ? groups : sms[dev < 64 ? dev : 0];
+    const int nsm = sms[dev < 64 ? dev : 0];
+    const int tiles = (s_k + LX_KT - 1) / LX_KT;
+    // About eight work items per SM, so that the CTAs finish together: with few query groups the
+    // key tiles are cut into runs (at least 8 tiles long, so that the q load and the pipeline fill
+    // stay a small share).
+    int chunks = groups >= 8 * nsm ? 1 : (8 * nsm + groups - 1) / groups;
+    if (chunks > (tiles + 7) / 8) chunks = (tiles + 7) / 8;
+    if (chunks < 1) chunks = 1;
+    const int chunk_tiles = (tiles + chunks - 1) / chunks;
+    const int items = groups * ((tiles + chunk_tiles - 1) / chunk_tiles);
+    LogitsParams p{q, k, k_scale, weights, ks, ke, logits, status, s_q, num_heads, s_k, logits_stride, chunk_tiles};
+    const int grid = items < nsm ? items : nsm;
     mqa_logits_tc_kernel<<<grid, LX_THREADS, LX_SMEM, stream>>>(p, qmap, kmap);
     return check_launch("mqa_logits_tc_kernel");
 }

@@ -43,7 +43,8 @@ def topk_indices(logits: torch.Tensor, ks: Optional[torch.Tensor], ke: Optional[
                  k: int = 2048) -> torch.Tensor:
     """Per row, the column numbers of the k largest logits inside [ks, ke) as int32 [rows, k],
     padded with -1 when fewer than k candidates exist.  Ties at the k-th value go to the lowest
-    columns.  The order inside a row is not part of the contract (two ascending runs)."""
+    columns.  The order inside a row is a fixed function of the input but not ascending, and not
+    part of the contract.  Rows of any width."""
     require_cuda(logits, ks, ke)
     assert logits.dim() == 2 and logits.dtype == torch.float32 and logits.stride(1) == 1
     rows, cols = logits.shape

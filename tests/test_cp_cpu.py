@@ -66,3 +66,62 @@ def test_context_parallel_decomposition_two_gloo_ranks():
         mp.spawn(_rank_main, args=(2, port, ret), nprocs=2, join=True)
         assert ret["empty_part"], "token 2 has no entry on rank 1: its partial must be empty"
         assert ret["err"] < 2e-2 and ret["lse_err"] < 1e-5, dict(ret)   # bf16 partials: 2^-8 relative
+
+
+def _indexer_inputs(seed, s_q, h, s_k):
+    g = torch.Generator().manual_seed(seed)
+    q = torch.randn(s_q, h, 128, generator=g).to(torch.float8_e4m3fn)
+    kf = torch.randn(s_k, 128, generator=g)
+    k_scale = kf.abs().amax(dim=1) / 448.0
+    k = (kf / k_scale.unsqueeze(1)).to(torch.float8_e4m3fn)
+    w = torch.randn(s_q, h, generator=g) * 0.1
+    ks = torch.tensor([0, 40, 300, 0], dtype=torch.int32)[:s_q]
+    ke = torch.tensor([s_k, 200, s_k - 3, 100], dtype=torch.int32)[:s_q]
+    return q, k, k_scale, w, ks, ke
+
+
+def test_local_window():
+    ks = torch.tensor([0, 40, 300, 0, 500], dtype=torch.int32)
+    ke = torch.tensor([512, 200, 509, 100, 500], dtype=torch.int32)
+    a, b = cp.local_window(ks, ke, 256, 512)
+    assert a.tolist() == [0, 0, 44, 0, 244] and b.tolist() == [256, 0, 253, 0, 244]
+    a, b = cp.local_window(ks, ke, 0, 256)
+    assert a.tolist() == [0, 40, 256, 0, 256] and b.tolist() == [256, 200, 256, 100, 256]
+
+
+def _indexer_rank_main(rank, world, port, ret):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    s_q, h, s_k, k = 4, 8, 512, 48
+    q, key, k_scale, w, ks, ke = _indexer_inputs(31, s_q, h, s_k)
+    lo, hi = cp.shard_context(s_k, rank, world)
+    ks_l, ke_l = cp.local_window(ks, ke, lo, hi)
+    logits = orc.mqa_logits_ref(q, key[lo:hi], k_scale[lo:hi], w, ks_l, ke_l)
+    local = orc.topk_ref(logits, k)
+    vals = torch.where(local >= 0, torch.gather(logits, 1, local.clamp(min=0).long()), torch.tensor(float("-inf")))
+    pos = torch.where(local >= 0, local + lo, local)
+    v_all = [torch.empty_like(vals) for _ in range(world)]
+    p_all = [torch.empty_like(pos) for _ in range(world)]
+    dist.all_gather(v_all, vals)
+    dist.all_gather(p_all, pos)
+    v, p = torch.cat(v_all, 1), torch.cat(p_all, 1)
+    pick = orc.topk_ref(v, k)
+    merged = torch.where(pick >= 0, torch.gather(p, 1, pick.clamp(min=0).long()), pick)
+    if rank == 0:
+        full = orc.mqa_logits_ref(q, key, k_scale, w, ks, ke)
+        want = orc.topk_ref(full, k)
+        ret["same_sets"] = all(set(merged[i][merged[i] >= 0].tolist()) == set(want[i][want[i] >= 0].tolist())
+                               for i in range(s_q))
+        ret["counts"] = [int((merged[i] >= 0).sum()) for i in range(s_q)]
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_indexer_candidate_merge_two_gloo_ranks():
+    """Per-shard top-k + merge of the candidates gives the top-k of the whole context."""
+    port = 30500 + os.getpid() % 1000
+    with mp.Manager() as m:
+        ret = m.dict()
+        mp.spawn(_indexer_rank_main, args=(2, port, ret), nprocs=2, join=True)
+        assert ret["same_sets"], dict(ret)
+        assert ret["counts"] == [48, 48, 48, 48]

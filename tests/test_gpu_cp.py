@@ -44,6 +44,81 @@ def test_cp_pieces_on_one_gpu(world, impl):
         H.compare_lse(lse, ref_lse, H.TC_LSE)
 
 
+def _indexer_case(seed, s_q, h, s_k):
+    g = torch.Generator().manual_seed(seed)
+    q = torch.randn(s_q, h, 128, generator=g).to(torch.float8_e4m3fn)
+    kf = torch.randn(s_k, 128, generator=g)
+    k_scale = kf.abs().amax(dim=1) / 448.0
+    k = (kf / k_scale.unsqueeze(1)).to(torch.float8_e4m3fn)
+    w = torch.randn(s_q, h, generator=g) * 0.1
+    ks = torch.zeros(s_q, dtype=torch.int32)
+    ke = (s_k - s_q + 1 + torch.arange(s_q)).to(torch.int32)
+    return q, k, k_scale, w, ks, ke
+
+
+def _check_selection(got, full_logits, k):
+    """got [T, k] int32: every row must hold min(k, finite entries) distinct columns whose logits
+    are not below the k-th largest, with every strictly larger one present."""
+    for r in range(got.shape[0]):
+        g = got[r][got[r] >= 0]
+        n = int(min(k, int(torch.isfinite(full_logits[r]).sum())))
+        assert g.numel() == n and torch.unique(g).numel() == n
+        if n:
+            thr = torch.topk(full_logits[r], n).values[-1]
+            vals = full_logits[r][g.long()]
+            assert float(vals.min()) >= float(thr)
+            assert int((full_logits[r] > thr).sum()) == int((vals > thr).sum())
+
+
+@pytest.mark.parametrize("world", [2, 4])
+def test_indexer_cp_pieces_on_one_gpu(world):
+    """Per-shard logits + top-k, candidates side by side, merge: the distributed selection without
+    the collective, against the oracle's logits over the whole context."""
+    from sparse_mla_sm120_b200 import cp
+    dev = torch.device("cuda:0")
+    s_q, h, s_k, k = 6, 64, 4096, 256
+    q, key, k_scale, w, ks, ke = _indexer_case(41, s_q, h, s_k)
+    ks[1], ke[1] = 1500, 1700          # fewer than k candidates, inside one shard (world 2) / two shards (world 4)
+    ks[2], ke[2] = 900, 3300
+    full = H.orc.mqa_logits_ref(q, key, k_scale, w, ks, ke)
+    vals, pos = [], []
+    for r in range(world):
+        lo, hi = cp.shard_context(s_k, r, world)
+        v, p = cp.local_candidates(q.to(dev), key[lo:hi].contiguous().to(dev), k_scale[lo:hi].contiguous().to(dev),
+                                   w.to(dev), ks.to(dev), ke.to(dev), lo, hi, k)
+        vals.append(v); pos.append(p)
+    got = cp.merge_candidates(torch.cat(vals, 1), torch.cat(pos, 1), k).cpu()
+    _check_selection(got, full, k)
+    assert int((got[1] >= 0).sum()) == 200
+
+
+def test_indexed_decode_pipeline_one_gpu():
+    """Indexer -> top-k -> attention in one call; the rows it selected are checked against the
+    oracle's logits, the attention output against the oracle over those rows."""
+    from sparse_mla_sm120_b200 import pipeline
+    dev = torch.device("cuda:0")
+    case = make_case(43, 6, 128, 256, 48, invalid_tail=0.0)
+    s_k = case["packed"].shape[0] * 64
+    q, key, k_scale, w, ks, ke = _indexer_case(44, 6, 64, s_k)
+    ke[3] = 100                          # fewer candidates than topk: -1 padding reaches the attention
+    out, lse, rows = pipeline.sparse_mla_indexed_decode_fwd(
+        case["q"].to(dev), case["packed"].to(dev), q.to(dev), key.to(dev), k_scale.to(dev), w.to(dev), ks.to(dev),
+        ke.to(dev), case["sm_scale"], topk=256)
+    torch.cuda.synchronize()
+    _check_selection(rows.cpu(), H.orc.mqa_logits_ref(q, key, k_scale, w, ks, ke), 256)
+    case["indices"] = rows.cpu()
+    ref_out, ref_lse = oracle_attn(case)
+    H.compare_out(out, ref_out, H.TC_ABS, H.TC_REL, H.TC_COS)
+    H.compare_lse(lse, ref_lse, H.TC_LSE)
+    # through a page table that reverses the pages
+    pages = s_k // 64
+    table = torch.arange(pages - 1, -1, -1, dtype=torch.int32).repeat(6, 1)
+    mapped = pipeline.positions_to_rows(rows, table.to(dev), 64).cpu()
+    r = rows.cpu()
+    want = torch.where(r >= 0, (pages - 1 - r // 64) * 64 + r % 64, r)
+    assert torch.equal(mapped, want.to(torch.int32))
+
+
 _RANK_SCRIPT = r'''
 import os, sys, torch, torch.distributed as dist
 sys.path.insert(0, os.environ["SMLA_ROOT"]); sys.path.insert(0, os.path.join(os.environ["SMLA_ROOT"], "tests"))
@@ -58,6 +133,32 @@ lo, hi = cp.shard_context(rows, rank, world)
 kv_local = case["packed"].view(-1, 656)[lo:hi].reshape(-1, 64, 1, 656).to(dev)
 out, lse = cp.sparse_mla_decode_cp_fwd(case["q"].to(dev), kv_local, case["indices"].to(dev), case["sm_scale"], lo, hi)
 torch.cuda.synchronize()
+ref_out, ref_lse = H.oracle_attn(case)
+H.compare_out(out, ref_out, H.TC_ABS, H.TC_REL, H.TC_COS)
+H.compare_lse(lse, ref_lse, H.TC_LSE)
+# indexer -> distributed top-k -> context-parallel attention
+g = torch.Generator().manual_seed(47)
+qi = torch.randn(4, 64, 128, generator=g).to(torch.float8_e4m3fn)
+kf = torch.randn(rows, 128, generator=g)
+k_scale = kf.abs().amax(dim=1) / 448.0
+ki = (kf / k_scale.unsqueeze(1)).to(torch.float8_e4m3fn)
+w = torch.randn(4, 64, generator=g) * 0.1
+ks = torch.tensor([0, 100, 0, 3000], dtype=torch.int32); ke = torch.tensor([rows, rows - 5, 700, 3100], dtype=torch.int32)
+out, lse, sel = cp.sparse_mla_indexed_decode_cp_fwd(case["q"].to(dev), kv_local, qi.to(dev), ki[lo:hi].contiguous().to(dev),
+    k_scale[lo:hi].contiguous().to(dev), w.to(dev), ks.to(dev), ke.to(dev), case["sm_scale"], lo, hi, topk=1024)
+torch.cuda.synchronize()
+sel = sel.cpu()
+full = H.orc.mqa_logits_ref(qi, ki, k_scale, w, ks, ke)
+for r in range(4):
+    got = sel[r][sel[r] >= 0]
+    n = min(1024, int(torch.isfinite(full[r]).sum()))
+    assert got.numel() == n and torch.unique(got).numel() == n, (r, got.numel(), n)
+    thr = torch.topk(full[r], n).values[-1]
+    assert float(full[r][got.long()].min()) >= float(thr)
+gathered = [torch.empty_like(sel) for _ in range(world)]
+dist.all_gather_object(gathered, sel)
+assert all(torch.equal(gathered[0], t) for t in gathered), "ranks disagree on the selection"
+case["indices"] = sel
 ref_out, ref_lse = H.oracle_attn(case)
 H.compare_out(out, ref_out, H.TC_ABS, H.TC_REL, H.TC_COS)
 H.compare_lse(lse, ref_lse, H.TC_LSE)
