@@ -6,7 +6,6 @@
 // followed by a per-row top-k, and the split of a global index list into one GPU's shard.
 #include <cstdint>
 
-#include <cstdio>
 #include "common.cuh"
 
 namespace smla {
@@ -216,30 +215,35 @@ __device__ __forceinline__ void pick_bin(const int* hist, int need, int lane, in
 // One-read selection.  A sample of the row (512 runs of 8 neighbouring logits, one 32-byte sector
 // each, evenly spread) gives a threshold that, with a margin of four standard deviations of the
 // estimate, lets through somewhat more than k entries (about 1.4 k for k = 2048 out of 65536).
-// The single pass over the row then appends the column of every entry at or above the threshold
-// to a candidate list in shared memory, and the exact k best are chosen among the few thousand
-// candidates (their logits are read again, into registers): radix select on the full 32-bit keys,
-// ties at the k-th key by lowest column.  Rows whose window has at most TS_DIRECT columns skip the
-// sample and list every column.  Any width of row is served (nothing but the candidates is kept
-// on chip), and several CTAs fit an SM, so the read of one row overlaps the selection of another.
-// When the guess fails -- fewer than k candidates, a list overflows (heavy ties, logits that
-// cluster far more than the sample saw) -- the row is marked for the multi-pass kernel.
-// The pass over the row is bound by instruction issue: it compares the logits as floats (one
-// instruction per entry; NaNs never become candidates) and runs one round of warp votes per 256
-// entries.
+// The single pass over the row then lists the column of every entry at or above the threshold
+// in shared memory, and the exact k best are chosen among the few thousand candidates: their
+// keys (read again, the row is still in the L2) go into one histogram of 4096 bins laid over the
+// range the candidates span, a parallel suffix sum finds the bin of the k-th, and the handful of
+// entries in that bin are ranked by (key, lower column first).  Rows whose window has at most
+// TS_DIRECT columns skip the sample and list every column.  Any width of row is served (nothing
+// but the candidates is kept on chip), and two CTAs fit an SM, so the read of one row overlaps
+// the selection of another.  When the guess fails -- fewer than k candidates, a list overflows
+// (heavy ties, logits that cluster far more than the sample saw), too many entries in the bin of
+// the k-th -- the row is marked for the multi-pass kernel.
 //
-// Order of the output: every warp owns the 128-column blocks warp, warp + 16, ... of the row and
-// appends to its own list in block order, lane order, column order; the lists are written out one
-// after the other.  The order is therefore a fixed function of the input (no atomics decide it),
-// though not ascending.
+// The pass over the row is kept free of warp-wide votes: a lane compares its logits as floats
+// (NaNs never become candidates) and only notes a bit per entry; after 65536 columns the lanes of
+// a warp exchange their counts once and every lane appends its own columns.
+//
+// Order of the output: warp w owns the 128-column blocks w, w + 16, ... of the row; its list holds,
+// per stretch of 65536 columns, the candidates of lane 0, then of lane 1, ... each in column
+// order; the lists are written out one after the other.  The order is a fixed function of the
+// input (no atomics decide it), though not ascending.
 constexpr int TS_THREADS = 512;
 constexpr int TS_WARPS = TS_THREADS / 32;
 constexpr int TS_LIST = 512;               // candidates per warp
-constexpr int TS_PER_LANE = TS_LIST / 32;
 constexpr int TS_SAMPLE = 4096;            // sampled logits: 512 runs of 8
-constexpr int TS_EQ = 1024;                // entries equal to the k-th key that are ranked by column
+constexpr int TS_EQ = 1024;                // entries in the bin of the k-th key, ranked one against the other
+constexpr int TS_BINS = 4096;
 constexpr int TS_DIRECT = TS_WARPS * TS_LIST - 128;   // windows up to this size need no threshold
 constexpr int TS_KMAX = 4096;              // largest k (the lists hold 8192)
+constexpr int TS_ROUNDS = 8;               // rounds of four blocks per warp between two appends
+constexpr int TS_SMEM = TS_WARPS * TS_LIST * 8 + TS_BINS * 4 + TS_EQ * 8;
 
 __device__ __forceinline__ float4 load_row4(const float* __restrict__ x, int j, int num_cols, bool vec_ok) {
     if (vec_ok && j + 3 < num_cols) return *reinterpret_cast<const float4*>(x + j);
@@ -255,27 +259,19 @@ __device__ __forceinline__ float key_to_float(uint32_t key) {      // inverse of
     return __uint_as_float((key & 0x80000000u) ? (key ^ 0x80000000u) : ~key);
 }
 
-// Adds one to hist[bin] for every lane with `on`; the lanes that share the bin of the first such
-// lane (nearly all of them while the radix select is at its leading digits) share one atomic.
-__device__ __forceinline__ void hist_add(int* hist, bool on, uint32_t bin, int lane) {
-    const uint32_t mm = __ballot_sync(0xffffffffu, on);
-    if (mm == 0) return;
-    const int first = __ffs(mm) - 1;
-    const uint32_t lead = __shfl_sync(0xffffffffu, bin, first);
-    const uint32_t same = __ballot_sync(0xffffffffu, on && bin == lead);
-    if (lane == first) atomicAdd(&hist[lead], __popc(same));
-    if (on && bin != lead) atomicAdd(&hist[bin], 1);
-}
-
 __global__ void __launch_bounds__(TS_THREADS, 2)
 topk_select_kernel(const float* __restrict__ logits, const int32_t* __restrict__ ks,
                    const int32_t* __restrict__ ke, int32_t* __restrict__ out, int num_cols,
                    int64_t logits_stride, int k) {
-    __shared__ __align__(16) int lists[TS_WARPS * TS_LIST];   // candidate columns
-    __shared__ int hist[2][256];
+    extern __shared__ __align__(16) uint8_t ts_smem[];
+    int* lists = reinterpret_cast<int*>(ts_smem);                               // [TS_WARPS][TS_LIST] candidate columns
+    uint32_t* keys = reinterpret_cast<uint32_t*>(ts_smem) + TS_WARPS * TS_LIST; // their keys
+    int* hist = reinterpret_cast<int*>(keys + TS_WARPS * TS_LIST);              // [TS_BINS]
+    uint32_t* eq_key = reinterpret_cast<uint32_t*>(hist + TS_BINS);             // [TS_EQ]
+    int* eq_col = reinterpret_cast<int*>(eq_key + TS_EQ);                       // [TS_EQ]
     __shared__ int sel_bin, sel_need, n_eq_s;
-    __shared__ int cw[TS_WARPS], cc[TS_WARPS];
-    __shared__ int eq_col[TS_EQ];
+    __shared__ uint32_t kmin_s, kmax_s;
+    __shared__ int cw[TS_WARPS], cc[TS_WARPS], wsum[TS_WARPS];
 
     const int row = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const float* x = logits + (size_t)row * logits_stride;
@@ -290,19 +286,12 @@ topk_select_kernel(const float* __restrict__ logits, const int32_t* __restrict__
     const int span = hi - lo;
     const uint32_t below = (1u << lane) - 1u;
 
-#ifdef SMLA_TK_TRACE
-    long long tk_t[16]; int tk_n = 0;
-#define TK_MARK() do { __syncthreads(); tk_t[tk_n++] = clock64(); } while (0)
-#else
-#define TK_MARK() do {} while (0)
-#endif
-    TK_MARK();
-    // ---- threshold from a sample
+    // ---- threshold from a sample (two 256-bin histograms at the start of hist[])
     uint32_t t_lo = NEG_INF_KEY + 1u;          // entries with key >= t_lo become candidates
     const bool sampled = (hi - base) > TS_DIRECT;
-    for (int b = tid; b < 512; b += TS_THREADS) (&hist[0][0])[b] = 0;
-    if (tid == 0) n_eq_s = 0;
+    if (tid == 0) { n_eq_s = 0; kmin_s = 0xffffffffu; kmax_s = 0u; }
     if (sampled) {
+        hist[tid] = 0;                         // TS_THREADS == 2 * 256
         __syncthreads();
         const int run_stride = span / (TS_SAMPLE / 8);   // >= 15: the runs of 8 do not overlap
         uint32_t h[TS_SAMPLE / TS_THREADS];
@@ -312,78 +301,91 @@ topk_select_kernel(const float* __restrict__ logits, const int32_t* __restrict__
             h[r] = order_key(x[lo + (i >> 3) * run_stride + (i & 7)]) >> 16;
         }
 #pragma unroll
-        for (int r = 0; r < TS_SAMPLE / TS_THREADS; ++r) hist_add(hist[0], h[r] > VALID16, h[r] >> 8, lane);
+        for (int r = 0; r < TS_SAMPLE / TS_THREADS; ++r)
+            if (h[r] > VALID16) atomicAdd(&hist[h[r] >> 8], 1);
         __syncthreads();
         // expected rank of the row's k-th entry inside the sample, plus four standard deviations
         const float m = (float)k * (float)TS_SAMPLE / (float)span;
         const int need_s = (int)(m + 4.f * sqrtf(m)) + 4;
-        if (warp == 0) pick_bin(hist[0], need_s, lane, &sel_bin, &sel_need);
+        if (warp == 0) pick_bin(hist, need_s, lane, &sel_bin, &sel_need);
         __syncthreads();
         if (sel_bin >= 0) {
             const uint32_t b1 = (uint32_t)sel_bin;
             const int need1 = sel_need;
 #pragma unroll
             for (int r = 0; r < TS_SAMPLE / TS_THREADS; ++r)
-                if (h[r] > VALID16 && (h[r] >> 8) == b1) atomicAdd(&hist[1][h[r] & 255u], 1);
+                if (h[r] > VALID16 && (h[r] >> 8) == b1) atomicAdd(&hist[256 + (h[r] & 255u)], 1);
             __syncthreads();
-            if (warp == 0) pick_bin(hist[1], need1, lane, &sel_bin, &sel_need);
+            if (warp == 0) pick_bin(hist + 256, need1, lane, &sel_bin, &sel_need);
             __syncthreads();
             t_lo = max(((b1 << 8) | (uint32_t)sel_bin) << 16, NEG_INF_KEY + 1u);
         }
     }
     const float t_f = key_to_float(t_lo);
 
-    TK_MARK();
-    // ---- the one pass over the row: candidate columns to the warp's list.  Two blocks (256
-    // entries, eight per lane) per round of votes; the loads of the next four blocks are issued
-    // before the current four are looked at.
+    // ---- the one pass over the row
     const int nblk = (hi - base + 127) >> 7;
     int* mine = lists + warp * TS_LIST;
+    uint32_t* mykeys = keys + warp * TS_LIST;
     int cnt = 0;                               // entries this warp has met (beyond TS_LIST they are only counted)
     const float4 none = make_float4(-INFINITY, -INFINITY, -INFINITY, -INFINITY);
-    auto load_blk = [&](int blk) -> float4 {
+    auto load_blk = [&](int blk) -> float4 {   // blocks past the end read as -inf
         return (blk < nblk) ? load_row4(x, base + blk * 128 + 4 * lane, num_cols, vec_ok) : none;
     };
-    float4 f[4], g[4];
+    for (int stretch = 0; stretch < nblk; stretch += TS_ROUNDS * 4 * TS_WARPS) {
+        uint32_t marks[TS_ROUNDS];             // bit 4u + e: entry e of the lane's float4 in block u of the round
+        float4 f[4], g[4];
 #pragma unroll
-    for (int u = 0; u < 4; ++u) f[u] = load_blk(warp + u * TS_WARPS);
-    for (int blk0 = warp; blk0 < nblk; blk0 += 4 * TS_WARPS) {
+        for (int u = 0; u < 4; ++u) f[u] = load_blk(stretch + warp + u * TS_WARPS);
 #pragma unroll
-        for (int u = 0; u < 4; ++u) g[u] = load_blk(blk0 + (4 + u) * TS_WARPS);
+        for (int r = 0; r < TS_ROUNDS; ++r) {
+            const int blk0 = stretch + r * 4 * TS_WARPS + warp;
+            if (r + 1 < TS_ROUNDS) {           // the next round's loads go out before this round is looked at
 #pragma unroll
-        for (int u = 0; u < 4; u += 2) {
-            const int blk_a = blk0 + u * TS_WARPS, blk_b = blk_a + TS_WARPS;     // blocks past the end hold -inf
-            const int ja = base + blk_a * 128 + 4 * lane, jb = ja + TS_WARPS * 128;
-            const float v[8] = {f[u].x, f[u].y, f[u].z, f[u].w, f[u + 1].x, f[u + 1].y, f[u + 1].z, f[u + 1].w};
+                for (int u = 0; u < 4; ++u) g[u] = load_blk(blk0 + (4 + u) * TS_WARPS);
+            }
             uint32_t m = 0;
 #pragma unroll
-            for (int e = 0; e < 8; ++e) m |= (uint32_t)(v[e] >= t_f) << e;
-            if (blk_a == 0 || blk_b >= nblk - 1) {                               // (uniform) the window's edges
+            for (int u = 0; u < 4; ++u) {
+                m |= (uint32_t)(f[u].x >= t_f) << (4 * u) | (uint32_t)(f[u].y >= t_f) << (4 * u + 1) |
+                     (uint32_t)(f[u].z >= t_f) << (4 * u + 2) | (uint32_t)(f[u].w >= t_f) << (4 * u + 3);
+            }
+            if (m != 0 && (blk0 == 0 || blk0 + 3 * TS_WARPS >= nblk - 1)) {       // the window's edges
 #pragma unroll
-                for (int e = 0; e < 8; ++e) {
-                    const int j = (e < 4 ? ja : jb) + (e & 3);
-                    if (j < lo || j >= hi) m &= ~(1u << e);
+                for (int b = 0; b < 16; ++b) {
+                    const int j = base + (blk0 + (b >> 2) * TS_WARPS) * 128 + 4 * lane + (b & 3);
+                    if (j < lo || j >= hi) m &= ~(1u << b);
                 }
             }
-            if (__ballot_sync(0xffffffffu, m != 0) == 0) continue;
-            const int c = __popc(m);
-            const uint32_t b0 = __ballot_sync(0xffffffffu, c & 1), b1 = __ballot_sync(0xffffffffu, c & 2),
-                           b2 = __ballot_sync(0xffffffffu, c & 4), b3 = __ballot_sync(0xffffffffu, c & 8);
-            int at = cnt + __popc(b0 & below) + 2 * __popc(b1 & below) + 4 * __popc(b2 & below) + 8 * __popc(b3 & below);
+            marks[r] = m;
 #pragma unroll
-            for (int e = 0; e < 8; ++e) {
-                if ((m >> e) & 1u) {
-                    if (at < TS_LIST) mine[at] = (e < 4 ? ja : jb) + (e & 3);
-                    ++at;
-                }
-            }
-            cnt += __popc(b0) + 2 * __popc(b1) + 4 * __popc(b2) + 8 * __popc(b3);
+            for (int u = 0; u < 4; ++u) f[u] = g[u];
         }
+        int c = 0;
 #pragma unroll
-        for (int u = 0; u < 4; ++u) f[u] = g[u];
+        for (int r = 0; r < TS_ROUNDS; ++r) c += __popc(marks[r]);
+        int incl = c;                          // inclusive prefix over the lanes
+#pragma unroll
+        for (int d = 1; d < 32; d <<= 1) {
+            const int t = __shfl_up_sync(0xffffffffu, incl, d);
+            if (lane >= d) incl += t;
+        }
+        int at = cnt + incl - c;
+#pragma unroll
+        for (int r = 0; r < TS_ROUNDS; ++r) {
+            uint32_t m = marks[r];
+            const int j0 = base + (stretch + r * 4 * TS_WARPS + warp) * 128 + 4 * lane;
+            while (m) {
+                const int b = __ffs(m) - 1;
+                m &= m - 1;
+                if (at < TS_LIST) mine[at] = j0 + (b >> 2) * (TS_WARPS * 128) + (b & 3);
+                ++at;
+            }
+        }
+        cnt += __shfl_sync(0xffffffffu, incl, 31);
     }
-    TK_MARK();
     if (lane == 0) cw[warp] = cnt;
+    for (int b = tid; b < TS_BINS; b += TS_THREADS) hist[b] = 0;
     __syncthreads();
     int total = 0;
     bool overflow = false;
@@ -393,53 +395,62 @@ topk_select_kernel(const float* __restrict__ logits, const int32_t* __restrict__
         if (tid == 0) o[0] = TK_REDO;
         return;
     }
-
-    // ---- the candidates of this warp's list, TS_PER_LANE per lane, into registers
     const int mycount = cnt;
-    const int nr = (mycount + 31) >> 5;        // rounds in use (uniform in the warp)
-    int col[TS_PER_LANE];
-    uint32_t key[TS_PER_LANE];
-#pragma unroll
-    for (int r = 0; r < TS_PER_LANE; ++r) {
-        const bool in = lane + 32 * r < mycount;
-        col[r] = in ? mine[lane + 32 * r] : -1;
-        key[r] = in ? order_key(x[col[r]]) : 0u;
-    }
-
-    // ---- the k-th largest key among the candidates (radix select, 8 bits per pass)
-    uint32_t kth = 0;                          // chosen: key > kth, and need_eq of the entries with key == kth
-    int need_eq = 0;
     const bool take_all = total <= k;
+    int thr_bin = -1, need_eq = 0, shift = 0;  // chosen: bin > thr_bin, and need_eq of the entries of bin thr_bin
+    uint32_t kmin = 0;
     if (!take_all) {
-        uint32_t prefix = 0, prefix_mask = 0;
-        int need = k;
-#pragma unroll
-        for (int pass = 0; pass < 4; ++pass) {
-            const int shift = 24 - 8 * pass;
-            int* hp = hist[pass & 1];
-            if (pass >= 2 || sampled) {        // used two passes ago, or by the sample (both were cleared at the start)
-                for (int b = tid; b < 256; b += TS_THREADS) hp[b] = 0;
-                __syncthreads();
-            }
-#pragma unroll
-            for (int r = 0; r < TS_PER_LANE; ++r) {
-                if (r < nr) hist_add(hp, col[r] >= 0 && (key[r] & prefix_mask) == prefix, (key[r] >> shift) & 255u, lane);
-            }
-            __syncthreads();
-            if (warp == 0) pick_bin(hp, need, lane, &sel_bin, &sel_need);
-            __syncthreads();
-            prefix |= (uint32_t)sel_bin << shift;      // sel_bin >= 0: at least `need` entries match the prefix
-            prefix_mask |= 255u << shift;
-            need = sel_need;
+        // ---- keys of the candidates, and the range they span
+        uint32_t vmin = 0xffffffffu, vmax = 0u;
+#pragma unroll 4
+        for (int i = lane; i < mycount; i += 32) {
+            const uint32_t key = order_key(x[mine[i]]);
+            mykeys[i] = key;
+            vmin = min(vmin, key); vmax = max(vmax, key);
         }
-        kth = prefix;
-        need_eq = need;
-        // the entries equal to the k-th key, to be ranked by column
+        vmin = __reduce_min_sync(0xffffffffu, vmin);
+        vmax = __reduce_max_sync(0xffffffffu, vmax);
+        if (lane == 0 && mycount > 0) { atomicMin(&kmin_s, vmin); atomicMax(&kmax_s, vmax); }
+        __syncthreads();
+        kmin = kmin_s;
+        const uint32_t range = kmax_s - kmin;
+        shift = max(0, 20 - (int)__clz(range | 1u));          // (range >> shift) < TS_BINS
+        for (int i = lane; i < mycount; i += 32) atomicAdd(&hist[(mykeys[i] - kmin) >> shift], 1);
+        __syncthreads();
+        // ---- the bin of the k-th: suffix sums over the bins, eight bins per thread
+        {
+            int hb[8], s = 0;
 #pragma unroll
-        for (int r = 0; r < TS_PER_LANE; ++r) {
-            if (col[r] >= 0 && key[r] == kth) {
+            for (int i = 0; i < 8; ++i) { hb[i] = hist[8 * tid + i]; s += hb[i]; }
+            int suf = s;                       // sum over the lanes >= this one
+#pragma unroll
+            for (int d = 1; d < 32; d <<= 1) {
+                const int t = __shfl_down_sync(0xffffffffu, suf, d);
+                if (lane + d < 32) suf += t;
+            }
+            if (lane == 0) wsum[warp] = suf;
+            __syncthreads();
+            int above = suf - s;
+#pragma unroll
+            for (int w = 0; w < TS_WARPS; ++w) above += (w > warp) ? wsum[w] : 0;
+            if (above < k && above + s >= k) {  // exactly one thread: total > k
+                int cum = above, b = 7;
+                for (; b > 0; --b) {
+                    if (cum + hb[b] >= k) break;
+                    cum += hb[b];
+                }
+                sel_bin = 8 * tid + b; sel_need = k - cum;
+            }
+            __syncthreads();
+        }
+        thr_bin = sel_bin;
+        need_eq = sel_need;
+        // ---- the entries of that bin, to be ranked one against the other
+        for (int i = lane; i < mycount; i += 32) {
+            const uint32_t key = mykeys[i];
+            if ((int)((key - kmin) >> shift) == thr_bin) {
                 const int at = atomicAdd(&n_eq_s, 1);
-                if (at < TS_EQ) eq_col[at] = col[r];
+                if (at < TS_EQ) { eq_key[at] = key; eq_col[at] = mine[i]; }
             }
         }
         __syncthreads();
@@ -448,45 +459,36 @@ topk_select_kernel(const float* __restrict__ logits, const int32_t* __restrict__
             return;
         }
     }
-    TK_MARK();
     const int n_eq = take_all ? 0 : n_eq_s;
+    auto chosen = [&](int i) -> bool {
+        if (take_all) return true;
+        const uint32_t key = mykeys[i];
+        const int bin = (int)((key - kmin) >> shift);
+        if (bin != thr_bin) return bin > thr_bin;
+        if (need_eq >= n_eq) return true;
+        const int c = mine[i];
+        int rank = 0;                          // entries of the bin that go first: larger key, or equal key and lower column
+        for (int j = 0; j < n_eq; ++j) rank += (eq_key[j] > key) || (eq_key[j] == key && eq_col[j] < c);
+        return rank < need_eq;
+    };
     // ---- write: every warp its own list, in list order
-    uint32_t votes[TS_PER_LANE];
     int nsel = 0;
-#pragma unroll
-    for (int r = 0; r < TS_PER_LANE; ++r) {
-        bool ch = false;
-        if (col[r] >= 0) {
-            if (take_all || key[r] > kth) ch = true;
-            else if (key[r] == kth) {
-                if (need_eq >= n_eq) ch = true;
-                else {
-                    int rank = 0;              // equal entries in lower columns
-                    for (int i = 0; i < n_eq; ++i) rank += eq_col[i] < col[r];
-                    ch = rank < need_eq;
-                }
-            }
-        }
-        votes[r] = (r < nr) ? __ballot_sync(0xffffffffu, ch) : 0u;
-        nsel += __popc(votes[r]);
+    for (int i0 = 0; i0 < mycount; i0 += 32) {
+        const bool ch = (i0 + lane < mycount) && chosen(i0 + lane);
+        nsel += __popc(__ballot_sync(0xffffffffu, ch));
     }
     if (lane == 0) cc[warp] = nsel;
     __syncthreads();
     int off = 0, filled = 0;
 #pragma unroll
     for (int w = 0; w < TS_WARPS; ++w) { if (w < warp) off += cc[w]; filled += cc[w]; }
-#pragma unroll
-    for (int r = 0; r < TS_PER_LANE; ++r) {
-        if ((votes[r] >> lane) & 1u) o[off + __popc(votes[r] & below)] = col[r];
-        off += __popc(votes[r]);
+    for (int i0 = 0; i0 < mycount; i0 += 32) {
+        const bool ch = (i0 + lane < mycount) && chosen(i0 + lane);
+        const uint32_t mc = __ballot_sync(0xffffffffu, ch);
+        if (ch) o[off + __popc(mc & below)] = mine[i0 + lane];
+        off += __popc(mc);
     }
     for (int r = filled + tid; r < k; r += TS_THREADS) o[r] = -1;
-#ifdef SMLA_TK_TRACE
-    TK_MARK();
-    if (tid == 0 && row == 0)
-        printf("select: sample %lld pass %lld select %lld write %lld (cand %d, eq %d)\n", tk_t[1] - tk_t[0], tk_t[2] - tk_t[1],
-               tk_t[3] - tk_t[2], tk_t[4] - tk_t[3], total, n_eq);
-#endif
 }
 
 // ---------------------------------------------------------------- context-parallel partition
@@ -542,7 +544,12 @@ int launch_topk(const float* logits, const int32_t* ks, const int32_t* ke, int32
     static bool attr_set[64] = {};
     int dev = 0;
     cudaGetDevice(&dev);
-    topk_select_kernel<<<num_rows, TS_THREADS, 0, stream>>>(logits, ks, ke, out, num_cols, logits_stride, k);
+    if (dev < 64 && !attr_set[dev]) {
+        const cudaError_t e = cudaFuncSetAttribute(topk_select_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, TS_SMEM);
+        if (e != cudaSuccess) return set_error((int)e, "topk_select_kernel: shared memory: %s", cudaGetErrorString(e));
+        attr_set[dev] = true;
+    }
+    topk_select_kernel<<<num_rows, TS_THREADS, TS_SMEM, stream>>>(logits, ks, ke, out, num_cols, logits_stride, k);
     if (const int rc = check_launch("topk_select_kernel")) return rc;
     // rows the one-read kernel gave up on (it marks them) are redone by the multi-pass kernel
     topk_kernel<<<num_rows, TK_THREADS, 0, stream>>>(logits, ks, ke, out, num_cols, logits_stride, k, 1);

@@ -180,6 +180,51 @@ def test_topk_many_ties_and_wide_rows():
                 assert torch.equal(torch.sort(tied).values, all_tied[:tied.numel()].to(torch.int32))
 
 
+def _check_topk_rows(got, masked, k):
+    for r in range(masked.shape[0]):
+        g = got[r][got[r] >= 0]
+        n = int(min(k, int(torch.isfinite(masked[r]).sum())))
+        assert g.numel() == n and torch.all(got[r][n:] == -1), (r, g.numel(), n)
+        assert torch.unique(g).numel() == n
+        if n:
+            thr = torch.topk(masked[r], n).values[-1]
+            vals = masked[r][g.long()]
+            assert float(vals.min()) >= float(thr)
+            assert int((masked[r] > thr).sum()) == int((vals > thr).sum())
+
+
+def test_topk_one_read_paths():
+    """The one-read kernel's branches: several stretches of 65536 columns with ragged window
+    edges, logits clustered at the end of the row, -inf inside the window (so many that the
+    sampled guess fails and the multi-pass kernel takes over), a row pointer that is not
+    16-byte aligned, and the same input twice (the order of the output is reproducible)."""
+    from sparse_mla_sm120_b200 import indexer
+    torch.manual_seed(9)
+    rows, cols, k = 5, 200000, 2048
+    logits = torch.randn(rows, cols)
+    logits[1, -5000:] += 3.0                                     # the recent tokens dominate
+    logits[2, torch.rand(cols) < 0.5] = float("-inf")            # half of the window is masked inside
+    logits[3, torch.rand(cols) < 0.995] = float("-inf")          # fewer than k finite entries
+    logits[4] = torch.linspace(-1.0, 1.0, cols)                  # monotone: the top-k is the tail
+    ks = torch.tensor([777, 0, 13, 0, 5], dtype=torch.int32)
+    ke = torch.tensor([199001, cols, cols - 1, cols, cols - 3], dtype=torch.int32)
+    masked = logits.clone()
+    j = torch.arange(cols).unsqueeze(0)
+    masked[(j < ks.view(-1, 1)) | (j >= ke.view(-1, 1))] = float("-inf")
+    dev_logits = masked.to(DEV)
+    got = indexer.topk_indices(dev_logits, ks.to(DEV), ke.to(DEV), k)
+    again = indexer.topk_indices(dev_logits, ks.to(DEV), ke.to(DEV), k)
+    assert torch.equal(got, again)
+    _check_topk_rows(got.cpu(), masked, k)
+    assert int((got[3] >= 0).sum().item()) == int(torch.isfinite(masked[3]).sum())
+    # misaligned rows: a view that starts one float into the buffer
+    shifted = torch.empty(3, 20001, device=DEV)
+    shifted[:, 1:] = dev_logits[:3, 50000:70000]
+    view = shifted[:, 1:]
+    got = indexer.topk_indices(view, None, None, 512).cpu()
+    _check_topk_rows(got, masked[:3, 50000:70000], 512)
+
+
 def test_cp_partition():
     from sparse_mla_sm120_b200 import cp
     torch.manual_seed(8)
