@@ -147,6 +147,30 @@ int smla_cp_partition_indices(const int32_t* indices, int32_t* local_indices, in
                               int num_tokens, int topk, int lo, int hi, void* stream);
 
 /*
+ * Distributed top-k of the indexer under context parallelism (rank g holds the keys of positions
+ * [lo, hi)); four small steps around smla_mqa_logits / smla_topk.  No counterpart in the
+ * reference.
+ *   smla_cp_local_window          ks/ke [num_tokens] (global positions) clipped to the shard and
+ *                                 rebased to lo.
+ *   smla_cp_candidates            picked [num_tokens, k] (columns of the shard's logits, -1 =
+ *                                 none) -> values [num_tokens, k] (the logits, -inf for none) and
+ *                                 positions [num_tokens, k] (picked + lo, -1 for none).
+ *   smla_cp_interleave_candidates gathered [world][2][num_tokens][k] (every rank's values, then
+ *                                 positions, as all-gathered) -> values / positions
+ *                                 [num_tokens][world * k], the candidates of a token side by side.
+ *   smla_cp_pick_positions        out[t][i] = positions[t][pick[t][i]] (pick: the columns
+ *                                 smla_topk chose among the world * k candidates; -1 stays -1).
+ */
+int smla_cp_local_window(const int32_t* ks, const int32_t* ke, int32_t* ks_local, int32_t* ke_local, int num_tokens,
+                         int lo, int hi, void* stream);
+int smla_cp_candidates(const float* logits, int64_t logits_stride, const int32_t* picked, float* values,
+                       int32_t* positions, int num_tokens, int k, int lo, void* stream);
+int smla_cp_interleave_candidates(const int32_t* gathered, float* values, int32_t* positions, int world, int num_tokens,
+                                  int k, void* stream);
+int smla_cp_pick_positions(const int32_t* positions, const int32_t* pick, int32_t* out, int num_tokens, int k,
+                           int num_candidates, void* stream);
+
+/*
  * Context-parallel local step: split-KV decode over this GPU's shard followed by the local
  * merge, giving ONE fp32 partial per token (normalised by its own sum) and its base-2 LSE, ready
  * to be exchanged.  Same arguments as smla_decode_splitkv; o_part [num_tokens, num_heads, 512]

@@ -124,53 +124,78 @@ def sparse_mla_decode_cp_fwd(q, kv_local, indices, sm_scale, shard_lo: int, shar
 
 def local_window(ks: torch.Tensor, ke: torch.Tensor, shard_lo: int, shard_hi: int):
     """The part of each query's window [ks, ke) (global positions) that falls into the shard, in
-    shard-local positions; empty windows come out as ks == ke."""
-    n_local = shard_hi - shard_lo
-    return ((ks - shard_lo).clamp(0, n_local).to(torch.int32), (ke - shard_lo).clamp(0, n_local).to(torch.int32))
+    shard-local positions; empty windows come out as ks == ke.  On CUDA tensors one kernel; on CPU
+    tensors (the host-side tests) plain torch."""
+    if not ks.is_cuda:
+        n_local = shard_hi - shard_lo
+        return ((ks - shard_lo).clamp(0, n_local).to(torch.int32), (ke - shard_lo).clamp(0, n_local).to(torch.int32))
+    assert ks.dtype == torch.int32 and ke.dtype == torch.int32 and ks.is_contiguous() and ke.is_contiguous()
+    ks_l, ke_l = torch.empty_like(ks), torch.empty_like(ke)
+    check(_lib.load().smla_cp_local_window(ptr(ks), ptr(ke), ptr(ks_l), ptr(ke_l), ks.numel(), shard_lo, shard_hi,
+                                           stream_ptr(ks.device)))
+    return ks_l, ke_l
 
 
-def local_candidates(qi, ki_local, k_scale_local, weights, ks, ke, shard_lo: int, shard_hi: int, k: int):
+def local_candidates(qi, ki_local, k_scale_local, weights, ks, ke, shard_lo: int, shard_hi: int, k: int,
+                     out: Optional[torch.Tensor] = None):
     """Score the shard's keys and keep the k best per query.
 
     ``qi`` [T, H_i, 128] e4m3 and ``weights`` [T, H_i] are the indexer queries (identical on every
     rank), ``ki_local`` [shard_hi - shard_lo, 128] e4m3 with ``k_scale_local`` the shard's keys,
     ``ks`` / ``ke`` [T] int32 the visible window of each query in GLOBAL positions.
-    Returns (values [T, k] fp32 with -inf padding, positions [T, k] int32 global with -1 padding)."""
+    Returns (values [T, k] fp32 with -inf padding, positions [T, k] int32 global with -1 padding);
+    ``out`` [2, T, k] int32, when given, receives both (values as their bit patterns)."""
     from . import indexer
+    T = qi.shape[0]
     ks_l, ke_l = local_window(ks, ke, shard_lo, shard_hi)
     logits = indexer.fp8_mqa_logits(qi, ki_local, k_scale_local, weights, ks_l, ke_l)
-    local = indexer.topk_indices(logits, ks_l, ke_l, k)
-    valid = local >= 0
-    vals = torch.gather(logits, 1, local.clamp(min=0).long())
-    vals = torch.where(valid, vals, torch.full_like(vals, float("-inf")))
-    return vals, torch.where(valid, local + shard_lo, local)
+    picked = indexer.topk_indices(logits, ks_l, ke_l, k)
+    if out is None:
+        out = torch.empty((2, T, k), dtype=torch.int32, device=qi.device)
+    vals, pos = out[0].view(torch.float32), out[1]
+    check(_lib.load().smla_cp_candidates(ptr(logits), logits.stride(0), ptr(picked), ptr(vals), ptr(pos), T, k, shard_lo,
+                                         stream_ptr(qi.device)))
+    return vals, pos
 
 
 def merge_candidates(vals: torch.Tensor, pos: torch.Tensor, k: int) -> torch.Tensor:
     """``vals`` / ``pos`` [T, G*k]: the candidates of all shards side by side.  Returns the global
     positions of the k best per row as int32 [T, k], -1 padded."""
     from . import indexer
-    pick = indexer.topk_indices(vals.contiguous(), None, None, k)        # columns of the candidate list
-    got = torch.gather(pos, 1, pick.clamp(min=0).long())
-    return torch.where(pick >= 0, got, pick).to(torch.int32)
+    vals, pos = vals.contiguous(), pos.contiguous()
+    pick = indexer.topk_indices(vals, None, None, k)                     # columns of the candidate list
+    out = torch.empty_like(pick)
+    check(_lib.load().smla_cp_pick_positions(ptr(pos), ptr(pick), ptr(out), vals.shape[0], k, vals.shape[1],
+                                             stream_ptr(vals.device)))
+    return out
+
+
+def interleave_candidates(gathered: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
+    """``gathered`` [G, 2, T, k] int32 (every rank's values and positions as all-gathered) ->
+    (values [T, G*k] fp32, positions [T, G*k] int32): the candidates of a token side by side."""
+    world, _, T, k = gathered.shape
+    vals_all = torch.empty((T, world * k), dtype=torch.float32, device=gathered.device)
+    pos_all = torch.empty((T, world * k), dtype=torch.int32, device=gathered.device)
+    check(_lib.load().smla_cp_interleave_candidates(ptr(gathered), ptr(vals_all), ptr(pos_all), world, T, k,
+                                                    stream_ptr(gathered.device)))
+    return vals_all, pos_all
 
 
 def select_indices_cp(qi, ki_local, k_scale_local, weights, ks, ke, shard_lo: int, shard_hi: int, k: int = 2048,
                       group=None) -> torch.Tensor:
     """Distributed top-k of the indexer logits over a context sharded across the ranks of
     ``group``.  Returns the same [T, k] int32 global positions on every rank.  Exchanged per
-    query token: G * k * 8 bytes."""
+    query token: G * k * 8 bytes, in one all-gather."""
     import torch.distributed as dist
     world = dist.get_world_size(group) if dist.is_initialized() else 1
-    vals, pos = local_candidates(qi, ki_local, k_scale_local, weights, ks, ke, shard_lo, shard_hi, k)
+    rank = dist.get_rank(group) if dist.is_initialized() else 0
+    T = qi.shape[0]
+    gathered = torch.empty((world, 2, T, k), dtype=torch.int32, device=qi.device)
+    _, pos = local_candidates(qi, ki_local, k_scale_local, weights, ks, ke, shard_lo, shard_hi, k, out=gathered[rank])
     if world == 1:
         return pos
-    T = vals.shape[0]
-    v_all = torch.empty((world, T, k), dtype=torch.float32, device=vals.device)
-    p_all = torch.empty((world, T, k), dtype=torch.int32, device=vals.device)
-    dist.all_gather_into_tensor(v_all, vals.contiguous(), group=group)
-    dist.all_gather_into_tensor(p_all, pos.contiguous(), group=group)
-    return merge_candidates(v_all.permute(1, 0, 2).reshape(T, world * k), p_all.permute(1, 0, 2).reshape(T, world * k), k)
+    dist.all_gather_into_tensor(gathered, gathered[rank], group=group)
+    return merge_candidates(*interleave_candidates(gathered), k)
 
 
 def sparse_mla_indexed_decode_cp_fwd(q, kv_local, qi, ki_local, k_scale_local, weights, ks, ke, sm_scale,

@@ -228,4 +228,34 @@ int smla_cp_partition_indices(const int32_t* indices, int32_t* local_indices, in
                                (cudaStream_t)stream);
 }
 
+int smla_cp_local_window(const int32_t* ks, const int32_t* ke, int32_t* ks_local, int32_t* ke_local, int num_tokens,
+                         int lo, int hi, void* stream) {
+    if (!ks || !ke || !ks_local || !ke_local) return set_error(SMLA_E_NULL, "smla_cp_local_window: null pointer argument");
+    if (num_tokens < 0 || hi < lo) return set_error(SMLA_E_SHAPE, "smla_cp_local_window: tokens=%d range=[%d,%d)", num_tokens, lo, hi);
+    return launch_cp_window(ks, ke, ks_local, ke_local, num_tokens, lo, hi, (cudaStream_t)stream);
+}
+
+int smla_cp_candidates(const float* logits, int64_t logits_stride, const int32_t* picked, float* values,
+                       int32_t* positions, int num_tokens, int k, int lo, void* stream) {
+    if (!logits || !picked || !values || !positions) return set_error(SMLA_E_NULL, "smla_cp_candidates: null pointer argument");
+    if (num_tokens < 0 || k < 0) return set_error(SMLA_E_SHAPE, "smla_cp_candidates: tokens=%d k=%d", num_tokens, k);
+    return launch_cp_candidates(logits, logits_stride, picked, values, positions, num_tokens, k, lo, (cudaStream_t)stream);
+}
+
+int smla_cp_interleave_candidates(const int32_t* gathered, float* values, int32_t* positions, int world, int num_tokens,
+                                  int k, void* stream) {
+    if (!gathered || !values || !positions) return set_error(SMLA_E_NULL, "smla_cp_interleave_candidates: null pointer argument");
+    if (world < 1 || num_tokens < 0 || k < 0)
+        return set_error(SMLA_E_SHAPE, "smla_cp_interleave_candidates: world=%d tokens=%d k=%d", world, num_tokens, k);
+    return launch_cp_interleave(gathered, reinterpret_cast<int32_t*>(values), positions, world, num_tokens, k, (cudaStream_t)stream);
+}
+
+int smla_cp_pick_positions(const int32_t* positions, const int32_t* pick, int32_t* out, int num_tokens, int k,
+                           int num_candidates, void* stream) {
+    if (!positions || !pick || !out) return set_error(SMLA_E_NULL, "smla_cp_pick_positions: null pointer argument");
+    if (num_tokens < 0 || k < 0 || num_candidates < 0)
+        return set_error(SMLA_E_SHAPE, "smla_cp_pick_positions: tokens=%d k=%d candidates=%d", num_tokens, k, num_candidates);
+    return launch_cp_pick(positions, pick, out, num_tokens, k, num_candidates, (cudaStream_t)stream);
+}
+
 }  // extern "C"

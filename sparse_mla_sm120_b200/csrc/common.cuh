@@ -106,4 +106,13 @@ int launch_topk(const float* logits, const int32_t* ks, const int32_t* ke, int32
 int launch_cp_partition(const int32_t* indices, int32_t* local_indices, int32_t* local_length,
                         int num_tokens, int topk, int lo, int hi, cudaStream_t stream);
 
+int launch_cp_window(const int32_t* ks, const int32_t* ke, int32_t* ks_local, int32_t* ke_local, int num_tokens,
+                     int lo, int hi, cudaStream_t stream);
+int launch_cp_candidates(const float* logits, int64_t logits_stride, const int32_t* picked, float* values,
+                         int32_t* positions, int num_tokens, int k, int lo, cudaStream_t stream);
+int launch_cp_interleave(const int32_t* gathered, int32_t* values, int32_t* positions, int world, int num_tokens, int k,
+                         cudaStream_t stream);
+int launch_cp_pick(const int32_t* positions, const int32_t* pick, int32_t* out, int num_tokens, int k, int num_candidates,
+                   cudaStream_t stream);
+
 }  // namespace smla

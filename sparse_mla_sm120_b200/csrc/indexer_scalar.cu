@@ -514,6 +514,54 @@ cp_partition_kernel(const int32_t* __restrict__ indices, int32_t* __restrict__ l
     if (lane == 0) local_length[row] = n;
 }
 
+
+// ---------------------------------------------------------------- distributed top-k: the glue
+// Window of every token clipped to the shard [lo, hi), in shard-local positions.
+__global__ void cp_window_kernel(const int32_t* __restrict__ ks, const int32_t* __restrict__ ke,
+                                 int32_t* __restrict__ ks_local, int32_t* __restrict__ ke_local,
+                                 int num_tokens, int lo, int hi) {
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= num_tokens) return;
+    const int n = hi - lo;
+    ks_local[i] = min(max(ks[i] - lo, 0), n);
+    ke_local[i] = min(max(ke[i] - lo, 0), n);
+}
+
+// The shard's candidates of a token: logit and global position of every picked column
+// (-inf / -1 where the shard had fewer than k).
+__global__ void cp_candidates_kernel(const float* __restrict__ logits, int64_t logits_stride,
+                                     const int32_t* __restrict__ picked, float* __restrict__ values,
+                                     int32_t* __restrict__ positions, int num_tokens, int k, int lo) {
+    const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= (int64_t)num_tokens * k) return;
+    const int c = picked[i];
+    values[i] = (c >= 0) ? logits[(i / k) * logits_stride + c] : -INFINITY;
+    positions[i] = (c >= 0) ? c + lo : -1;
+}
+
+// gathered [world][2][num_tokens][k] (values, then positions, of every rank) -> the candidates of
+// a token side by side: values / positions [num_tokens][world * k].
+__global__ void cp_interleave_kernel(const int32_t* __restrict__ gathered, int32_t* __restrict__ values,
+                                     int32_t* __restrict__ positions, int world, int num_tokens, int k) {
+    const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;   // index into [num_tokens][world][k]
+    const int64_t per = (int64_t)num_tokens * k;
+    if (i >= per * world) return;
+    const int j = (int)(i % k), g = (int)((i / k) % world);
+    const int64_t t = i / ((int64_t)k * world);
+    const int32_t* src = gathered + (int64_t)g * 2 * per + t * k + j;
+    values[i] = src[0];
+    positions[i] = src[per];
+}
+
+// out[t][i] = positions[t][pick[t][i]] (-1 where pick is -1).
+__global__ void cp_pick_kernel(const int32_t* __restrict__ positions, const int32_t* __restrict__ pick,
+                               int32_t* __restrict__ out, int num_tokens, int k, int num_candidates) {
+    const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= (int64_t)num_tokens * k) return;
+    const int c = pick[i];
+    out[i] = (c >= 0) ? positions[(i / k) * num_candidates + c] : -1;
+}
+
 }  // namespace
 
 int launch_mqa_logits_scalar(const uint8_t* q, const uint8_t* k, const float* k_scale, const float* weights,
@@ -562,6 +610,38 @@ int launch_cp_partition(const int32_t* indices, int32_t* local_indices, int32_t*
     cp_partition_kernel<<<(num_tokens + 7) / 8, 256, 0, stream>>>(indices, local_indices, local_length,
                                                                   num_tokens, topk, lo, hi);
     return check_launch("cp_partition_kernel");
+}
+
+int launch_cp_window(const int32_t* ks, const int32_t* ke, int32_t* ks_local, int32_t* ke_local, int num_tokens,
+                     int lo, int hi, cudaStream_t stream) {
+    if (num_tokens == 0) return 0;
+    cp_window_kernel<<<(num_tokens + 255) / 256, 256, 0, stream>>>(ks, ke, ks_local, ke_local, num_tokens, lo, hi);
+    return check_launch("cp_window_kernel");
+}
+
+int launch_cp_candidates(const float* logits, int64_t logits_stride, const int32_t* picked, float* values,
+                         int32_t* positions, int num_tokens, int k, int lo, cudaStream_t stream) {
+    const int64_t n = (int64_t)num_tokens * k;
+    if (n == 0) return 0;
+    cp_candidates_kernel<<<(unsigned)((n + 255) / 256), 256, 0, stream>>>(logits, logits_stride, picked, values, positions,
+                                                                           num_tokens, k, lo);
+    return check_launch("cp_candidates_kernel");
+}
+
+int launch_cp_interleave(const int32_t* gathered, int32_t* values, int32_t* positions, int world, int num_tokens, int k,
+                         cudaStream_t stream) {
+    const int64_t n = (int64_t)num_tokens * k * world;
+    if (n == 0) return 0;
+    cp_interleave_kernel<<<(unsigned)((n + 255) / 256), 256, 0, stream>>>(gathered, values, positions, world, num_tokens, k);
+    return check_launch("cp_interleave_kernel");
+}
+
+int launch_cp_pick(const int32_t* positions, const int32_t* pick, int32_t* out, int num_tokens, int k, int num_candidates,
+                   cudaStream_t stream) {
+    const int64_t n = (int64_t)num_tokens * k;
+    if (n == 0) return 0;
+    cp_pick_kernel<<<(unsigned)((n + 255) / 256), 256, 0, stream>>>(positions, pick, out, num_tokens, k, num_candidates);
+    return check_launch("cp_pick_kernel");
 }
 
 }  // namespace smla

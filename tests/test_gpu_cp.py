@@ -81,13 +81,15 @@ def test_indexer_cp_pieces_on_one_gpu(world):
     ks[1], ke[1] = 1500, 1700          # fewer than k candidates, inside one shard (world 2) / two shards (world 4)
     ks[2], ke[2] = 900, 3300
     full = H.orc.mqa_logits_ref(q, key, k_scale, w, ks, ke)
-    vals, pos = [], []
+    gathered = torch.empty((world, 2, s_q, k), dtype=torch.int32, device=dev)      # what the all-gather would leave
     for r in range(world):
         lo, hi = cp.shard_context(s_k, r, world)
-        v, p = cp.local_candidates(q.to(dev), key[lo:hi].contiguous().to(dev), k_scale[lo:hi].contiguous().to(dev),
-                                   w.to(dev), ks.to(dev), ke.to(dev), lo, hi, k)
-        vals.append(v); pos.append(p)
-    got = cp.merge_candidates(torch.cat(vals, 1), torch.cat(pos, 1), k).cpu()
+        cp.local_candidates(q.to(dev), key[lo:hi].contiguous().to(dev), k_scale[lo:hi].contiguous().to(dev),
+                            w.to(dev), ks.to(dev), ke.to(dev), lo, hi, k, out=gathered[r])
+    vals, pos = cp.interleave_candidates(gathered)
+    assert torch.equal(vals.view(torch.int32), gathered[:, 0].permute(1, 0, 2).reshape(s_q, world * k))
+    assert torch.equal(pos, gathered[:, 1].permute(1, 0, 2).reshape(s_q, world * k))
+    got = cp.merge_candidates(vals, pos, k).cpu()
     _check_selection(got, full, k)
     assert int((got[1] >= 0).sum()) == 200
 
