@@ -415,9 +415,38 @@ def run_cp_extra(device, rank, world):
     e1.record(); torch.cuda.synchronize()
     t = torch.tensor([e0.elapsed_time(e1) / n * 1e3], device=device)
     dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    return {"workload": "b=16, h=128, topk=2048, 131072-token context sharded over the ranks", "us_per_step": float(t.item()),
-            "timed": "partition + scheduler + local decode + local merge + 2 NCCL all-gathers + final merge (eager launches)",
-            "exchange_bytes_per_rank": b * HEADS * (D_V + 1) * 4}
+    res = {"workload": "b=16, h=128, topk=2048, 131072-token context sharded over the ranks", "us_per_step": float(t.item()),
+           "timed": "partition + scheduler + local decode + local merge + 2 NCCL all-gathers + final merge (eager launches)",
+           "exchange_bytes_per_rank": b * HEADS * (D_V + 1) * 4}
+    # the same step with the indexer in front: 16 tokens of ONE sequence whose 131072-token context
+    # (attention cache and indexer keys) is sharded; local logits + local top-k + candidate all-gather
+    # + global top-k, then the context-parallel decode
+    del kv_local, pools
+    kv_one = indexer.pack_kv_cache(torch.randn((rows, D_QK), device=device, generator=g).to(torch.bfloat16)).view(-1, BLOCK, 1, ROW)
+    hh = 64
+    qi = torch.randn((b, hh, 128), device=device, generator=gi).to(torch.float8_e4m3fn)
+    w = torch.randn((b, hh), device=device, generator=gi) * 0.1
+    kf = torch.randn((rows, 128), device=device, generator=g)
+    k_scale = kf.abs().amax(dim=1) / 448.0
+    ki = (kf / k_scale.unsqueeze(1)).to(torch.float8_e4m3fn)
+    ks = torch.zeros(b, dtype=torch.int32, device=device)
+    ke = (ctx - b + 1 + torch.arange(b, device=device)).to(torch.int32)
+
+    def step_indexed():
+        return cp.sparse_mla_indexed_decode_cp_fwd(q, kv_one, qi, ki, k_scale, w, ks, ke, SM_SCALE, lo, hi, topk=TOPK)
+
+    for _ in range(5):
+        step_indexed()
+    dist.barrier(); torch.cuda.synchronize()
+    e0.record()
+    for _ in range(n):
+        step_indexed()
+    e1.record(); torch.cuda.synchronize()
+    t = torch.tensor([e0.elapsed_time(e1) / n * 1e3], device=device)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    res["us_per_step_with_indexer"] = float(t.item())
+    res["indexer_exchange_bytes_per_rank"] = b * TOPK * 8
+    return res
 
 
 def run_extras(device, bf16_peak):
@@ -469,7 +498,56 @@ def run_extras(device, bf16_peak):
                               "frac_of_fp8_peak(2x measured bf16)": fl / out["mqa_logits"]["ms"] / 1e9 / (2 * bf16_peak),
                               "write_gbs": s_q * s_k * 4 / out["mqa_logits"]["ms"] / 1e6})
     out["topk"].update({"workload": "top-2048 of each of 4096 rows of 65536 fp32", "read_gbs": s_q * s_k * 4 / out["topk"]["ms"] / 1e6})
+    del logits, qi, ki
+    out["indexed_decode"] = run_indexed_decode_extra(device, g)
     return out
+
+
+def run_indexed_decode_extra(device, g):
+    """Indexer -> top-k -> sparse decode as one call: 16 tokens of one long sequence, 131072-token
+    context, 64 indexer heads, top-2048, 128 attention heads.  Eager launches and CUDA-graph replay."""
+    from sparse_mla_sm120_b200 import indexer, pipeline
+    t, ctx, hh = 16, 131072, 64
+    kv = indexer.pack_kv_cache(torch.randn((ctx, D_QK), device=device, generator=g).to(torch.bfloat16)).view(ctx // BLOCK, BLOCK, 1, ROW)
+    q = (torch.randn((t, HEADS, D_QK), device=device, generator=g) * 0.5).to(torch.bfloat16)
+    qi = torch.randn((t, hh, 128), device=device, generator=g).to(torch.float8_e4m3fn)
+    kf = torch.randn((ctx, 128), device=device, generator=g)
+    k_scale = kf.abs().amax(dim=1) / 448.0
+    ki = (kf / k_scale.unsqueeze(1)).to(torch.float8_e4m3fn)
+    w = torch.randn((t, hh), device=device, generator=g) * 0.1
+    ks = torch.zeros(t, dtype=torch.int32, device=device)
+    ke = (ctx - t + 1 + torch.arange(t, device=device)).to(torch.int32)
+
+    def step():
+        return pipeline.sparse_mla_indexed_decode_fwd(q, kv, qi, ki, k_scale, w, ks, ke, SM_SCALE, topk=TOPK)
+
+    def timed(fn, n=50):
+        for _ in range(5):
+            fn()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(n):
+            fn()
+        e1.record(); torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / n * 1e3
+
+    res = {"workload": "16 tokens, 131072-token context, 64 indexer heads, top-2048, h=128",
+           "timed": "fp8 logits + top-k + scheduler + split-KV decode + combine", "us_per_step_eager": timed(step)}
+    try:
+        side = torch.cuda.Stream(device=device)
+        side.wait_stream(torch.cuda.current_stream(device))
+        with torch.cuda.stream(side):
+            step()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, stream=side):
+                step()
+        torch.cuda.current_stream(device).wait_stream(side)
+        res["us_per_step_graph"] = timed(graph.replay)
+    except Exception as e:       # capture is an optimisation of the launch path, not a requirement
+        res["us_per_step_graph"] = None
+        res["graph_error"] = repr(e)
+    return res
 
 
 def cpu_baseline(pool, sets, n_req: int = 16):
