@@ -6,7 +6,6 @@
 // followed by a per-row top-k, and the split of a global index list into one GPU's shard.
 #include <cstdint>
 
-#include <cstdio>
 #include "common.cuh"
 
 namespace smla {
@@ -394,9 +393,6 @@ topk_select_kernel(const float* __restrict__ logits, const int32_t* __restrict__
     for (int w = 0; w < TS_WARPS; ++w) { total += cw[w]; overflow |= cw[w] > TS_LIST; }
     if (overflow || (sampled && total < k)) {  // (uniform) the guess failed: the multi-pass kernel redoes the row
         if (tid == 0) o[0] = TK_REDO;
-#ifdef SMLA_TK_TRACE
-        if (tid == 0) printf("redo row %d: overflow %d total %d t_f %g maxcw %d\n", row, (int)overflow, total, t_f, max(max(cw[0], cw[1]), max(cw[2], cw[3])));
-#endif
         return;
     }
     const int mycount = cnt;
@@ -460,9 +456,6 @@ topk_select_kernel(const float* __restrict__ logits, const int32_t* __restrict__
         __syncthreads();
         if (n_eq_s > TS_EQ) {                  // (uniform)
             if (tid == 0) o[0] = TK_REDO;
-#ifdef SMLA_TK_TRACE
-            if (tid == 0) printf("redo row %d: n_eq %d shift %d total %d\n", row, n_eq_s, shift, total);
-#endif
             return;
         }
     }
