@@ -252,6 +252,8 @@ __global__ void __launch_bounds__(TC_THREADS, 1) attn_tc_kernel(const AttnParams
         const uint32_t lane_addr = tmem + ((uint32_t)(quarter * 32) << 16);
         float* xch = reinterpret_cast<float*>(sm + XCH_OFF);   // [2][2][128]
         const bool live = row < p.num_heads;
+        const bool wide_out = (reinterpret_cast<size_t>(p.out) & 31) == 0;        // rows are 1024 bytes apart
+        const bool wide_acc = (reinterpret_cast<size_t>(p.o_accum) & 31) == 0;
         uint32_t it = 0;                          // running tile counter of this CTA
         bool ok = true;
         for (int req = meta.begin_req; req <= last_req && ok; ++req) {
@@ -442,16 +444,23 @@ __global__ void __launch_bounds__(TC_THREADS, 1) attn_tc_kernel(const AttnParams
                         tmem_ld32(lane_addr + TM_O + 128 * hh + c, o);
                         tmem_wait_ld();
                         if (live) {
+                            // a row's 64 bytes of this chunk: two full 32-byte sectors per lane (16-byte
+                            // stores, half a sector each, when the output is not 32-byte aligned)
+                            uint32_t pk[16];
 #pragma unroll
-                            for (int i = 0; i < 32; i += 8) {
-                                uint4 v;
-                                __nv_bfloat162 t0 = __floats2bfloat162_rn(__uint_as_float(o[i + 0]) * inv, __uint_as_float(o[i + 1]) * inv);
-                                __nv_bfloat162 t1 = __floats2bfloat162_rn(__uint_as_float(o[i + 2]) * inv, __uint_as_float(o[i + 3]) * inv);
-                                __nv_bfloat162 t2 = __floats2bfloat162_rn(__uint_as_float(o[i + 4]) * inv, __uint_as_float(o[i + 5]) * inv);
-                                __nv_bfloat162 t3 = __floats2bfloat162_rn(__uint_as_float(o[i + 6]) * inv, __uint_as_float(o[i + 7]) * inv);
-                                v.x = *reinterpret_cast<uint32_t*>(&t0); v.y = *reinterpret_cast<uint32_t*>(&t1);
-                                v.z = *reinterpret_cast<uint32_t*>(&t2); v.w = *reinterpret_cast<uint32_t*>(&t3);
-                                *reinterpret_cast<uint4*>(dst + c + i) = v;
+                            for (int i = 0; i < 16; ++i) {
+                                __nv_bfloat162 t = __floats2bfloat162_rn(__uint_as_float(o[2 * i]) * inv, __uint_as_float(o[2 * i + 1]) * inv);
+                                pk[i] = *reinterpret_cast<uint32_t*>(&t);
+                            }
+                            if (wide_out) {
+                                const uint32_t lo8[8] = {pk[0], pk[1], pk[2], pk[3], pk[4], pk[5], pk[6], pk[7]};
+                                const uint32_t hi8[8] = {pk[8], pk[9], pk[10], pk[11], pk[12], pk[13], pk[14], pk[15]};
+                                st_global_v8(dst + c, lo8);
+                                st_global_v8(dst + c + 16, hi8);
+                            } else {
+#pragma unroll
+                                for (int i = 0; i < 4; ++i)
+                                    *reinterpret_cast<uint4*>(dst + c + 8 * i) = make_uint4(pk[4 * i], pk[4 * i + 1], pk[4 * i + 2], pk[4 * i + 3]);
                             }
                         }
                     }
@@ -468,10 +477,17 @@ __global__ void __launch_bounds__(TC_THREADS, 1) attn_tc_kernel(const AttnParams
                         tmem_wait_ld();
                         if (live) {
 #pragma unroll
-                            for (int i = 0; i < 32; i += 4) {
-                                float4 v = make_float4(__uint_as_float(o[i]) * inv, __uint_as_float(o[i + 1]) * inv,
-                                                       __uint_as_float(o[i + 2]) * inv, __uint_as_float(o[i + 3]) * inv);
-                                *reinterpret_cast<float4*>(dst + c + i) = v;
+                            for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * inv);
+                            if (wide_acc) {
+#pragma unroll
+                                for (int i = 0; i < 32; i += 8) {
+                                    const uint32_t v8[8] = {o[i], o[i + 1], o[i + 2], o[i + 3], o[i + 4], o[i + 5], o[i + 6], o[i + 7]};
+                                    st_global_v8(dst + c + i, v8);
+                                }
+                            } else {
+#pragma unroll
+                                for (int i = 0; i < 32; i += 4)
+                                    *reinterpret_cast<uint4*>(dst + c + i) = make_uint4(o[i], o[i + 1], o[i + 2], o[i + 3]);
                             }
                         }
                     }

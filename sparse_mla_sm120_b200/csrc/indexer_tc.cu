@@ -149,16 +149,19 @@ __global__ void __launch_bounds__(LX_THREADS, 1) mqa_logits_tc_kernel(const Logi
                 const float* wq = wsm + qp * 64;
                 uint32_t d0[32], d1[32];
                 tmem_ld32(col0, d0);
+                // two scores per instruction: packed fp32 FMAs (same products, same four partial sums
+                // as four scalar FMA chains)
                 auto reduce = [&](const uint32_t (&d)[32], int c) {
-                    float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
+                    uint64_t a01 = 0ull, a23 = 0ull;
 #pragma unroll
                     for (int i = 0; i < 32; i += 4) {
-                        const float4 w4 = *reinterpret_cast<const float4*>(wq + c + i);
-                        a0 = fmaf(fmaxf(__uint_as_float(d[i + 0]), 0.f), w4.x, a0);
-                        a1 = fmaf(fmaxf(__uint_as_float(d[i + 1]), 0.f), w4.y, a1);
-                        a2 = fmaf(fmaxf(__uint_as_float(d[i + 2]), 0.f), w4.z, a2);
-                        a3 = fmaf(fmaxf(__uint_as_float(d[i + 3]), 0.f), w4.w, a3);
+                        const ulonglong2 w4 = *reinterpret_cast<const ulonglong2*>(wq + c + i);      // (w0, w1), (w2, w3)
+                        fma_f32x2(a01, pack_f32x2(fmaxf(__uint_as_float(d[i + 0]), 0.f), fmaxf(__uint_as_float(d[i + 1]), 0.f)), w4.x);
+                        fma_f32x2(a23, pack_f32x2(fmaxf(__uint_as_float(d[i + 2]), 0.f), fmaxf(__uint_as_float(d[i + 3]), 0.f)), w4.y);
                     }
+                    float a0, a1, a2, a3;
+                    unpack_f32x2(a01, a0, a1);
+                    unpack_f32x2(a23, a2, a3);
                     acc += (a0 + a1) + (a2 + a3);
                 };
                 tmem_wait_ld();

@@ -125,3 +125,13 @@ def test_indexer_candidate_merge_two_gloo_ranks():
         mp.spawn(_indexer_rank_main, args=(2, port, ret), nprocs=2, join=True)
         assert ret["same_sets"], dict(ret)
         assert ret["counts"] == [48, 48, 48, 48]
+
+
+def test_positions_to_rows_cpu():
+    """Logical positions -> physical cache rows through a page table (pure index arithmetic)."""
+    from sparse_mla_sm120_b200.pipeline import positions_to_rows
+    table = torch.tensor([[7, 2, 9], [0, 5, 1]], dtype=torch.int32)
+    pos = torch.tensor([[0, 63, 64, 130, -1], [191, 1, -1, 65, 128]], dtype=torch.int32)
+    rows = positions_to_rows(pos, table, 64)
+    assert rows.dtype == torch.int32
+    assert rows.tolist() == [[7 * 64, 7 * 64 + 63, 2 * 64, 9 * 64 + 2, -1], [1 * 64 + 63, 1, -1, 5 * 64 + 1, 1 * 64]]
