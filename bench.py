@@ -376,7 +376,7 @@ def run_ours(args):
 def run_cp_extra(device, rank, world):
     """Context-parallel long-context decode: 16 requests, 131072-token context sharded across the
     ranks, top-k 2048 uniform over the whole context.  Timed per step on the device, max over ranks:
-    index partition + scheduler + local split-KV decode + local merge + NCCL all-gather + final merge.
+    index partition + scheduler + local split-KV decode + local merge + one NCCL all-gather + final merge.
     (The indexer that would produce the indices is not part of this timing.)"""
     import torch.distributed as dist
     from sparse_mla_sm120_b200 import cp, indexer
@@ -398,10 +398,9 @@ def run_cp_extra(device, rank, world):
     def step():
         # entries outside the shard are already -1; compaction and the local length come from the partition kernel
         li, ln = cp.partition_indices(local, 0, b * rows)
-        o_all, l_all = cp._gather_buffers(device, world, b, HEADS)
+        packed, o_all, l_all = cp._gather_buffers(device, world, b, HEADS)
         cp.decode_partial(q, kv_local, li, ln, SM_SCALE, o_all[rank], l_all[rank])
-        dist.all_gather_into_tensor(o_all, o_all[rank])
-        dist.all_gather_into_tensor(l_all, l_all[rank])
+        dist.all_gather_into_tensor(packed, packed[rank])       # partials and LSEs of a rank are adjacent
         return cp.combine_parts(o_all, l_all)
 
     for _ in range(5):
@@ -416,7 +415,7 @@ def run_cp_extra(device, rank, world):
     t = torch.tensor([e0.elapsed_time(e1) / n * 1e3], device=device)
     dist.all_reduce(t, op=dist.ReduceOp.MAX)
     res = {"workload": "b=16, h=128, topk=2048, 131072-token context sharded over the ranks", "us_per_step": float(t.item()),
-           "timed": "partition + scheduler + local decode + local merge + 2 NCCL all-gathers + final merge (eager launches)",
+           "timed": "partition + scheduler + local decode + local merge + one NCCL all-gather + final merge (eager launches)",
            "exchange_bytes_per_rank": b * HEADS * (D_V + 1) * 4}
     # the same step with the indexer in front: 16 tokens of ONE sequence whose 131072-token context
     # (attention cache and indexer keys) is sharded; local logits + local top-k + candidate all-gather

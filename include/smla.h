@@ -195,6 +195,17 @@ int smla_combine_parts(const float* o_parts, const float* lse_parts, void* out, 
                        int parts, int num_tokens, int num_heads, const float* attn_sink, void* stream);
 
 /*
+ * The same merge when the partials of rank g start o_part_stride floats after those of rank
+ * g - 1 (and the LSEs lse_part_stride floats), e.g. one buffer per rank holding
+ * [num_tokens * num_heads * 512 partials | num_tokens * num_heads LSEs], which ONE all-gather
+ * fills: o_part_stride = lse_part_stride = num_tokens * num_heads * 513 and lse_parts =
+ * o_parts + num_tokens * num_heads * 512.  o_part_stride must be a multiple of 4 floats.
+ */
+int smla_combine_parts_strided(const float* o_parts, const float* lse_parts, void* out, float* out_lse,
+                               int parts, int num_tokens, int num_heads, int64_t o_part_stride,
+                               int64_t lse_part_stride, const float* attn_sink, void* stream);
+
+/*
  * Split-KV decode (scheduler + attention + combine in one call) that allocates nothing and takes
  * no scratch from the caller.  It has no counterpart in the reference.  It is for hosts that
  * cannot give this library device memory at call time: a process whose own pool already owns the

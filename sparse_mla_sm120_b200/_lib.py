@@ -25,6 +25,8 @@ _SIGS = {
                                     c_void_p, c_void_p, c_int, c_int, c_int, c_float, c_int, c_int64, c_int,
                                     c_void_p, c_int, c_void_p, c_void_p]),
     "smla_combine_parts": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p]),
+    "smla_combine_parts_strided": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int64, c_int64,
+                                           c_void_p, c_void_p]),
     "smla_noalloc_scratch_need": (c_size_t, [c_int, c_int, c_int]),
     "smla_decode_splitkv_noalloc": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
                                             c_float, c_int, c_int64, c_int, c_void_p, c_void_p, c_int, c_void_p,

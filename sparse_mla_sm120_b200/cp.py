@@ -55,10 +55,15 @@ _gather_bufs: Dict[Tuple, Tuple[torch.Tensor, torch.Tensor]] = {}
 
 
 def _gather_buffers(device, world, T, H):
+    """(packed, o_all, lse_all): one fp32 buffer [world, T*H*513 rounded up to 4] and its views o_all [world, T, H, 512],
+    lse_all [world, T, H].  A rank's partials and LSEs are adjacent, so ONE all-gather of ``packed``
+    exchanges both."""
     key = (device.index, world, T, H)
     if key not in _gather_bufs:
-        _gather_bufs[key] = (torch.empty((world, T, H, 512), dtype=torch.float32, device=device),
-                             torch.empty((world, T, H), dtype=torch.float32, device=device))
+        per = (T * H * 513 + 3) & ~3                      # a rank's share, kept 16-byte aligned
+        packed = torch.empty((world, per), dtype=torch.float32, device=device)
+        _gather_bufs[key] = (packed, packed[:, :T * H * 512].view(world, T, H, 512),
+                             packed[:, T * H * 512:T * H * 513].view(world, T, H))
     return _gather_bufs[key]
 
 
@@ -86,14 +91,18 @@ def decode_partial(q, kv_local, local_indices, local_length, sm_scale, o_part=No
 
 
 def combine_parts(o_parts, lse_parts, attn_sink=None, out=None):
-    """Merge [G, T, H, 512] fp32 partials and [G, T, H] base-2 LSEs -> (out bf16, lse)."""
+    """Merge [G, T, H, 512] fp32 partials and [G, T, H] base-2 LSEs -> (out bf16, lse).  The parts
+    of a rank must be contiguous; the ranks may lie any (4-float aligned) distance apart."""
     require_cuda(o_parts, lse_parts)
     G, T, H, _ = o_parts.shape
+    assert o_parts[0].is_contiguous() and lse_parts[0].is_contiguous()
     if out is None:
         out = torch.empty((T, H, 512), dtype=torch.bfloat16, device=o_parts.device)
     lse = torch.empty((T, H), dtype=torch.float32, device=o_parts.device)
-    check(_lib.load().smla_combine_parts(ptr(o_parts), ptr(lse_parts), ptr(out), ptr(lse), G, T, H,
-                                         ptr(attn_sink), stream_ptr(o_parts.device)))
+    o_stride = o_parts.stride(0) if G > 1 else T * H * 512
+    l_stride = lse_parts.stride(0) if G > 1 else T * H
+    check(_lib.load().smla_combine_parts_strided(ptr(o_parts), ptr(lse_parts), ptr(out), ptr(lse), G, T, H, o_stride,
+                                                 l_stride, ptr(attn_sink), stream_ptr(o_parts.device)))
     return out, lse
 
 
@@ -107,11 +116,10 @@ def sparse_mla_decode_cp_fwd(q, kv_local, indices, sm_scale, shard_lo: int, shar
     rank = dist.get_rank(group) if dist.is_initialized() else 0
     T, H, _ = q.shape
     local_idx, local_len = partition_indices(indices, shard_lo, shard_hi)
-    o_all, lse_all = _gather_buffers(q.device, world, T, H)
+    packed, o_all, lse_all = _gather_buffers(q.device, world, T, H)
     decode_partial(q, kv_local, local_idx, local_len, sm_scale, o_all[rank], lse_all[rank], impl=impl)
     if world > 1:
-        dist.all_gather_into_tensor(o_all, o_all[rank], group=group)
-        dist.all_gather_into_tensor(lse_all, lse_all[rank], group=group)
+        dist.all_gather_into_tensor(packed, packed[rank], group=group)       # partials and LSEs in one exchange
     return combine_parts(o_all, lse_all, attn_sink)
 
 

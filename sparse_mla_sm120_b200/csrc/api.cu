@@ -161,8 +161,23 @@ int smla_combine_parts(const float* o_parts, const float* lse_parts, void* out, 
     if (parts < 1 || num_tokens < 0 || num_heads < 1)
         return set_error(SMLA_E_SHAPE, "smla_combine_parts: parts=%d tokens=%d heads=%d", parts, num_tokens, num_heads);
     if (!aligned16(o_parts) || !aligned16(out)) return set_error(SMLA_E_ALIGN, "smla_combine_parts: unaligned buffer");
-    return launch_combine_parts(o_parts, lse_parts, (__nv_bfloat16*)out, out_lse, parts, num_tokens, num_heads,
+    return launch_combine_parts(o_parts, lse_parts, (__nv_bfloat16*)out, out_lse, parts, num_tokens, num_heads, 0, 0,
                                 attn_sink, (cudaStream_t)stream);
+}
+
+int smla_combine_parts_strided(const float* o_parts, const float* lse_parts, void* out, float* out_lse,
+                               int parts, int num_tokens, int num_heads, int64_t o_part_stride,
+                               int64_t lse_part_stride, const float* attn_sink, void* stream) {
+    if (!o_parts || !lse_parts || !out || !out_lse)
+        return set_error(SMLA_E_NULL, "smla_combine_parts_strided: null pointer argument");
+    if (parts < 1 || num_tokens < 0 || num_heads < 1 || o_part_stride < (int64_t)num_tokens * num_heads * 512 ||
+        lse_part_stride < (int64_t)num_tokens * num_heads)
+        return set_error(SMLA_E_SHAPE, "smla_combine_parts_strided: parts=%d tokens=%d heads=%d strides=%lld,%lld", parts,
+                         num_tokens, num_heads, (long long)o_part_stride, (long long)lse_part_stride);
+    if (!aligned16(o_parts) || !aligned16(out) || (o_part_stride % 4) != 0)
+        return set_error(SMLA_E_ALIGN, "smla_combine_parts_strided: unaligned buffer or stride");
+    return launch_combine_parts(o_parts, lse_parts, (__nv_bfloat16*)out, out_lse, parts, num_tokens, num_heads,
+                                o_part_stride, lse_part_stride, attn_sink, (cudaStream_t)stream);
 }
 
 int smla_prefill(const void* q, const void* kv, const int32_t* indices,

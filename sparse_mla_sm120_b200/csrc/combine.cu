@@ -24,7 +24,7 @@ __global__ void __launch_bounds__(WARPS * 32)
 combine_kernel(const float* __restrict__ o_accum, const float* __restrict__ lse_accum,
                OutT* __restrict__ out, float* __restrict__ out_lse,
                const int32_t* __restrict__ num_splits, const float* __restrict__ attn_sink,
-               int batch, int num_heads, int fixed_ns) {
+               int batch, int num_heads, int fixed_ns, int64_t part_stride_o, int64_t part_stride_l) {
     constexpr bool F32 = sizeof(OutT) == 4;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int64_t row = (int64_t)blockIdx.x * WARPS + warp;   // (token, head)
@@ -41,8 +41,10 @@ combine_kernel(const float* __restrict__ o_accum, const float* __restrict__ lse_
         s0 = tok; ns = fixed_ns; rec_stride = (size_t)batch;
     }
 
-    const size_t o_stride = rec_stride * num_heads * D_V;
-    const size_t l_stride = rec_stride * num_heads;
+    // strided mode may give the distance (in floats) between the parts explicitly: partials and
+    // LSEs of a rank then share one buffer, as one all-gather leaves them
+    const size_t o_stride = (num_splits == nullptr && part_stride_o > 0) ? (size_t)part_stride_o : rec_stride * num_heads * D_V;
+    const size_t l_stride = (num_splits == nullptr && part_stride_l > 0) ? (size_t)part_stride_l : rec_stride * num_heads;
     const float* lse_p = lse_accum + (size_t)s0 * num_heads + h;
     const float* o_p = o_accum + (size_t)s0 * num_heads * D_V + (size_t)h * D_V + lane * 4;
 
@@ -126,7 +128,7 @@ int launch_combine(const float* o_accum, const float* lse_accum, __nv_bfloat16* 
     if (rows == 0) return 0;
     const unsigned grid = (unsigned)((rows + WARPS - 1) / WARPS);
     combine_kernel<__nv_bfloat16><<<grid, WARPS * 32, 0, stream>>>(o_accum, lse_accum, out, out_lse, num_splits,
-                                                                    attn_sink, batch, num_heads, 0);
+                                                                    attn_sink, batch, num_heads, 0, 0, 0);
     return check_launch("combine_kernel");
 }
 
@@ -137,18 +139,21 @@ int launch_combine_f32(const float* o_accum, const float* lse_accum, float* out,
     if (rows == 0) return 0;
     const unsigned grid = (unsigned)((rows + WARPS - 1) / WARPS);
     combine_kernel<float><<<grid, WARPS * 32, 0, stream>>>(o_accum, lse_accum, out, out_lse, num_splits, nullptr,
-                                                            batch, num_heads, 0);
+                                                            batch, num_heads, 0, 0, 0);
     return check_launch("combine_kernel<f32>");
 }
 
-// Merge of `parts` per-GPU partials laid out [parts, batch, H, 512] / [parts, batch, H].
+// Merge of `parts` per-GPU partials laid out [parts, batch, H, 512] / [parts, batch, H]; non-zero
+// part strides (in floats) give the distance between two ranks' partials / LSEs explicitly.
 int launch_combine_parts(const float* o_parts, const float* lse_parts, __nv_bfloat16* out, float* out_lse,
-                         int parts, int batch, int num_heads, const float* attn_sink, cudaStream_t stream) {
+                         int parts, int batch, int num_heads, int64_t part_stride_o, int64_t part_stride_l,
+                         const float* attn_sink, cudaStream_t stream) {
     const int64_t rows = (int64_t)batch * num_heads;
     if (rows == 0) return 0;
     const unsigned grid = (unsigned)((rows + WARPS - 1) / WARPS);
     combine_kernel<__nv_bfloat16><<<grid, WARPS * 32, 0, stream>>>(o_parts, lse_parts, out, out_lse, nullptr,
-                                                                    attn_sink, batch, num_heads, parts);
+                                                                    attn_sink, batch, num_heads, parts, part_stride_o,
+                                                                    part_stride_l);
     return check_launch("combine_kernel<parts>");
 }
 

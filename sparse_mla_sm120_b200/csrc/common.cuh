@@ -88,7 +88,8 @@ int launch_combine(const float* o_accum, const float* lse_accum, __nv_bfloat16* 
 int launch_combine_f32(const float* o_accum, const float* lse_accum, float* out, float* out_lse,
                        const int32_t* num_splits, int batch, int num_heads, cudaStream_t stream);
 int launch_combine_parts(const float* o_parts, const float* lse_parts, __nv_bfloat16* out, float* out_lse,
-                         int parts, int batch, int num_heads, const float* attn_sink, cudaStream_t stream);
+                         int parts, int batch, int num_heads, int64_t part_stride_o, int64_t part_stride_l,
+                         const float* attn_sink, cudaStream_t stream);
 int launch_attn_scalar(const AttnParams& p, cudaStream_t stream);
 int launch_attn_tc(const AttnParams& p, cudaStream_t stream);
 int launch_attn_tc2(const AttnParams& p, cudaStream_t stream);

@@ -25,8 +25,11 @@ def test_cp_pieces_on_one_gpu(world, impl):
     case["indices"][4] = torch.where(case["indices"][4] < rows // world, case["indices"][4], -1)   # one-shard token
     ref_out, ref_lse = oracle_attn(case)
     q, idx = case["q"].to(dev), case["indices"].to(dev)
-    o_all = torch.empty((world, 5, 128, 512), dtype=torch.float32, device=dev)
-    l_all = torch.empty((world, 5, 128), dtype=torch.float32, device=dev)
+    if world == 4:      # the packed exchange buffer of the multi-GPU path: a rank's partials and LSEs adjacent
+        _, o_all, l_all = cp._gather_buffers(dev, world, 5, 128)
+    else:
+        o_all = torch.empty((world, 5, 128, 512), dtype=torch.float32, device=dev)
+        l_all = torch.empty((world, 5, 128), dtype=torch.float32, device=dev)
     for r in range(world):
         lo, hi = cp.shard_context(rows, r, world)
         kv_local = case["packed"].view(-1, 656)[lo:hi].reshape(-1, 64, 1, 656).to(dev)
