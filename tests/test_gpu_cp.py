@@ -115,6 +115,14 @@ def test_indexed_decode_pipeline_one_gpu():
     ref_out, ref_lse = oracle_attn(case)
     H.compare_out(out, ref_out, H.TC_ABS, H.TC_REL, H.TC_COS)
     H.compare_lse(lse, ref_lse, H.TC_LSE)
+    # the same step as a CUDA-graph replay, twice with different inputs
+    graphed = pipeline.GraphedIndexedDecode(case["packed"].to(dev), key.to(dev), k_scale.to(dev), 6, 128, 64,
+                                            case["sm_scale"], topk=256)
+    ke2 = ke.clone(); ke2[0] = 700
+    for ke_i in (ke2, ke):
+        g_out, g_lse, g_rows = graphed(case["q"].to(dev), q.to(dev), w.to(dev), ks.to(dev), ke_i.to(dev))
+    torch.cuda.synchronize()
+    assert torch.equal(g_rows, rows) and torch.equal(g_out, out) and torch.equal(g_lse, lse)
     # through a page table that reverses the pages
     pages = s_k // 64
     table = torch.arange(pages - 1, -1, -1, dtype=torch.int32).repeat(6, 1)
