@@ -227,23 +227,22 @@ __device__ __forceinline__ void pick_bin(const int* hist, int need, int lane, in
 // the k-th -- the row is marked for the multi-pass kernel.
 //
 // The pass over the row is kept free of warp-wide votes: a lane compares its logits as floats
-// (NaNs never become candidates) and only notes a bit per entry; after 65536 columns the lanes of
-// a warp exchange their counts once and every lane appends its own columns.
+// (NaNs never become candidates) and only notes a bit per entry; after a stretch of eight rounds
+// (65536 columns with 16 warps) the lanes of a warp exchange their counts once and every lane
+// appends its own columns.
 //
-// Order of the output: warp w owns the 128-column blocks w, w + 16, ... of the row; its list holds,
-// per stretch of 65536 columns, the candidates of lane 0, then of lane 1, ... each in column
-// order; the lists are written out one after the other.  The order is a fixed function of the
+// Order of the output: warp w owns the 128-column blocks w, w + warps, ... of the row; its list
+// holds, per stretch, the candidates of lane 0, then of lane 1, ... each in column order; the
+// lists are written out one after the other.  The order is a fixed function of the
 // input (no atomics decide it), though not ascending.
-constexpr int TS_THREADS = 512;
-constexpr int TS_WARPS = TS_THREADS / 32;
-constexpr int TS_LIST = 512;               // candidates per warp
+constexpr int TS_CAND = 8192;              // candidates a row may have in all (per warp: TS_CAND / warps)
 constexpr int TS_SAMPLE = 4096;            // sampled logits: 512 runs of 8
 constexpr int TS_EQ = 1024;                // entries in the bin of the k-th key, ranked one against the other
 constexpr int TS_BINS = 4096;
-constexpr int TS_DIRECT = TS_WARPS * TS_LIST - 128;   // windows up to this size need no threshold
+constexpr int TS_DIRECT = TS_CAND - 128;   // windows up to this size need no threshold
 constexpr int TS_KMAX = 4096;              // largest k (the lists hold 8192)
 constexpr int TS_ROUNDS = 8;               // rounds of four blocks per warp between two appends
-constexpr int TS_SMEM = TS_WARPS * TS_LIST * 8 + TS_BINS * 4 + TS_EQ * 8;
+constexpr int TS_SMEM = TS_CAND * 8 + TS_BINS * 4 + TS_EQ * 8;
 
 __device__ __forceinline__ float4 load_row4(const float* __restrict__ x, int j, int num_cols, bool vec_ok) {
     if (vec_ok && j + 3 < num_cols) return *reinterpret_cast<const float4*>(x + j);
@@ -259,10 +258,16 @@ __device__ __forceinline__ float key_to_float(uint32_t key) {      // inverse of
     return __uint_as_float((key & 0x80000000u) ? (key ^ 0x80000000u) : ~key);
 }
 
-__global__ void __launch_bounds__(TS_THREADS, 2)
+// TS_THREADS = 512: two CTAs per SM, for many rows; 1024: one CTA with twice the loads in flight,
+// for the few rows of a decode step (every row then has an SM to itself).
+template <int TS_THREADS>
+__global__ void __launch_bounds__(TS_THREADS, 1024 / TS_THREADS)
 topk_select_kernel(const float* __restrict__ logits, const int32_t* __restrict__ ks,
                    const int32_t* __restrict__ ke, int32_t* __restrict__ out, int num_cols,
                    int64_t logits_stride, int k) {
+    constexpr int TS_WARPS = TS_THREADS / 32;
+    constexpr int TS_LIST = TS_CAND / TS_WARPS;        // candidates per warp
+    constexpr int TS_BPT = TS_BINS / TS_THREADS;       // histogram bins per thread in the suffix sums
     extern __shared__ __align__(16) uint8_t ts_smem[];
     int* lists = reinterpret_cast<int*>(ts_smem);                               // [TS_WARPS][TS_LIST] candidate columns
     uint32_t* keys = reinterpret_cast<uint32_t*>(ts_smem) + TS_WARPS * TS_LIST; // their keys
@@ -270,7 +275,8 @@ topk_select_kernel(const float* __restrict__ logits, const int32_t* __restrict__
     uint32_t* eq_key = reinterpret_cast<uint32_t*>(hist + TS_BINS);             // [TS_EQ]
     int* eq_col = reinterpret_cast<int*>(eq_key + TS_EQ);                       // [TS_EQ]
     __shared__ int sel_bin, sel_need, n_eq_s;
-    __shared__ uint32_t kmin_s, kmax_s;
+    __shared__ uint32_t kmin_s, kmax_s, last_key_s;
+    __shared__ int last_col_s;
     __shared__ int cw[TS_WARPS], cc[TS_WARPS], wsum[TS_WARPS];
 
     const int row = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -291,7 +297,7 @@ topk_select_kernel(const float* __restrict__ logits, const int32_t* __restrict__
     const bool sampled = (hi - base) > TS_DIRECT;
     if (tid == 0) { n_eq_s = 0; kmin_s = 0xffffffffu; kmax_s = 0u; }
     if (sampled) {
-        hist[tid] = 0;                         // TS_THREADS == 2 * 256
+        if (tid < 512) hist[tid] = 0;
         __syncthreads();
         const int run_stride = span / (TS_SAMPLE / 8);   // >= 15: the runs of 8 do not overlap
         uint32_t h[TS_SAMPLE / TS_THREADS];
@@ -417,11 +423,11 @@ topk_select_kernel(const float* __restrict__ logits, const int32_t* __restrict__
         shift = max(0, 20 - (int)__clz(range | 1u));          // (range >> shift) < TS_BINS
         for (int i = lane; i < mycount; i += 32) atomicAdd(&hist[(mykeys[i] - kmin) >> shift], 1);
         __syncthreads();
-        // ---- the bin of the k-th: suffix sums over the bins, eight bins per thread
+        // ---- the bin of the k-th: suffix sums over the bins, TS_BPT bins per thread
         {
-            int hb[8], s = 0;
+            int hb[TS_BPT], s = 0;
 #pragma unroll
-            for (int i = 0; i < 8; ++i) { hb[i] = hist[8 * tid + i]; s += hb[i]; }
+            for (int i = 0; i < TS_BPT; ++i) { hb[i] = hist[TS_BPT * tid + i]; s += hb[i]; }
             int suf = s;                       // sum over the lanes >= this one
 #pragma unroll
             for (int d = 1; d < 32; d <<= 1) {
@@ -434,12 +440,12 @@ topk_select_kernel(const float* __restrict__ logits, const int32_t* __restrict__
 #pragma unroll
             for (int w = 0; w < TS_WARPS; ++w) above += (w > warp) ? wsum[w] : 0;
             if (above < k && above + s >= k) {  // exactly one thread: total > k
-                int cum = above, b = 7;
-                for (; b > 0; --b) {
-                    if (cum + hb[b] >= k) break;
-                    cum += hb[b];
+                int cum = above, b = TS_BPT - 1;
+#pragma unroll
+                for (int i = TS_BPT - 1; i > 0; --i) {
+                    if (b == i && cum + hb[i] < k) { cum += hb[i]; b = i - 1; }
                 }
-                sel_bin = 8 * tid + b; sel_need = k - cum;
+                sel_bin = TS_BPT * tid + b; sel_need = k - cum;
             }
             __syncthreads();
         }
@@ -460,16 +466,28 @@ topk_select_kernel(const float* __restrict__ logits, const int32_t* __restrict__
         }
     }
     const int n_eq = take_all ? 0 : n_eq_s;
+    // The last of the bin's entries to be taken, in the order (key descending, column ascending):
+    // every entry of the bin finds its own rank once (n_eq^2 comparisons spread over the CTA), the
+    // one of rank need_eq - 1 publishes itself, and membership is then a comparison with it.
+    if (!take_all && need_eq < n_eq) {
+        for (int i = tid; i < n_eq; i += TS_THREADS) {
+            const uint32_t key = eq_key[i];
+            const int c = eq_col[i];
+            int rank = 0;
+            for (int j = 0; j < n_eq; ++j) rank += (eq_key[j] > key) || (eq_key[j] == key && eq_col[j] < c);
+            if (rank == need_eq - 1) { last_key_s = key; last_col_s = c; }
+        }
+        __syncthreads();
+    }
+    const bool all_eq = need_eq >= n_eq;
+    const uint32_t last_key = all_eq ? 0u : last_key_s;
+    const int last_col = all_eq ? 0x7fffffff : last_col_s;
     auto chosen = [&](int i) -> bool {
         if (take_all) return true;
         const uint32_t key = mykeys[i];
         const int bin = (int)((key - kmin) >> shift);
         if (bin != thr_bin) return bin > thr_bin;
-        if (need_eq >= n_eq) return true;
-        const int c = mine[i];
-        int rank = 0;                          // entries of the bin that go first: larger key, or equal key and lower column
-        for (int j = 0; j < n_eq; ++j) rank += (eq_key[j] > key) || (eq_key[j] == key && eq_col[j] < c);
-        return rank < need_eq;
+        return key > last_key || (key == last_key && mine[i] <= last_col);
     };
     // ---- write: every warp its own list, in list order
     int nsel = 0;
@@ -590,14 +608,20 @@ int launch_topk(const float* logits, const int32_t* ks, const int32_t* ke, int32
         return check_launch("topk_kernel");
     }
     static bool attr_set[64] = {};
+    static int sms[64] = {};
     int dev = 0;
     cudaGetDevice(&dev);
     if (dev < 64 && !attr_set[dev]) {
-        const cudaError_t e = cudaFuncSetAttribute(topk_select_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, TS_SMEM);
+        cudaError_t e = cudaFuncSetAttribute(topk_select_kernel<512>, cudaFuncAttributeMaxDynamicSharedMemorySize, TS_SMEM);
+        if (e == cudaSuccess) e = cudaFuncSetAttribute(topk_select_kernel<1024>, cudaFuncAttributeMaxDynamicSharedMemorySize, TS_SMEM);
         if (e != cudaSuccess) return set_error((int)e, "topk_select_kernel: shared memory: %s", cudaGetErrorString(e));
+        cudaDeviceGetAttribute(&sms[dev], cudaDevAttrMultiProcessorCount, dev);
         attr_set[dev] = true;
     }
-    topk_select_kernel<<<num_rows, TS_THREADS, TS_SMEM, stream>>>(logits, ks, ke, out, num_cols, logits_stride, k);
+    if (num_rows <= sms[dev < 64 ? dev : 0])       // every row has an SM to itself
+        topk_select_kernel<1024><<<num_rows, 1024, TS_SMEM, stream>>>(logits, ks, ke, out, num_cols, logits_stride, k);
+    else
+        topk_select_kernel<512><<<num_rows, 512, TS_SMEM, stream>>>(logits, ks, ke, out, num_cols, logits_stride, k);
     if (const int rc = check_launch("topk_select_kernel")) return rc;
     // rows the one-read kernel gave up on (it marks them) are redone by the multi-pass kernel
     topk_kernel<<<num_rows, TK_THREADS, 0, stream>>>(logits, ks, ke, out, num_cols, logits_stride, k, 1);

@@ -54,6 +54,8 @@ class GraphedIndexedDecode:
                  block_table: Optional[torch.Tensor] = None, attn_sink: Optional[torch.Tensor] = None,
                  impl: int = IMPL_AUTO):
         dev = kv_cache.device
+        # the graph holds raw pointers into these: they must live as long as it does
+        self.kv_cache, self.ki, self.k_scale, self.block_table, self.attn_sink = kv_cache, ki, k_scale, block_table, attn_sink
         self.q = torch.zeros((num_tokens, num_heads, 576), dtype=torch.bfloat16, device=dev)
         self.qi = torch.zeros((num_tokens, indexer_heads, 128), dtype=torch.float8_e4m3fn, device=dev)
         self.weights = torch.zeros((num_tokens, indexer_heads), dtype=torch.float32, device=dev)
