@@ -405,6 +405,16 @@ topk_select_kernel(const float* __restrict__ logits, const int32_t* __restrict__
     const bool take_all = total <= k;
     int thr_bin = -1, need_eq = 0, shift = 0;  // chosen: bin > thr_bin, and need_eq of the entries of bin thr_bin
     uint32_t kmin = 0;
+    // Bins are linear in key space (robust against outliers: a key step is a relative step of the
+    // value) unless the candidates lie on both sides of zero: most of the key range between a
+    // small negative and a small positive value belongs to magnitudes no logit has, so the bins
+    // are then linear in the value itself.
+    bool by_value = false;
+    float vmin_f = 0.f, vscale = 0.f;
+    auto bin_of = [&](uint32_t key) -> int {
+        if (!by_value) return (int)((key - kmin) >> shift);
+        return min((int)((key_to_float(key) - vmin_f) * vscale), TS_BINS - 1);
+    };
     if (!take_all) {
         // ---- keys of the candidates, and the range they span
         uint32_t vmin = 0xffffffffu, vmax = 0u;
@@ -421,7 +431,11 @@ topk_select_kernel(const float* __restrict__ logits, const int32_t* __restrict__
         kmin = kmin_s;
         const uint32_t range = kmax_s - kmin;
         shift = max(0, 20 - (int)__clz(range | 1u));          // (range >> shift) < TS_BINS
-        for (int i = lane; i < mycount; i += 32) atomicAdd(&hist[(mykeys[i] - kmin) >> shift], 1);
+        vmin_f = key_to_float(kmin);
+        const float vmax_f = key_to_float(kmax_s);
+        by_value = vmin_f < 0.f && vmax_f > 0.f && (vmax_f - vmin_f) < INFINITY;
+        vscale = by_value ? (float)TS_BINS / (vmax_f - vmin_f) : 0.f;
+        for (int i = lane; i < mycount; i += 32) atomicAdd(&hist[bin_of(mykeys[i])], 1);
         __syncthreads();
         // ---- the bin of the k-th: suffix sums over the bins, TS_BPT bins per thread
         {
@@ -454,7 +468,7 @@ topk_select_kernel(const float* __restrict__ logits, const int32_t* __restrict__
         // ---- the entries of that bin, to be ranked one against the other
         for (int i = lane; i < mycount; i += 32) {
             const uint32_t key = mykeys[i];
-            if ((int)((key - kmin) >> shift) == thr_bin) {
+            if (bin_of(key) == thr_bin) {
                 const int at = atomicAdd(&n_eq_s, 1);
                 if (at < TS_EQ) { eq_key[at] = key; eq_col[at] = mine[i]; }
             }
@@ -485,7 +499,7 @@ topk_select_kernel(const float* __restrict__ logits, const int32_t* __restrict__
     auto chosen = [&](int i) -> bool {
         if (take_all) return true;
         const uint32_t key = mykeys[i];
-        const int bin = (int)((key - kmin) >> shift);
+        const int bin = bin_of(key);
         if (bin != thr_bin) return bin > thr_bin;
         return key > last_key || (key == last_key && mine[i] <= last_col);
     };

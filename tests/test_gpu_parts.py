@@ -217,6 +217,12 @@ def test_topk_one_read_paths():
     assert torch.equal(got, again)
     _check_topk_rows(got.cpu(), masked, k)
     assert int((got[3] >= 0).sum().item()) == int(torch.isfinite(masked[3]).sum())
+    # thresholds near zero: the candidates lie on both sides of zero (bins linear in the value)
+    near = torch.randn(6, 150000) * 0.03 + torch.tensor([-0.060, -0.066, -0.068, -0.070, -0.075, -0.2]).view(-1, 1)
+    near[4, ::7] = 0.0
+    near[4, 3::11] = -0.0
+    got = indexer.topk_indices(near.to(DEV), None, None, k).cpu()
+    _check_topk_rows(got, near, k)
     # misaligned rows: a view that starts one float into the buffer
     shifted = torch.empty(3, 20001, device=DEV)
     shifted[:, 1:] = dev_logits[:3, 50000:70000]
