@@ -73,13 +73,13 @@ def _check_selection(got, full_logits, k):
             assert int((full_logits[r] > thr).sum()) == int((vals > thr).sum())
 
 
-@pytest.mark.parametrize("world", [2, 4])
-def test_indexer_cp_pieces_on_one_gpu(world):
+@pytest.mark.parametrize("world,s_k,k", [(2, 4096, 256), (4, 4096, 256), (4, 16384, 2048), (8, 32768, 2048)])
+def test_indexer_cp_pieces_on_one_gpu(world, s_k, k):
     """Per-shard logits + top-k, candidates side by side, merge: the distributed selection without
     the collective, against the oracle's logits over the whole context."""
     from sparse_mla_sm120_b200 import cp
     dev = torch.device("cuda:0")
-    s_q, h, s_k, k = 6, 64, 4096, 256
+    s_q, h = 6, 64
     q, key, k_scale, w, ks, ke = _indexer_case(41, s_q, h, s_k)
     ks[1], ke[1] = 1500, 1700          # fewer than k candidates, inside one shard (world 2) / two shards (world 4)
     ks[2], ke[2] = 900, 3300
