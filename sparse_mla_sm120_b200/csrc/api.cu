@@ -53,13 +53,6 @@ extern "C" {
 const char* smla_last_error(void) { return g_err; }
 int smla_version(void) { return 100; }
 
-// Debugging aid, not part of the public header: registers a device buffer of 1 + 2*capacity
-// int64 (zeroed by the caller) that CTA 0 of the tcgen05 attention kernel fills with a timeline.
-int smla_debug_set_trace(void* buf, int capacity) {
-    set_attn_trace((long long*)buf, capacity);
-    return 0;
-}
-
 int smla_num_sms(void) {
     static int cache[64] = {};
     int dev = 0;
@@ -110,7 +103,7 @@ int smla_decode_splitkv(const void* q, const void* kv, const int32_t* indices,
     p.num_tokens = num_tokens; p.num_heads = num_heads; p.topk = topk; p.num_parts = num_sm_parts;
     p.page_block_size = page_block_size; p.block_stride = kv_block_stride_bytes; p.sm_scale = sm_scale;
     if (impl == SMLA_IMPL_SCALAR) return launch_attn_scalar(p, (cudaStream_t)stream);
-    if (impl == SMLA_IMPL_TC_PAIR) return launch_attn_tc2(p, (cudaStream_t)stream);
+    if (impl == SMLA_IMPL_TC_PAIR) return launch_attn_pair(p, (cudaStream_t)stream);
     return launch_attn_tc(p, (cudaStream_t)stream);
 }
 
@@ -147,7 +140,7 @@ int smla_decode_partial(const void* q, const void* kv, const int32_t* indices,
     p.force_partial = 1;
     p.page_block_size = page_block_size; p.block_stride = kv_block_stride_bytes; p.sm_scale = sm_scale;
     const int e = (impl == SMLA_IMPL_SCALAR) ? launch_attn_scalar(p, (cudaStream_t)stream)
-                  : (impl == SMLA_IMPL_TC_PAIR) ? launch_attn_tc2(p, (cudaStream_t)stream)
+                  : (impl == SMLA_IMPL_TC_PAIR) ? launch_attn_pair(p, (cudaStream_t)stream)
                                                 : launch_attn_tc(p, (cudaStream_t)stream);
     if (e) return e;
     return launch_combine_f32(o_accum, lse_accum, o_part, lse_part, num_splits, num_tokens, num_heads,
@@ -195,7 +188,7 @@ int smla_prefill(const void* q, const void* kv, const int32_t* indices,
     p.num_tokens = num_tokens; p.num_heads = num_heads; p.topk = topk; p.num_parts = num_tokens;
     p.page_block_size = page_block_size; p.block_stride = kv_block_stride_bytes; p.sm_scale = sm_scale;
     if (impl == SMLA_IMPL_SCALAR) return launch_attn_scalar(p, (cudaStream_t)stream);
-    if (impl == SMLA_IMPL_TC_PAIR) return launch_attn_tc2(p, (cudaStream_t)stream);
+    if (impl == SMLA_IMPL_TC_PAIR) return launch_attn_pair(p, (cudaStream_t)stream);
     return launch_attn_tc(p, (cudaStream_t)stream);
 }
 

@@ -1,0 +1,85 @@
+// Device helpers shared by the tensor-core attention kernels: a partition's work list, power-of-two
+// scale arithmetic and e4m3 / bf16 packing.
+#pragma once
+
+#include "common.cuh"
+
+namespace smla {
+namespace attn {
+
+struct Work {   // one request's share of a partition
+    int req, blk0, nblk, len, split_idx;
+    bool no_split;
+};
+
+__device__ __forceinline__ SchedMeta load_meta(const AttnParams& p, int part) {
+    SchedMeta m;
+    if (p.sched != nullptr) {
+        m = p.sched[part];
+    } else {
+        // no scheduler: the CTA pairs of the grid share the requests as contiguous, whole ranges
+        // (one request each when there are at least as many pairs as requests)
+        const long long pairs = gridDim.x >> 1;
+        m.begin_req = (int)((long long)part * p.num_tokens / pairs);
+        m.end_req = (int)((long long)(part + 1) * p.num_tokens / pairs) - 1;
+        m.begin_block = 0; m.end_block = 0x7fffffff;
+        m.begin_split = 0; m.first_split = m.last_split = 0; m.pad = 0;
+    }
+    return m;
+}
+
+__device__ __forceinline__ bool get_work(const AttnParams& p, const SchedMeta& m, int req, Work& w) {
+    int len = p.topk_length ? p.topk_length[req] : p.topk;
+    len = min(len, p.topk);
+    const int total = max((len + BLOCK_N - 1) / BLOCK_N, 1);
+    const int b0 = (req == m.begin_req) ? m.begin_block : 0;
+    const int b1 = min((req == m.end_req) ? m.end_block : total, total);
+    w.req = req; w.blk0 = b0; w.nblk = b1 - b0; w.len = len;
+    w.no_split = !p.force_partial &&
+                 ((req == m.begin_req) ? !m.first_split : ((req == m.end_req) ? !m.last_split : true));
+    w.split_idx = p.num_splits ? p.num_splits[req] + ((req == m.begin_req) ? m.begin_split : 0) : 0;
+    return w.nblk > 0;
+}
+
+__device__ __forceinline__ float pow2_ceil(float x) {
+    uint32_t b = __float_as_uint(x);
+    if (b & 0x007fffffu) b = (b + 0x00800000u) & 0x7f800000u;
+    return __uint_as_float(b);
+}
+
+__device__ __forceinline__ float ex2(float x) {   // 2^x, ex2(-inf) = +0
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
+__device__ __forceinline__ uint32_t pack_e4m3x4(float a, float b, float c, float d) {
+    uint16_t lo, hi;
+    asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;" : "=h"(lo) : "f"(b), "f"(a));
+    asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;" : "=h"(hi) : "f"(d), "f"(c));
+    return (uint32_t)lo | ((uint32_t)hi << 16);
+}
+
+// Multiplies four packed e4m3 values by a power of two (given as half2) with rounding.
+__device__ __forceinline__ uint32_t rescale_e4m3x4(uint32_t w, __half2 ratio) {
+    uint32_t lo, hi;
+    asm("cvt.rn.f16x2.e4m3x2 %0, %1;" : "=r"(lo) : "h"((uint16_t)(w & 0xffffu)));
+    asm("cvt.rn.f16x2.e4m3x2 %0, %1;" : "=r"(hi) : "h"((uint16_t)(w >> 16)));
+    __half2 a = __hmul2(*reinterpret_cast<__half2*>(&lo), ratio);
+    __half2 b = __hmul2(*reinterpret_cast<__half2*>(&hi), ratio);
+    uint16_t ra, rb;
+    asm("cvt.rn.satfinite.e4m3x2.f16x2 %0, %1;" : "=h"(ra) : "r"(*reinterpret_cast<uint32_t*>(&a)));
+    asm("cvt.rn.satfinite.e4m3x2.f16x2 %0, %1;" : "=h"(rb) : "r"(*reinterpret_cast<uint32_t*>(&b)));
+    return (uint32_t)ra | ((uint32_t)rb << 16);
+}
+
+__device__ __forceinline__ uint32_t mul_bf16x2(uint32_t w, __nv_bfloat162 f) {
+    __nv_bfloat162 r = __hmul2(*reinterpret_cast<__nv_bfloat162*>(&w), f);
+    return *reinterpret_cast<uint32_t*>(&r);
+}
+
+__device__ __forceinline__ float bf16lo(uint32_t w) { return __uint_as_float(w << 16); }
+__device__ __forceinline__ float bf16hi(uint32_t w) { return __uint_as_float(w & 0xffff0000u); }
+
+}  // namespace attn
+}  // namespace smla

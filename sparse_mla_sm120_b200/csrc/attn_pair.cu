@@ -1,0 +1,748 @@
+// Sparse-MLA attention on a pair of SMs (sm_100a): split-KV decode and prefill, tcgen05.mma.cta_group::2.
+//
+// Work unit.  A cluster of two CTAs owns one scheduler partition (a run of 64-token blocks of
+// consecutive requests, see sched.cu; without a scheduler: a contiguous share of the requests).  Every
+// MMA runs over the pair with M = 128: CTA r holds half of the (<= 128) query heads and, of every
+// 128-token tile, the 64 rows it gathered itself.
+//   * Q.K^T:  A = this CTA's Q rows, B = the two CTAs' own gathered rows (N = 128 tokens), so a
+//     656-byte row is gathered into ONE shared memory and each CTA receives the scores of its
+//     heads against all 128 tokens (lanes 0-63: tokens 0-63, lanes 64-127: tokens 64-127).
+//   * P.V:    A = this CTA's P' (64 heads x 128 tokens, shared memory), B = V^T with the N = 256
+//     output dims of an MMA split between the CTAs: CTA r supplies dims [256 r, 256 r + 256) of
+//     all 128 tokens.  For its own tokens these are bytes it already holds (copied inside shared
+//     memory into the V slots); for the partner's tokens it gathers the 256-byte half rows.
+//     Each CTA accumulates O for its heads over all 512 dims (lanes 0-63: dims 0-255, lanes
+//     64-127: dims 256-511; 256 columns of tensor memory).
+// Per token a CTA pair takes in 656 + 2 x 256 bytes instead of 2 x 656, and no score or softmax
+// work is duplicated.
+//
+// Numerics (the FP8 class of the reference's V32 kernels, which quantise Q and P to e4m3:
+// csrc/kernel/common/fp8_quant.cuh:44-103, csrc/kernel/decode/decode_v2_kernel.cuh:414-493):
+//   * Q no-PE is quantised to e4m3 with one power-of-two scale sq_h per head; Q RoPE stays bf16
+//     and is pre-divided by that scale.
+//   * K/V bytes are consumed as stored.  A row whose four 128-value tiles carry different
+//     scales is re-expressed against its largest scale s_t (a power-of-two shift: exact while the
+//     shifted value stays a normal e4m3 number, i.e. for scale ratios up to 2^9 on values near the
+//     tile maximum; below that the value rounds at 2^-9 of the row's largest tile maximum);
+//     K RoPE is pre-divided by s_t.  One accumulator then holds S = (q . k) / (sq_h * s_t).
+//   * The row scale of V is folded into the exponent: z = S*sq_h*s_t*sm_scale*log2e + log2(s_t),
+//     P' = 2^(z - m) with m the (lazily updated) running maximum of z, so that
+//     O_acc = sum_t P'_t * Vfp8_t needs no per-tile scale; the denominator is tracked apart as
+//     l = sum_t P'_t / s_t in fp32.  O = O_acc / l, LSE = log2(l) + m (base 2, as the reference).
+//   * P' is rounded to e4m3 (times 2^P_SHIFT); the accumulator is rescaled only when a row
+//     maximum grows by more than 2^RESCALE_TAU, which is exact because l and O share m.
+//   * Invalid entries (index < 0, position >= topk_length) are never loaded: their shared-memory
+//     rows are zero-filled and their weight is exactly 0 (NaN-safe, decode_v2_kernel.cuh:262-278).
+//
+// Warp roles (768 threads per CTA): warps 0-7 softmax + epilogue + Q quantisation (thread = one
+// head x 32 tokens of a tile; the four warps that share 32 heads exchange row maxima through
+// shared memory), warps 8-11 gather issuers (16-byte cp.async, never waiting for data), warps
+// 12-19 tile fix-up (RoPE pre-division, uneven-scale rewrite, per-token scale triples, the copy
+// of own V bytes), warp 20 lane 0 issues the score MMAs and warp 21 lane 0 the P.V MMAs -- in
+// the even CTA only, which is also where the barriers that collect arrivals from both CTAs
+// live.  Completion of MMAs reaches both CTAs through one tcgen05.commit per CTA (no multicast).
+// Every wait is bounded; a wait that gives up records a code in status[] and the CTA drains and
+// exits.  Warps that meet at a named barrier leave the loop together (a warp whose wait gave up
+// still goes to the next named barrier, where all of them see the flag).
+#include "attn_common.cuh"
+#include "sm100_ptx.cuh"
+
+namespace smla {
+
+namespace {
+
+using namespace ptx;
+using namespace attn;
+
+constexpr int N_SM_WARPS = 8, N_PR_WARPS = 4, N_FX_WARPS = 8;
+constexpr int FX_ROWS = 8;    // rows of a tile per fix-up warp
+constexpr int FX_WARP0 = N_SM_WARPS + N_PR_WARPS;
+constexpr int MMA_WARP = FX_WARP0 + N_FX_WARPS;
+constexpr int PAIR_THREADS = (MMA_WARP + 4) * 32;
+// Register budgets after the warpgroups trade registers (see attn_tc.cu for the rule they obey).
+constexpr int REGS_LAUNCH = 80, REGS_SOFTMAX = 128, REGS_OTHER = 48;
+static_assert(N_SM_WARPS * 32 * REGS_SOFTMAX + (N_PR_WARPS + N_FX_WARPS) * 32 * REGS_OTHER + 128 * REGS_LAUNCH
+                  <= PAIR_THREADS * REGS_LAUNCH, "register budgets exceed what the CTA owns");
+static_assert(65536 / PAIR_THREADS / 8 * 8 == REGS_LAUNCH, "launch-time registers per thread");
+
+constexpr int TILE_N = 128;            // tokens per tile: two scheduler blocks, 64 rows gathered by each CTA
+constexpr int OWN_N = 64;
+constexpr int NK = 2, NV = 2;          // K stages (own rows) and V stages (V slots + scale triples)
+constexpr int P_SHIFT = 5;             // P' is stored as e4m3(P' * 2^P_SHIFT)
+constexpr float RESCALE_TAU = 3.0f;    // lazy-rescale threshold (log2 units); P' <= 2^TAU
+
+// shared-memory map (bytes from a 1024-aligned base)
+constexpr uint32_t CHUNK = OWN_N * 128;              // one 128-dim chunk of 64 rows, K-major 128B swizzle
+constexpr uint32_t QN_OFF = 0;                       // Q no-PE e4m3: 4 chunks x [64 heads x 128 B]
+constexpr uint32_t QR_OFF = QN_OFF + 4 * CHUNK;      // Q RoPE bf16: [64 heads x 128 B]
+constexpr uint32_t PB_OFF = QR_OFF + CHUNK;          // P' e4m3: 2 buffers x [64 heads x 128 tokens]
+constexpr uint32_t KS_OFF = PB_OFF + 2 * CHUNK;      // K stages
+constexpr uint32_t KS_ROPE = 4 * CHUNK;              //   RoPE of the own rows
+constexpr uint32_t KS_RAW = KS_ROPE + CHUNK;         //   [128 tokens x 16 B] the rows' 4 fp32 scales as gathered (own and partner rows)
+constexpr uint32_t KS_BYTES = KS_RAW + TILE_N * 16;  // 43008
+constexpr uint32_t VS_OFF = KS_OFF + NK * KS_BYTES;  // V stages
+constexpr uint32_t VSLOT = 32 * 128;                 //   slot (kb, nb): 32 tokens x 128 dims, at (2 kb + nb) * VSLOT
+constexpr uint32_t VS_RAW = 8 * VSLOT;               //   [64 x 16 B] scales of the partner's rows
+constexpr uint32_t VS_TRIP = VS_RAW + OWN_N * 16;    //   [128 x 16 B] per token (s_t, log2 s_t, 1/s_t, 0)
+constexpr uint32_t VS_BYTES = VS_TRIP + TILE_N * 16; // 35840
+constexpr uint32_t XCH_OFF = VS_OFF + NV * VS_BYTES; // row-maximum exchange [2][4][64] fp32, then Q scales [64] fp32
+constexpr uint32_t XCH_BYTES = 2 * 4 * 64 * 4 + 64 * 4;
+constexpr uint32_t BAR_OFF = XCH_OFF + XCH_BYTES;
+// barriers (8 B each).  "P" barriers collect arrivals from both CTAs and are used in the even CTA only.
+constexpr int BAR_KLOADED = 0, BAR_KFULLP = BAR_KLOADED + NK, BAR_TRIP = BAR_KFULLP + NK, BAR_KEMPTY = BAR_TRIP + NK,
+              BAR_VLOADED = BAR_KEMPTY + NK, BAR_VFULLP = BAR_VLOADED + NV, BAR_VEMPTY = BAR_VFULLP + NV,
+              BAR_SREADY = BAR_VEMPTY + NV, BAR_SFREEP = BAR_SREADY + 2, BAR_PREADYP = BAR_SFREEP + 2,
+              BAR_PVDONE = BAR_PREADYP + 2, BAR_QREADYP = BAR_PVDONE + 2, NBAR = BAR_QREADYP + 1;
+constexpr uint32_t MISC_OFF = BAR_OFF + NBAR * 8;    // tmem base (4 B), abort flag (4 B)
+constexpr uint32_t SMEM_BYTES = MISC_OFF + 16;
+constexpr uint32_t SMEM_ALLOC = SMEM_BYTES + 1024;   // slack for the 1024-byte alignment
+static_assert(SMEM_ALLOC <= 227 * 1024, "shared memory budget");
+static_assert(KS_BYTES % 1024 == 0 && VS_BYTES % 1024 == 0 && KS_OFF % 1024 == 0, "swizzled tiles need 1024-byte alignment");
+
+constexpr uint32_t TMEM_COLS = 512;
+constexpr uint32_t TM_O = 0, TM_S = 256;   // O 256 columns; score buffer b at 256 + 64 b
+
+constexpr uint32_t IDESC_QK_F8 = instr_desc(FMT_E4M3, FMT_E4M3, false, false, 128, TILE_N);
+constexpr uint32_t IDESC_QK_BF16 = instr_desc(FMT_BF16, FMT_BF16, false, false, 128, TILE_N);
+constexpr uint32_t IDESC_PV_F8 = instr_desc(FMT_E4M3, FMT_E4M3, false, true, 128, 256);
+constexpr uint32_t DESC_HI_SW128 = desc_hi(1024, (uint32_t)SWIZZLE_128B);
+
+// give-up codes reported through status[0]
+enum { W_KEMPTY = 21, W_KLOADED = 22, W_KFULL = 23, W_TRIP = 24, W_VEMPTY = 25, W_VLOADED = 26, W_VFULL = 27,
+       W_SREADY = 28, W_SFREE = 29, W_PREADY = 30, W_PVDONE = 31, W_QREADY = 32 };
+
+__device__ __forceinline__ uint32_t swz(uint32_t row, uint32_t chunk16) { return row * 128u + ((chunk16 ^ (row & 7u)) << 4); }
+
+// ---------------------------------------------------------------------------------------------
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PAIR_THREADS, 1) attn_pair_kernel(const AttnParams p) {
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t raw = smem_u32(smem_raw);
+    const uint32_t base = (raw + 1023u) & ~1023u;
+    uint8_t* sm = smem_raw + (base - raw);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(sm + MISC_OFF + 4);
+    volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(sm + MISC_OFF);
+    auto bar = [&](int i) -> uint32_t { return base + BAR_OFF + 8u * i; };
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const uint32_t rank = cluster_ctarank();          // 0: the CTA that issues the MMAs
+    const int part = blockIdx.x >> 1;
+    const SchedMeta meta = load_meta(p, part);
+    const int heads_cta = (p.num_heads + 1) >> 1;     // heads per CTA
+    const int head0 = (int)rank * heads_cta;
+
+    if (tid == 0) {
+        for (int s = 0; s < NK; ++s) {
+            mbar_init(bar(BAR_KLOADED + s), N_PR_WARPS * 32);   // one arrive per issuer thread, when its copies have landed
+            mbar_init(bar(BAR_KFULLP + s), 2 * N_FX_WARPS);
+            mbar_init(bar(BAR_TRIP + s), N_FX_WARPS);
+            mbar_init(bar(BAR_KEMPTY + s), 1 + N_FX_WARPS);     // the score MMAs have read the stage and the own V bytes are copied
+        }
+        for (int s = 0; s < NV; ++s) {
+            mbar_init(bar(BAR_VLOADED + s), N_PR_WARPS * 32);
+            mbar_init(bar(BAR_VFULLP + s), 2 * N_FX_WARPS);
+            mbar_init(bar(BAR_VEMPTY + s), 1);
+        }
+        for (int b = 0; b < 2; ++b) {
+            mbar_init(bar(BAR_SREADY + b), 1);
+            mbar_init(bar(BAR_SFREEP + b), 2 * N_SM_WARPS);
+            mbar_init(bar(BAR_PREADYP + b), 2 * N_SM_WARPS);
+            mbar_init(bar(BAR_PVDONE + b), 1);
+        }
+        mbar_init(bar(BAR_QREADYP), 2 * N_SM_WARPS);
+        *abort_flag = 0;
+        mbar_init_fence();
+    }
+    if (warp == MMA_WARP) {
+        tmem_alloc_pair(base + MISC_OFF, TMEM_COLS);
+        tmem_relinquish_pair();
+    }
+    tc_fence_before();
+    __syncthreads();
+    cluster_sync_all();          // the partner's barriers exist before anything arrives on them
+    tc_fence_after();
+    const uint32_t tmem = *tmem_slot;
+    auto barp = [&](int i) -> uint32_t { return mapa_shared(bar(i), 0); };   // the even CTA's copy of barrier i
+
+    const int last_req = min(meta.end_req, p.num_tokens - 1);
+
+    if (warp < N_SM_WARPS) setmaxnreg_inc<REGS_SOFTMAX>();
+    else if (warp < MMA_WARP) setmaxnreg_dec<REGS_OTHER>();
+
+    if (warp < N_SM_WARPS) {
+        // =================================================================== softmax + epilogue
+        const int quarter = warp & 3, ch = warp >> 2;     // TMEM lane quarter, column half of a score buffer
+        const int grp = quarter & 1;                      // warps with equal grp share 32 heads
+        const int thalf = quarter >> 1;                   // scores: token half; accumulator: half of the output dims
+        const int hrow = grp * 32 + lane;                 // head row inside this CTA
+        const int head = head0 + hrow;
+        const bool live = hrow < heads_cta && head < p.num_heads;
+        const int xpart = thalf * 2 + ch;                 // which of the four partial rows this thread holds
+        const uint32_t lane_addr = tmem + ((uint32_t)(quarter * 32) << 16);
+        float* xch = reinterpret_cast<float*>(sm + XCH_OFF);   // [2][4][64]
+        float* sqv = xch + 2 * 4 * 64;                         // [64]
+        const bool wide_out = (reinterpret_cast<size_t>(p.out) & 31) == 0;        // rows are 1024 bytes apart
+        const bool wide_acc = (reinterpret_cast<size_t>(p.o_accum) & 31) == 0;
+        const int gt = ((warp >> 1) << 5) + lane;         // thread index inside the group of four warps (0..127)
+        uint32_t it = 0;                                  // running tile counter of this CTA
+        bool dead = false;                                // a wait of this warp gave up: no more work, only barriers
+        bool stop = false;
+        for (int req = meta.begin_req; req <= last_req && !stop; ++req) {
+            Work w;
+            if (!get_work(p, meta, req, w)) continue;
+            const int nst = (w.nblk + 1) >> 1;
+            // ---- Q: the group quantises its 32 heads; four threads per head, 128 no-PE dims + 16 RoPE dims each ----
+            if (!dead) {
+                const int qrow = grp * 32 + (gt >> 2), qpart = gt & 3;
+                const int qhead = head0 + qrow;
+                const bool qv = qrow < heads_cta && qhead < p.num_heads;
+                const __nv_bfloat16* src = p.q + ((size_t)req * p.num_heads + (qv ? qhead : 0)) * D_QK;
+                float am = 0.f;
+                uint4 x[16];
+#pragma unroll
+                for (int i = 0; i < 16; ++i) {
+                    x[i] = qv ? __ldg(reinterpret_cast<const uint4*>(src + qpart * 128 + 8 * i)) : make_uint4(0, 0, 0, 0);
+                    am = fmaxf(am, fmaxf(fmaxf(fmaxf(fabsf(bf16lo(x[i].x)), fabsf(bf16hi(x[i].x))), fmaxf(fabsf(bf16lo(x[i].y)), fabsf(bf16hi(x[i].y)))),
+                                         fmaxf(fmaxf(fabsf(bf16lo(x[i].z)), fabsf(bf16hi(x[i].z))), fmaxf(fabsf(bf16lo(x[i].w)), fabsf(bf16hi(x[i].w))))));
+                }
+                uint4 r0 = make_uint4(0, 0, 0, 0), r1 = r0;
+                if (qv) {
+                    r0 = __ldg(reinterpret_cast<const uint4*>(src + D_NOPE + qpart * 16));
+                    r1 = __ldg(reinterpret_cast<const uint4*>(src + D_NOPE + qpart * 16 + 8));
+                }
+                am = fmaxf(am, __shfl_xor_sync(0xffffffffu, am, 1));
+                am = fmaxf(am, __shfl_xor_sync(0xffffffffu, am, 2));
+                const float sq = pow2_ceil(fmaxf(am, 1e-4f) * (1.f / 448.f));
+                const float iq = __uint_as_float(0x7f000000u - __float_as_uint(sq));   // 1/sq, sq a power of two
+                uint8_t* qdst = sm + QN_OFF + qpart * CHUNK;
+#pragma unroll
+                for (int c = 0; c < 8; ++c) {
+                    const uint4 a = x[2 * c], b4 = x[2 * c + 1];
+                    uint4 o;
+                    o.x = pack_e4m3x4(bf16lo(a.x) * iq, bf16hi(a.x) * iq, bf16lo(a.y) * iq, bf16hi(a.y) * iq);
+                    o.y = pack_e4m3x4(bf16lo(a.z) * iq, bf16hi(a.z) * iq, bf16lo(a.w) * iq, bf16hi(a.w) * iq);
+                    o.z = pack_e4m3x4(bf16lo(b4.x) * iq, bf16hi(b4.x) * iq, bf16lo(b4.y) * iq, bf16hi(b4.y) * iq);
+                    o.w = pack_e4m3x4(bf16lo(b4.z) * iq, bf16hi(b4.z) * iq, bf16lo(b4.w) * iq, bf16hi(b4.w) * iq);
+                    *reinterpret_cast<uint4*>(qdst + swz(qrow, c)) = o;
+                }
+                const __nv_bfloat162 f = __float2bfloat162_rn(iq);
+                r0.x = mul_bf16x2(r0.x, f); r0.y = mul_bf16x2(r0.y, f); r0.z = mul_bf16x2(r0.z, f); r0.w = mul_bf16x2(r0.w, f);
+                r1.x = mul_bf16x2(r1.x, f); r1.y = mul_bf16x2(r1.y, f); r1.z = mul_bf16x2(r1.z, f); r1.w = mul_bf16x2(r1.w, f);
+                *reinterpret_cast<uint4*>(sm + QR_OFF + swz(qrow, 2 * qpart)) = r0;
+                *reinterpret_cast<uint4*>(sm + QR_OFF + swz(qrow, 2 * qpart + 1)) = r1;
+                if (qpart == 0) sqv[qrow] = sq;
+                fence_proxy_async();
+            }
+            if (named_bar_or(1 + grp, 128, dead || *abort_flag != 0)) { stop = true; break; }
+            const float my_sqc = live ? sqv[hrow] * p.sm_scale * LOG2E : 0.f;
+            __syncwarp();
+            if (lane == 0) mbar_arrive_cluster(barp(BAR_QREADYP));
+
+            float m_run = -INFINITY;   // running maximum of z (lags by at most RESCALE_TAU)
+            float l_run = 0.f;         // this thread's share of the sum of P'/s_t (scaled by 2^P_SHIFT)
+            float x_max = -INFINITY;   // this thread's share of the maximum of the scaled logits (max_logits output)
+            for (int j = 0; j < nst; ++j, ++it) {
+                const uint32_t b = it & 1u, vs = it % NV;
+                float z[32];
+                float mx_loc = -INFINITY;
+                const float4* tok = reinterpret_cast<const float4*>(sm + VS_OFF + vs * VS_BYTES + VS_TRIP) + 64 * thalf + 32 * ch;
+                if (!dead) dead = !mbar_wait_hot(bar(BAR_SREADY + b), (it >> 1) & 1u, abort_flag, W_SREADY);
+                if (!dead) dead = !mbar_wait(bar(BAR_TRIP + (it % NK)), (it / NK) & 1u, abort_flag, W_TRIP);
+                if (!dead) {
+                    tc_fence_after();
+                    uint32_t sv[32];
+                    tmem_ld32(lane_addr + TM_S + 64 * b + 32 * ch, sv);
+                    tmem_wait_ld();
+                    tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive_cluster(barp(BAR_SFREEP + b));   // the score buffer may be overwritten
+                    float mx0 = -INFINITY, mx1 = -INFINITY;
+#pragma unroll
+                    for (int t = 0; t < 32; t += 4) {
+                        const float2 a0 = *reinterpret_cast<const float2*>(tok + t), a1 = *reinterpret_cast<const float2*>(tok + t + 1);
+                        const float2 a2 = *reinterpret_cast<const float2*>(tok + t + 2), a3 = *reinterpret_cast<const float2*>(tok + t + 3);
+                        z[t + 0] = fmaf(__uint_as_float(sv[t + 0]) * a0.x, my_sqc, a0.y);
+                        z[t + 1] = fmaf(__uint_as_float(sv[t + 1]) * a1.x, my_sqc, a1.y);
+                        z[t + 2] = fmaf(__uint_as_float(sv[t + 2]) * a2.x, my_sqc, a2.y);
+                        z[t + 3] = fmaf(__uint_as_float(sv[t + 3]) * a3.x, my_sqc, a3.y);
+                        mx0 = fmaxf(mx0, fmaxf(z[t], z[t + 1]));
+                        mx1 = fmaxf(mx1, fmaxf(z[t + 2], z[t + 3]));
+                        if (p.out_max_logits != nullptr)   // z - log2(s_t) is the scaled logit itself (NaN for masked entries is ignored by fmaxf)
+                            x_max = fmaxf(x_max, fmaxf(fmaxf(z[t] - a0.y, z[t + 1] - a1.y), fmaxf(z[t + 2] - a2.y, z[t + 3] - a3.y)));
+                    }
+                    mx_loc = fmaxf(mx0, mx1);
+                    xch[(b * 4 + xpart) * 64 + hrow] = mx_loc;
+                }
+                if (named_bar_or(1 + grp, 128, dead || *abort_flag != 0)) { stop = true; break; }   // the four partial row maxima are in place
+                const float* xr = xch + b * 256 + hrow;
+                const float mx = fmaxf(fmaxf(xr[0], xr[64]), fmaxf(xr[128], xr[192]));
+                const bool grow = mx > m_run + RESCALE_TAU;   // false while the row has seen no valid entry
+                if (__any_sync(0xffffffffu, grow)) {
+                    if (j > 0) {   // the accumulator holds earlier tiles: wait for the last P.V, then scale it
+                        dead = !mbar_wait_hot(bar(BAR_PVDONE + ((it - 1) & 1u)), ((it - 1) >> 1) & 1u, abort_flag, W_PVDONE);
+                        if (dead) continue;
+                        tc_fence_after();
+                    }
+                    const float alpha = grow ? ex2(m_run - mx) : 1.f;   // 2^-inf = 0 for the first tile
+                    if (grow) { m_run = mx; l_run *= alpha; }
+                    if (j > 0) {
+#pragma unroll 1
+                        for (int c = 0; c < 128; c += 32) {
+                            uint32_t o[32];
+                            tmem_ld32(lane_addr + TM_O + 128 * ch + c, o);
+                            tmem_wait_ld();
+#pragma unroll
+                            for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+                            tmem_st32(lane_addr + TM_O + 128 * ch + c, o);
+                        }
+                        tmem_wait_st();
+                    }
+                }
+                if (it >= 2) {   // the P.V that read this P' buffer two tiles ago has completed
+                    dead = !mbar_wait_hot(bar(BAR_PVDONE + b), ((it - 2) >> 1) & 1u, abort_flag, W_PVDONE);
+                    if (dead) continue;
+                }
+                const float m_off = ((m_run == -INFINITY) ? 0.f : m_run) - (float)P_SHIFT;
+                uint32_t pw[8];
+                float l0 = 0.f, l1 = 0.f;
+#pragma unroll
+                for (int t = 0; t < 32; t += 4) {
+                    const float p0 = ex2(z[t + 0] - m_off), p1 = ex2(z[t + 1] - m_off);
+                    const float p2 = ex2(z[t + 2] - m_off), p3 = ex2(z[t + 3] - m_off);
+                    l0 = fmaf(p0, tok[t].z, l0); l1 = fmaf(p1, tok[t + 1].z, l1);
+                    l0 = fmaf(p2, tok[t + 2].z, l0); l1 = fmaf(p3, tok[t + 3].z, l1);
+                    pw[t >> 2] = pack_e4m3x4(p0, p1, p2, p3);
+                }
+                l_run += l0 + l1;
+                // P' of tokens [64*thalf + 32*ch, +32) of head hrow: two 16-byte pieces of the row
+                uint8_t* pb = sm + PB_OFF + b * CHUNK;
+                *reinterpret_cast<uint4*>(pb + swz(hrow, 4 * thalf + 2 * ch)) = make_uint4(pw[0], pw[1], pw[2], pw[3]);
+                *reinterpret_cast<uint4*>(pb + swz(hrow, 4 * thalf + 2 * ch + 1)) = make_uint4(pw[4], pw[5], pw[6], pw[7]);
+                fence_proxy_async();
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive_cluster(barp(BAR_PREADYP + b));
+            }
+            if (stop) break;
+            // ---- epilogue ---------------------------------------------------------------------
+            {
+                const uint32_t last = it - 1;
+                if (!dead) dead = !mbar_wait_hot(bar(BAR_PVDONE + (last & 1u)), (last >> 1) & 1u, abort_flag, W_PVDONE);
+                tc_fence_after();
+                if (named_bar_or(1 + grp, 128, dead || *abort_flag != 0)) { stop = true; break; }   // the partners have read the last tile's row maxima
+                xch[xpart * 64 + hrow] = l_run;
+                xch[256 + xpart * 64 + hrow] = x_max;
+                named_bar_sync(1 + grp, 128);
+                const float l_all = (xch[hrow] + xch[64 + hrow]) + (xch[128 + hrow] + xch[192 + hrow]);
+                const float xm = fmaxf(fmaxf(xch[256 + hrow], xch[320 + hrow]), fmaxf(xch[384 + hrow], xch[448 + hrow]));
+                float lse = (l_all > 0.f) ? (log2f(l_all) - (float)P_SHIFT + m_run) : NEG_BIG;
+                float denom = l_all;
+                if (w.no_split && p.attn_sink != nullptr && live) {
+                    const float sink2 = p.attn_sink[head] * LOG2E;
+                    denom = l_all + ((m_run == -INFINITY) ? INFINITY : exp2f(sink2 - m_run + (float)P_SHIFT));
+                    if (lse != NEG_BIG) lse += log2f(1.f + exp2f(sink2 - lse));
+                    else lse = sink2;
+                }
+                const float inv = (denom > 0.f) ? 1.f / denom : 0.f;
+                const int col0 = thalf * 256 + ch * 128;      // first output dim of this thread
+                if (w.no_split) {
+                    __nv_bfloat16* dst = p.out + ((size_t)req * p.num_heads + (live ? head : 0)) * D_V + col0;
+#pragma unroll 1
+                    for (int c = 0; c < 128; c += 32) {
+                        uint32_t o[32];
+                        tmem_ld32(lane_addr + TM_O + 128 * ch + c, o);
+                        tmem_wait_ld();
+                        if (live) {
+                            uint32_t pk[16];
+#pragma unroll
+                            for (int i = 0; i < 16; ++i) {
+                                __nv_bfloat162 t = __floats2bfloat162_rn(__uint_as_float(o[2 * i]) * inv, __uint_as_float(o[2 * i + 1]) * inv);
+                                pk[i] = *reinterpret_cast<uint32_t*>(&t);
+                            }
+                            if (wide_out) {
+                                const uint32_t lo8[8] = {pk[0], pk[1], pk[2], pk[3], pk[4], pk[5], pk[6], pk[7]};
+                                const uint32_t hi8[8] = {pk[8], pk[9], pk[10], pk[11], pk[12], pk[13], pk[14], pk[15]};
+                                st_global_v8(dst + c, lo8);
+                                st_global_v8(dst + c + 16, hi8);
+                            } else {
+#pragma unroll
+                                for (int i = 0; i < 4; ++i)
+                                    *reinterpret_cast<uint4*>(dst + c + 8 * i) = make_uint4(pk[4 * i], pk[4 * i + 1], pk[4 * i + 2], pk[4 * i + 3]);
+                            }
+                        }
+                    }
+                    if (live && xpart == 0) {
+                        p.out_lse[(size_t)req * p.num_heads + head] = lse;
+                        if (p.out_max_logits) p.out_max_logits[(size_t)req * p.num_heads + head] = (xm == -INFINITY) ? NEG_BIG : xm;
+                    }
+                } else {
+                    float* dst = p.o_accum + ((size_t)w.split_idx * p.num_heads + (live ? head : 0)) * D_V + col0;
+#pragma unroll 1
+                    for (int c = 0; c < 128; c += 32) {
+                        uint32_t o[32];
+                        tmem_ld32(lane_addr + TM_O + 128 * ch + c, o);
+                        tmem_wait_ld();
+                        if (live) {
+#pragma unroll
+                            for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * inv);
+                            if (wide_acc) {
+#pragma unroll
+                                for (int i = 0; i < 32; i += 8) {
+                                    const uint32_t v8[8] = {o[i], o[i + 1], o[i + 2], o[i + 3], o[i + 4], o[i + 5], o[i + 6], o[i + 7]};
+                                    st_global_v8(dst + c + i, v8);
+                                }
+                            } else {
+#pragma unroll
+                                for (int i = 0; i < 32; i += 4)
+                                    *reinterpret_cast<uint4*>(dst + c + i) = make_uint4(o[i], o[i + 1], o[i + 2], o[i + 3]);
+                            }
+                        }
+                    }
+                    if (live && xpart == 0) p.lse_accum[(size_t)w.split_idx * p.num_heads + head] = lse;
+                }
+                tc_fence_before();                  // the accumulator reads precede the next request's first P.V
+                named_bar_sync(1 + grp, 128);       // xch is free again
+            }
+        }
+    } else if (warp < FX_WARP0) {
+        // =================================================================== gather issuers
+        // Warp pw gathers rows [16*pw, +16) of this CTA's 64 rows of every tile (lanes 0-15 hold their
+        // row pointers) and the partner's rows [16*pw, +16) (lanes 16-31), never waiting for data.
+        // K part of a tile: the 512 no-PE bytes (one coalesced 512-byte request per row), the RoPE
+        // bytes, and the scale words of all 32 rows.  V part: bytes [256 r, +256) of the partner's
+        // rows into the V slots, and their scale words.  Rows without an entry are zero-filled.
+        // Issue order K(0) K(1) V(0) K(2) V(1) ...: the V part of a tile is needed one tile later.
+        const int pw = warp - N_SM_WARPS;
+        const int row0 = pw * 16;
+        const int my_row = row0 + (lane & 15);
+        const int peer = lane >> 4;                                  // lanes 16-31 look after the partner's rows
+        const int my_n = (peer ? (1 - (int)rank) : (int)rank) * OWN_N + my_row;   // token index inside the tile
+        const int pbs_shift = (p.page_block_size & (p.page_block_size - 1)) == 0 ? __ffs(p.page_block_size) - 1 : -1;
+        const unsigned long long kv_u = reinterpret_cast<unsigned long long>(p.kv);
+        uint32_t it = 0;
+        bool ok = true;
+        for (int req = meta.begin_req; req <= last_req && ok; ++req) {
+            Work w;
+            if (!get_work(p, meta, req, w)) continue;
+            const int nst = (w.nblk + 1) >> 1;
+            const int32_t* idx_row = p.indices + (size_t)req * p.topk;
+            const int lim = min(w.len, (w.blk0 + w.nblk) * BLOCK_N);
+            auto fetch_idx = [&](int j) -> int {
+                const int pos = w.blk0 * BLOCK_N + j * TILE_N + my_n;
+                return (j < nst && pos < lim) ? __ldg(idx_row + pos) : -1;
+            };
+            auto row_ptr = [&](int idx) -> unsigned long long {
+                if (idx < 0) return 0ull;      // rows without an entry travel as a null source: their copies zero-fill
+                const unsigned u = (unsigned)idx;
+                return reinterpret_cast<unsigned long long>(
+                    (pbs_shift >= 0)
+                        ? p.kv + (int64_t)(u >> pbs_shift) * p.block_stride + (int64_t)(u & (unsigned)(p.page_block_size - 1)) * ROW_BYTES
+                        : kv_row_ptr(p.kv, idx, p.page_block_size, p.block_stride));
+            };
+            auto v_part = [&](uint32_t t_it, unsigned long long src_u) -> bool {
+                const uint32_t vs = t_it % NV;
+                if (t_it >= NV && !mbar_wait_hot(bar(BAR_VEMPTY + vs), ((t_it / NV) - 1) & 1u, abort_flag, W_VEMPTY)) return false;
+                const uint32_t vbase = base + VS_OFF + vs * VS_BYTES;
+                const uint32_t piece = lane & 15;                       // 16-byte piece of the 256-byte half row
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                    const int r = row0 + 2 * i + peer;                  // partner's row (two rows per instruction)
+                    const unsigned long long s = __shfl_sync(0xffffffffu, src_u, 16 + 2 * i + peer);
+                    const uint32_t slot = ((2u * (1u - rank) + (uint32_t)(r >> 5)) * 2u + (piece >> 3)) * VSLOT;
+                    const bool v = s != 0ull;
+                    cp_async16_zfill(vbase + slot + swz((uint32_t)r & 31u, piece & 7u),
+                                     reinterpret_cast<const uint8_t*>(v ? s + 256u * rank + piece * 16u : kv_u), v ? 16u : 0u);
+                }
+                if (peer) {
+                    const bool v = src_u != 0ull;
+                    cp_async16_zfill(vbase + VS_RAW + my_row * 16, reinterpret_cast<const uint8_t*>(v ? src_u + SCALE_OFF : kv_u), v ? 16u : 0u);
+                }
+                cp_async_arrive_noinc(bar(BAR_VLOADED + vs));
+                return true;
+            };
+            int idx_next = fetch_idx(0), idx_next2 = fetch_idx(1);
+            unsigned long long src_prev = 0ull;
+#pragma unroll 1
+            for (int k = 0; k < nst && ok; ++k) {
+                const uint32_t t_it = it + k, ks = t_it % NK;
+                const unsigned long long my_src_u = row_ptr(idx_next);
+                idx_next = idx_next2;
+                idx_next2 = fetch_idx(k + 2);
+                if (t_it >= NK) {
+                    ok = mbar_wait_hot(bar(BAR_KEMPTY + ks), ((t_it / NK) - 1) & 1u, abort_flag, W_KEMPTY);
+                    if (!ok) break;
+                }
+                const uint32_t kbase = base + KS_OFF + ks * KS_BYTES;
+#pragma unroll
+                for (int hb = 0; hb < 2; ++hb) {       // two batches of 8 rows keep the register count low
+                    unsigned long long srcs[8];
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) srcs[i] = __shfl_sync(0xffffffffu, my_src_u, hb * 8 + i);
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) {
+                        const int r = row0 + hb * 8 + i;
+                        const bool v = srcs[i] != 0ull;
+                        cp_async16_zfill(kbase + (lane >> 3) * CHUNK + swz((uint32_t)r, (uint32_t)lane & 7u),
+                                         reinterpret_cast<const uint8_t*>(v ? srcs[i] + lane * 16 : kv_u), v ? 16u : 0u);
+                    }
+                }
+#pragma unroll
+                for (int g = 0; g < 4; ++g) {
+                    const unsigned long long rs = __shfl_sync(0xffffffffu, my_src_u, g * 4 + (lane >> 3));
+                    const int r = row0 + g * 4 + (lane >> 3);
+                    const bool v = rs != 0ull;
+                    cp_async16_zfill(kbase + KS_ROPE + swz((uint32_t)r, (uint32_t)lane & 7u),
+                                     reinterpret_cast<const uint8_t*>(v ? rs + ROPE_OFF + (lane & 7) * 16 : kv_u), v ? 16u : 0u);
+                }
+                {
+                    const bool v = my_src_u != 0ull;
+                    cp_async16_zfill(kbase + KS_RAW + my_n * 16, reinterpret_cast<const uint8_t*>(v ? my_src_u + SCALE_OFF : kv_u), v ? 16u : 0u);
+                }
+                cp_async_arrive_noinc(bar(BAR_KLOADED + ks));
+                if (k >= 1) { ok = v_part(t_it - 1, src_prev); if (!ok) break; }
+                src_prev = my_src_u;
+            }
+            if (ok && nst > 0) ok = v_part(it + nst - 1, src_prev);
+            it += nst;
+        }
+        cp_async_wait_all();
+    } else if (warp < MMA_WARP) {
+        // =================================================================== tile fix-up
+        // Warp fw owns rows [8*fw, +8) of this CTA's rows and of the partner's rows.  K part: RoPE
+        // pre-division and uneven-scale rewrite of the own rows (-> the score MMAs may start), then,
+        // once the V stage is free, the scale triples of its 16 tokens and the copy of its rows'
+        // V bytes into the V slots.  V part: uneven-scale rewrite of the partner's half rows.
+        const int fw = warp - FX_WARP0;
+        const int row0 = fw * FX_ROWS;
+        const int my_row = row0 + (lane & 7);
+        const int blk = lane >> 3;
+        uint32_t it = 0;
+        bool ok = true;
+        auto v_part = [&](uint32_t t_it) -> bool {
+            const uint32_t vs = t_it % NV;
+            if (!mbar_wait_hot(bar(BAR_VLOADED + vs), (t_it / NV) & 1u, abort_flag, W_VLOADED)) return false;
+            uint8_t* vp = sm + VS_OFF + vs * VS_BYTES;
+            const float4 sc = *reinterpret_cast<const float4*>(vp + VS_RAW + my_row * 16);
+            const float smax = fmaxf(fmaxf(sc.x, sc.y), fmaxf(sc.z, sc.w));
+            const float inv_s = (smax > 0.f) ? __uint_as_float(0x7f000000u - __float_as_uint(smax)) : 0.f;
+            // ratio of (row lane % 8, this CTA's chunk (lane / 8) % 2) to the row scale: a power of two <= 1
+            const float mine = rank ? ((blk & 1) ? sc.w : sc.z) : ((blk & 1) ? sc.y : sc.x);
+            const float my_ratio = mine * inv_s;
+            uint32_t fix = __ballot_sync(0xffffffffu, my_ratio != 1.f && smax > 0.f) & 0xffffu;   // rows x 2 chunks
+            fix = (fix | (fix >> 8)) & 0xffu;
+            while (fix) {
+                const int i = __ffs(fix) - 1;
+                fix &= fix - 1;
+                const int r = row0 + i;
+                const float ratio_f = __shfl_sync(0xffffffffu, my_ratio, ((lane >> 3) & 1) * 8 + i);   // (row i, chunk (lane/8)%2)
+                if (lane < 16 && ratio_f != 1.f) {
+                    const uint32_t slot = ((2u * (1u - rank) + (uint32_t)(r >> 5)) * 2u + (uint32_t)(lane >> 3)) * VSLOT;
+                    uint4* q4 = reinterpret_cast<uint4*>(vp + slot + swz((uint32_t)r & 31u, (uint32_t)lane & 7u));
+                    const __half2 ratio = __float2half2_rn(ratio_f);
+                    uint4 v = *q4;
+                    v.x = rescale_e4m3x4(v.x, ratio); v.y = rescale_e4m3x4(v.y, ratio);
+                    v.z = rescale_e4m3x4(v.z, ratio); v.w = rescale_e4m3x4(v.w, ratio);
+                    *q4 = v;
+                }
+            }
+            fence_proxy_async();
+            __syncwarp();
+            if (lane == 0) mbar_arrive_cluster(barp(BAR_VFULLP + vs));
+            return true;
+        };
+        for (int req = meta.begin_req; req <= last_req && ok; ++req) {
+            Work w;
+            if (!get_work(p, meta, req, w)) continue;
+            const int nst = (w.nblk + 1) >> 1;
+#pragma unroll 1
+            for (int k = 0; k < nst && ok; ++k) {
+                const uint32_t t_it = it + k, ks = t_it % NK, vs = t_it % NV;
+                ok = mbar_wait_hot(bar(BAR_KLOADED + ks), (t_it / NK) & 1u, abort_flag, W_KLOADED);
+                if (!ok) break;
+                uint8_t* kp = sm + KS_OFF + ks * KS_BYTES;
+                uint8_t* vp = sm + VS_OFF + vs * VS_BYTES;
+                // RoPE chunks of this lane: 2 passes of 4 rows x 8 chunks
+                uint4 rv[2];
+#pragma unroll
+                for (int g = 0; g < 2; ++g) rv[g] = *reinterpret_cast<const uint4*>(kp + KS_ROPE + swz((uint32_t)(row0 + g * 4 + (lane >> 3)), (uint32_t)lane & 7u));
+                // row scale, validity (a zero-filled scale word marks a row that was not loaded)
+                const float4 sc = *reinterpret_cast<const float4*>(kp + KS_RAW + (rank * OWN_N + my_row) * 16);
+                const float smax = fmaxf(fmaxf(sc.x, sc.y), fmaxf(sc.z, sc.w));
+                const bool uneven = (sc.x != smax) | (sc.y != smax) | (sc.z != smax) | (sc.w != smax);
+                const float inv_s = (smax > 0.f) ? __uint_as_float(0x7f000000u - __float_as_uint(smax)) : 0.f;
+                const float my_ratio = (blk == 0 ? sc.x : (blk == 1 ? sc.y : (blk == 2 ? sc.z : sc.w))) * inv_s;
+#pragma unroll
+                for (int g = 0; g < 2; ++g) {
+                    const int rl = g * 4 + (lane >> 3);
+                    const __nv_bfloat162 f = __float2bfloat162_rn(__shfl_sync(0xffffffffu, inv_s, rl));
+                    uint4 v = rv[g];
+                    v.x = mul_bf16x2(v.x, f); v.y = mul_bf16x2(v.y, f);
+                    v.z = mul_bf16x2(v.z, f); v.w = mul_bf16x2(v.w, f);
+                    *reinterpret_cast<uint4*>(kp + KS_ROPE + swz((uint32_t)(row0 + rl), (uint32_t)lane & 7u)) = v;
+                }
+                // no-PE tiles whose scale is below the row scale: shift them onto the row scale.
+                // Lane l rewrites 16-byte chunk l of a flagged row (block l / 8).
+                uint32_t fix = __ballot_sync(0xffffffffu, uneven && smax > 0.f) & 0xffu;
+                while (fix) {
+                    const int i = __ffs(fix) - 1;
+                    fix &= fix - 1;
+                    const float ratio_f = __shfl_sync(0xffffffffu, my_ratio, (lane & 24) + i);   // (row i, my block)
+                    if (ratio_f != 1.f) {
+                        uint4* q4 = reinterpret_cast<uint4*>(kp + blk * CHUNK + swz((uint32_t)(row0 + i), (uint32_t)lane & 7u));
+                        const __half2 ratio = __float2half2_rn(ratio_f);
+                        uint4 v = *q4;
+                        v.x = rescale_e4m3x4(v.x, ratio); v.y = rescale_e4m3x4(v.y, ratio);
+                        v.z = rescale_e4m3x4(v.z, ratio); v.w = rescale_e4m3x4(v.w, ratio);
+                        *q4 = v;
+                    }
+                }
+                fence_proxy_async();
+                __syncwarp();
+                if (lane == 0) mbar_arrive_cluster(barp(BAR_KFULLP + ks));
+                // the V stage of this tile is free once the P.V two tiles back has completed
+                if (t_it >= NV) {
+                    ok = mbar_wait(bar(BAR_VEMPTY + vs), ((t_it / NV) - 1) & 1u, abort_flag, W_VEMPTY);
+                    if (!ok) break;
+                }
+                // scale triples of tokens [8 fw, +8) of this CTA (lanes 0-7) and of the partner (lanes 8-15)
+                if (lane < 16) {
+                    const int n = ((lane < 8) ? (int)rank : 1 - (int)rank) * OWN_N + my_row;
+                    const float4 s4 = *reinterpret_cast<const float4*>(kp + KS_RAW + n * 16);
+                    const float sm4 = fmaxf(fmaxf(s4.x, s4.y), fmaxf(s4.z, s4.w));
+                    const float is4 = (sm4 > 0.f) ? __uint_as_float(0x7f000000u - __float_as_uint(sm4)) : 0.f;
+                    *reinterpret_cast<float4*>(vp + VS_TRIP + n * 16) =
+                        make_float4(sm4, (sm4 > 0.f) ? (float)((int)(__float_as_uint(sm4) >> 23) - 127) : -INFINITY, is4, 0.f);
+                }
+                // own V bytes: rows [8 fw, +8), this CTA's two chunks -> V slots (same swizzle)
+#pragma unroll
+                for (int u = 0; u < 4; ++u) {
+                    const int pidx = lane + 32 * u;                    // 8 rows x 2 chunks x 8 pieces
+                    const uint32_t r = (uint32_t)(row0 + (pidx >> 4)), nb = (uint32_t)(pidx >> 3) & 1u, c = (uint32_t)pidx & 7u;
+                    const uint4 v = *reinterpret_cast<const uint4*>(kp + (2u * rank + nb) * CHUNK + swz(r, c));
+                    *reinterpret_cast<uint4*>(vp + ((2u * rank + (r >> 5)) * 2u + nb) * VSLOT + swz(r & 31u, c)) = v;
+                }
+                fence_proxy_async();
+                __syncwarp();
+                if (lane == 0) { mbar_arrive(bar(BAR_TRIP + ks)); mbar_arrive(bar(BAR_KEMPTY + ks)); }
+                if (k >= 1) { ok = v_part(t_it - 1); if (!ok) break; }
+            }
+            if (ok && nst > 0) ok = v_part(it + nst - 1);
+            it += nst;
+        }
+    } else if (warp == MMA_WARP && lane == 0 && rank == 0) {
+        // =================================================================== score MMA issue (even CTA)
+        uint32_t it = 0, rq = 0;
+        bool ok = true;
+        const uint32_t qn_lo = desc_lo(base + QN_OFF, 16), qr_lo = desc_lo(base + QR_OFF, 16);
+        for (int req = meta.begin_req; req <= last_req && ok; ++req) {
+            Work w;
+            if (!get_work(p, meta, req, w)) continue;
+            const int nst = (w.nblk + 1) >> 1;
+            ok = mbar_wait_thread_cluster(bar(BAR_QREADYP), rq & 1u, abort_flag, W_QREADY);
+            if (!ok) break;
+            ++rq;
+            for (int j = 0; j < nst && ok; ++j, ++it) {
+                const uint32_t ks = it % NK, b = it & 1u;
+                if (it >= 2) {
+                    ok = mbar_wait_thread_cluster(bar(BAR_SFREEP + b), ((it - 2) >> 1) & 1u, abort_flag, W_SFREE);
+                    if (!ok) break;
+                }
+                ok = mbar_wait_thread_cluster(bar(BAR_KFULLP + ks), (it / NK) & 1u, abort_flag, W_KFULL);
+                if (!ok) break;
+                tc_fence_after();
+                const uint32_t kb_lo = desc_lo(base + KS_OFF + ks * KS_BYTES, 16);
+                const uint32_t d = tmem + TM_S + 64 * b;
+#pragma unroll
+                for (int kc = 0; kc < 4; ++kc) {
+#pragma unroll
+                    for (int s = 0; s < 4; ++s) {
+                        mma_pair_f8(d, make_desc(qn_lo + ((kc * CHUNK + s * 32) >> 4), DESC_HI_SW128),
+                                    make_desc(kb_lo + ((kc * CHUNK + s * 32) >> 4), DESC_HI_SW128), IDESC_QK_F8, (kc | s) != 0);
+                    }
+                }
+#pragma unroll
+                for (int s = 0; s < 4; ++s) {
+                    mma_pair_f16(d, make_desc(qr_lo + ((s * 32) >> 4), DESC_HI_SW128),
+                                 make_desc(kb_lo + ((KS_ROPE + s * 32) >> 4), DESC_HI_SW128), IDESC_QK_BF16, true);
+                }
+                tc_commit_pair(bar(BAR_SREADY + b));
+                tc_commit_pair(mapa_shared(bar(BAR_SREADY + b), 1));
+                tc_commit_pair(bar(BAR_KEMPTY + ks));
+                tc_commit_pair(mapa_shared(bar(BAR_KEMPTY + ks), 1));
+            }
+        }
+    } else if (warp == MMA_WARP + 1 && lane == 0 && rank == 0) {
+        // =================================================================== P.V MMA issue (even CTA)
+        uint32_t it = 0;
+        bool ok = true;
+        for (int req = meta.begin_req; req <= last_req && ok; ++req) {
+            Work w;
+            if (!get_work(p, meta, req, w)) continue;
+            const int nst = (w.nblk + 1) >> 1;
+            for (int j = 0; j < nst && ok; ++j, ++it) {
+                const uint32_t vs = it % NV, b = it & 1u;
+                ok = mbar_wait_thread_cluster(bar(BAR_PREADYP + b), (it >> 1) & 1u, abort_flag, W_PREADY);
+                if (!ok) break;
+                ok = mbar_wait_thread_cluster(bar(BAR_VFULLP + vs), (it / NV) & 1u, abort_flag, W_VFULL);
+                if (!ok) break;
+                tc_fence_after();
+                const uint32_t pa_lo = desc_lo(base + PB_OFF + b * CHUNK, 16);
+                const uint32_t vb_lo = desc_lo(base + VS_OFF + vs * VS_BYTES, VSLOT);
+#pragma unroll
+                for (int kb = 0; kb < 4; ++kb) {
+#pragma unroll
+                    for (int nb = 0; nb < 2; ++nb) {
+                        mma_pair_f8(tmem + TM_O + 128 * nb, make_desc(pa_lo + ((kb * 32) >> 4), DESC_HI_SW128),
+                                    make_desc(vb_lo + (((2 * kb + nb) * VSLOT) >> 4), DESC_HI_SW128), IDESC_PV_F8, (j | kb) != 0);
+                    }
+                }
+                tc_commit_pair(bar(BAR_VEMPTY + vs));
+                tc_commit_pair(mapa_shared(bar(BAR_VEMPTY + vs), 1));
+                tc_commit_pair(bar(BAR_PVDONE + b));
+                tc_commit_pair(mapa_shared(bar(BAR_PVDONE + b), 1));
+            }
+        }
+    }
+
+    // ------------------------------------------------------------------------ teardown
+    tc_fence_before();
+    __syncthreads();
+    cluster_sync_all();        // the partner may still arrive on this CTA's barriers until here
+    if (tid == 0 && *abort_flag != 0 && p.status != nullptr) {
+        atomicCAS(p.status, 0, *abort_flag);
+        atomicAdd(p.status + 1, 1);
+        p.status[2] = blockIdx.x;
+    }
+    if (warp == MMA_WARP) {
+        tc_fence_after();
+        tmem_dealloc_pair(tmem, TMEM_COLS);
+    }
+}
+
+}  // namespace
+
+int launch_attn_pair(const AttnParams& p, cudaStream_t stream) {
+    if (p.num_tokens == 0) return 0;
+    static bool attr_set[64] = {};
+    static int sm_count[64] = {};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev < 0 || dev >= 64) return set_error(SMLA_E_SHAPE, "attn_pair_kernel: device ordinal %d not supported", dev);
+    if (!attr_set[dev]) {
+        cudaFuncAttributes fa;
+        if (cudaFuncGetAttributes(&fa, attn_pair_kernel) != cudaSuccess || fa.numRegs != REGS_LAUNCH)
+            return set_error(SMLA_E_DEVICE, "attn_pair_kernel: compiled with %d registers per thread, the warpgroup budgets assume %d",
+                             fa.numRegs, REGS_LAUNCH);
+        const cudaError_t e = cudaFuncSetAttribute(attn_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_ALLOC);
+        if (e != cudaSuccess) return set_error((int)e, "attn_pair_kernel: cannot reserve %u bytes of shared memory: %s",
+                                               SMEM_ALLOC, cudaGetErrorString(e));
+        cudaDeviceGetAttribute(&sm_count[dev], cudaDevAttrMultiProcessorCount, dev);
+        attr_set[dev] = true;
+    }
+    // Without a scheduler the grid is persistent: at most one CTA per SM, each pair walks its share of the requests.
+    const int max_pairs = sm_count[dev] >= 2 ? sm_count[dev] / 2 : 1;
+    const int parts = p.sched ? p.num_parts : (p.num_tokens < max_pairs ? p.num_tokens : max_pairs);
+    attn_pair_kernel<<<2 * parts, PAIR_THREADS, SMEM_ALLOC, stream>>>(p);
+    return check_launch("attn_pair_kernel");
+}
+
+}  // namespace smla

@@ -40,17 +40,15 @@
 // Every wait is bounded; a wait that gives up records a code in status[] and the CTA drains and
 // exits.
 #include "common.cuh"
+#include "attn_common.cuh"
 #include "sm100_ptx.cuh"
-
-#ifndef SMLA_DBG
-#define SMLA_DBG 0   // debugging switches for timing experiments: 1 skip softmax math, 2 skip fix-up work, 4 skip copies, 32 no register trading
-#endif
 
 namespace smla {
 
 namespace {
 
 using namespace ptx;
+using namespace attn;
 
 constexpr int N_SM_WARPS = 8, N_PR_WARPS = 4, N_FX_WARPS = 8;
 constexpr int FX_ROWS = 8;    // rows of a tile per fix-up warp
@@ -68,9 +66,6 @@ static_assert(N_SM_WARPS * 32 * REGS_SOFTMAX + (N_PR_WARPS + N_FX_WARPS) * 32 * 
 static_assert((N_SM_WARPS % 4) == 0 && (N_PR_WARPS % 4) == 0 && (N_FX_WARPS % 4) == 0, "setmaxnreg acts on whole warpgroups");
 static_assert(65536 / TC_THREADS / 8 * 8 == REGS_LAUNCH, "launch-time registers per thread");
 constexpr int NSTAGE = 5;
-#ifndef SMLA_HOT
-#define SMLA_HOT 15    // which waits block in the barrier instead of sleeping between polls: 1 scores, 2 loaded, 4 empty, 8 P.V done
-#endif
 constexpr int P_SHIFT = 5;             // P' is stored as e4m3(P' * 2^P_SHIFT)
 constexpr float RESCALE_TAU = 3.0f;    // lazy-rescale threshold (log2 units); P' <= 2^TAU
 
@@ -106,101 +101,8 @@ constexpr uint32_t DESC_HI_SW128 = desc_hi(1024, (uint32_t)SWIZZLE_128B);
 // give-up codes reported through status[0]
 enum { W_EMPTY = 1, W_FULL = 2, W_SREADY = 3, W_PREADY = 4, W_PVDONE = 5, W_QREADY = 6, W_LOADED = 7 };
 
-// Optional timeline of CTA 0 (debugging aid): when a trace buffer has been registered with
-// smla_debug_set_trace, lane 0 of every warp appends (tag, tile, SM clock) records to its own
-// region of the buffer with plain stores (no atomics, so that tracing does not stall the warp).
-struct Trace {
-    long long* buf;   // [warps][cap][2]
-    int cap;
-};
-struct TraceCursor {
-    int n = 0;
-};
-__device__ __forceinline__ void trace(const Trace& t, TraceCursor& c, int tag, int tile) {
-    if (t.buf != nullptr && blockIdx.x == 0 && (threadIdx.x & 31) == 0 && c.n < t.cap) {
-        long long* slot = t.buf + ((size_t)(threadIdx.x >> 5) * t.cap + c.n) * 2;
-        slot[0] = ((long long)tag << 32) | (unsigned)tile;
-        slot[1] = clock64();
-        ++c.n;
-    }
-}
-
-struct Work {   // one request's share of a partition
-    int req, blk0, nblk, len, split_idx;
-    bool no_split;
-};
-
-__device__ __forceinline__ SchedMeta load_meta(const AttnParams& p, int part) {
-    SchedMeta m;
-    if (p.sched != nullptr) {
-        m = p.sched[part];
-    } else {
-        // no scheduler: the CTA pairs of the grid share the requests as contiguous, whole ranges
-        // (one request each when there are at least as many pairs as requests)
-        const long long pairs = gridDim.x >> 1;
-        m.begin_req = (int)((long long)part * p.num_tokens / pairs);
-        m.end_req = (int)((long long)(part + 1) * p.num_tokens / pairs) - 1;
-        m.begin_block = 0; m.end_block = 0x7fffffff;
-        m.begin_split = 0; m.first_split = m.last_split = 0; m.pad = 0;
-    }
-    return m;
-}
-
-__device__ __forceinline__ bool get_work(const AttnParams& p, const SchedMeta& m, int req, Work& w) {
-    int len = p.topk_length ? p.topk_length[req] : p.topk;
-    len = min(len, p.topk);
-    const int total = max((len + BLOCK_N - 1) / BLOCK_N, 1);
-    const int b0 = (req == m.begin_req) ? m.begin_block : 0;
-    const int b1 = min((req == m.end_req) ? m.end_block : total, total);
-    w.req = req; w.blk0 = b0; w.nblk = b1 - b0; w.len = len;
-    w.no_split = !p.force_partial &&
-                 ((req == m.begin_req) ? !m.first_split : ((req == m.end_req) ? !m.last_split : true));
-    w.split_idx = p.num_splits ? p.num_splits[req] + ((req == m.begin_req) ? m.begin_split : 0) : 0;
-    return w.nblk > 0;
-}
-
-__device__ __forceinline__ float pow2_ceil(float x) {
-    uint32_t b = __float_as_uint(x);
-    if (b & 0x007fffffu) b = (b + 0x00800000u) & 0x7f800000u;
-    return __uint_as_float(b);
-}
-
-__device__ __forceinline__ float ex2(float x) {   // 2^x, ex2(-inf) = +0
-    float y;
-    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
-    return y;
-}
-
-__device__ __forceinline__ uint32_t pack_e4m3x4(float a, float b, float c, float d) {
-    uint16_t lo, hi;
-    asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;" : "=h"(lo) : "f"(b), "f"(a));
-    asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;" : "=h"(hi) : "f"(d), "f"(c));
-    return (uint32_t)lo | ((uint32_t)hi << 16);
-}
-
-// Multiplies four packed e4m3 values by a power of two (given as half2) with rounding.
-__device__ __forceinline__ uint32_t rescale_e4m3x4(uint32_t w, __half2 ratio) {
-    uint32_t lo, hi;
-    asm("cvt.rn.f16x2.e4m3x2 %0, %1;" : "=r"(lo) : "h"((uint16_t)(w & 0xffffu)));
-    asm("cvt.rn.f16x2.e4m3x2 %0, %1;" : "=r"(hi) : "h"((uint16_t)(w >> 16)));
-    __half2 a = __hmul2(*reinterpret_cast<__half2*>(&lo), ratio);
-    __half2 b = __hmul2(*reinterpret_cast<__half2*>(&hi), ratio);
-    uint16_t ra, rb;
-    asm("cvt.rn.satfinite.e4m3x2.f16x2 %0, %1;" : "=h"(ra) : "r"(*reinterpret_cast<uint32_t*>(&a)));
-    asm("cvt.rn.satfinite.e4m3x2.f16x2 %0, %1;" : "=h"(rb) : "r"(*reinterpret_cast<uint32_t*>(&b)));
-    return (uint32_t)ra | ((uint32_t)rb << 16);
-}
-
-__device__ __forceinline__ uint32_t mul_bf16x2(uint32_t w, __nv_bfloat162 f) {
-    __nv_bfloat162 r = __hmul2(*reinterpret_cast<__nv_bfloat162*>(&w), f);
-    return *reinterpret_cast<uint32_t*>(&r);
-}
-
-__device__ __forceinline__ float bf16lo(uint32_t w) { return __uint_as_float(w << 16); }
-__device__ __forceinline__ float bf16hi(uint32_t w) { return __uint_as_float(w & 0xffff0000u); }
-
 // ---------------------------------------------------------------------------------------------
-__global__ void __launch_bounds__(TC_THREADS, 1) attn_tc_kernel(const AttnParams p, const Trace tr) {
+__global__ void __launch_bounds__(TC_THREADS, 1) attn_tc_kernel(const AttnParams p) {
     extern __shared__ uint8_t smem_raw[];
     const uint32_t raw = smem_u32(smem_raw);
     const uint32_t base = (raw + 1023u) & ~1023u;
@@ -211,8 +113,6 @@ __global__ void __launch_bounds__(TC_THREADS, 1) attn_tc_kernel(const AttnParams
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int part = blockIdx.x >> 1, half = blockIdx.x & 1;
-    TraceCursor tc;
-    trace(tr, tc, 1, 0);
     const SchedMeta meta = load_meta(p, part);
 
     if (tid == 0) {
@@ -240,10 +140,8 @@ __global__ void __launch_bounds__(TC_THREADS, 1) attn_tc_kernel(const AttnParams
 
     const int last_req = min(meta.end_req, p.num_tokens - 1);
 
-    if (!(SMLA_DBG & 32)) {
-        if (warp < N_SM_WARPS) setmaxnreg_inc<REGS_SOFTMAX>();
-        else if (warp < MMA_WARP) setmaxnreg_dec<REGS_OTHER>();
-    }
+    if (warp < N_SM_WARPS) setmaxnreg_inc<REGS_SOFTMAX>();
+    else if (warp < MMA_WARP) setmaxnreg_dec<REGS_OTHER>();
 
     if (warp < N_SM_WARPS) {
         // =================================================================== softmax + epilogue
@@ -336,15 +234,12 @@ __global__ void __launch_bounds__(TC_THREADS, 1) attn_tc_kernel(const AttnParams
             float x_max = -INFINITY;   // this half's maximum of the scaled logits (max_logits output)
             for (int j = 0; j < w.nblk && ok; ++j, ++it) {
                 const uint32_t b = it & 1u, st = it % NSTAGE;
-                ok = (SMLA_HOT & 1) ? mbar_wait_hot(bar(BAR_SREADY + b), (it >> 1) & 1u, abort_flag, W_SREADY)
-                                    : mbar_wait(bar(BAR_SREADY + b), (it >> 1) & 1u, abort_flag, W_SREADY);
+                ok = mbar_wait_hot(bar(BAR_SREADY + b), (it >> 1) & 1u, abort_flag, W_SREADY);
                 if (!ok) break;
                 // the per-token scale arrays of this stage were published with the tile itself
                 ok = (mbar_wait(bar(BAR_FULL + st), (it / NSTAGE) & 1u, abort_flag, W_FULL));
                 if (!ok) break;
                 tc_fence_after();
-                trace(tr, tc, 10 + warp, it);
-                if (SMLA_DBG & 1) { tc_fence_before(); mbar_arrive(bar(BAR_PREADY + b)); continue; }
                 uint32_t sv[32];
                 tmem_ld32(lane_addr + TM_S + 64 * b + 32 * hh, sv);
                 // per token (s_t, log2 s_t, 1/s_t, 0), published with the tile by the fix-up warps
@@ -369,12 +264,10 @@ __global__ void __launch_bounds__(TC_THREADS, 1) attn_tc_kernel(const AttnParams
                 xch[b * 256 + hh * 128 + row] = fmaxf(mx0, mx1);
                 named_bar_sync(1 + quarter, 64);   // also: both warps have finished reading S[b]
                 const float mx = fmaxf(fmaxf(mx0, mx1), xch[b * 256 + (1 - hh) * 128 + row]);
-                trace(tr, tc, 20 + warp, it);
                 const bool grow = mx > m_run + RESCALE_TAU;   // false while the row has seen no valid entry
                 if (__any_sync(0xffffffffu, grow)) {
                     if (j > 0) {   // the accumulator holds earlier tiles: wait for the last P.V, then scale it
-                        ok = (SMLA_HOT & 8) ? mbar_wait_hot(bar(BAR_PVDONE + ((it - 1) & 1u)), ((it - 1) >> 1) & 1u, abort_flag, W_PVDONE)
-                                            : mbar_wait(bar(BAR_PVDONE + ((it - 1) & 1u)), ((it - 1) >> 1) & 1u, abort_flag, W_PVDONE);
+                        ok = mbar_wait_hot(bar(BAR_PVDONE + ((it - 1) & 1u)), ((it - 1) >> 1) & 1u, abort_flag, W_PVDONE);
                         if (!ok) break;
                         tc_fence_after();
                     }
@@ -410,14 +303,12 @@ __global__ void __launch_bounds__(TC_THREADS, 1) attn_tc_kernel(const AttnParams
                 tmem_wait_st();
                 tc_fence_before();
                 mbar_arrive(bar(BAR_PREADY + b));
-                trace(tr, tc, 30 + warp, it);
             }
             if (!ok) break;
             // ---- epilogue ---------------------------------------------------------------------
             {
                 const uint32_t last = it - 1;
-                ok = (SMLA_HOT & 8) ? mbar_wait_hot(bar(BAR_PVDONE + (last & 1u)), (last >> 1) & 1u, abort_flag, W_PVDONE)
-                                    : mbar_wait(bar(BAR_PVDONE + (last & 1u)), (last >> 1) & 1u, abort_flag, W_PVDONE);
+                ok = mbar_wait_hot(bar(BAR_PVDONE + (last & 1u)), (last >> 1) & 1u, abort_flag, W_PVDONE);
                 if (!ok) break;
                 tc_fence_after();
                 named_bar_sync(1 + quarter, 64);   // the partner has read the last tile's row maximum
@@ -494,7 +385,6 @@ __global__ void __launch_bounds__(TC_THREADS, 1) attn_tc_kernel(const AttnParams
                     if (live && half == 0 && hh == 0) p.lse_accum[(size_t)w.split_idx * p.num_heads + row] = lse;
                 }
                 named_bar_sync(1 + quarter, 64);   // xch is free again
-                trace(tr, tc, 2, it);
             }
         }
     } else if (warp < FX_WARP0) {
@@ -536,12 +426,9 @@ __global__ void __launch_bounds__(TC_THREADS, 1) attn_tc_kernel(const AttnParams
                 unsigned long long my_src_u = 0ull;
                 if (idx >= 0) my_src_u = reinterpret_cast<unsigned long long>(row_ptr(idx));
                 if (t_it >= NSTAGE) {
-                    ok = (SMLA_HOT & 4) ? mbar_wait_hot(bar(BAR_EMPTY + st), ((t_it / NSTAGE) - 1) & 1u, abort_flag, W_EMPTY)
-                                        : mbar_wait(bar(BAR_EMPTY + st), ((t_it / NSTAGE) - 1) & 1u, abort_flag, W_EMPTY);
+                    ok = mbar_wait_hot(bar(BAR_EMPTY + st), ((t_it / NSTAGE) - 1) & 1u, abort_flag, W_EMPTY);
                     if (!ok) break;
                 }
-                trace(tr, tc, 60 + pw, t_it);
-                if (SMLA_DBG & 4) { mbar_arrive(bar(BAR_LOADED + st)); continue; }
                 const uint32_t sbase = base + ST_OFF + st * ST_BYTES;
                 const unsigned long long kv_u = reinterpret_cast<unsigned long long>(p.kv);
 #pragma unroll
@@ -570,7 +457,6 @@ __global__ void __launch_bounds__(TC_THREADS, 1) attn_tc_kernel(const AttnParams
                     cp_async16_zfill(sbase + ST_SCALE + my_row * 16, reinterpret_cast<const uint8_t*>(v ? my_src_u + SCALE_OFF : kv_u), v ? 16u : 0u);
                 }
                 cp_async_arrive_noinc(bar(BAR_LOADED + st));
-                trace(tr, tc, 70 + pw, t_it);
             }
             it += w.nblk;
         }
@@ -592,11 +478,8 @@ __global__ void __launch_bounds__(TC_THREADS, 1) attn_tc_kernel(const AttnParams
 #pragma unroll 1
             for (int k = 0; k < w.nblk && ok; ++k, ++it) {
                 const uint32_t st = it % NSTAGE;
-                ok = (SMLA_HOT & 2) ? mbar_wait_hot(bar(BAR_LOADED + st), (it / NSTAGE) & 1u, abort_flag, W_LOADED)
-                                    : mbar_wait(bar(BAR_LOADED + st), (it / NSTAGE) & 1u, abort_flag, W_LOADED);
+                ok = mbar_wait_hot(bar(BAR_LOADED + st), (it / NSTAGE) & 1u, abort_flag, W_LOADED);
                 if (!ok) break;
-                trace(tr, tc, 40, it);
-                if (SMLA_DBG & 2) { mbar_arrive(bar(BAR_FULL + st)); continue; }
                 uint8_t* sp = sm + ST_OFF + st * ST_BYTES;
                 // RoPE chunks of this lane: 2 passes of 4 rows x 8 chunks
                 uint4 rv[2];
@@ -626,7 +509,6 @@ __global__ void __launch_bounds__(TC_THREADS, 1) attn_tc_kernel(const AttnParams
                     v.z = mul_bf16x2(v.z, f); v.w = mul_bf16x2(v.w, f);
                     *reinterpret_cast<uint4*>(sp + ST_ROPE + r * 128 + ((((uint32_t)lane & 7u) ^ ((uint32_t)r & 7u)) << 4)) = v;
                 }
-                trace(tr, tc, 43, it);
                 // no-PE tiles whose scale is below the row scale: shift them onto the row scale.
                 // Lane l rewrites 16-byte chunk l of a flagged row (block l / 8).
                 uint32_t fix = __ballot_sync(0xffffffffu, uneven && smax > 0.f) & 0xffu;
@@ -644,10 +526,8 @@ __global__ void __launch_bounds__(TC_THREADS, 1) attn_tc_kernel(const AttnParams
                         *q4 = v;
                     }
                 }
-                trace(tr, tc, 46, it);
                 fence_proxy_async();
                 mbar_arrive(bar(BAR_FULL + st));
-                trace(tr, tc, 50, it);
             }
         }
     } else if (warp == MMA_WARP && lane == 0) {
@@ -676,7 +556,6 @@ __global__ void __launch_bounds__(TC_THREADS, 1) attn_tc_kernel(const AttnParams
                 ok = mbar_wait_thread(bar(BAR_FULL + st), (it / NSTAGE) & 1u, abort_flag, W_FULL);
                 if (!ok) break;
                 tc_fence_after();
-                trace(tr, tc, 80, it);
                 const uint32_t kb_lo = desc_lo(base + ST_OFF + st * ST_BYTES, 16);
                 const uint32_t d = tmem + TM_S + 64 * b;
 #pragma unroll
@@ -693,7 +572,6 @@ __global__ void __launch_bounds__(TC_THREADS, 1) attn_tc_kernel(const AttnParams
                             make_desc(kb_lo + ((ST_ROPE + ks * 32) >> 4), DESC_HI_SW128), IDESC_QK_BF16, true);
                 }
                 tc_commit(bar(BAR_SREADY + b));
-                trace(tr, tc, 81, it);
             }
         }
     } else if (warp == MMA_WARP + 1 && lane == 0) {
@@ -708,7 +586,6 @@ __global__ void __launch_bounds__(TC_THREADS, 1) attn_tc_kernel(const AttnParams
                 ok = mbar_wait_thread(bar(BAR_PREADY + b), (it >> 1) & 1u, abort_flag, W_PREADY);
                 if (!ok) break;
                 tc_fence_after();
-                trace(tr, tc, 82, it);
                 // V = the no-PE bytes of the same stage, read MN-major: 128-dim chunks 8192 B apart,
                 // 8-token groups 1024 B apart; this CTA's half of the output dims is two chunks.
                 const uint32_t vb_lo = desc_lo(base + ST_OFF + st * ST_BYTES + (uint32_t)half * 2 * KV_CHUNK, KV_CHUNK);
@@ -719,7 +596,6 @@ __global__ void __launch_bounds__(TC_THREADS, 1) attn_tc_kernel(const AttnParams
                 }
                 tc_commit(bar(BAR_EMPTY + st));
                 tc_commit(bar(BAR_PVDONE + b));
-                trace(tr, tc, 83, it);
             }
         }
     }
@@ -736,14 +612,9 @@ __global__ void __launch_bounds__(TC_THREADS, 1) attn_tc_kernel(const AttnParams
         tc_fence_after();
         tmem_dealloc(tmem, TMEM_COLS);
     }
-    trace(tr, tc, 3, 0);
 }
 
 }  // namespace
-
-static Trace g_trace = {nullptr, 0};
-void set_attn_trace(long long* buf, int cap) { g_trace.buf = buf; g_trace.cap = cap; }
-void get_attn_trace(long long** buf, int* cap) { *buf = g_trace.buf; *cap = g_trace.cap; }
 
 int launch_attn_tc(const AttnParams& p, cudaStream_t stream) {
     if (p.num_tokens == 0) return 0;
@@ -765,7 +636,7 @@ int launch_attn_tc(const AttnParams& p, cudaStream_t stream) {
     // Without a scheduler the grid is persistent: at most one CTA per SM, each pair walks its share of the requests.
     const int max_pairs = (dev < 64 && sm_count[dev] >= 2) ? sm_count[dev] / 2 : 1;
     const int parts = p.sched ? p.num_parts : (p.num_tokens < max_pairs ? p.num_tokens : max_pairs);
-    attn_tc_kernel<<<2 * parts, TC_THREADS, SMEM_ALLOC, stream>>>(p, g_trace);
+    attn_tc_kernel<<<2 * parts, TC_THREADS, SMEM_ALLOC, stream>>>(p);
     return check_launch("attn_tc_kernel");
 }
 

@@ -92,9 +92,7 @@ int launch_combine_parts(const float* o_parts, const float* lse_parts, __nv_bflo
                          const float* attn_sink, cudaStream_t stream);
 int launch_attn_scalar(const AttnParams& p, cudaStream_t stream);
 int launch_attn_tc(const AttnParams& p, cudaStream_t stream);
-int launch_attn_tc2(const AttnParams& p, cudaStream_t stream);
-void set_attn_trace(long long* buf, int cap);
-void get_attn_trace(long long** buf, int* cap);
+int launch_attn_pair(const AttnParams& p, cudaStream_t stream);
 int launch_pack_kv(const __nv_bfloat16* kv, uint8_t* packed, int64_t num_rows, cudaStream_t stream);
 int launch_mqa_logits_scalar(const uint8_t* q, const uint8_t* k, const float* k_scale, const float* weights,
                              const int32_t* ks, const int32_t* ke, float* logits, int s_q, int num_heads,

@@ -291,6 +291,18 @@ __device__ __forceinline__ void named_bar_sync(uint32_t id, uint32_t threads) {
     asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
 }
 
+// Named barrier that also ORs a predicate over its participants: every thread receives the same
+// answer, so warps that must leave a loop together can decide on it.
+__device__ __forceinline__ bool named_bar_or(uint32_t id, uint32_t threads, bool pred) {
+    uint32_t r;
+    asm volatile(
+        "{\n\t.reg .pred p, q;\n\tsetp.ne.b32 q, %3, 0;\n\t"
+        "bar.red.or.pred p, %1, %2, q;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(r) : "r"(id), "r"(threads), "r"((uint32_t)pred) : "memory");
+    return r != 0;
+}
+
 // ------------------------------------------------------------------ descriptors
 // Shared-memory matrix descriptor of tcgen05.mma: start address, leading / stride byte offsets
 // (all in 16-byte units), descriptor version 1 (bits 46-47) and the swizzle mode (bits 61-63).
@@ -328,6 +340,39 @@ __device__ __forceinline__ void mma_f8_ts(uint32_t d_tmem, uint32_t a_tmem, uint
         "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
         "tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], [%1], %2, %3, p;\n\t}"
         ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"((uint32_t)accumulate) : "memory");
+}
+
+// ------------------------------------------------------------------ CTA-pair forms (cta_group::2)
+// Tensor-memory allocation for a pair of CTAs (ranks 2k, 2k+1 of a cluster): executed by one warp
+// with the same index in both CTAs, each passing the same shared-memory offset.
+__device__ __forceinline__ void tmem_alloc_pair(uint32_t smem_dst, uint32_t cols) {
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_dst), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish_pair() {
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc_pair(uint32_t taddr, uint32_t cols) {
+    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols) : "memory");
+}
+// Arrives once on the barrier (a shared::cluster address: this CTA's or, through mapa_shared, the
+// partner's) when every pair MMA issued so far by this thread has completed in both CTAs.
+__device__ __forceinline__ void tc_commit_pair(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+// D (+)= A * B over the pair, M = 128: each CTA supplies 64 rows of A and N/2 rows of B at the same
+// shared-memory offsets and receives its 64 rows of D as 128 lanes x N/2 columns (lanes 0-63 hold
+// columns [0, N/2) of the rows, lanes 64-127 columns [N/2, N)).  Issued by one thread of the even CTA.
+__device__ __forceinline__ void mma_pair_f8(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, bool accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::2.kind::f8f6f4 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"((uint32_t)accumulate) : "memory");
+}
+__device__ __forceinline__ void mma_pair_f16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, bool accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"((uint32_t)accumulate) : "memory");
 }
 
 // Descriptor halves for operands whose address changes while everything else stays fixed:
