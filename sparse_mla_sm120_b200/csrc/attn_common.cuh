@@ -73,6 +73,22 @@ __device__ __forceinline__ uint32_t rescale_e4m3x4(uint32_t w, __half2 ratio) {
     return (uint32_t)ra | ((uint32_t)rb << 16);
 }
 
+// Divides four packed e4m3 values by 2^d with integer arithmetic: the exponent field of every byte drops
+// by d (`sub` = d * 8 in every byte, d <= 15).  Exact while the result stays a normal number; a result
+// below 2^-6 is cut to the subnormal grid or to zero (off by at most 2^-7, i.e. 2^-15 of the largest
+// e4m3 value), which is far below the rounding step of the values that dominate a row.
+__device__ __forceinline__ uint32_t shift_down_e4m3x4(uint32_t w, uint32_t sub) {
+    const uint32_t t = ((w & 0x7f7f7f7fu) | 0x80808080u) - sub;   // bit 7 of a byte survives iff its magnitude >= sub
+    const uint32_t m = t & 0x80808080u;
+    const uint32_t keep = (m - (m >> 7)) | m;                      // 0xff in the bytes that did not underflow
+    return (t & 0x7f7f7f7fu & keep) | (w & 0x80808080u);
+}
+// d * 8 in every byte for a ratio 2^-d (a power of two <= 1).
+__device__ __forceinline__ uint32_t shift_bytes_of_ratio(float ratio) {
+    const int d = min(127 - (int)(__float_as_uint(ratio) >> 23), 15);
+    return (uint32_t)(d * 8) * 0x01010101u;
+}
+
 __device__ __forceinline__ uint32_t mul_bf16x2(uint32_t w, __nv_bfloat162 f) {
     __nv_bfloat162 r = __hmul2(*reinterpret_cast<__nv_bfloat162*>(&w), f);
     return *reinterpret_cast<uint32_t*>(&r);

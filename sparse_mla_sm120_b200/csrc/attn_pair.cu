@@ -55,26 +55,32 @@ using namespace ptx;
 using namespace attn;
 
 constexpr int N_SM_WARPS = 8, N_PR_WARPS = 4, N_FX_WARPS = 8;
+constexpr int N_PRK_WARPS = 2;    // gather: 2 warps for the K part, 2 for the V part
+constexpr int N_FXK_WARPS = 4;    // fix-up: 4 warps for own rows, 4 for the partner's
 constexpr int FX_ROWS = 8;    // rows of a tile per fix-up warp
 constexpr int FX_WARP0 = N_SM_WARPS + N_PR_WARPS;
 constexpr int MMA_WARP = FX_WARP0 + N_FX_WARPS;
 constexpr int PAIR_THREADS = (MMA_WARP + 4) * 32;
-// Register budgets after the warpgroups trade registers (see attn_tc.cu for the rule they obey).
-constexpr int REGS_LAUNCH = 80, REGS_SOFTMAX = 128, REGS_OTHER = 48;
-static_assert(N_SM_WARPS * 32 * REGS_SOFTMAX + (N_PR_WARPS + N_FX_WARPS) * 32 * REGS_OTHER + 128 * REGS_LAUNCH
+// Register budgets after the warpgroups trade registers.  setmaxnreg.inc can only draw on what the CTA
+// was launched with (PAIR_THREADS x REGS_LAUNCH), so the budgets must fit it or the increase would block
+// for ever; the launcher checks the compiled register count against REGS_LAUNCH before it launches.
+// With 48 registers the gather and fix-up loops spilled to local memory, which made every step of
+// theirs several times slower; the two MMA-issuing threads need few registers, so their warpgroup gives
+// up half of its allocation too.
+constexpr int REGS_LAUNCH = 80, REGS_SOFTMAX = 136, REGS_OTHER = 56, REGS_MMA = 40;
+static_assert(N_SM_WARPS * 32 * REGS_SOFTMAX + (N_PR_WARPS + N_FX_WARPS) * 32 * REGS_OTHER + 128 * REGS_MMA
                   <= PAIR_THREADS * REGS_LAUNCH, "register budgets exceed what the CTA owns");
 static_assert(65536 / PAIR_THREADS / 8 * 8 == REGS_LAUNCH, "launch-time registers per thread");
 
 constexpr int TILE_N = 128;            // tokens per tile: two scheduler blocks, 64 rows gathered by each CTA
 constexpr int OWN_N = 64;
-constexpr int NK = 2, NV = 2;          // K stages (own rows) and V stages (V slots + scale triples)
+constexpr int NK = 3, NV = 2;          // K stages (own rows) and V stages (V slots + scale triples)
 constexpr int P_SHIFT = 5;             // P' is stored as e4m3(P' * 2^P_SHIFT)
 constexpr float RESCALE_TAU = 3.0f;    // lazy-rescale threshold (log2 units); P' <= 2^TAU
 
 // shared-memory map (bytes from a 1024-aligned base)
 constexpr uint32_t CHUNK = OWN_N * 128;              // one 128-dim chunk of 64 rows, K-major 128B swizzle
-constexpr uint32_t QN_OFF = 0;                       // Q no-PE e4m3: 4 chunks x [64 heads x 128 B]
-constexpr uint32_t QR_OFF = QN_OFF + 4 * CHUNK;      // Q RoPE bf16: [64 heads x 128 B]
+constexpr uint32_t QR_OFF = 0;                       // Q RoPE bf16: [64 heads x 128 B]
 constexpr uint32_t PB_OFF = QR_OFF + CHUNK;          // P' e4m3: 2 buffers x [64 heads x 128 tokens]
 constexpr uint32_t KS_OFF = PB_OFF + 2 * CHUNK;      // K stages
 constexpr uint32_t KS_ROPE = 4 * CHUNK;              //   RoPE of the own rows
@@ -100,7 +106,7 @@ static_assert(SMEM_ALLOC <= 227 * 1024, "shared memory budget");
 static_assert(KS_BYTES % 1024 == 0 && VS_BYTES % 1024 == 0 && KS_OFF % 1024 == 0, "swizzled tiles need 1024-byte alignment");
 
 constexpr uint32_t TMEM_COLS = 512;
-constexpr uint32_t TM_O = 0, TM_S = 256;   // O 256 columns; score buffer b at 256 + 64 b
+constexpr uint32_t TM_O = 0, TM_S = 256, TM_Q = 384;   // O 256 columns; score buffer b at 256 + 64 b; Q no-PE 128 columns
 
 constexpr uint32_t IDESC_QK_F8 = instr_desc(FMT_E4M3, FMT_E4M3, false, false, 128, TILE_N);
 constexpr uint32_t IDESC_QK_BF16 = instr_desc(FMT_BF16, FMT_BF16, false, false, 128, TILE_N);
@@ -110,6 +116,34 @@ constexpr uint32_t DESC_HI_SW128 = desc_hi(1024, (uint32_t)SWIZZLE_128B);
 // give-up codes reported through status[0]
 enum { W_KEMPTY = 21, W_KLOADED = 22, W_KFULL = 23, W_TRIP = 24, W_VEMPTY = 25, W_VLOADED = 26, W_VFULL = 27,
        W_SREADY = 28, W_SFREE = 29, W_PREADY = 30, W_PVDONE = 31, W_QREADY = 32 };
+
+#ifdef SMLA_TRACE
+// Timeline of one CTA (instrumented builds only): lane 0 of every warp appends (tag, tile, clock) records.
+__device__ long long* g_trace_buf = nullptr;   // [warps][cap][2]
+__device__ int g_trace_cap = 0;
+struct TraceCursor { int n = 0; };
+__device__ int g_trace_block = 0;
+__device__ __forceinline__ void trace(TraceCursor& c, int tag, int tile) {
+    if (g_trace_buf != nullptr && (int)blockIdx.x == g_trace_block && (threadIdx.x & 31) == 0 && c.n < g_trace_cap) {
+        long long* slot = g_trace_buf + ((size_t)(threadIdx.x >> 5) * g_trace_cap + c.n) * 2;
+        slot[0] = ((long long)tag << 32) | (unsigned)tile;
+        slot[1] = clock64();
+        ++c.n;
+    }
+}
+#define TRACE(tag, tile) trace(tcur, tag, (int)(tile))
+#else
+#define TRACE(tag, tile)
+#endif
+#ifdef SMLA_PROF
+// Cycle sum of one phase (bin SMLA_PROF, chosen at compile time) per warp of one CTA, written once at the end:
+// PROF(i) adds the time since the last PROF point to the sum when i is the chosen bin.
+__device__ long long* g_prof_buf = nullptr;     // [warps][2]: the sum and the kernel's length
+__device__ int g_prof_block = 0;
+#define PROF(i) { const unsigned now_ = (unsigned)clock(); if ((i) == SMLA_PROF) prof_acc += now_ - prof_last; prof_last = now_; }
+#else
+#define PROF(i)
+#endif
 
 __device__ __forceinline__ uint32_t swz(uint32_t row, uint32_t chunk16) { return row * 128u + ((chunk16 ^ (row & 7u)) << 4); }
 
@@ -124,6 +158,15 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PAIR_THREADS, 1) att
     auto bar = [&](int i) -> uint32_t { return base + BAR_OFF + 8u * i; };
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+#ifdef SMLA_TRACE
+    TraceCursor tcur;
+#endif
+#ifdef SMLA_PROF
+    unsigned prof_acc = 0;
+    unsigned prof_last = (unsigned)clock();
+    const unsigned prof_start = prof_last;
+#endif
+    TRACE(1, 0);
     const uint32_t rank = cluster_ctarank();          // 0: the CTA that issues the MMAs
     const int part = blockIdx.x >> 1;
     const SchedMeta meta = load_meta(p, part);
@@ -132,13 +175,13 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PAIR_THREADS, 1) att
 
     if (tid == 0) {
         for (int s = 0; s < NK; ++s) {
-            mbar_init(bar(BAR_KLOADED + s), N_PR_WARPS * 32);   // one arrive per issuer thread, when its copies have landed
-            mbar_init(bar(BAR_KFULLP + s), 2 * N_FX_WARPS);
-            mbar_init(bar(BAR_TRIP + s), N_FX_WARPS);
-            mbar_init(bar(BAR_KEMPTY + s), 1 + N_FX_WARPS);     // the score MMAs have read the stage and the own V bytes are copied
+            mbar_init(bar(BAR_KLOADED + s), N_PRK_WARPS * 32);   // one arrive per issuer thread, when its copies have landed
+            mbar_init(bar(BAR_KFULLP + s), 2 * N_FXK_WARPS);
+            mbar_init(bar(BAR_TRIP + s), N_FXK_WARPS);
+            mbar_init(bar(BAR_KEMPTY + s), 1 + N_FXK_WARPS);     // the score MMAs have read the stage and the own V bytes are copied
         }
         for (int s = 0; s < NV; ++s) {
-            mbar_init(bar(BAR_VLOADED + s), N_PR_WARPS * 32);
+            mbar_init(bar(BAR_VLOADED + s), (N_PR_WARPS - N_PRK_WARPS) * 32);
             mbar_init(bar(BAR_VFULLP + s), 2 * N_FX_WARPS);
             mbar_init(bar(BAR_VEMPTY + s), 1);
         }
@@ -160,6 +203,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PAIR_THREADS, 1) att
     __syncthreads();
     cluster_sync_all();          // the partner's barriers exist before anything arrives on them
     tc_fence_after();
+    TRACE(6, 0);
     const uint32_t tmem = *tmem_slot;
     auto barp = [&](int i) -> uint32_t { return mapa_shared(bar(i), 0); };   // the even CTA's copy of barrier i
 
@@ -167,6 +211,8 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PAIR_THREADS, 1) att
 
     if (warp < N_SM_WARPS) setmaxnreg_inc<REGS_SOFTMAX>();
     else if (warp < MMA_WARP) setmaxnreg_dec<REGS_OTHER>();
+    else setmaxnreg_dec<REGS_MMA>();
+    TRACE(7, 0);
 
     if (warp < N_SM_WARPS) {
         // =================================================================== softmax + epilogue
@@ -182,7 +228,6 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PAIR_THREADS, 1) att
         float* sqv = xch + 2 * 4 * 64;                         // [64]
         const bool wide_out = (reinterpret_cast<size_t>(p.out) & 31) == 0;        // rows are 1024 bytes apart
         const bool wide_acc = (reinterpret_cast<size_t>(p.o_accum) & 31) == 0;
-        const int gt = ((warp >> 1) << 5) + lane;         // thread index inside the group of four warps (0..127)
         uint32_t it = 0;                                  // running tile counter of this CTA
         bool dead = false;                                // a wait of this warp gave up: no more work, only barriers
         bool stop = false;
@@ -190,52 +235,89 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PAIR_THREADS, 1) att
             Work w;
             if (!get_work(p, meta, req, w)) continue;
             const int nst = (w.nblk + 1) >> 1;
-            // ---- Q: the group quantises its 32 heads; four threads per head, 128 no-PE dims + 16 RoPE dims each ----
-            if (!dead) {
-                const int qrow = grp * 32 + (gt >> 2), qpart = gt & 3;
-                const int qhead = head0 + qrow;
-                const bool qv = qrow < heads_cta && qhead < p.num_heads;
-                const __nv_bfloat16* src = p.q + ((size_t)req * p.num_heads + (qv ? qhead : 0)) * D_QK;
-                float am = 0.f;
-                uint4 x[16];
+            // ---- Q: warp (quarter, ch) quantises no-PE dims [256*ch, +256) of the 32 heads of its lane quarter into
+            // tensor memory (the A operand of a pair MMA wants the CTA's 64 rows twice: quarters 2 and 3 repeat the
+            // work of quarters 0 and 1).  The 16x256b store shape takes a row from four lanes: lane (g = lane/4,
+            // c = lane%4) holds, for every block i of 32 dims, dims [32i + 8c, +8) of rows g and g + 8 of a 16-row
+            // group, which is also how it loads them (16 bytes of bf16 per row and block).  A group stays in
+            // registers between finding its rows' maxima and quantising them.
+            {
+                const int g = lane >> 2, c4 = lane & 3;
+#pragma unroll 1
+                for (int hf = 0; hf < 2; ++hf) {
+                    const int r_a = grp * 32 + 16 * hf + g, r_b = r_a + 8;      // head rows inside the CTA
+                    const bool v_a = !dead && r_a < heads_cta && head0 + r_a < p.num_heads;
+                    const bool v_b = !dead && r_b < heads_cta && head0 + r_b < p.num_heads;
+                    const __nv_bfloat16* src_a = p.q + ((size_t)req * p.num_heads + (v_a ? head0 + r_a : 0)) * D_QK + ch * 256 + c4 * 8;
+                    const __nv_bfloat16* src_b = p.q + ((size_t)req * p.num_heads + (v_b ? head0 + r_b : 0)) * D_QK + ch * 256 + c4 * 8;
+                    uint4 xa[8], xb[8];
 #pragma unroll
-                for (int i = 0; i < 16; ++i) {
-                    x[i] = qv ? __ldg(reinterpret_cast<const uint4*>(src + qpart * 128 + 8 * i)) : make_uint4(0, 0, 0, 0);
-                    am = fmaxf(am, fmaxf(fmaxf(fmaxf(fabsf(bf16lo(x[i].x)), fabsf(bf16hi(x[i].x))), fmaxf(fabsf(bf16lo(x[i].y)), fabsf(bf16hi(x[i].y)))),
-                                         fmaxf(fmaxf(fabsf(bf16lo(x[i].z)), fabsf(bf16hi(x[i].z))), fmaxf(fabsf(bf16lo(x[i].w)), fabsf(bf16hi(x[i].w))))));
-                }
-                uint4 r0 = make_uint4(0, 0, 0, 0), r1 = r0;
-                if (qv) {
-                    r0 = __ldg(reinterpret_cast<const uint4*>(src + D_NOPE + qpart * 16));
-                    r1 = __ldg(reinterpret_cast<const uint4*>(src + D_NOPE + qpart * 16 + 8));
-                }
-                am = fmaxf(am, __shfl_xor_sync(0xffffffffu, am, 1));
-                am = fmaxf(am, __shfl_xor_sync(0xffffffffu, am, 2));
-                const float sq = pow2_ceil(fmaxf(am, 1e-4f) * (1.f / 448.f));
-                const float iq = __uint_as_float(0x7f000000u - __float_as_uint(sq));   // 1/sq, sq a power of two
-                uint8_t* qdst = sm + QN_OFF + qpart * CHUNK;
+                    for (int i = 0; i < 8; ++i) {
+                        xa[i] = v_a ? __ldg(reinterpret_cast<const uint4*>(src_a + 32 * i)) : make_uint4(0, 0, 0, 0);
+                        xb[i] = v_b ? __ldg(reinterpret_cast<const uint4*>(src_b + 32 * i)) : make_uint4(0, 0, 0, 0);
+                    }
+                    auto absmax8 = [](const uint4& a) {
+                        return fmaxf(fmaxf(fmaxf(fabsf(bf16lo(a.x)), fabsf(bf16hi(a.x))), fmaxf(fabsf(bf16lo(a.y)), fabsf(bf16hi(a.y)))),
+                                     fmaxf(fmaxf(fabsf(bf16lo(a.z)), fabsf(bf16hi(a.z))), fmaxf(fabsf(bf16lo(a.w)), fabsf(bf16hi(a.w)))));
+                    };
+                    float am_a = 0.f, am_b = 0.f;
 #pragma unroll
-                for (int c = 0; c < 8; ++c) {
-                    const uint4 a = x[2 * c], b4 = x[2 * c + 1];
-                    uint4 o;
-                    o.x = pack_e4m3x4(bf16lo(a.x) * iq, bf16hi(a.x) * iq, bf16lo(a.y) * iq, bf16hi(a.y) * iq);
-                    o.y = pack_e4m3x4(bf16lo(a.z) * iq, bf16hi(a.z) * iq, bf16lo(a.w) * iq, bf16hi(a.w) * iq);
-                    o.z = pack_e4m3x4(bf16lo(b4.x) * iq, bf16hi(b4.x) * iq, bf16lo(b4.y) * iq, bf16hi(b4.y) * iq);
-                    o.w = pack_e4m3x4(bf16lo(b4.z) * iq, bf16hi(b4.z) * iq, bf16lo(b4.w) * iq, bf16hi(b4.w) * iq);
-                    *reinterpret_cast<uint4*>(qdst + swz(qrow, c)) = o;
+                    for (int i = 0; i < 8; ++i) { am_a = fmaxf(am_a, absmax8(xa[i])); am_b = fmaxf(am_b, absmax8(xb[i])); }
+                    am_a = fmaxf(am_a, __shfl_xor_sync(0xffffffffu, am_a, 1)); am_b = fmaxf(am_b, __shfl_xor_sync(0xffffffffu, am_b, 1));
+                    am_a = fmaxf(am_a, __shfl_xor_sync(0xffffffffu, am_a, 2)); am_b = fmaxf(am_b, __shfl_xor_sync(0xffffffffu, am_b, 2));
+                    // both column halves of a row agree on one scale (the repeating quarter writes the same values)
+                    if (c4 == 0) { xch[ch * 64 + r_a] = am_a; xch[ch * 64 + r_b] = am_b; }
+                    named_bar_sync(1 + grp, 128);
+                    am_a = fmaxf(am_a, xch[(1 - ch) * 64 + r_a]);
+                    am_b = fmaxf(am_b, xch[(1 - ch) * 64 + r_b]);
+                    const float sq_a = pow2_ceil(fmaxf(am_a, 1e-4f) * (1.f / 448.f)), sq_b = pow2_ceil(fmaxf(am_b, 1e-4f) * (1.f / 448.f));
+                    const float ia = __uint_as_float(0x7f000000u - __float_as_uint(sq_a));   // 1/sq, sq a power of two
+                    const float ib = __uint_as_float(0x7f000000u - __float_as_uint(sq_b));
+                    if (c4 == 0) { sqv[r_a] = sq_a; sqv[r_b] = sq_b; }
+                    if (!dead) {
+#pragma unroll
+                        for (int h4 = 0; h4 < 2; ++h4) {
+                            uint32_t wq[16];
+#pragma unroll
+                            for (int kk = 0; kk < 4; ++kk) {
+                                const uint4 a = xa[4 * h4 + kk], b4 = xb[4 * h4 + kk];
+                                wq[4 * kk + 0] = pack_e4m3x4(bf16lo(a.x) * ia, bf16hi(a.x) * ia, bf16lo(a.y) * ia, bf16hi(a.y) * ia);
+                                wq[4 * kk + 1] = pack_e4m3x4(bf16lo(a.z) * ia, bf16hi(a.z) * ia, bf16lo(a.w) * ia, bf16hi(a.w) * ia);
+                                wq[4 * kk + 2] = pack_e4m3x4(bf16lo(b4.x) * ib, bf16hi(b4.x) * ib, bf16lo(b4.y) * ib, bf16hi(b4.y) * ib);
+                                wq[4 * kk + 3] = pack_e4m3x4(bf16lo(b4.z) * ib, bf16hi(b4.z) * ib, bf16lo(b4.w) * ib, bf16hi(b4.w) * ib);
+                            }
+                            tmem_st_16x256b_x4(tmem + ((uint32_t)(quarter * 32 + 16 * hf) << 16) + TM_Q + ch * 64 + h4 * 32, wq);
+                        }
+                    }
                 }
-                const __nv_bfloat162 f = __float2bfloat162_rn(iq);
-                r0.x = mul_bf16x2(r0.x, f); r0.y = mul_bf16x2(r0.y, f); r0.z = mul_bf16x2(r0.z, f); r0.w = mul_bf16x2(r0.w, f);
-                r1.x = mul_bf16x2(r1.x, f); r1.y = mul_bf16x2(r1.y, f); r1.z = mul_bf16x2(r1.z, f); r1.w = mul_bf16x2(r1.w, f);
-                *reinterpret_cast<uint4*>(sm + QR_OFF + swz(qrow, 2 * qpart)) = r0;
-                *reinterpret_cast<uint4*>(sm + QR_OFF + swz(qrow, 2 * qpart + 1)) = r1;
-                if (qpart == 0) sqv[qrow] = sq;
-                fence_proxy_async();
+                __syncwarp();
+                named_bar_sync(1 + grp, 128);   // the scales of the group's 32 rows are in sqv
+                // Q RoPE (shared memory, bf16, pre-divided by sq): the two warps of quarter grp store 16 rows each
+                if (thalf == 0 && !dead) {
+#pragma unroll
+                    for (int gg = 0; gg < 4; ++gg) {
+                        const int rl = ch * 16 + gg * 4 + (lane >> 3);          // row inside the group's 32
+                        const int hr = grp * 32 + rl;
+                        uint4 c = make_uint4(0, 0, 0, 0);
+                        if (hr < heads_cta && head0 + hr < p.num_heads)
+                            c = __ldg(reinterpret_cast<const uint4*>(p.q + ((size_t)req * p.num_heads + head0 + hr) * D_QK + D_NOPE + (lane & 7) * 8));
+                        const __nv_bfloat162 f = __float2bfloat162_rn(__uint_as_float(0x7f000000u - __float_as_uint(sqv[hr])));   // 1/sq
+                        c.x = mul_bf16x2(c.x, f); c.y = mul_bf16x2(c.y, f); c.z = mul_bf16x2(c.z, f); c.w = mul_bf16x2(c.w, f);
+                        *reinterpret_cast<uint4*>(sm + QR_OFF + swz((uint32_t)hr, (uint32_t)lane & 7u)) = c;
+                    }
+                    fence_proxy_async();
+                }
+                if (!dead) {
+                    tmem_wait_st();
+                    tc_fence_before();     // also orders the previous epilogue's TMEM reads before the next MMAs
+                }
             }
             if (named_bar_or(1 + grp, 128, dead || *abort_flag != 0)) { stop = true; break; }
+            TRACE(2, it);
+            PROF(11);
             const float my_sqc = live ? sqv[hrow] * p.sm_scale * LOG2E : 0.f;
             __syncwarp();
-            if (lane == 0) mbar_arrive_cluster(barp(BAR_QREADYP));
+            if (lane == 0) mbar_arrive_remote(barp(BAR_QREADYP));
 
             float m_run = -INFINITY;   // running maximum of z (lags by at most RESCALE_TAU)
             float l_run = 0.f;         // this thread's share of the sum of P'/s_t (scaled by 2^P_SHIFT)
@@ -245,16 +327,21 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PAIR_THREADS, 1) att
                 float z[32];
                 float mx_loc = -INFINITY;
                 const float4* tok = reinterpret_cast<const float4*>(sm + VS_OFF + vs * VS_BYTES + VS_TRIP) + 64 * thalf + 32 * ch;
+                PROF(0);
                 if (!dead) dead = !mbar_wait_hot(bar(BAR_SREADY + b), (it >> 1) & 1u, abort_flag, W_SREADY);
-                if (!dead) dead = !mbar_wait(bar(BAR_TRIP + (it % NK)), (it / NK) & 1u, abort_flag, W_TRIP);
+                PROF(1);
+                TRACE(10, it);
+                if (!dead) dead = !mbar_wait_hot(bar(BAR_TRIP + (it % NK)), (it / NK) & 1u, abort_flag, W_TRIP);
+                PROF(2);
                 if (!dead) {
                     tc_fence_after();
                     uint32_t sv[32];
                     tmem_ld32(lane_addr + TM_S + 64 * b + 32 * ch, sv);
                     tmem_wait_ld();
+                    PROF(3);
                     tc_fence_before();
                     __syncwarp();
-                    if (lane == 0) mbar_arrive_cluster(barp(BAR_SFREEP + b));   // the score buffer may be overwritten
+                    if (lane == 0) mbar_arrive_remote(barp(BAR_SFREEP + b));   // the score buffer may be overwritten
                     float mx0 = -INFINITY, mx1 = -INFINITY;
 #pragma unroll
                     for (int t = 0; t < 32; t += 4) {
@@ -271,10 +358,12 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PAIR_THREADS, 1) att
                     }
                     mx_loc = fmaxf(mx0, mx1);
                     xch[(b * 4 + xpart) * 64 + hrow] = mx_loc;
+                    PROF(4);
                 }
                 if (named_bar_or(1 + grp, 128, dead || *abort_flag != 0)) { stop = true; break; }   // the four partial row maxima are in place
                 const float* xr = xch + b * 256 + hrow;
                 const float mx = fmaxf(fmaxf(xr[0], xr[64]), fmaxf(xr[128], xr[192]));
+                PROF(5);
                 const bool grow = mx > m_run + RESCALE_TAU;   // false while the row has seen no valid entry
                 if (__any_sync(0xffffffffu, grow)) {
                     if (j > 0) {   // the accumulator holds earlier tiles: wait for the last P.V, then scale it
@@ -297,10 +386,12 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PAIR_THREADS, 1) att
                         tmem_wait_st();
                     }
                 }
+                PROF(6);
                 if (it >= 2) {   // the P.V that read this P' buffer two tiles ago has completed
                     dead = !mbar_wait_hot(bar(BAR_PVDONE + b), ((it - 2) >> 1) & 1u, abort_flag, W_PVDONE);
                     if (dead) continue;
                 }
+                PROF(7);
                 const float m_off = ((m_run == -INFINITY) ? 0.f : m_run) - (float)P_SHIFT;
                 uint32_t pw[8];
                 float l0 = 0.f, l1 = 0.f;
@@ -313,16 +404,21 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PAIR_THREADS, 1) att
                     pw[t >> 2] = pack_e4m3x4(p0, p1, p2, p3);
                 }
                 l_run += l0 + l1;
+                PROF(8);
                 // P' of tokens [64*thalf + 32*ch, +32) of head hrow: two 16-byte pieces of the row
                 uint8_t* pb = sm + PB_OFF + b * CHUNK;
                 *reinterpret_cast<uint4*>(pb + swz(hrow, 4 * thalf + 2 * ch)) = make_uint4(pw[0], pw[1], pw[2], pw[3]);
                 *reinterpret_cast<uint4*>(pb + swz(hrow, 4 * thalf + 2 * ch + 1)) = make_uint4(pw[4], pw[5], pw[6], pw[7]);
                 fence_proxy_async();
+                PROF(9);
                 tc_fence_before();
                 __syncwarp();
-                if (lane == 0) mbar_arrive_cluster(barp(BAR_PREADYP + b));
+                if (lane == 0) mbar_arrive_remote(barp(BAR_PREADYP + b));
+                PROF(10);
+                TRACE(14, it);
             }
             if (stop) break;
+            TRACE(3, it);
             // ---- epilogue ---------------------------------------------------------------------
             {
                 const uint32_t last = it - 1;
@@ -401,21 +497,23 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PAIR_THREADS, 1) att
                 }
                 tc_fence_before();                  // the accumulator reads precede the next request's first P.V
                 named_bar_sync(1 + grp, 128);       // xch is free again
+                PROF(12);
+                TRACE(4, it);
             }
         }
     } else if (warp < FX_WARP0) {
         // =================================================================== gather issuers
-        // Warp pw gathers rows [16*pw, +16) of this CTA's 64 rows of every tile (lanes 0-15 hold their
-        // row pointers) and the partner's rows [16*pw, +16) (lanes 16-31), never waiting for data.
-        // K part of a tile: the 512 no-PE bytes (one coalesced 512-byte request per row), the RoPE
-        // bytes, and the scale words of all 32 rows.  V part: bytes [256 r, +256) of the partner's
-        // rows into the V slots, and their scale words.  Rows without an entry are zero-filled.
-        // Issue order K(0) K(1) V(0) K(2) V(1) ...: the V part of a tile is needed one tile later.
+        // Warps 8-9 gather the K part of every tile (this CTA's 64 rows: the 512 no-PE bytes as one coalesced
+        // 512-byte request per row, the RoPE bytes, and the scale words of these rows and of the partner's),
+        // warps 10-11 the V part (bytes [256 r, +256) of the partner's rows into the V slots, and their scale
+        // words).  Each of the two kinds waits only for its own stage to be free, so the V part of a tile
+        // starts as soon as the P.V two tiles back has completed.  Nothing here waits for data; rows without
+        // an entry are zero-filled.  A warp covers 32 rows in two passes of 16: lanes 0-15 hold the row
+        // pointers of this CTA's rows, lanes 16-31 those of the partner's.
         const int pw = warp - N_SM_WARPS;
-        const int row0 = pw * 16;
-        const int my_row = row0 + (lane & 15);
+        const bool k_role = pw < N_PRK_WARPS;
+        const int rows0 = (k_role ? pw : pw - N_PRK_WARPS) * 32;     // first of this warp's 32 rows
         const int peer = lane >> 4;                                  // lanes 16-31 look after the partner's rows
-        const int my_n = (peer ? (1 - (int)rank) : (int)rank) * OWN_N + my_row;   // token index inside the tile
         const int pbs_shift = (p.page_block_size & (p.page_block_size - 1)) == 0 ? __ffs(p.page_block_size) - 1 : -1;
         const unsigned long long kv_u = reinterpret_cast<unsigned long long>(p.kv);
         uint32_t it = 0;
@@ -426,9 +524,11 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PAIR_THREADS, 1) att
             const int nst = (w.nblk + 1) >> 1;
             const int32_t* idx_row = p.indices + (size_t)req * p.topk;
             const int lim = min(w.len, (w.blk0 + w.nblk) * BLOCK_N);
-            auto fetch_idx = [&](int j) -> int {
-                const int pos = w.blk0 * BLOCK_N + j * TILE_N + my_n;
-                return (j < nst && pos < lim) ? __ldg(idx_row + pos) : -1;
+            // index of (tile j, pass ps) for this lane: row rows0 + 16 ps + lane % 16 of this CTA or of the partner
+            auto fetch_idx = [&](int j, int ps) -> int {
+                const int n = (peer ? (1 - (int)rank) : (int)rank) * OWN_N + rows0 + 16 * ps + (lane & 15);
+                const int pos = w.blk0 * BLOCK_N + j * TILE_N + n;
+                return (j < nst && pos < lim && (!k_role ? peer != 0 : true)) ? __ldg(idx_row + pos) : -1;
             };
             auto row_ptr = [&](int idx) -> unsigned long long {
                 if (idx < 0) return 0ull;      // rows without an entry travel as a null source: their copies zero-fill
@@ -438,117 +538,95 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PAIR_THREADS, 1) att
                         ? p.kv + (int64_t)(u >> pbs_shift) * p.block_stride + (int64_t)(u & (unsigned)(p.page_block_size - 1)) * ROW_BYTES
                         : kv_row_ptr(p.kv, idx, p.page_block_size, p.block_stride));
             };
-            auto v_part = [&](uint32_t t_it, unsigned long long src_u) -> bool {
-                const uint32_t vs = t_it % NV;
-                if (t_it >= NV && !mbar_wait_hot(bar(BAR_VEMPTY + vs), ((t_it / NV) - 1) & 1u, abort_flag, W_VEMPTY)) return false;
-                const uint32_t vbase = base + VS_OFF + vs * VS_BYTES;
-                const uint32_t piece = lane & 15;                       // 16-byte piece of the 256-byte half row
-#pragma unroll
-                for (int i = 0; i < 8; ++i) {
-                    const int r = row0 + 2 * i + peer;                  // partner's row (two rows per instruction)
-                    const unsigned long long s = __shfl_sync(0xffffffffu, src_u, 16 + 2 * i + peer);
-                    const uint32_t slot = ((2u * (1u - rank) + (uint32_t)(r >> 5)) * 2u + (piece >> 3)) * VSLOT;
-                    const bool v = s != 0ull;
-                    cp_async16_zfill(vbase + slot + swz((uint32_t)r & 31u, piece & 7u),
-                                     reinterpret_cast<const uint8_t*>(v ? s + 256u * rank + piece * 16u : kv_u), v ? 16u : 0u);
-                }
-                if (peer) {
-                    const bool v = src_u != 0ull;
-                    cp_async16_zfill(vbase + VS_RAW + my_row * 16, reinterpret_cast<const uint8_t*>(v ? src_u + SCALE_OFF : kv_u), v ? 16u : 0u);
-                }
-                cp_async_arrive_noinc(bar(BAR_VLOADED + vs));
-                return true;
-            };
-            int idx_next = fetch_idx(0), idx_next2 = fetch_idx(1);
-            unsigned long long src_prev = 0ull;
+            int idx_a = fetch_idx(0, 0), idx_b = fetch_idx(0, 1);           // this tile, passes 0 and 1
+            int nxt_a = fetch_idx(1, 0), nxt_b = fetch_idx(1, 1);           // next tile
 #pragma unroll 1
             for (int k = 0; k < nst && ok; ++k) {
-                const uint32_t t_it = it + k, ks = t_it % NK;
-                const unsigned long long my_src_u = row_ptr(idx_next);
-                idx_next = idx_next2;
-                idx_next2 = fetch_idx(k + 2);
-                if (t_it >= NK) {
-                    ok = mbar_wait_hot(bar(BAR_KEMPTY + ks), ((t_it / NK) - 1) & 1u, abort_flag, W_KEMPTY);
-                    if (!ok) break;
-                }
-                const uint32_t kbase = base + KS_OFF + ks * KS_BYTES;
-#pragma unroll
-                for (int hb = 0; hb < 2; ++hb) {       // two batches of 8 rows keep the register count low
-                    unsigned long long srcs[8];
-#pragma unroll
-                    for (int i = 0; i < 8; ++i) srcs[i] = __shfl_sync(0xffffffffu, my_src_u, hb * 8 + i);
-#pragma unroll
-                    for (int i = 0; i < 8; ++i) {
-                        const int r = row0 + hb * 8 + i;
-                        const bool v = srcs[i] != 0ull;
-                        cp_async16_zfill(kbase + (lane >> 3) * CHUNK + swz((uint32_t)r, (uint32_t)lane & 7u),
-                                         reinterpret_cast<const uint8_t*>(v ? srcs[i] + lane * 16 : kv_u), v ? 16u : 0u);
+                const uint32_t t_it = it + k;
+                const unsigned long long src_a = row_ptr(idx_a), src_b = row_ptr(idx_b);
+                idx_a = nxt_a; idx_b = nxt_b;
+                nxt_a = fetch_idx(k + 2, 0); nxt_b = fetch_idx(k + 2, 1);
+                if (k_role) {
+                    const uint32_t ks = t_it % NK;
+                    if (t_it >= NK) {
+                        ok = mbar_wait_hot(bar(BAR_KEMPTY + ks), ((t_it / NK) - 1) & 1u, abort_flag, W_KEMPTY);
+                        if (!ok) break;
                     }
-                }
+                    const uint32_t kbase = base + KS_OFF + ks * KS_BYTES;
 #pragma unroll
-                for (int g = 0; g < 4; ++g) {
-                    const unsigned long long rs = __shfl_sync(0xffffffffu, my_src_u, g * 4 + (lane >> 3));
-                    const int r = row0 + g * 4 + (lane >> 3);
-                    const bool v = rs != 0ull;
-                    cp_async16_zfill(kbase + KS_ROPE + swz((uint32_t)r, (uint32_t)lane & 7u),
-                                     reinterpret_cast<const uint8_t*>(v ? rs + ROPE_OFF + (lane & 7) * 16 : kv_u), v ? 16u : 0u);
+                    for (int ps = 0; ps < 2; ++ps) {
+                        const unsigned long long my_src_u = ps ? src_b : src_a;
+                        const int row0 = rows0 + 16 * ps;
+#pragma unroll
+                        for (int hb = 0; hb < 2; ++hb) {       // two batches of 8 rows keep the register count low
+                            unsigned long long srcs[8];
+#pragma unroll
+                            for (int i = 0; i < 8; ++i) srcs[i] = __shfl_sync(0xffffffffu, my_src_u, hb * 8 + i);
+#pragma unroll
+                            for (int i = 0; i < 8; ++i) {
+                                const int r = row0 + hb * 8 + i;
+                                const bool v = srcs[i] != 0ull;
+                                cp_async16_zfill(kbase + (lane >> 3) * CHUNK + swz((uint32_t)r, (uint32_t)lane & 7u),
+                                                 reinterpret_cast<const uint8_t*>(v ? srcs[i] + lane * 16 : kv_u), v ? 16u : 0u);
+                            }
+                        }
+#pragma unroll
+                        for (int g = 0; g < 4; ++g) {
+                            const unsigned long long rs = __shfl_sync(0xffffffffu, my_src_u, g * 4 + (lane >> 3));
+                            const int r = row0 + g * 4 + (lane >> 3);
+                            const bool v = rs != 0ull;
+                            cp_async16_zfill(kbase + KS_ROPE + swz((uint32_t)r, (uint32_t)lane & 7u),
+                                             reinterpret_cast<const uint8_t*>(v ? rs + ROPE_OFF + (lane & 7) * 16 : kv_u), v ? 16u : 0u);
+                        }
+                        {
+                            const int n = (peer ? (1 - (int)rank) : (int)rank) * OWN_N + row0 + (lane & 15);   // token index inside the tile
+                            const bool v = my_src_u != 0ull;
+                            cp_async16_zfill(kbase + KS_RAW + n * 16, reinterpret_cast<const uint8_t*>(v ? my_src_u + SCALE_OFF : kv_u), v ? 16u : 0u);
+                        }
+                    }
+                    cp_async_arrive_noinc(bar(BAR_KLOADED + ks));
+                } else {
+                    const uint32_t vs = t_it % NV;
+                    if (t_it >= NV) {
+                        ok = mbar_wait_hot(bar(BAR_VEMPTY + vs), ((t_it / NV) - 1) & 1u, abort_flag, W_VEMPTY);
+                        if (!ok) break;
+                    }
+                    const uint32_t vbase = base + VS_OFF + vs * VS_BYTES;
+                    const uint32_t piece = lane & 15;                       // 16-byte piece of the 256-byte half row
+#pragma unroll
+                    for (int ps = 0; ps < 2; ++ps) {
+                        const unsigned long long src_u = ps ? src_b : src_a;
+                        const int row0 = rows0 + 16 * ps;
+#pragma unroll
+                        for (int i = 0; i < 8; ++i) {
+                            const int r = row0 + 2 * i + peer;                  // partner's row (two rows per instruction)
+                            const unsigned long long s = __shfl_sync(0xffffffffu, src_u, 16 + 2 * i + peer);
+                            const uint32_t slot = ((2u * (1u - rank) + (uint32_t)(r >> 5)) * 2u + (piece >> 3)) * VSLOT;
+                            const bool v = s != 0ull;
+                            cp_async16_zfill(vbase + slot + swz((uint32_t)r & 31u, piece & 7u),
+                                             reinterpret_cast<const uint8_t*>(v ? s + 256u * rank + piece * 16u : kv_u), v ? 16u : 0u);
+                        }
+                        if (peer) {
+                            const bool v = src_u != 0ull;
+                            cp_async16_zfill(vbase + VS_RAW + (row0 + (lane & 15)) * 16, reinterpret_cast<const uint8_t*>(v ? src_u + SCALE_OFF : kv_u), v ? 16u : 0u);
+                        }
+                    }
+                    cp_async_arrive_noinc(bar(BAR_VLOADED + vs));
                 }
-                {
-                    const bool v = my_src_u != 0ull;
-                    cp_async16_zfill(kbase + KS_RAW + my_n * 16, reinterpret_cast<const uint8_t*>(v ? my_src_u + SCALE_OFF : kv_u), v ? 16u : 0u);
-                }
-                cp_async_arrive_noinc(bar(BAR_KLOADED + ks));
-                if (k >= 1) { ok = v_part(t_it - 1, src_prev); if (!ok) break; }
-                src_prev = my_src_u;
             }
-            if (ok && nst > 0) ok = v_part(it + nst - 1, src_prev);
             it += nst;
         }
         cp_async_wait_all();
-    } else if (warp < MMA_WARP) {
-        // =================================================================== tile fix-up
-        // Warp fw owns rows [8*fw, +8) of this CTA's rows and of the partner's rows.  K part: RoPE
-        // pre-division and uneven-scale rewrite of the own rows (-> the score MMAs may start), then,
-        // once the V stage is free, the scale triples of its 16 tokens and the copy of its rows'
-        // V bytes into the V slots.  V part: uneven-scale rewrite of the partner's half rows.
-        const int fw = warp - FX_WARP0;
-        const int row0 = fw * FX_ROWS;
-        const int my_row = row0 + (lane & 7);
+    } else if (warp < FX_WARP0 + N_FXK_WARPS) {
+        // =================================================================== tile fix-up, own rows
+        // Warp kf owns rows [16*kf, +16) of this CTA's rows (two groups of 8).  First: RoPE pre-division and
+        // uneven-scale rewrite (-> the score MMAs may start).  Then, once the V stage of the tile is free,
+        // the scale triples of its 32 tokens (its own rows and the same rows of the partner) and the copy of
+        // its rows' V bytes into the V slots (-> the K stage may be refilled).
+        const int kf = warp - FX_WARP0;
         const int blk = lane >> 3;
         uint32_t it = 0;
         bool ok = true;
-        auto v_part = [&](uint32_t t_it) -> bool {
-            const uint32_t vs = t_it % NV;
-            if (!mbar_wait_hot(bar(BAR_VLOADED + vs), (t_it / NV) & 1u, abort_flag, W_VLOADED)) return false;
-            uint8_t* vp = sm + VS_OFF + vs * VS_BYTES;
-            const float4 sc = *reinterpret_cast<const float4*>(vp + VS_RAW + my_row * 16);
-            const float smax = fmaxf(fmaxf(sc.x, sc.y), fmaxf(sc.z, sc.w));
-            const float inv_s = (smax > 0.f) ? __uint_as_float(0x7f000000u - __float_as_uint(smax)) : 0.f;
-            // ratio of (row lane % 8, this CTA's chunk (lane / 8) % 2) to the row scale: a power of two <= 1
-            const float mine = rank ? ((blk & 1) ? sc.w : sc.z) : ((blk & 1) ? sc.y : sc.x);
-            const float my_ratio = mine * inv_s;
-            uint32_t fix = __ballot_sync(0xffffffffu, my_ratio != 1.f && smax > 0.f) & 0xffffu;   // rows x 2 chunks
-            fix = (fix | (fix >> 8)) & 0xffu;
-            while (fix) {
-                const int i = __ffs(fix) - 1;
-                fix &= fix - 1;
-                const int r = row0 + i;
-                const float ratio_f = __shfl_sync(0xffffffffu, my_ratio, ((lane >> 3) & 1) * 8 + i);   // (row i, chunk (lane/8)%2)
-                if (lane < 16 && ratio_f != 1.f) {
-                    const uint32_t slot = ((2u * (1u - rank) + (uint32_t)(r >> 5)) * 2u + (uint32_t)(lane >> 3)) * VSLOT;
-                    uint4* q4 = reinterpret_cast<uint4*>(vp + slot + swz((uint32_t)r & 31u, (uint32_t)lane & 7u));
-                    const __half2 ratio = __float2half2_rn(ratio_f);
-                    uint4 v = *q4;
-                    v.x = rescale_e4m3x4(v.x, ratio); v.y = rescale_e4m3x4(v.y, ratio);
-                    v.z = rescale_e4m3x4(v.z, ratio); v.w = rescale_e4m3x4(v.w, ratio);
-                    *q4 = v;
-                }
-            }
-            fence_proxy_async();
-            __syncwarp();
-            if (lane == 0) mbar_arrive_cluster(barp(BAR_VFULLP + vs));
-            return true;
-        };
         for (int req = meta.begin_req; req <= last_req && ok; ++req) {
             Work w;
             if (!get_work(p, meta, req, w)) continue;
@@ -556,107 +634,186 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PAIR_THREADS, 1) att
 #pragma unroll 1
             for (int k = 0; k < nst && ok; ++k) {
                 const uint32_t t_it = it + k, ks = t_it % NK, vs = t_it % NV;
+                PROF(0);
                 ok = mbar_wait_hot(bar(BAR_KLOADED + ks), (t_it / NK) & 1u, abort_flag, W_KLOADED);
                 if (!ok) break;
+                PROF(1);
+                TRACE(30, t_it);
                 uint8_t* kp = sm + KS_OFF + ks * KS_BYTES;
                 uint8_t* vp = sm + VS_OFF + vs * VS_BYTES;
-                // RoPE chunks of this lane: 2 passes of 4 rows x 8 chunks
-                uint4 rv[2];
+#pragma unroll 1
+                for (int g8 = 0; g8 < 2; ++g8) {
+                    const int row0 = kf * 16 + g8 * FX_ROWS;
+                    const int my_row = row0 + (lane & 7);
+                    // RoPE chunks of this lane: 2 passes of 4 rows x 8 chunks
+                    uint4 rv[2];
 #pragma unroll
-                for (int g = 0; g < 2; ++g) rv[g] = *reinterpret_cast<const uint4*>(kp + KS_ROPE + swz((uint32_t)(row0 + g * 4 + (lane >> 3)), (uint32_t)lane & 7u));
-                // row scale, validity (a zero-filled scale word marks a row that was not loaded)
-                const float4 sc = *reinterpret_cast<const float4*>(kp + KS_RAW + (rank * OWN_N + my_row) * 16);
-                const float smax = fmaxf(fmaxf(sc.x, sc.y), fmaxf(sc.z, sc.w));
-                const bool uneven = (sc.x != smax) | (sc.y != smax) | (sc.z != smax) | (sc.w != smax);
-                const float inv_s = (smax > 0.f) ? __uint_as_float(0x7f000000u - __float_as_uint(smax)) : 0.f;
-                const float my_ratio = (blk == 0 ? sc.x : (blk == 1 ? sc.y : (blk == 2 ? sc.z : sc.w))) * inv_s;
+                    for (int g = 0; g < 2; ++g) rv[g] = *reinterpret_cast<const uint4*>(kp + KS_ROPE + swz((uint32_t)(row0 + g * 4 + (lane >> 3)), (uint32_t)lane & 7u));
+                    // row scale, validity (a zero-filled scale word marks a row that was not loaded)
+                    const float4 sc = *reinterpret_cast<const float4*>(kp + KS_RAW + (rank * OWN_N + my_row) * 16);
+                    const float smax = fmaxf(fmaxf(sc.x, sc.y), fmaxf(sc.z, sc.w));
+                    const bool uneven = (sc.x != smax) | (sc.y != smax) | (sc.z != smax) | (sc.w != smax);
+                    const float inv_s = (smax > 0.f) ? __uint_as_float(0x7f000000u - __float_as_uint(smax)) : 0.f;
+                    const float my_ratio = (blk == 0 ? sc.x : (blk == 1 ? sc.y : (blk == 2 ? sc.z : sc.w))) * inv_s;
 #pragma unroll
-                for (int g = 0; g < 2; ++g) {
-                    const int rl = g * 4 + (lane >> 3);
-                    const __nv_bfloat162 f = __float2bfloat162_rn(__shfl_sync(0xffffffffu, inv_s, rl));
-                    uint4 v = rv[g];
-                    v.x = mul_bf16x2(v.x, f); v.y = mul_bf16x2(v.y, f);
-                    v.z = mul_bf16x2(v.z, f); v.w = mul_bf16x2(v.w, f);
-                    *reinterpret_cast<uint4*>(kp + KS_ROPE + swz((uint32_t)(row0 + rl), (uint32_t)lane & 7u)) = v;
-                }
-                // no-PE tiles whose scale is below the row scale: shift them onto the row scale.
-                // Lane l rewrites 16-byte chunk l of a flagged row (block l / 8).
-                uint32_t fix = __ballot_sync(0xffffffffu, uneven && smax > 0.f) & 0xffu;
-                while (fix) {
-                    const int i = __ffs(fix) - 1;
-                    fix &= fix - 1;
-                    const float ratio_f = __shfl_sync(0xffffffffu, my_ratio, (lane & 24) + i);   // (row i, my block)
-                    if (ratio_f != 1.f) {
-                        uint4* q4 = reinterpret_cast<uint4*>(kp + blk * CHUNK + swz((uint32_t)(row0 + i), (uint32_t)lane & 7u));
-                        const __half2 ratio = __float2half2_rn(ratio_f);
-                        uint4 v = *q4;
-                        v.x = rescale_e4m3x4(v.x, ratio); v.y = rescale_e4m3x4(v.y, ratio);
-                        v.z = rescale_e4m3x4(v.z, ratio); v.w = rescale_e4m3x4(v.w, ratio);
-                        *q4 = v;
+                    for (int g = 0; g < 2; ++g) {
+                        const int rl = g * 4 + (lane >> 3);
+                        const __nv_bfloat162 f = __float2bfloat162_rn(__shfl_sync(0xffffffffu, inv_s, rl));
+                        uint4 v = rv[g];
+                        v.x = mul_bf16x2(v.x, f); v.y = mul_bf16x2(v.y, f);
+                        v.z = mul_bf16x2(v.z, f); v.w = mul_bf16x2(v.w, f);
+                        *reinterpret_cast<uint4*>(kp + KS_ROPE + swz((uint32_t)(row0 + rl), (uint32_t)lane & 7u)) = v;
+                    }
+                    // no-PE tiles whose scale is below the row scale: shift them onto the row scale.
+                    // Lane l rewrites 16-byte chunk l of a flagged row (block l / 8).
+                    uint32_t fix = __ballot_sync(0xffffffffu, uneven && smax > 0.f) & 0xffu;
+                    while (fix) {
+                        const int i = __ffs(fix) - 1;
+                        fix &= fix - 1;
+                        const float ratio_f = __shfl_sync(0xffffffffu, my_ratio, (lane & 24) + i);   // (row i, my block)
+                        if (ratio_f != 1.f) {
+                            uint4* q4 = reinterpret_cast<uint4*>(kp + blk * CHUNK + swz((uint32_t)(row0 + i), (uint32_t)lane & 7u));
+                            const uint32_t sub = shift_bytes_of_ratio(ratio_f);
+                            uint4 v = *q4;
+                            v.x = shift_down_e4m3x4(v.x, sub); v.y = shift_down_e4m3x4(v.y, sub);
+                            v.z = shift_down_e4m3x4(v.z, sub); v.w = shift_down_e4m3x4(v.w, sub);
+                            *q4 = v;
+                        }
                     }
                 }
+                PROF(2);
                 fence_proxy_async();
                 __syncwarp();
-                if (lane == 0) mbar_arrive_cluster(barp(BAR_KFULLP + ks));
-                // the V stage of this tile is free once the P.V two tiles back has completed
+                if (lane == 0) mbar_arrive_remote(barp(BAR_KFULLP + ks));
+                PROF(3);
+                TRACE(31, t_it);
+                // the V stage of this tile is free once the P.V NV tiles back has completed
                 if (t_it >= NV) {
-                    ok = mbar_wait(bar(BAR_VEMPTY + vs), ((t_it / NV) - 1) & 1u, abort_flag, W_VEMPTY);
+                    ok = mbar_wait_hot(bar(BAR_VEMPTY + vs), ((t_it / NV) - 1) & 1u, abort_flag, W_VEMPTY);
                     if (!ok) break;
                 }
-                // scale triples of tokens [8 fw, +8) of this CTA (lanes 0-7) and of the partner (lanes 8-15)
-                if (lane < 16) {
-                    const int n = ((lane < 8) ? (int)rank : 1 - (int)rank) * OWN_N + my_row;
+                PROF(4);
+                TRACE(32, t_it);
+                // scale triples of tokens [16 kf, +16) of this CTA (lanes 0-15) and of the partner (lanes 16-31)
+                {
+                    const int n = ((lane < 16) ? (int)rank : 1 - (int)rank) * OWN_N + kf * 16 + (lane & 15);
                     const float4 s4 = *reinterpret_cast<const float4*>(kp + KS_RAW + n * 16);
                     const float sm4 = fmaxf(fmaxf(s4.x, s4.y), fmaxf(s4.z, s4.w));
                     const float is4 = (sm4 > 0.f) ? __uint_as_float(0x7f000000u - __float_as_uint(sm4)) : 0.f;
                     *reinterpret_cast<float4*>(vp + VS_TRIP + n * 16) =
                         make_float4(sm4, (sm4 > 0.f) ? (float)((int)(__float_as_uint(sm4) >> 23) - 127) : -INFINITY, is4, 0.f);
                 }
-                // own V bytes: rows [8 fw, +8), this CTA's two chunks -> V slots (same swizzle)
+                // own V bytes: rows [16 kf, +16), this CTA's two chunks -> V slots (same swizzle)
 #pragma unroll
-                for (int u = 0; u < 4; ++u) {
-                    const int pidx = lane + 32 * u;                    // 8 rows x 2 chunks x 8 pieces
-                    const uint32_t r = (uint32_t)(row0 + (pidx >> 4)), nb = (uint32_t)(pidx >> 3) & 1u, c = (uint32_t)pidx & 7u;
+                for (int u = 0; u < 8; ++u) {
+                    const int pidx = lane + 32 * u;                    // 16 rows x 2 chunks x 8 pieces
+                    const uint32_t r = (uint32_t)(kf * 16 + (pidx >> 4)), nb = (uint32_t)(pidx >> 3) & 1u, c = (uint32_t)pidx & 7u;
                     const uint4 v = *reinterpret_cast<const uint4*>(kp + (2u * rank + nb) * CHUNK + swz(r, c));
                     *reinterpret_cast<uint4*>(vp + ((2u * rank + (r >> 5)) * 2u + nb) * VSLOT + swz(r & 31u, c)) = v;
                 }
+                PROF(5);
                 fence_proxy_async();
                 __syncwarp();
-                if (lane == 0) { mbar_arrive(bar(BAR_TRIP + ks)); mbar_arrive(bar(BAR_KEMPTY + ks)); }
-                if (k >= 1) { ok = v_part(t_it - 1); if (!ok) break; }
+                if (lane == 0) {
+                    mbar_arrive(bar(BAR_TRIP + ks));
+                    mbar_arrive(bar(BAR_KEMPTY + ks));
+                    mbar_arrive_remote(barp(BAR_VFULLP + vs));
+                }
+                PROF(6);
+                TRACE(33, t_it);
             }
-            if (ok && nst > 0) ok = v_part(it + nst - 1);
+            it += nst;
+        }
+    } else if (warp < MMA_WARP) {
+        // =================================================================== tile fix-up, partner's half rows
+        // Warp vf owns rows [16*vf, +16) of the partner's rows in the V slots: uneven-scale rewrite.
+        const int vf = warp - FX_WARP0 - N_FXK_WARPS;
+        const int blk = lane >> 3;
+        uint32_t it = 0;
+        bool ok = true;
+        for (int req = meta.begin_req; req <= last_req && ok; ++req) {
+            Work w;
+            if (!get_work(p, meta, req, w)) continue;
+            const int nst = (w.nblk + 1) >> 1;
+#pragma unroll 1
+            for (int k = 0; k < nst && ok; ++k) {
+                const uint32_t t_it = it + k, vs = t_it % NV;
+                PROF(0);
+                ok = mbar_wait_hot(bar(BAR_VLOADED + vs), (t_it / NV) & 1u, abort_flag, W_VLOADED);
+                if (!ok) break;
+                PROF(1);
+                TRACE(34, t_it);
+                uint8_t* vp = sm + VS_OFF + vs * VS_BYTES;
+#pragma unroll 1
+                for (int g8 = 0; g8 < 2; ++g8) {
+                    const int row0 = vf * 16 + g8 * FX_ROWS;
+                    const int my_row = row0 + (lane & 7);
+                    const float4 sc = *reinterpret_cast<const float4*>(vp + VS_RAW + my_row * 16);
+                    const float smax = fmaxf(fmaxf(sc.x, sc.y), fmaxf(sc.z, sc.w));
+                    const float inv_s = (smax > 0.f) ? __uint_as_float(0x7f000000u - __float_as_uint(smax)) : 0.f;
+                    // ratio of (row lane % 8, this CTA's chunk (lane / 8) % 2) to the row scale: a power of two <= 1
+                    const float mine = rank ? ((blk & 1) ? sc.w : sc.z) : ((blk & 1) ? sc.y : sc.x);
+                    const float my_ratio = mine * inv_s;
+                    uint32_t fix = __ballot_sync(0xffffffffu, my_ratio != 1.f && smax > 0.f) & 0xffffu;   // rows x 2 chunks
+                    fix = (fix | (fix >> 8)) & 0xffu;
+                    while (fix) {
+                        const int i = __ffs(fix) - 1;
+                        fix &= fix - 1;
+                        const int r = row0 + i;
+                        const float ratio_f = __shfl_sync(0xffffffffu, my_ratio, ((lane >> 3) & 1) * 8 + i);   // (row i, chunk (lane/8)%2)
+                        if (lane < 16 && ratio_f != 1.f) {
+                            const uint32_t slot = ((2u * (1u - rank) + (uint32_t)(r >> 5)) * 2u + (uint32_t)(lane >> 3)) * VSLOT;
+                            uint4* q4 = reinterpret_cast<uint4*>(vp + slot + swz((uint32_t)r & 31u, (uint32_t)lane & 7u));
+                            const uint32_t sub = shift_bytes_of_ratio(ratio_f);
+                            uint4 v = *q4;
+                            v.x = shift_down_e4m3x4(v.x, sub); v.y = shift_down_e4m3x4(v.y, sub);
+                            v.z = shift_down_e4m3x4(v.z, sub); v.w = shift_down_e4m3x4(v.w, sub);
+                            *q4 = v;
+                        }
+                    }
+                }
+                PROF(2);
+                fence_proxy_async();
+                __syncwarp();
+                if (lane == 0) mbar_arrive_remote(barp(BAR_VFULLP + vs));
+                PROF(3);
+                TRACE(35, t_it);
+            }
             it += nst;
         }
     } else if (warp == MMA_WARP && lane == 0 && rank == 0) {
         // =================================================================== score MMA issue (even CTA)
         uint32_t it = 0, rq = 0;
         bool ok = true;
-        const uint32_t qn_lo = desc_lo(base + QN_OFF, 16), qr_lo = desc_lo(base + QR_OFF, 16);
+        const uint32_t qr_lo = desc_lo(base + QR_OFF, 16);
         for (int req = meta.begin_req; req <= last_req && ok; ++req) {
             Work w;
             if (!get_work(p, meta, req, w)) continue;
             const int nst = (w.nblk + 1) >> 1;
-            ok = mbar_wait_thread_cluster(bar(BAR_QREADYP), rq & 1u, abort_flag, W_QREADY);
+            ok = mbar_wait_thread(bar(BAR_QREADYP), rq & 1u, abort_flag, W_QREADY);
             if (!ok) break;
             ++rq;
             for (int j = 0; j < nst && ok; ++j, ++it) {
                 const uint32_t ks = it % NK, b = it & 1u;
+                PROF(0);
                 if (it >= 2) {
-                    ok = mbar_wait_thread_cluster(bar(BAR_SFREEP + b), ((it - 2) >> 1) & 1u, abort_flag, W_SFREE);
+                    ok = mbar_wait_thread(bar(BAR_SFREEP + b), ((it - 2) >> 1) & 1u, abort_flag, W_SFREE);
                     if (!ok) break;
                 }
-                ok = mbar_wait_thread_cluster(bar(BAR_KFULLP + ks), (it / NK) & 1u, abort_flag, W_KFULL);
+                PROF(1);
+                ok = mbar_wait_thread(bar(BAR_KFULLP + ks), (it / NK) & 1u, abort_flag, W_KFULL);
                 if (!ok) break;
+                PROF(2);
                 tc_fence_after();
+                TRACE(40, it);
                 const uint32_t kb_lo = desc_lo(base + KS_OFF + ks * KS_BYTES, 16);
                 const uint32_t d = tmem + TM_S + 64 * b;
 #pragma unroll
                 for (int kc = 0; kc < 4; ++kc) {
 #pragma unroll
                     for (int s = 0; s < 4; ++s) {
-                        mma_pair_f8(d, make_desc(qn_lo + ((kc * CHUNK + s * 32) >> 4), DESC_HI_SW128),
-                                    make_desc(kb_lo + ((kc * CHUNK + s * 32) >> 4), DESC_HI_SW128), IDESC_QK_F8, (kc | s) != 0);
+                        mma_pair_f8_ts(d, tmem + TM_Q + 32 * kc + 8 * s,
+                                       make_desc(kb_lo + ((kc * CHUNK + s * 32) >> 4), DESC_HI_SW128), IDESC_QK_F8, (kc | s) != 0);
                     }
                 }
 #pragma unroll
@@ -668,6 +825,8 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PAIR_THREADS, 1) att
                 tc_commit_pair(mapa_shared(bar(BAR_SREADY + b), 1));
                 tc_commit_pair(bar(BAR_KEMPTY + ks));
                 tc_commit_pair(mapa_shared(bar(BAR_KEMPTY + ks), 1));
+                PROF(3);
+                TRACE(41, it);
             }
         }
     } else if (warp == MMA_WARP + 1 && lane == 0 && rank == 0) {
@@ -680,11 +839,16 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PAIR_THREADS, 1) att
             const int nst = (w.nblk + 1) >> 1;
             for (int j = 0; j < nst && ok; ++j, ++it) {
                 const uint32_t vs = it % NV, b = it & 1u;
-                ok = mbar_wait_thread_cluster(bar(BAR_PREADYP + b), (it >> 1) & 1u, abort_flag, W_PREADY);
+                PROF(0);
+                ok = mbar_wait_thread(bar(BAR_PREADYP + b), (it >> 1) & 1u, abort_flag, W_PREADY);
                 if (!ok) break;
-                ok = mbar_wait_thread_cluster(bar(BAR_VFULLP + vs), (it / NV) & 1u, abort_flag, W_VFULL);
+                PROF(1);
+                TRACE(50, it);
+                ok = mbar_wait_thread(bar(BAR_VFULLP + vs), (it / NV) & 1u, abort_flag, W_VFULL);
                 if (!ok) break;
+                PROF(2);
                 tc_fence_after();
+                TRACE(51, it);
                 const uint32_t pa_lo = desc_lo(base + PB_OFF + b * CHUNK, 16);
                 const uint32_t vb_lo = desc_lo(base + VS_OFF + vs * VS_BYTES, VSLOT);
 #pragma unroll
@@ -699,6 +863,8 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PAIR_THREADS, 1) att
                 tc_commit_pair(mapa_shared(bar(BAR_VEMPTY + vs), 1));
                 tc_commit_pair(bar(BAR_PVDONE + b));
                 tc_commit_pair(mapa_shared(bar(BAR_PVDONE + b), 1));
+                PROF(3);
+                TRACE(52, it);
             }
         }
     }
@@ -716,9 +882,32 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PAIR_THREADS, 1) att
         tc_fence_after();
         tmem_dealloc_pair(tmem, TMEM_COLS);
     }
+    TRACE(5, 0);
+#ifdef SMLA_PROF
+    if (g_prof_buf != nullptr && (int)blockIdx.x == g_prof_block && lane == 0) {
+        g_prof_buf[warp * 2] = prof_acc;
+        g_prof_buf[warp * 2 + 1] = (unsigned)clock() - prof_start;
+    }
+#endif
 }
 
 }  // namespace
+
+#ifdef SMLA_TRACE
+extern "C" int smla_trace_set(long long* buf, int cap, int block) {
+    cudaMemcpyToSymbol(g_trace_buf, &buf, sizeof(buf));
+    cudaMemcpyToSymbol(g_trace_cap, &cap, sizeof(cap));
+    cudaMemcpyToSymbol(g_trace_block, &block, sizeof(block));
+    return (int)cudaGetLastError();
+}
+#endif
+#ifdef SMLA_PROF
+extern "C" int smla_prof_set(long long* buf, int block) {
+    cudaMemcpyToSymbol(g_prof_buf, &buf, sizeof(buf));
+    cudaMemcpyToSymbol(g_prof_block, &block, sizeof(block));
+    return (int)cudaGetLastError();
+}
+#endif
 
 int launch_attn_pair(const AttnParams& p, cudaStream_t stream) {
     if (p.num_tokens == 0) return 0;

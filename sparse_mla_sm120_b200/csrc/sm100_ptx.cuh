@@ -128,6 +128,13 @@ __device__ __forceinline__ void st_cluster_f32(uint32_t addr, float v) {
 __device__ __forceinline__ void mbar_arrive_cluster(uint32_t remote_bar) {
     asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(remote_bar) : "memory");
 }
+// Arrive on a barrier given by its shared::cluster address (this CTA's or, through mapa_shared, another
+// CTA's) with the default CTA-scope release.  For signals that only say "my part is ready" about data
+// that stays inside this SM (shared-memory operands of a pair MMA, tensor memory): a cluster-scope
+// release makes every such arrive wait for a memory barrier (about a thousand cycles under load).
+__device__ __forceinline__ void mbar_arrive_remote(uint32_t cluster_bar) {
+    asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(cluster_bar) : "memory");
+}
 // Arrive on a barrier of another CTA and add `bytes` to its pending transaction count.
 __device__ __forceinline__ void mbar_arrive_expect_tx_cluster(uint32_t remote_bar, uint32_t bytes) {
     asm volatile("mbarrier.arrive.expect_tx.release.cluster.shared::cluster.b64 _, [%0], %1;" ::"r"(remote_bar), "r"(bytes) : "memory");
@@ -367,6 +374,14 @@ __device__ __forceinline__ void mma_pair_f8(uint32_t d_tmem, uint64_t a_desc, ui
         "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
         "tcgen05.mma.cta_group::2.kind::f8f6f4 [%0], %1, %2, %3, p;\n\t}"
         ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"((uint32_t)accumulate) : "memory");
+}
+// The same with A read from tensor memory: lane = row, K packed along the columns; the 64 rows of a
+// CTA must be present twice, in lanes 0-63 and again in lanes 64-127.
+__device__ __forceinline__ void mma_pair_f8_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc, bool accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::2.kind::f8f6f4 [%0], [%1], %2, %3, p;\n\t}"
+        ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"((uint32_t)accumulate) : "memory");
 }
 __device__ __forceinline__ void mma_pair_f16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, bool accumulate) {
     asm volatile(
