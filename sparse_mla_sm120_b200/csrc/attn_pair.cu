@@ -20,15 +20,18 @@
 // csrc/kernel/common/fp8_quant.cuh:44-103, csrc/kernel/decode/decode_v2_kernel.cuh:414-493):
 //   * Q no-PE is quantised to e4m3 with one power-of-two scale sq_h per head; Q RoPE stays bf16
 //     and is pre-divided by that scale.
-//   * K/V bytes are consumed as stored.  A row whose four 128-value tiles carry different
-//     scales is re-expressed against its largest scale s_t (a power-of-two shift: exact while the
-//     shifted value stays a normal e4m3 number, i.e. for scale ratios up to 2^9 on values near the
-//     tile maximum; below that the value rounds at 2^-9 of the row's largest tile maximum);
-//     K RoPE is pre-divided by s_t.  One accumulator then holds S = (q . k) / (sq_h * s_t).
-//   * The row scale of V is folded into the exponent: z = S*sq_h*s_t*sm_scale*log2e + log2(s_t),
+//   * K/V bytes are consumed as stored, re-expressed against ONE scale s per 128-token tile: the
+//     largest of the 4 x 128 scales of the tile's rows.  A 128-value block with a smaller scale is
+//     shifted down (a power-of-two division done on the exponent fields: exact while the shifted
+//     value stays a normal e4m3 number; a value that would fall below 2^-6 is cut to the subnormal
+//     grid, i.e. it is off by at most 2^-15 of the largest value the tile can hold, which is far
+//     below the e4m3 rounding step of the values that dominate a dot product).  K RoPE is
+//     pre-divided by s.  One accumulator then holds S = (q . k) / (sq_h * s).
+//   * The tile scale of V is folded into the exponent: z = S*sq_h*s*sm_scale*log2e + log2(s),
 //     P' = 2^(z - m) with m the (lazily updated) running maximum of z, so that
 //     O_acc = sum_t P'_t * Vfp8_t needs no per-tile scale; the denominator is tracked apart as
-//     l = sum_t P'_t / s_t in fp32.  O = O_acc / l, LSE = log2(l) + m (base 2, as the reference).
+//     l = sum over tiles of (sum_t P'_t) / s in fp32.  O = O_acc / l, LSE = log2(l) + m (base 2, as
+//     the reference).  With one scale per tile the softmax loops read nothing per token.
 //   * P' is rounded to e4m3 (times 2^P_SHIFT); the accumulator is rescaled only when a row
 //     maximum grows by more than 2^RESCALE_TAU, which is exact because l and O share m.
 //   * Invalid entries (index < 0, position >= topk_length) are never loaded: their shared-memory
@@ -57,7 +60,6 @@ using namespace attn;
 constexpr int N_SM_WARPS = 8, N_PR_WARPS = 4, N_FX_WARPS = 8;
 constexpr int N_PRK_WARPS = 2;    // gather: 2 warps for the K part, 2 for the V part
 constexpr int N_FXK_WARPS = 4;    // fix-up: 4 warps for own rows, 4 for the partner's
-constexpr int FX_ROWS = 8;    // rows of a tile per fix-up warp
 constexpr int FX_WARP0 = N_SM_WARPS + N_PR_WARPS;
 constexpr int MMA_WARP = FX_WARP0 + N_FX_WARPS;
 constexpr int PAIR_THREADS = (MMA_WARP + 4) * 32;
@@ -88,9 +90,9 @@ constexpr uint32_t KS_RAW = KS_ROPE + CHUNK;         //   [128 tokens x 16 B] th
 constexpr uint32_t KS_BYTES = KS_RAW + TILE_N * 16;  // 43008
 constexpr uint32_t VS_OFF = KS_OFF + NK * KS_BYTES;  // V stages
 constexpr uint32_t VSLOT = 32 * 128;                 //   slot (kb, nb): 32 tokens x 128 dims, at (2 kb + nb) * VSLOT
-constexpr uint32_t VS_RAW = 8 * VSLOT;               //   [64 x 16 B] scales of the partner's rows
-constexpr uint32_t VS_TRIP = VS_RAW + OWN_N * 16;    //   [128 x 16 B] per token (s_t, log2 s_t, 1/s_t, 0)
-constexpr uint32_t VS_BYTES = VS_TRIP + TILE_N * 16; // 35840
+constexpr uint32_t VS_RAW = 8 * VSLOT;               //   [128 tokens x 16 B] the rows' scales as gathered (all rows of the tile)
+constexpr uint32_t VS_INFO = VS_RAW + TILE_N * 16;   //   tile scale (s, log2 s, 1/s, 0) and the 128 validity bits of the tile
+constexpr uint32_t VS_BYTES = VS_INFO + 1024;        // 35840
 constexpr uint32_t XCH_OFF = VS_OFF + NV * VS_BYTES; // row-maximum exchange [2][4][64] fp32, then Q scales [64] fp32
 constexpr uint32_t XCH_BYTES = 2 * 4 * 64 * 4 + 64 * 4;
 constexpr uint32_t BAR_OFF = XCH_OFF + XCH_BYTES;
@@ -144,6 +146,22 @@ __device__ int g_prof_block = 0;
 #else
 #define PROF(i)
 #endif
+
+// Scale of a tile and the validity bits of its 128 tokens from their gathered scale words ([128] float4 in
+// shared memory; a row that was not loaded has all-zero scales).  Every lane returns the same values.
+__device__ __forceinline__ float tile_scale(const uint8_t* raw, int lane, uint32_t (&valid)[4]) {
+    float m = 0.f;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        const float4 s4 = *reinterpret_cast<const float4*>(raw + (32 * j + lane) * 16);
+        const float r = fmaxf(fmaxf(s4.x, s4.y), fmaxf(s4.z, s4.w));
+        valid[j] = __ballot_sync(0xffffffffu, r > 0.f);
+        m = fmaxf(m, r);
+    }
+#pragma unroll
+    for (int o = 16; o >= 1; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+    return m;
+}
 
 __device__ __forceinline__ uint32_t swz(uint32_t row, uint32_t chunk16) { return row * 128u + ((chunk16 ^ (row & 7u)) << 4); }
 
@@ -208,6 +226,14 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PAIR_THREADS, 1) att
     auto barp = [&](int i) -> uint32_t { return mapa_shared(bar(i), 0); };   // the even CTA's copy of barrier i
 
     const int last_req = min(meta.end_req, p.num_tokens - 1);
+    // The softmax warps read Q before anything else can start: the other warps, idle until then, ask L2 for this
+    // CTA's half of the first request's Q rows (128-byte lines).
+    if (warp >= N_SM_WARPS && warp < MMA_WARP && meta.begin_req <= last_req) {
+        const uint8_t* q0 = reinterpret_cast<const uint8_t*>(p.q + ((size_t)meta.begin_req * p.num_heads + head0) * D_QK);
+        const int lines = (min(heads_cta, max(p.num_heads - head0, 0)) * D_QK * 2 + 127) >> 7;
+        for (int i = tid - N_SM_WARPS * 32; i < lines; i += (MMA_WARP - N_SM_WARPS) * 32)
+            asm volatile("prefetch.global.L2 [%0];" ::"l"(q0 + (size_t)i * 128));
+    }
 
     if (warp < N_SM_WARPS) setmaxnreg_inc<REGS_SOFTMAX>();
     else if (warp < MMA_WARP) setmaxnreg_dec<REGS_OTHER>();
@@ -239,8 +265,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PAIR_THREADS, 1) att
             // tensor memory (the A operand of a pair MMA wants the CTA's 64 rows twice: quarters 2 and 3 repeat the
             // work of quarters 0 and 1).  The 16x256b store shape takes a row from four lanes: lane (g = lane/4,
             // c = lane%4) holds, for every block i of 32 dims, dims [32i + 8c, +8) of rows g and g + 8 of a 16-row
-            // group, which is also how it loads them (16 bytes of bf16 per row and block).  A group stays in
-            // registers between finding its rows' maxima and quantising them.
+            // group, which is also how it loads them (16 bytes of bf16 per row and block).
             {
                 const int g = lane >> 2, c4 = lane & 3;
 #pragma unroll 1
@@ -250,19 +275,19 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PAIR_THREADS, 1) att
                     const bool v_b = !dead && r_b < heads_cta && head0 + r_b < p.num_heads;
                     const __nv_bfloat16* src_a = p.q + ((size_t)req * p.num_heads + (v_a ? head0 + r_a : 0)) * D_QK + ch * 256 + c4 * 8;
                     const __nv_bfloat16* src_b = p.q + ((size_t)req * p.num_heads + (v_b ? head0 + r_b : 0)) * D_QK + ch * 256 + c4 * 8;
-                    uint4 xa[8], xb[8];
-#pragma unroll
-                    for (int i = 0; i < 8; ++i) {
-                        xa[i] = v_a ? __ldg(reinterpret_cast<const uint4*>(src_a + 32 * i)) : make_uint4(0, 0, 0, 0);
-                        xb[i] = v_b ? __ldg(reinterpret_cast<const uint4*>(src_b + 32 * i)) : make_uint4(0, 0, 0, 0);
-                    }
+                    // two passes over the rows' bytes (the second is served by L1/L2): keeping a 16-row group in
+                    // registers between the maxima and the quantisation spilled
                     auto absmax8 = [](const uint4& a) {
                         return fmaxf(fmaxf(fmaxf(fabsf(bf16lo(a.x)), fabsf(bf16hi(a.x))), fmaxf(fabsf(bf16lo(a.y)), fabsf(bf16hi(a.y)))),
                                      fmaxf(fmaxf(fabsf(bf16lo(a.z)), fabsf(bf16hi(a.z))), fmaxf(fabsf(bf16lo(a.w)), fabsf(bf16hi(a.w)))));
                     };
                     float am_a = 0.f, am_b = 0.f;
 #pragma unroll
-                    for (int i = 0; i < 8; ++i) { am_a = fmaxf(am_a, absmax8(xa[i])); am_b = fmaxf(am_b, absmax8(xb[i])); }
+                    for (int i = 0; i < 8; ++i) {
+                        const uint4 xa = v_a ? __ldg(reinterpret_cast<const uint4*>(src_a + 32 * i)) : make_uint4(0, 0, 0, 0);
+                        const uint4 xb = v_b ? __ldg(reinterpret_cast<const uint4*>(src_b + 32 * i)) : make_uint4(0, 0, 0, 0);
+                        am_a = fmaxf(am_a, absmax8(xa)); am_b = fmaxf(am_b, absmax8(xb));
+                    }
                     am_a = fmaxf(am_a, __shfl_xor_sync(0xffffffffu, am_a, 1)); am_b = fmaxf(am_b, __shfl_xor_sync(0xffffffffu, am_b, 1));
                     am_a = fmaxf(am_a, __shfl_xor_sync(0xffffffffu, am_a, 2)); am_b = fmaxf(am_b, __shfl_xor_sync(0xffffffffu, am_b, 2));
                     // both column halves of a row agree on one scale (the repeating quarter writes the same values)
@@ -275,12 +300,13 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PAIR_THREADS, 1) att
                     const float ib = __uint_as_float(0x7f000000u - __float_as_uint(sq_b));
                     if (c4 == 0) { sqv[r_a] = sq_a; sqv[r_b] = sq_b; }
                     if (!dead) {
-#pragma unroll
+#pragma unroll 1
                         for (int h4 = 0; h4 < 2; ++h4) {
                             uint32_t wq[16];
 #pragma unroll
                             for (int kk = 0; kk < 4; ++kk) {
-                                const uint4 a = xa[4 * h4 + kk], b4 = xb[4 * h4 + kk];
+                                const uint4 a = v_a ? __ldg(reinterpret_cast<const uint4*>(src_a + 32 * (4 * h4 + kk))) : make_uint4(0, 0, 0, 0);
+                                const uint4 b4 = v_b ? __ldg(reinterpret_cast<const uint4*>(src_b + 32 * (4 * h4 + kk))) : make_uint4(0, 0, 0, 0);
                                 wq[4 * kk + 0] = pack_e4m3x4(bf16lo(a.x) * ia, bf16hi(a.x) * ia, bf16lo(a.y) * ia, bf16hi(a.y) * ia);
                                 wq[4 * kk + 1] = pack_e4m3x4(bf16lo(a.z) * ia, bf16hi(a.z) * ia, bf16lo(a.w) * ia, bf16hi(a.w) * ia);
                                 wq[4 * kk + 2] = pack_e4m3x4(bf16lo(b4.x) * ib, bf16hi(b4.x) * ib, bf16lo(b4.y) * ib, bf16hi(b4.y) * ib);
@@ -320,13 +346,13 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PAIR_THREADS, 1) att
             if (lane == 0) mbar_arrive_remote(barp(BAR_QREADYP));
 
             float m_run = -INFINITY;   // running maximum of z (lags by at most RESCALE_TAU)
-            float l_run = 0.f;         // this thread's share of the sum of P'/s_t (scaled by 2^P_SHIFT)
+            float l_run = 0.f;         // this thread's share of the sum of P'/s (scaled by 2^P_SHIFT)
             float x_max = -INFINITY;   // this thread's share of the maximum of the scaled logits (max_logits output)
             for (int j = 0; j < nst; ++j, ++it) {
                 const uint32_t b = it & 1u, vs = it % NV;
                 float z[32];
-                float mx_loc = -INFINITY;
-                const float4* tok = reinterpret_cast<const float4*>(sm + VS_OFF + vs * VS_BYTES + VS_TRIP) + 64 * thalf + 32 * ch;
+                float mx_loc = -INFINITY, inv_tile = 0.f;
+                const uint8_t* info = sm + VS_OFF + vs * VS_BYTES + VS_INFO;
                 PROF(0);
                 if (!dead) dead = !mbar_wait_hot(bar(BAR_SREADY + b), (it >> 1) & 1u, abort_flag, W_SREADY);
                 PROF(1);
@@ -342,20 +368,29 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PAIR_THREADS, 1) att
                     tc_fence_before();
                     __syncwarp();
                     if (lane == 0) mbar_arrive_remote(barp(BAR_SFREEP + b));   // the score buffer may be overwritten
+                    const float4 ti = *reinterpret_cast<const float4*>(info);                 // (s, log2 s, 1/s, 0) of the tile
+                    const uint32_t valid = reinterpret_cast<const uint32_t*>(info + 16)[2 * thalf + ch];   // this thread's 32 tokens
+                    const float c_tile = ti.x * my_sqc, off = ti.y;
+                    inv_tile = ti.z;
                     float mx0 = -INFINITY, mx1 = -INFINITY;
 #pragma unroll
                     for (int t = 0; t < 32; t += 4) {
-                        const float2 a0 = *reinterpret_cast<const float2*>(tok + t), a1 = *reinterpret_cast<const float2*>(tok + t + 1);
-                        const float2 a2 = *reinterpret_cast<const float2*>(tok + t + 2), a3 = *reinterpret_cast<const float2*>(tok + t + 3);
-                        z[t + 0] = fmaf(__uint_as_float(sv[t + 0]) * a0.x, my_sqc, a0.y);
-                        z[t + 1] = fmaf(__uint_as_float(sv[t + 1]) * a1.x, my_sqc, a1.y);
-                        z[t + 2] = fmaf(__uint_as_float(sv[t + 2]) * a2.x, my_sqc, a2.y);
-                        z[t + 3] = fmaf(__uint_as_float(sv[t + 3]) * a3.x, my_sqc, a3.y);
+                        z[t + 0] = fmaf(__uint_as_float(sv[t + 0]), c_tile, off);
+                        z[t + 1] = fmaf(__uint_as_float(sv[t + 1]), c_tile, off);
+                        z[t + 2] = fmaf(__uint_as_float(sv[t + 2]), c_tile, off);
+                        z[t + 3] = fmaf(__uint_as_float(sv[t + 3]), c_tile, off);
+                    }
+                    if (valid != 0xffffffffu) {     // tokens without an entry: weight exactly 0
+#pragma unroll
+                        for (int t = 0; t < 32; ++t) z[t] = ((valid >> t) & 1u) ? z[t] : -INFINITY;
+                    }
+#pragma unroll
+                    for (int t = 0; t < 32; t += 4) {
                         mx0 = fmaxf(mx0, fmaxf(z[t], z[t + 1]));
                         mx1 = fmaxf(mx1, fmaxf(z[t + 2], z[t + 3]));
-                        if (p.out_max_logits != nullptr)   // z - log2(s_t) is the scaled logit itself (NaN for masked entries is ignored by fmaxf)
-                            x_max = fmaxf(x_max, fmaxf(fmaxf(z[t] - a0.y, z[t + 1] - a1.y), fmaxf(z[t + 2] - a2.y, z[t + 3] - a3.y)));
                     }
+                    // z - log2(s) is the scaled logit itself
+                    if (p.out_max_logits != nullptr && fmaxf(mx0, mx1) > -INFINITY) x_max = fmaxf(x_max, fmaxf(mx0, mx1) - off);
                     mx_loc = fmaxf(mx0, mx1);
                     xch[(b * 4 + xpart) * 64 + hrow] = mx_loc;
                     PROF(4);
@@ -399,11 +434,10 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PAIR_THREADS, 1) att
                 for (int t = 0; t < 32; t += 4) {
                     const float p0 = ex2(z[t + 0] - m_off), p1 = ex2(z[t + 1] - m_off);
                     const float p2 = ex2(z[t + 2] - m_off), p3 = ex2(z[t + 3] - m_off);
-                    l0 = fmaf(p0, tok[t].z, l0); l1 = fmaf(p1, tok[t + 1].z, l1);
-                    l0 = fmaf(p2, tok[t + 2].z, l0); l1 = fmaf(p3, tok[t + 3].z, l1);
+                    l0 += p0 + p2; l1 += p1 + p3;
                     pw[t >> 2] = pack_e4m3x4(p0, p1, p2, p3);
                 }
-                l_run += l0 + l1;
+                l_run = fmaf(l0 + l1, inv_tile, l_run);
                 PROF(8);
                 // P' of tokens [64*thalf + 32*ch, +32) of head hrow: two 16-byte pieces of the row
                 uint8_t* pb = sm + PB_OFF + b * CHUNK;
@@ -528,7 +562,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PAIR_THREADS, 1) att
             auto fetch_idx = [&](int j, int ps) -> int {
                 const int n = (peer ? (1 - (int)rank) : (int)rank) * OWN_N + rows0 + 16 * ps + (lane & 15);
                 const int pos = w.blk0 * BLOCK_N + j * TILE_N + n;
-                return (j < nst && pos < lim && (!k_role ? peer != 0 : true)) ? __ldg(idx_row + pos) : -1;
+                return (j < nst && pos < lim) ? __ldg(idx_row + pos) : -1;
             };
             auto row_ptr = [&](int idx) -> unsigned long long {
                 if (idx < 0) return 0ull;      // rows without an entry travel as a null source: their copies zero-fill
@@ -606,9 +640,10 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PAIR_THREADS, 1) att
                             cp_async16_zfill(vbase + slot + swz((uint32_t)r & 31u, piece & 7u),
                                              reinterpret_cast<const uint8_t*>(v ? s + 256u * rank + piece * 16u : kv_u), v ? 16u : 0u);
                         }
-                        if (peer) {
+                        {   // scale words of the tile's rows: this CTA's (lanes 0-15) and the partner's (lanes 16-31)
+                            const int n = (peer ? (1 - (int)rank) : (int)rank) * OWN_N + row0 + (lane & 15);
                             const bool v = src_u != 0ull;
-                            cp_async16_zfill(vbase + VS_RAW + (row0 + (lane & 15)) * 16, reinterpret_cast<const uint8_t*>(v ? src_u + SCALE_OFF : kv_u), v ? 16u : 0u);
+                            cp_async16_zfill(vbase + VS_RAW + n * 16, reinterpret_cast<const uint8_t*>(v ? src_u + SCALE_OFF : kv_u), v ? 16u : 0u);
                         }
                     }
                     cp_async_arrive_noinc(bar(BAR_VLOADED + vs));
@@ -641,43 +676,42 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PAIR_THREADS, 1) att
                 TRACE(30, t_it);
                 uint8_t* kp = sm + KS_OFF + ks * KS_BYTES;
                 uint8_t* vp = sm + VS_OFF + vs * VS_BYTES;
+                uint32_t valid[4];
+                const float s_tile = tile_scale(kp + KS_RAW, lane, valid);
+                const float inv_tile = (s_tile > 0.f) ? __uint_as_float(0x7f000000u - __float_as_uint(s_tile)) : 0.f;
+                const __nv_bfloat162 rope_f = __float2bfloat162_rn(inv_tile);
+                // RoPE of rows [16 kf, +16), pre-divided by the tile scale: 4 passes of 4 rows x 8 chunks
+#pragma unroll
+                for (int g = 0; g < 4; ++g) {
+                    uint4* r4 = reinterpret_cast<uint4*>(kp + KS_ROPE + swz((uint32_t)(kf * 16 + g * 4 + (lane >> 3)), (uint32_t)lane & 7u));
+                    uint4 v = *r4;
+                    v.x = mul_bf16x2(v.x, rope_f); v.y = mul_bf16x2(v.y, rope_f);
+                    v.z = mul_bf16x2(v.z, rope_f); v.w = mul_bf16x2(v.w, rope_f);
+                    *r4 = v;
+                }
+                // 128-value blocks whose scale is below the tile scale are shifted onto the tile scale.  Row by row,
+                // lane l looks after 16-byte chunk l of the row's 512 bytes (block l / 8); no branches between rows,
+                // so that the loads of several rows are in flight together.
 #pragma unroll 1
-                for (int g8 = 0; g8 < 2; ++g8) {
-                    const int row0 = kf * 16 + g8 * FX_ROWS;
-                    const int my_row = row0 + (lane & 7);
-                    // RoPE chunks of this lane: 2 passes of 4 rows x 8 chunks
-                    uint4 rv[2];
+                for (int i0 = 0; i0 < 16; i0 += 4) {      // four rows at a time: their loads are issued before any store
+                    uint32_t sub[4];
+                    uint4 v[4];
+                    uint4* q4[4];
 #pragma unroll
-                    for (int g = 0; g < 2; ++g) rv[g] = *reinterpret_cast<const uint4*>(kp + KS_ROPE + swz((uint32_t)(row0 + g * 4 + (lane >> 3)), (uint32_t)lane & 7u));
-                    // row scale, validity (a zero-filled scale word marks a row that was not loaded)
-                    const float4 sc = *reinterpret_cast<const float4*>(kp + KS_RAW + (rank * OWN_N + my_row) * 16);
-                    const float smax = fmaxf(fmaxf(sc.x, sc.y), fmaxf(sc.z, sc.w));
-                    const bool uneven = (sc.x != smax) | (sc.y != smax) | (sc.z != smax) | (sc.w != smax);
-                    const float inv_s = (smax > 0.f) ? __uint_as_float(0x7f000000u - __float_as_uint(smax)) : 0.f;
-                    const float my_ratio = (blk == 0 ? sc.x : (blk == 1 ? sc.y : (blk == 2 ? sc.z : sc.w))) * inv_s;
-#pragma unroll
-                    for (int g = 0; g < 2; ++g) {
-                        const int rl = g * 4 + (lane >> 3);
-                        const __nv_bfloat162 f = __float2bfloat162_rn(__shfl_sync(0xffffffffu, inv_s, rl));
-                        uint4 v = rv[g];
-                        v.x = mul_bf16x2(v.x, f); v.y = mul_bf16x2(v.y, f);
-                        v.z = mul_bf16x2(v.z, f); v.w = mul_bf16x2(v.w, f);
-                        *reinterpret_cast<uint4*>(kp + KS_ROPE + swz((uint32_t)(row0 + rl), (uint32_t)lane & 7u)) = v;
+                    for (int u = 0; u < 4; ++u) {
+                        const int row = kf * 16 + i0 + u;
+                        const float sc = *reinterpret_cast<const float*>(kp + KS_RAW + (rank * OWN_N + row) * 16 + blk * 4);
+                        sub[u] = (sc > 0.f) ? shift_bytes_of_ratio(sc * inv_tile) : 0u;      // 0 for a block that is at the tile scale
+                        q4[u] = reinterpret_cast<uint4*>(kp + blk * CHUNK + swz((uint32_t)row, (uint32_t)lane & 7u));
                     }
-                    // no-PE tiles whose scale is below the row scale: shift them onto the row scale.
-                    // Lane l rewrites 16-byte chunk l of a flagged row (block l / 8).
-                    uint32_t fix = __ballot_sync(0xffffffffu, uneven && smax > 0.f) & 0xffu;
-                    while (fix) {
-                        const int i = __ffs(fix) - 1;
-                        fix &= fix - 1;
-                        const float ratio_f = __shfl_sync(0xffffffffu, my_ratio, (lane & 24) + i);   // (row i, my block)
-                        if (ratio_f != 1.f) {
-                            uint4* q4 = reinterpret_cast<uint4*>(kp + blk * CHUNK + swz((uint32_t)(row0 + i), (uint32_t)lane & 7u));
-                            const uint32_t sub = shift_bytes_of_ratio(ratio_f);
-                            uint4 v = *q4;
-                            v.x = shift_down_e4m3x4(v.x, sub); v.y = shift_down_e4m3x4(v.y, sub);
-                            v.z = shift_down_e4m3x4(v.z, sub); v.w = shift_down_e4m3x4(v.w, sub);
-                            *q4 = v;
+#pragma unroll
+                    for (int u = 0; u < 4; ++u) if (sub[u] != 0u) v[u] = *q4[u];
+#pragma unroll
+                    for (int u = 0; u < 4; ++u) {
+                        if (sub[u] != 0u) {
+                            v[u].x = shift_down_e4m3x4(v[u].x, sub[u]); v[u].y = shift_down_e4m3x4(v[u].y, sub[u]);
+                            v[u].z = shift_down_e4m3x4(v[u].z, sub[u]); v[u].w = shift_down_e4m3x4(v[u].w, sub[u]);
+                            *q4[u] = v[u];
                         }
                     }
                 }
@@ -694,14 +728,11 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PAIR_THREADS, 1) att
                 }
                 PROF(4);
                 TRACE(32, t_it);
-                // scale triples of tokens [16 kf, +16) of this CTA (lanes 0-15) and of the partner (lanes 16-31)
-                {
-                    const int n = ((lane < 16) ? (int)rank : 1 - (int)rank) * OWN_N + kf * 16 + (lane & 15);
-                    const float4 s4 = *reinterpret_cast<const float4*>(kp + KS_RAW + n * 16);
-                    const float sm4 = fmaxf(fmaxf(s4.x, s4.y), fmaxf(s4.z, s4.w));
-                    const float is4 = (sm4 > 0.f) ? __uint_as_float(0x7f000000u - __float_as_uint(sm4)) : 0.f;
-                    *reinterpret_cast<float4*>(vp + VS_TRIP + n * 16) =
-                        make_float4(sm4, (sm4 > 0.f) ? (float)((int)(__float_as_uint(sm4) >> 23) - 127) : -INFINITY, is4, 0.f);
+                // the tile's scale and validity bits for the softmax warps
+                if (kf == 0 && lane == 0) {
+                    *reinterpret_cast<float4*>(vp + VS_INFO) =
+                        make_float4(s_tile, (s_tile > 0.f) ? (float)((int)(__float_as_uint(s_tile) >> 23) - 127) : -INFINITY, inv_tile, 0.f);
+                    *reinterpret_cast<uint4*>(vp + VS_INFO + 16) = make_uint4(valid[0], valid[1], valid[2], valid[3]);
                 }
                 // own V bytes: rows [16 kf, +16), this CTA's two chunks -> V slots (same swizzle)
 #pragma unroll
@@ -728,7 +759,6 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PAIR_THREADS, 1) att
         // =================================================================== tile fix-up, partner's half rows
         // Warp vf owns rows [16*vf, +16) of the partner's rows in the V slots: uneven-scale rewrite.
         const int vf = warp - FX_WARP0 - N_FXK_WARPS;
-        const int blk = lane >> 3;
         uint32_t it = 0;
         bool ok = true;
         for (int req = meta.begin_req; req <= last_req && ok; ++req) {
@@ -744,31 +774,32 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PAIR_THREADS, 1) att
                 PROF(1);
                 TRACE(34, t_it);
                 uint8_t* vp = sm + VS_OFF + vs * VS_BYTES;
+                uint32_t valid[4];
+                const float s_tile = tile_scale(vp + VS_RAW, lane, valid);
+                const float inv_tile = (s_tile > 0.f) ? __uint_as_float(0x7f000000u - __float_as_uint(s_tile)) : 0.f;
+                // The partner's half rows [16 vf, +16): two rows per pass; lane l looks after row l / 16 of the pair,
+                // block (l / 8) % 2 of this CTA's two, 16-byte chunk l % 8.
 #pragma unroll 1
-                for (int g8 = 0; g8 < 2; ++g8) {
-                    const int row0 = vf * 16 + g8 * FX_ROWS;
-                    const int my_row = row0 + (lane & 7);
-                    const float4 sc = *reinterpret_cast<const float4*>(vp + VS_RAW + my_row * 16);
-                    const float smax = fmaxf(fmaxf(sc.x, sc.y), fmaxf(sc.z, sc.w));
-                    const float inv_s = (smax > 0.f) ? __uint_as_float(0x7f000000u - __float_as_uint(smax)) : 0.f;
-                    // ratio of (row lane % 8, this CTA's chunk (lane / 8) % 2) to the row scale: a power of two <= 1
-                    const float mine = rank ? ((blk & 1) ? sc.w : sc.z) : ((blk & 1) ? sc.y : sc.x);
-                    const float my_ratio = mine * inv_s;
-                    uint32_t fix = __ballot_sync(0xffffffffu, my_ratio != 1.f && smax > 0.f) & 0xffffu;   // rows x 2 chunks
-                    fix = (fix | (fix >> 8)) & 0xffu;
-                    while (fix) {
-                        const int i = __ffs(fix) - 1;
-                        fix &= fix - 1;
-                        const int r = row0 + i;
-                        const float ratio_f = __shfl_sync(0xffffffffu, my_ratio, ((lane >> 3) & 1) * 8 + i);   // (row i, chunk (lane/8)%2)
-                        if (lane < 16 && ratio_f != 1.f) {
-                            const uint32_t slot = ((2u * (1u - rank) + (uint32_t)(r >> 5)) * 2u + (uint32_t)(lane >> 3)) * VSLOT;
-                            uint4* q4 = reinterpret_cast<uint4*>(vp + slot + swz((uint32_t)r & 31u, (uint32_t)lane & 7u));
-                            const uint32_t sub = shift_bytes_of_ratio(ratio_f);
-                            uint4 v = *q4;
-                            v.x = shift_down_e4m3x4(v.x, sub); v.y = shift_down_e4m3x4(v.y, sub);
-                            v.z = shift_down_e4m3x4(v.z, sub); v.w = shift_down_e4m3x4(v.w, sub);
-                            *q4 = v;
+                for (int i0 = 0; i0 < 8; i0 += 4) {
+                    uint32_t sub[4];
+                    uint4 v[4];
+                    uint4* q4[4];
+#pragma unroll
+                    for (int u = 0; u < 4; ++u) {
+                        const int r = vf * 16 + 2 * (i0 + u) + (lane >> 4);
+                        const uint32_t nb = (uint32_t)(lane >> 3) & 1u;
+                        const float sc = *reinterpret_cast<const float*>(vp + VS_RAW + ((1 - (int)rank) * OWN_N + r) * 16 + (2 * rank + nb) * 4);
+                        sub[u] = (sc > 0.f) ? shift_bytes_of_ratio(sc * inv_tile) : 0u;
+                        q4[u] = reinterpret_cast<uint4*>(vp + ((2u * (1u - rank) + (uint32_t)(r >> 5)) * 2u + nb) * VSLOT + swz((uint32_t)r & 31u, (uint32_t)lane & 7u));
+                    }
+#pragma unroll
+                    for (int u = 0; u < 4; ++u) if (sub[u] != 0u) v[u] = *q4[u];
+#pragma unroll
+                    for (int u = 0; u < 4; ++u) {
+                        if (sub[u] != 0u) {
+                            v[u].x = shift_down_e4m3x4(v[u].x, sub[u]); v[u].y = shift_down_e4m3x4(v[u].y, sub[u]);
+                            v[u].z = shift_down_e4m3x4(v[u].z, sub[u]); v[u].w = shift_down_e4m3x4(v[u].w, sub[u]);
+                            *q4[u] = v[u];
                         }
                     }
                 }
