@@ -185,6 +185,29 @@ int smla_decode_partial(const void* q, const void* kv, const int32_t* indices,
                         const int32_t* topk_length, int impl, int32_t* status, void* stream);
 
 /*
+ * The same local step with the result cut into head slices for an all-to-all: slice d (the heads
+ * [d * num_heads / slices, (d + 1) * num_heads / slices), destined for rank d) starts slice_stride
+ * floats after slice d - 1 and holds [num_tokens, num_heads / slices, 512] partials followed by the
+ * slice's [num_tokens, num_heads / slices] LSEs.  slice_stride must be a multiple of 512 floats and
+ * at least num_tokens * (num_heads / slices) * 513.  No counterpart in the reference.
+ */
+int smla_decode_partial_sliced(const void* q, const void* kv, const int32_t* indices,
+                               float* o_accum, float* lse_accum, float* send, int slices, int64_t slice_stride,
+                               const int32_t* sched_meta, const int32_t* num_splits,
+                               int num_tokens, int num_heads, int topk, float sm_scale,
+                               int page_block_size, int64_t kv_block_stride_bytes, int num_sm_parts,
+                               const int32_t* topk_length, int impl, int32_t* status, void* stream);
+
+/*
+ * Reassembles the all-gathered head slices of the merged output: chunk g of `gathered` (chunk_bytes
+ * apart, a multiple of 16) holds [num_tokens, heads_per_slice, 512] bf16 followed by
+ * [num_tokens, heads_per_slice] fp32 LSEs -> out [num_tokens, slices * heads_per_slice, 512] bf16 and
+ * lse [num_tokens, slices * heads_per_slice].  No counterpart in the reference.
+ */
+int smla_cp_unslice(const void* gathered, void* out, float* lse, int slices, int num_tokens, int heads_per_slice,
+                    int64_t chunk_bytes, void* stream);
+
+/*
  * Final merge of the context-parallel exchange: o_parts [parts, num_tokens, num_heads, 512] fp32
  * and lse_parts [parts, num_tokens, num_heads] fp32 (the layout an all-gather of the per-GPU
  * partials produces) -> out bf16 and base-2 LSE, sink applied if given.  Same arithmetic as

@@ -24,6 +24,10 @@ _SIGS = {
     "smla_decode_partial": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                     c_void_p, c_void_p, c_int, c_int, c_int, c_float, c_int, c_int64, c_int,
                                     c_void_p, c_int, c_void_p, c_void_p]),
+    "smla_decode_partial_sliced": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int64,
+                                           c_void_p, c_void_p, c_int, c_int, c_int, c_float, c_int, c_int64, c_int,
+                                           c_void_p, c_int, c_void_p, c_void_p]),
+    "smla_cp_unslice": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int64, c_void_p]),
     "smla_combine_parts": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p]),
     "smla_combine_parts_strided": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int64, c_int64,
                                            c_void_p, c_void_p]),

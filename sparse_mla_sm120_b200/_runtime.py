@@ -84,22 +84,38 @@ def pick_num_sm_parts(num_tokens: int, sms: int) -> int:
     return max_parts
 
 
+_SCRATCH_LIMIT = 64      # cached call shapes per process before the least recently used one is dropped
+
+
 def scratch(device: torch.device, total_splits: int, num_heads: int, num_tokens: int, num_parts: int):
-    """Cached scratch for one decode call shape (the reference allocates these on every call,
-    flash_mla_sm120/ops.py:78-99)."""
-    key = (device.index, total_splits, num_heads, num_tokens, num_parts)
-    ws = _scratch.get(key)
+    """Cached scratch for one decode call shape on the current stream (the reference allocates
+    these on every call, flash_mla_sm120/ops.py:78-99).
+
+    The key includes the stream: two calls of the same shape on different streams get different
+    buffers, so they cannot race on ``o_accum``.  An entry that is handed out while its stream is
+    being captured into a CUDA graph is pinned: the graph keeps raw pointers into it, so it is
+    never evicted.  Past _SCRATCH_LIMIT entries the least recently used unpinned one is dropped
+    (it was allocated on, and only ever used on, its own stream, so the caching allocator may
+    reuse it in stream order)."""
+    stream = torch.cuda.current_stream(device)
+    key = (device.index, stream.cuda_stream, total_splits, num_heads, num_tokens, num_parts)
+    ws = _scratch.pop(key, None)
     if ws is None:
         ws = {
             "o_accum": torch.empty((total_splits, 1, num_heads, 512), dtype=torch.float32, device=device),
             "lse_accum": torch.empty((total_splits, 1, num_heads), dtype=torch.float32, device=device),
             "sched_meta": torch.empty(num_parts * 8, dtype=torch.int32, device=device),
             "num_splits": torch.empty(num_tokens + 1, dtype=torch.int32, device=device),
-            "status": torch.zeros(4, dtype=torch.int32, device=device),
+            "pinned": False,
         }
-        if len(_scratch) > 64:
-            _scratch.clear()
-        _scratch[key] = ws
+    if torch.cuda.is_current_stream_capturing():
+        ws["pinned"] = True
+    _scratch[key] = ws                      # most recently used last
+    if len(_scratch) > _SCRATCH_LIMIT:
+        for old in list(_scratch):
+            if not _scratch[old]["pinned"] and old != key:
+                del _scratch[old]
+                break
     return ws
 
 
@@ -122,6 +138,11 @@ def check_status(device: Optional[torch.device] = None) -> None:
     vals = st.tolist()
     if vals[0] != 0:
         st.zero_()
-        names = {1: "empty", 2: "full", 3: "s_ready", 4: "p_ready", 5: "pv_done", 6: "q_ready"}
+        names = {1: "empty", 2: "full", 3: "s_ready", 4: "p_ready", 5: "pv_done", 6: "q_ready", 7: "loaded",
+                 11: "indexer q_full", 12: "indexer k_full", 13: "indexer k_empty", 14: "indexer d_full",
+                 15: "indexer d_empty", 16: "indexer q_empty", 17: "indexer tmem",
+                 21: "pair k_empty", 22: "pair k_loaded", 23: "pair k_full", 24: "pair tile_info", 25: "pair v_empty",
+                 26: "pair v_loaded", 27: "pair v_full", 28: "pair s_ready", 29: "pair s_free", 30: "pair p_ready",
+                 31: "pair pv_done", 32: "pair q_ready"}
         raise _lib.SmlaError(f"kernel wait gave up: barrier={names.get(vals[0], vals[0])} "
                              f"ctas={vals[1]} last_cta={vals[2]}")

@@ -7,9 +7,14 @@ The reference has no multi-GPU code.  Two shardings are offered:
 * long-context decode shards the KV context: rank g holds rows [g*L/G, (g+1)*L/G) of every
   sequence.  Each rank keeps the entries of the global index list that fall into its shard
   (``partition_indices``), runs split-KV decode over them to one fp32 partial + base-2 LSE per
-  token, the partials are all-gathered and merged with the same LSE-weighted combine that merges
-  split-KV partials (``sparse_mla_decode_cp_fwd``).  A token with no entry on a rank contributes
-  LSE = -1e30 and drops out of the merge exactly.
+  token, and the partials are merged with the same LSE-weighted combine that merges split-KV
+  partials (``sparse_mla_decode_cp_fwd``).  The exchange costs every rank the same whatever the
+  number of ranks G: an all-to-all by head slice (rank d receives, from everybody, the partials of
+  heads [d*H/G, (d+1)*H/G)), a merge of those H/G heads, and an all-gather of the bf16 result
+  (about 4 MB in and 2 MB out per rank at 16 tokens x 128 heads).  When the heads do not divide by
+  G the partials are all-gathered whole instead.  A token with no entry on a rank contributes
+  LSE = -1e30 and drops out of the merge exactly.  ``sparse_mla_prefill_cp_fwd`` runs the same
+  step over chunks of query tokens; ``GraphedCpDecode`` replays it as one CUDA graph.
 """
 from __future__ import annotations
 
@@ -62,6 +67,8 @@ def _gather_buffers(device, world, T, H):
     if key not in _gather_bufs:
         per = (T * H * 513 + 3) & ~3                      # a rank's share, kept 16-byte aligned
         packed = torch.empty((world, per), dtype=torch.float32, device=device)
+        if len(_gather_bufs) >= 16:
+            _gather_bufs.pop(next(iter(_gather_bufs)))
         _gather_bufs[key] = (packed, packed[:, :T * H * 512].view(world, T, H, 512),
                              packed[:, T * H * 512:T * H * 513].view(world, T, H))
     return _gather_bufs[key]
@@ -106,8 +113,72 @@ def combine_parts(o_parts, lse_parts, attn_sink=None, out=None):
     return out, lse
 
 
+_a2a_bufs: Dict[Tuple, Dict[str, torch.Tensor]] = {}
+
+
+def _a2a_buffers(device, world, T, H):
+    """Exchange buffers of the head-sliced path, cached per (device, stream, shape): ``send`` / ``recv``
+    [world, c] fp32 with c = T*(H/world)*513 rounded up to a multiple of 512 floats (a slice's partials, then its
+    LSEs), ``mine`` the merged bf16 slice followed by its fp32 LSEs as bytes, ``gathered`` [world, bytes]."""
+    stream = torch.cuda.current_stream(device).cuda_stream
+    key = (device.index, stream, world, T, H)
+    b = _a2a_bufs.get(key)
+    if b is None:
+        hs = H // world
+        c = -(-(T * hs * 513) // 512) * 512
+        chunk_bytes = -(-(T * hs * (1024 + 4)) // 16) * 16
+        b = {"send": torch.empty((world, c), dtype=torch.float32, device=device),
+             "recv": torch.empty((world, c), dtype=torch.float32, device=device),
+             "mine": torch.empty(chunk_bytes, dtype=torch.uint8, device=device),
+             "gathered": torch.empty((world, chunk_bytes), dtype=torch.uint8, device=device),
+             "c": c, "chunk_bytes": chunk_bytes}
+        if len(_a2a_bufs) >= 16:                 # a serving process uses a handful of shapes: drop the oldest
+            _a2a_bufs.pop(next(iter(_a2a_bufs)))
+        _a2a_bufs[key] = b
+    return b
+
+
+def decode_partial_sliced(q, kv_local, local_indices, local_length, sm_scale, send, slices: int, slice_stride: int,
+                          impl: int = IMPL_AUTO, num_sm_parts: Optional[int] = None):
+    """Local step of the head-sliced exchange: like ``decode_partial``, the result written as
+    ``slices`` head slices into ``send`` (see smla_decode_partial_sliced)."""
+    require_cuda(q, kv_local, local_indices, local_length, send)
+    T, H, _ = q.shape
+    topk = local_indices.shape[-1]
+    pbs, stride = kv_geometry(kv_local)
+    if num_sm_parts is None:
+        num_sm_parts = pick_num_sm_parts(T, num_sms(q.device))
+    ws = scratch(q.device, T + num_sm_parts, H, T, num_sm_parts)
+    lib, stream = _lib.load(), stream_ptr(q.device)
+    check(lib.smla_sched_meta(T, topk, 0, num_sm_parts, FIXED_OVERHEAD, ptr(local_length), None,
+                              ptr(ws["sched_meta"]), ptr(ws["num_splits"]), stream))
+    check(lib.smla_decode_partial_sliced(ptr(q), ptr(kv_local), ptr(local_indices), ptr(ws["o_accum"]),
+                                         ptr(ws["lse_accum"]), ptr(send), slices, slice_stride, ptr(ws["sched_meta"]),
+                                         ptr(ws["num_splits"]), T, H, topk, float(sm_scale), pbs, stride, num_sm_parts,
+                                         ptr(local_length), impl, ptr(status_buffer(q.device)), stream))
+
+
+def merge_head_slice(recv: torch.Tensor, mine: torch.Tensor, world: int, T: int, hs: int, c: int, attn_sink_slice=None):
+    """Merge the ``world`` partials of this rank's head slice (``recv`` [world, c] fp32 as received) into
+    ``mine``: [T, hs, 512] bf16 followed by [T, hs] fp32 base-2 LSEs."""
+    out_b = mine[:T * hs * 1024].view(torch.bfloat16)
+    lse_b = mine[T * hs * 1024:T * hs * 1028].view(torch.float32)
+    check(_lib.load().smla_combine_parts_strided(ptr(recv), recv.data_ptr() + T * hs * 512 * 4, ptr(out_b), ptr(lse_b), world,
+                                                 T, hs, c, c, ptr(attn_sink_slice), stream_ptr(recv.device)))
+
+
+def unslice(gathered: torch.Tensor, world: int, T: int, hs: int, chunk_bytes: int, out=None):
+    """[world] chunks of (bf16 [T, hs, 512], fp32 [T, hs]) -> (out [T, world*hs, 512] bf16, lse [T, world*hs])."""
+    dev = gathered.device
+    if out is None:
+        out = torch.empty((T, world * hs, 512), dtype=torch.bfloat16, device=dev)
+    lse = torch.empty((T, world * hs), dtype=torch.float32, device=dev)
+    check(_lib.load().smla_cp_unslice(ptr(gathered), ptr(out), ptr(lse), world, T, hs, chunk_bytes, stream_ptr(dev)))
+    return out, lse
+
+
 def sparse_mla_decode_cp_fwd(q, kv_local, indices, sm_scale, shard_lo: int, shard_hi: int, group=None,
-                             attn_sink=None, impl: int = IMPL_AUTO):
+                             attn_sink=None, impl: int = IMPL_AUTO, out=None):
     """Context-parallel decode.  ``indices`` [T, topk] are global row numbers of the full context
     (identical on every rank), ``kv_local`` holds rows [shard_lo, shard_hi) of it.
     Returns (out [T, H, 512] bf16, lse [T, H] fp32 base-2), identical on every rank."""
@@ -116,11 +187,88 @@ def sparse_mla_decode_cp_fwd(q, kv_local, indices, sm_scale, shard_lo: int, shar
     rank = dist.get_rank(group) if dist.is_initialized() else 0
     T, H, _ = q.shape
     local_idx, local_len = partition_indices(indices, shard_lo, shard_hi)
+    if world > 1 and H % world == 0:
+        # head-sliced exchange: per-rank traffic does not grow with the number of ranks
+        b = _a2a_buffers(q.device, world, T, H)
+        hs = H // world
+        decode_partial_sliced(q, kv_local, local_idx, local_len, sm_scale, b["send"], world, b["c"], impl=impl)
+        dist.all_to_all_single(b["recv"], b["send"], group=group)
+        sink = attn_sink[rank * hs:(rank + 1) * hs] if attn_sink is not None else None
+        merge_head_slice(b["recv"], b["mine"], world, T, hs, b["c"], sink)
+        dist.all_gather_into_tensor(b["gathered"], b["mine"], group=group)
+        return unslice(b["gathered"], world, T, hs, b["chunk_bytes"], out)
     packed, o_all, lse_all = _gather_buffers(q.device, world, T, H)
     decode_partial(q, kv_local, local_idx, local_len, sm_scale, o_all[rank], lse_all[rank], impl=impl)
     if world > 1:
         dist.all_gather_into_tensor(packed, packed[rank], group=group)       # partials and LSEs in one exchange
-    return combine_parts(o_all, lse_all, attn_sink)
+    return combine_parts(o_all, lse_all, attn_sink, out)
+
+
+def sparse_mla_prefill_cp_fwd(q, kv_local, indices, sm_scale, shard_lo: int, shard_hi: int, group=None,
+                              attn_sink=None, impl: int = IMPL_AUTO, chunk_tokens: int = 256):
+    """Context-parallel prefill: the KV context is sharded as for decode, every rank holds all the
+    query tokens.  The tokens are processed in chunks (the fp32 partials of a chunk are what is
+    exchanged: chunk_tokens x H x 2 KB per rank) through the same partition -> partial -> exchange ->
+    merge step.  Returns (out [T, H, 512] bf16, lse [T, H] fp32 base-2), identical on every rank."""
+    T, H, _ = q.shape
+    out = torch.empty((T, H, 512), dtype=torch.bfloat16, device=q.device)
+    lse = torch.empty((T, H), dtype=torch.float32, device=q.device)
+    for t0 in range(0, T, chunk_tokens):
+        t1 = min(t0 + chunk_tokens, T)
+        o, l = sparse_mla_decode_cp_fwd(q[t0:t1], kv_local, indices[t0:t1], sm_scale, shard_lo, shard_hi, group,
+                                        attn_sink, impl, out=out[t0:t1])
+        lse[t0:t1] = l
+    return out, lse
+
+
+class GraphedCpDecode:
+    """One context-parallel decode step (index partition, local decode, exchange, merge) captured
+    into a CUDA graph, collectives included: one graph launch per step instead of about ten
+    launches and two collectives issued from the host.  Shapes are fixed at construction, the cache
+    shard is bound by reference, q and the indices are copied into static buffers before a replay.
+    If the capture fails (a process-group backend that cannot be captured) the object runs the
+    step eagerly and ``self.graph`` is None."""
+
+    def __init__(self, kv_local, num_tokens: int, num_heads: int, topk: int, sm_scale: float, shard_lo: int,
+                 shard_hi: int, group=None, attn_sink=None, impl: int = IMPL_AUTO):
+        dev = kv_local.device
+        self.kv_local, self.attn_sink = kv_local, attn_sink
+        self.q = torch.zeros((num_tokens, num_heads, 576), dtype=torch.bfloat16, device=dev)
+        self.indices = torch.full((num_tokens, topk), -1, dtype=torch.int32, device=dev)
+        self.out = torch.empty((num_tokens, num_heads, 512), dtype=torch.bfloat16, device=dev)
+
+        def step():
+            return sparse_mla_decode_cp_fwd(self.q, kv_local, self.indices, sm_scale, shard_lo, shard_hi, group, attn_sink,
+                                            impl, out=self.out)
+
+        self._step = step
+        self.graph = None
+        side = torch.cuda.Stream(device=dev)
+        side.wait_stream(torch.cuda.current_stream(dev))
+        with torch.cuda.stream(side):
+            for _ in range(2):
+                step()                               # warm-up: library load, buffers, communicator set-up
+            side.synchronize()
+            try:
+                graph = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(graph, stream=side):
+                    _, self.lse = step()
+                self.graph = graph
+            except Exception:                        # noqa: BLE001 - any capture failure means: run eagerly
+                self.graph = None
+        torch.cuda.current_stream(dev).wait_stream(side)
+
+    def __call__(self, q, indices):
+        self.q.copy_(q)
+        self.indices.copy_(indices)
+        return self.replay()
+
+    def replay(self):
+        if self.graph is None:
+            _, self.lse = self._step()
+        else:
+            self.graph.replay()
+        return self.out, self.lse
 
 
 # ----------------------------------------------------------------------------------------------

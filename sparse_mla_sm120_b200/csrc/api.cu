@@ -119,18 +119,19 @@ int smla_combine(const float* o_accum, const float* lse_accum, void* out, float*
                           max_nsplits, attn_sink, (cudaStream_t)stream);
 }
 
-int smla_decode_partial(const void* q, const void* kv, const int32_t* indices,
-                        float* o_accum, float* lse_accum, float* o_part, float* lse_part,
-                        const int32_t* sched_meta, const int32_t* num_splits,
-                        int num_tokens, int num_heads, int topk, float sm_scale,
-                        int page_block_size, int64_t kv_block_stride_bytes, int num_sm_parts,
-                        const int32_t* topk_length, int impl, int32_t* status, void* stream) {
-    if (int e = check_attn_common("smla_decode_partial", q, kv, indices, o_part, lse_part, num_tokens, num_heads,
+static int decode_partial_common(const char* fn, const void* q, const void* kv, const int32_t* indices,
+                                 float* o_accum, float* lse_accum, float* o_part, float* lse_part,
+                                 const int32_t* sched_meta, const int32_t* num_splits,
+                                 int num_tokens, int num_heads, int topk, float sm_scale,
+                                 int page_block_size, int64_t kv_block_stride_bytes, int num_sm_parts,
+                                 const int32_t* topk_length, int impl, int32_t* status, int slices, int64_t slice_stride,
+                                 void* stream) {
+    if (int e = check_attn_common(fn, q, kv, indices, o_part, lse_part, num_tokens, num_heads,
                                   topk, page_block_size, kv_block_stride_bytes, impl)) return e;
     if (!o_accum || !lse_accum || !sched_meta || !num_splits)
-        return set_error(SMLA_E_NULL, "smla_decode_partial: null scratch or scheduler pointer");
-    if (!aligned16(o_accum)) return set_error(SMLA_E_ALIGN, "smla_decode_partial: o_accum not 16-byte aligned");
-    if (num_sm_parts < 1) return set_error(SMLA_E_SHAPE, "smla_decode_partial: num_sm_parts=%d", num_sm_parts);
+        return set_error(SMLA_E_NULL, "%s: null scratch or scheduler pointer", fn);
+    if (!aligned16(o_accum)) return set_error(SMLA_E_ALIGN, "%s: o_accum not 16-byte aligned", fn);
+    if (num_sm_parts < 1) return set_error(SMLA_E_SHAPE, "%s: num_sm_parts=%d", fn, num_sm_parts);
     AttnParams p{};
     p.q = (const __nv_bfloat16*)q; p.kv = (const uint8_t*)kv; p.indices = indices;
     p.o_accum = o_accum; p.lse_accum = lse_accum; p.out = nullptr; p.out_lse = nullptr;
@@ -143,8 +144,47 @@ int smla_decode_partial(const void* q, const void* kv, const int32_t* indices,
                   : (impl == SMLA_IMPL_TC_PAIR) ? launch_attn_pair(p, (cudaStream_t)stream)
                                                 : launch_attn_tc(p, (cudaStream_t)stream);
     if (e) return e;
-    return launch_combine_f32(o_accum, lse_accum, o_part, lse_part, num_splits, num_tokens, num_heads,
+    return launch_combine_f32(o_accum, lse_accum, o_part, lse_part, num_splits, num_tokens, num_heads, slices, slice_stride,
                               (cudaStream_t)stream);
+}
+
+int smla_decode_partial(const void* q, const void* kv, const int32_t* indices,
+                        float* o_accum, float* lse_accum, float* o_part, float* lse_part,
+                        const int32_t* sched_meta, const int32_t* num_splits,
+                        int num_tokens, int num_heads, int topk, float sm_scale,
+                        int page_block_size, int64_t kv_block_stride_bytes, int num_sm_parts,
+                        const int32_t* topk_length, int impl, int32_t* status, void* stream) {
+    return decode_partial_common("smla_decode_partial", q, kv, indices, o_accum, lse_accum, o_part, lse_part, sched_meta,
+                                 num_splits, num_tokens, num_heads, topk, sm_scale, page_block_size, kv_block_stride_bytes,
+                                 num_sm_parts, topk_length, impl, status, 1, 0, stream);
+}
+
+int smla_decode_partial_sliced(const void* q, const void* kv, const int32_t* indices,
+                               float* o_accum, float* lse_accum, float* send, int slices, int64_t slice_stride,
+                               const int32_t* sched_meta, const int32_t* num_splits,
+                               int num_tokens, int num_heads, int topk, float sm_scale,
+                               int page_block_size, int64_t kv_block_stride_bytes, int num_sm_parts,
+                               const int32_t* topk_length, int impl, int32_t* status, void* stream) {
+    if (slices < 1 || num_heads % (slices < 1 ? 1 : slices) != 0)
+        return set_error(SMLA_E_SHAPE, "smla_decode_partial_sliced: %d heads do not divide into %d slices", num_heads, slices);
+    const int64_t need = (int64_t)num_tokens * (num_heads / slices) * (D_V + 1);
+    if (slice_stride < need || slice_stride % D_V != 0 || !aligned16(send))
+        return set_error(SMLA_E_SHAPE, "smla_decode_partial_sliced: slice stride %lld must be a multiple of %d floats and hold %lld",
+                         (long long)slice_stride, D_V, (long long)need);
+    return decode_partial_common("smla_decode_partial_sliced", q, kv, indices, o_accum, lse_accum, send, send, sched_meta,
+                                 num_splits, num_tokens, num_heads, topk, sm_scale, page_block_size, kv_block_stride_bytes,
+                                 num_sm_parts, topk_length, impl, status, slices, slice_stride, stream);
+}
+
+int smla_cp_unslice(const void* gathered, void* out, float* lse, int slices, int num_tokens, int heads_per_slice,
+                    int64_t chunk_bytes, void* stream) {
+    if (!gathered || !out || !lse) return set_error(SMLA_E_NULL, "smla_cp_unslice: null pointer argument");
+    if (slices < 1 || num_tokens < 0 || heads_per_slice < 1 ||
+        chunk_bytes < (int64_t)num_tokens * heads_per_slice * (D_V * 2 + 4) || (chunk_bytes & 15))
+        return set_error(SMLA_E_SHAPE, "smla_cp_unslice: slices=%d tokens=%d heads=%d chunk=%lld", slices, num_tokens,
+                         heads_per_slice, (long long)chunk_bytes);
+    if (!aligned16(gathered) || !aligned16(out)) return set_error(SMLA_E_ALIGN, "smla_cp_unslice: unaligned buffer");
+    return launch_cp_unslice(gathered, (__nv_bfloat16*)out, lse, slices, num_tokens, heads_per_slice, chunk_bytes, (cudaStream_t)stream);
 }
 
 int smla_combine_parts(const float* o_parts, const float* lse_parts, void* out, float* out_lse,

@@ -24,7 +24,8 @@ __global__ void __launch_bounds__(WARPS * 32)
 combine_kernel(const float* __restrict__ o_accum, const float* __restrict__ lse_accum,
                OutT* __restrict__ out, float* __restrict__ out_lse,
                const int32_t* __restrict__ num_splits, const float* __restrict__ attn_sink,
-               int batch, int num_heads, int fixed_ns, int64_t part_stride_o, int64_t part_stride_l) {
+               int batch, int num_heads, int fixed_ns, int64_t part_stride_o, int64_t part_stride_l,
+               int out_slices, int64_t out_slice_stride) {
     constexpr bool F32 = sizeof(OutT) == 4;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int64_t row = (int64_t)blockIdx.x * WARPS + warp;   // (token, head)
@@ -69,7 +70,17 @@ combine_kernel(const float* __restrict__ o_accum, const float* __restrict__ lse_
             lse = sink2;
         }
     }
-    if (lane == 0) out_lse[row] = lse;
+    // fp32 output cut into head slices (one per destination rank of an all-to-all): slice d holds
+    // [batch, num_heads / out_slices, 512] partials followed by its [batch, num_heads / out_slices] LSEs
+    size_t out_row = (size_t)row;
+    float* lse_dst = out_lse + row;
+    if (F32 && out_slices > 1) {
+        const int hs = num_heads / out_slices, d = h / hs;
+        out_row = (size_t)tok * hs + (h - d * hs);
+        lse_dst = reinterpret_cast<float*>(out) + (size_t)d * out_slice_stride + (size_t)batch * hs * D_V + out_row;
+        out_row += (size_t)d * out_slice_stride / D_V;      // out_slice_stride is a multiple of D_V floats
+    }
+    if (lane == 0) *lse_dst = lse;
 
     float4 acc[4];
 #pragma unroll
@@ -101,7 +112,7 @@ combine_kernel(const float* __restrict__ o_accum, const float* __restrict__ lse_
         }
     }
     if constexpr (F32) {
-        float* o_out = reinterpret_cast<float*>(out) + (size_t)row * D_V + lane * 4;
+        float* o_out = reinterpret_cast<float*>(out) + out_row * D_V + lane * 4;
 #pragma unroll
         for (int i = 0; i < 4; ++i) *reinterpret_cast<float4*>(o_out + i * 128) = acc[i];
         return;
@@ -128,18 +139,21 @@ int launch_combine(const float* o_accum, const float* lse_accum, __nv_bfloat16* 
     if (rows == 0) return 0;
     const unsigned grid = (unsigned)((rows + WARPS - 1) / WARPS);
     combine_kernel<__nv_bfloat16><<<grid, WARPS * 32, 0, stream>>>(o_accum, lse_accum, out, out_lse, num_splits,
-                                                                    attn_sink, batch, num_heads, 0, 0, 0);
+                                                                    attn_sink, batch, num_heads, 0, 0, 0, 1, 0);
     return check_launch("combine_kernel");
 }
 
 // Local merge for the context-parallel path: every token (also those with one split) to fp32.
+// With out_slices > 1 the result is written as `out_slices` head slices, slice d at out + d * out_slice_stride
+// floats: [batch, num_heads / out_slices, 512] partials, then the slice's LSEs (out_lse is not used).
 int launch_combine_f32(const float* o_accum, const float* lse_accum, float* out, float* out_lse,
-                       const int32_t* num_splits, int batch, int num_heads, cudaStream_t stream) {
+                       const int32_t* num_splits, int batch, int num_heads, int out_slices, int64_t out_slice_stride,
+                       cudaStream_t stream) {
     const int64_t rows = (int64_t)batch * num_heads;
     if (rows == 0) return 0;
     const unsigned grid = (unsigned)((rows + WARPS - 1) / WARPS);
     combine_kernel<float><<<grid, WARPS * 32, 0, stream>>>(o_accum, lse_accum, out, out_lse, num_splits, nullptr,
-                                                            batch, num_heads, 0, 0, 0);
+                                                            batch, num_heads, 0, 0, 0, out_slices, out_slice_stride);
     return check_launch("combine_kernel<f32>");
 }
 
@@ -153,8 +167,38 @@ int launch_combine_parts(const float* o_parts, const float* lse_parts, __nv_bflo
     const unsigned grid = (unsigned)((rows + WARPS - 1) / WARPS);
     combine_kernel<__nv_bfloat16><<<grid, WARPS * 32, 0, stream>>>(o_parts, lse_parts, out, out_lse, nullptr,
                                                                     attn_sink, batch, num_heads, parts, part_stride_o,
-                                                                    part_stride_l);
+                                                                    part_stride_l, 1, 0);
     return check_launch("combine_kernel<parts>");
+}
+
+namespace {
+// gathered: `slices` chunks of `chunk_bytes`, chunk g = [num_tokens, hs, 512] bf16 followed by [num_tokens, hs] fp32
+// (the merged output of head slice g and its LSEs) -> out [num_tokens, slices * hs, 512] bf16, lse [num_tokens, slices * hs].
+__global__ void cp_unslice_kernel(const uint8_t* __restrict__ gathered, __nv_bfloat16* __restrict__ out, float* __restrict__ lse,
+                                  int slices, int num_tokens, int hs, int64_t chunk_bytes) {
+    const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;      // one 16-byte piece of the output
+    const int64_t pieces = (int64_t)num_tokens * slices * hs * (D_V / 8);
+    if (i < pieces) {
+        const int c = (int)(i % (D_V / 8));
+        const int64_t row = i / (D_V / 8);                                 // (token, head)
+        const int h = (int)(row % ((int64_t)slices * hs)), t = (int)(row / ((int64_t)slices * hs));
+        const int g = h / hs, hh = h - g * hs;
+        const uint4 v = *reinterpret_cast<const uint4*>(gathered + (size_t)g * chunk_bytes + ((size_t)t * hs + hh) * (D_V * 2) + c * 16);
+        *reinterpret_cast<uint4*>(out + (size_t)row * D_V + c * 8) = v;
+        if (c == 0)
+            lse[row] = *reinterpret_cast<const float*>(gathered + (size_t)g * chunk_bytes + (size_t)num_tokens * hs * (D_V * 2) +
+                                                       ((size_t)t * hs + hh) * 4);
+    }
+}
+}  // namespace
+
+int launch_cp_unslice(const void* gathered, __nv_bfloat16* out, float* lse, int slices, int num_tokens, int hs,
+                      int64_t chunk_bytes, cudaStream_t stream) {
+    const int64_t pieces = (int64_t)num_tokens * slices * hs * (D_V / 8);
+    if (pieces == 0) return 0;
+    cp_unslice_kernel<<<(unsigned)((pieces + 255) / 256), 256, 0, stream>>>((const uint8_t*)gathered, out, lse, slices, num_tokens, hs,
+                                                                           chunk_bytes);
+    return check_launch("cp_unslice_kernel");
 }
 
 }  // namespace smla

@@ -86,7 +86,10 @@ int launch_combine(const float* o_accum, const float* lse_accum, __nv_bfloat16* 
                    const int32_t* num_splits, int batch, int num_heads, int max_nsplits,
                    const float* attn_sink, cudaStream_t stream);
 int launch_combine_f32(const float* o_accum, const float* lse_accum, float* out, float* out_lse,
-                       const int32_t* num_splits, int batch, int num_heads, cudaStream_t stream);
+                       const int32_t* num_splits, int batch, int num_heads, int out_slices, int64_t out_slice_stride,
+                       cudaStream_t stream);
+int launch_cp_unslice(const void* gathered, __nv_bfloat16* out, float* lse, int slices, int num_tokens, int hs,
+                      int64_t chunk_bytes, cudaStream_t stream);
 int launch_combine_parts(const float* o_parts, const float* lse_parts, __nv_bfloat16* out, float* out_lse,
                          int parts, int batch, int num_heads, int64_t part_stride_o, int64_t part_stride_l,
                          const float* attn_sink, cudaStream_t stream);

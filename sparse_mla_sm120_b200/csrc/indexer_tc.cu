@@ -72,7 +72,7 @@ __global__ void __launch_bounds__(LX_THREADS, 1) mqa_logits_tc_kernel(const Logi
         for (int s = 0; s < LX_KSTAGE; ++s) { mbar_init(bar(LXB_KFULL + s), 1); mbar_init(bar(LXB_KEMPTY + s), 1); }
         for (int b = 0; b < 2; ++b) { mbar_init(bar(LXB_DFULL + b), 1); mbar_init(bar(LXB_DEMPTY + b), LX_EPI_WARPS * 32); }
         mbar_init(bar(LXB_QFULL), 32);
-        mbar_init(bar(LXB_QEMPTY), 1);
+        mbar_init(bar(LXB_QEMPTY), 1 + LX_EPI_WARPS);   // the MMAs have read q and every epilogue warp has seen the group's phase
         *abort_flag = 0;
         mbar_init_fence();
     }
@@ -131,6 +131,11 @@ __global__ void __launch_bounds__(LX_THREADS, 1) mqa_logits_tc_kernel(const Logi
             if (t1 > t0) {
                 ok = mbar_wait(bar(LXB_QFULL), qn & 1u, abort_flag, 11);   // weights of the group are in shared memory
                 if (!ok) break;
+                // The loader may arm the next group only after this warp has seen this one: otherwise two phases
+                // of QFULL could complete before a slow epilogue warp waits for the first (a group of one or two
+                // tiles needs nothing from the epilogue), and its parity wait would then refer to a later phase.
+                __syncwarp();
+                if (lane == 0) mbar_arrive(bar(LXB_QEMPTY));
                 ++qn;
             }
             for (int t = t0; t < t1 && ok; ++t, ++it) {

@@ -128,6 +128,25 @@ def test_mqa_logits(s_q, h, s_k, impl):
     assert float((got[fin] - ref[fin]).abs().max()) <= 1e-4 * float(ref[fin].abs().max())
 
 
+def test_mqa_logits_short_then_long_items():
+    """Causal windows over a long key range: the first work items of a CTA need one or two key tiles, later ones
+    five or six.  (A group of one or two tiles needs nothing from the epilogue warps, so the loader could once
+    arm two groups before a slow epilogue warp had waited for the first; the status word must stay clear.)"""
+    from sparse_mla_sm120_b200 import indexer
+    from sparse_mla_sm120_b200._runtime import check_status
+    s_q, h, s_k = 800, 64, 2048
+    q, k, k_scale, w, _, _ = _indexer_case(11, s_q, h, s_k)
+    ks = torch.zeros(s_q, dtype=torch.int32)
+    ke = (torch.arange(s_q, dtype=torch.int32) + 1)
+    ref = orc.mqa_logits_ref(q, k, k_scale, w, ks, ke)
+    for _ in range(3):
+        got = indexer.fp8_mqa_logits(q.to(DEV), k.to(DEV), k_scale.to(DEV), w.to(DEV), ks.to(DEV), ke.to(DEV)).cpu()
+        check_status(torch.device(DEV))
+        assert torch.equal(torch.isinf(got), torch.isinf(ref)), "range mask differs"
+        fin = ~torch.isinf(ref)
+        assert float((got[fin] - ref[fin]).abs().max()) <= 1e-4 * float(ref[fin].abs().max())
+
+
 def test_topk_sets():
     from sparse_mla_sm120_b200 import indexer
     torch.manual_seed(5)
