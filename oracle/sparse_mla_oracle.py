@@ -336,3 +336,61 @@ def cp_partition_ref(indices: torch.Tensor, lo: int, hi: int) -> Tuple[torch.Ten
         local[t, :keep.numel()] = keep
         length[t] = keep.numel()
     return local, length
+
+
+# --------------------------------------------------------------------------- FP8-class numerics
+def emulate_fp8_attention(q: torch.Tensor, packed: torch.Tensor, indices: torch.Tensor, sm_scale: float,
+                          topk_length: Optional[torch.Tensor] = None, p_shift: int = 5
+                          ) -> Tuple[torch.Tensor, torch.Tensor]:
+    """The attention of ``ref_sparse_attn`` with the roundings a kernel of the FP8 class makes, in
+    fp32 on the CPU: used to DERIVE the tolerances of the tensor-core kernels instead of fitting
+    them to a kernel's output.  It restates numerics, not an implementation:
+
+      * Q no-PE -> e4m3 with one power-of-two scale per head, amax floor 1e-4 (the reference
+        quantises Q the same way, per 128-value tile: csrc/kernel/common/fp8_quant.cuh:44-103);
+        Q RoPE and K RoPE stay bf16;
+      * K / V are the stored e4m3 bytes times their power-of-two scales, exactly (no bf16
+        rounding of the dequantised value, unlike ``dequantize_kv_v32``: the tensor core reads the bytes);
+      * logits and softmax statistics in fp32;
+      * the softmax weight times the row's V scale is rounded to e4m3 (scaled by 2**p_shift against
+        the row maximum) before it multiplies V, as the reference's kernels round P
+        (csrc/kernel/decode/decode_v2_kernel.cuh:414-493); the denominator uses the unrounded weights.
+
+    q [T, H, 576] bf16, packed [..., 656] uint8 rows, indices [T, topk] int32.
+    Returns (out bf16 [T, H, 512], lse natural log [T, H])."""
+    T, H, _ = q.shape
+    rows = packed.reshape(-1, ROW_BYTES)
+    fp8 = rows[:, :D_NOPE].contiguous().view(torch.float8_e4m3fn).float().view(-1, NUM_TILES, QUANT_TILE)
+    sc = rows[:, D_NOPE:D_NOPE + 16].contiguous().view(torch.float32).view(-1, NUM_TILES)
+    k_nope = (fp8 * sc.unsqueeze(-1)).view(-1, D_NOPE)                       # exact: scales are powers of two
+    k_rope = rows[:, D_NOPE + 16:].contiguous().view(torch.bfloat16).float()
+    s_row = sc.amax(dim=1)                                                  # the row's largest scale
+    qf = q.float()
+    amax = qf[..., :D_NOPE].abs().amax(dim=-1).clamp(min=1e-4)
+    sq = pow2_scale(amax / 448.0)
+    q8 = (qf[..., :D_NOPE] / sq.unsqueeze(-1)).clamp(-448, 448).to(torch.float8_e4m3fn).float() * sq.unsqueeze(-1)
+    topk = indices.shape[-1]
+    invalid = indices < 0
+    if topk_length is not None:
+        invalid = invalid | (torch.arange(topk).view(1, topk) >= topk_length.view(T, 1))
+    idx = indices.clamp(min=0).long()
+    out = torch.zeros(T, H, D_V)
+    lse = torch.full((T, H), float("-inf"))
+    for t in range(T):
+        kn, kr, st = k_nope[idx[t]], k_rope[idx[t]], s_row[idx[t]]
+        x = (q8[t] @ kn.T + qf[t, :, D_NOPE:] @ kr.T) * (sm_scale * LOG2E)        # [H, topk], base-2 logits
+        x[:, invalid[t]] = float("-inf")
+        z = x + st.clamp(min=1e-38).log2().unsqueeze(0)                           # the row's V scale rides in the exponent
+        z[:, invalid[t]] = float("-inf")
+        m = z.amax(dim=1, keepdim=True)
+        live = torch.isfinite(m.squeeze(1))
+        m = torch.where(torch.isfinite(m), m, torch.zeros_like(m))
+        p = torch.exp2(z - m + p_shift)
+        p8 = p.clamp(max=448).to(torch.float8_e4m3fn).float()
+        v_raw = kn / st.clamp(min=1e-38).unsqueeze(1)                             # V in units of its row scale
+        v_raw[invalid[t]] = 0.0
+        l = (p / st.clamp(min=1e-38).unsqueeze(0)).sum(dim=1)
+        o = (p8 @ v_raw) / l.clamp(min=1e-38).unsqueeze(1)
+        out[t] = torch.where(live.unsqueeze(1), o, torch.zeros_like(o))
+        lse[t] = torch.where(live, (l.clamp(min=1e-38).log2() + m.squeeze(1) - p_shift) * LN2, torch.full_like(l, float("-inf")))
+    return out.to(torch.bfloat16), lse

@@ -18,23 +18,6 @@ from ._runtime import (BLOCK_N, FIXED_OVERHEAD, kv_geometry, num_sms, pick_num_s
                        scratch, status_buffer, stream_ptr)
 
 
-def _effective_stride_kv_row(kv_cache: torch.Tensor) -> int:
-    """Per-token byte stride such that block * stride == the page stride.
-
-    Mirrors flash_mla_sm120/ops.py:23-45 for callers that use it; the kernels here take the
-    page stride itself (see _runtime.kv_geometry)."""
-    if kv_cache.dim() < 3:
-        return kv_cache.stride(-2) * kv_cache.element_size()
-    page_block_size = kv_cache.shape[-3]
-    natural = kv_cache.stride(-2) * kv_cache.element_size()
-    block_stride = kv_cache.stride(0) * kv_cache.element_size()
-    if block_stride == page_block_size * natural:
-        return natural
-    assert block_stride % page_block_size == 0, (
-        f"kv_cache block stride {block_stride} not divisible by page_block_size {page_block_size}")
-    return block_stride // page_block_size
-
-
 def _reject_extra(extra_k_cache, extra_indices, extra_topk_length, extra_topk):
     if extra_k_cache is not None or extra_indices is not None or extra_topk_length is not None or extra_topk:
         raise NotImplementedError("the second (extra) KV cache of the MODEL1 layout is not built")

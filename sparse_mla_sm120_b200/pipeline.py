@@ -1,9 +1,9 @@
 """Indexer -> top-k -> sparse attention as one call (one GPU).
 
-The reference ships the three kernels separately (the attention ops in sparse_mla_sm120/ops.py,
-the indexer benchmarked by benchmarks/bench_lighting_indexer.py) and a serving stack chains them
-per layer.  Here the chain is one function on one stream with no host synchronisation in between,
-so it can be captured into a CUDA graph as a whole."""
+The reference has the attention ops only (sparse_mla_sm120/ops.py, flash_mla_sm120/ops.py); the
+indices they consume come from an indexer outside it (flash_mla_sm120/interface.py:39-58), and a
+serving stack chains the steps per layer.  Here the chain is one function on one stream with no
+host synchronisation in between, so it can be captured into a CUDA graph as a whole."""
 from __future__ import annotations
 
 from typing import Optional, Tuple

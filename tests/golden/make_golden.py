@@ -80,4 +80,6 @@ def main(ref_root: str, out_dir: str) -> None:
 
 if __name__ == "__main__":
     import os
-    main(sys.argv[1] if len(sys.argv) > 1 else "/root/reference", os.path.dirname(os.path.abspath(__file__)))
+    if len(sys.argv) < 2:
+        sys.exit("usage: python tests/golden/make_golden.py /path/to/reference")
+    main(sys.argv[1], os.path.dirname(os.path.abspath(__file__)))

@@ -21,17 +21,26 @@ from oracle import sparse_mla_oracle as orc  # noqa: E402
 LN2 = math.log(2.0)
 
 # Tolerances.  The exact fp32 kernel must agree with the fp32 oracle to bf16 rounding of the
-# output.  The tensor-core kernel quantises Q and the softmax weights to e4m3 (3 mantissa bits),
-# as the reference's V32 kernels do; its bounds are the FlashMLA-style form the reference uses
-# for its own FP8 paths (tests/test_v4_features.py:28-31) plus a cosine bound.
-# e4m3 rounding is up to 2^-4 relative (3.6 % rms) per softmax weight; over the top-k sum the
-# errors are independent, so the output error is noise of about 3 % of the output's own rms
-# magnitude (measured: mean |d| 2.7 % of rms, 1 - cos 4e-4).  The elementwise bound therefore
-# carries a term proportional to rms(reference) (6 sigma of that noise) besides the FlashMLA form.
+# output.  The tensor-core kernels quantise Q and the softmax weights to e4m3 (3 mantissa bits),
+# as the reference's V32 kernels do; what that costs is DERIVED from oracle.emulate_fp8_attention,
+# a CPU restatement of those roundings that shares no code with any kernel.  Its distance to the
+# fp32 oracle (seeded cases of tests/test_oracle_golden.py::test_fp8_emulation_distance):
+#   reference-grid data (randn/10):  max |d| 3-6e-4            (the reference's own bar is 1e-3)
+#   benchmark-like data (kv randn, q 0.5 randn):
+#       |d| exceeds the FlashMLA form 1e-3 + 2.01/128 max(|a|,|b|) (tests/test_v4_features.py:28-31)
+#       by 0.10-0.12 x rms(reference), 1 - cos = 3.8-4.3e-4, LSE error 1.9-2.5e-3.
+# The elementwise bound for benchmark-like data therefore carries the term TC_NOISE x rms(reference)
+# with TC_NOISE = 0.2 (1.7 x the emulation), the cosine bound is 1e-3 (2.3 x) and the LSE bound 1e-2.
+# Data on which the roundings cost more (peaked softmax, scales spread over 2^9, rows averaging few
+# tokens) are not given a hand-picked multiplier: check_against_emulation bounds the kernel's distance
+# to the oracle by EMU_MARGIN x the emulation's distance on the same inputs.
 SCALAR_ABS, SCALAR_REL, SCALAR_LSE = 2e-5, 2.0 ** -7, 2e-4
 TC_ABS, TC_REL, TC_COS, TC_LSE = 1e-3, 2.01 / 128, 1e-3, 1e-2
 TC_PREFILL_ABS, TC_PREFILL_REL = 8e-4, 3.01 / 128
 TC_NOISE = 0.2       # x rms(reference output)
+EMU_MARGIN = 1.5     # a kernel rounds at other positions than the emulation (lazily updated maximum, scale per
+                     # tile instead of per row): two realisations of the same noise, whose maxima over 1e5-1e7
+                     # elements differ by up to about 1.3 x
 
 
 def bf16_from_bits(a: np.ndarray) -> torch.Tensor:
@@ -90,15 +99,39 @@ def compare_lse(lse2_kernel: torch.Tensor, lse_ref: torch.Tensor, tol: float):
     return err
 
 
-def compare_out(out_kernel: torch.Tensor, out_ref: torch.Tensor, abs_tol, rel_tol, cos_tol=None, noise=1.0):
+def compare_out(out_kernel: torch.Tensor, out_ref: torch.Tensor, abs_tol, rel_tol, cos_tol=None):
     """|d| <= abs_tol + rel_tol*max(|a|,|b|) elementwise; when cos_tol is given (FP8 kernel) the
     absolute term grows by TC_NOISE * rms(reference) and 1 - cos must stay below cos_tol."""
     if cos_tol is not None:
-        abs_tol = abs_tol + noise * TC_NOISE * float(out_ref.float().pow(2).mean().sqrt())
-        cos_tol = cos_tol * noise * noise
+        abs_tol = abs_tol + TC_NOISE * float(out_ref.float().pow(2).mean().sqrt())
     ok, max_diff, nbad = orc.allclose_report(out_kernel.cpu(), out_ref, abs_tol, rel_tol)
     assert ok, f"{nbad} elements outside |d| <= {abs_tol} + {rel_tol}*max(|a|,|b|); max diff {max_diff}"
     if cos_tol is not None:
         cd = orc.cos_diff(out_kernel.cpu(), out_ref)
         assert cd <= cos_tol, f"1 - cos = {cd} > {cos_tol}"
     return max_diff
+
+
+def check_against_emulation(out_kernel, lse2_kernel, case, ref_out, ref_lse, topk_length=None):
+    """FP8-class check whose tolerance is derived on the spot: the kernel may be EMU_MARGIN times as far
+    from the fp32 oracle as oracle.emulate_fp8_attention is on the same inputs (largest element, rms and
+    1 - cos of the output; largest LSE difference), plus the bf16 rounding of the output."""
+    emu_out, emu_lse = orc.emulate_fp8_attention(case["q"], case["packed"], case["indices"], case["sm_scale"],
+                                                 topk_length=topk_length)
+    ref = ref_out.float()
+    e_emu, e_k = (emu_out.float() - ref), (out_kernel.cpu().float() - ref)
+    bf16_step = 2.0 ** -8 * float(ref.abs().max())
+    assert float(e_k.abs().max()) <= EMU_MARGIN * float(e_emu.abs().max()) + bf16_step, \
+        f"max |d| {float(e_k.abs().max())} against the emulation's {float(e_emu.abs().max())}"
+    assert float(e_k.pow(2).mean().sqrt()) <= EMU_MARGIN * float(e_emu.pow(2).mean().sqrt()) + 1e-6, \
+        f"rms d {float(e_k.pow(2).mean().sqrt())} against the emulation's {float(e_emu.pow(2).mean().sqrt())}"
+    cd_k, cd_e = orc.cos_diff(out_kernel.cpu(), ref_out), orc.cos_diff(emu_out, ref_out)
+    assert cd_k <= EMU_MARGIN ** 2 * cd_e + 1e-5, f"1 - cos {cd_k} against the emulation's {cd_e}"
+    k = lse2_to_nat(lse2_kernel.cpu())
+    r = ref_lse.double()
+    empty = torch.isinf(r) & (r < 0)
+    assert torch.equal(empty, torch.isinf(k) & (k < 0)), "rows without a valid entry differ"
+    if (~empty).any():
+        d_k = float((k - r)[~empty].abs().max())
+        d_e = float((emu_lse.double() - r)[~empty].abs().max())
+        assert d_k <= EMU_MARGIN * d_e + 2e-3, f"LSE error {d_k} against the emulation's {d_e}"

@@ -52,10 +52,19 @@ def _prefill(case, impl, topk_length=None, attn_sink=None):
     return out.cpu(), mx.cpu(), lse.cpu()
 
 
-def _check(out, lse2, ref_out, ref_lse, impl, prefill=False, noise=1.0):
+def _check(out, lse2, ref_out, ref_lse, impl, prefill=False):
     a, r, c, l = _tols(impl, prefill)
-    H.compare_out(out, ref_out, a, r, c, noise)
-    H.compare_lse(lse2, ref_lse, l * noise)
+    H.compare_out(out, ref_out, a, r, c)
+    H.compare_lse(lse2, ref_lse, l)
+
+
+def _check_hard(out, lse2, ref_out, ref_lse, impl, case, topk_length=None):
+    """Inputs on which the FP8 roundings cost more than on benchmark-like data: the exact kernel keeps its
+    bound, the tensor-core kernels are held to what the emulated numerics cost on the same inputs."""
+    if impl == SCALAR:
+        _check(out, lse2, ref_out, ref_lse, impl)
+    else:
+        H.check_against_emulation(out, lse2, case, ref_out, ref_lse, topk_length=topk_length)
 
 
 # ------------------------------------------------------------------ golden fixtures
@@ -115,14 +124,24 @@ def test_scale_spread_rows(impl):
     case["packed"] = orc.quantize_kv_v32(kv.to(torch.bfloat16))
     ref_out, ref_lse = oracle_attn(case)
     out, lse = _decode(case, impl)
-    _check(out, lse, ref_out, ref_lse, impl, noise=1.5)   # values span 2^9 between tiles: single outliers at 1.2x the bound
+    _check_hard(out, lse, ref_out, ref_lse, impl, case)
+    if impl != SCALAR:
+        # every 128-dim output tile against ITS OWN magnitude (the 8x tile would otherwise hide the 1/64 and
+        # 1e-3 tiles): the re-expression against the largest scale must not cost a small tile its precision
+        emu_out, _ = orc.emulate_fp8_attention(case["q"], case["packed"], case["indices"], case["sm_scale"])
+        for c in range(4):
+            sl = slice(128 * c, 128 * c + 128)
+            e_k = (out.cpu().float()[..., sl] - ref_out.float()[..., sl]).pow(2).mean().sqrt()
+            e_e = (emu_out.float()[..., sl] - ref_out.float()[..., sl]).pow(2).mean().sqrt()
+            rms = ref_out.float()[..., sl].pow(2).mean().sqrt()
+            assert float(e_k) <= H.EMU_MARGIN * float(e_e) + 2.0 ** -8 * float(rms), (c, float(e_k), float(e_e), float(rms))
 
 
 @pytest.mark.parametrize("impl", [SCALAR, TC, TC_PAIR])
 def test_peaked_attention_and_rescale(impl):
     """Logits that keep growing along the index list force accumulator rescales; a few dominant
     keys make the distribution peaked.  With logits of +-6 the e4m3 rounding of Q alone moves
-    single weights by 10-15 %, so the FP8 kernel gets twice the usual noise allowance here."""
+    single weights by 10-15 %: the FP8 kernels are held to the emulated numerics on the same inputs."""
     case = make_case(5, 2, 64, 512, 16, kv_std=1.0, q_std=1.5, invalid_tail=0.0)
     deq = orc.dequantize_kv_v32(case["packed"]).reshape(-1, 576).float()
     # order each request's indices by ascending logit of head 0, so the maximum rises to the end
@@ -131,7 +150,7 @@ def test_peaked_attention_and_rescale(impl):
         case["indices"][t] = case["indices"][t][torch.argsort(s)]
     ref_out, ref_lse = oracle_attn(case)
     out, lse = _decode(case, impl, num_sm_parts=2)
-    _check(out, lse, ref_out, ref_lse, impl, noise=2.0)
+    _check_hard(out, lse, ref_out, ref_lse, impl, case)
 
 
 @pytest.mark.parametrize("impl", [SCALAR, TC, TC_PAIR])
@@ -265,8 +284,42 @@ def test_many_tokens_per_cta(impl):
     tl[::7] = 64          # some tokens with one tile, so that tile ownership flips between tokens
     tl[3::11] = 0         # and some with none
     ref_out, ref_lse = oracle_attn(case, topk_length=tl)
-    # 13 M outputs, many of them averages over 64 tokens only: the noise term of the bound (a 6-sigma figure) gets 1.5x
+    # 13 M outputs, many of them averages over 64 tokens only
     out, mx, lse = _prefill(case, impl, topk_length=tl)
-    _check(out, lse, ref_out, ref_lse, impl, prefill=True, noise=1.5)
+    _check_hard(out, lse, ref_out, ref_lse, impl, case, topk_length=tl)
     out, lse = _decode(case, impl, num_sm_parts=200, topk_length=tl)     # the unsplit decode path takes the same route
-    _check(out, lse, ref_out, ref_lse, impl, noise=1.5)
+    _check_hard(out, lse, ref_out, ref_lse, impl, case, topk_length=tl)
+
+
+@pytest.mark.parametrize("impl", [TC, TC_PAIR])
+@pytest.mark.parametrize("magnitude", [0.1, 0.5, 1.0, 2.0, 5.0])
+def test_precision_vs_magnitude(impl, magnitude):
+    """The reference's magnitude sweep for the 656-byte layout (tests/test_precision_magnitude.py:201-232):
+    q and kv are randn x magnitude, 128 heads, top-k 2048; mean |error| / mean |reference| must stay below
+    10 %, for decode (2 requests) and prefill (4 tokens)."""
+    g = torch.Generator().manual_seed(42)
+    kv = (torch.randn(64, 64, 1, 576, generator=g) * magnitude).to(torch.bfloat16)
+    packed = orc.quantize_kv_v32(kv)
+    q = (torch.randn(4, 128, 576, generator=g) * magnitude).to(torch.bfloat16)
+    idx = torch.randint(0, 64 * 64, (4, 2048), generator=g, dtype=torch.int32)
+    case = {"packed": packed, "q": q, "indices": idx, "sm_scale": 576 ** -0.5}
+    ref_out, _ = oracle_attn(case)
+    out_p, _, _ = _prefill(case, impl)
+    two = {"packed": packed, "q": q[:2].contiguous(), "indices": idx[:2].contiguous(), "sm_scale": case["sm_scale"]}
+    out_d, _ = _decode(two, impl)
+    for name, o, r in (("prefill", out_p, ref_out), ("decode", out_d, ref_out[:2])):
+        rel = float((o.cpu().float() - r.float()).abs().mean()) / float(r.float().abs().mean())
+        assert rel < 0.10, f"{name}: relative error {rel:.3%} at magnitude {magnitude}"
+
+
+@pytest.mark.parametrize("impl", [SCALAR, TC, TC_PAIR])
+@pytest.mark.parametrize("topk", [1, 100, 257])
+def test_topk_not_a_multiple_of_the_block(impl, topk):
+    """Index lists of any length: the last block of a list is partly filled."""
+    case = make_case(61, 3, 128, topk, 8, invalid_tail=0.0)
+    ref_out, ref_lse = oracle_attn(case)
+    for parts in (None, 2):
+        out, lse = _decode(case, impl, num_sm_parts=parts)
+        _check(out, lse, ref_out, ref_lse, impl)
+    out, mx, lse = _prefill(case, impl)
+    _check(out, lse, ref_out, ref_lse, impl, prefill=True)

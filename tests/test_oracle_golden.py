@@ -60,3 +60,23 @@ def test_topk_length_masks_tail():
     idx2[0, 40:] = -1
     out2, lse2 = orc.ref_sparse_attn(c["q"].unsqueeze(1), deq, idx2.unsqueeze(1), c["sm_scale"], 512)
     assert torch.equal(out, out2) and torch.equal(lse, lse2)
+
+
+def test_fp8_emulation_distance():
+    """The numbers the tensor-core tolerances of helpers.py are derived from: distance of the emulated FP8-class
+    numerics to the fp32 oracle on reference-grid and benchmark-like data."""
+    import helpers as H
+    case = H.make_case(2, 2, 128, 1024, 32, kv_std=0.1, q_std=0.1, clamp=1.0)
+    ref_out, ref_lse = H.oracle_attn(case)
+    emu_out, emu_lse = orc.emulate_fp8_attention(case["q"], case["packed"], case["indices"], case["sm_scale"])
+    assert float((emu_out.float() - ref_out.float()).abs().max()) < 1e-3          # the reference's bar on its own data
+    case = H.make_case(4, 3, 64, 512, 32, kv_std=1.0, q_std=0.5)
+    ref_out, ref_lse = H.oracle_attn(case)
+    emu_out, emu_lse = orc.emulate_fp8_attention(case["q"], case["packed"], case["indices"], case["sm_scale"])
+    H.compare_out(emu_out, ref_out, H.TC_ABS, H.TC_REL, H.TC_COS)                 # the emulation sits inside the kernel bounds
+    fin = torch.isfinite(ref_lse)
+    assert float((emu_lse[fin] - ref_lse[fin]).abs().max()) < H.TC_LSE
+    d = (emu_out.float() - ref_out.float()).abs()
+    rms = float(ref_out.float().pow(2).mean().sqrt())
+    excess = float((d - (H.TC_ABS + H.TC_REL * torch.maximum(emu_out.float().abs(), ref_out.float().abs()))).max()) / rms
+    assert 0.03 < excess < H.TC_NOISE / 1.3, excess                               # TC_NOISE keeps >= 1.3 x margin over it
