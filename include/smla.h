@@ -47,6 +47,23 @@ enum {
     SMLA_IMPL_TC_PAIR = 3  /* the same numerics with the score work shared inside a two-CTA cluster (experimental) */
 };
 
+/*
+ * Cache layouts (csrc/model/kv_cache_traits.cuh:16-59 and :61-111).
+ *   V32     656 bytes per token, scales inline: 512 e4m3 | 4 fp32 scales | 64 bf16; q has 576 dims,
+ *           V is the 512 dequantised values.
+ *   MODEL1  584 bytes per token, scales in a footer: a page of `page_block_size` tokens is
+ *           page_block_size x 576 data bytes (448 e4m3 | 64 bf16 per token) followed by
+ *           page_block_size x 8 footer bytes (7 UE8M0 scales, one per 64 values, + 1 pad);
+ *           q has 512 dims, V is the whole dequantised row (448 values + the 64 bf16).
+ */
+enum {
+    SMLA_LAYOUT_V32 = 0,
+    SMLA_LAYOUT_MODEL1 = 1
+};
+#define SMLA_M1_D_QK 512
+#define SMLA_M1_ROW_BYTES 584
+#define SMLA_M1_DATA_BYTES 576
+
 const char* smla_last_error(void);
 int smla_version(void);
 
@@ -76,8 +93,8 @@ int smla_sched_meta(int b, int topk, int extra_topk, int num_sm_parts, int fixed
  *   out        [num_tokens, num_heads, 512] bf16 (written directly for unsplit requests)
  *   out_lse    [num_tokens, num_heads] fp32, base-2 LSE of the scaled logits, -1e30 when empty
  *   attn_sink  [num_heads] fp32 natural-log sink logit or NULL; topk_length [num_tokens] or NULL
- * num_heads in 1..128; topk a multiple of 64.  status (device int32[4], may be NULL) receives a
- * non-zero code when a bounded wait inside the tcgen05 kernel gave up.
+ * num_heads in 1..128; topk >= 1 (a last block that is partly filled is masked).  status (device
+ * int32[4], may be NULL) receives a non-zero code when a bounded wait inside the tcgen05 kernel gave up.
  */
 int smla_decode_splitkv(const void* q, const void* kv, const int32_t* indices,
                         float* o_accum, float* lse_accum, void* out, float* out_lse,
@@ -108,6 +125,35 @@ int smla_prefill(const void* q, const void* kv, const int32_t* indices,
                  int page_block_size, int64_t kv_block_stride_bytes,
                  const float* attn_sink, const int32_t* topk_length,
                  int impl, int32_t* status, void* stream);
+
+/*
+ * The two calls above with everything the reference's entry points take besides
+ * (csrc/binding.cpp:96-164 and :185-247, kernel arguments csrc/kernel/decode/decode_v2_kernel.cuh:40-66):
+ * the cache layout, and a second ("extra") cache with its own page size, index array
+ * [num_tokens, extra_topk] and lengths.  A request walks max(ceil(topk_length/64), 1) blocks of the main
+ * cache, then ceil(extra_topk_length/64) blocks of the extra cache (decode_v2_kernel.cuh:109-115); one
+ * softmax runs over both.  For SMLA_LAYOUT_MODEL1 q is [num_tokens, num_heads, 512].  extra_kv NULL and
+ * extra_topk 0 = no second cache; the scheduler must have been given the same extra_topk and
+ * extra_topk_length.  These calls run the exact fp32 kernel (SMLA_IMPL_SCALAR); the tcgen05 kernels serve
+ * SMLA_LAYOUT_V32 without a second cache through smla_decode_splitkv / smla_prefill.
+ */
+int smla_decode_splitkv_ext(const void* q, const void* kv, const int32_t* indices,
+                            const void* extra_kv, const int32_t* extra_indices,
+                            float* o_accum, float* lse_accum, void* out, float* out_lse,
+                            const int32_t* sched_meta, const int32_t* num_splits,
+                            int num_tokens, int num_heads, int topk, int extra_topk, float sm_scale, int layout,
+                            int page_block_size, int64_t kv_block_stride_bytes,
+                            int extra_page_block_size, int64_t extra_block_stride_bytes, int num_sm_parts,
+                            const float* attn_sink, const int32_t* topk_length, const int32_t* extra_topk_length,
+                            int32_t* status, void* stream);
+int smla_prefill_ext(const void* q, const void* kv, const int32_t* indices,
+                     const void* extra_kv, const int32_t* extra_indices,
+                     void* out, float* out_lse, float* out_max_logits,
+                     int num_tokens, int num_heads, int topk, int extra_topk, float sm_scale, int layout,
+                     int page_block_size, int64_t kv_block_stride_bytes,
+                     int extra_page_block_size, int64_t extra_block_stride_bytes,
+                     const float* attn_sink, const int32_t* topk_length, const int32_t* extra_topk_length,
+                     int32_t* status, void* stream);
 
 /*
  * bf16 -> packed 656-byte rows (the writer of the cache format).  No kernel of the reference

@@ -80,6 +80,54 @@ def dequantize_kv_v32(packed: torch.Tensor) -> torch.Tensor:
     return out.view(nb, bs, 1, D_QK)
 
 
+# --------------------------------------------------------------------------- MODEL1 row format
+M1_D_NOPE = 448
+M1_D_QK = 512
+M1_TILE = 64
+M1_NUM_TILES = 7
+M1_DATA_BYTES = M1_D_NOPE + D_ROPE * 2     # 576: e4m3 values + bf16 RoPE of one token
+M1_SCALE_BYTES = 8                         # 7 UE8M0 scales + 1 pad
+M1_ROW_BYTES = M1_DATA_BYTES + M1_SCALE_BYTES  # 584 logical bytes per token
+
+
+def quantize_kv_model1(kv_bf16: torch.Tensor) -> torch.Tensor:
+    """bf16 [num_blocks, block, 1, 512] -> uint8 [num_blocks, block, 1, 584], footer-ordered.
+
+    The bytes of a page are NOT token-major: first block x 576 data bytes (per token 448 e4m3 |
+    64 bf16 RoPE), then block x 8 footer bytes (per token 7 UE8M0 exponents, one per 64 values, and a
+    pad byte).  Follows tests/test_decode.py:76-116."""
+    nb, bs, hk, d = kv_bf16.shape
+    assert d == M1_D_QK and hk == 1
+    kv = kv_bf16.squeeze(2)
+    tiles = kv[..., :M1_D_NOPE].float().reshape(nb, bs, M1_NUM_TILES, M1_TILE)
+    scale = pow2_scale(tiles.abs().amax(dim=-1).clamp(min=1e-4) / 448.0)          # [nb, bs, 7]
+    fp8 = (tiles / scale.unsqueeze(-1)).clamp(-448, 448).to(torch.float8_e4m3fn)
+    data = torch.zeros(nb, bs, M1_DATA_BYTES, dtype=torch.uint8)
+    data[..., :M1_D_NOPE] = fp8.view(torch.uint8).reshape(nb, bs, M1_D_NOPE)
+    data[..., M1_D_NOPE:] = kv[..., M1_D_NOPE:].to(torch.bfloat16).contiguous().view(torch.uint8).reshape(nb, bs, D_ROPE * 2)
+    footer = torch.zeros(nb, bs, M1_SCALE_BYTES, dtype=torch.uint8)
+    footer[..., :M1_NUM_TILES] = ((scale.to(torch.float32).contiguous().view(torch.int32) >> 23) & 0xFF).to(torch.uint8)
+    page = torch.cat([data.reshape(nb, bs * M1_DATA_BYTES), footer.reshape(nb, bs * M1_SCALE_BYTES)], dim=1)
+    return page.contiguous().view(nb, bs, 1, M1_ROW_BYTES)
+
+
+def dequantize_kv_model1(packed: torch.Tensor) -> torch.Tensor:
+    """uint8 [num_blocks, block, 1, 584] (footer-ordered pages) -> bf16 [num_blocks, block, 1, 512].
+
+    value = bf16(e4m3 * 2^(ue8m0 - 127)); RoPE verbatim.  Follows tests/test_decode.py:119-147."""
+    nb, bs, hk, bpt = packed.shape
+    assert bpt == M1_ROW_BYTES and hk == 1
+    page = packed.reshape(nb, bs * bpt)
+    data = page[:, :bs * M1_DATA_BYTES].reshape(nb, bs, M1_DATA_BYTES)
+    footer = page[:, bs * M1_DATA_BYTES:].reshape(nb, bs, M1_SCALE_BYTES)
+    fp8 = data[..., :M1_D_NOPE].contiguous().view(torch.float8_e4m3fn).float().reshape(nb, bs, M1_NUM_TILES, M1_TILE)
+    scale = torch.pow(2.0, footer[..., :M1_NUM_TILES].float() - 127.0)
+    out = torch.zeros(nb, bs, M1_D_QK, dtype=torch.bfloat16)
+    out[..., :M1_D_NOPE] = (fp8 * scale.unsqueeze(-1)).to(torch.bfloat16).reshape(nb, bs, M1_D_NOPE)
+    out[..., M1_D_NOPE:] = data[..., M1_D_NOPE:].contiguous().view(torch.bfloat16).reshape(nb, bs, D_ROPE)
+    return out.view(nb, bs, 1, M1_D_QK)
+
+
 # --------------------------------------------------------------------------- attention
 def ref_sparse_attn(q: torch.Tensor, kv_dequant: torch.Tensor, indices: torch.Tensor,
                     sm_scale: float, d_v: int = D_V,
@@ -115,6 +163,46 @@ def ref_sparse_attn(q: torch.Tensor, kv_dequant: torch.Tensor, indices: torch.Te
     vals = gathered[..., :d_v].clone()
     vals[invalid.unsqueeze(-1).expand_as(vals)] = 0.0
     out = torch.einsum("bsht,bstd->bshd", weights, vals)
+    return out.to(torch.bfloat16), lse
+
+
+def ref_sparse_attn_dual(q: torch.Tensor, kv_dequant: torch.Tensor, indices: torch.Tensor, sm_scale: float,
+                         d_v: int = D_V, topk_length: Optional[torch.Tensor] = None,
+                         extra_kv_dequant: Optional[torch.Tensor] = None,
+                         extra_indices: Optional[torch.Tensor] = None,
+                         extra_topk_length: Optional[torch.Tensor] = None,
+                         attn_sink: Optional[torch.Tensor] = None) -> Tuple[torch.Tensor, torch.Tensor]:
+    """Sparse attention over the rows of a main cache and, optionally, of a second cache, fp32.
+
+    q [b, s_q, h, d_qk] bf16; the rows named by ``indices`` [b, s_q, topk] (masked past ``topk_length``
+    [b]) and by ``extra_indices`` [b, s_q, extra_topk] (masked past ``extra_topk_length`` [b]) enter ONE
+    softmax; V is the first d_v values of a row.  ``attn_sink`` [h] (natural-log logit, +-inf allowed)
+    scales the output by 1 / (1 + exp(sink - lse)) BEFORE the rounding to bf16; the returned LSE does not
+    include the sink.  A row without any valid entry gives output 0 and LSE -inf.
+    Follows tests/test_v4_features.py:50-101 (ref_v4_decode)."""
+    b, s_q, h_q, d_qk = q.shape
+
+    def scope(kv, idx, length):
+        n = idx.shape[-1]
+        bad = idx < 0
+        if length is not None:
+            bad = bad | (torch.arange(n).view(1, 1, n) >= length.view(b, 1, 1))
+        rows = kv.reshape(-1, d_qk).float().index_select(0, idx.clamp(min=0).reshape(-1).long())
+        return rows.view(b, s_q, n, d_qk), bad
+
+    gathered, invalid = scope(kv_dequant, indices, topk_length)
+    if extra_kv_dequant is not None and extra_indices is not None:
+        g2, i2 = scope(extra_kv_dequant, extra_indices, extra_topk_length)
+        gathered, invalid = torch.cat([gathered, g2], dim=2), torch.cat([invalid, i2], dim=2)
+    gathered = torch.nan_to_num(gathered, nan=0.0, posinf=float("inf"), neginf=float("-inf"))
+    P = torch.einsum("bshd,bstd->bsht", q.float(), gathered) * sm_scale
+    P[invalid.unsqueeze(2).expand_as(P)] = float("-inf")
+    lse = torch.logsumexp(P, dim=-1)
+    lse_safe = lse.masked_fill(lse == float("-inf"), float("inf"))
+    out = torch.einsum("bsht,bstd->bshd", torch.exp(P - lse_safe.unsqueeze(-1)), gathered[..., :d_v])
+    if attn_sink is not None:
+        out = out * (1.0 / (1.0 + torch.exp(attn_sink.view(1, 1, h_q).float() - lse))).unsqueeze(-1)
+    out[(lse == float("-inf")).unsqueeze(-1).expand_as(out)] = 0.0
     return out.to(torch.bfloat16), lse
 
 

@@ -9,6 +9,7 @@ from ctypes import c_char_p, c_float, c_int, c_int32, c_int64, c_size_t, c_void_
 from .build import LIB_PATH
 
 IMPL_AUTO, IMPL_SCALAR, IMPL_TC, IMPL_TC_PAIR = 0, 1, 2, 3
+LAYOUT_V32, LAYOUT_MODEL1 = 0, 1
 
 _lib = None
 
@@ -38,6 +39,10 @@ _SIGS = {
     "smla_combine": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p]),
     "smla_prefill": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
                              c_float, c_int, c_int64, c_void_p, c_void_p, c_int, c_void_p, c_void_p]),
+    "smla_decode_splitkv_ext": (c_int, [c_void_p] * 11 + [c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_int64,
+                                                          c_int, c_int64, c_int] + [c_void_p] * 5),
+    "smla_prefill_ext": (c_int, [c_void_p] * 8 + [c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_int64, c_int,
+                                                  c_int64] + [c_void_p] * 5),
     "smla_pack_kv": (c_int, [c_void_p, c_void_p, c_int64, c_void_p]),
     "smla_mqa_logits": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                 c_int, c_int, c_int, c_int64, c_int, c_void_p, c_void_p]),

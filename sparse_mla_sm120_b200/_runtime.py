@@ -37,25 +37,36 @@ def require_cuda(*tensors: Optional[torch.Tensor]) -> None:
             raise ValueError("sparse_mla_sm120_b200 runs on CUDA tensors only (there is no CPU path)")
 
 
+def kv_layout(kv_cache: torch.Tensor) -> int:
+    """LAYOUT_V32 for 656-byte rows, LAYOUT_MODEL1 for 584-byte rows."""
+    if kv_cache.dtype not in (torch.uint8, torch.int8, torch.float8_e4m3fn):
+        raise ValueError(f"kv_cache must be a byte tensor, got {kv_cache.dtype}")
+    row = kv_cache.shape[-1]
+    if row == 656:
+        return _lib.LAYOUT_V32
+    if row == 584:
+        return _lib.LAYOUT_MODEL1
+    raise ValueError(f"kv_cache rows must be 656 bytes (V32) or 584 bytes (MODEL1), got {row}")
+
+
 def kv_geometry(kv_cache: torch.Tensor) -> Tuple[int, int]:
     """(page_block_size, bytes between pages) of a packed cache tensor.
 
-    Accepts [num_blocks, block, 1, 656], the legacy flat [pool, 1, 656] and [pool, 656].  A page
-    stride larger than block*656 (a padded allocation) is honoured; the reference computes the
-    same quantity in flash_mla_sm120/ops.py:23-45 but its V32 gather then ignores it."""
-    if kv_cache.dtype not in (torch.uint8, torch.int8, torch.float8_e4m3fn):
-        raise ValueError(f"kv_cache must be a byte tensor, got {kv_cache.dtype}")
-    if kv_cache.shape[-1] != 656:
-        if kv_cache.shape[-1] == 584:
-            raise NotImplementedError("the 584-byte (MODEL1) cache layout is not built")
-        raise ValueError(f"kv_cache rows must be 656 bytes, got {kv_cache.shape[-1]}")
+    V32 (656-byte rows): accepts [num_blocks, block, 1, 656], the legacy flat [pool, 1, 656] and
+    [pool, 656].  MODEL1 (584 bytes per token, scales in a footer of the page): [num_blocks, block, 1, 584]
+    only, since the position of the footer depends on the page size.  A page stride larger than
+    block * row (a padded allocation) is honoured; flash_mla_sm120/ops.py:23-45 computes the same quantity."""
+    layout = kv_layout(kv_cache)
+    row = kv_cache.shape[-1]
     if kv_cache.stride(-1) != 1:
         raise ValueError("kv_cache rows must be contiguous")
     if kv_cache.dim() == 4:
         block = kv_cache.shape[1]
-        if kv_cache.shape[2] != 1 or kv_cache.stride(1) != 656:
-            raise ValueError("kv_cache must be [num_blocks, block, 1, 656] with 656-byte rows")
+        if kv_cache.shape[2] != 1 or kv_cache.stride(1) != row:
+            raise ValueError(f"kv_cache must be [num_blocks, block, 1, {row}] with {row}-byte rows")
         return block, kv_cache.stride(0)
+    if layout != _lib.LAYOUT_V32:
+        raise ValueError("a MODEL1 cache must be [num_blocks, block, 1, 584]")
     if kv_cache.dim() == 3:
         if kv_cache.shape[1] != 1 or kv_cache.stride(0) != 656:
             raise ValueError("kv_cache must be [pool, 1, 656] with 656-byte rows")
@@ -67,6 +78,15 @@ def kv_geometry(kv_cache: torch.Tensor) -> Tuple[int, int]:
         pool = max(kv_cache.shape[0], 1)
         return pool, pool * 656
     raise ValueError(f"unsupported kv_cache rank {kv_cache.dim()}")
+
+
+def pick_num_sm_parts_fp32(num_tokens: int, num_heads: int, sms: int) -> int:
+    """Partitions for the fp32 kernel, which runs ceil(heads / 8) CTAs per partition: requests stay
+    whole when they already give two CTAs per SM, otherwise the work is cut so that they do."""
+    tiles = -(-num_heads // 8)
+    if num_tokens * tiles >= 2 * sms:
+        return num_tokens
+    return max(2 * sms // tiles, 1)
 
 
 def pick_num_sm_parts(num_tokens: int, sms: int) -> int:

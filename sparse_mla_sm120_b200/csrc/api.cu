@@ -232,6 +232,93 @@ int smla_prefill(const void* q, const void* kv, const int32_t* indices,
     return launch_attn_tc(p, (cudaStream_t)stream);
 }
 
+static int check_ext(const char* fn, const void* q, const void* kv, const int32_t* indices, const void* extra_kv,
+                     const int32_t* extra_indices, const void* out, const float* out_lse, int num_tokens, int num_heads,
+                     int topk, int extra_topk, int layout, int page_block_size, int64_t stride,
+                     int extra_page_block_size, int64_t extra_stride) {
+    if (layout != SMLA_LAYOUT_V32 && layout != SMLA_LAYOUT_MODEL1)
+        return set_error(SMLA_E_SHAPE, "%s: unknown cache layout %d", fn, layout);
+    const int row = (layout == SMLA_LAYOUT_MODEL1) ? SMLA_M1_ROW_BYTES : ROW_BYTES;
+    if (!q || !kv || !indices || !out || !out_lse) return set_error(SMLA_E_NULL, "%s: null pointer argument", fn);
+    if (num_tokens < 0) return set_error(SMLA_E_SHAPE, "%s: num_tokens=%d", fn, num_tokens);
+    if (num_heads < 1 || num_heads > 128)
+        return set_error(SMLA_E_SHAPE, "%s: num_heads=%d, supported 1..128", fn, num_heads);
+    if (topk < 1 || extra_topk < 0) return set_error(SMLA_E_SHAPE, "%s: topk=%d extra_topk=%d", fn, topk, extra_topk);
+    if (page_block_size < 1) return set_error(SMLA_E_SHAPE, "%s: page_block_size=%d", fn, page_block_size);
+    if (!aligned16(q) || !aligned16(out)) return set_error(SMLA_E_ALIGN, "%s: q and out must be 16-byte aligned", fn);
+    if ((reinterpret_cast<uintptr_t>(kv) & 3u) || (stride & 3))
+        return set_error(SMLA_E_ALIGN, "%s: kv and the page stride must be 4-byte aligned", fn);
+    if (stride < (int64_t)page_block_size * row)
+        return set_error(SMLA_E_SHAPE, "%s: page stride %lld smaller than %d rows of %d bytes", fn, (long long)stride,
+                         page_block_size, row);
+    if (extra_topk > 0) {
+        if (!extra_kv || !extra_indices) return set_error(SMLA_E_NULL, "%s: extra_topk=%d without an extra cache or indices", fn, extra_topk);
+        if (extra_page_block_size < 1 || extra_stride < (int64_t)extra_page_block_size * row)
+            return set_error(SMLA_E_SHAPE, "%s: extra page of %d rows with stride %lld", fn, extra_page_block_size,
+                             (long long)extra_stride);
+        if ((reinterpret_cast<uintptr_t>(extra_kv) & 3u) || (extra_stride & 3))
+            return set_error(SMLA_E_ALIGN, "%s: extra_kv and its page stride must be 4-byte aligned", fn);
+    }
+    return 0;
+}
+
+int smla_decode_splitkv_ext(const void* q, const void* kv, const int32_t* indices,
+                            const void* extra_kv, const int32_t* extra_indices,
+                            float* o_accum, float* lse_accum, void* out, float* out_lse,
+                            const int32_t* sched_meta, const int32_t* num_splits,
+                            int num_tokens, int num_heads, int topk, int extra_topk, float sm_scale, int layout,
+                            int page_block_size, int64_t kv_block_stride_bytes,
+                            int extra_page_block_size, int64_t extra_block_stride_bytes, int num_sm_parts,
+                            const float* attn_sink, const int32_t* topk_length, const int32_t* extra_topk_length,
+                            int32_t* status, void* stream) {
+    if (int e = check_ext("smla_decode_splitkv_ext", q, kv, indices, extra_kv, extra_indices, out, out_lse, num_tokens,
+                          num_heads, topk, extra_topk, layout, page_block_size, kv_block_stride_bytes,
+                          extra_page_block_size, extra_block_stride_bytes)) return e;
+    if (!o_accum || !lse_accum || !sched_meta || !num_splits)
+        return set_error(SMLA_E_NULL, "smla_decode_splitkv_ext: null scratch or scheduler pointer");
+    if (num_sm_parts < 1) return set_error(SMLA_E_SHAPE, "smla_decode_splitkv_ext: num_sm_parts=%d", num_sm_parts);
+    AttnParams p{};
+    p.q = (const __nv_bfloat16*)q; p.kv = (const uint8_t*)kv; p.indices = indices;
+    p.o_accum = o_accum; p.lse_accum = lse_accum; p.out = (__nv_bfloat16*)out; p.out_lse = out_lse;
+    p.sched = (const SchedMeta*)sched_meta; p.num_splits = num_splits;
+    p.attn_sink = attn_sink; p.topk_length = topk_length; p.status = status;
+    p.num_tokens = num_tokens; p.num_heads = num_heads; p.topk = topk; p.num_parts = num_sm_parts;
+    p.page_block_size = page_block_size; p.block_stride = kv_block_stride_bytes; p.sm_scale = sm_scale;
+    p.layout = layout;
+    if (extra_topk > 0) {
+        p.extra_kv = (const uint8_t*)extra_kv; p.extra_indices = extra_indices; p.extra_topk_length = extra_topk_length;
+        p.extra_topk = extra_topk; p.extra_page_block_size = extra_page_block_size;
+        p.extra_block_stride = extra_block_stride_bytes;
+    }
+    return launch_attn_scalar(p, (cudaStream_t)stream);
+}
+
+int smla_prefill_ext(const void* q, const void* kv, const int32_t* indices,
+                     const void* extra_kv, const int32_t* extra_indices,
+                     void* out, float* out_lse, float* out_max_logits,
+                     int num_tokens, int num_heads, int topk, int extra_topk, float sm_scale, int layout,
+                     int page_block_size, int64_t kv_block_stride_bytes,
+                     int extra_page_block_size, int64_t extra_block_stride_bytes,
+                     const float* attn_sink, const int32_t* topk_length, const int32_t* extra_topk_length,
+                     int32_t* status, void* stream) {
+    if (int e = check_ext("smla_prefill_ext", q, kv, indices, extra_kv, extra_indices, out, out_lse, num_tokens,
+                          num_heads, topk, extra_topk, layout, page_block_size, kv_block_stride_bytes,
+                          extra_page_block_size, extra_block_stride_bytes)) return e;
+    AttnParams p{};
+    p.q = (const __nv_bfloat16*)q; p.kv = (const uint8_t*)kv; p.indices = indices;
+    p.out = (__nv_bfloat16*)out; p.out_lse = out_lse; p.out_max_logits = out_max_logits;
+    p.attn_sink = attn_sink; p.topk_length = topk_length; p.status = status;
+    p.num_tokens = num_tokens; p.num_heads = num_heads; p.topk = topk; p.num_parts = num_tokens;
+    p.page_block_size = page_block_size; p.block_stride = kv_block_stride_bytes; p.sm_scale = sm_scale;
+    p.layout = layout;
+    if (extra_topk > 0) {
+        p.extra_kv = (const uint8_t*)extra_kv; p.extra_indices = extra_indices; p.extra_topk_length = extra_topk_length;
+        p.extra_topk = extra_topk; p.extra_page_block_size = extra_page_block_size;
+        p.extra_block_stride = extra_block_stride_bytes;
+    }
+    return launch_attn_scalar(p, (cudaStream_t)stream);
+}
+
 int smla_pack_kv(const void* kv_bf16, void* packed, int64_t num_rows, void* stream) {
     if (!kv_bf16 || !packed) return set_error(SMLA_E_NULL, "smla_pack_kv: null pointer argument");
     if (num_rows < 0) return set_error(SMLA_E_SHAPE, "smla_pack_kv: num_rows=%lld", (long long)num_rows);

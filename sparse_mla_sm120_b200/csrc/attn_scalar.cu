@@ -11,6 +11,16 @@
 // One CTA = (8 heads, one scheduler partition).  Per 64-token block it walks 8 sub-tiles of
 // 8 tokens: dequantise 8 rows to shared memory, 64 dot products of length 576 (4 threads each),
 // online softmax per head, then P.V with one thread per (head, 16 output dims).
+//
+// It is also the kernel that serves the second cache layout and the second ("extra") cache:
+//  * layout MODEL1 (csrc/model/kv_cache_traits.cuh:61-111): a page of `block` tokens is
+//    block x 576 data bytes (448 e4m3 + 64 bf16 RoPE per token) followed by a footer of
+//    block x 8 bytes (7 UE8M0 scales, one per 64 values, + 1 pad); q has 512 dims and V is the
+//    whole dequantised row, RoPE included.
+//  * extra cache (decode_v2_kernel.cuh:109-115, 147-160, 351-361): after the
+//    max(ceil(topk_length/64),1) blocks of the main cache a request walks
+//    ceil(extra_topk_length/64) blocks whose rows come from a second cache through a second
+//    index array; the softmax runs over both.
 #include "common.cuh"
 
 namespace smla {
@@ -22,7 +32,42 @@ constexpr int ST = 8;        // tokens per sub-tile
 constexpr int THREADS = 256;
 constexpr int KPAD = D_QK + 1;
 
+constexpr int M1_NOPE = 448;       // MODEL1: e4m3 values per row
+constexpr int M1_DATA = 576;       // MODEL1: data bytes per token (448 + 64 bf16)
+constexpr int M1_SCALE_BYTES = 8;  // MODEL1: footer bytes per token
+
+// Dequantise one gathered row into `dst` (fp32), one warp per row.  The reference rounds the
+// dequantised value to bf16 (tests/test_decode.py:66-69, :139-141), exact for power-of-two scales.
+template <int LAYOUT>
+__device__ __forceinline__ void load_row(float* dst, const uint8_t* kv, int idx, int page_block_size,
+                                         int64_t block_stride, int lane) {
+    if (LAYOUT == SMLA_LAYOUT_V32) {
+        const uint8_t* row = kv_row_ptr(kv, idx, page_block_size, block_stride);
+        const float* sc = reinterpret_cast<const float*>(row + SCALE_OFF);
+        for (int d = lane; d < D_NOPE; d += 32)
+            dst[d] = __bfloat162float(__float2bfloat16(e4m3_to_float(row[d]) * sc[d >> 7]));
+        const __nv_bfloat16* rope = reinterpret_cast<const __nv_bfloat16*>(row + ROPE_OFF);
+        for (int d = lane; d < D_ROPE; d += 32) dst[D_NOPE + d] = __bfloat162float(rope[d]);
+    } else {
+        const unsigned u = (unsigned)idx;
+        const unsigned blk = u / (unsigned)page_block_size;
+        const unsigned in = u - blk * (unsigned)page_block_size;
+        const uint8_t* page = kv + (int64_t)blk * block_stride;
+        const uint8_t* row = page + (int64_t)in * M1_DATA;
+        const uint8_t* sc = page + (int64_t)page_block_size * M1_DATA + (int64_t)in * M1_SCALE_BYTES;
+        for (int d = lane; d < M1_NOPE; d += 32) {
+            const uint32_t e = sc[d >> 6];                       // UE8M0: 2^(e-127)
+            const float scale = __uint_as_float(e ? (e << 23) : 0x00400000u);
+            dst[d] = __bfloat162float(__float2bfloat16(e4m3_to_float(row[d]) * scale));
+        }
+        const __nv_bfloat16* rope = reinterpret_cast<const __nv_bfloat16*>(row + M1_NOPE);
+        for (int d = lane; d < D_ROPE; d += 32) dst[M1_NOPE + d] = __bfloat162float(rope[d]);
+    }
+}
+
+template <int LAYOUT>
 __global__ void __launch_bounds__(THREADS) attn_scalar_kernel(const AttnParams p) {
+    constexpr int DQ = (LAYOUT == SMLA_LAYOUT_V32) ? D_QK : 512;   // q / K row length
     __shared__ float qs[HT][D_QK];
     __shared__ float ks[ST][KPAD];
     __shared__ float ps[HT][ST];
@@ -46,7 +91,13 @@ __global__ void __launch_bounds__(THREADS) attn_scalar_kernel(const AttnParams p
     for (int req = meta.begin_req; req <= meta.end_req && req < p.num_tokens; ++req) {
         int len = p.topk_length ? p.topk_length[req] : p.topk;
         len = min(len, p.topk);
-        const int total_blocks = max((len + BLOCK_N - 1) / BLOCK_N, 1);
+        const int main_blocks = max((len + BLOCK_N - 1) / BLOCK_N, 1);
+        int extra_len = 0;
+        if (p.extra_topk > 0) {
+            extra_len = p.extra_topk_length ? p.extra_topk_length[req] : p.extra_topk;
+            extra_len = max(min(extra_len, p.extra_topk), 0);
+        }
+        const int total_blocks = main_blocks + (extra_len + BLOCK_N - 1) / BLOCK_N;
         const int blk0 = (req == meta.begin_req) ? meta.begin_block : 0;
         const int blk1 = min((req == meta.end_req) ? meta.end_block : total_blocks, total_blocks);
         if (blk1 - blk0 <= 0) continue;
@@ -55,16 +106,18 @@ __global__ void __launch_bounds__(THREADS) attn_scalar_kernel(const AttnParams p
         const int split_idx = p.num_splits ? p.num_splits[req] + ((req == meta.begin_req) ? meta.begin_split : 0) : 0;
 
         __syncthreads();  // previous request's epilogue has finished with shared state
-        for (int i = tid; i < HT * D_QK; i += THREADS) {
-            const int h = i / D_QK, d = i - h * D_QK;
+        for (int i = tid; i < HT * DQ; i += THREADS) {
+            const int h = i / DQ, d = i - h * DQ;
             qs[h][d] = (h0 + h < p.num_heads)
-                           ? __bfloat162float(p.q[((size_t)req * p.num_heads + h0 + h) * D_QK + d]) : 0.f;
+                           ? __bfloat162float(p.q[((size_t)req * p.num_heads + h0 + h) * DQ + d]) : 0.f;
         }
         if (tid < HT) { m_s[tid] = NEG_BIG; l_s[tid] = 0.f; }
         float acc[16];
 #pragma unroll
         for (int j = 0; j < 16; ++j) acc[j] = 0.f;
         const int32_t* idx_row = p.indices + (size_t)req * p.topk;
+        const int32_t* extra_idx_row = p.extra_topk > 0 ? p.extra_indices + (size_t)req * p.extra_topk : nullptr;
+        const int main_end = main_blocks * BLOCK_N;   // positions from here on belong to the extra cache
 
         for (int pos0 = blk0 * BLOCK_N; pos0 < blk1 * BLOCK_N; pos0 += ST) {
             __syncthreads();
@@ -72,19 +125,19 @@ __global__ void __launch_bounds__(THREADS) attn_scalar_kernel(const AttnParams p
             {
                 const int r = warp;  // THREADS/32 == ST
                 const int pos = pos0 + r;
-                const int idx = (pos < len) ? idx_row[pos] : -1;
+                int idx = -1;
+                const bool from_extra = pos >= main_end;
+                if (!from_extra) {
+                    if (pos < len) idx = idx_row[pos];
+                } else if (pos - main_end < extra_len) {
+                    idx = extra_idx_row[pos - main_end];
+                }
                 if (lane == 0) valid_s[r] = (idx >= 0);
                 if (idx >= 0) {
-                    const uint8_t* row = kv_row_ptr(p.kv, idx, p.page_block_size, p.block_stride);
-                    const float* sc = reinterpret_cast<const float*>(row + SCALE_OFF);
-                    for (int d = lane; d < D_NOPE; d += 32) {
-                        // the reference rounds the dequantised value to bf16 (exact for power-of-two scales)
-                        ks[r][d] = __bfloat162float(__float2bfloat16(e4m3_to_float(row[d]) * sc[d >> 7]));
-                    }
-                    const __nv_bfloat16* rope = reinterpret_cast<const __nv_bfloat16*>(row + ROPE_OFF);
-                    for (int d = lane; d < D_ROPE; d += 32) ks[r][D_NOPE + d] = __bfloat162float(rope[d]);
+                    if (!from_extra) load_row<LAYOUT>(ks[r], p.kv, idx, p.page_block_size, p.block_stride, lane);
+                    else load_row<LAYOUT>(ks[r], p.extra_kv, idx, p.extra_page_block_size, p.extra_block_stride, lane);
                 } else {
-                    for (int d = lane; d < D_QK; d += 32) ks[r][d] = 0.f;  // exact zero: no 0*NaN in P.V
+                    for (int d = lane; d < DQ; d += 32) ks[r][d] = 0.f;  // exact zero: no 0*NaN in P.V
                 }
             }
             __syncthreads();
@@ -93,7 +146,7 @@ __global__ void __launch_bounds__(THREADS) attn_scalar_kernel(const AttnParams p
                 const int pair = tid >> 2, part4 = tid & 3;
                 const int h = pair / ST, t = pair % ST;
                 float s = 0.f;
-                for (int d = part4; d < D_QK; d += 4) s += qs[h][d] * ks[t][d];
+                for (int d = part4; d < DQ; d += 4) s += qs[h][d] * ks[t][d];
                 s += __shfl_xor_sync(0xffffffffu, s, 1);
                 s += __shfl_xor_sync(0xffffffffu, s, 2);
                 if (part4 == 0) ps[h][t] = valid_s[t] ? s * scale2 : NEG_BIG;
@@ -166,7 +219,8 @@ int launch_attn_scalar(const AttnParams& p, cudaStream_t stream) {
     if (p.num_tokens == 0) return 0;
     const int parts = p.sched ? p.num_parts : p.num_tokens;
     dim3 grid(parts, (p.num_heads + HT - 1) / HT);
-    attn_scalar_kernel<<<grid, THREADS, 0, stream>>>(p);
+    if (p.layout == SMLA_LAYOUT_MODEL1) attn_scalar_kernel<SMLA_LAYOUT_MODEL1><<<grid, THREADS, 0, stream>>>(p);
+    else attn_scalar_kernel<SMLA_LAYOUT_V32><<<grid, THREADS, 0, stream>>>(p);
     return check_launch("attn_scalar_kernel");
 }
 

@@ -48,6 +48,14 @@ struct AttnParams {
     int page_block_size;
     int64_t block_stride;        // bytes between pages
     float sm_scale;
+    // Served by the fp32 kernel only: the cache layout and the second ("extra") cache.
+    int layout;                       // SMLA_LAYOUT_*
+    const uint8_t* extra_kv;          // null = none
+    const int32_t* extra_indices;     // [T, extra_topk]
+    const int32_t* extra_topk_length; // [T] or null
+    int extra_topk;
+    int extra_page_block_size;
+    int64_t extra_block_stride;
 };
 
 __device__ __forceinline__ const uint8_t* kv_row_ptr(const uint8_t* kv, int idx, int page_block_size,

@@ -13,8 +13,8 @@ layer with the same metadata object) can switch over:
   the later ones.  Here the object also keeps the split-KV scratch, and when every request gets
   its own partition there is nothing to schedule: the attention kernel runs alone.
 
-Only sparse attention over an FP8 cache is served (as in the reference); the second ("extra")
-cache of the MODEL1 layout raises NotImplementedError.
+Only sparse attention over an FP8 cache is served (as in the reference).  Both cache layouts and the
+second ("extra") cache are taken; see flash_ops for which kernel serves which.
 """
 from __future__ import annotations
 
@@ -24,10 +24,10 @@ from typing import Optional, Tuple
 import torch
 
 from . import _lib
-from ._lib import IMPL_AUTO, check
-from ._runtime import (BLOCK_N, FIXED_OVERHEAD, kv_geometry, num_sms, pick_num_sm_parts, ptr, require_cuda,
-                       status_buffer, stream_ptr)
-from .flash_ops import _check_q, _reject_extra, sparse_mla_prefill_fwd
+from ._lib import IMPL_AUTO, LAYOUT_V32, check
+from ._runtime import (BLOCK_N, FIXED_OVERHEAD, kv_geometry, num_sms, pick_num_sm_parts, pick_num_sm_parts_fp32, ptr,
+                       require_cuda, status_buffer, stream_ptr)
+from .flash_ops import _check_q, _Extra, _layout, sparse_mla_prefill_fwd
 
 
 @dataclasses.dataclass
@@ -97,7 +97,6 @@ def flash_mla_with_kvcache(
         raise ValueError("an FP8 KV cache is required")
     if head_dim_v != 512:
         raise ValueError(f"head_dim_v must be 512, got {head_dim_v}")
-    _reject_extra(extra_k_cache, extra_indices_in_kvcache, extra_topk_length, 0)
     if softmax_scale is None:
         softmax_scale = q.shape[-1] ** (-0.5)
 
@@ -108,25 +107,32 @@ def flash_mla_with_kvcache(
     num_tokens, num_heads, _ = q_in.shape
     topk = indices.shape[-1]
     idx_in = indices.reshape(num_tokens, topk)
+    layout = _layout(q_in, k_cache)
     page_block_size, page_stride = kv_geometry(k_cache)
     require_cuda(q_in, k_cache, idx_in)
     assert idx_in.dtype == torch.int32 and idx_in.is_contiguous()
+    extra_topk = extra_indices_in_kvcache.shape[-1] if extra_indices_in_kvcache is not None else 0
+    extra_idx = None if extra_indices_in_kvcache is None else extra_indices_in_kvcache.reshape(num_tokens, -1)
+    ex = _Extra(layout, num_tokens, extra_k_cache, extra_idx, extra_topk, extra_topk_length)
+    fp32_only = layout != LAYOUT_V32 or ex.topk > 0
 
     cfg = FlashMLASchedMeta.Config(b=batch, s_q=s_q, h_q=num_heads, page_block_size=k_cache.shape[1],
                                    h_k=k_cache.shape[2], causal=causal, is_fp8_kvcache=is_fp8_kvcache, topk=topk,
-                                   extra_page_block_size=None, extra_topk=None)
+                                   extra_page_block_size=extra_k_cache.shape[1] if extra_k_cache is not None else None,
+                                   extra_topk=ex.topk if ex.topk > 0 else None)
     lib = _lib.load()
     stream = stream_ptr(q.device)
     if not meta.have_initialized:
         meta.have_initialized = True
         meta.config = cfg
-        meta.num_sm_parts = pick_num_sm_parts(num_tokens, num_sms(q.device))
-        meta.max_nsplits = min(max(-(-topk // BLOCK_N), 1), meta.num_sm_parts)
+        meta.num_sm_parts = (pick_num_sm_parts_fp32(num_tokens, num_heads, num_sms(q.device)) if fp32_only
+                             else pick_num_sm_parts(num_tokens, num_sms(q.device)))
+        meta.max_nsplits = min(max(-(-topk // BLOCK_N), 1) + -(-ex.topk // BLOCK_N), meta.num_sm_parts)
         if meta.num_sm_parts != num_tokens:
             meta.tile_scheduler_metadata = torch.empty(meta.num_sm_parts * 8, dtype=torch.int32, device=q.device)
             meta.num_splits = torch.empty(num_tokens + 1, dtype=torch.int32, device=q.device)
-            check(lib.smla_sched_meta(num_tokens, topk, 0, meta.num_sm_parts, FIXED_OVERHEAD, ptr(topk_length), None,
-                                      ptr(meta.tile_scheduler_metadata), ptr(meta.num_splits), stream))
+            check(lib.smla_sched_meta(num_tokens, topk, ex.topk, meta.num_sm_parts, FIXED_OVERHEAD, ptr(topk_length),
+                                      ptr(ex.length), ptr(meta.tile_scheduler_metadata), ptr(meta.num_splits), stream))
             records = num_tokens + meta.num_sm_parts
             meta.o_accum = torch.empty((records, 1, num_heads, head_dim_v), dtype=torch.float32, device=q.device)
             meta.lse_accum = torch.empty((records, 1, num_heads), dtype=torch.float32, device=q.device)
@@ -139,7 +145,20 @@ def flash_mla_with_kvcache(
         output = torch.empty((num_tokens, num_heads, head_dim_v), dtype=torch.bfloat16, device=q.device)
     out_lse = torch.empty((num_tokens, num_heads), dtype=torch.float32, device=q.device)
     st = status_buffer(q.device)
-    if meta.num_sm_parts == num_tokens:
+    if fp32_only and meta.num_sm_parts == num_tokens:
+        check(lib.smla_prefill_ext(
+            ptr(q_in), ptr(k_cache), ptr(idx_in), ptr(ex.kv), ptr(ex.indices), ptr(output), ptr(out_lse), None,
+            num_tokens, num_heads, topk, ex.topk, float(softmax_scale), layout, page_block_size, page_stride,
+            ex.block, ex.stride, ptr(attn_sink), ptr(topk_length), ptr(ex.length), ptr(st), stream))
+    elif fp32_only:
+        check(lib.smla_decode_splitkv_ext(
+            ptr(q_in), ptr(k_cache), ptr(idx_in), ptr(ex.kv), ptr(ex.indices), ptr(meta.o_accum), ptr(meta.lse_accum),
+            ptr(output), ptr(out_lse), ptr(meta.tile_scheduler_metadata), ptr(meta.num_splits), num_tokens, num_heads,
+            topk, ex.topk, float(softmax_scale), layout, page_block_size, page_stride, ex.block, ex.stride,
+            meta.num_sm_parts, ptr(attn_sink), ptr(topk_length), ptr(ex.length), ptr(st), stream))
+        check(lib.smla_combine(ptr(meta.o_accum), ptr(meta.lse_accum), ptr(output), ptr(out_lse), ptr(meta.num_splits),
+                               num_tokens, num_heads, meta.max_nsplits, ptr(attn_sink), stream))
+    elif meta.num_sm_parts == num_tokens:
         check(lib.smla_prefill(ptr(q_in), ptr(k_cache), ptr(idx_in), ptr(output), ptr(out_lse), None, num_tokens,
                                num_heads, topk, float(softmax_scale), page_block_size, page_stride, ptr(attn_sink),
                                ptr(topk_length), impl, ptr(st), stream))

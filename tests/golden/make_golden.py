@@ -2,12 +2,13 @@
 
 Run once where the reference checkout is mounted:
 
-    python tests/golden/make_golden.py /path/to/reference
+    python tests/golden/make_golden.py /path/to/reference [v32|model1|all]
 
 The reference's test modules import its CUDA extension at module import; that import is
 satisfied with empty stub modules because only the pure-PyTorch helpers are called
-(quantize_kv_v32, dequantize_kv_v32, ref_sparse_attn_decode from tests/test_decode.py and
-combine_v2_ref from tests/test_combine.py).  bf16 tensors are stored as their uint16 bit
+(quantize_kv_v32, dequantize_kv_v32, quantize_kv_model1, dequantize_kv_model1 and
+ref_sparse_attn_decode from tests/test_decode.py, combine_v2_ref from tests/test_combine.py,
+ref_v4_decode from tests/test_v4_features.py).  bf16 tensors are stored as their uint16 bit
 patterns so that the .npz files need nothing but numpy to read.
 """
 import sys
@@ -21,11 +22,74 @@ def _bits(t: torch.Tensor) -> np.ndarray:
     return t.contiguous().view(torch.uint16).numpy() if t.dtype == torch.bfloat16 else t.contiguous().numpy()
 
 
-def main(ref_root: str, out_dir: str) -> None:
+def _stub_extension(ref_root: str) -> None:
     for name in ("flash_mla_sm120", "flash_mla_sm120.cuda"):
         sys.modules[name] = types.ModuleType(name)
     sys.modules["flash_mla_sm120"].cuda = sys.modules["flash_mla_sm120.cuda"]
+    for fn in ("get_decode_metadata", "sparse_mla_splitkv_v2_fwd", "sparse_mla_combine_v2_fwd",
+               "sparse_mla_prefill_fwd"):
+        setattr(sys.modules["flash_mla_sm120.cuda"], fn, None)
     sys.path.insert(0, ref_root + "/tests")
+
+
+def main_model1(ref_root: str, out_dir: str) -> None:
+    """The 584-byte footer layout and attention over it, with the second cache, lengths and sink."""
+    _stub_extension(ref_root)
+    import test_decode as ref_dec
+    import test_v4_features as ref_v4
+
+    torch.manual_seed(7)
+    kv = (torch.randn(3, 64, 1, 512, dtype=torch.bfloat16) * torch.tensor([0.1, 1.0, 40.0]).view(3, 1, 1, 1).bfloat16())
+    kv[0, 0] = 0  # an all-zero row exercises the 1e-4 amax floor
+    packed = ref_dec.quantize_kv_model1(kv)
+    deq = ref_dec.dequantize_kv_model1(packed)
+    np.savez_compressed(out_dir + "/kv_format_model1.npz", kv_bf16=_bits(kv), packed=packed.numpy(),
+                        dequant_bf16=_bits(deq))
+
+    cases = {
+        # name: (b, h, topk, extra_topk, lengths?, sink?, block, num_blocks)
+        "attn_m1_h16": (2, 16, 128, 0, False, False, 64, 6),
+        "attn_m1_h64_extra": (3, 64, 192, 96, True, True, 64, 6),
+        "attn_m1_h8_block16": (2, 8, 100, 40, True, False, 16, 20),
+    }
+    for name, (b, h, topk, etopk, lengths, sink, block, nblk) in cases.items():
+        torch.manual_seed(321)
+        kv = (torch.randn(nblk, block, 1, 512, dtype=torch.bfloat16) / 2).clamp(-3, 3)
+        packed = ref_dec.quantize_kv_model1(kv)
+        deq = ref_dec.dequantize_kv_model1(packed)
+        q = (torch.randn(b, 1, h, 512, dtype=torch.bfloat16) / 2)
+        idx = torch.randint(0, nblk * block, (b, 1, topk), dtype=torch.int32)
+        idx[:, :, -10:] = -1
+        rec = dict(packed=packed.numpy(), q_bf16=_bits(q), indices=idx.numpy())
+        tl = etl = epacked = edeq = eidx = attn_sink = None
+        if lengths:
+            tl = torch.randint(0, topk + 1, (b,), dtype=torch.int32)
+            tl[0] = 0                                  # a request whose main cache contributes nothing
+            rec["topk_length"] = tl.numpy()
+        if etopk:
+            ekv = (torch.randn(4, block, 1, 512, dtype=torch.bfloat16) / 2).clamp(-3, 3)
+            epacked = ref_dec.quantize_kv_model1(ekv)
+            edeq = ref_dec.dequantize_kv_model1(epacked)
+            eidx = torch.randint(0, 4 * block, (b, 1, etopk), dtype=torch.int32)
+            eidx[:, :, ::7] = -1
+            rec["extra_packed"], rec["extra_indices"] = epacked.numpy(), eidx.numpy()
+            if lengths:
+                etl = torch.randint(1, etopk + 1, (b,), dtype=torch.int32)
+                rec["extra_topk_length"] = etl.numpy()
+        if sink:
+            attn_sink = torch.randn(h) * 2.0
+            attn_sink[3], attn_sink[5] = float("inf"), float("-inf")
+            rec["attn_sink"] = attn_sink.numpy()
+        sm_scale = 512 ** -0.5
+        out, lse = ref_v4.ref_v4_decode(q, deq, idx, sm_scale, 512, topk_length=tl, extra_kv_dequant=edeq,
+                                        extra_indices=eidx, extra_topk_length=etl, attn_sink=attn_sink)
+        np.savez_compressed(out_dir + f"/{name}.npz", sm_scale=np.float32(sm_scale), out_bf16=_bits(out),
+                            lse=lse.numpy(), **rec)
+    print("MODEL1 golden fixtures written to", out_dir)
+
+
+def main(ref_root: str, out_dir: str) -> None:
+    _stub_extension(ref_root)
     import test_decode as ref_dec
     import test_combine as ref_comb
 
@@ -81,5 +145,10 @@ def main(ref_root: str, out_dir: str) -> None:
 if __name__ == "__main__":
     import os
     if len(sys.argv) < 2:
-        sys.exit("usage: python tests/golden/make_golden.py /path/to/reference")
-    main(sys.argv[1], os.path.dirname(os.path.abspath(__file__)))
+        sys.exit("usage: python tests/golden/make_golden.py /path/to/reference [v32|model1|all]")
+    which = sys.argv[2] if len(sys.argv) > 2 else "all"
+    here = os.path.dirname(os.path.abspath(__file__))
+    if which in ("v32", "all"):
+        main(sys.argv[1], here)
+    if which in ("model1", "all"):
+        main_model1(sys.argv[1], here)

@@ -318,8 +318,11 @@ def test_topk_not_a_multiple_of_the_block(impl, topk):
     """Index lists of any length: the last block of a list is partly filled."""
     case = make_case(61, 3, 128, topk, 8, invalid_tail=0.0)
     ref_out, ref_lse = oracle_attn(case)
+    # a row that averages fewer keys than one block shows Q's e4m3 rounding undamped
+    check = (lambda o, l, **kw: _check_hard(o, l, ref_out, ref_lse, impl, case)) if topk < 64 else \
+            (lambda o, l, **kw: _check(o, l, ref_out, ref_lse, impl, **kw))
     for parts in (None, 2):
         out, lse = _decode(case, impl, num_sm_parts=parts)
-        _check(out, lse, ref_out, ref_lse, impl)
+        check(out, lse)
     out, mx, lse = _prefill(case, impl)
-    _check(out, lse, ref_out, ref_lse, impl, prefill=True)
+    check(out, lse, prefill=True)

@@ -80,3 +80,48 @@ def test_fp8_emulation_distance():
     rms = float(ref_out.float().pow(2).mean().sqrt())
     excess = float((d - (H.TC_ABS + H.TC_REL * torch.maximum(emu_out.float().abs(), ref_out.float().abs()))).max()) / rms
     assert 0.03 < excess < H.TC_NOISE / 1.3, excess                               # TC_NOISE keeps >= 1.3 x margin over it
+
+
+M1_CASES = ("attn_m1_h16", "attn_m1_h64_extra", "attn_m1_h8_block16")
+
+
+def load_m1_case(golden_dir, name):
+    """A MODEL1 fixture as CPU tensors (absent arrays -> None)."""
+    g = _load(golden_dir, name)
+    t = lambda k: torch.from_numpy(g[k]) if k in g else None  # noqa: E731
+    return {"packed": t("packed"), "q": bf16_from_bits(g["q_bf16"]), "indices": t("indices"),
+            "topk_length": t("topk_length"), "extra_packed": t("extra_packed"), "extra_indices": t("extra_indices"),
+            "extra_topk_length": t("extra_topk_length"), "attn_sink": t("attn_sink"),
+            "sm_scale": float(g["sm_scale"]), "out": bf16_from_bits(g["out_bf16"]), "lse": t("lse")}
+
+
+def test_model1_format_roundtrip(golden_dir):
+    g = _load(golden_dir, "kv_format_model1")
+    kv = bf16_from_bits(g["kv_bf16"])
+    assert np.array_equal(orc.quantize_kv_model1(kv).numpy(), g["packed"]), "footer-ordered bytes differ from the reference writer"
+    deq = orc.dequantize_kv_model1(torch.from_numpy(g["packed"]))
+    assert np.array_equal(deq.view(torch.uint16).numpy(), g["dequant_bf16"]), "dequantised bf16 differs"
+    # the footer of a page starts after block x 576 data bytes and its pad bytes are zero
+    page = torch.from_numpy(g["packed"]).reshape(3, 64 * 584)
+    assert not page[:, 64 * 576:].reshape(3, 64, 8)[..., 7].any()
+
+
+def test_model1_attention_matches_reference(golden_dir):
+    for name in M1_CASES:
+        c = load_m1_case(golden_dir, name)
+        edeq = None if c["extra_packed"] is None else orc.dequantize_kv_model1(c["extra_packed"])
+        out, lse = orc.ref_sparse_attn_dual(c["q"], orc.dequantize_kv_model1(c["packed"]), c["indices"], c["sm_scale"],
+                                            512, c["topk_length"], edeq, c["extra_indices"], c["extra_topk_length"],
+                                            c["attn_sink"])
+        assert torch.equal(out.view(torch.uint16), c["out"].view(torch.uint16)), name
+        assert torch.equal(lse, c["lse"]), name
+
+
+def test_dual_attention_without_extras_is_the_v32_oracle():
+    """ref_sparse_attn_dual restricted to one cache, no lengths and no sink is ref_sparse_attn."""
+    from helpers import make_case
+    c = make_case(5, 2, 8, 128, 4)
+    deq = orc.dequantize_kv_v32(c["packed"])
+    a = orc.ref_sparse_attn(c["q"].unsqueeze(1), deq, c["indices"].unsqueeze(1), c["sm_scale"], 512)
+    b = orc.ref_sparse_attn_dual(c["q"].unsqueeze(1), deq, c["indices"].unsqueeze(1), c["sm_scale"], 512)
+    assert torch.equal(a[0].view(torch.uint16), b[0].view(torch.uint16)) and torch.equal(a[1], b[1])
