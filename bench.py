@@ -3,17 +3,22 @@
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference] [--no-extras]
 
-One step = one split-KV decode call (scheduler -> attention -> combine) over one batch of the
+One step = one call of the public decode op (``sparse_mla_decode_fwd``) over one batch of the
 DeepSeek-V3.2-shape decode configuration: 64 requests per GPU, 128 query heads, top-k 2048,
 per-request KV length uniform in [4096, 32768] in a paged (block 64) pool of packed 656-byte
-FP8 rows.  All inputs are synthetic and seeded.  With N > 1 every rank serves its own 64
-requests (decode batches shard by sequence, nothing is exchanged), so scaling is weak.
+FP8 rows.  At this batch size the op's policy gives every request its own partition, so the op
+is ONE launch, the attention kernel (nothing to schedule or to combine); the split-KV form of the
+same step (scheduler + attention + combine) is timed beside it as ``extras.split_kv_decode``.
+All inputs are synthetic and seeded.  With N > 1 every rank serves its own 64 requests (decode
+batches shard by sequence, nothing is exchanged), so scaling is weak.
 
 Printed line: ``value`` is the algorithmic HBM traffic of the whole job divided by the step time
 with inputs resident on the device (CUDA-graph replay of the public op); ``e2e`` is the same
 through the public op with q / indices coming from pinned host memory and the output copied back
 every step (the paged KV cache is device-resident state, as in any serving engine).
-``--impl reference`` times the reference's CPU PyTorch path (restated in oracle/) on the host cores.
+``roofline`` is the attention kernel alone, timed live with CUDA events.
+``--impl reference`` times the reference's CPU PyTorch path (restated in oracle/) on the host
+cores, on the same seeded sample of the step as this arm's ``cpu_baseline``.
 """
 from __future__ import annotations
 
@@ -37,9 +42,10 @@ NSETS = 8   # rotating (q, indices) sets so that consecutive steps gather differ
 SM_SCALE = D_QK ** -0.5
 WORKLOAD = ("V3.2-shape sparse-MLA decode: b=64/GPU, s_q=1, h_q=128, topk=2048, d_qk=576, d_v=512, "
             "KV len U[4096,32768], paged block 64, packed FP8 656 B rows")
-# DRAM bytes per launch of the attention kernel from the ncu capture summarised in
-# profiles/attn_tc_decode_b64.md (dram__bytes_read.sum + dram__bytes_write.sum of one launch).
-NCU_TRAFFIC_BYTES = 113_699_328
+# DRAM bytes of one launch of the attention kernel on this workload's shape, from one ncu capture
+# (dram__bytes_read.sum + dram__bytes_write.sum); the capture's summary is kept with the other profiles.
+NCU_TRAFFIC_BYTES = 91_298_048
+CPU_SAMPLE_REQUESTS = 16   # requests of one step that the CPU legs compute
 
 
 def algorithmic_bytes(num_tokens: int, n_valid: int) -> int:
@@ -329,14 +335,14 @@ def run_ours(args):
         cp_extra = None
     if rank == 0 and not args.no_extras:
         try:
-            extras = run_extras(device, bf16_peak)
+            extras = run_extras(device, hbm_peak, bf16_peak, peak_kind)
         except Exception as e:  # the headline line must still print
             extras = {"error": repr(e)}
     if cp_extra is not None:
         extras["cp_decode"] = cp_extra
     if split_extra is not None:
         extras["split_kv_decode"] = split_extra
-    cpu = cpu_baseline(pool, sets) if rank == 0 else None
+    cpu = cpu_baseline() if rank == 0 else None
 
     if rank == 0:
         total_bytes = bytes_step * world
@@ -361,7 +367,7 @@ def run_ours(args):
                     "note": "paged KV cache is device-resident state; q and indices come from pinned host memory, output and LSE go "
                             "back, every step; copies and kernel of neighbouring steps overlap on three streams"},
             "gpu_launches": launches_per_step * args.steps,
-            "roofline": {"bound": "hbm", "kernel": "attn_tc_kernel", "achieved": bytes_step / k_secs / 1e9, "peak": hbm_peak,
+            "roofline": {"bound": "hbm", "kernel": "attn_pair_kernel", "achieved": bytes_step / k_secs / 1e9, "peak": hbm_peak,
                          "unit": "GB/s", "frac": bytes_step / k_secs / 1e9 / hbm_peak, "peak_kind": f"of {peak_kind}",
                          "kernel_us": k_secs * 1e6, "traffic": NCU_TRAFFIC_BYTES,
                          "frac_of_8TBs_nominal": bytes_step / k_secs / 8e12},
@@ -374,53 +380,94 @@ def run_ours(args):
 
 
 def run_cp_extra(device, rank, world):
-    """Context-parallel long-context decode: 16 requests, 131072-token context sharded across the
-    ranks, top-k 2048 uniform over the whole context.  Timed per step on the device, max over ranks:
-    index partition + scheduler + local split-KV decode + local merge + one NCCL all-gather + final merge.
+    """Context-parallel long-context decode: 16 requests, 131072-token context per request sharded across the
+    ranks, top-k 2048 uniform over the whole context.  Timed per step on the device, max over ranks: index
+    partition + scheduler + local split-KV decode + local merge cut into head slices + all-to-all by head slice +
+    merge of H/G heads + all-gather of the bf16 result + reassembly.  Eager launches and the whole step
+    captured into one CUDA graph (collectives included).  ``speedup_vs_1gpu`` compares with the same 16
+    requests decoded on ONE GPU that holds the whole context (measured on rank 0).
     (The indexer that would produce the indices is not part of this timing.)"""
     import torch.distributed as dist
-    from sparse_mla_sm120_b200 import cp, indexer
+    from sparse_mla_sm120_b200 import cp, flash_ops, indexer
     b, ctx = 16, 131072
     lo, hi = cp.shard_context(ctx, rank, world)
     rows = hi - lo
+    assert rows * world == ctx
     g = torch.Generator(device=device).manual_seed(99 + rank)
     pools = []
-    for _ in range(b):   # one contiguous shard per request; rows of request i live at [i*rows, (i+1)*rows)
+    for _ in range(b):   # one contiguous shard per request; rows of request i live at [i*rows, (i+1)*rows) of the local pool
         pools.append(indexer.pack_kv_cache(torch.randn((rows, D_QK), device=device, generator=g).to(torch.bfloat16)))
     kv_local = torch.cat(pools).view(-1, BLOCK, 1, ROW)
+    del pools
     gi = torch.Generator(device=device).manual_seed(7)      # same indices on every rank
     q = (torch.randn((b, HEADS, D_QK), device=device, generator=gi) * 0.5).to(torch.bfloat16)
     pos = torch.stack([torch.randperm(ctx, device=device, generator=gi)[:TOPK] for _ in range(b)])
-    # global row number = request * ctx + position; the local pool stores request i's shard at i*rows
-    in_shard = (pos >= lo) & (pos < hi)
-    local = torch.where(in_shard, pos - lo + torch.arange(b, device=device).view(-1, 1) * rows, torch.full_like(pos, -1)).to(torch.int32)
+    # One global row numbering in which every rank's rows are one range: rank g holds [g*b*rows, (g+1)*b*rows),
+    # request i's position p lives at (p // rows) * b * rows + i * rows + p % rows.
+    req = torch.arange(b, device=device).view(-1, 1)
+    indices = ((pos // rows) * (b * rows) + req * rows + pos % rows).to(torch.int32)
+    s_lo, s_hi = rank * b * rows, (rank + 1) * b * rows
 
-    def step():
-        # entries outside the shard are already -1; compaction and the local length come from the partition kernel
-        li, ln = cp.partition_indices(local, 0, b * rows)
-        packed, o_all, l_all = cp._gather_buffers(device, world, b, HEADS)
-        cp.decode_partial(q, kv_local, li, ln, SM_SCALE, o_all[rank], l_all[rank])
-        dist.all_gather_into_tensor(packed, packed[rank])       # partials and LSEs of a rank are adjacent
-        return cp.combine_parts(o_all, l_all)
+    def timed(fn, n=50):
+        for _ in range(5):
+            fn()
+        dist.barrier(); torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(n):
+            fn()
+        e1.record(); torch.cuda.synchronize()
+        t = torch.tensor([e0.elapsed_time(e1) / n * 1e3], device=device)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
 
-    for _ in range(5):
-        step()
-    dist.barrier(); torch.cuda.synchronize()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    n = 50
-    e0.record()
-    for _ in range(n):
-        step()
-    e1.record(); torch.cuda.synchronize()
-    t = torch.tensor([e0.elapsed_time(e1) / n * 1e3], device=device)
-    dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    res = {"workload": "b=16, h=128, topk=2048, 131072-token context sharded over the ranks", "us_per_step": float(t.item()),
-           "timed": "partition + scheduler + local decode + local merge + one NCCL all-gather + final merge (eager launches)",
-           "exchange_bytes_per_rank": b * HEADS * (D_V + 1) * 4}
+    hs = HEADS // world
+    res = {"workload": "b=16, h=128, topk=2048, 131072-token context per request sharded over the ranks",
+           "timed": "partition + scheduler + local decode + sliced local merge + all-to-all by head slice + merge of H/G heads + "
+                    "all-gather of the bf16 result + reassembly",
+           "us_per_step": timed(lambda: cp.sparse_mla_decode_cp_fwd(q, kv_local, indices, SM_SCALE, s_lo, s_hi)),
+           "exchange_bytes_per_rank": {"all_to_all_out": (world - 1) * b * hs * (D_V + 1) * 4,
+                                       "all_gather_in": (world - 1) * b * hs * (D_V * 2 + 4)}}
+    try:
+        graphed = cp.GraphedCpDecode(kv_local, b, HEADS, TOPK, SM_SCALE, s_lo, s_hi)
+        graphed(q, indices)
+        res["us_per_step_graph"] = timed(graphed.replay)
+        res["graph_captured"] = graphed.graph is not None
+        del graphed
+    except Exception as e:       # noqa: BLE001 - capture is an optimisation of the launch path, not a requirement
+        res["us_per_step_graph"] = None
+        res["graph_error"] = repr(e)
+    # the same 16 requests on ONE GPU holding all 16 x 131072 rows (1.4 GB), on rank 0
+    one = None
+    if rank == 0:
+        full = torch.empty((b * ctx // BLOCK, BLOCK, 1, ROW), dtype=torch.uint8, device=device)
+        g1 = torch.Generator(device=device).manual_seed(5)
+        step_rows = 1 << 18
+        for r0 in range(0, b * ctx, step_rows):
+            full.view(-1, ROW)[r0:r0 + step_rows] = indexer.pack_kv_cache(
+                torch.randn((step_rows, D_QK), device=device, generator=g1).to(torch.bfloat16))
+        idx1 = (pos + req * ctx).to(torch.int32)
+        for _ in range(3):
+            flash_ops.sparse_mla_decode_fwd(q, full, idx1, SM_SCALE)
+        torch.cuda.synchronize()
+        gr = torch.cuda.CUDAGraph()
+        side = torch.cuda.Stream()
+        with torch.cuda.stream(side):
+            flash_ops.sparse_mla_decode_fwd(q, full, idx1, SM_SCALE); side.synchronize()
+            with torch.cuda.graph(gr, stream=side):
+                flash_ops.sparse_mla_decode_fwd(q, full, idx1, SM_SCALE)
+        torch.cuda.synchronize()
+        one = _time_cuda(gr.replay, 100, warm=5) * 1e3
+        del full, gr
+    t1 = torch.tensor([one if one is not None else 0.0], device=device)
+    dist.broadcast(t1, 0)
+    res["one_gpu_us_per_step"] = float(t1.item())
+    best = min(x for x in (res["us_per_step"], res.get("us_per_step_graph")) if x)
+    res["speedup_vs_1gpu"] = float(t1.item()) / best
     # the same step with the indexer in front: 16 tokens of ONE sequence whose 131072-token context
     # (attention cache and indexer keys) is sharded; local logits + local top-k + candidate all-gather
     # + global top-k, then the context-parallel decode
-    del kv_local, pools
+    del kv_local
     kv_one = indexer.pack_kv_cache(torch.randn((rows, D_QK), device=device, generator=g).to(torch.bfloat16)).view(-1, BLOCK, 1, ROW)
     hh = 64
     qi = torch.randn((b, hh, 128), device=device, generator=gi).to(torch.float8_e4m3fn)
@@ -430,49 +477,105 @@ def run_cp_extra(device, rank, world):
     ki = (kf / k_scale.unsqueeze(1)).to(torch.float8_e4m3fn)
     ks = torch.zeros(b, dtype=torch.int32, device=device)
     ke = (ctx - b + 1 + torch.arange(b, device=device)).to(torch.int32)
-
-    def step_indexed():
-        return cp.sparse_mla_indexed_decode_cp_fwd(q, kv_one, qi, ki, k_scale, w, ks, ke, SM_SCALE, lo, hi, topk=TOPK)
-
-    for _ in range(5):
-        step_indexed()
-    dist.barrier(); torch.cuda.synchronize()
-    e0.record()
-    for _ in range(n):
-        step_indexed()
-    e1.record(); torch.cuda.synchronize()
-    t = torch.tensor([e0.elapsed_time(e1) / n * 1e3], device=device)
-    dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    res["us_per_step_with_indexer"] = float(t.item())
+    res["us_per_step_with_indexer"] = timed(
+        lambda: cp.sparse_mla_indexed_decode_cp_fwd(q, kv_one, qi, ki, k_scale, w, ks, ke, SM_SCALE, lo, hi, topk=TOPK))
     res["indexer_exchange_bytes_per_rank"] = b * TOPK * 8
     return res
 
 
-def run_extras(device, bf16_peak):
-    """Secondary measurements of the other kernels on the path (not part of the timed step)."""
+def _time_cuda(fn, n, warm=2):
+    for _ in range(warm):
+        fn()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(n):
+        fn()
+    e1.record(); torch.cuda.synchronize()
+    return e0.elapsed_time(e1) / n          # ms
+
+
+def _cpu_attention_slice(q, kv_packed, idx, tokens):
+    """The reference's CPU path (oracle port) on the first `tokens` query tokens of a GPU case, best of 3."""
+    from oracle import sparse_mla_oracle as orc
+    torch.set_num_threads(os.cpu_count())
+    qc, ic = q[:tokens].cpu().unsqueeze(1), idx[:tokens].cpu().unsqueeze(1)
+    packed = kv_packed.cpu()
+    best = None
+    for _ in range(3):
+        t0 = time.perf_counter()
+        orc.ref_sparse_attn(qc, orc.dequantize_kv_v32(packed), ic, SM_SCALE, D_V)
+        dt = time.perf_counter() - t0
+        best = dt if best is None else min(best, dt)
+    return best
+
+
+def run_extras(device, hbm_peak, bf16_peak, peak_kind):
+    """Secondary measurements of the other kernels and shapes on the path (not part of the timed step)."""
     from sparse_mla_sm120_b200 import flash_ops, indexer
     out = {}
     g = torch.Generator(device=device).manual_seed(7)
-    # prefill: s_q 4096, H 128, topk 2048 over 8192 rows, causal top-k
+    # ---- prefill: s_q 4096, H 128, topk 2048 over 8192 rows, causal top-k (token i sees 4096 + i keys)
     s_q, rows = 4096, 8192
     kv = indexer.pack_kv_cache(torch.randn((rows, D_QK), device=device, generator=g).to(torch.bfloat16)).view(rows // 64, 64, 1, ROW)
     q = torch.randn((s_q, HEADS, D_QK), device=device, generator=g).to(torch.bfloat16)
     idx = torch.stack([torch.randperm(4096 + i, device=device, generator=g)[:TOPK] for i in range(s_q)]).to(torch.int32)
-    for _ in range(2):
-        flash_ops.sparse_mla_prefill_fwd(q, kv, idx, SM_SCALE)
-    torch.cuda.synchronize()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    n = 5
-    e0.record()
-    for _ in range(n):
-        flash_ops.sparse_mla_prefill_fwd(q, kv, idx, SM_SCALE)
-    e1.record(); torch.cuda.synchronize()
-    ms = e0.elapsed_time(e1) / n
+    ms = _time_cuda(lambda: flash_ops.sparse_mla_prefill_fwd(q, kv, idx, SM_SCALE), 5)
     flops = 2.0 * s_q * HEADS * TOPK * (D_QK + D_V)
-    out["prefill"] = {"workload": "s_q=4096, h=128, topk=2048, KV 8192 rows", "ms": ms,
-                      "tflops": flops / ms / 1e9, "frac_of_bf16_peak": flops / ms / 1e9 / bf16_peak}
-    del q, idx, kv
-    # indexer: q e4m3 [4096, 64, 128], k e4m3 [65536, 128], ke = 61440 + i, then top-2048 per row
+    cpu_tokens = 8
+    cpu_s = _cpu_attention_slice(q, kv, idx, cpu_tokens)
+    out["prefill"] = {
+        "workload": "s_q=4096, h=128, topk=2048, KV 8192 rows, causal top-k", "ms": ms, "tflops": flops / ms / 1e9,
+        "roofline": {"bound": "tensor", "kernel": "attn_pair_kernel", "achieved": flops / ms / 1e9, "peak": bf16_peak, "unit": "TFLOP/s",
+                     "frac": flops / ms / 1e9 / bf16_peak, "peak_kind": f"of {peak_kind} (dense BF16; the kernel's MMAs are FP8)",
+                     "traffic": None},
+        "cpu_baseline": {"value": flops * cpu_tokens / s_q / cpu_s / 1e12, "unit": "TFLOP/s", "cores": os.cpu_count(), "kind": "port",
+                         "sample": f"first {cpu_tokens} of {s_q} query tokens, best of 3", "seconds": cpu_s}}
+    # ---- the same prefill with the start of a sequence in it: token i sees i + 1 keys, and its index list is
+    # padded with -1 once they run out (tokens 0..2047), as a serving engine hands it over
+    idx_c = torch.full((s_q, TOPK), -1, dtype=torch.int32, device=device)
+    for i in range(s_q):
+        n = min(i + 1, TOPK)
+        idx_c[i, :n] = torch.randperm(i + 1, device=device, generator=g)[:n].to(torch.int32)
+    ms_c = _time_cuda(lambda: flash_ops.sparse_mla_prefill_fwd(q, kv, idx_c, SM_SCALE), 5)
+    valid = float((idx_c >= 0).sum())
+    fl_c = 2.0 * HEADS * valid * (D_QK + D_V)
+    out["prefill_causal_padded"] = {
+        "workload": "s_q=4096 from the start of a sequence: token i has min(i+1, 2048) entries, the rest of its list is -1",
+        "ms": ms_c, "valid_entries": valid, "tflops": fl_c / ms_c / 1e9,
+        "roofline": {"bound": "tensor", "kernel": "attn_pair_kernel", "achieved": fl_c / ms_c / 1e9, "peak": bf16_peak, "unit": "TFLOP/s",
+                     "frac": fl_c / ms_c / 1e9 / bf16_peak, "peak_kind": f"of {peak_kind} (dense BF16; flops of valid entries only)",
+                     "traffic": None}}
+    del q, idx, idx_c, kv
+    # ---- decode with two query tokens per request (multi-token prediction): the workload of the headline
+    # with s_q = 2, i.e. 128 query tokens, each with its own index list
+    try:
+        pool, sets, _ = build_workload(device, 4321, B_PER_GPU)
+        q2 = (torch.randn((B_PER_GPU, 2, HEADS, D_QK), device=device, generator=g) * 0.5).to(torch.bfloat16)
+        i2 = torch.stack([sets[0][1], sets[1][1]], dim=1).contiguous()               # [b, 2, topk]
+        from sparse_mla_sm120_b200 import interface
+        meta, _ = interface.get_mla_metadata()
+        run2 = lambda: interface.flash_mla_with_kvcache(q2, pool, None, None, D_V, meta, None, SM_SCALE, False, True, indices=i2)
+        run2(); torch.cuda.synchronize()
+        gr = torch.cuda.CUDAGraph()
+        side = torch.cuda.Stream()
+        with torch.cuda.stream(side):
+            run2(); side.synchronize()
+            with torch.cuda.graph(gr, stream=side):
+                run2()
+        torch.cuda.synchronize()
+        ms2 = _time_cuda(gr.replay, 200, warm=5)
+        by2 = algorithmic_bytes(2 * B_PER_GPU, TOPK)
+        out["decode_mtp_sq2"] = {
+            "workload": "the headline's decode with s_q=2: 64 requests x 2 query tokens, h=128, topk=2048, through flash_mla_with_kvcache",
+            "us_per_step": ms2 * 1e3, "num_sm_parts": meta.num_sm_parts,
+            "roofline": {"bound": "hbm", "kernel": "attn_pair_kernel", "achieved": by2 / ms2 / 1e6, "peak": hbm_peak, "unit": "GB/s",
+                         "frac": by2 / ms2 / 1e6 / hbm_peak, "peak_kind": f"of {peak_kind}", "traffic": None,
+                         "note": "whole step (CUDA graph replay), algorithmic bytes count each token's gathered rows"}}
+        del pool, sets, q2, i2
+    except Exception as e:           # noqa: BLE001 - a secondary measurement must not take the others down
+        out["decode_mtp_sq2"] = {"error": repr(e)}
+    # ---- indexer: q e4m3 [4096, 64, 128], k e4m3 [65536, 128], ke = 61440 + i, then top-2048 per row
     s_q, s_k, hh = 4096, 65536, 64
     qi = torch.randn((s_q, hh, 128), device=device, generator=g).to(torch.float8_e4m3fn)
     kf = torch.randn((s_k, 128), device=device, generator=g)
@@ -482,21 +585,34 @@ def run_extras(device, bf16_peak):
     ks = torch.zeros(s_q, dtype=torch.int32, device=device)
     ke = (61440 + torch.arange(s_q, device=device)).to(torch.int32)
     logits = torch.empty((s_q, s_k), dtype=torch.float32, device=device)
-    for name, fn in (("mqa_logits", lambda: indexer.fp8_mqa_logits(qi, ki, k_scale, w, ks, ke, out=logits)),
-                     ("topk", lambda: indexer.topk_indices(logits, ks, ke, TOPK))):
-        fn(); fn()
-        torch.cuda.synchronize()
-        e0.record()
-        for _ in range(3):
-            fn()
-        e1.record(); torch.cuda.synchronize()
-        out[name] = {"ms": e0.elapsed_time(e1) / 3}
+    out["mqa_logits"] = {"ms": _time_cuda(lambda: indexer.fp8_mqa_logits(qi, ki, k_scale, w, ks, ke, out=logits), 3)}
+    out["topk"] = {"ms": _time_cuda(lambda: indexer.topk_indices(logits, ks, ke, TOPK), 3)}
     pairs = float(ke.double().sum())
     fl = 2.0 * hh * 128 * pairs
-    out["mqa_logits"].update({"workload": "s_q=4096, 64 heads, d=128, s_k=65536, ke=61440+i", "tflops": fl / out["mqa_logits"]["ms"] / 1e9,
-                              "frac_of_fp8_peak(2x measured bf16)": fl / out["mqa_logits"]["ms"] / 1e9 / (2 * bf16_peak),
-                              "write_gbs": s_q * s_k * 4 / out["mqa_logits"]["ms"] / 1e6})
-    out["topk"].update({"workload": "top-2048 of each of 4096 rows of 65536 fp32", "read_gbs": s_q * s_k * 4 / out["topk"]["ms"] / 1e6})
+    mq = out["mqa_logits"]
+    # CPU slice: the oracle's formula on the first 32 query rows against the first 8192 keys
+    from oracle import sparse_mla_oracle as orc
+    cq, ck = 32, 8192
+    qs_, kc_, kss_, ws_ = qi[:cq].cpu(), ki[:ck].cpu(), k_scale[:ck].cpu(), w[:cq].cpu()
+    z0, z1 = torch.zeros(cq, dtype=torch.int32), torch.full((cq,), ck, dtype=torch.int32)
+    best = None
+    for _ in range(3):
+        t0 = time.perf_counter()
+        orc.mqa_logits_ref(qs_, kc_, kss_, ws_, z0, z1)
+        dt = time.perf_counter() - t0
+        best = dt if best is None else min(best, dt)
+    mq.update({"workload": "s_q=4096, 64 heads, d=128, s_k=65536, ke=61440+i", "tflops": fl / mq["ms"] / 1e9,
+               "write_gbs": s_q * s_k * 4 / mq["ms"] / 1e6,
+               "roofline": {"bound": "tensor", "kernel": "mqa_logits_tc_kernel", "achieved": fl / mq["ms"] / 1e9, "peak": 2 * bf16_peak,
+                            "unit": "TFLOP/s", "frac": fl / mq["ms"] / 1e9 / (2 * bf16_peak),
+                            "peak_kind": f"2 x the {peak_kind} dense BF16 rate (the kernel's MMAs are FP8)", "traffic": None,
+                            "hbm_write_frac": s_q * s_k * 4 / mq["ms"] / 1e6 / hbm_peak},
+               "cpu_baseline": {"value": 2.0 * hh * 128 * cq * ck / best / 1e12, "unit": "TFLOP/s", "cores": os.cpu_count(), "kind": "port",
+                                "sample": f"first {cq} query rows x first {ck} keys, best of 3", "seconds": best}})
+    out["topk"].update({"workload": "top-2048 of each of 4096 rows of 65536 fp32", "read_gbs": s_q * s_k * 4 / out["topk"]["ms"] / 1e6,
+                        "roofline": {"bound": "hbm", "kernel": "topk_kernel", "achieved": s_q * s_k * 4 / out["topk"]["ms"] / 1e6,
+                                     "peak": hbm_peak, "unit": "GB/s", "frac": s_q * s_k * 4 / out["topk"]["ms"] / 1e6 / hbm_peak,
+                                     "peak_kind": f"of {peak_kind}", "traffic": None}})
     del logits, qi, ki
     out["indexed_decode"] = run_indexed_decode_extra(device, g)
     return out
@@ -543,36 +659,12 @@ def run_indexed_decode_extra(device, g):
     return res
 
 
-def cpu_baseline(pool, sets, n_req: int = 16):
-    """The reference's CPU PyTorch path (oracle port) on a bounded sample: n_req of the 64
-    requests of one step, all host threads."""
-    from oracle import sparse_mla_oracle as orc
-    q, idx = sets[0]
-    rows = pool.view(-1, ROW)[idx[:n_req].reshape(-1).long()].cpu()
-    qc = q[:n_req].cpu().unsqueeze(1)
-    local_idx = torch.arange(n_req * TOPK, dtype=torch.int32).view(n_req, 1, TOPK)
-    torch.set_num_threads(os.cpu_count())
-    best = None
-    for _ in range(5):
-        t0 = time.perf_counter()
-        deq = orc.dequantize_kv_v32(rows.view(-1, 64, 1, ROW))
-        orc.ref_sparse_attn(qc, deq, local_idx, SM_SCALE, D_V)
-        dt = time.perf_counter() - t0
-        best = dt if best is None else min(best, dt)
-    return {"value": algorithmic_bytes(n_req, TOPK) / best / 1e9, "unit": "GB/s", "cores": os.cpu_count(),
-            "kind": "port", "sample": f"{n_req} of {B_PER_GPU} requests of one step (dequantise gathered rows + fp32 attention), best of 5",
-            "seconds": best}
-
-
-def run_reference(args):
-    """The reference's own CPU implementation of the path (its PyTorch reference functions,
-    restated in oracle/), timed on the host cores on a bounded sample per step."""
-    rank = int(os.environ.get("RANK", "0"))
-    if rank != 0:
-        return
+def cpu_sample_step(n_req: int = CPU_SAMPLE_REQUESTS):
+    """The bounded CPU sample of one decode step that BOTH arms time: n_req of the step's 64 requests (a
+    request's work does not depend on the others), seeded, built on the host.  Returns (step function,
+    algorithmic bytes of the sample, description)."""
     from oracle import sparse_mla_oracle as orc
     torch.set_num_threads(os.cpu_count())
-    n_req = 16
     g = torch.Generator().manual_seed(1234)
     kv = torch.randn(n_req * TOPK // 64, 64, 1, D_QK, generator=g).to(torch.bfloat16)
     packed = orc.quantize_kv_v32(kv)
@@ -580,22 +672,53 @@ def run_reference(args):
     idx = torch.stack([torch.randperm(n_req * TOPK, generator=g)[:TOPK] for _ in range(n_req)]).view(n_req, 1, TOPK).int()
 
     def step():
-        deq = orc.dequantize_kv_v32(packed)
+        deq = orc.dequantize_kv_v32(packed)          # the reference's CPU path dequantises, then attends in fp32
         orc.ref_sparse_attn(q, deq, idx, SM_SCALE, D_V)
 
+    sample = (f"{n_req} of the {B_PER_GPU} requests of one step (dequantise the gathered rows + fp32 attention), seed 1234, "
+              f"{os.cpu_count()} host threads")
+    return step, algorithmic_bytes(n_req, TOPK), sample
+
+
+def cpu_baseline():
+    """The reference's CPU PyTorch path (oracle port) on the bounded sample, best of 5."""
+    step, nbytes, sample = cpu_sample_step()
+    best = None
+    for _ in range(5):
+        t0 = time.perf_counter()
+        step()
+        dt = time.perf_counter() - t0
+        best = dt if best is None else min(best, dt)
+    return {"value": nbytes / best / 1e9, "unit": "GB/s", "cores": os.cpu_count(), "kind": "port",
+            "sample": sample + ", best of 5", "seconds": best}
+
+
+def run_reference(args):
+    """The reference's own CPU implementation of the path (its PyTorch reference functions, restated in
+    oracle/), timed on the host cores.  One timed step computes the bounded sample (the same one as the
+    other arm's cpu_baseline); ``ms_per_step`` is scaled to the whole 64-request step, ``ms_per_sample``
+    is what was measured."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    step, nbytes, sample = cpu_sample_step()
     for _ in range(args.warmup):
         step()
     t0 = time.perf_counter()
     for _ in range(args.steps):
         step()
     secs = time.perf_counter() - t0
-    value = algorithmic_bytes(n_req, TOPK) * args.steps / secs / 1e9
-    sample = f"{n_req} of {B_PER_GPU} requests per step on the CPU (the step's unit work scales linearly with requests)"
+    value = nbytes * args.steps / secs / 1e9
+    world = int(os.environ.get("WORLD_SIZE", "1"))
     print(json.dumps({
         "impl": "reference", "metric": "sparse_mla_decode_algorithmic_hbm_throughput", "value": value, "unit": "GB/s",
-        "n_gpus": int(os.environ.get("WORLD_SIZE", "1")), "steps": args.steps, "warmup": args.warmup,
-        "ms_per_step": secs / args.steps * 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
-        "dtype": "f32", "data": "synthetic", "config": {"workload": WORKLOAD, "sample": sample},
+        "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": secs / args.steps * 1e3 * (B_PER_GPU / CPU_SAMPLE_REQUESTS),
+        "ms_per_sample": secs / args.steps * 1e3,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "f32", "data": "synthetic",
+        "config": {"workload": WORKLOAD, "sample": sample,
+                   "note": "one host runs this arm whatever N is: a ratio against the N-GPU arm divides N GPUs by one host"},
         "cpu_baseline": {"value": value, "unit": "GB/s", "cores": os.cpu_count(), "kind": "port", "sample": sample},
         "e2e": {"value": value, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,

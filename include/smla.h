@@ -43,8 +43,7 @@ enum {
 enum {
     SMLA_IMPL_AUTO = 0,    /* tcgen05 kernel */
     SMLA_IMPL_SCALAR = 1,  /* fp32 CUDA-core kernel: slow, exact; a second opinion in tests */
-    SMLA_IMPL_TC = 2,      /* tcgen05/TMEM kernel, FP8 QK^T and PV */
-    SMLA_IMPL_TC_PAIR = 3  /* the same numerics with the score work shared inside a two-CTA cluster (experimental) */
+    SMLA_IMPL_TC = 2       /* tcgen05/TMEM kernel on a pair of SMs (cta_group::2), FP8 QK^T and PV */
 };
 
 /*

@@ -8,7 +8,7 @@ from ctypes import c_char_p, c_float, c_int, c_int32, c_int64, c_size_t, c_void_
 
 from .build import LIB_PATH
 
-IMPL_AUTO, IMPL_SCALAR, IMPL_TC, IMPL_TC_PAIR = 0, 1, 2, 3
+IMPL_AUTO, IMPL_SCALAR, IMPL_TC = 0, 1, 2
 LAYOUT_V32, LAYOUT_MODEL1 = 0, 1
 
 _lib = None

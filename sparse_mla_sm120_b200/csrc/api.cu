@@ -25,7 +25,7 @@ int check_launch(const char* what) {
 
 static bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
-static int check_attn_common(const char* fn, const void* q, const void* kv, const int32_t* indices,
+int check_attn_common(const char* fn, const void* q, const void* kv, const int32_t* indices,
                              const void* out, const float* out_lse, int num_tokens, int num_heads, int topk,
                              int page_block_size, int64_t stride, int impl) {
     if (!q || !kv || !indices || !out || !out_lse) return set_error(SMLA_E_NULL, "%s: null pointer argument", fn);
@@ -39,7 +39,7 @@ static int check_attn_common(const char* fn, const void* q, const void* kv, cons
     if (stride < (int64_t)page_block_size * ROW_BYTES)
         return set_error(SMLA_E_SHAPE, "%s: page stride %lld smaller than %d rows of %d bytes", fn,
                          (long long)stride, page_block_size, ROW_BYTES);
-    if (impl != SMLA_IMPL_AUTO && impl != SMLA_IMPL_SCALAR && impl != SMLA_IMPL_TC && impl != SMLA_IMPL_TC_PAIR)
+    if (impl != SMLA_IMPL_AUTO && impl != SMLA_IMPL_SCALAR && impl != SMLA_IMPL_TC)
         return set_error(SMLA_E_SHAPE, "%s: unknown impl %d", fn, impl);
     return 0;
 }
@@ -103,8 +103,7 @@ int smla_decode_splitkv(const void* q, const void* kv, const int32_t* indices,
     p.num_tokens = num_tokens; p.num_heads = num_heads; p.topk = topk; p.num_parts = num_sm_parts;
     p.page_block_size = page_block_size; p.block_stride = kv_block_stride_bytes; p.sm_scale = sm_scale;
     if (impl == SMLA_IMPL_SCALAR) return launch_attn_scalar(p, (cudaStream_t)stream);
-    if (impl == SMLA_IMPL_TC_PAIR) return launch_attn_pair(p, (cudaStream_t)stream);
-    return launch_attn_tc(p, (cudaStream_t)stream);
+    return launch_attn_pair(p, (cudaStream_t)stream);
 }
 
 int smla_combine(const float* o_accum, const float* lse_accum, void* out, float* out_lse,
@@ -140,9 +139,7 @@ static int decode_partial_common(const char* fn, const void* q, const void* kv, 
     p.num_tokens = num_tokens; p.num_heads = num_heads; p.topk = topk; p.num_parts = num_sm_parts;
     p.force_partial = 1;
     p.page_block_size = page_block_size; p.block_stride = kv_block_stride_bytes; p.sm_scale = sm_scale;
-    const int e = (impl == SMLA_IMPL_SCALAR) ? launch_attn_scalar(p, (cudaStream_t)stream)
-                  : (impl == SMLA_IMPL_TC_PAIR) ? launch_attn_pair(p, (cudaStream_t)stream)
-                                                : launch_attn_tc(p, (cudaStream_t)stream);
+    const int e = (impl == SMLA_IMPL_SCALAR) ? launch_attn_scalar(p, (cudaStream_t)stream) : launch_attn_pair(p, (cudaStream_t)stream);
     if (e) return e;
     return launch_combine_f32(o_accum, lse_accum, o_part, lse_part, num_splits, num_tokens, num_heads, slices, slice_stride,
                               (cudaStream_t)stream);
@@ -228,8 +225,7 @@ int smla_prefill(const void* q, const void* kv, const int32_t* indices,
     p.num_tokens = num_tokens; p.num_heads = num_heads; p.topk = topk; p.num_parts = num_tokens;
     p.page_block_size = page_block_size; p.block_stride = kv_block_stride_bytes; p.sm_scale = sm_scale;
     if (impl == SMLA_IMPL_SCALAR) return launch_attn_scalar(p, (cudaStream_t)stream);
-    if (impl == SMLA_IMPL_TC_PAIR) return launch_attn_pair(p, (cudaStream_t)stream);
-    return launch_attn_tc(p, (cudaStream_t)stream);
+    return launch_attn_pair(p, (cudaStream_t)stream);
 }
 
 static int check_ext(const char* fn, const void* q, const void* kv, const int32_t* indices, const void* extra_kv,

@@ -79,8 +79,8 @@ __device__ __forceinline__ uint32_t rescale_e4m3x4(uint32_t w, __half2 ratio) {
 // e4m3 value), which is far below the rounding step of the values that dominate a row.
 __device__ __forceinline__ uint32_t shift_down_e4m3x4(uint32_t w, uint32_t sub) {
     const uint32_t t = ((w & 0x7f7f7f7fu) | 0x80808080u) - sub;   // bit 7 of a byte survives iff its magnitude >= sub
-    const uint32_t m = t & 0x80808080u;
-    const uint32_t keep = (m - (m >> 7)) | m;                      // 0xff in the bytes that did not underflow
+    uint32_t keep;                                                 // every byte's bit 7 spread over the byte: 0xff where no underflow
+    asm("prmt.b32 %0, %1, %1, 0xba98;" : "=r"(keep) : "r"(t));     // (selector bit 3 = replicate the sign of the chosen byte)
     return (t & 0x7f7f7f7fu & keep) | (w & 0x80808080u);
 }
 // d * 8 in every byte for a ratio 2^-d (a power of two <= 1).

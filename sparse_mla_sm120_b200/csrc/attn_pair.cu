@@ -9,41 +9,47 @@
 //     heads against all 128 tokens (lanes 0-63: tokens 0-63, lanes 64-127: tokens 64-127).
 //   * P.V:    A = this CTA's P' (64 heads x 128 tokens, shared memory), B = V^T with the N = 256
 //     output dims of an MMA split between the CTAs: CTA r supplies dims [256 r, 256 r + 256) of
-//     all 128 tokens.  For its own tokens these are bytes it already holds (copied inside shared
-//     memory into the V slots); for the partner's tokens it gathers the 256-byte half rows.
-//     Each CTA accumulates O for its heads over all 512 dims (lanes 0-63: dims 0-255, lanes
-//     64-127: dims 256-511; 256 columns of tensor memory).
-// Per token a CTA pair takes in 656 + 2 x 256 bytes instead of 2 x 656, and no score or softmax
-// work is duplicated.
+//     all 128 tokens.  These bytes are copied out of the K stages, where the rows already lie in
+//     the layout the MMA wants: each CTA sends, with bulk shared-memory copies, the quarter tiles
+//     of its own 64 rows to its own V slots and to its partner's (the destination CTA's barrier
+//     counts the bytes as they land).  Each CTA accumulates O for its heads over all 512 dims
+//     (lanes 0-63: dims 0-255, lanes 64-127: dims 256-511; 256 columns of tensor memory).
+// A gathered row enters ONE SM from L2 (656 bytes per token per pair instead of 2 x 656), and no
+// score or softmax work is duplicated.
 //
 // Numerics (the FP8 class of the reference's V32 kernels, which quantise Q and P to e4m3:
 // csrc/kernel/common/fp8_quant.cuh:44-103, csrc/kernel/decode/decode_v2_kernel.cuh:414-493):
 //   * Q no-PE is quantised to e4m3 with one power-of-two scale sq_h per head; Q RoPE stays bf16
 //     and is pre-divided by that scale.
-//   * K/V bytes are consumed as stored, re-expressed against ONE scale s per 128-token tile: the
-//     largest of the 4 x 128 scales of the tile's rows.  A 128-value block with a smaller scale is
-//     shifted down (a power-of-two division done on the exponent fields: exact while the shifted
-//     value stays a normal e4m3 number; a value that would fall below 2^-6 is cut to the subnormal
-//     grid, i.e. it is off by at most 2^-15 of the largest value the tile can hold, which is far
-//     below the e4m3 rounding step of the values that dominate a dot product).  K RoPE is
+//   * K/V bytes are consumed as stored, re-expressed against ONE scale s per half tile (the 64 rows
+//     one CTA gathered): the largest of the 4 x 64 scales of these rows.  A 128-value block with a
+//     smaller scale is shifted down (a power-of-two division done on the exponent fields: exact
+//     while the shifted value stays a normal e4m3 number; a value that would fall below 2^-6 is cut
+//     to the subnormal grid, i.e. it is off by at most 2^-15 of the largest value the half tile can
+//     hold, which is far below the e4m3 rounding step of the values that dominate a dot product).
+//     The shift happens in registers on the way from global to shared memory.  K RoPE is
 //     pre-divided by s.  One accumulator then holds S = (q . k) / (sq_h * s).
-//   * The tile scale of V is folded into the exponent: z = S*sq_h*s*sm_scale*log2e + log2(s),
+//   * The scale of V is folded into the exponent: z = S*sq_h*s*sm_scale*log2e + log2(s),
 //     P' = 2^(z - m) with m the (lazily updated) running maximum of z, so that
-//     O_acc = sum_t P'_t * Vfp8_t needs no per-tile scale; the denominator is tracked apart as
-//     l = sum over tiles of (sum_t P'_t) / s in fp32.  O = O_acc / l, LSE = log2(l) + m (base 2, as
-//     the reference).  With one scale per tile the softmax loops read nothing per token.
+//     O_acc = sum_t P'_t * Vfp8_t needs no scale; the denominator is tracked apart as
+//     l = sum over half tiles of (sum_t P'_t) / s in fp32.  O = O_acc / l, LSE = log2(l) + m (base 2,
+//     as the reference).  A softmax thread's 32 tokens lie in one half tile, so its loops read
+//     nothing per token.
 //   * P' is rounded to e4m3 (times 2^P_SHIFT); the accumulator is rescaled only when a row
 //     maximum grows by more than 2^RESCALE_TAU, which is exact because l and O share m.
 //   * Invalid entries (index < 0, position >= topk_length) are never loaded: their shared-memory
 //     rows are zero-filled and their weight is exactly 0 (NaN-safe, decode_v2_kernel.cuh:262-278).
 //
-// Warp roles (768 threads per CTA): warps 0-7 softmax + epilogue + Q quantisation (thread = one
+// Warp roles (640 threads per CTA): warps 0-7 softmax + epilogue + Q quantisation (thread = one
 // head x 32 tokens of a tile; the four warps that share 32 heads exchange row maxima through
-// shared memory), warps 8-11 gather issuers (16-byte cp.async, never waiting for data), warps
-// 12-19 tile fix-up (RoPE pre-division, uneven-scale rewrite, per-token scale triples, the copy
-// of own V bytes), warp 20 lane 0 issues the score MMAs and warp 21 lane 0 the P.V MMAs -- in
-// the even CTA only, which is also where the barriers that collect arrivals from both CTAs
-// live.  Completion of MMAs reaches both CTAs through one tcgen05.commit per CTA (no multicast).
+// shared memory).  Warps 8-15 gather: warp g brings rows [8 g, +8) of the CTA's 64 into a raw stage
+// with 16-byte asynchronous copies (two tiles of the CTA are in flight), reads them into registers,
+// the eight warps agree on the half tile's scale through shared memory, shift and store.  Warp 16 lane 0 issues the score MMAs
+// and warp 17 lane 0 the P.V MMAs -- in the even CTA only, which is also where the barriers that
+// collect arrivals from both CTAs live.  Warp
+// 19 lane 0 issues the bulk copies K stage -> V slots (own and partner's), sends the half tile's
+// scale record to the partner, waits for the V slots of its CTA to fill and passes that on (V full
+// to the even CTA, K stage free to both).  Completion of MMAs reaches both CTAs through one tcgen05.commit per CTA (no multicast).
 // Every wait is bounded; a wait that gives up records a code in status[] and the CTA drains and
 // exits.  Warps that meet at a named barrier leave the loop together (a warp whose wait gave up
 // still goes to the next named barrier, where all of them see the flag).
@@ -57,26 +63,24 @@ namespace {
 using namespace ptx;
 using namespace attn;
 
-constexpr int N_SM_WARPS = 8, N_PR_WARPS = 4, N_FX_WARPS = 8;
-constexpr int N_PRK_WARPS = 2;    // gather: 2 warps for the K part, 2 for the V part
-constexpr int N_FXK_WARPS = 4;    // fix-up: 4 warps for own rows, 4 for the partner's
-constexpr int FX_WARP0 = N_SM_WARPS + N_PR_WARPS;
-constexpr int MMA_WARP = FX_WARP0 + N_FX_WARPS;
-constexpr int PAIR_THREADS = (MMA_WARP + 4) * 32;
+constexpr int N_SM_WARPS = 8, N_G_WARPS = 8;
+constexpr int MMA_WARP = N_SM_WARPS + N_G_WARPS;
+constexpr int FWD_WARP = MMA_WARP + 3;
+constexpr int PROD_WARP0 = MMA_WARP + 4, N_P_WARPS = 4;      // copy issuers: warp p looks after the rows of gather warps 2 p and 2 p + 1
+constexpr int PAIR_THREADS = (PROD_WARP0 + N_P_WARPS) * 32;
 // Register budgets after the warpgroups trade registers.  setmaxnreg.inc can only draw on what the CTA
 // was launched with (PAIR_THREADS x REGS_LAUNCH), so the budgets must fit it or the increase would block
 // for ever; the launcher checks the compiled register count against REGS_LAUNCH before it launches.
-// With 48 registers the gather and fix-up loops spilled to local memory, which made every step of
-// theirs several times slower; the two MMA-issuing threads need few registers, so their warpgroup gives
-// up half of its allocation too.
-constexpr int REGS_LAUNCH = 80, REGS_SOFTMAX = 136, REGS_OTHER = 56, REGS_MMA = 40;
-static_assert(N_SM_WARPS * 32 * REGS_SOFTMAX + (N_PR_WARPS + N_FX_WARPS) * 32 * REGS_OTHER + 128 * REGS_MMA
+// A gather thread keeps 8 + 2 sixteen-byte pieces in flight; the MMA-issuing and copy threads need few
+// registers, so their warpgroup gives up more than half of its allocation.
+constexpr int REGS_LAUNCH = 80, REGS_SOFTMAX = 128, REGS_GATHER = 72, REGS_MMA = 40, REGS_PROD = 40;
+static_assert(N_SM_WARPS * 32 * REGS_SOFTMAX + N_G_WARPS * 32 * REGS_GATHER + 128 * REGS_MMA + N_P_WARPS * 32 * REGS_PROD
                   <= PAIR_THREADS * REGS_LAUNCH, "register budgets exceed what the CTA owns");
 static_assert(65536 / PAIR_THREADS / 8 * 8 == REGS_LAUNCH, "launch-time registers per thread");
 
 constexpr int TILE_N = 128;            // tokens per tile: two scheduler blocks, 64 rows gathered by each CTA
 constexpr int OWN_N = 64;
-constexpr int NK = 3, NV = 2;          // K stages (own rows) and V stages (V slots + scale triples)
+constexpr int NK = 2, NV = 1, NR = 2;  // K stages (own rows, MMA layout), V stages (V slots), raw stages (own rows as they lie in the cache)
 constexpr int P_SHIFT = 5;             // P' is stored as e4m3(P' * 2^P_SHIFT)
 constexpr float RESCALE_TAU = 3.0f;    // lazy-rescale threshold (log2 units); P' <= 2^TAU
 
@@ -86,26 +90,32 @@ constexpr uint32_t QR_OFF = 0;                       // Q RoPE bf16: [64 heads x
 constexpr uint32_t PB_OFF = QR_OFF + CHUNK;          // P' e4m3: 2 buffers x [64 heads x 128 tokens]
 constexpr uint32_t KS_OFF = PB_OFF + 2 * CHUNK;      // K stages
 constexpr uint32_t KS_ROPE = 4 * CHUNK;              //   RoPE of the own rows
-constexpr uint32_t KS_RAW = KS_ROPE + CHUNK;         //   [128 tokens x 16 B] the rows' 4 fp32 scales as gathered (own and partner rows)
-constexpr uint32_t KS_BYTES = KS_RAW + TILE_N * 16;  // 43008
+constexpr uint32_t KS_BYTES = KS_ROPE + CHUNK;       // 40960
 constexpr uint32_t VS_OFF = KS_OFF + NK * KS_BYTES;  // V stages
-constexpr uint32_t VSLOT = 32 * 128;                 //   slot (kb, nb): 32 tokens x 128 dims, at (2 kb + nb) * VSLOT
-constexpr uint32_t VS_RAW = 8 * VSLOT;               //   [128 tokens x 16 B] the rows' scales as gathered (all rows of the tile)
-constexpr uint32_t VS_INFO = VS_RAW + TILE_N * 16;   //   tile scale (s, log2 s, 1/s, 0) and the 128 validity bits of the tile
-constexpr uint32_t VS_BYTES = VS_INFO + 1024;        // 35840
-constexpr uint32_t XCH_OFF = VS_OFF + NV * VS_BYTES; // row-maximum exchange [2][4][64] fp32, then Q scales [64] fp32
+constexpr uint32_t VSLOT = 32 * 128;                 //   slot (kb, nb): 32 tokens x 128 dims, at (4 nb + kb) * VSLOT
+constexpr uint32_t VS_BYTES = 8 * VSLOT;             // 32768
+constexpr uint32_t RAW_OFF = VS_OFF + NV * VS_BYTES; // raw stages: [64 rows x 656 B] as they lie in the cache
+constexpr uint32_t RAW_BYTES = OWN_N * ROW_BYTES;    // 41984
+constexpr int INFO_RING = 8;                         // half-tile records outlive their K stage: the softmax reads them after the scores
+constexpr uint32_t INFO_OFF = RAW_OFF + NR * RAW_BYTES;  // [INFO_RING][2 halves] x 32 B: (s, log2 s, 1/s, 0) and the 64 validity bits of the half tile
+constexpr uint32_t GX_OFF = INFO_OFF + INFO_RING * 64; // [2][N_G_WARPS] x 8 B: per gather warp the largest scale and the validity bits of its rows
+constexpr uint32_t XCH_OFF = GX_OFF + 2 * N_G_WARPS * 8; // row-maximum exchange [2][4][64] fp32, then Q scales [64] fp32
 constexpr uint32_t XCH_BYTES = 2 * 4 * 64 * 4 + 64 * 4;
 constexpr uint32_t BAR_OFF = XCH_OFF + XCH_BYTES;
 // barriers (8 B each).  "P" barriers collect arrivals from both CTAs and are used in the even CTA only.
-constexpr int BAR_KLOADED = 0, BAR_KFULLP = BAR_KLOADED + NK, BAR_TRIP = BAR_KFULLP + NK, BAR_KEMPTY = BAR_TRIP + NK,
-              BAR_VLOADED = BAR_KEMPTY + NK, BAR_VFULLP = BAR_VLOADED + NV, BAR_VEMPTY = BAR_VFULLP + NV,
-              BAR_SREADY = BAR_VEMPTY + NV, BAR_SFREEP = BAR_SREADY + 2, BAR_PREADYP = BAR_SFREEP + 2,
-              BAR_PVDONE = BAR_PREADYP + 2, BAR_QREADYP = BAR_PVDONE + 2, NBAR = BAR_QREADYP + 1;
+constexpr int BAR_KSTORED = 0, BAR_KFULLP = BAR_KSTORED + NK, BAR_KEMPTY = BAR_KFULLP + NK,
+              BAR_VFULL = BAR_KEMPTY + NK, BAR_VFULLP = BAR_VFULL + NV, BAR_VEMPTY = BAR_VFULLP + NV,
+              BAR_INFO = BAR_VEMPTY + NV, BAR_SREADY = BAR_INFO + INFO_RING, BAR_SFREEP = BAR_SREADY + 2,
+              BAR_PREADYP = BAR_SFREEP + 2, BAR_PVDONE = BAR_PREADYP + 2, BAR_QREADYP = BAR_PVDONE + 2,
+              BAR_RAWFULL = BAR_QREADYP + 1, BAR_RAWEMPTY = BAR_RAWFULL + NR * N_P_WARPS, BAR_QSTAGE = BAR_RAWEMPTY + NR * N_P_WARPS,
+              BAR_QFREE = BAR_QSTAGE + 1, NBAR = BAR_QFREE + 1;
 constexpr uint32_t MISC_OFF = BAR_OFF + NBAR * 8;    // tmem base (4 B), abort flag (4 B)
 constexpr uint32_t SMEM_BYTES = MISC_OFF + 16;
 constexpr uint32_t SMEM_ALLOC = SMEM_BYTES + 1024;   // slack for the 1024-byte alignment
 static_assert(SMEM_ALLOC <= 227 * 1024, "shared memory budget");
 static_assert(KS_BYTES % 1024 == 0 && VS_BYTES % 1024 == 0 && KS_OFF % 1024 == 0, "swizzled tiles need 1024-byte alignment");
+static_assert(NK * KS_BYTES >= OWN_N * D_QK * 2, "the K stages hold the staged Q rows of a CTA");
+static_assert(BAR_OFF % 8 == 0 && INFO_OFF % 16 == 0 && RAW_OFF % 16 == 0 && RAW_BYTES % 16 == 0, "alignment of barriers and bulk-copied records");
 
 constexpr uint32_t TMEM_COLS = 512;
 constexpr uint32_t TM_O = 0, TM_S = 256, TM_Q = 384;   // O 256 columns; score buffer b at 256 + 64 b; Q no-PE 128 columns
@@ -116,7 +126,7 @@ constexpr uint32_t IDESC_PV_F8 = instr_desc(FMT_E4M3, FMT_E4M3, false, true, 128
 constexpr uint32_t DESC_HI_SW128 = desc_hi(1024, (uint32_t)SWIZZLE_128B);
 
 // give-up codes reported through status[0]
-enum { W_KEMPTY = 21, W_KLOADED = 22, W_KFULL = 23, W_TRIP = 24, W_VEMPTY = 25, W_VLOADED = 26, W_VFULL = 27,
+enum { W_QSTAGE = 17, W_QFREE = 18, W_RAWEMPTY = 19, W_RAWFULL = 20, W_KEMPTY = 21, W_KSTORED = 22, W_KFULL = 23, W_INFO = 24, W_VEMPTY = 25, W_VFULL_CTA = 26, W_VFULL = 27,
        W_SREADY = 28, W_SFREE = 29, W_PREADY = 30, W_PVDONE = 31, W_QREADY = 32 };
 
 #ifdef SMLA_TRACE
@@ -147,22 +157,6 @@ __device__ int g_prof_block = 0;
 #define PROF(i)
 #endif
 
-// Scale of a tile and the validity bits of its 128 tokens from their gathered scale words ([128] float4 in
-// shared memory; a row that was not loaded has all-zero scales).  Every lane returns the same values.
-__device__ __forceinline__ float tile_scale(const uint8_t* raw, int lane, uint32_t (&valid)[4]) {
-    float m = 0.f;
-#pragma unroll
-    for (int j = 0; j < 4; ++j) {
-        const float4 s4 = *reinterpret_cast<const float4*>(raw + (32 * j + lane) * 16);
-        const float r = fmaxf(fmaxf(s4.x, s4.y), fmaxf(s4.z, s4.w));
-        valid[j] = __ballot_sync(0xffffffffu, r > 0.f);
-        m = fmaxf(m, r);
-    }
-#pragma unroll
-    for (int o = 16; o >= 1; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
-    return m;
-}
-
 __device__ __forceinline__ uint32_t swz(uint32_t row, uint32_t chunk16) { return row * 128u + ((chunk16 ^ (row & 7u)) << 4); }
 
 // ---------------------------------------------------------------------------------------------
@@ -191,17 +185,35 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PAIR_THREADS, 1) att
     const int heads_cta = (p.num_heads + 1) >> 1;     // heads per CTA
     const int head0 = (int)rank * heads_cta;
 
+    // The Q rows of the first request (this CTA's heads: one contiguous piece of global memory) come in by one bulk
+    // copy into the K stages, which are empty until the first tile has been gathered and shifted; the softmax warps
+    // then quantise Q out of shared memory instead of waiting for global memory several times in a row.
+    const int last_req = min(meta.end_req, p.num_tokens - 1);
+    const int live_heads = min(heads_cta, max(p.num_heads - head0, 0));
+    Work w_first;
+    const bool q_staged = meta.begin_req <= last_req && live_heads > 0 && get_work(p, meta, meta.begin_req, w_first);
+
     if (tid == 0) {
+        mbar_init(bar(BAR_QSTAGE), 1);
+        mbar_init(bar(BAR_QFREE), N_SM_WARPS);
         for (int s = 0; s < NK; ++s) {
-            mbar_init(bar(BAR_KLOADED + s), N_PRK_WARPS * 32);   // one arrive per issuer thread, when its copies have landed
-            mbar_init(bar(BAR_KFULLP + s), 2 * N_FXK_WARPS);
-            mbar_init(bar(BAR_TRIP + s), N_FXK_WARPS);
-            mbar_init(bar(BAR_KEMPTY + s), 1 + N_FXK_WARPS);     // the score MMAs have read the stage and the own V bytes are copied
+            mbar_init(bar(BAR_KSTORED + s), N_G_WARPS);          // this CTA's rows of the stage are in shared memory
+            mbar_init(bar(BAR_KFULLP + s), 2 * N_G_WARPS);       // both CTAs' rows are
+            mbar_init(bar(BAR_KEMPTY + s), 3);                   // the score MMAs have read the stage; both CTAs' V slots hold its copies
         }
         for (int s = 0; s < NV; ++s) {
-            mbar_init(bar(BAR_VLOADED + s), (N_PR_WARPS - N_PRK_WARPS) * 32);
-            mbar_init(bar(BAR_VFULLP + s), 2 * N_FX_WARPS);
+            mbar_init(bar(BAR_VFULL + s), 1);                    // + the bytes of the four quarter tiles copied into this CTA's slots
+            mbar_init(bar(BAR_VFULLP + s), 2);
             mbar_init(bar(BAR_VEMPTY + s), 1);
+        }
+        for (int s = 0; s < INFO_RING; ++s) mbar_init(bar(BAR_INFO + s), 1);   // + the bytes of the partner's record
+        for (int s = 0; s < NR * N_P_WARPS; ++s) {
+#ifdef SMLA_ROWS_BULK
+            mbar_init(bar(BAR_RAWFULL + s), 1);
+#else
+            mbar_init(bar(BAR_RAWFULL + s), 32);       // a copy warp's 16 rows of a raw stage: one arrive per lane when its copies have landed
+#endif
+            mbar_init(bar(BAR_RAWEMPTY + s), 2);       // the two gather warps that read these rows have them in registers
         }
         for (int b = 0; b < 2; ++b) {
             mbar_init(bar(BAR_SREADY + b), 1);
@@ -212,6 +224,12 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PAIR_THREADS, 1) att
         mbar_init(bar(BAR_QREADYP), 2 * N_SM_WARPS);
         *abort_flag = 0;
         mbar_init_fence();
+        if (q_staged) {
+            const uint32_t bytes = (uint32_t)live_heads * D_QK * 2;
+            mbar_arrive_expect_tx(bar(BAR_QSTAGE), bytes);
+            bulk_copy_g2s(base + KS_OFF, reinterpret_cast<unsigned long long>(p.q + ((size_t)meta.begin_req * p.num_heads + head0) * D_QK),
+                          bytes, bar(BAR_QSTAGE));
+        }
     }
     if (warp == MMA_WARP) {
         tmem_alloc_pair(base + MISC_OFF, TMEM_COLS);
@@ -225,19 +243,10 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PAIR_THREADS, 1) att
     const uint32_t tmem = *tmem_slot;
     auto barp = [&](int i) -> uint32_t { return mapa_shared(bar(i), 0); };   // the even CTA's copy of barrier i
 
-    const int last_req = min(meta.end_req, p.num_tokens - 1);
-    // The softmax warps read Q before anything else can start: the other warps, idle until then, ask L2 for this
-    // CTA's half of the first request's Q rows (128-byte lines).
-    if (warp >= N_SM_WARPS && warp < MMA_WARP && meta.begin_req <= last_req) {
-        const uint8_t* q0 = reinterpret_cast<const uint8_t*>(p.q + ((size_t)meta.begin_req * p.num_heads + head0) * D_QK);
-        const int lines = (min(heads_cta, max(p.num_heads - head0, 0)) * D_QK * 2 + 127) >> 7;
-        for (int i = tid - N_SM_WARPS * 32; i < lines; i += (MMA_WARP - N_SM_WARPS) * 32)
-            asm volatile("prefetch.global.L2 [%0];" ::"l"(q0 + (size_t)i * 128));
-    }
-
     if (warp < N_SM_WARPS) setmaxnreg_inc<REGS_SOFTMAX>();
-    else if (warp < MMA_WARP) setmaxnreg_dec<REGS_OTHER>();
-    else setmaxnreg_dec<REGS_MMA>();
+    else if (warp < MMA_WARP) setmaxnreg_dec<REGS_GATHER>();
+    else if (warp < PROD_WARP0) setmaxnreg_dec<REGS_MMA>();
+    else setmaxnreg_dec<REGS_PROD>();
     TRACE(7, 0);
 
     if (warp < N_SM_WARPS) {
@@ -268,13 +277,18 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PAIR_THREADS, 1) att
             // group, which is also how it loads them (16 bytes of bf16 per row and block).
             {
                 const int g = lane >> 2, c4 = lane & 3;
+                const bool from_smem = q_staged && req == meta.begin_req;
+                if (from_smem && !dead) dead = !mbar_wait_hot(bar(BAR_QSTAGE), 0u, abort_flag, W_QSTAGE);
+                // row (head0 + r) of the request's Q, wherever it lies
+                const __nv_bfloat16* qrows = from_smem ? reinterpret_cast<const __nv_bfloat16*>(sm + KS_OFF) - (size_t)head0 * D_QK
+                                                       : p.q + (size_t)req * p.num_heads * D_QK;
 #pragma unroll 1
                 for (int hf = 0; hf < 2; ++hf) {
                     const int r_a = grp * 32 + 16 * hf + g, r_b = r_a + 8;      // head rows inside the CTA
                     const bool v_a = !dead && r_a < heads_cta && head0 + r_a < p.num_heads;
                     const bool v_b = !dead && r_b < heads_cta && head0 + r_b < p.num_heads;
-                    const __nv_bfloat16* src_a = p.q + ((size_t)req * p.num_heads + (v_a ? head0 + r_a : 0)) * D_QK + ch * 256 + c4 * 8;
-                    const __nv_bfloat16* src_b = p.q + ((size_t)req * p.num_heads + (v_b ? head0 + r_b : 0)) * D_QK + ch * 256 + c4 * 8;
+                    const __nv_bfloat16* src_a = qrows + (size_t)(head0 + (v_a ? r_a : 0)) * D_QK + ch * 256 + c4 * 8;
+                    const __nv_bfloat16* src_b = qrows + (size_t)(head0 + (v_b ? r_b : 0)) * D_QK + ch * 256 + c4 * 8;
                     // two passes over the rows' bytes (the second is served by L1/L2): keeping a 16-row group in
                     // registers between the maxima and the quantisation spilled
                     auto absmax8 = [](const uint4& a) {
@@ -284,8 +298,8 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PAIR_THREADS, 1) att
                     float am_a = 0.f, am_b = 0.f;
 #pragma unroll
                     for (int i = 0; i < 8; ++i) {
-                        const uint4 xa = v_a ? __ldg(reinterpret_cast<const uint4*>(src_a + 32 * i)) : make_uint4(0, 0, 0, 0);
-                        const uint4 xb = v_b ? __ldg(reinterpret_cast<const uint4*>(src_b + 32 * i)) : make_uint4(0, 0, 0, 0);
+                        const uint4 xa = v_a ? *reinterpret_cast<const uint4*>(src_a + 32 * i) : make_uint4(0, 0, 0, 0);
+                        const uint4 xb = v_b ? *reinterpret_cast<const uint4*>(src_b + 32 * i) : make_uint4(0, 0, 0, 0);
                         am_a = fmaxf(am_a, absmax8(xa)); am_b = fmaxf(am_b, absmax8(xb));
                     }
                     am_a = fmaxf(am_a, __shfl_xor_sync(0xffffffffu, am_a, 1)); am_b = fmaxf(am_b, __shfl_xor_sync(0xffffffffu, am_b, 1));
@@ -305,8 +319,8 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PAIR_THREADS, 1) att
                             uint32_t wq[16];
 #pragma unroll
                             for (int kk = 0; kk < 4; ++kk) {
-                                const uint4 a = v_a ? __ldg(reinterpret_cast<const uint4*>(src_a + 32 * (4 * h4 + kk))) : make_uint4(0, 0, 0, 0);
-                                const uint4 b4 = v_b ? __ldg(reinterpret_cast<const uint4*>(src_b + 32 * (4 * h4 + kk))) : make_uint4(0, 0, 0, 0);
+                                const uint4 a = v_a ? *reinterpret_cast<const uint4*>(src_a + 32 * (4 * h4 + kk)) : make_uint4(0, 0, 0, 0);
+                                const uint4 b4 = v_b ? *reinterpret_cast<const uint4*>(src_b + 32 * (4 * h4 + kk)) : make_uint4(0, 0, 0, 0);
                                 wq[4 * kk + 0] = pack_e4m3x4(bf16lo(a.x) * ia, bf16hi(a.x) * ia, bf16lo(a.y) * ia, bf16hi(a.y) * ia);
                                 wq[4 * kk + 1] = pack_e4m3x4(bf16lo(a.z) * ia, bf16hi(a.z) * ia, bf16lo(a.w) * ia, bf16hi(a.w) * ia);
                                 wq[4 * kk + 2] = pack_e4m3x4(bf16lo(b4.x) * ib, bf16hi(b4.x) * ib, bf16lo(b4.y) * ib, bf16hi(b4.y) * ib);
@@ -326,7 +340,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PAIR_THREADS, 1) att
                         const int hr = grp * 32 + rl;
                         uint4 c = make_uint4(0, 0, 0, 0);
                         if (hr < heads_cta && head0 + hr < p.num_heads)
-                            c = __ldg(reinterpret_cast<const uint4*>(p.q + ((size_t)req * p.num_heads + head0 + hr) * D_QK + D_NOPE + (lane & 7) * 8));
+                            c = *reinterpret_cast<const uint4*>(qrows + (size_t)(head0 + hr) * D_QK + D_NOPE + (lane & 7) * 8);
                         const __nv_bfloat162 f = __float2bfloat162_rn(__uint_as_float(0x7f000000u - __float_as_uint(sqv[hr])));   // 1/sq
                         c.x = mul_bf16x2(c.x, f); c.y = mul_bf16x2(c.y, f); c.z = mul_bf16x2(c.z, f); c.w = mul_bf16x2(c.w, f);
                         *reinterpret_cast<uint4*>(sm + QR_OFF + swz((uint32_t)hr, (uint32_t)lane & 7u)) = c;
@@ -337,6 +351,8 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PAIR_THREADS, 1) att
                     tmem_wait_st();
                     tc_fence_before();     // also orders the previous epilogue's TMEM reads before the next MMAs
                 }
+                __syncwarp();
+                if (from_smem && lane == 0) mbar_arrive(bar(BAR_QFREE));   // this warp has read the staged rows for the last time
             }
             if (named_bar_or(1 + grp, 128, dead || *abort_flag != 0)) { stop = true; break; }
             TRACE(2, it);
@@ -349,15 +365,15 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PAIR_THREADS, 1) att
             float l_run = 0.f;         // this thread's share of the sum of P'/s (scaled by 2^P_SHIFT)
             float x_max = -INFINITY;   // this thread's share of the maximum of the scaled logits (max_logits output)
             for (int j = 0; j < nst; ++j, ++it) {
-                const uint32_t b = it & 1u, vs = it % NV;
+                const uint32_t b = it & 1u;
                 float z[32];
                 float mx_loc = -INFINITY, inv_tile = 0.f;
-                const uint8_t* info = sm + VS_OFF + vs * VS_BYTES + VS_INFO;
+                const uint8_t* info = sm + INFO_OFF + (it & (INFO_RING - 1)) * 64 + thalf * 32;   // the record of this thread's half tile
                 PROF(0);
                 if (!dead) dead = !mbar_wait_hot(bar(BAR_SREADY + b), (it >> 1) & 1u, abort_flag, W_SREADY);
                 PROF(1);
                 TRACE(10, it);
-                if (!dead) dead = !mbar_wait_hot(bar(BAR_TRIP + (it % NK)), (it / NK) & 1u, abort_flag, W_TRIP);
+                if (!dead) dead = !mbar_wait_hot(bar(BAR_INFO + (it & (INFO_RING - 1))), (it / INFO_RING) & 1u, abort_flag, W_INFO);
                 PROF(2);
                 if (!dead) {
                     tc_fence_after();
@@ -368,8 +384,8 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PAIR_THREADS, 1) att
                     tc_fence_before();
                     __syncwarp();
                     if (lane == 0) mbar_arrive_remote(barp(BAR_SFREEP + b));   // the score buffer may be overwritten
-                    const float4 ti = *reinterpret_cast<const float4*>(info);                 // (s, log2 s, 1/s, 0) of the tile
-                    const uint32_t valid = reinterpret_cast<const uint32_t*>(info + 16)[2 * thalf + ch];   // this thread's 32 tokens
+                    const float4 ti = *reinterpret_cast<const float4*>(info);                 // (s, log2 s, 1/s, 0) of the half tile
+                    const uint32_t valid = reinterpret_cast<const uint32_t*>(info + 16)[ch];  // this thread's 32 tokens
                     const float c_tile = ti.x * my_sqc, off = ti.y;
                     inv_tile = ti.z;
                     float mx0 = -INFINITY, mx1 = -INFINITY;
@@ -535,280 +551,115 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PAIR_THREADS, 1) att
                 TRACE(4, it);
             }
         }
-    } else if (warp < FX_WARP0) {
-        // =================================================================== gather issuers
-        // Warps 8-9 gather the K part of every tile (this CTA's 64 rows: the 512 no-PE bytes as one coalesced
-        // 512-byte request per row, the RoPE bytes, and the scale words of these rows and of the partner's),
-        // warps 10-11 the V part (bytes [256 r, +256) of the partner's rows into the V slots, and their scale
-        // words).  Each of the two kinds waits only for its own stage to be free, so the V part of a tile
-        // starts as soon as the P.V two tiles back has completed.  Nothing here waits for data; rows without
-        // an entry are zero-filled.  A warp covers 32 rows in two passes of 16: lanes 0-15 hold the row
-        // pointers of this CTA's rows, lanes 16-31 those of the partner's.
-        const int pw = warp - N_SM_WARPS;
-        const bool k_role = pw < N_PRK_WARPS;
-        const int rows0 = (k_role ? pw : pw - N_PRK_WARPS) * 32;     // first of this warp's 32 rows
-        const int peer = lane >> 4;                                  // lanes 16-31 look after the partner's rows
+    } else if (warp < MMA_WARP) {
+        // =================================================================== gather
+        // Warp gw reads rows [8 gw, +8) of this CTA's 64 rows of every tile from the raw stage into registers: per
+        // row one 16-byte piece of the 512 no-PE bytes per lane, plus (spread over the lanes) the rows' RoPE bytes
+        // and scale words.  The eight warps then agree on the half tile's scale, every lane shifts its pieces
+        // onto it and stores them in the layout the MMAs read.
+        const int gw = warp - N_SM_WARPS;
+        const int blk = lane >> 3;                                   // 128-value block of this lane's piece
         const int pbs_shift = (p.page_block_size & (p.page_block_size - 1)) == 0 ? __ffs(p.page_block_size) - 1 : -1;
-        const unsigned long long kv_u = reinterpret_cast<unsigned long long>(p.kv);
+        float2* gx = reinterpret_cast<float2*>(sm + GX_OFF);         // [2][N_G_WARPS]
         uint32_t it = 0;
-        bool ok = true;
-        for (int req = meta.begin_req; req <= last_req && ok; ++req) {
+        bool ok = true, stop = false;
+        for (int req = meta.begin_req; req <= last_req && !stop; ++req) {
             Work w;
             if (!get_work(p, meta, req, w)) continue;
             const int nst = (w.nblk + 1) >> 1;
             const int32_t* idx_row = p.indices + (size_t)req * p.topk;
             const int lim = min(w.len, (w.blk0 + w.nblk) * BLOCK_N);
-            // index of (tile j, pass ps) for this lane: row rows0 + 16 ps + lane % 16 of this CTA or of the partner
-            auto fetch_idx = [&](int j, int ps) -> int {
-                const int n = (peer ? (1 - (int)rank) : (int)rank) * OWN_N + rows0 + 16 * ps + (lane & 15);
-                const int pos = w.blk0 * BLOCK_N + j * TILE_N + n;
+            auto fetch_idx = [&](int j) -> int {                     // row 8 gw + lane % 8 of tile j
+                const int pos = w.blk0 * BLOCK_N + j * TILE_N + (int)rank * OWN_N + gw * 8 + (lane & 7);
                 return (j < nst && pos < lim) ? __ldg(idx_row + pos) : -1;
             };
-            auto row_ptr = [&](int idx) -> unsigned long long {
-                if (idx < 0) return 0ull;      // rows without an entry travel as a null source: their copies zero-fill
-                const unsigned u = (unsigned)idx;
-                return reinterpret_cast<unsigned long long>(
-                    (pbs_shift >= 0)
-                        ? p.kv + (int64_t)(u >> pbs_shift) * p.block_stride + (int64_t)(u & (unsigned)(p.page_block_size - 1)) * ROW_BYTES
-                        : kv_row_ptr(p.kv, idx, p.page_block_size, p.block_stride));
-            };
-            int idx_a = fetch_idx(0, 0), idx_b = fetch_idx(0, 1);           // this tile, passes 0 and 1
-            int nxt_a = fetch_idx(1, 0), nxt_b = fetch_idx(1, 1);           // next tile
+            // Which of the warp's rows have an entry (the rows themselves are brought in by the copy warps).
+            int idx_cur = fetch_idx(0), idx_nxt = fetch_idx(1);
 #pragma unroll 1
-            for (int k = 0; k < nst && ok; ++k) {
-                const uint32_t t_it = it + k;
-                const unsigned long long src_a = row_ptr(idx_a), src_b = row_ptr(idx_b);
-                idx_a = nxt_a; idx_b = nxt_b;
-                nxt_a = fetch_idx(k + 2, 0); nxt_b = fetch_idx(k + 2, 1);
-                if (k_role) {
-                    const uint32_t ks = t_it % NK;
-                    if (t_it >= NK) {
-                        ok = mbar_wait_hot(bar(BAR_KEMPTY + ks), ((t_it / NK) - 1) & 1u, abort_flag, W_KEMPTY);
-                        if (!ok) break;
-                    }
-                    const uint32_t kbase = base + KS_OFF + ks * KS_BYTES;
-#pragma unroll
-                    for (int ps = 0; ps < 2; ++ps) {
-                        const unsigned long long my_src_u = ps ? src_b : src_a;
-                        const int row0 = rows0 + 16 * ps;
-#pragma unroll
-                        for (int hb = 0; hb < 2; ++hb) {       // two batches of 8 rows keep the register count low
-                            unsigned long long srcs[8];
-#pragma unroll
-                            for (int i = 0; i < 8; ++i) srcs[i] = __shfl_sync(0xffffffffu, my_src_u, hb * 8 + i);
-#pragma unroll
-                            for (int i = 0; i < 8; ++i) {
-                                const int r = row0 + hb * 8 + i;
-                                const bool v = srcs[i] != 0ull;
-                                cp_async16_zfill(kbase + (lane >> 3) * CHUNK + swz((uint32_t)r, (uint32_t)lane & 7u),
-                                                 reinterpret_cast<const uint8_t*>(v ? srcs[i] + lane * 16 : kv_u), v ? 16u : 0u);
-                            }
-                        }
-#pragma unroll
-                        for (int g = 0; g < 4; ++g) {
-                            const unsigned long long rs = __shfl_sync(0xffffffffu, my_src_u, g * 4 + (lane >> 3));
-                            const int r = row0 + g * 4 + (lane >> 3);
-                            const bool v = rs != 0ull;
-                            cp_async16_zfill(kbase + KS_ROPE + swz((uint32_t)r, (uint32_t)lane & 7u),
-                                             reinterpret_cast<const uint8_t*>(v ? rs + ROPE_OFF + (lane & 7) * 16 : kv_u), v ? 16u : 0u);
-                        }
-                        {
-                            const int n = (peer ? (1 - (int)rank) : (int)rank) * OWN_N + row0 + (lane & 15);   // token index inside the tile
-                            const bool v = my_src_u != 0ull;
-                            cp_async16_zfill(kbase + KS_RAW + n * 16, reinterpret_cast<const uint8_t*>(v ? my_src_u + SCALE_OFF : kv_u), v ? 16u : 0u);
-                        }
-                    }
-                    cp_async_arrive_noinc(bar(BAR_KLOADED + ks));
-                } else {
-                    const uint32_t vs = t_it % NV;
-                    if (t_it >= NV) {
-                        ok = mbar_wait_hot(bar(BAR_VEMPTY + vs), ((t_it / NV) - 1) & 1u, abort_flag, W_VEMPTY);
-                        if (!ok) break;
-                    }
-                    const uint32_t vbase = base + VS_OFF + vs * VS_BYTES;
-                    const uint32_t piece = lane & 15;                       // 16-byte piece of the 256-byte half row
-#pragma unroll
-                    for (int ps = 0; ps < 2; ++ps) {
-                        const unsigned long long src_u = ps ? src_b : src_a;
-                        const int row0 = rows0 + 16 * ps;
-#pragma unroll
-                        for (int i = 0; i < 8; ++i) {
-                            const int r = row0 + 2 * i + peer;                  // partner's row (two rows per instruction)
-                            const unsigned long long s = __shfl_sync(0xffffffffu, src_u, 16 + 2 * i + peer);
-                            const uint32_t slot = ((2u * (1u - rank) + (uint32_t)(r >> 5)) * 2u + (piece >> 3)) * VSLOT;
-                            const bool v = s != 0ull;
-                            cp_async16_zfill(vbase + slot + swz((uint32_t)r & 31u, piece & 7u),
-                                             reinterpret_cast<const uint8_t*>(v ? s + 256u * rank + piece * 16u : kv_u), v ? 16u : 0u);
-                        }
-                        {   // scale words of the tile's rows: this CTA's (lanes 0-15) and the partner's (lanes 16-31)
-                            const int n = (peer ? (1 - (int)rank) : (int)rank) * OWN_N + row0 + (lane & 15);
-                            const bool v = src_u != 0ull;
-                            cp_async16_zfill(vbase + VS_RAW + n * 16, reinterpret_cast<const uint8_t*>(v ? src_u + SCALE_OFF : kv_u), v ? 16u : 0u);
-                        }
-                    }
-                    cp_async_arrive_noinc(bar(BAR_VLOADED + vs));
-                }
-            }
-            it += nst;
-        }
-        cp_async_wait_all();
-    } else if (warp < FX_WARP0 + N_FXK_WARPS) {
-        // =================================================================== tile fix-up, own rows
-        // Warp kf owns rows [16*kf, +16) of this CTA's rows (two groups of 8).  First: RoPE pre-division and
-        // uneven-scale rewrite (-> the score MMAs may start).  Then, once the V stage of the tile is free,
-        // the scale triples of its 32 tokens (its own rows and the same rows of the partner) and the copy of
-        // its rows' V bytes into the V slots (-> the K stage may be refilled).
-        const int kf = warp - FX_WARP0;
-        const int blk = lane >> 3;
-        uint32_t it = 0;
-        bool ok = true;
-        for (int req = meta.begin_req; req <= last_req && ok; ++req) {
-            Work w;
-            if (!get_work(p, meta, req, w)) continue;
-            const int nst = (w.nblk + 1) >> 1;
-#pragma unroll 1
-            for (int k = 0; k < nst && ok; ++k) {
-                const uint32_t t_it = it + k, ks = t_it % NK, vs = t_it % NV;
+            for (int k = 0; k < nst; ++k) {
+                const uint32_t t_it = it + k, ks = t_it % NK, rs = t_it % NR;
                 PROF(0);
-                ok = mbar_wait_hot(bar(BAR_KLOADED + ks), (t_it / NK) & 1u, abort_flag, W_KLOADED);
-                if (!ok) break;
+                if (ok) ok = mbar_wait_hot(bar(BAR_RAWFULL + rs * N_P_WARPS + (gw >> 1)), (t_it / NR) & 1u, abort_flag, W_RAWFULL);
                 PROF(1);
-                TRACE(30, t_it);
-                uint8_t* kp = sm + KS_OFF + ks * KS_BYTES;
-                uint8_t* vp = sm + VS_OFF + vs * VS_BYTES;
-                uint32_t valid[4];
-                const float s_tile = tile_scale(kp + KS_RAW, lane, valid);
-                const float inv_tile = (s_tile > 0.f) ? __uint_as_float(0x7f000000u - __float_as_uint(s_tile)) : 0.f;
-                const __nv_bfloat162 rope_f = __float2bfloat162_rn(inv_tile);
-                // RoPE of rows [16 kf, +16), pre-divided by the tile scale: 4 passes of 4 rows x 8 chunks
+                const uint32_t vbits = __ballot_sync(0xffffffffu, idx_cur >= 0) & 0xffu;
+                idx_cur = idx_nxt;
+                idx_nxt = fetch_idx(k + 2);
+                const uint8_t* raw_rows = sm + RAW_OFF + rs * RAW_BYTES + (gw * 8) * ROW_BYTES;
+                uint4 nope[8], rp[2];
+                float sc = 0.f;
+                if (ok) {
 #pragma unroll
-                for (int g = 0; g < 4; ++g) {
-                    uint4* r4 = reinterpret_cast<uint4*>(kp + KS_ROPE + swz((uint32_t)(kf * 16 + g * 4 + (lane >> 3)), (uint32_t)lane & 7u));
-                    uint4 v = *r4;
-                    v.x = mul_bf16x2(v.x, rope_f); v.y = mul_bf16x2(v.y, rope_f);
-                    v.z = mul_bf16x2(v.z, rope_f); v.w = mul_bf16x2(v.w, rope_f);
-                    *r4 = v;
+                    for (int i = 0; i < 8; ++i)
+                        nope[i] = ((vbits >> i) & 1u) ? *reinterpret_cast<const uint4*>(raw_rows + i * ROW_BYTES + lane * 16) : make_uint4(0, 0, 0, 0);
+#pragma unroll
+                    for (int u = 0; u < 2; ++u) {                            // RoPE piece lane % 8 of rows lane / 8 and lane / 8 + 4
+                        const int r = (lane >> 3) + 4 * u;
+                        rp[u] = ((vbits >> r) & 1u) ? *reinterpret_cast<const uint4*>(raw_rows + r * ROW_BYTES + ROPE_OFF + (lane & 7) * 16)
+                                                    : make_uint4(0, 0, 0, 0);
+                    }
+                    if ((vbits >> (lane >> 2)) & 1u)                         // scale lane % 4 of row lane / 4
+                        sc = *reinterpret_cast<const float*>(raw_rows + (lane >> 2) * ROW_BYTES + SCALE_OFF + (lane & 3) * 4);
+                } else {
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) nope[i] = make_uint4(0, 0, 0, 0);
+                    rp[0] = rp[1] = make_uint4(0, 0, 0, 0);
                 }
-                // 128-value blocks whose scale is below the tile scale are shifted onto the tile scale.  Row by row,
-                // lane l looks after 16-byte chunk l of the row's 512 bytes (block l / 8); no branches between rows,
-                // so that the loads of several rows are in flight together.
-#pragma unroll 1
-                for (int i0 = 0; i0 < 16; i0 += 4) {      // four rows at a time: their loads are issued before any store
-                    uint32_t sub[4];
-                    uint4 v[4];
-                    uint4* q4[4];
+                float wm = sc;
 #pragma unroll
-                    for (int u = 0; u < 4; ++u) {
-                        const int row = kf * 16 + i0 + u;
-                        const float sc = *reinterpret_cast<const float*>(kp + KS_RAW + (rank * OWN_N + row) * 16 + blk * 4);
-                        sub[u] = (sc > 0.f) ? shift_bytes_of_ratio(sc * inv_tile) : 0u;      // 0 for a block that is at the tile scale
-                        q4[u] = reinterpret_cast<uint4*>(kp + blk * CHUNK + swz((uint32_t)row, (uint32_t)lane & 7u));
-                    }
-#pragma unroll
-                    for (int u = 0; u < 4; ++u) if (sub[u] != 0u) v[u] = *q4[u];
-#pragma unroll
-                    for (int u = 0; u < 4; ++u) {
-                        if (sub[u] != 0u) {
-                            v[u].x = shift_down_e4m3x4(v[u].x, sub[u]); v[u].y = shift_down_e4m3x4(v[u].y, sub[u]);
-                            v[u].z = shift_down_e4m3x4(v[u].z, sub[u]); v[u].w = shift_down_e4m3x4(v[u].w, sub[u]);
-                            *q4[u] = v[u];
-                        }
-                    }
+                for (int o = 16; o >= 1; o >>= 1) wm = fmaxf(wm, __shfl_xor_sync(0xffffffffu, wm, o));
+                if (lane == 0) {
+                    gx[(t_it & 1u) * N_G_WARPS + gw] = make_float2(wm, __uint_as_float(vbits));
+                    // the maximum needed the last shared-memory load of every lane (they return in order): the warp's rows
+                    // have left the raw stage
+                    mbar_arrive(bar(BAR_RAWEMPTY + rs * N_P_WARPS + (gw >> 1)));
                 }
                 PROF(2);
-                fence_proxy_async();
-                __syncwarp();
-                if (lane == 0) mbar_arrive_remote(barp(BAR_KFULLP + ks));
+                if (ok && t_it >= NK) ok = mbar_wait_hot(bar(BAR_KEMPTY + ks), ((t_it / NK) - 1) & 1u, abort_flag, W_KEMPTY);
+                if (ok && t_it < NK && q_staged) ok = mbar_wait_hot(bar(BAR_QFREE), 0u, abort_flag, W_QFREE);   // the K stages held Q until now
                 PROF(3);
-                TRACE(31, t_it);
-                // the V stage of this tile is free once the P.V NV tiles back has completed
-                if (t_it >= NV) {
-                    ok = mbar_wait_hot(bar(BAR_VEMPTY + vs), ((t_it / NV) - 1) & 1u, abort_flag, W_VEMPTY);
-                    if (!ok) break;
-                }
+                if (named_bar_or(3, N_G_WARPS * 32, !ok || *abort_flag != 0)) { stop = true; break; }
                 PROF(4);
-                TRACE(32, t_it);
-                // the tile's scale and validity bits for the softmax warps
-                if (kf == 0 && lane == 0) {
-                    *reinterpret_cast<float4*>(vp + VS_INFO) =
-                        make_float4(s_tile, (s_tile > 0.f) ? (float)((int)(__float_as_uint(s_tile) >> 23) - 127) : -INFINITY, inv_tile, 0.f);
-                    *reinterpret_cast<uint4*>(vp + VS_INFO + 16) = make_uint4(valid[0], valid[1], valid[2], valid[3]);
-                }
-                // own V bytes: rows [16 kf, +16), this CTA's two chunks -> V slots (same swizzle)
+                // the half tile's scale and validity bits from the eight warps' records
+                const float2 g = gx[(t_it & 1u) * N_G_WARPS + (lane & 7)];
+                float s_half = g.x;
+                uint32_t vpart = __float_as_uint(g.y) << (8 * (lane & 3));
+                s_half = fmaxf(s_half, __shfl_xor_sync(0xffffffffu, s_half, 1)); vpart |= __shfl_xor_sync(0xffffffffu, vpart, 1);
+                s_half = fmaxf(s_half, __shfl_xor_sync(0xffffffffu, s_half, 2)); vpart |= __shfl_xor_sync(0xffffffffu, vpart, 2);
+                s_half = fmaxf(s_half, __shfl_xor_sync(0xffffffffu, s_half, 4));
+                const uint32_t vword1 = __shfl_sync(0xffffffffu, vpart, 4);      // rows 32-63 (lane 0 holds rows 0-31)
+                const float inv_half = (s_half > 0.f) ? __uint_as_float(0x7f000000u - __float_as_uint(s_half)) : 0.f;
+                const __nv_bfloat162 rope_f = __float2bfloat162_rn(inv_half);
+                uint8_t* kp = sm + KS_OFF + ks * KS_BYTES;
 #pragma unroll
-                for (int u = 0; u < 8; ++u) {
-                    const int pidx = lane + 32 * u;                    // 16 rows x 2 chunks x 8 pieces
-                    const uint32_t r = (uint32_t)(kf * 16 + (pidx >> 4)), nb = (uint32_t)(pidx >> 3) & 1u, c = (uint32_t)pidx & 7u;
-                    const uint4 v = *reinterpret_cast<const uint4*>(kp + (2u * rank + nb) * CHUNK + swz(r, c));
-                    *reinterpret_cast<uint4*>(vp + ((2u * rank + (r >> 5)) * 2u + nb) * VSLOT + swz(r & 31u, c)) = v;
+                for (int i = 0; i < 8; ++i) {
+                    const float sci = __shfl_sync(0xffffffffu, sc, 4 * i + blk);
+                    const uint32_t sub = (sci > 0.f) ? shift_bytes_of_ratio(sci * inv_half) : 0u;   // 0 for a block that is at the scale
+                    uint4 v = nope[i];      // no branch on sub: a shift by 0 is the identity, and a branch would keep the rows' chains apart
+                    v.x = shift_down_e4m3x4(v.x, sub); v.y = shift_down_e4m3x4(v.y, sub);
+                    v.z = shift_down_e4m3x4(v.z, sub); v.w = shift_down_e4m3x4(v.w, sub);
+                    *reinterpret_cast<uint4*>(kp + blk * CHUNK + swz((uint32_t)(gw * 8 + i), (uint32_t)lane & 7u)) = v;
+                }
+#pragma unroll
+                for (int u = 0; u < 2; ++u) {
+                    uint4 v = rp[u];
+                    v.x = mul_bf16x2(v.x, rope_f); v.y = mul_bf16x2(v.y, rope_f);
+                    v.z = mul_bf16x2(v.z, rope_f); v.w = mul_bf16x2(v.w, rope_f);
+                    *reinterpret_cast<uint4*>(kp + KS_ROPE + swz((uint32_t)(gw * 8 + (lane >> 3) + 4 * u), (uint32_t)lane & 7u)) = v;
+                }
+                if (gw == 0 && lane == 0) {      // this half tile's record: read by this CTA's softmax warps and sent to the partner's
+                    uint8_t* rec = sm + INFO_OFF + (t_it & (INFO_RING - 1)) * 64 + rank * 32;
+                    *reinterpret_cast<float4*>(rec) =
+                        make_float4(s_half, (s_half > 0.f) ? (float)((int)(__float_as_uint(s_half) >> 23) - 127) : -INFINITY, inv_half, 0.f);
+                    *reinterpret_cast<uint2*>(rec + 16) = make_uint2(vpart, vword1);
                 }
                 PROF(5);
                 fence_proxy_async();
                 __syncwarp();
                 if (lane == 0) {
-                    mbar_arrive(bar(BAR_TRIP + ks));
-                    mbar_arrive(bar(BAR_KEMPTY + ks));
-                    mbar_arrive_remote(barp(BAR_VFULLP + vs));
+                    mbar_arrive(bar(BAR_KSTORED + ks));
+                    mbar_arrive_remote(barp(BAR_KFULLP + ks));
                 }
                 PROF(6);
-                TRACE(33, t_it);
-            }
-            it += nst;
-        }
-    } else if (warp < MMA_WARP) {
-        // =================================================================== tile fix-up, partner's half rows
-        // Warp vf owns rows [16*vf, +16) of the partner's rows in the V slots: uneven-scale rewrite.
-        const int vf = warp - FX_WARP0 - N_FXK_WARPS;
-        uint32_t it = 0;
-        bool ok = true;
-        for (int req = meta.begin_req; req <= last_req && ok; ++req) {
-            Work w;
-            if (!get_work(p, meta, req, w)) continue;
-            const int nst = (w.nblk + 1) >> 1;
-#pragma unroll 1
-            for (int k = 0; k < nst && ok; ++k) {
-                const uint32_t t_it = it + k, vs = t_it % NV;
-                PROF(0);
-                ok = mbar_wait_hot(bar(BAR_VLOADED + vs), (t_it / NV) & 1u, abort_flag, W_VLOADED);
-                if (!ok) break;
-                PROF(1);
-                TRACE(34, t_it);
-                uint8_t* vp = sm + VS_OFF + vs * VS_BYTES;
-                uint32_t valid[4];
-                const float s_tile = tile_scale(vp + VS_RAW, lane, valid);
-                const float inv_tile = (s_tile > 0.f) ? __uint_as_float(0x7f000000u - __float_as_uint(s_tile)) : 0.f;
-                // The partner's half rows [16 vf, +16): two rows per pass; lane l looks after row l / 16 of the pair,
-                // block (l / 8) % 2 of this CTA's two, 16-byte chunk l % 8.
-#pragma unroll 1
-                for (int i0 = 0; i0 < 8; i0 += 4) {
-                    uint32_t sub[4];
-                    uint4 v[4];
-                    uint4* q4[4];
-#pragma unroll
-                    for (int u = 0; u < 4; ++u) {
-                        const int r = vf * 16 + 2 * (i0 + u) + (lane >> 4);
-                        const uint32_t nb = (uint32_t)(lane >> 3) & 1u;
-                        const float sc = *reinterpret_cast<const float*>(vp + VS_RAW + ((1 - (int)rank) * OWN_N + r) * 16 + (2 * rank + nb) * 4);
-                        sub[u] = (sc > 0.f) ? shift_bytes_of_ratio(sc * inv_tile) : 0u;
-                        q4[u] = reinterpret_cast<uint4*>(vp + ((2u * (1u - rank) + (uint32_t)(r >> 5)) * 2u + nb) * VSLOT + swz((uint32_t)r & 31u, (uint32_t)lane & 7u));
-                    }
-#pragma unroll
-                    for (int u = 0; u < 4; ++u) if (sub[u] != 0u) v[u] = *q4[u];
-#pragma unroll
-                    for (int u = 0; u < 4; ++u) {
-                        if (sub[u] != 0u) {
-                            v[u].x = shift_down_e4m3x4(v[u].x, sub[u]); v[u].y = shift_down_e4m3x4(v[u].y, sub[u]);
-                            v[u].z = shift_down_e4m3x4(v[u].z, sub[u]); v[u].w = shift_down_e4m3x4(v[u].w, sub[u]);
-                            *q4[u] = v[u];
-                        }
-                    }
-                }
-                PROF(2);
-                fence_proxy_async();
-                __syncwarp();
-                if (lane == 0) mbar_arrive_remote(barp(BAR_VFULLP + vs));
-                PROF(3);
-                TRACE(35, t_it);
             }
             it += nst;
         }
@@ -887,7 +738,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PAIR_THREADS, 1) att
 #pragma unroll
                     for (int nb = 0; nb < 2; ++nb) {
                         mma_pair_f8(tmem + TM_O + 128 * nb, make_desc(pa_lo + ((kb * 32) >> 4), DESC_HI_SW128),
-                                    make_desc(vb_lo + (((2 * kb + nb) * VSLOT) >> 4), DESC_HI_SW128), IDESC_PV_F8, (j | kb) != 0);
+                                    make_desc(vb_lo + (((4 * nb + kb) * VSLOT) >> 4), DESC_HI_SW128), IDESC_PV_F8, (j | kb) != 0);
                     }
                 }
                 tc_commit_pair(bar(BAR_VEMPTY + vs));
@@ -898,9 +749,141 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PAIR_THREADS, 1) att
                 TRACE(52, it);
             }
         }
+    } else if (warp == FWD_WARP && lane == 0) {
+        // =================================================================== K stage -> V slots (both CTAs)
+        // The no-PE bytes of this CTA's 64 rows lie in the K stage as four chunks of [64 rows x 128 dims], which is
+        // two V slots each (rows 0-31 and 32-63) in the slots' own layout.  Chunks 2 r and 2 r + 1 go to CTA r: the
+        // chunks of the own dims stay in this CTA, the others cross to the partner.  The destination's barrier
+        // counts the bytes.  The half tile's scale record travels the same way.  When this CTA's slots are full
+        // (its own copies and the partner's have landed) the thread passes that on: V full to the even CTA,
+        // K stage free to both.
+        const uint32_t peer = 1u - rank;
+        uint32_t it = 0;
+        bool ok = true;
+        for (int req = meta.begin_req; req <= last_req && ok; ++req) {
+            Work w;
+            if (!get_work(p, meta, req, w)) continue;
+            const int nst = (w.nblk + 1) >> 1;
+            for (int j = 0; j < nst && ok; ++j, ++it) {
+                const uint32_t ks = it % NK, vs = it % NV, ir = it & (INFO_RING - 1);
+                ok = mbar_wait_thread(bar(BAR_KSTORED + ks), (it / NK) & 1u, abort_flag, W_KSTORED);
+                if (!ok) break;
+                mbar_arrive_expect_tx(bar(BAR_INFO + ir), 32);
+                bulk_copy_to_cluster(mapa_shared(base + INFO_OFF + ir * 64 + rank * 32, peer), base + INFO_OFF + ir * 64 + rank * 32, 32,
+                                     mapa_shared(bar(BAR_INFO + ir), peer));
+                if (it >= NV) {
+                    ok = mbar_wait_thread(bar(BAR_VEMPTY + vs), ((it / NV) - 1) & 1u, abort_flag, W_VEMPTY);
+                    if (!ok) break;
+                }
+#ifdef SMLA_EXP_NOVCOPY
+                mbar_arrive(bar(BAR_VFULL + vs));
+                for (uint32_t r = 0; r < 0; ++r) {
+#else
+                mbar_arrive_expect_tx(bar(BAR_VFULL + vs), 4 * CHUNK);
+#pragma unroll
+                for (uint32_t r = 0; r < 2; ++r) {
+#endif
+#pragma unroll
+                    for (uint32_t nb = 0; nb < 2; ++nb) {
+                        bulk_copy_to_cluster(mapa_shared(base + VS_OFF + vs * VS_BYTES + (4 * nb + 2 * rank) * VSLOT, r),
+                                             base + KS_OFF + ks * KS_BYTES + (2 * r + nb) * CHUNK, CHUNK,
+                                             mapa_shared(bar(BAR_VFULL + vs), r));
+                    }
+                }
+                ok = mbar_wait_thread(bar(BAR_VFULL + vs), (it / NV) & 1u, abort_flag, W_VFULL_CTA);
+                if (!ok) break;
+                mbar_arrive_remote(barp(BAR_VFULLP + vs));
+                // the copies out of this CTA's K stage into its own slots and the partner's copies into them are done
+                mbar_arrive(bar(BAR_KEMPTY + ks));
+                mbar_arrive_remote(mapa_shared(bar(BAR_KEMPTY + ks), peer));
+            }
+        }
+    }
+    else if (warp >= PROD_WARP0) {
+        // =================================================================== global -> raw stage (both CTAs)
+        // Copy warp pw brings rows [16 pw, +16) of every tile of this CTA into the raw stage as 16-byte
+        // asynchronous copies (the mechanism with the highest rate for scattered rows): per row one instruction
+        // for the 512 no-PE bytes, and 5 instructions for the 16 rows' 9 x 16 bytes of scales and RoPE.  A row
+        // without an entry is zero-filled.  The tile NR ahead is issued as soon as the two gather warps that
+        // read these rows have taken the tile out of the stage; each lane's arrive on the warp's barrier of the
+        // stage fires when its copies have landed.  Issuing blocks while the SM has its fill of loads in
+        // flight, which is why no working warp does it.
+        const int pw = warp - PROD_WARP0;
+        const int pbs_shift = (p.page_block_size & (p.page_block_size - 1)) == 0 ? __ffs(p.page_block_size) - 1 : -1;
+        const unsigned long long kv_u = reinterpret_cast<unsigned long long>(p.kv);
+        uint32_t it = 0;
+        bool ok = true;
+        for (int req = meta.begin_req; req <= last_req && ok; ++req) {
+            Work w;
+            if (!get_work(p, meta, req, w)) continue;
+            const int nst = (w.nblk + 1) >> 1;
+            const int32_t* idx_row = p.indices + (size_t)req * p.topk;
+            const int lim = min(w.len, (w.blk0 + w.nblk) * BLOCK_N);
+            auto fetch_idx = [&](int j) -> int {                     // row 16 pw + lane % 16 of tile j
+                const int pos = w.blk0 * BLOCK_N + j * TILE_N + (int)rank * OWN_N + pw * 16 + (lane & 15);
+                return (j < nst && pos < lim) ? __ldg(idx_row + pos) : -1;
+            };
+            auto issue_rows = [&](int idx, uint32_t t_it) {          // idx: lanes 0-15 hold the rows' indices
+                const uint32_t stage = t_it % NR;
+                unsigned long long src = 0ull;
+                if (idx >= 0) {
+                    const unsigned u = (unsigned)idx;
+                    src = reinterpret_cast<unsigned long long>(
+                        (pbs_shift >= 0)
+                            ? p.kv + (int64_t)(u >> pbs_shift) * p.block_stride + (int64_t)(u & (unsigned)(p.page_block_size - 1)) * ROW_BYTES
+                            : kv_row_ptr(p.kv, idx, p.page_block_size, p.block_stride));
+                }
+                const uint32_t dst0 = base + RAW_OFF + stage * RAW_BYTES + (pw * 16) * ROW_BYTES;
+#ifdef SMLA_ROWS_BULK
+                const uint32_t fb = bar(BAR_RAWFULL + stage * N_P_WARPS + pw);
+                const uint32_t nvalid = __popc(__ballot_sync(0xffffffffu, src != 0ull) & 0xffffu);
+                if (lane == 0) mbar_arrive_expect_tx(fb, nvalid * ROW_BYTES);
+                __syncwarp();
+                if (lane < 16 && src != 0ull) bulk_copy_g2s(dst0 + lane * ROW_BYTES, src, ROW_BYTES, fb);
+#else
+#pragma unroll 4
+                for (int i = 0; i < 16; ++i) {
+                    const unsigned long long a = __shfl_sync(0xffffffffu, src, i);
+                    cp_async16_zfill(dst0 + i * ROW_BYTES + lane * 16, reinterpret_cast<const uint8_t*>(a ? a + lane * 16 : kv_u), a ? 16u : 0u);
+                }
+#pragma unroll
+                for (int u = 0; u < 5; ++u) {                        // 144 tail pieces: 9 per row
+                    const int e = lane + 32 * u, r = e / 9, piece = 32 + e - 9 * r;
+                    const unsigned long long a = __shfl_sync(0xffffffffu, src, r & 15);
+                    if (e < 144)
+                        cp_async16_zfill(dst0 + r * ROW_BYTES + piece * 16, reinterpret_cast<const uint8_t*>(a ? a + piece * 16 : kv_u), a ? 16u : 0u);
+                }
+                cp_async_arrive_noinc(bar(BAR_RAWFULL + stage * N_P_WARPS + pw));
+#endif
+            };
+            // The raw stages that the first NR tiles of a request go to are free once the gather warps have taken the
+            // last NR tiles before them out (for the very first tiles of the CTA there is nothing to wait for).
+#pragma unroll 1
+            for (int j = 0; j < NR && j < nst && ok; ++j) {
+                const uint32_t t_it = it + j;
+                const int idx = fetch_idx(j);
+                if (t_it >= NR) ok = mbar_wait_hot(bar(BAR_RAWEMPTY + (t_it % NR) * N_P_WARPS + pw), ((t_it / NR) - 1) & 1u, abort_flag, W_RAWEMPTY);
+                if (ok) issue_rows(idx, t_it);
+            }
+            int idx_ahead = fetch_idx(NR);               // read one tile before it is turned into addresses
+#pragma unroll 1
+            for (int j = 0; j + NR < nst && ok; ++j) {   // the tile NR ahead goes into the raw stage that has just been emptied
+                const uint32_t t_it = it + j;
+                ok = mbar_wait_hot(bar(BAR_RAWEMPTY + (t_it % NR) * N_P_WARPS + pw), (t_it / NR) & 1u, abort_flag, W_RAWEMPTY);
+                if (!ok) break;
+                issue_rows(idx_ahead, t_it + NR);
+                idx_ahead = fetch_idx(j + NR + 1);
+            }
+            it += nst;
+        }
+        cp_async_wait_all();     // nothing is outstanding unless a wait gave up
     }
 
     // ------------------------------------------------------------------------ teardown
+    if (*abort_flag != 0) {        // a wait gave up: bulk copies into or out of this CTA may still be in flight; give them time to land
+        const long long t0 = clock64();
+        while (clock64() - t0 < 200000) { }
+    }
     tc_fence_before();
     __syncthreads();
     cluster_sync_all();        // the partner may still arrive on this CTA's barriers until here

@@ -85,6 +85,10 @@ __device__ __forceinline__ float warp_sum(float v) {
 // Host-side error plumbing (api.cu).
 int set_error(int code, const char* fmt, ...);
 int check_launch(const char* what);
+// Argument checks shared by the attention entry points (nothing is launched when it fails).
+int check_attn_common(const char* fn, const void* q, const void* kv, const int32_t* indices, const void* out,
+                      const float* out_lse, int num_tokens, int num_heads, int topk, int page_block_size, int64_t stride,
+                      int impl);
 
 // Launchers (one per translation unit).
 int launch_sched_meta(int b, int topk, int extra_topk, int num_sm_parts, int fixed_overhead,
@@ -102,7 +106,6 @@ int launch_combine_parts(const float* o_parts, const float* lse_parts, __nv_bflo
                          int parts, int batch, int num_heads, int64_t part_stride_o, int64_t part_stride_l,
                          const float* attn_sink, cudaStream_t stream);
 int launch_attn_scalar(const AttnParams& p, cudaStream_t stream);
-int launch_attn_tc(const AttnParams& p, cudaStream_t stream);
 int launch_attn_pair(const AttnParams& p, cudaStream_t stream);
 int launch_pack_kv(const __nv_bfloat16* kv, uint8_t* packed, int64_t num_rows, cudaStream_t stream);
 int launch_mqa_logits_scalar(const uint8_t* q, const uint8_t* k, const float* k_scale, const float* weights,

@@ -62,8 +62,9 @@ extern "C" int smla_decode_splitkv_noalloc(const void* q, const void* kv, const 
                                            int page_block_size, int64_t kv_block_stride_bytes, int num_sm_parts,
                                            const float* attn_sink, const int32_t* topk_length,
                                            int impl, int32_t* status, void* stream) {
-    if (!q || !kv || !indices || !out || !out_lse)
-        return set_error(SMLA_E_NULL, "smla_decode_splitkv_noalloc: null pointer argument");
+    // every check of the attention call comes first: a refused call launches nothing, the scheduler included
+    if (int e = check_attn_common("smla_decode_splitkv_noalloc", q, kv, indices, out, out_lse, num_tokens, num_heads, topk,
+                                  page_block_size, kv_block_stride_bytes, impl)) return e;
     if (num_tokens < 1 || num_tokens > 8192 || num_heads < 1 || num_heads > 128 || topk < 1 || num_sm_parts < 1 ||
         page_block_size < 1)
         return set_error(SMLA_E_SHAPE, "smla_decode_splitkv_noalloc: tokens=%d heads=%d topk=%d parts=%d page=%d",

@@ -74,12 +74,28 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
 // give-up protocol as mbar_wait.
 __device__ __forceinline__ bool mbar_wait_hot(uint32_t bar, uint32_t parity, volatile int* abort, int code) {
     uint32_t ok = 0;
+#ifdef SMLA_POLL_LANE0
+    // One polling lane per warp: 32 lanes re-polling one barrier are 32 shared-memory requests per round, which
+    // the working warps of the SM pay for.  The other lanes then take one (successful) poll of their own, which
+    // is what orders their later reads after the barrier's completion.
+    if ((threadIdx.x & 31) == 0) {
+        for (uint32_t i = 0; i < WAIT_POLLS; ++i) {
+            if (mbar_try_wait(bar, parity, WAIT_HINT_NS)) { ok = 1; break; }
+            if ((i & 255u) == 255u && *abort != 0) break;
+        }
+        if (!ok) atomicCAS(const_cast<int*>(abort), 0, code);
+    }
+    ok = __shfl_sync(0xffffffffu, ok, 0);
+    if (ok && (threadIdx.x & 31) != 0) ok = mbar_try_wait(bar, parity, WAIT_HINT_NS) ? 1u : 0u;
+    return __all_sync(0xffffffffu, ok != 0);
+#else
     for (uint32_t i = 0; i < WAIT_POLLS; ++i) {
         if (mbar_try_wait(bar, parity, WAIT_HINT_NS)) { ok = 1; break; }
         if ((i & 255u) == 255u && *abort != 0) break;
     }
     if (!ok) atomicCAS(const_cast<int*>(abort), 0, code);
     return __all_sync(0xffffffffu, ok != 0);
+#endif
 }
 
 // ------------------------------------------------------------------ thread-block cluster
@@ -144,6 +160,12 @@ __device__ __forceinline__ void mbar_arrive_expect_tx_cluster(uint32_t remote_ba
 __device__ __forceinline__ void bulk_copy_to_cluster(uint32_t remote_dst, uint32_t local_src, uint32_t bytes, uint32_t remote_bar) {
     asm volatile("cp.async.bulk.shared::cluster.shared::cta.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
                  ::"r"(remote_dst), "r"(local_src), "r"(bytes), "r"(remote_bar) : "memory");
+}
+// Untiled bulk copy global -> this CTA's shared memory (both 16-byte aligned, size a multiple of 16);
+// the barrier receives the byte count when the data has landed.
+__device__ __forceinline__ void bulk_copy_g2s(uint32_t dst, unsigned long long src, uint32_t bytes, uint32_t bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                 ::"r"(dst), "l"(src), "r"(bytes), "r"(bar) : "memory");
 }
 // One poll with cluster-scope acquire: for barriers that another CTA arrives on after writing here.
 __device__ __forceinline__ bool mbar_try_wait_cluster(uint32_t bar, uint32_t parity) {

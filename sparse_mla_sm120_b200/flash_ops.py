@@ -165,13 +165,13 @@ def sparse_mla_decode_fwd(
     _check_q(q)
     layout = _layout(q, kv_cache)
     page_block_size, page_stride = kv_geometry(kv_cache)
-    require_cuda(q, kv_cache, indices)
     if d_v != 512:
         raise ValueError(f"d_v must be 512, got {d_v}")
     num_tokens, num_heads, _ = q.shape
     topk = indices.shape[-1]
     assert indices.dtype == torch.int32 and indices.is_contiguous()
     ex = _Extra(layout, num_tokens, extra_k_cache, extra_indices, extra_topk, extra_topk_length)
+    require_cuda(q, kv_cache, indices)
     fp32_only = layout != LAYOUT_V32 or ex.topk > 0
 
     if num_sm_parts is None:

@@ -54,20 +54,27 @@ def test_argument_errors_do_not_launch(lib):
         _lib.check(-2)
 
 
-def test_python_surface_rejects_cpu_tensors_and_unbuilt_features():
+def test_python_surface_rejects_cpu_tensors_and_mismatched_layouts():
+    """There is no CPU path, and q's width must go with the cache layout (576 with 656-byte rows, 512 with the
+    584-byte footer layout); all refused before any device work."""
     import torch
     import sparse_mla_sm120_b200 as smla
     q = torch.zeros(1, 128, 576, dtype=torch.bfloat16)
     kv = torch.zeros(4, 64, 1, 656, dtype=torch.uint8)
+    kv_m1 = torch.zeros(4, 64, 1, 584, dtype=torch.uint8)
     idx = torch.zeros(1, 64, dtype=torch.int32)
     with pytest.raises(ValueError, match="CUDA"):
         smla.flash_ops.sparse_mla_decode_fwd(q, kv, idx, 1.0)
-    with pytest.raises(NotImplementedError):
+    with pytest.raises(ValueError, match="CUDA"):
+        smla.flash_ops.sparse_mla_decode_fwd(q[..., :512].contiguous(), kv_m1, idx, 1.0)
+    with pytest.raises(ValueError, match="does not go with"):
         smla.flash_ops.sparse_mla_decode_fwd(q[..., :512].contiguous(), kv, idx, 1.0)
-    with pytest.raises(NotImplementedError):
-        smla.flash_ops.sparse_mla_decode_fwd(q, kv, idx, 1.0, extra_k_cache=kv, extra_indices=idx, extra_topk=64)
-    with pytest.raises(NotImplementedError):
-        smla.flash_ops.sparse_mla_prefill_fwd(q, torch.zeros(4, 64, 1, 584, dtype=torch.uint8), idx, 1.0)
+    with pytest.raises(ValueError, match="does not go with"):
+        smla.flash_ops.sparse_mla_prefill_fwd(q, kv_m1, idx, 1.0)
+    with pytest.raises(ValueError, match="layout of the main cache"):
+        smla.flash_ops.sparse_mla_decode_fwd(q, kv, idx, 1.0, extra_k_cache=kv_m1, extra_indices=idx, extra_topk=64)
+    with pytest.raises(ValueError, match="needs extra_k_cache"):
+        smla.flash_ops.sparse_mla_decode_fwd(q, kv, idx, 1.0, extra_topk=64)
 
 
 def test_split_policy():
@@ -94,7 +101,6 @@ def test_flashmla_surface_argument_checks():
         interface.flash_mla_with_kvcache(q, kv, None, None, 512, meta, None, None, False, True, indices=None)
     with pytest.raises(ValueError):
         interface.flash_mla_with_kvcache(q, kv, None, None, 512, meta, None, None, False, False, indices=idx)
-    with pytest.raises(NotImplementedError):
-        interface.flash_mla_with_kvcache(q, kv, None, None, 512, meta, None, None, False, True, indices=idx,
-                                         extra_k_cache=kv)
+    with pytest.raises(ValueError):    # no CPU path
+        interface.flash_mla_with_kvcache(q, kv, None, None, 512, meta, None, None, False, True, indices=idx)
     assert not meta.have_initialized

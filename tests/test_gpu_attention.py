@@ -13,7 +13,7 @@ from helpers import bf16_from_bits, make_case, oracle_attn, orc
 
 pytestmark = pytest.mark.gpu
 
-SCALAR, TC, TC_PAIR = 1, 2, 3
+SCALAR, TC = 1, 2
 
 
 def _tols(impl, prefill=False):
@@ -68,7 +68,7 @@ def _check_hard(out, lse2, ref_out, ref_lse, impl, case, topk_length=None):
 
 
 # ------------------------------------------------------------------ golden fixtures
-@pytest.mark.parametrize("impl", [SCALAR, TC, TC_PAIR])
+@pytest.mark.parametrize("impl", [SCALAR, TC])
 @pytest.mark.parametrize("name", ["attn_h16", "attn_h128", "attn_h64_lonely"])
 def test_golden_fixtures(golden_dir, name, impl):
     g = np.load(f"{golden_dir}/{name}.npz")
@@ -89,7 +89,7 @@ def test_golden_fixtures(golden_dir, name, impl):
 
 
 # ------------------------------------------------------------------ reference test grid (tests/test_decode.py:223-234)
-@pytest.mark.parametrize("impl", [SCALAR, TC, TC_PAIR])
+@pytest.mark.parametrize("impl", [SCALAR, TC])
 @pytest.mark.parametrize("num_heads,batch", [(128, 1), (128, 4), (16, 1), (16, 4), (64, 1), (64, 4), (8, 1), (8, 4)])
 def test_decode_reference_grid(num_heads, batch, impl):
     """topk 2048, data randn/10 clamped, last 10 indices -1, bound max|dO| < 1e-3 as the reference."""
@@ -102,7 +102,7 @@ def test_decode_reference_grid(num_heads, batch, impl):
     _check(out, lse, ref_out, ref_lse, impl)
 
 
-@pytest.mark.parametrize("impl", [SCALAR, TC, TC_PAIR])
+@pytest.mark.parametrize("impl", [SCALAR, TC])
 def test_decode_v32_shape_values(impl):
     """Benchmark-like value distribution (kv randn, q randn*0.5), mixed per-tile scales."""
     case = make_case(7, 6, 128, 2048, 96, kv_std=1.0, q_std=0.5, invalid_tail=0.1)
@@ -112,7 +112,7 @@ def test_decode_v32_shape_values(impl):
         _check(out, lse, ref_out, ref_lse, impl)
 
 
-@pytest.mark.parametrize("impl", [SCALAR, TC, TC_PAIR])
+@pytest.mark.parametrize("impl", [SCALAR, TC])
 def test_scale_spread_rows(impl):
     """Rows whose four tiles carry very different scales exercise the re-expression against the
     largest scale."""
@@ -137,7 +137,7 @@ def test_scale_spread_rows(impl):
             assert float(e_k) <= H.EMU_MARGIN * float(e_e) + 2.0 ** -8 * float(rms), (c, float(e_k), float(e_e), float(rms))
 
 
-@pytest.mark.parametrize("impl", [SCALAR, TC, TC_PAIR])
+@pytest.mark.parametrize("impl", [SCALAR, TC])
 def test_peaked_attention_and_rescale(impl):
     """Logits that keep growing along the index list force accumulator rescales; a few dominant
     keys make the distribution peaked.  With logits of +-6 the e4m3 rounding of Q alone moves
@@ -153,7 +153,7 @@ def test_peaked_attention_and_rescale(impl):
     _check_hard(out, lse, ref_out, ref_lse, impl, case)
 
 
-@pytest.mark.parametrize("impl", [SCALAR, TC, TC_PAIR])
+@pytest.mark.parametrize("impl", [SCALAR, TC])
 def test_topk_length_and_ragged(impl):
     case = make_case(9, 5, 32, 512, 16, invalid_tail=0.0)
     tl = torch.tensor([512, 100, 0, 64, 333], dtype=torch.int32)
@@ -166,7 +166,7 @@ def test_topk_length_and_ragged(impl):
     assert not out[2].any()
 
 
-@pytest.mark.parametrize("impl", [SCALAR, TC, TC_PAIR])
+@pytest.mark.parametrize("impl", [SCALAR, TC])
 def test_minus_one_handling_is_exact(impl):
     """Moving the -1 entries around, or poisoning the row that -1 would be clamped to with NaN,
     must not change a single bit (tests/test_nan_safe.py:13-32 poisons slot 0 the same way)."""
@@ -195,7 +195,7 @@ def test_minus_one_handling_is_exact(impl):
     _check(out2, lse2, o_ref, l_ref, impl)
 
 
-@pytest.mark.parametrize("impl", [SCALAR, TC, TC_PAIR])
+@pytest.mark.parametrize("impl", [SCALAR, TC])
 def test_attn_sink(impl):
     case = make_case(21, 4, 64, 512, 16, invalid_tail=0.1)
     case["indices"][3] = -1
@@ -212,7 +212,7 @@ def test_attn_sink(impl):
         assert torch.all(k[~fin] < -1e20)
 
 
-@pytest.mark.parametrize("impl", [SCALAR, TC, TC_PAIR])
+@pytest.mark.parametrize("impl", [SCALAR, TC])
 @pytest.mark.parametrize("num_heads,num_tokens", [(128, 65), (64, 65), (16, 100)])
 def test_prefill_reference_grid(num_heads, num_tokens, impl):
     """tests/test_prefill.py:56-71: topk 2048, randn/10 data, bound 1e-3; plus max_logits."""
@@ -275,7 +275,7 @@ def test_padded_page_stride():
     H.compare_out(out.cpu(), ref_out, H.TC_ABS, H.TC_REL, H.TC_COS)
 
 
-@pytest.mark.parametrize("impl", [TC, TC_PAIR])
+@pytest.mark.parametrize("impl", [TC])
 def test_many_tokens_per_cta(impl):
     """More query tokens than CTA pairs: without a scheduler every pair walks a run of tokens
     (Q reloaded, accumulator restarted, rings and barrier phases carried over between them)."""
@@ -291,7 +291,7 @@ def test_many_tokens_per_cta(impl):
     _check_hard(out, lse, ref_out, ref_lse, impl, case, topk_length=tl)
 
 
-@pytest.mark.parametrize("impl", [TC, TC_PAIR])
+@pytest.mark.parametrize("impl", [TC])
 @pytest.mark.parametrize("magnitude", [0.1, 0.5, 1.0, 2.0, 5.0])
 def test_precision_vs_magnitude(impl, magnitude):
     """The reference's magnitude sweep for the 656-byte layout (tests/test_precision_magnitude.py:201-232):
@@ -312,7 +312,7 @@ def test_precision_vs_magnitude(impl, magnitude):
         assert rel < 0.10, f"{name}: relative error {rel:.3%} at magnitude {magnitude}"
 
 
-@pytest.mark.parametrize("impl", [SCALAR, TC, TC_PAIR])
+@pytest.mark.parametrize("impl", [SCALAR, TC])
 @pytest.mark.parametrize("topk", [1, 100, 257])
 def test_topk_not_a_multiple_of_the_block(impl, topk):
     """Index lists of any length: the last block of a list is partly filled."""

@@ -13,7 +13,7 @@ def _check(out, lse_bhs, ref_out, ref_lse, b, s_q):
     heads = ref_out.shape[1]
     assert out.shape == (b, s_q, heads, 512) and out.dtype == torch.bfloat16
     assert lse_bhs.shape == (b, heads, s_q) and lse_bhs.dtype == torch.float32
-    H.compare_out(out.reshape(b * s_q, heads, 512).cpu(), ref_out, H.TC_ABS, H.TC_REL, H.TC_COS, 1.0)
+    H.compare_out(out.reshape(b * s_q, heads, 512).cpu(), ref_out, H.TC_ABS, H.TC_REL, H.TC_COS)
     lse_tok = lse_bhs.permute(0, 2, 1).reshape(b * s_q, heads).cpu()
     H.compare_lse(lse_tok, ref_lse, H.TC_LSE)
 

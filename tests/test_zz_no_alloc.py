@@ -57,3 +57,23 @@ def test_noalloc_rejects_what_does_not_fit():
     assert lib.smla_noalloc_scratch_need(64, 128, 74) > (16 << 20)
     with pytest.raises(ValueError, match="scratch"):
         _noalloc(lib, q, kv, idx, case["sm_scale"], 74)
+
+
+def test_noalloc_refuses_bad_arguments_before_launching_anything():
+    """An unknown kernel selector or a misaligned q is refused by the argument checks; the scheduler, which
+    runs first, must not have been launched (the scratch keeps the previous call's records)."""
+    from sparse_mla_sm120_b200 import _lib
+    from sparse_mla_sm120_b200._runtime import ptr, stream_ptr
+    lib = _lib.load()
+    dev = torch.device("cuda:0")
+    case = make_case(34, 2, 16, 128, 2)
+    q, kv, idx = case["q"].to(dev), case["packed"].to(dev), case["indices"].to(dev)
+    _noalloc(lib, q, kv, idx, case["sm_scale"], 3)
+    torch.cuda.synchronize()
+    out = torch.empty(2, 16, 512, dtype=torch.bfloat16, device=dev)
+    lse = torch.empty(2, 16, dtype=torch.float32, device=dev)
+    for impl, q_ptr in ((77, ptr(q)), (0, ptr(q) + 2)):
+        rc = lib.smla_decode_splitkv_noalloc(q_ptr, ptr(kv), ptr(idx), ptr(out), ptr(lse), 2, 16, 128,
+                                             float(case["sm_scale"]), 64, 64 * 656, 3, None, None, impl, None,
+                                             stream_ptr(dev))
+        assert rc < 0, lib.smla_last_error()
