@@ -40,16 +40,19 @@
 //   * Invalid entries (index < 0, position >= topk_length) are never loaded: their shared-memory
 //     rows are zero-filled and their weight is exactly 0 (NaN-safe, decode_v2_kernel.cuh:262-278).
 //
-// Warp roles (640 threads per CTA): warps 0-7 softmax + epilogue + Q quantisation (thread = one
-// head x 32 tokens of a tile; the four warps that share 32 heads exchange row maxima through
-// shared memory).  Warps 8-15 gather: warp g brings rows [8 g, +8) of the CTA's 64 into a raw stage
-// with 16-byte asynchronous copies (two tiles of the CTA are in flight), reads them into registers,
-// the eight warps agree on the half tile's scale through shared memory, shift and store.  Warp 16 lane 0 issues the score MMAs
-// and warp 17 lane 0 the P.V MMAs -- in the even CTA only, which is also where the barriers that
-// collect arrivals from both CTAs live.  Warp
-// 19 lane 0 issues the bulk copies K stage -> V slots (own and partner's), sends the half tile's
-// scale record to the partner, waits for the V slots of its CTA to fill and passes that on (V full
-// to the even CTA, K stage free to both).  Completion of MMAs reaches both CTAs through one tcgen05.commit per CTA (no multicast).
+// Warp roles (768 threads per CTA):
+//   warps 0-7    softmax + epilogue + Q quantisation (thread = one head x 32 tokens of a tile; the four
+//                warps that share 32 heads exchange row maxima through shared memory).
+//   warps 8-15   gather: warp g reads rows [8 g, +8) of the CTA's 64 from a raw stage (the rows as they
+//                lie in the cache) into registers, the eight warps agree on the half tile's scale through
+//                shared memory, every lane shifts its pieces and stores them in the layout the MMAs read.
+//   warp 16      lane 0 issues the score MMAs, warp 17 lane 0 the P.V MMAs -- in the even CTA only, which
+//                is also where the barriers that collect arrivals from both CTAs live.  Completion of
+//                MMAs reaches both CTAs through one tcgen05.commit per CTA.
+//   warp 19      lane 0 issues the bulk copies K stage -> V slots (own and partner's), sends the half
+//                tile's scale record to the partner, waits for the V slots of its CTA to fill and passes
+//                that on (V full to the even CTA, K stage free to both).
+//   warps 20-23  copy issuers: one bulk copy global -> raw stage per row, two tiles ahead.
 // Every wait is bounded; a wait that gives up records a code in status[] and the CTA drains and
 // exits.  Warps that meet at a named barrier leave the loop together (a warp whose wait gave up
 // still goes to the next named barrier, where all of them see the flag).
@@ -64,6 +67,8 @@ using namespace ptx;
 using namespace attn;
 
 constexpr int N_SM_WARPS = 8, N_G_WARPS = 8;
+constexpr int RPW = 64 / N_G_WARPS;     // rows of a tile per gather warp
+constexpr int WPW = 32 / RPW;           // gather warps per 32 rows (one word of validity bits)
 constexpr int MMA_WARP = N_SM_WARPS + N_G_WARPS;
 constexpr int FWD_WARP = MMA_WARP + 3;
 constexpr int PROD_WARP0 = MMA_WARP + 4, N_P_WARPS = 4;      // copy issuers: warp p looks after the rows of gather warps 2 p and 2 p + 1
@@ -208,12 +213,8 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PAIR_THREADS, 1) att
         }
         for (int s = 0; s < INFO_RING; ++s) mbar_init(bar(BAR_INFO + s), 1);   // + the bytes of the partner's record
         for (int s = 0; s < NR * N_P_WARPS; ++s) {
-#ifdef SMLA_ROWS_BULK
-            mbar_init(bar(BAR_RAWFULL + s), 1);
-#else
-            mbar_init(bar(BAR_RAWFULL + s), 32);       // a copy warp's 16 rows of a raw stage: one arrive per lane when its copies have landed
-#endif
-            mbar_init(bar(BAR_RAWEMPTY + s), 2);       // the two gather warps that read these rows have them in registers
+            mbar_init(bar(BAR_RAWFULL + s), 1);        // + the bytes of a copy warp's 16 rows of a raw stage
+            mbar_init(bar(BAR_RAWEMPTY + s), 16 / RPW); // the gather warps that read these 16 rows have them in registers
         }
         for (int b = 0; b < 2; ++b) {
             mbar_init(bar(BAR_SREADY + b), 1);
@@ -569,8 +570,8 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PAIR_THREADS, 1) att
             const int nst = (w.nblk + 1) >> 1;
             const int32_t* idx_row = p.indices + (size_t)req * p.topk;
             const int lim = min(w.len, (w.blk0 + w.nblk) * BLOCK_N);
-            auto fetch_idx = [&](int j) -> int {                     // row 8 gw + lane % 8 of tile j
-                const int pos = w.blk0 * BLOCK_N + j * TILE_N + (int)rank * OWN_N + gw * 8 + (lane & 7);
+            auto fetch_idx = [&](int j) -> int {                     // row RPW gw + lane % RPW of tile j
+                const int pos = w.blk0 * BLOCK_N + j * TILE_N + (int)rank * OWN_N + gw * RPW + (lane & (RPW - 1));
                 return (j < nst && pos < lim) ? __ldg(idx_row + pos) : -1;
             };
             // Which of the warp's rows have an entry (the rows themselves are brought in by the copy warps).
@@ -579,30 +580,31 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PAIR_THREADS, 1) att
             for (int k = 0; k < nst; ++k) {
                 const uint32_t t_it = it + k, ks = t_it % NK, rs = t_it % NR;
                 PROF(0);
-                if (ok) ok = mbar_wait_hot(bar(BAR_RAWFULL + rs * N_P_WARPS + (gw >> 1)), (t_it / NR) & 1u, abort_flag, W_RAWFULL);
+                if (ok) ok = mbar_wait_hot(bar(BAR_RAWFULL + rs * N_P_WARPS + gw * RPW / 16), (t_it / NR) & 1u, abort_flag, W_RAWFULL);
                 PROF(1);
-                const uint32_t vbits = __ballot_sync(0xffffffffu, idx_cur >= 0) & 0xffu;
+                const uint32_t vbits = __ballot_sync(0xffffffffu, idx_cur >= 0) & ((1u << RPW) - 1u);
                 idx_cur = idx_nxt;
                 idx_nxt = fetch_idx(k + 2);
-                const uint8_t* raw_rows = sm + RAW_OFF + rs * RAW_BYTES + (gw * 8) * ROW_BYTES;
-                uint4 nope[8], rp[2];
+                const uint8_t* raw_rows = sm + RAW_OFF + rs * RAW_BYTES + (gw * RPW) * ROW_BYTES;
+                uint4 nope[RPW], rp[RPW / 4];
                 float sc = 0.f;
                 if (ok) {
 #pragma unroll
-                    for (int i = 0; i < 8; ++i)
+                    for (int i = 0; i < RPW; ++i)
                         nope[i] = ((vbits >> i) & 1u) ? *reinterpret_cast<const uint4*>(raw_rows + i * ROW_BYTES + lane * 16) : make_uint4(0, 0, 0, 0);
 #pragma unroll
-                    for (int u = 0; u < 2; ++u) {                            // RoPE piece lane % 8 of rows lane / 8 and lane / 8 + 4
+                    for (int u = 0; u < RPW / 4; ++u) {                      // RoPE piece lane % 8 of row lane / 8 (+ 4 u)
                         const int r = (lane >> 3) + 4 * u;
                         rp[u] = ((vbits >> r) & 1u) ? *reinterpret_cast<const uint4*>(raw_rows + r * ROW_BYTES + ROPE_OFF + (lane & 7) * 16)
                                                     : make_uint4(0, 0, 0, 0);
                     }
-                    if ((vbits >> (lane >> 2)) & 1u)                         // scale lane % 4 of row lane / 4
+                    if (lane < 4 * RPW && ((vbits >> (lane >> 2)) & 1u))     // scale lane % 4 of row lane / 4
                         sc = *reinterpret_cast<const float*>(raw_rows + (lane >> 2) * ROW_BYTES + SCALE_OFF + (lane & 3) * 4);
                 } else {
 #pragma unroll
-                    for (int i = 0; i < 8; ++i) nope[i] = make_uint4(0, 0, 0, 0);
-                    rp[0] = rp[1] = make_uint4(0, 0, 0, 0);
+                    for (int i = 0; i < RPW; ++i) nope[i] = make_uint4(0, 0, 0, 0);
+#pragma unroll
+                    for (int u = 0; u < RPW / 4; ++u) rp[u] = make_uint4(0, 0, 0, 0);
                 }
                 float wm = sc;
 #pragma unroll
@@ -611,7 +613,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PAIR_THREADS, 1) att
                     gx[(t_it & 1u) * N_G_WARPS + gw] = make_float2(wm, __uint_as_float(vbits));
                     // the maximum needed the last shared-memory load of every lane (they return in order): the warp's rows
                     // have left the raw stage
-                    mbar_arrive(bar(BAR_RAWEMPTY + rs * N_P_WARPS + (gw >> 1)));
+                    mbar_arrive(bar(BAR_RAWEMPTY + rs * N_P_WARPS + gw * RPW / 16));
                 }
                 PROF(2);
                 if (ok && t_it >= NK) ok = mbar_wait_hot(bar(BAR_KEMPTY + ks), ((t_it / NK) - 1) & 1u, abort_flag, W_KEMPTY);
@@ -620,31 +622,33 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PAIR_THREADS, 1) att
                 if (named_bar_or(3, N_G_WARPS * 32, !ok || *abort_flag != 0)) { stop = true; break; }
                 PROF(4);
                 // the half tile's scale and validity bits from the eight warps' records
-                const float2 g = gx[(t_it & 1u) * N_G_WARPS + (lane & 7)];
+                const float2 g = gx[(t_it & 1u) * N_G_WARPS + (lane & (N_G_WARPS - 1))];
                 float s_half = g.x;
-                uint32_t vpart = __float_as_uint(g.y) << (8 * (lane & 3));
-                s_half = fmaxf(s_half, __shfl_xor_sync(0xffffffffu, s_half, 1)); vpart |= __shfl_xor_sync(0xffffffffu, vpart, 1);
-                s_half = fmaxf(s_half, __shfl_xor_sync(0xffffffffu, s_half, 2)); vpart |= __shfl_xor_sync(0xffffffffu, vpart, 2);
-                s_half = fmaxf(s_half, __shfl_xor_sync(0xffffffffu, s_half, 4));
-                const uint32_t vword1 = __shfl_sync(0xffffffffu, vpart, 4);      // rows 32-63 (lane 0 holds rows 0-31)
+                uint32_t vpart = __float_as_uint(g.y) << (RPW * (lane & (WPW - 1)));     // warp g looks after rows [RPW g, +RPW)
+#pragma unroll
+                for (int o = 1; o < N_G_WARPS; o <<= 1) {
+                    s_half = fmaxf(s_half, __shfl_xor_sync(0xffffffffu, s_half, o));
+                    if (o < WPW) vpart |= __shfl_xor_sync(0xffffffffu, vpart, o);
+                }
+                const uint32_t vword1 = __shfl_sync(0xffffffffu, vpart, WPW);    // rows 32-63 (lane 0 holds rows 0-31)
                 const float inv_half = (s_half > 0.f) ? __uint_as_float(0x7f000000u - __float_as_uint(s_half)) : 0.f;
                 const __nv_bfloat162 rope_f = __float2bfloat162_rn(inv_half);
                 uint8_t* kp = sm + KS_OFF + ks * KS_BYTES;
 #pragma unroll
-                for (int i = 0; i < 8; ++i) {
+                for (int i = 0; i < RPW; ++i) {
                     const float sci = __shfl_sync(0xffffffffu, sc, 4 * i + blk);
                     const uint32_t sub = (sci > 0.f) ? shift_bytes_of_ratio(sci * inv_half) : 0u;   // 0 for a block that is at the scale
                     uint4 v = nope[i];      // no branch on sub: a shift by 0 is the identity, and a branch would keep the rows' chains apart
                     v.x = shift_down_e4m3x4(v.x, sub); v.y = shift_down_e4m3x4(v.y, sub);
                     v.z = shift_down_e4m3x4(v.z, sub); v.w = shift_down_e4m3x4(v.w, sub);
-                    *reinterpret_cast<uint4*>(kp + blk * CHUNK + swz((uint32_t)(gw * 8 + i), (uint32_t)lane & 7u)) = v;
+                    *reinterpret_cast<uint4*>(kp + blk * CHUNK + swz((uint32_t)(gw * RPW + i), (uint32_t)lane & 7u)) = v;
                 }
 #pragma unroll
-                for (int u = 0; u < 2; ++u) {
+                for (int u = 0; u < RPW / 4; ++u) {
                     uint4 v = rp[u];
                     v.x = mul_bf16x2(v.x, rope_f); v.y = mul_bf16x2(v.y, rope_f);
                     v.z = mul_bf16x2(v.z, rope_f); v.w = mul_bf16x2(v.w, rope_f);
-                    *reinterpret_cast<uint4*>(kp + KS_ROPE + swz((uint32_t)(gw * 8 + (lane >> 3) + 4 * u), (uint32_t)lane & 7u)) = v;
+                    *reinterpret_cast<uint4*>(kp + KS_ROPE + swz((uint32_t)(gw * RPW + (lane >> 3) + 4 * u), (uint32_t)lane & 7u)) = v;
                 }
                 if (gw == 0 && lane == 0) {      // this half tile's record: read by this CTA's softmax warps and sent to the partner's
                     uint8_t* rec = sm + INFO_OFF + (t_it & (INFO_RING - 1)) * 64 + rank * 32;
@@ -801,16 +805,13 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PAIR_THREADS, 1) att
     }
     else if (warp >= PROD_WARP0) {
         // =================================================================== global -> raw stage (both CTAs)
-        // Copy warp pw brings rows [16 pw, +16) of every tile of this CTA into the raw stage as 16-byte
-        // asynchronous copies (the mechanism with the highest rate for scattered rows): per row one instruction
-        // for the 512 no-PE bytes, and 5 instructions for the 16 rows' 9 x 16 bytes of scales and RoPE.  A row
-        // without an entry is zero-filled.  The tile NR ahead is issued as soon as the two gather warps that
-        // read these rows have taken the tile out of the stage; each lane's arrive on the warp's barrier of the
-        // stage fires when its copies have landed.  Issuing blocks while the SM has its fill of loads in
-        // flight, which is why no working warp does it.
+        // Copy warp pw brings rows [16 pw, +16) of every tile of this CTA into the raw stage, one bulk copy per row
+        // (lanes 0-15; no load/store unit and no registers involved, two tiles of the CTA are in flight).  Nothing
+        // is copied for a row without an entry.  The tile NR ahead is issued as soon as the gather warps that read
+        // these rows have taken the tile out of the stage; the warp's barrier of the stage counts the bytes.
+        // Issuing a copy blocks while the copy unit is busy, which is why no working warp does it.
         const int pw = warp - PROD_WARP0;
         const int pbs_shift = (p.page_block_size & (p.page_block_size - 1)) == 0 ? __ffs(p.page_block_size) - 1 : -1;
-        const unsigned long long kv_u = reinterpret_cast<unsigned long long>(p.kv);
         uint32_t it = 0;
         bool ok = true;
         for (int req = meta.begin_req; req <= last_req && ok; ++req) {
@@ -834,27 +835,11 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PAIR_THREADS, 1) att
                             : kv_row_ptr(p.kv, idx, p.page_block_size, p.block_stride));
                 }
                 const uint32_t dst0 = base + RAW_OFF + stage * RAW_BYTES + (pw * 16) * ROW_BYTES;
-#ifdef SMLA_ROWS_BULK
                 const uint32_t fb = bar(BAR_RAWFULL + stage * N_P_WARPS + pw);
                 const uint32_t nvalid = __popc(__ballot_sync(0xffffffffu, src != 0ull) & 0xffffu);
                 if (lane == 0) mbar_arrive_expect_tx(fb, nvalid * ROW_BYTES);
                 __syncwarp();
                 if (lane < 16 && src != 0ull) bulk_copy_g2s(dst0 + lane * ROW_BYTES, src, ROW_BYTES, fb);
-#else
-#pragma unroll 4
-                for (int i = 0; i < 16; ++i) {
-                    const unsigned long long a = __shfl_sync(0xffffffffu, src, i);
-                    cp_async16_zfill(dst0 + i * ROW_BYTES + lane * 16, reinterpret_cast<const uint8_t*>(a ? a + lane * 16 : kv_u), a ? 16u : 0u);
-                }
-#pragma unroll
-                for (int u = 0; u < 5; ++u) {                        // 144 tail pieces: 9 per row
-                    const int e = lane + 32 * u, r = e / 9, piece = 32 + e - 9 * r;
-                    const unsigned long long a = __shfl_sync(0xffffffffu, src, r & 15);
-                    if (e < 144)
-                        cp_async16_zfill(dst0 + r * ROW_BYTES + piece * 16, reinterpret_cast<const uint8_t*>(a ? a + piece * 16 : kv_u), a ? 16u : 0u);
-                }
-                cp_async_arrive_noinc(bar(BAR_RAWFULL + stage * N_P_WARPS + pw));
-#endif
             };
             // The raw stages that the first NR tiles of a request go to are free once the gather warps have taken the
             // last NR tiles before them out (for the very first tiles of the CTA there is nothing to wait for).
@@ -876,7 +861,6 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PAIR_THREADS, 1) att
             }
             it += nst;
         }
-        cp_async_wait_all();     // nothing is outstanding unless a wait gave up
     }
 
     // ------------------------------------------------------------------------ teardown

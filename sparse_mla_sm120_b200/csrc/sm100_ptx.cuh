@@ -91,6 +91,9 @@ __device__ __forceinline__ bool mbar_wait_hot(uint32_t bar, uint32_t parity, vol
 #else
     for (uint32_t i = 0; i < WAIT_POLLS; ++i) {
         if (mbar_try_wait(bar, parity, WAIT_HINT_NS)) { ok = 1; break; }
+#ifdef SMLA_WAIT_SLEEP_NS
+        __nanosleep(SMLA_WAIT_SLEEP_NS);     // a warp that re-polls at once takes issue slots from the working warps of its scheduler
+#endif
         if ((i & 255u) == 255u && *abort != 0) break;
     }
     if (!ok) atomicCAS(const_cast<int*>(abort), 0, code);
@@ -201,6 +204,9 @@ __device__ __forceinline__ bool mbar_wait_thread_cluster(uint32_t bar, uint32_t 
 __device__ __forceinline__ bool mbar_wait_thread(uint32_t bar, uint32_t parity, volatile int* abort, int code) {
     for (uint32_t i = 0; i < WAIT_POLLS; ++i) {
         if (mbar_try_wait(bar, parity, WAIT_HINT_NS)) return true;
+#ifdef SMLA_WAIT_SLEEP_NS
+        __nanosleep(SMLA_WAIT_SLEEP_NS);
+#endif
         if ((i & 255u) == 255u && *abort != 0) return false;
     }
     atomicCAS(const_cast<int*>(abort), 0, code);
