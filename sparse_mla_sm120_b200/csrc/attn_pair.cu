@@ -78,7 +78,7 @@ constexpr int PAIR_THREADS = (PROD_WARP0 + N_P_WARPS) * 32;
 // for ever; the launcher checks the compiled register count against REGS_LAUNCH before it launches.
 // A gather thread keeps 8 + 2 sixteen-byte pieces in flight; the MMA-issuing and copy threads need few
 // registers, so their warpgroup gives up more than half of its allocation.
-constexpr int REGS_LAUNCH = 80, REGS_SOFTMAX = 128, REGS_GATHER = 72, REGS_MMA = 40, REGS_PROD = 40;
+constexpr int REGS_LAUNCH = 80, REGS_SOFTMAX = 120, REGS_GATHER = 80, REGS_MMA = 40, REGS_PROD = 40;
 static_assert(N_SM_WARPS * 32 * REGS_SOFTMAX + N_G_WARPS * 32 * REGS_GATHER + 128 * REGS_MMA + N_P_WARPS * 32 * REGS_PROD
                   <= PAIR_THREADS * REGS_LAUNCH, "register budgets exceed what the CTA owns");
 static_assert(65536 / PAIR_THREADS / 8 * 8 == REGS_LAUNCH, "launch-time registers per thread");
@@ -186,17 +186,8 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PAIR_THREADS, 1) att
     TRACE(1, 0);
     const uint32_t rank = cluster_ctarank();          // 0: the CTA that issues the MMAs
     const int part = blockIdx.x >> 1;
-    const SchedMeta meta = load_meta(p, part);
     const int heads_cta = (p.num_heads + 1) >> 1;     // heads per CTA
     const int head0 = (int)rank * heads_cta;
-
-    // The Q rows of the first request (this CTA's heads: one contiguous piece of global memory) come in by one bulk
-    // copy into the K stages, which are empty until the first tile has been gathered and shifted; the softmax warps
-    // then quantise Q out of shared memory instead of waiting for global memory several times in a row.
-    const int last_req = min(meta.end_req, p.num_tokens - 1);
-    const int live_heads = min(heads_cta, max(p.num_heads - head0, 0));
-    Work w_first;
-    const bool q_staged = meta.begin_req <= last_req && live_heads > 0 && get_work(p, meta, meta.begin_req, w_first);
 
     if (tid == 0) {
         mbar_init(bar(BAR_QSTAGE), 1);
@@ -225,12 +216,6 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PAIR_THREADS, 1) att
         mbar_init(bar(BAR_QREADYP), 2 * N_SM_WARPS);
         *abort_flag = 0;
         mbar_init_fence();
-        if (q_staged) {
-            const uint32_t bytes = (uint32_t)live_heads * D_QK * 2;
-            mbar_arrive_expect_tx(bar(BAR_QSTAGE), bytes);
-            bulk_copy_g2s(base + KS_OFF, reinterpret_cast<unsigned long long>(p.q + ((size_t)meta.begin_req * p.num_heads + head0) * D_QK),
-                          bytes, bar(BAR_QSTAGE));
-        }
     }
     if (warp == MMA_WARP) {
         tmem_alloc_pair(base + MISC_OFF, TMEM_COLS);
@@ -243,6 +228,26 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PAIR_THREADS, 1) att
     TRACE(6, 0);
     const uint32_t tmem = *tmem_slot;
     auto barp = [&](int i) -> uint32_t { return mapa_shared(bar(i), 0); };   // the even CTA's copy of barrier i
+
+    // Everything above needs nothing from the kernels before this one.  From here on the scheduler's records are
+    // read (when this kernel was launched as a dependent of the scheduler kernel it may have started before that
+    // one finished), and the kernel after this one may start its own prologue.
+    grid_dep_wait();
+    grid_dep_launch();
+    const SchedMeta meta = load_meta(p, part);
+    // The Q rows of the first request (this CTA's heads: one contiguous piece of global memory) come in by one bulk
+    // copy into the K stages, which are empty until the first tile has been gathered and shifted; the softmax warps
+    // then quantise Q out of shared memory instead of waiting for global memory several times in a row.
+    const int last_req = min(meta.end_req, p.num_tokens - 1);
+    const int live_heads = min(heads_cta, max(p.num_heads - head0, 0));
+    Work w_first;
+    const bool q_staged = meta.begin_req <= last_req && live_heads > 0 && get_work(p, meta, meta.begin_req, w_first);
+    if (tid == 0 && q_staged) {
+        const uint32_t bytes = (uint32_t)live_heads * D_QK * 2;
+        mbar_arrive_expect_tx(bar(BAR_QSTAGE), bytes);
+        bulk_copy_g2s(base + KS_OFF, reinterpret_cast<unsigned long long>(p.q + ((size_t)meta.begin_req * p.num_heads + head0) * D_QK),
+                      bytes, bar(BAR_QSTAGE));
+    }
 
     if (warp < N_SM_WARPS) setmaxnreg_inc<REGS_SOFTMAX>();
     else if (warp < MMA_WARP) setmaxnreg_dec<REGS_GATHER>();
@@ -358,6 +363,15 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PAIR_THREADS, 1) att
             if (named_bar_or(1 + grp, 128, dead || *abort_flag != 0)) { stop = true; break; }
             TRACE(2, it);
             PROF(11);
+            // The next request's Q rows are read from global memory by the next Q phase, several dependent rounds of
+            // loads with nothing else to do: ask L2 for them now (this CTA's heads, 128-byte lines), a whole request
+            // of tiles ahead.
+            if (req + 1 <= last_req) {
+                const uint8_t* qn = reinterpret_cast<const uint8_t*>(p.q + ((size_t)(req + 1) * p.num_heads + head0) * D_QK);
+                const int lines = (live_heads * D_QK * 2 + 127) >> 7;
+                for (int i = tid; i < lines; i += N_SM_WARPS * 32)
+                    asm volatile("prefetch.global.L2 [%0];" ::"l"(qn + (size_t)i * 128));
+            }
             const float my_sqc = live ? sqv[hrow] * p.sm_scale * LOG2E : 0.f;
             __syncwarp();
             if (lane == 0) mbar_arrive_remote(barp(BAR_QREADYP));
@@ -928,7 +942,10 @@ int launch_attn_pair(const AttnParams& p, cudaStream_t stream) {
     // Without a scheduler the grid is persistent: at most one CTA per SM, each pair walks its share of the requests.
     const int max_pairs = sm_count[dev] >= 2 ? sm_count[dev] / 2 : 1;
     const int parts = p.sched ? p.num_parts : (p.num_tokens < max_pairs ? p.num_tokens : max_pairs);
-    attn_pair_kernel<<<2 * parts, PAIR_THREADS, SMEM_ALLOC, stream>>>(p);
+    if (p.sched != nullptr)      // the scheduler kernel runs just before: start while it finishes
+        launch_dependent(attn_pair_kernel, dim3(2 * parts), dim3(PAIR_THREADS), SMEM_ALLOC, stream, p);
+    else
+        attn_pair_kernel<<<2 * parts, PAIR_THREADS, SMEM_ALLOC, stream>>>(p);
     return check_launch("attn_pair_kernel");
 }
 

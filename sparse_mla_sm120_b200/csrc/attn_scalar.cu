@@ -81,6 +81,7 @@ __global__ void __launch_bounds__(THREADS) attn_scalar_kernel(const AttnParams p
 
     SchedMeta meta;
     if (p.sched != nullptr) {
+        grid_dep_wait();
         meta = p.sched[part];
     } else {  // one partition per token, whole request, never split
         meta.begin_req = meta.end_req = part;

@@ -29,6 +29,7 @@ combine_kernel(const float* __restrict__ o_accum, const float* __restrict__ lse_
     constexpr bool F32 = sizeof(OutT) == 4;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int64_t row = (int64_t)blockIdx.x * WARPS + warp;   // (token, head)
+    grid_dep_wait();      // the partials of the attention kernel before this one are complete
     if (row >= (int64_t)batch * num_heads) return;
     const int tok = (int)(row / num_heads), h = (int)(row % num_heads);
     int s0, ns;
@@ -138,7 +139,7 @@ int launch_combine(const float* o_accum, const float* lse_accum, __nv_bfloat16* 
     const int64_t rows = (int64_t)batch * num_heads;
     if (rows == 0) return 0;
     const unsigned grid = (unsigned)((rows + WARPS - 1) / WARPS);
-    combine_kernel<__nv_bfloat16><<<grid, WARPS * 32, 0, stream>>>(o_accum, lse_accum, out, out_lse, num_splits,
+    launch_dependent(combine_kernel<__nv_bfloat16>, dim3(grid), dim3(WARPS * 32), 0, stream, o_accum, lse_accum, out, out_lse, num_splits,
                                                                     attn_sink, batch, num_heads, 0, 0, 0, 1, 0);
     return check_launch("combine_kernel");
 }
@@ -152,7 +153,7 @@ int launch_combine_f32(const float* o_accum, const float* lse_accum, float* out,
     const int64_t rows = (int64_t)batch * num_heads;
     if (rows == 0) return 0;
     const unsigned grid = (unsigned)((rows + WARPS - 1) / WARPS);
-    combine_kernel<float><<<grid, WARPS * 32, 0, stream>>>(o_accum, lse_accum, out, out_lse, num_splits, nullptr,
+    launch_dependent(combine_kernel<float>, dim3(grid), dim3(WARPS * 32), 0, stream, o_accum, lse_accum, out, out_lse, num_splits, nullptr,
                                                             batch, num_heads, 0, 0, 0, out_slices, out_slice_stride);
     return check_launch("combine_kernel<f32>");
 }
@@ -165,7 +166,7 @@ int launch_combine_parts(const float* o_parts, const float* lse_parts, __nv_bflo
     const int64_t rows = (int64_t)batch * num_heads;
     if (rows == 0) return 0;
     const unsigned grid = (unsigned)((rows + WARPS - 1) / WARPS);
-    combine_kernel<__nv_bfloat16><<<grid, WARPS * 32, 0, stream>>>(o_parts, lse_parts, out, out_lse, nullptr,
+    launch_dependent(combine_kernel<__nv_bfloat16>, dim3(grid), dim3(WARPS * 32), 0, stream, o_parts, lse_parts, out, out_lse, nullptr,
                                                                     attn_sink, batch, num_heads, parts, part_stride_o,
                                                                     part_stride_l, 1, 0);
     return check_launch("combine_kernel<parts>");

@@ -82,6 +82,25 @@ __device__ __forceinline__ float warp_sum(float v) {
     return v;
 }
 
+// Programmatic dependent launch: a kernel launched with launch_dependent() may start (and run everything that comes
+// before its grid_dep_wait()) while the kernel before it on the stream is still running; grid_dep_wait() returns
+// when that kernel has completed and its writes are visible.  A kernel that calls grid_dep_launch() lets the next
+// one start early.  Both are no-ops in a kernel that was launched the ordinary way.  The reference uses the same
+// mechanism between its scheduler, decode and combine kernels (csrc/kernel/decode/decode_launch.cu:46-49).
+__device__ __forceinline__ void grid_dep_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void grid_dep_launch() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_dependent(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid; cfg.blockDim = block; cfg.dynamicSmemBytes = smem; cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr; cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+
 // Host-side error plumbing (api.cu).
 int set_error(int code, const char* fmt, ...);
 int check_launch(const char* what);

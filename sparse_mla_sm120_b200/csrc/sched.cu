@@ -22,6 +22,7 @@ struct SchedArgs {
 };
 
 __global__ void __launch_bounds__(32) sched_meta_kernel(const SchedArgs a) {
+    grid_dep_launch();   // the attention kernel may start its prologue; it waits for this kernel before it reads the records
     extern __shared__ int sh[];
     int* nblk = sh;                    // [b]   blocks of request i
     int* nsp = sh + a.b;               // [b+1] nsp[i+1] = splits of request i, then their prefix sum
