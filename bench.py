@@ -44,7 +44,7 @@ WORKLOAD = ("V3.2-shape sparse-MLA decode: b=64/GPU, s_q=1, h_q=128, topk=2048, 
             "KV len U[4096,32768], paged block 64, packed FP8 656 B rows")
 # DRAM bytes of one launch of the attention kernel on this workload's shape, from one ncu capture
 # (dram__bytes_read.sum + dram__bytes_write.sum); the capture's summary is kept with the other profiles.
-NCU_TRAFFIC_BYTES = 91_298_048
+NCU_TRAFFIC_BYTES = 88_533_504
 CPU_SAMPLE_REQUESTS = 64   # requests of one step that the CPU legs compute: the whole step (about 0.13 s on 16 host threads)
 
 

@@ -39,6 +39,16 @@ enum {
     SMLA_E_DEVICE = -6       /* the kernel reported a device-side status (see smla_device_status) */
 };
 
+/*
+ * Device-side status.  The tcgen05 kernels bound every wait; a wait that gives up writes its code to
+ * status[0] (first one wins), counts the CTAs that gave up in status[1] and names one of them in status[2].
+ * smla_device_status copies the four words to the host (it synchronises the stream: not for the hot
+ * path), clears status[0..3] on the device when a code was set, and returns 0 or SMLA_E_DEVICE with the
+ * wait's name in smla_last_error().  smla_status_string names a code ("" for 0, "unknown" otherwise).
+ */
+int smla_device_status(int32_t* status, int32_t host_out[4], void* stream);
+const char* smla_status_string(int code);
+
 /* Kernel selection for the attention entry points. */
 enum {
     SMLA_IMPL_AUTO = 0,    /* tcgen05 kernel */

@@ -16,6 +16,8 @@ _lib = None
 _SIGS = {
     "smla_last_error": (c_char_p, []),
     "smla_version": (c_int, []),
+    "smla_device_status": (c_int, [c_void_p, c_void_p, c_void_p]),
+    "smla_status_string": (c_char_p, [c_int]),
     "smla_num_sms": (c_int, []),
     "smla_workspace_bytes": (c_size_t, [c_int, c_int, c_int]),
     "smla_sched_meta": (c_int, [c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]),

@@ -1,6 +1,7 @@
 """Host-side glue shared by the op modules: pointers, streams, cached scratch, split policy."""
 from __future__ import annotations
 
+import ctypes
 from typing import Dict, Optional, Tuple
 
 import torch
@@ -155,14 +156,7 @@ def check_status(device: Optional[torch.device] = None) -> None:
     if device is None:
         device = torch.device("cuda", torch.cuda.current_device())
     st = status_buffer(device)
-    vals = st.tolist()
-    if vals[0] != 0:
-        st.zero_()
-        names = {1: "empty", 2: "full", 3: "s_ready", 4: "p_ready", 5: "pv_done", 6: "q_ready", 7: "loaded",
-                 11: "indexer q_full", 12: "indexer k_full", 13: "indexer k_empty", 14: "indexer d_full",
-                 15: "indexer d_empty", 16: "indexer q_empty", 17: "indexer tmem",
-                 21: "pair k_empty", 22: "pair k_loaded", 23: "pair k_full", 24: "pair tile_info", 25: "pair v_empty",
-                 26: "pair v_loaded", 27: "pair v_full", 28: "pair s_ready", 29: "pair s_free", 30: "pair p_ready",
-                 31: "pair pv_done", 32: "pair q_ready"}
-        raise _lib.SmlaError(f"kernel wait gave up: barrier={names.get(vals[0], vals[0])} "
-                             f"ctas={vals[1]} last_cta={vals[2]}")
+    host = (ctypes.c_int32 * 4)()
+    rc = _lib.load().smla_device_status(ptr(st), ctypes.addressof(host), stream_ptr(device))
+    if rc != 0:
+        raise _lib.SmlaError(_lib.load().smla_last_error().decode())

@@ -51,6 +51,33 @@ using namespace smla;
 extern "C" {
 
 const char* smla_last_error(void) { return g_err; }
+
+const char* smla_status_string(int code) {
+    switch (code) {
+        case 0: return "";
+        case 11: return "indexer q_full"; case 12: return "indexer k_full"; case 13: return "indexer k_empty";
+        case 14: return "indexer d_full"; case 15: return "indexer d_empty"; case 16: return "indexer q_empty";
+        case 17: return "indexer tmem";
+        case 21: return "attention k_empty"; case 22: return "attention k_stored"; case 23: return "attention k_full";
+        case 24: return "attention half-tile record"; case 25: return "attention v_empty"; case 26: return "attention v_full (one CTA)";
+        case 27: return "attention v_full"; case 28: return "attention s_ready"; case 29: return "attention s_free";
+        case 30: return "attention p_ready"; case 31: return "attention pv_done"; case 32: return "attention q_ready";
+        case 33: return "attention q_staged"; case 34: return "attention q_free"; case 35: return "attention raw_empty";
+        case 36: return "attention raw_full";
+        default: return "unknown";
+    }
+}
+
+int smla_device_status(int32_t* status, int32_t host_out[4], void* stream) {
+    if (!status || !host_out) return set_error(SMLA_E_NULL, "smla_device_status: null pointer argument");
+    cudaError_t e = cudaMemcpyAsync(host_out, status, 4 * sizeof(int32_t), cudaMemcpyDeviceToHost, (cudaStream_t)stream);
+    if (e == cudaSuccess) e = cudaStreamSynchronize((cudaStream_t)stream);
+    if (e != cudaSuccess) return set_error((int)e, "smla_device_status: %s", cudaGetErrorString(e));
+    if (host_out[0] == 0) return 0;
+    cudaMemsetAsync(status, 0, 4 * sizeof(int32_t), (cudaStream_t)stream);
+    return set_error(SMLA_E_DEVICE, "kernel wait gave up: %s (code %d), %d CTAs, one of them CTA %d", smla_status_string(host_out[0]),
+                     host_out[0], host_out[1], host_out[2]);
+}
 int smla_version(void) { return 100; }
 
 int smla_num_sms(void) {

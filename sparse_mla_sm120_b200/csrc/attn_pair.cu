@@ -131,7 +131,7 @@ constexpr uint32_t IDESC_PV_F8 = instr_desc(FMT_E4M3, FMT_E4M3, false, true, 128
 constexpr uint32_t DESC_HI_SW128 = desc_hi(1024, (uint32_t)SWIZZLE_128B);
 
 // give-up codes reported through status[0]
-enum { W_QSTAGE = 17, W_QFREE = 18, W_RAWEMPTY = 19, W_RAWFULL = 20, W_KEMPTY = 21, W_KSTORED = 22, W_KFULL = 23, W_INFO = 24, W_VEMPTY = 25, W_VFULL_CTA = 26, W_VFULL = 27,
+enum { W_QSTAGE = 33, W_QFREE = 34, W_RAWEMPTY = 35, W_RAWFULL = 36, W_KEMPTY = 21, W_KSTORED = 22, W_KFULL = 23, W_INFO = 24, W_VEMPTY = 25, W_VFULL_CTA = 26, W_VFULL = 27,
        W_SREADY = 28, W_SFREE = 29, W_PREADY = 30, W_PVDONE = 31, W_QREADY = 32 };
 
 #ifdef SMLA_TRACE

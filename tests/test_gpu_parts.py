@@ -259,3 +259,27 @@ def test_cp_partition():
         ref_local, ref_len = orc.cp_partition_ref(idx, lo, hi)
         local, length = cp.partition_indices(idx.to(DEV), lo, hi)
         assert torch.equal(local.cpu(), ref_local) and torch.equal(length.cpu(), ref_len)
+
+
+def test_device_status_report_and_clear():
+    """The host side of a bounded wait that gave up, without making one give up: a status record is written into
+    the device buffer by hand; smla_device_status must report it, name the wait and clear the buffer."""
+    import ctypes
+    from sparse_mla_sm120_b200 import _lib
+    from sparse_mla_sm120_b200._runtime import check_status, ptr, status_buffer, stream_ptr
+    dev = torch.device(DEV)
+    lib = _lib.load()
+    st = status_buffer(dev)
+    st.zero_()
+    host = (ctypes.c_int32 * 4)()
+    assert lib.smla_device_status(ptr(st), ctypes.addressof(host), stream_ptr(dev)) == 0
+    st.copy_(torch.tensor([29, 2, 5, 0], dtype=torch.int32))
+    rc = lib.smla_device_status(ptr(st), ctypes.addressof(host), stream_ptr(dev))
+    assert rc == -6 and list(host) == [29, 2, 5, 0]
+    assert b"attention s_free" in lib.smla_last_error()
+    torch.cuda.synchronize()
+    assert st.tolist() == [0, 0, 0, 0]
+    st.copy_(torch.tensor([13, 1, 0, 0], dtype=torch.int32))
+    with pytest.raises(_lib.SmlaError, match="indexer k_empty"):
+        check_status(dev)
+    check_status(dev)       # cleared by the report
