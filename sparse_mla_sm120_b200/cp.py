@@ -28,6 +28,13 @@ from ._runtime import (FIXED_OVERHEAD, kv_geometry, num_sms, pick_num_sm_parts, 
                        status_buffer, stream_ptr)
 
 
+# Below this many bytes received per rank the partials of all ranks are simply all-gathered and merged (one
+# collective, (G-1) x T x H x 2052 bytes in); above it the exchange is all-to-all by head slice + all-gather of
+# the bf16 result (two collectives, traffic independent of G).  Both collectives cost 10-20 us of latency at
+# these sizes, which is what the limit weighs against the bytes.
+ALL_GATHER_LIMIT_BYTES = 8 << 20
+
+
 def shard_requests(num_requests: int, rank: int, world: int) -> Tuple[int, int]:
     """[begin, end) of the requests rank serves when a decode batch is sharded by sequence."""
     per, rem = divmod(num_requests, world)
@@ -187,7 +194,7 @@ def sparse_mla_decode_cp_fwd(q, kv_local, indices, sm_scale, shard_lo: int, shar
     rank = dist.get_rank(group) if dist.is_initialized() else 0
     T, H, _ = q.shape
     local_idx, local_len = partition_indices(indices, shard_lo, shard_hi)
-    if world > 1 and H % world == 0:
+    if world > 1 and H % world == 0 and (world - 1) * T * H * 2052 > ALL_GATHER_LIMIT_BYTES:
         # head-sliced exchange: per-rank traffic does not grow with the number of ranks
         b = _a2a_buffers(q.device, world, T, H)
         hs = H // world
@@ -262,6 +269,13 @@ class GraphedCpDecode:
         self.q.copy_(q)
         self.indices.copy_(indices)
         return self.replay()
+
+    def close(self):
+        """Drops the captured graph.  Call it before the process group is destroyed: a communicator whose
+        collectives are still referenced by a live CUDA graph may not shut down."""
+        torch.cuda.synchronize(self.q.device)
+        self.graph = None
+        self._step = None
 
     def replay(self):
         if self.graph is None:

@@ -793,14 +793,9 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PAIR_THREADS, 1) att
                     ok = mbar_wait_thread(bar(BAR_VEMPTY + vs), ((it / NV) - 1) & 1u, abort_flag, W_VEMPTY);
                     if (!ok) break;
                 }
-#ifdef SMLA_EXP_NOVCOPY
-                mbar_arrive(bar(BAR_VFULL + vs));
-                for (uint32_t r = 0; r < 0; ++r) {
-#else
                 mbar_arrive_expect_tx(bar(BAR_VFULL + vs), 4 * CHUNK);
 #pragma unroll
                 for (uint32_t r = 0; r < 2; ++r) {
-#endif
 #pragma unroll
                     for (uint32_t nb = 0; nb < 2; ++nb) {
                         bulk_copy_to_cluster(mapa_shared(base + VS_OFF + vs * VS_BYTES + (4 * nb + 2 * rank) * VSLOT, r),

@@ -31,7 +31,7 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity, uin
         "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
         "selp.u32 %0, 1, 0, p;\n\t}"
         : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
-    (void)hint_ns;
+    (void)hint_ns;     // passing the hint as the instruction's time limit made waits on the critical path wake later
     return ok != 0;
 }
 // One non-blocking poll.
@@ -74,31 +74,12 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
 // give-up protocol as mbar_wait.
 __device__ __forceinline__ bool mbar_wait_hot(uint32_t bar, uint32_t parity, volatile int* abort, int code) {
     uint32_t ok = 0;
-#ifdef SMLA_POLL_LANE0
-    // One polling lane per warp: 32 lanes re-polling one barrier are 32 shared-memory requests per round, which
-    // the working warps of the SM pay for.  The other lanes then take one (successful) poll of their own, which
-    // is what orders their later reads after the barrier's completion.
-    if ((threadIdx.x & 31) == 0) {
-        for (uint32_t i = 0; i < WAIT_POLLS; ++i) {
-            if (mbar_try_wait(bar, parity, WAIT_HINT_NS)) { ok = 1; break; }
-            if ((i & 255u) == 255u && *abort != 0) break;
-        }
-        if (!ok) atomicCAS(const_cast<int*>(abort), 0, code);
-    }
-    ok = __shfl_sync(0xffffffffu, ok, 0);
-    if (ok && (threadIdx.x & 31) != 0) ok = mbar_try_wait(bar, parity, WAIT_HINT_NS) ? 1u : 0u;
-    return __all_sync(0xffffffffu, ok != 0);
-#else
     for (uint32_t i = 0; i < WAIT_POLLS; ++i) {
         if (mbar_try_wait(bar, parity, WAIT_HINT_NS)) { ok = 1; break; }
-#ifdef SMLA_WAIT_SLEEP_NS
-        __nanosleep(SMLA_WAIT_SLEEP_NS);     // a warp that re-polls at once takes issue slots from the working warps of its scheduler
-#endif
         if ((i & 255u) == 255u && *abort != 0) break;
     }
     if (!ok) atomicCAS(const_cast<int*>(abort), 0, code);
     return __all_sync(0xffffffffu, ok != 0);
-#endif
 }
 
 // ------------------------------------------------------------------ thread-block cluster
@@ -204,9 +185,6 @@ __device__ __forceinline__ bool mbar_wait_thread_cluster(uint32_t bar, uint32_t 
 __device__ __forceinline__ bool mbar_wait_thread(uint32_t bar, uint32_t parity, volatile int* abort, int code) {
     for (uint32_t i = 0; i < WAIT_POLLS; ++i) {
         if (mbar_try_wait(bar, parity, WAIT_HINT_NS)) return true;
-#ifdef SMLA_WAIT_SLEEP_NS
-        __nanosleep(SMLA_WAIT_SLEEP_NS);
-#endif
         if ((i & 255u) == 255u && *abort != 0) return false;
     }
     atomicCAS(const_cast<int*>(abort), 0, code);

@@ -14,6 +14,8 @@ from helpers import make_case, oracle_attn, ROOT
 
 pytestmark = pytest.mark.gpu
 
+DEV = "cuda:0"
+
 
 @pytest.mark.parametrize("impl", [1, 2])
 @pytest.mark.parametrize("world", [2, 4])
@@ -187,6 +189,25 @@ torch.cuda.synchronize()
 ref_out, ref_lse = H.oracle_attn(case)
 H.compare_out(out, ref_out, H.TC_ABS, H.TC_REL, H.TC_COS)
 H.compare_lse(lse, ref_lse, H.TC_LSE)
+# the same step captured into one CUDA graph (collectives included), replayed twice on fresh inputs
+graphed = cp.GraphedCpDecode(kv_local, 4, 128, 1024, case["sm_scale"], lo, hi)
+for _ in range(2):
+    g_out, g_lse = graphed(case["q"].to(dev), case["indices"].to(dev))
+    torch.cuda.synchronize()
+    assert torch.equal(g_out, out) and torch.equal(g_lse, lse), "graph replay differs from the eager step"
+graphed.close()
+# the head-sliced exchange (the default above a traffic limit), forced for this small case
+cp.ALL_GATHER_LIMIT_BYTES = 0
+s_out, s_lse = cp.sparse_mla_decode_cp_fwd(case["q"].to(dev), kv_local, case["indices"].to(dev), case["sm_scale"], lo, hi)
+torch.cuda.synchronize()
+H.compare_out(s_out, ref_out, H.TC_ABS, H.TC_REL, H.TC_COS)
+H.compare_lse(s_lse, ref_lse, H.TC_LSE)
+# context-parallel prefill: the query tokens in chunks of 3 through the same exchange
+p_out, p_lse = cp.sparse_mla_prefill_cp_fwd(case["q"].to(dev), kv_local, case["indices"].to(dev), case["sm_scale"], lo, hi,
+                                           chunk_tokens=3)
+torch.cuda.synchronize()
+H.compare_out(p_out, ref_out, H.TC_ABS, H.TC_REL, H.TC_COS)
+H.compare_lse(p_lse, ref_lse, H.TC_LSE)
 # indexer -> distributed top-k -> context-parallel attention
 g = torch.Generator().manual_seed(47)
 qi = torch.randn(4, 64, 128, generator=g).to(torch.float8_e4m3fn)
@@ -213,9 +234,24 @@ case["indices"] = sel
 ref_out, ref_lse = H.oracle_attn(case)
 H.compare_out(out, ref_out, H.TC_ABS, H.TC_REL, H.TC_COS)
 H.compare_lse(lse, ref_lse, H.TC_LSE)
-dist.barrier(); dist.destroy_process_group()
-print("rank", rank, "ok")
+print("rank", rank, "ok", flush=True)
+dist.barrier(); torch.cuda.synchronize()
+os._exit(0)      # every rank leaves at once; nothing here depends on an orderly shutdown of the communicator
 '''
+
+
+def test_cp_prefill_chunks_without_a_process_group():
+    """Context-parallel prefill with a world of one: the chunking of the query tokens and the partition of the
+    indices over a shard that is the whole context."""
+    from sparse_mla_sm120_b200 import cp
+    case = make_case(31, 7, 64, 256, 16, invalid_tail=0.1)
+    ref_out, ref_lse = oracle_attn(case)
+    rows = case["packed"].shape[0] * 64
+    out, lse = cp.sparse_mla_prefill_cp_fwd(case["q"].to(DEV), case["packed"].to(DEV), case["indices"].to(DEV), case["sm_scale"],
+                                            0, rows, chunk_tokens=3)
+    torch.cuda.synchronize()
+    H.compare_out(out.cpu(), ref_out, H.TC_ABS, H.TC_REL, H.TC_COS)
+    H.compare_lse(lse.cpu(), ref_lse, H.TC_LSE)
 
 
 @pytest.mark.parametrize("world", [2, 4])
