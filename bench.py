@@ -580,6 +580,24 @@ def run_extras(device, hbm_peak, bf16_peak, peak_kind):
             "roofline": {"bound": "hbm", "kernel": "attn_pair_kernel", "achieved": by2 / ms2 / 1e6, "peak": hbm_peak, "unit": "GB/s",
                          "frac": by2 / ms2 / 1e6 / hbm_peak, "peak_kind": f"of {peak_kind}", "traffic": None,
                          "note": "whole step (CUDA graph replay), algorithmic bytes count each token's gathered rows"}}
+        # ---- small decode batches of the same shape (the split-KV path: scheduler + attention + combine as
+        # dependent launches), CUDA-graph replay
+        small = {}
+        for bsz in (1, 8, 32):
+            qs_, is_ = sets[0][0][:bsz].contiguous(), sets[0][1][:bsz].contiguous()
+            runb = lambda: flash_ops.sparse_mla_decode_fwd(qs_, pool, is_, SM_SCALE)
+            runb(); torch.cuda.synchronize()
+            gb = torch.cuda.CUDAGraph()
+            with torch.cuda.stream(side):
+                runb(); side.synchronize()
+                with torch.cuda.graph(gb, stream=side):
+                    runb()
+            torch.cuda.synchronize()
+            us = _time_cuda(gb.replay, 200, warm=5) * 1e3
+            small[f"b{bsz}"] = {"us_per_step": us, "gbs": algorithmic_bytes(bsz, TOPK) / us / 1e3}
+            del gb
+        out["decode_small_batches"] = {"workload": "the headline's decode shape at 1, 8 and 32 requests (rows of the first input set)",
+                                       **small}
         del pool, sets, q2, i2
     except Exception as e:           # noqa: BLE001 - a secondary measurement must not take the others down
         out["decode_mtp_sq2"] = {"error": repr(e)}

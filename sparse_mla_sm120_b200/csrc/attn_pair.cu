@@ -119,7 +119,8 @@ constexpr uint32_t SMEM_BYTES = MISC_OFF + 16;
 constexpr uint32_t SMEM_ALLOC = SMEM_BYTES + 1024;   // slack for the 1024-byte alignment
 static_assert(SMEM_ALLOC <= 227 * 1024, "shared memory budget");
 static_assert(KS_BYTES % 1024 == 0 && VS_BYTES % 1024 == 0 && KS_OFF % 1024 == 0, "swizzled tiles need 1024-byte alignment");
-static_assert(NK * KS_BYTES >= OWN_N * D_QK * 2, "the K stages hold the staged Q rows of a CTA");
+constexpr uint32_t QSTAGE_OFF = KS_OFF + KS_BYTES;   // the staged Q rows of the first request: K stage 1 and the V stage behind it
+static_assert(NK == 2 && (NK - 1) * KS_BYTES + NV * VS_BYTES >= OWN_N * D_QK * 2, "K stage 1 + V stage hold the staged Q rows of a CTA");
 static_assert(BAR_OFF % 8 == 0 && INFO_OFF % 16 == 0 && RAW_OFF % 16 == 0 && RAW_BYTES % 16 == 0, "alignment of barriers and bulk-copied records");
 
 constexpr uint32_t TMEM_COLS = 512;
@@ -191,7 +192,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PAIR_THREADS, 1) att
 
     if (tid == 0) {
         mbar_init(bar(BAR_QSTAGE), 1);
-        mbar_init(bar(BAR_QFREE), N_SM_WARPS);
+        mbar_init(bar(BAR_QFREE), 2 * N_SM_WARPS);   // both CTAs' softmax warps: the partner's copies land in this CTA's V stage too
         for (int s = 0; s < NK; ++s) {
             mbar_init(bar(BAR_KSTORED + s), N_G_WARPS);          // this CTA's rows of the stage are in shared memory
             mbar_init(bar(BAR_KFULLP + s), 2 * N_G_WARPS);       // both CTAs' rows are
@@ -236,16 +237,18 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PAIR_THREADS, 1) att
     grid_dep_launch();
     const SchedMeta meta = load_meta(p, part);
     // The Q rows of the first request (this CTA's heads: one contiguous piece of global memory) come in by one bulk
-    // copy into the K stages, which are empty until the first tile has been gathered and shifted; the softmax warps
-    // then quantise Q out of shared memory instead of waiting for global memory several times in a row.
+    // copy into K stage 1 and the V stage behind it, which nothing needs before the second tile is stored and the
+    // first tile's V copies are issued; the softmax warps then quantise Q out of shared memory instead of waiting
+    // for global memory several times in a row.  K stage 0 takes the first tile meanwhile.
     const int last_req = min(meta.end_req, p.num_tokens - 1);
     const int live_heads = min(heads_cta, max(p.num_heads - head0, 0));
     Work w_first;
-    const bool q_staged = meta.begin_req <= last_req && live_heads > 0 && get_work(p, meta, meta.begin_req, w_first);
+    const bool first_work = meta.begin_req <= last_req && get_work(p, meta, meta.begin_req, w_first);   // the same in both CTAs
+    const bool q_staged = first_work && live_heads > 0;
     if (tid == 0 && q_staged) {
         const uint32_t bytes = (uint32_t)live_heads * D_QK * 2;
         mbar_arrive_expect_tx(bar(BAR_QSTAGE), bytes);
-        bulk_copy_g2s(base + KS_OFF, reinterpret_cast<unsigned long long>(p.q + ((size_t)meta.begin_req * p.num_heads + head0) * D_QK),
+        bulk_copy_g2s(base + QSTAGE_OFF, reinterpret_cast<unsigned long long>(p.q + ((size_t)meta.begin_req * p.num_heads + head0) * D_QK),
                       bytes, bar(BAR_QSTAGE));
     }
 
@@ -286,7 +289,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PAIR_THREADS, 1) att
                 const bool from_smem = q_staged && req == meta.begin_req;
                 if (from_smem && !dead) dead = !mbar_wait_hot(bar(BAR_QSTAGE), 0u, abort_flag, W_QSTAGE);
                 // row (head0 + r) of the request's Q, wherever it lies
-                const __nv_bfloat16* qrows = from_smem ? reinterpret_cast<const __nv_bfloat16*>(sm + KS_OFF) - (size_t)head0 * D_QK
+                const __nv_bfloat16* qrows = from_smem ? reinterpret_cast<const __nv_bfloat16*>(sm + QSTAGE_OFF) - (size_t)head0 * D_QK
                                                        : p.q + (size_t)req * p.num_heads * D_QK;
 #pragma unroll 1
                 for (int hf = 0; hf < 2; ++hf) {
@@ -358,7 +361,10 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PAIR_THREADS, 1) att
                     tc_fence_before();     // also orders the previous epilogue's TMEM reads before the next MMAs
                 }
                 __syncwarp();
-                if (from_smem && lane == 0) mbar_arrive(bar(BAR_QFREE));   // this warp has read the staged rows for the last time
+                if (first_work && req == meta.begin_req && lane == 0) {   // this warp has read the staged rows for the last time (if any): tell both CTAs
+                    mbar_arrive(bar(BAR_QFREE));
+                    mbar_arrive_remote(mapa_shared(bar(BAR_QFREE), 1u - rank));
+                }
             }
             if (named_bar_or(1 + grp, 128, dead || *abort_flag != 0)) { stop = true; break; }
             TRACE(2, it);
@@ -631,7 +637,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PAIR_THREADS, 1) att
                 }
                 PROF(2);
                 if (ok && t_it >= NK) ok = mbar_wait_hot(bar(BAR_KEMPTY + ks), ((t_it / NK) - 1) & 1u, abort_flag, W_KEMPTY);
-                if (ok && t_it < NK && q_staged) ok = mbar_wait_hot(bar(BAR_QFREE), 0u, abort_flag, W_QFREE);   // the K stages held Q until now
+                if (ok && t_it < NK && ks != 0 && first_work) ok = mbar_wait_hot(bar(BAR_QFREE), 0u, abort_flag, W_QFREE);   // K stage 1 held Q until now
                 PROF(3);
                 if (named_bar_or(3, N_G_WARPS * 32, !ok || *abort_flag != 0)) { stop = true; break; }
                 PROF(4);
@@ -791,6 +797,9 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PAIR_THREADS, 1) att
                                      mapa_shared(bar(BAR_INFO + ir), peer));
                 if (it >= NV) {
                     ok = mbar_wait_thread(bar(BAR_VEMPTY + vs), ((it / NV) - 1) & 1u, abort_flag, W_VEMPTY);
+                    if (!ok) break;
+                } else if (first_work) {    // the V stages of both CTAs held Q until the softmax warps had read it
+                    ok = mbar_wait_thread(bar(BAR_QFREE), 0u, abort_flag, W_QFREE);
                     if (!ok) break;
                 }
                 mbar_arrive_expect_tx(bar(BAR_VFULL + vs), 4 * CHUNK);
