@@ -600,8 +600,10 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PAIR_THREADS, 1) att
             for (int k = 0; k < nst; ++k) {
                 const uint32_t t_it = it + k, ks = t_it % NK, rs = t_it % NR;
                 PROF(0);
+                TRACE(60, t_it);
                 if (ok) ok = mbar_wait_hot(bar(BAR_RAWFULL + rs * N_P_WARPS + gw * RPW / 16), (t_it / NR) & 1u, abort_flag, W_RAWFULL);
                 PROF(1);
+                TRACE(61, t_it);
                 const uint32_t vbits = __ballot_sync(0xffffffffu, idx_cur >= 0) & ((1u << RPW) - 1u);
                 idx_cur = idx_nxt;
                 idx_nxt = fetch_idx(k + 2);
@@ -636,11 +638,14 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PAIR_THREADS, 1) att
                     mbar_arrive(bar(BAR_RAWEMPTY + rs * N_P_WARPS + gw * RPW / 16));
                 }
                 PROF(2);
+                TRACE(62, t_it);
                 if (ok && t_it >= NK) ok = mbar_wait_hot(bar(BAR_KEMPTY + ks), ((t_it / NK) - 1) & 1u, abort_flag, W_KEMPTY);
                 if (ok && t_it < NK && ks != 0 && first_work) ok = mbar_wait_hot(bar(BAR_QFREE), 0u, abort_flag, W_QFREE);   // K stage 1 held Q until now
                 PROF(3);
+                TRACE(63, t_it);
                 if (named_bar_or(3, N_G_WARPS * 32, !ok || *abort_flag != 0)) { stop = true; break; }
                 PROF(4);
+                TRACE(64, t_it);
                 // the half tile's scale and validity bits from the eight warps' records
                 const float2 g = gx[(t_it & 1u) * N_G_WARPS + (lane & (N_G_WARPS - 1))];
                 float s_half = g.x;
@@ -677,6 +682,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PAIR_THREADS, 1) att
                     *reinterpret_cast<uint2*>(rec + 16) = make_uint2(vpart, vword1);
                 }
                 PROF(5);
+                TRACE(65, t_it);
                 fence_proxy_async();
                 __syncwarp();
                 if (lane == 0) {
