@@ -149,7 +149,11 @@ __device__ __forceinline__ void trace(TraceCursor& c, int tag, int tile) {
         ++c.n;
     }
 }
+#ifdef SMLA_TRACE_GATHER_ONLY      // only the 6x trace points of the gather role (the other roles keep their registers)
+#define TRACE(tag, tile) { if ((tag) >= 60 && (tag) < 70) trace(tcur, tag, (int)(tile)); }
+#else
 #define TRACE(tag, tile) trace(tcur, tag, (int)(tile))
+#endif
 #else
 #define TRACE(tag, tile)
 #endif
