@@ -21,20 +21,20 @@
 // csrc/kernel/common/fp8_quant.cuh:44-103, csrc/kernel/decode/decode_v2_kernel.cuh:414-493):
 //   * Q no-PE is quantised to e4m3 with one power-of-two scale sq_h per head; Q RoPE stays bf16
 //     and is pre-divided by that scale.
-//   * K/V bytes are consumed as stored, re-expressed against ONE scale s per half tile (the 64 rows
-//     one CTA gathered): the largest of the 4 x 64 scales of these rows.  A 128-value block with a
-//     smaller scale is shifted down (a power-of-two division done on the exponent fields: exact
-//     while the shifted value stays a normal e4m3 number; a value that would fall below 2^-6 is cut
-//     to the subnormal grid, i.e. it is off by at most 2^-15 of the largest value the half tile can
-//     hold, which is far below the e4m3 rounding step of the values that dominate a dot product).
-//     The shift happens in registers on the way from global to shared memory.  K RoPE is
-//     pre-divided by s.  One accumulator then holds S = (q . k) / (sq_h * s).
+//   * K/V bytes are consumed as stored, re-expressed against ONE scale s per group of eight rows (the
+//     rows one gather warp handles): the largest of the 4 x 8 scales of these rows.  A 128-value
+//     block with a smaller scale is shifted down (a power-of-two division done on the exponent
+//     fields: exact while the shifted value stays a normal e4m3 number; a value that would fall below
+//     2^-6 is cut to the subnormal grid, i.e. it is off by at most 2^-15 of the largest value the
+//     group can hold, which is far below the e4m3 rounding step of the values that dominate a dot
+//     product).  The shift happens in registers on the way from the raw stage to the MMA layout.
+//     K RoPE is pre-divided by s.  One accumulator then holds S = (q . k) / (sq_h * s).
 //   * The scale of V is folded into the exponent: z = S*sq_h*s*sm_scale*log2e + log2(s),
 //     P' = 2^(z - m) with m the (lazily updated) running maximum of z, so that
 //     O_acc = sum_t P'_t * Vfp8_t needs no scale; the denominator is tracked apart as
-//     l = sum over half tiles of (sum_t P'_t) / s in fp32.  O = O_acc / l, LSE = log2(l) + m (base 2,
-//     as the reference).  A softmax thread's 32 tokens lie in one half tile, so its loops read
-//     nothing per token.
+//     l = sum over groups of (sum_t P'_t) / s in fp32.  O = O_acc / l, LSE = log2(l) + m (base 2,
+//     as the reference).  A softmax thread's 32 tokens are four such groups, so its loops read four
+//     records per tile and nothing per token.
 //   * P' is rounded to e4m3 (times 2^P_SHIFT); the accumulator is rescaled only when a row
 //     maximum grows by more than 2^RESCALE_TAU, which is exact because l and O share m.
 //   * Invalid entries (index < 0, position >= topk_length) are never loaded: their shared-memory
@@ -44,13 +44,14 @@
 //   warps 0-7    softmax + epilogue + Q quantisation (thread = one head x 32 tokens of a tile; the four
 //                warps that share 32 heads exchange row maxima through shared memory).
 //   warps 8-15   gather: warp g reads rows [8 g, +8) of the CTA's 64 from a raw stage (the rows as they
-//                lie in the cache) into registers, the eight warps agree on the half tile's scale through
-//                shared memory, every lane shifts its pieces and stores them in the layout the MMAs read.
+//                lie in the cache) into registers, takes the largest of their scales as the scale of its
+//                group, every lane shifts its pieces and stores them in the layout the MMAs read.  The
+//                gather warps never wait for each other.
 //   warp 16      lane 0 issues the score MMAs, warp 17 lane 0 the P.V MMAs -- in the even CTA only, which
 //                is also where the barriers that collect arrivals from both CTAs live.  Completion of
 //                MMAs reaches both CTAs through one tcgen05.commit per CTA.
 //   warp 19      lane 0 issues the bulk copies K stage -> V slots (own and partner's), sends the half
-//                tile's scale record to the partner, waits for the V slots of its CTA to fill and passes
+//                tile's scale records to the partner, waits for the V slots of its CTA to fill and passes
 //                that on (V full to the even CTA, K stage free to both).
 //   warps 20-23  copy issuers: one bulk copy global -> raw stage per row, two tiles ahead.
 // Every wait is bounded; a wait that gives up records a code in status[] and the CTA drains and
@@ -68,7 +69,6 @@ using namespace attn;
 
 constexpr int N_SM_WARPS = 8, N_G_WARPS = 8;
 constexpr int RPW = 64 / N_G_WARPS;     // rows of a tile per gather warp
-constexpr int WPW = 32 / RPW;           // gather warps per 32 rows (one word of validity bits)
 constexpr int MMA_WARP = N_SM_WARPS + N_G_WARPS;
 constexpr int FWD_WARP = MMA_WARP + 3;
 constexpr int PROD_WARP0 = MMA_WARP + 4, N_P_WARPS = 4;      // copy issuers: warp p looks after the rows of gather warps 2 p and 2 p + 1
@@ -102,9 +102,9 @@ constexpr uint32_t VS_BYTES = 8 * VSLOT;             // 32768
 constexpr uint32_t RAW_OFF = VS_OFF + NV * VS_BYTES; // raw stages: [64 rows x 656 B] as they lie in the cache
 constexpr uint32_t RAW_BYTES = OWN_N * ROW_BYTES;    // 41984
 constexpr int INFO_RING = 8;                         // half-tile records outlive their K stage: the softmax reads them after the scores
-constexpr uint32_t INFO_OFF = RAW_OFF + NR * RAW_BYTES;  // [INFO_RING][2 halves] x 32 B: (s, log2 s, 1/s, 0) and the 64 validity bits of the half tile
-constexpr uint32_t GX_OFF = INFO_OFF + INFO_RING * 64; // [2][N_G_WARPS] x 8 B: per gather warp the largest scale and the validity bits of its rows
-constexpr uint32_t XCH_OFF = GX_OFF + 2 * N_G_WARPS * 8; // row-maximum exchange [2][4][64] fp32, then Q scales [64] fp32
+constexpr uint32_t INFO_HALF = N_G_WARPS * 16;       // a half tile's record: per gather warp (s, log2 s, 1/s, validity bits) of its RPW rows
+constexpr uint32_t INFO_OFF = RAW_OFF + NR * RAW_BYTES;  // [INFO_RING][2 halves] x INFO_HALF
+constexpr uint32_t XCH_OFF = INFO_OFF + INFO_RING * 2 * INFO_HALF; // row-maximum exchange [2][4][64] fp32, then Q scales [64] fp32
 constexpr uint32_t XCH_BYTES = 2 * 4 * 64 * 4 + 64 * 4;
 constexpr uint32_t BAR_OFF = XCH_OFF + XCH_BYTES;
 // barriers (8 B each).  "P" barriers collect arrivals from both CTAs and are used in the even CTA only.
@@ -121,6 +121,7 @@ static_assert(SMEM_ALLOC <= 227 * 1024, "shared memory budget");
 static_assert(KS_BYTES % 1024 == 0 && VS_BYTES % 1024 == 0 && KS_OFF % 1024 == 0, "swizzled tiles need 1024-byte alignment");
 constexpr uint32_t QSTAGE_OFF = KS_OFF + KS_BYTES;   // the staged Q rows of the first request: K stage 1 and the V stage behind it
 static_assert(NK == 2 && (NK - 1) * KS_BYTES + NV * VS_BYTES >= OWN_N * D_QK * 2, "K stage 1 + V stage hold the staged Q rows of a CTA");
+static_assert(RPW == 8, "a softmax thread reads the records of four groups of eight tokens");
 static_assert(BAR_OFF % 8 == 0 && INFO_OFF % 16 == 0 && RAW_OFF % 16 == 0 && RAW_BYTES % 16 == 0, "alignment of barriers and bulk-copied records");
 
 constexpr uint32_t TMEM_COLS = 512;
@@ -392,8 +393,10 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PAIR_THREADS, 1) att
             for (int j = 0; j < nst; ++j, ++it) {
                 const uint32_t b = it & 1u;
                 float z[32];
-                float mx_loc = -INFINITY, inv_tile = 0.f;
-                const uint8_t* info = sm + INFO_OFF + (it & (INFO_RING - 1)) * 64 + thalf * 32;   // the record of this thread's half tile
+                float mx_loc = -INFINITY;
+                float inv_g[4] = {0.f, 0.f, 0.f, 0.f};     // 1/s of the four groups of eight tokens that this thread holds
+                // the records of this thread's 32 tokens: half tile thalf, gather warps [4 ch, 4 ch + 4)
+                const uint8_t* info = sm + INFO_OFF + (it & (INFO_RING - 1)) * (2 * INFO_HALF) + thalf * INFO_HALF + ch * 64;
                 PROF(0);
                 if (!dead) dead = !mbar_wait_hot(bar(BAR_SREADY + b), (it >> 1) & 1u, abort_flag, W_SREADY);
                 PROF(1);
@@ -409,29 +412,26 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PAIR_THREADS, 1) att
                     tc_fence_before();
                     __syncwarp();
                     if (lane == 0) mbar_arrive_remote(barp(BAR_SFREEP + b));   // the score buffer may be overwritten
-                    const float4 ti = *reinterpret_cast<const float4*>(info);                 // (s, log2 s, 1/s, 0) of the half tile
-                    const uint32_t valid = reinterpret_cast<const uint32_t*>(info + 16)[ch];  // this thread's 32 tokens
-                    const float c_tile = ti.x * my_sqc, off = ti.y;
-                    inv_tile = ti.z;
+                    uint32_t valid = 0u;
                     float mx0 = -INFINITY, mx1 = -INFINITY;
 #pragma unroll
-                    for (int t = 0; t < 32; t += 4) {
-                        z[t + 0] = fmaf(__uint_as_float(sv[t + 0]), c_tile, off);
-                        z[t + 1] = fmaf(__uint_as_float(sv[t + 1]), c_tile, off);
-                        z[t + 2] = fmaf(__uint_as_float(sv[t + 2]), c_tile, off);
-                        z[t + 3] = fmaf(__uint_as_float(sv[t + 3]), c_tile, off);
-                    }
-                    if (valid != 0xffffffffu) {     // tokens without an entry: weight exactly 0
+                    for (int g = 0; g < 4; ++g) {
+                        const float4 ti = *reinterpret_cast<const float4*>(info + 16 * g);    // (s, log2 s, 1/s, validity bits) of the group
+                        const float c_g = ti.x * my_sqc, off = ti.y;
+                        inv_g[g] = ti.z;
+                        valid |= (__float_as_uint(ti.w) & 0xffu) << (8 * g);
+                        float gm = -INFINITY;
 #pragma unroll
-                        for (int t = 0; t < 32; ++t) z[t] = ((valid >> t) & 1u) ? z[t] : -INFINITY;
+                        for (int t = 8 * g; t < 8 * g + 8; ++t) {
+                            z[t] = fmaf(__uint_as_float(sv[t]), c_g, off);
+                            if (!((__float_as_uint(ti.w) >> (t - 8 * g)) & 1u)) z[t] = -INFINITY;   // no entry: weight exactly 0
+                            gm = fmaxf(gm, z[t]);
+                        }
+                        // z - log2(s) is the scaled logit itself
+                        if (p.out_max_logits != nullptr && gm > -INFINITY) x_max = fmaxf(x_max, gm - off);
+                        if (g & 1) mx1 = fmaxf(mx1, gm); else mx0 = fmaxf(mx0, gm);
                     }
-#pragma unroll
-                    for (int t = 0; t < 32; t += 4) {
-                        mx0 = fmaxf(mx0, fmaxf(z[t], z[t + 1]));
-                        mx1 = fmaxf(mx1, fmaxf(z[t + 2], z[t + 3]));
-                    }
-                    // z - log2(s) is the scaled logit itself
-                    if (p.out_max_logits != nullptr && fmaxf(mx0, mx1) > -INFINITY) x_max = fmaxf(x_max, fmaxf(mx0, mx1) - off);
+                    (void)valid;
                     mx_loc = fmaxf(mx0, mx1);
                     xch[(b * 4 + xpart) * 64 + hrow] = mx_loc;
                     PROF(4);
@@ -470,15 +470,18 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PAIR_THREADS, 1) att
                 PROF(7);
                 const float m_off = ((m_run == -INFINITY) ? 0.f : m_run) - (float)P_SHIFT;
                 uint32_t pw[8];
-                float l0 = 0.f, l1 = 0.f;
 #pragma unroll
-                for (int t = 0; t < 32; t += 4) {
-                    const float p0 = ex2(z[t + 0] - m_off), p1 = ex2(z[t + 1] - m_off);
-                    const float p2 = ex2(z[t + 2] - m_off), p3 = ex2(z[t + 3] - m_off);
-                    l0 += p0 + p2; l1 += p1 + p3;
-                    pw[t >> 2] = pack_e4m3x4(p0, p1, p2, p3);
+                for (int g = 0; g < 4; ++g) {
+                    float l0 = 0.f, l1 = 0.f;
+#pragma unroll
+                    for (int t = 8 * g; t < 8 * g + 8; t += 4) {
+                        const float p0 = ex2(z[t + 0] - m_off), p1 = ex2(z[t + 1] - m_off);
+                        const float p2 = ex2(z[t + 2] - m_off), p3 = ex2(z[t + 3] - m_off);
+                        l0 += p0 + p2; l1 += p1 + p3;
+                        pw[t >> 2] = pack_e4m3x4(p0, p1, p2, p3);
+                    }
+                    l_run = fmaf(l0 + l1, inv_g[g], l_run);
                 }
-                l_run = fmaf(l0 + l1, inv_tile, l_run);
                 PROF(8);
                 // P' of tokens [64*thalf + 32*ch, +32) of head hrow: two 16-byte pieces of the row
                 uint8_t* pb = sm + PB_OFF + b * CHUNK;
@@ -580,12 +583,11 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PAIR_THREADS, 1) att
         // =================================================================== gather
         // Warp gw reads rows [8 gw, +8) of this CTA's 64 rows of every tile from the raw stage into registers: per
         // row one 16-byte piece of the 512 no-PE bytes per lane, plus (spread over the lanes) the rows' RoPE bytes
-        // and scale words.  The eight warps then agree on the half tile's scale, every lane shifts its pieces
-        // onto it and stores them in the layout the MMAs read.
+        // and scale words.  The largest of the rows' scales is the scale of the warp's group; every lane shifts its
+        // pieces onto it and stores them in the layout the MMAs read.
         const int gw = warp - N_SM_WARPS;
         const int blk = lane >> 3;                                   // 128-value block of this lane's piece
         const int pbs_shift = (p.page_block_size & (p.page_block_size - 1)) == 0 ? __ffs(p.page_block_size) - 1 : -1;
-        float2* gx = reinterpret_cast<float2*>(sm + GX_OFF);         // [2][N_G_WARPS]
         uint32_t it = 0;
         bool ok = true, stop = false;
         for (int req = meta.begin_req; req <= last_req && !stop; ++req) {
@@ -635,31 +637,20 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PAIR_THREADS, 1) att
                 float wm = sc;
 #pragma unroll
                 for (int o = 16; o >= 1; o >>= 1) wm = fmaxf(wm, __shfl_xor_sync(0xffffffffu, wm, o));
-                if (lane == 0) {
-                    gx[(t_it & 1u) * N_G_WARPS + gw] = make_float2(wm, __uint_as_float(vbits));
-                    // the maximum needed the last shared-memory load of every lane (they return in order): the warp's rows
-                    // have left the raw stage
-                    mbar_arrive(bar(BAR_RAWEMPTY + rs * N_P_WARPS + gw * RPW / 16));
-                }
+                // the maximum needed the last shared-memory load of every lane (they return in order): the warp's rows
+                // have left the raw stage
+                if (lane == 0) mbar_arrive(bar(BAR_RAWEMPTY + rs * N_P_WARPS + gw * RPW / 16));
                 PROF(2);
                 TRACE(62, t_it);
                 if (ok && t_it >= NK) ok = mbar_wait_hot(bar(BAR_KEMPTY + ks), ((t_it / NK) - 1) & 1u, abort_flag, W_KEMPTY);
                 if (ok && t_it < NK && ks != 0 && first_work) ok = mbar_wait_hot(bar(BAR_QFREE), 0u, abort_flag, W_QFREE);   // K stage 1 held Q until now
                 PROF(3);
                 TRACE(63, t_it);
-                if (named_bar_or(3, N_G_WARPS * 32, !ok || *abort_flag != 0)) { stop = true; break; }
+                if (!ok) { stop = true; break; }
                 PROF(4);
                 TRACE(64, t_it);
-                // the half tile's scale and validity bits from the eight warps' records
-                const float2 g = gx[(t_it & 1u) * N_G_WARPS + (lane & (N_G_WARPS - 1))];
-                float s_half = g.x;
-                uint32_t vpart = __float_as_uint(g.y) << (RPW * (lane & (WPW - 1)));     // warp g looks after rows [RPW g, +RPW)
-#pragma unroll
-                for (int o = 1; o < N_G_WARPS; o <<= 1) {
-                    s_half = fmaxf(s_half, __shfl_xor_sync(0xffffffffu, s_half, o));
-                    if (o < WPW) vpart |= __shfl_xor_sync(0xffffffffu, vpart, o);
-                }
-                const uint32_t vword1 = __shfl_sync(0xffffffffu, vpart, WPW);    // rows 32-63 (lane 0 holds rows 0-31)
+                // one scale for the warp's RPW rows: the largest of their 4 x RPW scales
+                const float s_half = wm;
                 const float inv_half = (s_half > 0.f) ? __uint_as_float(0x7f000000u - __float_as_uint(s_half)) : 0.f;
                 const __nv_bfloat162 rope_f = __float2bfloat162_rn(inv_half);
                 uint8_t* kp = sm + KS_OFF + ks * KS_BYTES;
@@ -679,11 +670,11 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PAIR_THREADS, 1) att
                     v.z = mul_bf16x2(v.z, rope_f); v.w = mul_bf16x2(v.w, rope_f);
                     *reinterpret_cast<uint4*>(kp + KS_ROPE + swz((uint32_t)(gw * RPW + (lane >> 3) + 4 * u), (uint32_t)lane & 7u)) = v;
                 }
-                if (gw == 0 && lane == 0) {      // this half tile's record: read by this CTA's softmax warps and sent to the partner's
-                    uint8_t* rec = sm + INFO_OFF + (t_it & (INFO_RING - 1)) * 64 + rank * 32;
+                if (lane == 0) {      // the record of the warp's rows: read by this CTA's softmax warps and sent to the partner's
+                    uint8_t* rec = sm + INFO_OFF + (t_it & (INFO_RING - 1)) * (2 * INFO_HALF) + rank * INFO_HALF + gw * 16;
                     *reinterpret_cast<float4*>(rec) =
-                        make_float4(s_half, (s_half > 0.f) ? (float)((int)(__float_as_uint(s_half) >> 23) - 127) : -INFINITY, inv_half, 0.f);
-                    *reinterpret_cast<uint2*>(rec + 16) = make_uint2(vpart, vword1);
+                        make_float4(s_half, (s_half > 0.f) ? (float)((int)(__float_as_uint(s_half) >> 23) - 127) : -INFINITY, inv_half,
+                                    __uint_as_float(vbits));
                 }
                 PROF(5);
                 TRACE(65, t_it);
@@ -788,7 +779,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PAIR_THREADS, 1) att
         // The no-PE bytes of this CTA's 64 rows lie in the K stage as four chunks of [64 rows x 128 dims], which is
         // two V slots each (rows 0-31 and 32-63) in the slots' own layout.  Chunks 2 r and 2 r + 1 go to CTA r: the
         // chunks of the own dims stay in this CTA, the others cross to the partner.  The destination's barrier
-        // counts the bytes.  The half tile's scale record travels the same way.  When this CTA's slots are full
+        // counts the bytes.  The half tile's scale records travel the same way.  When this CTA's slots are full
         // (its own copies and the partner's have landed) the thread passes that on: V full to the even CTA,
         // K stage free to both.
         const uint32_t peer = 1u - rank;
@@ -802,9 +793,9 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PAIR_THREADS, 1) att
                 const uint32_t ks = it % NK, vs = it % NV, ir = it & (INFO_RING - 1);
                 ok = mbar_wait_thread(bar(BAR_KSTORED + ks), (it / NK) & 1u, abort_flag, W_KSTORED);
                 if (!ok) break;
-                mbar_arrive_expect_tx(bar(BAR_INFO + ir), 32);
-                bulk_copy_to_cluster(mapa_shared(base + INFO_OFF + ir * 64 + rank * 32, peer), base + INFO_OFF + ir * 64 + rank * 32, 32,
-                                     mapa_shared(bar(BAR_INFO + ir), peer));
+                mbar_arrive_expect_tx(bar(BAR_INFO + ir), INFO_HALF);
+                bulk_copy_to_cluster(mapa_shared(base + INFO_OFF + ir * (2 * INFO_HALF) + rank * INFO_HALF, peer),
+                                     base + INFO_OFF + ir * (2 * INFO_HALF) + rank * INFO_HALF, INFO_HALF, mapa_shared(bar(BAR_INFO + ir), peer));
                 if (it >= NV) {
                     ok = mbar_wait_thread(bar(BAR_VEMPTY + vs), ((it / NV) - 1) & 1u, abort_flag, W_VEMPTY);
                     if (!ok) break;
