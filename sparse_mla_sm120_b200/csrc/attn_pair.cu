@@ -150,8 +150,8 @@ __device__ __forceinline__ void trace(TraceCursor& c, int tag, int tile) {
         ++c.n;
     }
 }
-#ifdef SMLA_TRACE_GATHER_ONLY      // only the 6x trace points of the gather role (the other roles keep their registers)
-#define TRACE(tag, tile) { if ((tag) >= 60 && (tag) < 70) trace(tcur, tag, (int)(tile)); }
+#ifdef SMLA_TRACE_FROM             // only the trace points with tags in [SMLA_TRACE_FROM, SMLA_TRACE_TO): the other roles keep their registers
+#define TRACE(tag, tile) { if ((tag) >= SMLA_TRACE_FROM && (tag) < SMLA_TRACE_TO) trace(tcur, tag, (int)(tile)); }
 #else
 #define TRACE(tag, tile) trace(tcur, tag, (int)(tile))
 #endif
@@ -654,10 +654,11 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PAIR_THREADS, 1) att
                 const float inv_half = (s_half > 0.f) ? __uint_as_float(0x7f000000u - __float_as_uint(s_half)) : 0.f;
                 const __nv_bfloat162 rope_f = __float2bfloat162_rn(inv_half);
                 uint8_t* kp = sm + KS_OFF + ks * KS_BYTES;
+                // exponent shift of the block whose scale this lane loaded (row lane / 4, block lane % 4): 0 for a block at the scale
+                const uint32_t my_sub = (sc > 0.f) ? shift_bytes_of_ratio(sc * inv_half) : 0u;
 #pragma unroll
                 for (int i = 0; i < RPW; ++i) {
-                    const float sci = __shfl_sync(0xffffffffu, sc, 4 * i + blk);
-                    const uint32_t sub = (sci > 0.f) ? shift_bytes_of_ratio(sci * inv_half) : 0u;   // 0 for a block that is at the scale
+                    const uint32_t sub = __shfl_sync(0xffffffffu, my_sub, 4 * i + blk);
                     uint4 v = nope[i];      // no branch on sub: a shift by 0 is the identity, and a branch would keep the rows' chains apart
                     v.x = shift_down_e4m3x4(v.x, sub); v.y = shift_down_e4m3x4(v.y, sub);
                     v.z = shift_down_e4m3x4(v.z, sub); v.w = shift_down_e4m3x4(v.w, sub);
@@ -791,8 +792,10 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PAIR_THREADS, 1) att
             const int nst = (w.nblk + 1) >> 1;
             for (int j = 0; j < nst && ok; ++j, ++it) {
                 const uint32_t ks = it % NK, vs = it % NV, ir = it & (INFO_RING - 1);
+                TRACE(70, it);
                 ok = mbar_wait_thread(bar(BAR_KSTORED + ks), (it / NK) & 1u, abort_flag, W_KSTORED);
                 if (!ok) break;
+                TRACE(71, it);
                 mbar_arrive_expect_tx(bar(BAR_INFO + ir), INFO_HALF);
                 bulk_copy_to_cluster(mapa_shared(base + INFO_OFF + ir * (2 * INFO_HALF) + rank * INFO_HALF, peer),
                                      base + INFO_OFF + ir * (2 * INFO_HALF) + rank * INFO_HALF, INFO_HALF, mapa_shared(bar(BAR_INFO + ir), peer));
@@ -803,6 +806,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PAIR_THREADS, 1) att
                     ok = mbar_wait_thread(bar(BAR_QFREE), 0u, abort_flag, W_QFREE);
                     if (!ok) break;
                 }
+                TRACE(72, it);
                 mbar_arrive_expect_tx(bar(BAR_VFULL + vs), 4 * CHUNK);
 #pragma unroll
                 for (uint32_t r = 0; r < 2; ++r) {
@@ -813,8 +817,10 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PAIR_THREADS, 1) att
                                              mapa_shared(bar(BAR_VFULL + vs), r));
                     }
                 }
+                TRACE(73, it);
                 ok = mbar_wait_thread(bar(BAR_VFULL + vs), (it / NV) & 1u, abort_flag, W_VFULL_CTA);
                 if (!ok) break;
+                TRACE(74, it);
                 mbar_arrive_remote(barp(BAR_VFULLP + vs));
                 // the copies out of this CTA's K stage into its own slots and the partner's copies into them are done
                 mbar_arrive(bar(BAR_KEMPTY + ks));
