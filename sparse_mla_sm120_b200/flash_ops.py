@@ -176,7 +176,7 @@ def sparse_mla_decode_fwd(
 
     if num_sm_parts is None:
         num_sm_parts = (pick_num_sm_parts_fp32(num_tokens, num_heads, num_sms(q.device)) if fp32_only
-                        else pick_num_sm_parts(num_tokens, num_sms(q.device)))
+                        else pick_num_sm_parts(num_tokens, num_sms(q.device), -(-topk // BLOCK_N)))
     lib = _lib.load()
     stream = stream_ptr(q.device)
     if out is not None:

@@ -126,7 +126,7 @@ def flash_mla_with_kvcache(
         meta.have_initialized = True
         meta.config = cfg
         meta.num_sm_parts = (pick_num_sm_parts_fp32(num_tokens, num_heads, num_sms(q.device)) if fp32_only
-                             else pick_num_sm_parts(num_tokens, num_sms(q.device)))
+                             else pick_num_sm_parts(num_tokens, num_sms(q.device), -(-topk // BLOCK_N)))
         meta.max_nsplits = min(max(-(-topk // BLOCK_N), 1) + -(-ex.topk // BLOCK_N), meta.num_sm_parts)
         if meta.num_sm_parts != num_tokens:
             meta.tile_scheduler_metadata = torch.empty(meta.num_sm_parts * 8, dtype=torch.int32, device=q.device)

@@ -81,8 +81,13 @@ def test_split_policy():
     from sparse_mla_sm120_b200._runtime import pick_num_sm_parts
     assert pick_num_sm_parts(64, 148) == 64      # 128 CTAs on 148 SMs: unsplit
     assert pick_num_sm_parts(128, 148) == 128    # two nearly full waves: unsplit
-    assert pick_num_sm_parts(1, 148) == 74       # small batch: cut into sms/2 partitions
+    assert pick_num_sm_parts(1, 148) == 74       # small batch, top-k unknown: cut into sms/2 partitions
     assert pick_num_sm_parts(80, 148) == 74
+    # with the top-k known, no partition gets fewer than four 64-token blocks
+    assert pick_num_sm_parts(1, 148, 32) == 8
+    assert pick_num_sm_parts(4, 148, 32) == 32
+    assert pick_num_sm_parts(16, 148, 32) == 74
+    assert pick_num_sm_parts(4, 148, 1) == 4     # nothing worth splitting: one partition per request, attention kernel alone
 
 
 def test_flashmla_surface_argument_checks():
