@@ -17,7 +17,7 @@ from typing import Optional, Tuple
 import torch
 
 from . import _lib
-from ._lib import IMPL_AUTO, IMPL_SCALAR, LAYOUT_MODEL1, LAYOUT_V32, check
+from ._lib import IMPL_AUTO, LAYOUT_MODEL1, LAYOUT_V32, check
 from ._runtime import (BLOCK_N, FIXED_OVERHEAD, kv_geometry, kv_layout, num_sms, pick_num_sm_parts,
                        pick_num_sm_parts_fp32, ptr, require_cuda, scratch, status_buffer, stream_ptr)
 
