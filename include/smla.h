@@ -143,8 +143,9 @@ int smla_prefill(const void* q, const void* kv, const int32_t* indices,
  * cache, then ceil(extra_topk_length/64) blocks of the extra cache (decode_v2_kernel.cuh:109-115); one
  * softmax runs over both.  For SMLA_LAYOUT_MODEL1 q is [num_tokens, num_heads, 512].  extra_kv NULL and
  * extra_topk 0 = no second cache; the scheduler must have been given the same extra_topk and
- * extra_topk_length.  These calls run the exact fp32 kernel (SMLA_IMPL_SCALAR); the tcgen05 kernels serve
- * SMLA_LAYOUT_V32 without a second cache through smla_decode_splitkv / smla_prefill.
+ * extra_topk_length.  impl as above; SMLA_IMPL_AUTO runs the tcgen05 kernel when both caches and their page
+ * strides are 16-byte aligned (what its bulk copies need) and the fp32 kernel otherwise, SMLA_IMPL_TC refuses
+ * unaligned caches with SMLA_E_ALIGN.
  */
 int smla_decode_splitkv_ext(const void* q, const void* kv, const int32_t* indices,
                             const void* extra_kv, const int32_t* extra_indices,
@@ -154,7 +155,7 @@ int smla_decode_splitkv_ext(const void* q, const void* kv, const int32_t* indice
                             int page_block_size, int64_t kv_block_stride_bytes,
                             int extra_page_block_size, int64_t extra_block_stride_bytes, int num_sm_parts,
                             const float* attn_sink, const int32_t* topk_length, const int32_t* extra_topk_length,
-                            int32_t* status, void* stream);
+                            int impl, int32_t* status, void* stream);
 int smla_prefill_ext(const void* q, const void* kv, const int32_t* indices,
                      const void* extra_kv, const int32_t* extra_indices,
                      void* out, float* out_lse, float* out_max_logits,
@@ -162,7 +163,7 @@ int smla_prefill_ext(const void* q, const void* kv, const int32_t* indices,
                      int page_block_size, int64_t kv_block_stride_bytes,
                      int extra_page_block_size, int64_t extra_block_stride_bytes,
                      const float* attn_sink, const int32_t* topk_length, const int32_t* extra_topk_length,
-                     int32_t* status, void* stream);
+                     int impl, int32_t* status, void* stream);
 
 /*
  * bf16 -> packed 656-byte rows (the writer of the cache format).  No kernel of the reference

@@ -482,3 +482,92 @@ def emulate_fp8_attention(q: torch.Tensor, packed: torch.Tensor, indices: torch.
         out[t] = torch.where(live.unsqueeze(1), o, torch.zeros_like(o))
         lse[t] = torch.where(live, (l.clamp(min=1e-38).log2() + m.squeeze(1) - p_shift) * LN2, torch.full_like(l, float("-inf")))
     return out.to(torch.bfloat16), lse
+
+
+def _fp8_class_rows(packed: torch.Tensor):
+    """What a kernel of the FP8 class sees of every row of a cache, for either layout (told apart by the row size):
+    (k_nope exact fp32 [N, nope], k_rope fp32 [N, 64], s_row [N], v_raw [N, 512] in units of s_row).
+
+    V32: s_row is the row's largest scale and V its no-PE values.  MODEL1: V is the whole row, so its RoPE
+    part is rounded to e4m3 as well, against a scale s_row that covers both the row's scales and its RoPE
+    (2^ceil(log2(amax / 448)))."""
+    if packed.shape[-1] == ROW_BYTES:
+        rows = packed.reshape(-1, ROW_BYTES)
+        fp8 = rows[:, :D_NOPE].contiguous().view(torch.float8_e4m3fn).float().view(-1, NUM_TILES, QUANT_TILE)
+        sc = rows[:, D_NOPE:D_NOPE + 16].contiguous().view(torch.float32).view(-1, NUM_TILES)
+        k_nope = (fp8 * sc.unsqueeze(-1)).view(-1, D_NOPE)
+        k_rope = rows[:, D_NOPE + 16:].contiguous().view(torch.bfloat16).float()
+        s_row = sc.amax(dim=1)
+        return k_nope, k_rope, s_row, k_nope / s_row.clamp(min=1e-38).unsqueeze(1)
+    nb, bs, hk, bpt = packed.shape
+    assert bpt == M1_ROW_BYTES and hk == 1
+    page = packed.reshape(nb, bs * bpt)
+    data = page[:, :bs * M1_DATA_BYTES].reshape(nb * bs, M1_DATA_BYTES)
+    footer = page[:, bs * M1_DATA_BYTES:].reshape(nb * bs, M1_SCALE_BYTES)
+    fp8 = data[:, :M1_D_NOPE].contiguous().view(torch.float8_e4m3fn).float().view(-1, M1_NUM_TILES, M1_TILE)
+    sc = torch.pow(2.0, footer[:, :M1_NUM_TILES].float() - 127.0)
+    k_nope = (fp8 * sc.unsqueeze(-1)).view(-1, M1_D_NOPE)
+    k_rope = data[:, M1_D_NOPE:].contiguous().view(torch.bfloat16).float()
+    need = k_rope.abs().amax(dim=1) / 448.0
+    s_rope = torch.where(need > 0, torch.pow(2.0, need.clamp(min=1e-38).log2().ceil()), torch.zeros_like(need))
+    s_row = torch.maximum(sc.amax(dim=1), s_rope)
+    inv = 1.0 / s_row.clamp(min=1e-38).unsqueeze(1)
+    v_rope = (k_rope * inv).clamp(-448, 448).to(torch.float8_e4m3fn).float()
+    return k_nope, k_rope, s_row, torch.cat([k_nope * inv, v_rope], dim=1)
+
+
+def emulate_fp8_attention_dual(q: torch.Tensor, packed: torch.Tensor, indices: torch.Tensor, sm_scale: float,
+                               topk_length: Optional[torch.Tensor] = None,
+                               extra_packed: Optional[torch.Tensor] = None,
+                               extra_indices: Optional[torch.Tensor] = None,
+                               extra_topk_length: Optional[torch.Tensor] = None,
+                               attn_sink: Optional[torch.Tensor] = None, p_shift: int = 5
+                               ) -> Tuple[torch.Tensor, torch.Tensor]:
+    """``emulate_fp8_attention`` for everything ``ref_sparse_attn_dual`` takes: either cache layout, a
+    second cache whose rows join the same softmax, and a sink (applied as there: the output is scaled, the
+    LSE is not).  Same roundings, same purpose: the distance of this function to the fp32 oracle is what a
+    tensor-core kernel is allowed, it restates no kernel.
+
+    q [T, H, 576 | 512] bf16, indices [T, topk], extra_indices [T, extra_topk].
+    Returns (out bf16 [T, H, 512], lse natural log [T, H])."""
+    T, H, d_qk = q.shape
+    nope = D_NOPE if packed.shape[-1] == ROW_BYTES else M1_D_NOPE
+    assert d_qk == nope + D_ROPE
+    caches = [(_fp8_class_rows(packed), indices, topk_length)]
+    if extra_packed is not None and extra_indices is not None:
+        caches.append((_fp8_class_rows(extra_packed), extra_indices, extra_topk_length))
+    qf = q.float()
+    amax = qf[..., :nope].abs().amax(dim=-1).clamp(min=1e-4)
+    sq = pow2_scale(amax / 448.0)
+    q8 = (qf[..., :nope] / sq.unsqueeze(-1)).clamp(-448, 448).to(torch.float8_e4m3fn).float() * sq.unsqueeze(-1)
+    out = torch.zeros(T, H, D_V)
+    lse = torch.full((T, H), float("-inf"))
+    for t in range(T):
+        kn, kr, st, vr, bad = [], [], [], [], []
+        for (c_nope, c_rope, c_s, c_v), idx, length in caches:
+            n = idx.shape[-1]
+            b = idx[t] < 0
+            if length is not None:
+                b = b | (torch.arange(n) >= int(length[t]))
+            i = idx[t].clamp(min=0).long()
+            kn.append(c_nope[i]); kr.append(c_rope[i]); st.append(c_s[i]); vr.append(c_v[i]); bad.append(b)
+        kn, kr, st, vr, bad = torch.cat(kn), torch.cat(kr), torch.cat(st), torch.cat(vr), torch.cat(bad)
+        x = (q8[t] @ kn.T + qf[t, :, nope:] @ kr.T) * (sm_scale * LOG2E)
+        z = x + st.clamp(min=1e-38).log2().unsqueeze(0)
+        z[:, bad] = float("-inf")
+        m = z.amax(dim=1, keepdim=True)
+        live = torch.isfinite(m.squeeze(1))
+        m = torch.where(torch.isfinite(m), m, torch.zeros_like(m))
+        p = torch.exp2(z - m + p_shift)
+        p8 = p.clamp(max=448).to(torch.float8_e4m3fn).float()
+        vr = vr.clone()
+        vr[bad] = 0.0
+        l = (p / st.clamp(min=1e-38).unsqueeze(0)).sum(dim=1)
+        o = (p8 @ vr) / l.clamp(min=1e-38).unsqueeze(1)
+        row_lse = torch.where(live, (l.clamp(min=1e-38).log2() + m.squeeze(1) - p_shift) * LN2, torch.full_like(l, float("-inf")))
+        if attn_sink is not None:
+            o = o * (1.0 / (1.0 + torch.exp(attn_sink.float() - row_lse))).unsqueeze(1)
+        out[t] = torch.where(live.unsqueeze(1), o, torch.zeros_like(o))
+        lse[t] = row_lse
+    return out.to(torch.bfloat16), lse
+

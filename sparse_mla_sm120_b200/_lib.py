@@ -42,9 +42,9 @@ _SIGS = {
     "smla_prefill": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
                              c_float, c_int, c_int64, c_void_p, c_void_p, c_int, c_void_p, c_void_p]),
     "smla_decode_splitkv_ext": (c_int, [c_void_p] * 11 + [c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_int64,
-                                                          c_int, c_int64, c_int] + [c_void_p] * 5),
+                                                          c_int, c_int64, c_int] + [c_void_p] * 3 + [c_int, c_void_p, c_void_p]),
     "smla_prefill_ext": (c_int, [c_void_p] * 8 + [c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_int64, c_int,
-                                                  c_int64] + [c_void_p] * 5),
+                                                  c_int64] + [c_void_p] * 3 + [c_int, c_void_p, c_void_p]),
     "smla_pack_kv": (c_int, [c_void_p, c_void_p, c_int64, c_void_p]),
     "smla_mqa_logits": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                 c_int, c_int, c_int, c_int64, c_int, c_void_p, c_void_p]),

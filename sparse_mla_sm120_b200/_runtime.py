@@ -81,6 +81,15 @@ def kv_geometry(kv_cache: torch.Tensor) -> Tuple[int, int]:
     raise ValueError(f"unsupported kv_cache rank {kv_cache.dim()}")
 
 
+def tc_aligned(kv_cache: torch.Tensor, extra_kv: Optional[torch.Tensor] = None) -> bool:
+    """What the tensor-core kernel's bulk copies need of the caches of an `_ext` call: base addresses and page
+    strides that are multiples of 16 bytes (the library checks the same and falls back to the fp32 kernel)."""
+    for t in (kv_cache, extra_kv):
+        if t is not None and (t.data_ptr() % 16 != 0 or kv_geometry(t)[1] % 16 != 0):
+            return False
+    return True
+
+
 def pick_num_sm_parts_fp32(num_tokens: int, num_heads: int, sms: int) -> int:
     """Partitions for the fp32 kernel, which runs ceil(heads / 8) CTAs per partition: requests stay
     whole when they already give two CTAs per SM, otherwise the work is cut so that they do."""

@@ -285,6 +285,17 @@ static int check_ext(const char* fn, const void* q, const void* kv, const int32_
     return 0;
 }
 
+// impl AUTO: the tensor-core kernel when the caches are aligned for its bulk copies, else the fp32 kernel.
+static int launch_ext(const char* fn, const AttnParams& p, int impl, cudaStream_t stream) {
+    if (impl != SMLA_IMPL_AUTO && impl != SMLA_IMPL_SCALAR && impl != SMLA_IMPL_TC)
+        return set_error(SMLA_E_SHAPE, "%s: unknown impl %d", fn, impl);
+    if (impl == SMLA_IMPL_SCALAR) return launch_attn_scalar(p, stream);
+    if (attn_pair_takes(p)) return launch_attn_pair(p, stream);
+    if (impl == SMLA_IMPL_TC)
+        return set_error(SMLA_E_ALIGN, "%s: the tensor-core kernel needs 16-byte aligned caches and page strides", fn);
+    return launch_attn_scalar(p, stream);
+}
+
 int smla_decode_splitkv_ext(const void* q, const void* kv, const int32_t* indices,
                             const void* extra_kv, const int32_t* extra_indices,
                             float* o_accum, float* lse_accum, void* out, float* out_lse,
@@ -293,7 +304,7 @@ int smla_decode_splitkv_ext(const void* q, const void* kv, const int32_t* indice
                             int page_block_size, int64_t kv_block_stride_bytes,
                             int extra_page_block_size, int64_t extra_block_stride_bytes, int num_sm_parts,
                             const float* attn_sink, const int32_t* topk_length, const int32_t* extra_topk_length,
-                            int32_t* status, void* stream) {
+                            int impl, int32_t* status, void* stream) {
     if (int e = check_ext("smla_decode_splitkv_ext", q, kv, indices, extra_kv, extra_indices, out, out_lse, num_tokens,
                           num_heads, topk, extra_topk, layout, page_block_size, kv_block_stride_bytes,
                           extra_page_block_size, extra_block_stride_bytes)) return e;
@@ -313,7 +324,7 @@ int smla_decode_splitkv_ext(const void* q, const void* kv, const int32_t* indice
         p.extra_topk = extra_topk; p.extra_page_block_size = extra_page_block_size;
         p.extra_block_stride = extra_block_stride_bytes;
     }
-    return launch_attn_scalar(p, (cudaStream_t)stream);
+    return launch_ext("smla_decode_splitkv_ext", p, impl, (cudaStream_t)stream);
 }
 
 int smla_prefill_ext(const void* q, const void* kv, const int32_t* indices,
@@ -323,7 +334,7 @@ int smla_prefill_ext(const void* q, const void* kv, const int32_t* indices,
                      int page_block_size, int64_t kv_block_stride_bytes,
                      int extra_page_block_size, int64_t extra_block_stride_bytes,
                      const float* attn_sink, const int32_t* topk_length, const int32_t* extra_topk_length,
-                     int32_t* status, void* stream) {
+                     int impl, int32_t* status, void* stream) {
     if (int e = check_ext("smla_prefill_ext", q, kv, indices, extra_kv, extra_indices, out, out_lse, num_tokens,
                           num_heads, topk, extra_topk, layout, page_block_size, kv_block_stride_bytes,
                           extra_page_block_size, extra_block_stride_bytes)) return e;
@@ -339,7 +350,7 @@ int smla_prefill_ext(const void* q, const void* kv, const int32_t* indices,
         p.extra_topk = extra_topk; p.extra_page_block_size = extra_page_block_size;
         p.extra_block_stride = extra_block_stride_bytes;
     }
-    return launch_attn_scalar(p, (cudaStream_t)stream);
+    return launch_ext("smla_prefill_ext", p, impl, (cudaStream_t)stream);
 }
 
 int smla_pack_kv(const void* kv_bf16, void* packed, int64_t num_rows, void* stream) {

@@ -9,6 +9,7 @@ namespace attn {
 
 struct Work {   // one request's share of a partition
     int req, blk0, nblk, len, split_idx;
+    int main_blocks, extra_len;   // blocks [0, main_blocks) of a request walk the main cache, the rest the second ("extra") cache
     bool no_split;
 };
 
@@ -31,7 +32,15 @@ __device__ __forceinline__ SchedMeta load_meta(const AttnParams& p, int part) {
 __device__ __forceinline__ bool get_work(const AttnParams& p, const SchedMeta& m, int req, Work& w) {
     int len = p.topk_length ? p.topk_length[req] : p.topk;
     len = min(len, p.topk);
-    const int total = max((len + BLOCK_N - 1) / BLOCK_N, 1);
+    // A request walks max(ceil(len / 64), 1) blocks of the main cache, then ceil(extra_len / 64) blocks of the
+    // second cache when there is one (csrc/kernel/decode/decode_v2_kernel.cuh:109-115).
+    w.main_blocks = max((len + BLOCK_N - 1) / BLOCK_N, 1);
+    w.extra_len = 0;
+    if (p.extra_topk > 0) {
+        const int el = p.extra_topk_length ? p.extra_topk_length[req] : p.extra_topk;
+        w.extra_len = max(min(el, p.extra_topk), 0);
+    }
+    const int total = w.main_blocks + (w.extra_len + BLOCK_N - 1) / BLOCK_N;
     const int b0 = (req == m.begin_req) ? m.begin_block : 0;
     const int b1 = min((req == m.end_req) ? m.end_block : total, total);
     w.req = req; w.blk0 = b0; w.nblk = b1 - b0; w.len = len;
@@ -39,6 +48,18 @@ __device__ __forceinline__ bool get_work(const AttnParams& p, const SchedMeta& m
                  ((req == m.begin_req) ? !m.first_split : ((req == m.end_req) ? !m.last_split : true));
     w.split_idx = p.num_splits ? p.num_splits[req] + ((req == m.begin_req) ? m.begin_split : 0) : 0;
     return w.nblk > 0;
+}
+
+// Entry r of 64-token block b of the request: its index in the cache that block walks, or -1 when there is no
+// entry (past the request's length, past the partition's share, or a -1 in the index array).
+__device__ __forceinline__ int fetch_entry(const AttnParams& p, const Work& w, int b, int r) {
+    if (b >= w.blk0 + w.nblk) return -1;
+    if (b < w.main_blocks) {
+        const int pos = b * BLOCK_N + r;
+        return pos < w.len ? __ldg(p.indices + (size_t)w.req * p.topk + pos) : -1;
+    }
+    const int pos = (b - w.main_blocks) * BLOCK_N + r;
+    return pos < w.extra_len ? __ldg(p.extra_indices + (size_t)w.req * p.extra_topk + pos) : -1;
 }
 
 __device__ __forceinline__ float pow2_ceil(float x) {

@@ -170,8 +170,55 @@ __device__ int g_prof_block = 0;
 
 __device__ __forceinline__ uint32_t swz(uint32_t row, uint32_t chunk16) { return row * 128u + ((chunk16 ^ (row & 7u)) << 4); }
 
-// ---------------------------------------------------------------------------------------------
+// What differs between the two cache layouts (csrc/model/kv_cache_traits.cuh:20-111).
+//   V32:    a row is 512 e4m3 | 4 fp32 scales (one per 128 values) | 64 bf16 RoPE = 656 bytes; q has 576 dims, V is the
+//           512 no-PE values.
+//   MODEL1: a row is 448 e4m3 | 64 bf16 RoPE = 576 bytes, its 7 UE8M0 scales (one per 64 values, + 1 pad byte) lie
+//           in the page's footer; q has 512 dims and V is the whole row, RoPE included.  The kernel keeps the layout
+//           of the stages: the no-PE bytes fill chunks 0-2 and the lower half of chunk 3, and the row's RoPE,
+//           quantised to e4m3 against the group's scale, fills the upper half of chunk 3, so that the V copies and
+//           the P.V MMAs are the same; the score MMAs skip the upper half of chunk 3 and use the bf16 RoPE.
+template <int LAYOUT> struct Lay;
+template <> struct Lay<SMLA_LAYOUT_V32> {
+    static constexpr bool M1 = false;
+    static constexpr int QD = D_QK, NOPE = D_NOPE, DATA = ROW_BYTES, ROPE_AT = ROPE_OFF;
+};
+template <> struct Lay<SMLA_LAYOUT_MODEL1> {
+    static constexpr bool M1 = true;
+    static constexpr int QD = SMLA_M1_D_QK, NOPE = 448, DATA = SMLA_M1_DATA_BYTES, ROPE_AT = 448;
+};
+
+// Where row idx of a cache lies: the page's first byte (by reference) and the row's number inside the page.
+struct CacheGeom {
+    const uint8_t* base;
+    int64_t stride;
+    int pbs, shift;    // rows per page; log2 of it, or -1 when it is not a power of two
+};
+__device__ __forceinline__ CacheGeom cache_geom(const uint8_t* base, int64_t stride, int pbs) {
+    CacheGeom c;
+    c.base = base; c.stride = stride; c.pbs = pbs;
+    c.shift = (pbs & (pbs - 1)) == 0 ? __ffs(pbs) - 1 : -1;
+    return c;
+}
+__device__ __forceinline__ const uint8_t* cache_page(const CacheGeom& c, int idx, unsigned& in) {
+    const unsigned u = (unsigned)idx;
+    const unsigned blk = c.shift >= 0 ? (u >> c.shift) : u / (unsigned)c.pbs;
+    in = u - blk * (unsigned)c.pbs;
+    return c.base + (int64_t)blk * c.stride;
+}
+
+// Entry r of this CTA's rows of tile j of a request (block blk0 + 2 j + rank of the request).  EXTRA = false: the
+// request walks the main cache only, `lim` is the end of its share of the index row.
+template <bool EXTRA>
+__device__ __forceinline__ int tile_entry(const AttnParams& p, const Work& w, int j, int rank, int r, int nst, int lim) {
+    if (EXTRA) return fetch_entry(p, w, w.blk0 + 2 * j + rank, r);
+    const int pos = w.blk0 * BLOCK_N + j * TILE_N + rank * OWN_N + r;
+    return (j < nst && pos < lim) ? __ldg(p.indices + (size_t)w.req * p.topk + pos) : -1;
+}
+
+template <int LAYOUT, bool EXTRA>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PAIR_THREADS, 1) attn_pair_kernel(const AttnParams p) {
+    using L = Lay<LAYOUT>;
     extern __shared__ uint8_t smem_raw[];
     const uint32_t raw = smem_u32(smem_raw);
     const uint32_t base = (raw + 1023u) & ~1023u;
@@ -251,9 +298,9 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PAIR_THREADS, 1) att
     const bool first_work = meta.begin_req <= last_req && get_work(p, meta, meta.begin_req, w_first);   // the same in both CTAs
     const bool q_staged = first_work && live_heads > 0;
     if (tid == 0 && q_staged) {
-        const uint32_t bytes = (uint32_t)live_heads * D_QK * 2;
+        const uint32_t bytes = (uint32_t)live_heads * L::QD * 2;
         mbar_arrive_expect_tx(bar(BAR_QSTAGE), bytes);
-        bulk_copy_g2s(base + QSTAGE_OFF, reinterpret_cast<unsigned long long>(p.q + ((size_t)meta.begin_req * p.num_heads + head0) * D_QK),
+        bulk_copy_g2s(base + QSTAGE_OFF, reinterpret_cast<unsigned long long>(p.q + ((size_t)meta.begin_req * p.num_heads + head0) * L::QD),
                       bytes, bar(BAR_QSTAGE));
     }
 
@@ -294,15 +341,17 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PAIR_THREADS, 1) att
                 const bool from_smem = q_staged && req == meta.begin_req;
                 if (from_smem && !dead) dead = !mbar_wait_hot(bar(BAR_QSTAGE), 0u, abort_flag, W_QSTAGE);
                 // row (head0 + r) of the request's Q, wherever it lies
-                const __nv_bfloat16* qrows = from_smem ? reinterpret_cast<const __nv_bfloat16*>(sm + QSTAGE_OFF) - (size_t)head0 * D_QK
-                                                       : p.q + (size_t)req * p.num_heads * D_QK;
+                const __nv_bfloat16* qrows = from_smem ? reinterpret_cast<const __nv_bfloat16*>(sm + QSTAGE_OFF) - (size_t)head0 * L::QD
+                                                       : p.q + (size_t)req * p.num_heads * L::QD;
+                // blocks of 32 dims of this warp's 256 that are no-PE dims (MODEL1: 448 = 256 + 6 x 32; the rest stays zero and no MMA reads it)
+                const int nblk32 = !L::M1 ? 8 : ((L::NOPE - ch * 256 >= 256) ? 8 : (L::NOPE - ch * 256) / 32);
 #pragma unroll 1
                 for (int hf = 0; hf < 2; ++hf) {
                     const int r_a = grp * 32 + 16 * hf + g, r_b = r_a + 8;      // head rows inside the CTA
                     const bool v_a = !dead && r_a < heads_cta && head0 + r_a < p.num_heads;
                     const bool v_b = !dead && r_b < heads_cta && head0 + r_b < p.num_heads;
-                    const __nv_bfloat16* src_a = qrows + (size_t)(head0 + (v_a ? r_a : 0)) * D_QK + ch * 256 + c4 * 8;
-                    const __nv_bfloat16* src_b = qrows + (size_t)(head0 + (v_b ? r_b : 0)) * D_QK + ch * 256 + c4 * 8;
+                    const __nv_bfloat16* src_a = qrows + (size_t)(head0 + (v_a ? r_a : 0)) * L::QD + ch * 256 + c4 * 8;
+                    const __nv_bfloat16* src_b = qrows + (size_t)(head0 + (v_b ? r_b : 0)) * L::QD + ch * 256 + c4 * 8;
                     // two passes over the rows' bytes (the second is served by L1/L2): keeping a 16-row group in
                     // registers between the maxima and the quantisation spilled
                     auto absmax8 = [](const uint4& a) {
@@ -312,8 +361,8 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PAIR_THREADS, 1) att
                     float am_a = 0.f, am_b = 0.f;
 #pragma unroll
                     for (int i = 0; i < 8; ++i) {
-                        const uint4 xa = v_a ? *reinterpret_cast<const uint4*>(src_a + 32 * i) : make_uint4(0, 0, 0, 0);
-                        const uint4 xb = v_b ? *reinterpret_cast<const uint4*>(src_b + 32 * i) : make_uint4(0, 0, 0, 0);
+                        const uint4 xa = (v_a && i < nblk32) ? *reinterpret_cast<const uint4*>(src_a + 32 * i) : make_uint4(0, 0, 0, 0);
+                        const uint4 xb = (v_b && i < nblk32) ? *reinterpret_cast<const uint4*>(src_b + 32 * i) : make_uint4(0, 0, 0, 0);
                         am_a = fmaxf(am_a, absmax8(xa)); am_b = fmaxf(am_b, absmax8(xb));
                     }
                     am_a = fmaxf(am_a, __shfl_xor_sync(0xffffffffu, am_a, 1)); am_b = fmaxf(am_b, __shfl_xor_sync(0xffffffffu, am_b, 1));
@@ -333,8 +382,9 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PAIR_THREADS, 1) att
                             uint32_t wq[16];
 #pragma unroll
                             for (int kk = 0; kk < 4; ++kk) {
-                                const uint4 a = v_a ? *reinterpret_cast<const uint4*>(src_a + 32 * (4 * h4 + kk)) : make_uint4(0, 0, 0, 0);
-                                const uint4 b4 = v_b ? *reinterpret_cast<const uint4*>(src_b + 32 * (4 * h4 + kk)) : make_uint4(0, 0, 0, 0);
+                                const bool in = 4 * h4 + kk < nblk32;
+                                const uint4 a = (v_a && in) ? *reinterpret_cast<const uint4*>(src_a + 32 * (4 * h4 + kk)) : make_uint4(0, 0, 0, 0);
+                                const uint4 b4 = (v_b && in) ? *reinterpret_cast<const uint4*>(src_b + 32 * (4 * h4 + kk)) : make_uint4(0, 0, 0, 0);
                                 wq[4 * kk + 0] = pack_e4m3x4(bf16lo(a.x) * ia, bf16hi(a.x) * ia, bf16lo(a.y) * ia, bf16hi(a.y) * ia);
                                 wq[4 * kk + 1] = pack_e4m3x4(bf16lo(a.z) * ia, bf16hi(a.z) * ia, bf16lo(a.w) * ia, bf16hi(a.w) * ia);
                                 wq[4 * kk + 2] = pack_e4m3x4(bf16lo(b4.x) * ib, bf16hi(b4.x) * ib, bf16lo(b4.y) * ib, bf16hi(b4.y) * ib);
@@ -354,7 +404,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PAIR_THREADS, 1) att
                         const int hr = grp * 32 + rl;
                         uint4 c = make_uint4(0, 0, 0, 0);
                         if (hr < heads_cta && head0 + hr < p.num_heads)
-                            c = *reinterpret_cast<const uint4*>(qrows + (size_t)(head0 + hr) * D_QK + D_NOPE + (lane & 7) * 8);
+                            c = *reinterpret_cast<const uint4*>(qrows + (size_t)(head0 + hr) * L::QD + L::NOPE + (lane & 7) * 8);
                         const __nv_bfloat162 f = __float2bfloat162_rn(__uint_as_float(0x7f000000u - __float_as_uint(sqv[hr])));   // 1/sq
                         c.x = mul_bf16x2(c.x, f); c.y = mul_bf16x2(c.y, f); c.z = mul_bf16x2(c.z, f); c.w = mul_bf16x2(c.w, f);
                         *reinterpret_cast<uint4*>(sm + QR_OFF + swz((uint32_t)hr, (uint32_t)lane & 7u)) = c;
@@ -378,8 +428,8 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PAIR_THREADS, 1) att
             // loads with nothing else to do: ask L2 for them now (this CTA's heads, 128-byte lines), a whole request
             // of tiles ahead.
             if (req + 1 <= last_req) {
-                const uint8_t* qn = reinterpret_cast<const uint8_t*>(p.q + ((size_t)(req + 1) * p.num_heads + head0) * D_QK);
-                const int lines = (live_heads * D_QK * 2 + 127) >> 7;
+                const uint8_t* qn = reinterpret_cast<const uint8_t*>(p.q + ((size_t)(req + 1) * p.num_heads + head0) * L::QD);
+                const int lines = (live_heads * L::QD * 2 + 127) >> 7;
                 for (int i = tid; i < lines; i += N_SM_WARPS * 32)
                     asm volatile("prefetch.global.L2 [%0];" ::"l"(qn + (size_t)i * 128));
             }
@@ -585,23 +635,31 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PAIR_THREADS, 1) att
         // row one 16-byte piece of the 512 no-PE bytes per lane, plus (spread over the lanes) the rows' RoPE bytes
         // and scale words.  The largest of the rows' scales is the scale of the warp's group; every lane shifts its
         // pieces onto it and stores them in the layout the MMAs read.
+        // MODEL1: 28 lanes hold the 448 no-PE bytes of a row; the rows' scale bytes do not travel with the rows (they
+        // lie in the page footer), so the warp reads them from global memory itself, a tile ahead of their use.
         const int gw = warp - N_SM_WARPS;
-        const int blk = lane >> 3;                                   // 128-value block of this lane's piece
-        const int pbs_shift = (p.page_block_size & (p.page_block_size - 1)) == 0 ? __ffs(p.page_block_size) - 1 : -1;
+        const int blk = lane >> 3;                                   // 128-value chunk of this lane's piece
+        const CacheGeom main_c = cache_geom(p.kv, p.block_stride, p.page_block_size);
+        const CacheGeom extra_c = cache_geom(p.extra_kv, p.extra_block_stride, p.extra_topk > 0 ? p.extra_page_block_size : 1);
         uint32_t it = 0;
         bool ok = true, stop = false;
         for (int req = meta.begin_req; req <= last_req && !stop; ++req) {
             Work w;
             if (!get_work(p, meta, req, w)) continue;
             const int nst = (w.nblk + 1) >> 1;
-            const int32_t* idx_row = p.indices + (size_t)req * p.topk;
+            // tile j of this CTA is block blk0 + 2 j + rank of the request; this lane looks after row RPW gw + lane % RPW
             const int lim = min(w.len, (w.blk0 + w.nblk) * BLOCK_N);
-            auto fetch_idx = [&](int j) -> int {                     // row RPW gw + lane % RPW of tile j
-                const int pos = w.blk0 * BLOCK_N + j * TILE_N + (int)rank * OWN_N + gw * RPW + (lane & (RPW - 1));
-                return (j < nst && pos < lim) ? __ldg(idx_row + pos) : -1;
+            auto fetch_idx = [&](int j) -> int { return tile_entry<EXTRA>(p, w, j, (int)rank, gw * RPW + (lane & (RPW - 1)), nst, lim); };
+            auto fetch_scales = [&](int j, int idx) -> uint2 {       // MODEL1: the row's 7 UE8M0 bytes (+ 1 pad)
+                if (!L::M1 || idx < 0) return make_uint2(0u, 0u);
+                const CacheGeom& c = (!EXTRA || w.blk0 + 2 * j + (int)rank < w.main_blocks) ? main_c : extra_c;
+                unsigned in;
+                const uint8_t* pg = cache_page(c, idx, in);
+                return __ldg(reinterpret_cast<const uint2*>(pg + (int64_t)c.pbs * L::DATA + (int64_t)in * 8));
             };
             // Which of the warp's rows have an entry (the rows themselves are brought in by the copy warps).
             int idx_cur = fetch_idx(0), idx_nxt = fetch_idx(1);
+            uint2 sc8_nxt = fetch_scales(0, idx_cur);
 #pragma unroll 1
             for (int k = 0; k < nst; ++k) {
                 const uint32_t t_it = it + k, ks = t_it % NK, rs = t_it % NR;
@@ -611,6 +669,8 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PAIR_THREADS, 1) att
                 PROF(1);
                 TRACE(61, t_it);
                 const uint32_t vbits = __ballot_sync(0xffffffffu, idx_cur >= 0) & ((1u << RPW) - 1u);
+                const uint2 sc8 = sc8_nxt;
+                sc8_nxt = fetch_scales(k + 1, idx_nxt);
                 idx_cur = idx_nxt;
                 idx_nxt = fetch_idx(k + 2);
                 const uint8_t* raw_rows = sm + RAW_OFF + rs * RAW_BYTES + (gw * RPW) * ROW_BYTES;
@@ -623,10 +683,10 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PAIR_THREADS, 1) att
 #pragma unroll
                     for (int u = 0; u < RPW / 4; ++u) {                      // RoPE piece lane % 8 of row lane / 8 (+ 4 u)
                         const int r = (lane >> 3) + 4 * u;
-                        rp[u] = ((vbits >> r) & 1u) ? *reinterpret_cast<const uint4*>(raw_rows + r * ROW_BYTES + ROPE_OFF + (lane & 7) * 16)
+                        rp[u] = ((vbits >> r) & 1u) ? *reinterpret_cast<const uint4*>(raw_rows + r * ROW_BYTES + L::ROPE_AT + (lane & 7) * 16)
                                                     : make_uint4(0, 0, 0, 0);
                     }
-                    if (lane < 4 * RPW && ((vbits >> (lane >> 2)) & 1u))     // scale lane % 4 of row lane / 4
+                    if (!L::M1 && lane < 4 * RPW && ((vbits >> (lane >> 2)) & 1u))     // scale lane % 4 of row lane / 4
                         sc = *reinterpret_cast<const float*>(raw_rows + (lane >> 2) * ROW_BYTES + SCALE_OFF + (lane & 3) * 4);
                 } else {
 #pragma unroll
@@ -635,6 +695,23 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PAIR_THREADS, 1) att
                     for (int u = 0; u < RPW / 4; ++u) rp[u] = make_uint4(0, 0, 0, 0);
                 }
                 float wm = sc;
+                if (L::M1) {
+                    // The group's scale as a biased exponent: the largest of the rows' 7 scale bytes (0 for a row without
+                    // an entry) and of what the rows' RoPE needs to fit e4m3 (2^ceil(log2(amax / 448))).
+                    uint32_t e = __vmaxu4(sc8.x, sc8.y & 0x00ffffffu);
+                    e = max(max(e & 0xffu, (e >> 8) & 0xffu), max((e >> 16) & 0xffu, e >> 24));
+                    auto absmax8 = [](const uint4& a) {
+                        return fmaxf(fmaxf(fmaxf(fabsf(bf16lo(a.x)), fabsf(bf16hi(a.x))), fmaxf(fabsf(bf16lo(a.y)), fabsf(bf16hi(a.y)))),
+                                     fmaxf(fmaxf(fabsf(bf16lo(a.z)), fabsf(bf16hi(a.z))), fmaxf(fabsf(bf16lo(a.w)), fabsf(bf16hi(a.w)))));
+                    };
+                    float am = 0.f;
+#pragma unroll
+                    for (int u = 0; u < RPW / 4; ++u) am = fmaxf(am, absmax8(rp[u]));
+                    const uint32_t ab = __float_as_uint(am * (1.f / 448.f));
+                    e = max(e, (ab >> 23) + ((ab & 0x007fffffu) ? 1u : 0u));
+                    if (vbits != 0u) e = max(e, 1u);
+                    wm = __uint_as_float(min(e, 254u) << 23);
+                }
 #pragma unroll
                 for (int o = 16; o >= 1; o >>= 1) wm = fmaxf(wm, __shfl_xor_sync(0xffffffffu, wm, o));
                 // the maximum needed the last shared-memory load of every lane (they return in order): the warp's rows
@@ -654,15 +731,36 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PAIR_THREADS, 1) att
                 const float inv_half = (s_half > 0.f) ? __uint_as_float(0x7f000000u - __float_as_uint(s_half)) : 0.f;
                 const __nv_bfloat162 rope_f = __float2bfloat162_rn(inv_half);
                 uint8_t* kp = sm + KS_OFF + ks * KS_BYTES;
-                // exponent shift of the block whose scale this lane loaded (row lane / 4, block lane % 4): 0 for a block at the scale
-                const uint32_t my_sub = (sc > 0.f) ? shift_bytes_of_ratio(sc * inv_half) : 0u;
+                // V32: exponent shift of the block whose scale this lane loaded (row lane / 4, block lane % 4): 0 for a block at the scale.
+                // MODEL1: lanes 0-7 pass on exponents 0-3 of row lane, lanes 8-15 exponents 4-6 of row lane - 8.
+                const uint32_t my_sub = L::M1 ? ((lane & 8) ? sc8.y : sc8.x) : ((sc > 0.f) ? shift_bytes_of_ratio(sc * inv_half) : 0u);
+                const uint32_t e_grp = __float_as_uint(s_half) >> 23;
+                const int bk = lane >> 2;                            // MODEL1: 64-value block of this lane's piece (0-6 in the lanes that store)
 #pragma unroll
                 for (int i = 0; i < RPW; ++i) {
-                    const uint32_t sub = __shfl_sync(0xffffffffu, my_sub, 4 * i + blk);
+                    uint32_t sub;
+                    if (L::M1) {
+                        const uint32_t ew = __shfl_sync(0xffffffffu, my_sub, i + ((bk & 4) ? 8 : 0));
+                        sub = min(e_grp - ((ew >> (8 * (bk & 3))) & 0xffu), 15u) * 0x08080808u;
+                    } else {
+                        sub = __shfl_sync(0xffffffffu, my_sub, 4 * i + blk);
+                    }
                     uint4 v = nope[i];      // no branch on sub: a shift by 0 is the identity, and a branch would keep the rows' chains apart
                     v.x = shift_down_e4m3x4(v.x, sub); v.y = shift_down_e4m3x4(v.y, sub);
                     v.z = shift_down_e4m3x4(v.z, sub); v.w = shift_down_e4m3x4(v.w, sub);
-                    *reinterpret_cast<uint4*>(kp + blk * CHUNK + swz((uint32_t)(gw * RPW + i), (uint32_t)lane & 7u)) = v;
+                    if (!L::M1 || lane < L::NOPE / 16)
+                        *reinterpret_cast<uint4*>(kp + blk * CHUNK + swz((uint32_t)(gw * RPW + i), (uint32_t)lane & 7u)) = v;
+                }
+                if (L::M1) {      // V's RoPE columns: e4m3(rope / s) into dims [448, 512) of the rows, the upper half of chunk 3
+#pragma unroll
+                    for (int u = 0; u < RPW / 4; ++u) {
+                        const uint4 v = rp[u];
+                        const uint32_t lo = pack_e4m3x4(bf16lo(v.x) * inv_half, bf16hi(v.x) * inv_half, bf16lo(v.y) * inv_half, bf16hi(v.y) * inv_half);
+                        const uint32_t hi = pack_e4m3x4(bf16lo(v.z) * inv_half, bf16hi(v.z) * inv_half, bf16lo(v.w) * inv_half, bf16hi(v.w) * inv_half);
+                        const uint32_t pc = (uint32_t)lane & 7u;      // piece of 8 values
+                        *reinterpret_cast<uint2*>(kp + 3 * CHUNK + swz((uint32_t)(gw * RPW + (lane >> 3) + 4 * u), 4u + (pc >> 1)) + (pc & 1u) * 8u) =
+                            make_uint2(lo, hi);
+                    }
                 }
 #pragma unroll
                 for (int u = 0; u < RPW / 4; ++u) {
@@ -720,8 +818,9 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PAIR_THREADS, 1) att
                 for (int kc = 0; kc < 4; ++kc) {
 #pragma unroll
                     for (int s = 0; s < 4; ++s) {
-                        mma_pair_f8_ts(d, tmem + TM_Q + 32 * kc + 8 * s,
-                                       make_desc(kb_lo + ((kc * CHUNK + s * 32) >> 4), DESC_HI_SW128), IDESC_QK_F8, (kc | s) != 0);
+                        if (32 * (4 * kc + s) < L::NOPE)      // MODEL1: the last 64 bytes of chunk 3 are V's RoPE columns
+                            mma_pair_f8_ts(d, tmem + TM_Q + 32 * kc + 8 * s,
+                                           make_desc(kb_lo + ((kc * CHUNK + s * 32) >> 4), DESC_HI_SW128), IDESC_QK_F8, (kc | s) != 0);
                     }
                 }
 #pragma unroll
@@ -836,35 +935,32 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PAIR_THREADS, 1) att
         // these rows have taken the tile out of the stage; the warp's barrier of the stage counts the bytes.
         // Issuing a copy blocks while the copy unit is busy, which is why no working warp does it.
         const int pw = warp - PROD_WARP0;
-        const int pbs_shift = (p.page_block_size & (p.page_block_size - 1)) == 0 ? __ffs(p.page_block_size) - 1 : -1;
+        const CacheGeom main_c = cache_geom(p.kv, p.block_stride, p.page_block_size);
+        const CacheGeom extra_c = cache_geom(p.extra_kv, p.extra_block_stride, p.extra_topk > 0 ? p.extra_page_block_size : 1);
         uint32_t it = 0;
         bool ok = true;
         for (int req = meta.begin_req; req <= last_req && ok; ++req) {
             Work w;
             if (!get_work(p, meta, req, w)) continue;
             const int nst = (w.nblk + 1) >> 1;
-            const int32_t* idx_row = p.indices + (size_t)req * p.topk;
+            // tile j of this CTA is block blk0 + 2 j + rank of the request; row 16 pw + lane % 16
             const int lim = min(w.len, (w.blk0 + w.nblk) * BLOCK_N);
-            auto fetch_idx = [&](int j) -> int {                     // row 16 pw + lane % 16 of tile j
-                const int pos = w.blk0 * BLOCK_N + j * TILE_N + (int)rank * OWN_N + pw * 16 + (lane & 15);
-                return (j < nst && pos < lim) ? __ldg(idx_row + pos) : -1;
-            };
-            auto issue_rows = [&](int idx, uint32_t t_it) {          // idx: lanes 0-15 hold the rows' indices
+            auto fetch_idx = [&](int j) -> int { return tile_entry<EXTRA>(p, w, j, (int)rank, pw * 16 + (lane & 15), nst, lim); };
+            auto issue_rows = [&](int idx, int j, uint32_t t_it) {   // idx: lanes 0-15 hold the indices of the rows of tile j
                 const uint32_t stage = t_it % NR;
                 unsigned long long src = 0ull;
                 if (idx >= 0) {
-                    const unsigned u = (unsigned)idx;
-                    src = reinterpret_cast<unsigned long long>(
-                        (pbs_shift >= 0)
-                            ? p.kv + (int64_t)(u >> pbs_shift) * p.block_stride + (int64_t)(u & (unsigned)(p.page_block_size - 1)) * ROW_BYTES
-                            : kv_row_ptr(p.kv, idx, p.page_block_size, p.block_stride));
+                    const CacheGeom& c = (!EXTRA || w.blk0 + 2 * j + (int)rank < w.main_blocks) ? main_c : extra_c;
+                    unsigned in;
+                    const uint8_t* pg = cache_page(c, idx, in);
+                    src = reinterpret_cast<unsigned long long>(pg + (int64_t)in * L::DATA);
                 }
                 const uint32_t dst0 = base + RAW_OFF + stage * RAW_BYTES + (pw * 16) * ROW_BYTES;
                 const uint32_t fb = bar(BAR_RAWFULL + stage * N_P_WARPS + pw);
                 const uint32_t nvalid = __popc(__ballot_sync(0xffffffffu, src != 0ull) & 0xffffu);
-                if (lane == 0) mbar_arrive_expect_tx(fb, nvalid * ROW_BYTES);
+                if (lane == 0) mbar_arrive_expect_tx(fb, nvalid * L::DATA);
                 __syncwarp();
-                if (lane < 16 && src != 0ull) bulk_copy_g2s(dst0 + lane * ROW_BYTES, src, ROW_BYTES, fb);
+                if (lane < 16 && src != 0ull) bulk_copy_g2s(dst0 + lane * ROW_BYTES, src, L::DATA, fb);
             };
             // The raw stages that the first NR tiles of a request go to are free once the gather warps have taken the
             // last NR tiles before them out (for the very first tiles of the CTA there is nothing to wait for).
@@ -873,7 +969,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PAIR_THREADS, 1) att
                 const uint32_t t_it = it + j;
                 const int idx = fetch_idx(j);
                 if (t_it >= NR) ok = mbar_wait_hot(bar(BAR_RAWEMPTY + (t_it % NR) * N_P_WARPS + pw), ((t_it / NR) - 1) & 1u, abort_flag, W_RAWEMPTY);
-                if (ok) issue_rows(idx, t_it);
+                if (ok) issue_rows(idx, j, t_it);
             }
             int idx_ahead = fetch_idx(NR);               // read one tile before it is turned into addresses
 #pragma unroll 1
@@ -881,7 +977,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PAIR_THREADS, 1) att
                 const uint32_t t_it = it + j;
                 ok = mbar_wait_hot(bar(BAR_RAWEMPTY + (t_it % NR) * N_P_WARPS + pw), (t_it / NR) & 1u, abort_flag, W_RAWEMPTY);
                 if (!ok) break;
-                issue_rows(idx_ahead, t_it + NR);
+                issue_rows(idx_ahead, j + NR, t_it + NR);
                 idx_ahead = fetch_idx(j + NR + 1);
             }
             it += nst;
@@ -932,8 +1028,10 @@ extern "C" int smla_prof_set(long long* buf, int block) {
 }
 #endif
 
-int launch_attn_pair(const AttnParams& p, cudaStream_t stream) {
-    if (p.num_tokens == 0) return 0;
+namespace {
+
+template <int LAYOUT, bool EXTRA>
+int launch_pair_layout(const AttnParams& p, cudaStream_t stream) {
     static bool attr_set[64] = {};
     static int sm_count[64] = {};
     int dev = 0;
@@ -941,10 +1039,10 @@ int launch_attn_pair(const AttnParams& p, cudaStream_t stream) {
     if (dev < 0 || dev >= 64) return set_error(SMLA_E_SHAPE, "attn_pair_kernel: device ordinal %d not supported", dev);
     if (!attr_set[dev]) {
         cudaFuncAttributes fa;
-        if (cudaFuncGetAttributes(&fa, attn_pair_kernel) != cudaSuccess || fa.numRegs != REGS_LAUNCH)
+        if (cudaFuncGetAttributes(&fa, attn_pair_kernel<LAYOUT, EXTRA>) != cudaSuccess || fa.numRegs != REGS_LAUNCH)
             return set_error(SMLA_E_DEVICE, "attn_pair_kernel: compiled with %d registers per thread, the warpgroup budgets assume %d",
                              fa.numRegs, REGS_LAUNCH);
-        const cudaError_t e = cudaFuncSetAttribute(attn_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_ALLOC);
+        const cudaError_t e = cudaFuncSetAttribute(attn_pair_kernel<LAYOUT, EXTRA>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_ALLOC);
         if (e != cudaSuccess) return set_error((int)e, "attn_pair_kernel: cannot reserve %u bytes of shared memory: %s",
                                                SMEM_ALLOC, cudaGetErrorString(e));
         cudaDeviceGetAttribute(&sm_count[dev], cudaDevAttrMultiProcessorCount, dev);
@@ -954,10 +1052,29 @@ int launch_attn_pair(const AttnParams& p, cudaStream_t stream) {
     const int max_pairs = sm_count[dev] >= 2 ? sm_count[dev] / 2 : 1;
     const int parts = p.sched ? p.num_parts : (p.num_tokens < max_pairs ? p.num_tokens : max_pairs);
     if (p.sched != nullptr)      // the scheduler kernel runs just before: start while it finishes
-        launch_dependent(attn_pair_kernel, dim3(2 * parts), dim3(PAIR_THREADS), SMEM_ALLOC, stream, p);
+        launch_dependent(attn_pair_kernel<LAYOUT, EXTRA>, dim3(2 * parts), dim3(PAIR_THREADS), SMEM_ALLOC, stream, p);
     else
-        attn_pair_kernel<<<2 * parts, PAIR_THREADS, SMEM_ALLOC, stream>>>(p);
+        attn_pair_kernel<LAYOUT, EXTRA><<<2 * parts, PAIR_THREADS, SMEM_ALLOC, stream>>>(p);
     return check_launch("attn_pair_kernel");
+}
+
+}  // namespace
+
+// The bulk copies that bring rows in want 16-byte aligned sources: both caches' base addresses and page strides
+// (a row's offset inside its page is a multiple of 16 in both layouts).
+bool attn_pair_takes(const AttnParams& p) {
+    auto al = [](const void* q, int64_t stride) { return (reinterpret_cast<uintptr_t>(q) & 15u) == 0 && (stride & 15) == 0; };
+    return p.num_heads >= 1 && p.num_heads <= 128 && al(p.kv, p.block_stride) &&
+           (p.extra_topk == 0 || al(p.extra_kv, p.extra_block_stride));
+}
+
+int launch_attn_pair(const AttnParams& p, cudaStream_t stream) {
+    if (p.num_tokens == 0) return 0;
+    if (p.layout == SMLA_LAYOUT_MODEL1)
+        return p.extra_topk > 0 ? launch_pair_layout<SMLA_LAYOUT_MODEL1, true>(p, stream)
+                                : launch_pair_layout<SMLA_LAYOUT_MODEL1, false>(p, stream);
+    return p.extra_topk > 0 ? launch_pair_layout<SMLA_LAYOUT_V32, true>(p, stream)
+                            : launch_pair_layout<SMLA_LAYOUT_V32, false>(p, stream);
 }
 
 }  // namespace smla

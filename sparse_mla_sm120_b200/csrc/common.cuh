@@ -48,7 +48,7 @@ struct AttnParams {
     int page_block_size;
     int64_t block_stride;        // bytes between pages
     float sm_scale;
-    // Served by the fp32 kernel only: the cache layout and the second ("extra") cache.
+    // The cache layout and the second ("extra") cache.
     int layout;                       // SMLA_LAYOUT_*
     const uint8_t* extra_kv;          // null = none
     const int32_t* extra_indices;     // [T, extra_topk]
@@ -126,6 +126,7 @@ int launch_combine_parts(const float* o_parts, const float* lse_parts, __nv_bflo
                          const float* attn_sink, cudaStream_t stream);
 int launch_attn_scalar(const AttnParams& p, cudaStream_t stream);
 int launch_attn_pair(const AttnParams& p, cudaStream_t stream);
+bool attn_pair_takes(const AttnParams& p);   // alignment of the caches that the tensor-core kernel's bulk copies need
 int launch_pack_kv(const __nv_bfloat16* kv, uint8_t* packed, int64_t num_rows, cudaStream_t stream);
 int launch_mqa_logits_scalar(const uint8_t* q, const uint8_t* k, const float* k_scale, const float* weights,
                              const int32_t* ks, const int32_t* ke, float* logits, int s_q, int num_heads,

@@ -17,9 +17,9 @@ from typing import Optional, Tuple
 import torch
 
 from . import _lib
-from ._lib import IMPL_AUTO, LAYOUT_MODEL1, LAYOUT_V32, check
+from ._lib import IMPL_AUTO, IMPL_SCALAR, LAYOUT_MODEL1, LAYOUT_V32, check
 from ._runtime import (BLOCK_N, FIXED_OVERHEAD, kv_geometry, kv_layout, num_sms, pick_num_sm_parts,
-                       pick_num_sm_parts_fp32, ptr, require_cuda, scratch, status_buffer, stream_ptr)
+                       pick_num_sm_parts_fp32, ptr, require_cuda, scratch, status_buffer, stream_ptr, tc_aligned)
 
 
 def _check_q(q: torch.Tensor):
@@ -91,7 +91,7 @@ def sparse_mla_splitkv_v2_fwd(Q, KV_cache, indices, o_accum, lse_accum, output, 
             ptr(Q), ptr(KV_cache), ptr(indices), ptr(ex.kv), ptr(ex.indices), ptr(o_accum), ptr(lse_accum),
             ptr(output), ptr(out_lse), ptr(sched_meta), ptr(num_splits), num_tokens, num_heads, topk, ex.topk,
             float(sm_scale), layout, page_block_size, int(stride_kv_row) * int(page_block_size), ex.block, ex.stride,
-            num_sm_parts, ptr(attn_sink), ptr(topk_length), ptr(ex.length), ptr(st), stream_ptr(Q.device)))
+            num_sm_parts, ptr(attn_sink), ptr(topk_length), ptr(ex.length), impl, ptr(st), stream_ptr(Q.device)))
         return
     check(_lib.load().smla_decode_splitkv(
         ptr(Q), ptr(KV_cache), ptr(indices), ptr(o_accum), ptr(lse_accum), ptr(output), ptr(out_lse),
@@ -128,7 +128,7 @@ def sparse_mla_prefill_raw(Q, KV_cache, indices, output, out_lse, sm_scale, topk
             ptr(Q), ptr(KV_cache), ptr(indices), ptr(ex.kv), ptr(ex.indices), ptr(output), ptr(out_lse),
             ptr(out_max_logits), num_tokens, num_heads, topk, ex.topk, float(sm_scale), layout, page_block_size,
             int(stride_kv_row) * int(page_block_size), ex.block, ex.stride, ptr(attn_sink), ptr(topk_length), None,
-            ptr(st), stream_ptr(Q.device)))
+            impl, ptr(st), stream_ptr(Q.device)))
         return
     check(_lib.load().smla_prefill(
         ptr(Q), ptr(KV_cache), ptr(indices), ptr(output), ptr(out_lse), ptr(out_max_logits), num_tokens,
@@ -172,11 +172,13 @@ def sparse_mla_decode_fwd(
     assert indices.dtype == torch.int32 and indices.is_contiguous()
     ex = _Extra(layout, num_tokens, extra_k_cache, extra_indices, extra_topk, extra_topk_length)
     require_cuda(q, kv_cache, indices)
-    fp32_only = layout != LAYOUT_V32 or ex.topk > 0
+    use_ext = layout != LAYOUT_V32 or ex.topk > 0
+    blocks = max(-(-topk // BLOCK_N), 1) + -(-ex.topk // BLOCK_N)
 
     if num_sm_parts is None:
-        num_sm_parts = (pick_num_sm_parts_fp32(num_tokens, num_heads, num_sms(q.device)) if fp32_only
-                        else pick_num_sm_parts(num_tokens, num_sms(q.device), -(-topk // BLOCK_N)))
+        fp32 = use_ext and (impl == IMPL_SCALAR or not tc_aligned(kv_cache, ex.kv))
+        num_sm_parts = (pick_num_sm_parts_fp32(num_tokens, num_heads, num_sms(q.device)) if fp32
+                        else pick_num_sm_parts(num_tokens, num_sms(q.device), blocks))
     lib = _lib.load()
     stream = stream_ptr(q.device)
     if out is not None:
@@ -184,13 +186,13 @@ def sparse_mla_decode_fwd(
     else:
         output = torch.empty((num_tokens, num_heads, d_v), dtype=torch.bfloat16, device=q.device)
     out_lse = torch.empty((num_tokens, num_heads), dtype=torch.float32, device=q.device)
-    if fp32_only:
+    if use_ext:
         st = ptr(status_buffer(q.device))
         if num_sm_parts == num_tokens:
             check(lib.smla_prefill_ext(
                 ptr(q), ptr(kv_cache), ptr(indices), ptr(ex.kv), ptr(ex.indices), ptr(output), ptr(out_lse), None,
                 num_tokens, num_heads, topk, ex.topk, float(sm_scale), layout, page_block_size, page_stride,
-                ex.block, ex.stride, ptr(attn_sink), ptr(topk_length), ptr(ex.length), st, stream))
+                ex.block, ex.stride, ptr(attn_sink), ptr(topk_length), ptr(ex.length), impl, st, stream))
             return output, out_lse
         ws = scratch(q.device, num_tokens + num_sm_parts, num_heads, num_tokens, num_sm_parts)
         check(lib.smla_sched_meta(num_tokens, topk, ex.topk, num_sm_parts, FIXED_OVERHEAD, ptr(topk_length),
@@ -199,8 +201,7 @@ def sparse_mla_decode_fwd(
             ptr(q), ptr(kv_cache), ptr(indices), ptr(ex.kv), ptr(ex.indices), ptr(ws["o_accum"]),
             ptr(ws["lse_accum"]), ptr(output), ptr(out_lse), ptr(ws["sched_meta"]), ptr(ws["num_splits"]),
             num_tokens, num_heads, topk, ex.topk, float(sm_scale), layout, page_block_size, page_stride,
-            ex.block, ex.stride, num_sm_parts, ptr(attn_sink), ptr(topk_length), ptr(ex.length), st, stream))
-        blocks = max(-(-topk // BLOCK_N), 1) + -(-ex.topk // BLOCK_N)
+            ex.block, ex.stride, num_sm_parts, ptr(attn_sink), ptr(topk_length), ptr(ex.length), impl, st, stream))
         check(lib.smla_combine(ptr(ws["o_accum"]), ptr(ws["lse_accum"]), ptr(output), ptr(out_lse),
                                ptr(ws["num_splits"]), num_tokens, num_heads, min(blocks, num_sm_parts),
                                ptr(attn_sink), stream))
@@ -267,7 +268,7 @@ def sparse_mla_prefill_fwd(
         check(_lib.load().smla_prefill_ext(
             ptr(q), ptr(kv_cache), ptr(indices), ptr(ex.kv), ptr(ex.indices), ptr(output), ptr(lse), ptr(max_logits),
             num_tokens, num_heads, topk, ex.topk, float(sm_scale), layout, page_block_size, page_stride, ex.block,
-            ex.stride, ptr(attn_sink), ptr(topk_length), None, ptr(status_buffer(q.device)), stream_ptr(q.device)))
+            ex.stride, ptr(attn_sink), ptr(topk_length), None, impl, ptr(status_buffer(q.device)), stream_ptr(q.device)))
         return output, max_logits, lse
     check(_lib.load().smla_prefill(
         ptr(q), ptr(kv_cache), ptr(indices), ptr(output), ptr(lse), ptr(max_logits), num_tokens, num_heads,

@@ -24,9 +24,9 @@ from typing import Optional, Tuple
 import torch
 
 from . import _lib
-from ._lib import IMPL_AUTO, LAYOUT_V32, check
+from ._lib import IMPL_AUTO, IMPL_SCALAR, LAYOUT_V32, check
 from ._runtime import (BLOCK_N, FIXED_OVERHEAD, kv_geometry, num_sms, pick_num_sm_parts, pick_num_sm_parts_fp32, ptr,
-                       require_cuda, status_buffer, stream_ptr)
+                       require_cuda, status_buffer, stream_ptr, tc_aligned)
 from .flash_ops import _check_q, _Extra, _layout, sparse_mla_prefill_fwd
 
 
@@ -114,7 +114,8 @@ def flash_mla_with_kvcache(
     extra_topk = extra_indices_in_kvcache.shape[-1] if extra_indices_in_kvcache is not None else 0
     extra_idx = None if extra_indices_in_kvcache is None else extra_indices_in_kvcache.reshape(num_tokens, -1)
     ex = _Extra(layout, num_tokens, extra_k_cache, extra_idx, extra_topk, extra_topk_length)
-    fp32_only = layout != LAYOUT_V32 or ex.topk > 0
+    use_ext = layout != LAYOUT_V32 or ex.topk > 0
+    blocks = max(-(-topk // BLOCK_N), 1) + -(-ex.topk // BLOCK_N)
 
     cfg = FlashMLASchedMeta.Config(b=batch, s_q=s_q, h_q=num_heads, page_block_size=k_cache.shape[1],
                                    h_k=k_cache.shape[2], causal=causal, is_fp8_kvcache=is_fp8_kvcache, topk=topk,
@@ -125,9 +126,10 @@ def flash_mla_with_kvcache(
     if not meta.have_initialized:
         meta.have_initialized = True
         meta.config = cfg
-        meta.num_sm_parts = (pick_num_sm_parts_fp32(num_tokens, num_heads, num_sms(q.device)) if fp32_only
-                             else pick_num_sm_parts(num_tokens, num_sms(q.device), -(-topk // BLOCK_N)))
-        meta.max_nsplits = min(max(-(-topk // BLOCK_N), 1) + -(-ex.topk // BLOCK_N), meta.num_sm_parts)
+        fp32 = use_ext and (impl == IMPL_SCALAR or not tc_aligned(k_cache, ex.kv))
+        meta.num_sm_parts = (pick_num_sm_parts_fp32(num_tokens, num_heads, num_sms(q.device)) if fp32
+                             else pick_num_sm_parts(num_tokens, num_sms(q.device), blocks))
+        meta.max_nsplits = min(blocks, meta.num_sm_parts)
         if meta.num_sm_parts != num_tokens:
             meta.tile_scheduler_metadata = torch.empty(meta.num_sm_parts * 8, dtype=torch.int32, device=q.device)
             meta.num_splits = torch.empty(num_tokens + 1, dtype=torch.int32, device=q.device)
@@ -145,17 +147,17 @@ def flash_mla_with_kvcache(
         output = torch.empty((num_tokens, num_heads, head_dim_v), dtype=torch.bfloat16, device=q.device)
     out_lse = torch.empty((num_tokens, num_heads), dtype=torch.float32, device=q.device)
     st = status_buffer(q.device)
-    if fp32_only and meta.num_sm_parts == num_tokens:
+    if use_ext and meta.num_sm_parts == num_tokens:
         check(lib.smla_prefill_ext(
             ptr(q_in), ptr(k_cache), ptr(idx_in), ptr(ex.kv), ptr(ex.indices), ptr(output), ptr(out_lse), None,
             num_tokens, num_heads, topk, ex.topk, float(softmax_scale), layout, page_block_size, page_stride,
-            ex.block, ex.stride, ptr(attn_sink), ptr(topk_length), ptr(ex.length), ptr(st), stream))
-    elif fp32_only:
+            ex.block, ex.stride, ptr(attn_sink), ptr(topk_length), ptr(ex.length), impl, ptr(st), stream))
+    elif use_ext:
         check(lib.smla_decode_splitkv_ext(
             ptr(q_in), ptr(k_cache), ptr(idx_in), ptr(ex.kv), ptr(ex.indices), ptr(meta.o_accum), ptr(meta.lse_accum),
             ptr(output), ptr(out_lse), ptr(meta.tile_scheduler_metadata), ptr(meta.num_splits), num_tokens, num_heads,
             topk, ex.topk, float(softmax_scale), layout, page_block_size, page_stride, ex.block, ex.stride,
-            meta.num_sm_parts, ptr(attn_sink), ptr(topk_length), ptr(ex.length), ptr(st), stream))
+            meta.num_sm_parts, ptr(attn_sink), ptr(topk_length), ptr(ex.length), impl, ptr(st), stream))
         check(lib.smla_combine(ptr(meta.o_accum), ptr(meta.lse_accum), ptr(output), ptr(out_lse), ptr(meta.num_splits),
                                num_tokens, num_heads, meta.max_nsplits, ptr(attn_sink), stream))
     elif meta.num_sm_parts == num_tokens:

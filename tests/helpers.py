@@ -112,12 +112,9 @@ def compare_out(out_kernel: torch.Tensor, out_ref: torch.Tensor, abs_tol, rel_to
     return max_diff
 
 
-def check_against_emulation(out_kernel, lse2_kernel, case, ref_out, ref_lse, topk_length=None):
-    """FP8-class check whose tolerance is derived on the spot: the kernel may be EMU_MARGIN times as far
-    from the fp32 oracle as oracle.emulate_fp8_attention is on the same inputs (largest element, rms and
-    1 - cos of the output; largest LSE difference), plus the bf16 rounding of the output."""
-    emu_out, emu_lse = orc.emulate_fp8_attention(case["q"], case["packed"], case["indices"], case["sm_scale"],
-                                                 topk_length=topk_length)
+def check_against_emulated(out_kernel, lse_kernel, emu_out, emu_lse, ref_out, ref_lse):
+    """The comparison of check_against_emulation for emulation results computed by the caller; the three LSE
+    arrays are natural logarithms and may hold infinities, which must agree in place and sign."""
     ref = ref_out.float()
     e_emu, e_k = (emu_out.float() - ref), (out_kernel.cpu().float() - ref)
     bf16_step = 2.0 ** -8 * float(ref.abs().max())
@@ -127,11 +124,21 @@ def check_against_emulation(out_kernel, lse2_kernel, case, ref_out, ref_lse, top
         f"rms d {float(e_k.pow(2).mean().sqrt())} against the emulation's {float(e_emu.pow(2).mean().sqrt())}"
     cd_k, cd_e = orc.cos_diff(out_kernel.cpu(), ref_out), orc.cos_diff(emu_out, ref_out)
     assert cd_k <= EMU_MARGIN ** 2 * cd_e + 1e-5, f"1 - cos {cd_k} against the emulation's {cd_e}"
-    k = lse2_to_nat(lse2_kernel.cpu())
-    r = ref_lse.double()
-    empty = torch.isinf(r) & (r < 0)
-    assert torch.equal(empty, torch.isinf(k) & (k < 0)), "rows without a valid entry differ"
-    if (~empty).any():
-        d_k = float((k - r)[~empty].abs().max())
-        d_e = float((emu_lse.double() - r)[~empty].abs().max())
+    k, r, e = lse_kernel.double(), ref_lse.double(), emu_lse.double()
+    inf = torch.isinf(r)
+    assert torch.equal(inf, torch.isinf(k)) and torch.equal(torch.sign(r[inf]), torch.sign(k[inf])), \
+        "rows without a valid entry (or with an infinite sink) differ"
+    if (~inf).any():
+        d_k = float((k - r)[~inf].abs().max())
+        d_e = float((e - r)[~inf].abs().max())
         assert d_k <= EMU_MARGIN * d_e + 2e-3, f"LSE error {d_k} against the emulation's {d_e}"
+
+
+def check_against_emulation(out_kernel, lse2_kernel, case, ref_out, ref_lse, topk_length=None):
+    """FP8-class check whose tolerance is derived on the spot: the kernel may be EMU_MARGIN times as far
+    from the fp32 oracle as oracle.emulate_fp8_attention is on the same inputs (largest element, rms and
+    1 - cos of the output; largest LSE difference), plus the bf16 rounding of the output."""
+    emu_out, emu_lse = orc.emulate_fp8_attention(case["q"], case["packed"], case["indices"], case["sm_scale"],
+                                                 topk_length=topk_length)
+    check_against_emulated(out_kernel, lse2_to_nat(lse2_kernel.cpu()), emu_out, emu_lse, ref_out, ref_lse)
+

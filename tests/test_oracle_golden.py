@@ -82,6 +82,28 @@ def test_fp8_emulation_distance():
     assert 0.03 < excess < H.TC_NOISE / 1.3, excess                               # TC_NOISE keeps >= 1.3 x margin over it
 
 
+def test_fp8_emulation_of_both_layouts_and_two_caches(golden_dir):
+    """emulate_fp8_attention_dual: on V32 inputs without a second cache it is emulate_fp8_attention; on the MODEL1
+    fixtures (second cache, lengths, sink) it stays inside the fixed FP8-class bounds around the reference's results."""
+    import helpers as H
+    case = H.make_case(3, 4, 16, 256, 8)
+    a = orc.emulate_fp8_attention(case["q"], case["packed"], case["indices"], case["sm_scale"])
+    b = orc.emulate_fp8_attention_dual(case["q"], case["packed"], case["indices"], case["sm_scale"])
+    assert torch.equal(a[0], b[0]) and torch.equal(a[1], b[1])
+    for name in M1_CASES:
+        c = load_m1_case(golden_dir, name)
+        bq, _, h, d = c["q"].shape
+        flat = lambda t: None if t is None else t.reshape(bq, -1)  # noqa: E731
+        out, lse = orc.emulate_fp8_attention_dual(c["q"].view(bq, h, d), c["packed"], flat(c["indices"]), c["sm_scale"],
+                                                  c["topk_length"], c["extra_packed"], flat(c["extra_indices"]),
+                                                  c["extra_topk_length"], c["attn_sink"])
+        H.compare_out(out, c["out"].view(bq, h, 512), H.TC_ABS, H.TC_REL, H.TC_COS)
+        ref = c["lse"].view(bq, h)
+        fin = torch.isfinite(ref)
+        assert torch.equal(torch.isfinite(lse), fin)
+        assert float((lse[fin] - ref[fin]).abs().max()) < H.TC_LSE
+
+
 M1_CASES = ("attn_m1_h16", "attn_m1_h64_extra", "attn_m1_h8_block16")
 
 
