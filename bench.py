@@ -601,6 +601,49 @@ def run_extras(device, hbm_peak, bf16_peak, peak_kind):
         del pool, sets, q2, i2
     except Exception as e:           # noqa: BLE001 - a secondary measurement must not take the others down
         out["decode_mtp_sq2"] = {"error": repr(e)}
+    # ---- the headline's decode shape over the second cache layout (MODEL1: 584 bytes per token, 448 e4m3 + 64 bf16
+    # RoPE + 7 UE8M0 scales in the page footer; q is 512 wide), alone and with a second cache of 512 more entries
+    try:
+        pages, blk = 4096, 64                                   # 262144 tokens, 153 MB: larger than L2
+        def m1_pool(npages):
+            nope = (torch.randn((npages * blk, 448), device=device, generator=g) * 60).clamp(-448, 448).to(torch.float8_e4m3fn)
+            rope = torch.randn((npages * blk, 64), device=device, generator=g).to(torch.bfloat16)
+            data = torch.cat([nope.view(torch.uint8), rope.view(torch.uint8)], dim=1).view(npages, blk * 576)
+            footer = torch.full((npages, blk, 8), 120, dtype=torch.uint8, device=device)   # 2^-7 for every block of 64 values
+            footer[..., :7] += torch.randint(0, 3, (npages, blk, 7), device=device, generator=g, dtype=torch.uint8)
+            footer[..., 7] = 0
+            return torch.cat([data, footer.view(npages, blk * 8)], dim=1).view(npages, blk, 1, 584)
+        pool1 = m1_pool(pages)
+        qm = (torch.randn((B_PER_GPU, HEADS, 512), device=device, generator=g) * 0.5).to(torch.bfloat16)
+        im = torch.stack([torch.randperm(pages * blk, device=device, generator=g)[:TOPK] for _ in range(B_PER_GPU)]).to(torch.int32)
+        epool = m1_pool(256)
+        ie = torch.stack([torch.randperm(256 * blk, device=device, generator=g)[:512] for _ in range(B_PER_GPU)]).to(torch.int32)
+        side = torch.cuda.Stream()
+        res = {}
+        for name, kw, entries in (("main_cache_only", {}, TOPK),
+                                  ("with_extra_cache_512", {"extra_k_cache": epool, "extra_indices": ie, "extra_topk": 512}, TOPK + 512)):
+            runm = lambda: flash_ops.sparse_mla_decode_fwd(qm, pool1, im, 512 ** -0.5, impl=2, **kw)   # 2 = the tensor-core kernel
+            runm(); torch.cuda.synchronize()
+            gm = torch.cuda.CUDAGraph()
+            with torch.cuda.stream(side):
+                runm(); side.synchronize()
+                with torch.cuda.graph(gm, stream=side):
+                    runm()
+            torch.cuda.synchronize()
+            us = _time_cuda(gm.replay, 200, warm=5) * 1e3
+            bym = B_PER_GPU * (entries * 584 + HEADS * 512 * 2 + HEADS * D_V * 2 + entries * 4 + HEADS * 4)
+            res[name] = {"us_per_step": us, "entries_per_request": entries,
+                         "roofline": {"bound": "hbm", "kernel": "attn_pair_kernel", "achieved": bym / us / 1e3, "peak": hbm_peak,
+                                      "unit": "GB/s", "frac": bym / us / 1e3 / hbm_peak, "peak_kind": f"of {peak_kind}", "traffic": None}}
+            del gm
+        exact_ms = _time_cuda(lambda: flash_ops.sparse_mla_decode_fwd(qm, pool1, im, 512 ** -0.5, impl=1), 3, warm=1)
+        out["decode_model1"] = {"workload": "64 requests, h=128, topk=2048 over a MODEL1 cache (584 bytes per token, q 512 wide), "
+                                            "262144-token pool; CUDA graph replay of the whole step on the tensor-core kernel "
+                                            "(impl=IMPL_TC; the default for this layout is the exact fp32 kernel)",
+                                "exact_fp32_kernel_us_per_step": exact_ms * 1e3, **res}
+        del pool1, epool, qm, im, ie
+    except Exception as e:           # noqa: BLE001
+        out["decode_model1"] = {"error": repr(e)}
     # ---- indexer: q e4m3 [4096, 64, 128], k e4m3 [65536, 128], ke = 61440 + i, then top-2048 per row
     s_q, s_k, hh = 4096, 65536, 64
     qi = torch.randn((s_q, hh, 128), device=device, generator=g).to(torch.float8_e4m3fn)

@@ -143,9 +143,12 @@ int smla_prefill(const void* q, const void* kv, const int32_t* indices,
  * cache, then ceil(extra_topk_length/64) blocks of the extra cache (decode_v2_kernel.cuh:109-115); one
  * softmax runs over both.  For SMLA_LAYOUT_MODEL1 q is [num_tokens, num_heads, 512].  extra_kv NULL and
  * extra_topk 0 = no second cache; the scheduler must have been given the same extra_topk and
- * extra_topk_length.  impl as above; SMLA_IMPL_AUTO runs the tcgen05 kernel when both caches and their page
- * strides are 16-byte aligned (what its bulk copies need) and the fp32 kernel otherwise, SMLA_IMPL_TC refuses
- * unaligned caches with SMLA_E_ALIGN.
+ * extra_topk_length.  impl as above, with two differences.  SMLA_IMPL_TC refuses caches whose base address or
+ * page stride is not a multiple of 16 bytes (what the kernel's bulk copies need) with SMLA_E_ALIGN; SMLA_IMPL_AUTO
+ * runs the fp32 kernel for them.  And SMLA_IMPL_AUTO runs the fp32 kernel for SMLA_LAYOUT_MODEL1: V includes the
+ * row's RoPE there, which the tcgen05 kernel rounds to e4m3 with the rest of V (the reference multiplies it in
+ * bf16, csrc/kernel/common/xv_rope_mma.cuh:23-93), so results of rows with few entries differ from the
+ * reference's by up to about 2e-3 on its own test data; callers that accept this ask for SMLA_IMPL_TC.
  */
 int smla_decode_splitkv_ext(const void* q, const void* kv, const int32_t* indices,
                             const void* extra_kv, const int32_t* extra_indices,

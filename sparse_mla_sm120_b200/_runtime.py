@@ -2,6 +2,7 @@
 from __future__ import annotations
 
 import ctypes
+import os
 from typing import Dict, Optional, Tuple
 
 import torch
@@ -79,6 +80,21 @@ def kv_geometry(kv_cache: torch.Tensor) -> Tuple[int, int]:
         pool = max(kv_cache.shape[0], 1)
         return pool, pool * 656
     raise ValueError(f"unsupported kv_cache rank {kv_cache.dim()}")
+
+
+# What IMPL_AUTO means for a MODEL1 cache.  The tensor-core kernel rounds V's RoPE columns to e4m3 (the reference
+# keeps them in bf16), which costs up to about 2e-3 on rows with few entries and fails some of the reference's own
+# V4 tests by a small margin; the default is therefore the exact fp32 kernel.  A deployment that accepts FP8-class
+# error in those 64 columns sets SMLA_MODEL1_IMPL=tc in the environment (or assigns _lib.IMPL_TC here) and gets the
+# tensor-core kernel, about two orders of magnitude faster.
+MODEL1_DEFAULT_IMPL = _lib.IMPL_TC if os.environ.get("SMLA_MODEL1_IMPL", "").lower() in ("tc", "2") else _lib.IMPL_SCALAR
+
+
+def resolve_impl(impl: int, layout: int) -> int:
+    """IMPL_AUTO for a MODEL1 cache -> MODEL1_DEFAULT_IMPL; everything else unchanged."""
+    if impl == _lib.IMPL_AUTO and layout == _lib.LAYOUT_MODEL1:
+        return MODEL1_DEFAULT_IMPL
+    return impl
 
 
 def tc_aligned(kv_cache: torch.Tensor, extra_kv: Optional[torch.Tensor] = None) -> bool:

@@ -17,6 +17,9 @@
 // A gathered row enters ONE SM from L2 (656 bytes per token per pair instead of 2 x 656), and no
 // score or softmax work is duplicated.
 //
+// The kernel is a template over the cache layout (656-byte V32 rows, or MODEL1 pages with a scale footer, see Lay<>
+// below) and over whether a request also walks a second cache (its blocks follow those of the main cache).
+//
 // Numerics (the FP8 class of the reference's V32 kernels, which quantise Q and P to e4m3:
 // csrc/kernel/common/fp8_quant.cuh:44-103, csrc/kernel/decode/decode_v2_kernel.cuh:414-493):
 //   * Q no-PE is quantised to e4m3 with one power-of-two scale sq_h per head; Q RoPE stays bf16

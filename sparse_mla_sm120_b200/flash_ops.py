@@ -19,7 +19,8 @@ import torch
 from . import _lib
 from ._lib import IMPL_AUTO, IMPL_SCALAR, LAYOUT_MODEL1, LAYOUT_V32, check
 from ._runtime import (BLOCK_N, FIXED_OVERHEAD, kv_geometry, kv_layout, num_sms, pick_num_sm_parts,
-                       pick_num_sm_parts_fp32, ptr, require_cuda, scratch, status_buffer, stream_ptr, tc_aligned)
+                       pick_num_sm_parts_fp32, ptr, require_cuda, resolve_impl, scratch, status_buffer, stream_ptr,
+                       tc_aligned)
 
 
 def _check_q(q: torch.Tensor):
@@ -85,6 +86,7 @@ def sparse_mla_splitkv_v2_fwd(Q, KV_cache, indices, o_accum, lse_accum, output, 
     num_tokens, num_heads, _ = Q.shape
     st = status_buffer(Q.device)
     layout = _layout(Q, KV_cache)
+    impl = resolve_impl(impl, layout)
     ex = _Extra(layout, num_tokens, extra_k_cache, extra_indices, extra_topk, extra_topk_length)
     if layout != LAYOUT_V32 or ex.topk:
         check(_lib.load().smla_decode_splitkv_ext(
@@ -122,6 +124,7 @@ def sparse_mla_prefill_raw(Q, KV_cache, indices, output, out_lse, sm_scale, topk
     num_tokens, num_heads, _ = Q.shape
     st = status_buffer(Q.device)
     layout = _layout(Q, KV_cache)
+    impl = resolve_impl(impl, layout)
     ex = _Extra(layout, num_tokens, extra_k_cache, extra_indices, extra_topk)
     if layout != LAYOUT_V32 or ex.topk:
         check(_lib.load().smla_prefill_ext(
@@ -164,6 +167,7 @@ def sparse_mla_decode_fwd(
     Signature and results follow flash_mla_sm120/ops.py:48-119."""
     _check_q(q)
     layout = _layout(q, kv_cache)
+    impl = resolve_impl(impl, layout)
     page_block_size, page_stride = kv_geometry(kv_cache)
     if d_v != 512:
         raise ValueError(f"d_v must be 512, got {d_v}")
@@ -250,6 +254,7 @@ def sparse_mla_prefill_fwd(
     flash_mla_sm120/ops.py:122-165."""
     _check_q(q)
     layout = _layout(q, kv_cache)
+    impl = resolve_impl(impl, layout)
     page_block_size, page_stride = kv_geometry(kv_cache)
     require_cuda(q, kv_cache, indices)
     if d_v != 512:

@@ -26,7 +26,7 @@ import torch
 from . import _lib
 from ._lib import IMPL_AUTO, IMPL_SCALAR, LAYOUT_V32, check
 from ._runtime import (BLOCK_N, FIXED_OVERHEAD, kv_geometry, num_sms, pick_num_sm_parts, pick_num_sm_parts_fp32, ptr,
-                       require_cuda, status_buffer, stream_ptr, tc_aligned)
+                       require_cuda, resolve_impl, status_buffer, stream_ptr, tc_aligned)
 from .flash_ops import _check_q, _Extra, _layout, sparse_mla_prefill_fwd
 
 
@@ -108,6 +108,7 @@ def flash_mla_with_kvcache(
     topk = indices.shape[-1]
     idx_in = indices.reshape(num_tokens, topk)
     layout = _layout(q_in, k_cache)
+    impl = resolve_impl(impl, layout)
     page_block_size, page_stride = kv_geometry(k_cache)
     require_cuda(q_in, k_cache, idx_in)
     assert idx_in.dtype == torch.int32 and idx_in.is_contiguous()

@@ -77,6 +77,17 @@ def test_python_surface_rejects_cpu_tensors_and_mismatched_layouts():
         smla.flash_ops.sparse_mla_decode_fwd(q, kv, idx, 1.0, extra_topk=64)
 
 
+def test_model1_default_impl():
+    """IMPL_AUTO resolves per layout: the tensor-core kernel for 656-byte rows, the exact fp32 kernel for MODEL1
+    unless the module switch says otherwise; an explicit choice is never changed."""
+    from sparse_mla_sm120_b200 import _runtime
+    L = _lib
+    assert _runtime.resolve_impl(L.IMPL_AUTO, L.LAYOUT_V32) == L.IMPL_AUTO
+    assert _runtime.resolve_impl(L.IMPL_AUTO, L.LAYOUT_MODEL1) == _runtime.MODEL1_DEFAULT_IMPL == L.IMPL_SCALAR
+    assert _runtime.resolve_impl(L.IMPL_TC, L.LAYOUT_MODEL1) == L.IMPL_TC
+    assert _runtime.resolve_impl(L.IMPL_SCALAR, L.LAYOUT_V32) == L.IMPL_SCALAR
+
+
 def test_split_policy():
     from sparse_mla_sm120_b200._runtime import pick_num_sm_parts
     assert pick_num_sm_parts(64, 148) == 64      # 128 CTAs on 148 SMs: unsplit

@@ -228,7 +228,7 @@ def test_model1_prefill(h, tokens, topk, extra, impl):
         topk_length=_dev(c["topk_length"]), extra_k_cache=_dev(c["extra_packed"]),
         extra_indices_in_kvcache=eidx)
     torch.cuda.synchronize()
-    if impl == TC:     # the FlashMLA-shaped wrapper runs the default kernel, which is the tensor-core one
+    if impl == FP32:   # the FlashMLA-shaped wrapper runs the default kernel, which for this layout is the fp32 one
         assert torch.equal(out2, out) and torch.equal(lse2, lse) and torch.equal(mx2, mx)
     t = 0
     idx = c["indices"][t, 0]
@@ -289,14 +289,40 @@ def test_layout_mismatch_is_refused():
 def test_unaligned_pages_fall_back_to_the_fp32_kernel():
     """The tensor-core kernel's bulk copies need page strides that are multiples of 16 bytes: asked for by name it
     refuses others, left to choose the library runs the fp32 kernel."""
-    from sparse_mla_sm120_b200 import flash_ops
     c = _m1_case(5, 2, 16, 128, nblk=8)
     nb, bs = c["packed"].shape[:2]
     wide = torch.zeros(nb, bs * 584 + 8, dtype=torch.uint8)
     wide[:, :bs * 584] = c["packed"].reshape(nb, -1)
-    ref_out, ref_lse = _oracle(c)
     c["packed"] = _dev(wide)[:, :bs * 584].view(nb, bs, 1, 584)
+    with pytest.raises(ValueError, match="aligned"):
+        _decode(c, impl=TC)
+    # 656-byte rows with a second cache whose pages are 8 bytes further apart than their rows need
+    c = _m1_case(6, 2, 16, 128, extra_topk=64, nblk=8, layout="v32")
+    ref_out, ref_lse = _oracle(c)
+    nb, bs = c["extra_packed"].shape[:2]
+    wide = torch.zeros(nb, bs * 656 + 8, dtype=torch.uint8)
+    wide[:, :bs * 656] = c["extra_packed"].reshape(nb, -1)
+    c["extra_packed"] = _dev(wide)[:, :bs * 656].view(nb, bs, 1, 656)
     out, lse = _decode(c, impl=0)
     _compare(out, lse, ref_out, ref_lse, impl=FP32)
     with pytest.raises(ValueError, match="aligned"):
         _decode(c, impl=TC)
+
+
+def test_model1_default_kernel_and_its_switch():
+    """Left to choose, a MODEL1 call runs the exact fp32 kernel; _runtime.MODEL1_DEFAULT_IMPL (or SMLA_MODEL1_IMPL=tc
+    in the environment) makes the tensor-core kernel the default."""
+    from sparse_mla_sm120_b200 import _runtime
+    c = _m1_case(8, 3, 64, 256, extra_topk=64, nblk=16)
+    exact, _ = _decode(c, impl=FP32)
+    fast, _ = _decode(c, impl=TC)
+    assert not torch.equal(exact, fast)
+    assert _runtime.MODEL1_DEFAULT_IMPL == FP32
+    auto, _ = _decode(c, impl=0)
+    assert torch.equal(auto, exact)
+    _runtime.MODEL1_DEFAULT_IMPL = TC
+    try:
+        auto, _ = _decode(c, impl=0)
+    finally:
+        _runtime.MODEL1_DEFAULT_IMPL = FP32
+    assert torch.equal(auto, fast)

@@ -36,11 +36,11 @@ def test_reference_file(path):
     if not ref or not os.path.exists(os.path.join(ref, path)):
         pytest.skip("SMLA_REFERENCE_TESTS does not point at a checkout of the reference")
     env = dict(os.environ, PYTHONPATH=ROOT + os.pathsep + os.environ.get("PYTHONPATH", ""))
-    cmd = [sys.executable, "-m", "pytest", path, "-q", "-x", "-p", "no:cacheprovider"]
+    cmd = [sys.executable, "-m", "pytest", path, "-q", "-rf", "--tb=line", "-p", "no:cacheprovider"]
     if SELECTION[path]:
         cmd += ["-k", SELECTION[path]]
     res = subprocess.run(cmd, cwd=ref, env=env, capture_output=True, text=True, timeout=1200)
-    tail = (res.stdout + res.stderr)[-3000:]
+    tail = (res.stdout + res.stderr)[-6000:]
     log = os.environ.get("SMLA_REFERENCE_LOG")
     if log:
         with open(log, "a") as f:
