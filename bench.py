@@ -488,6 +488,16 @@ def run_cp_extra(device, rank, world):
     res["us_per_step_with_indexer"] = timed(
         lambda: cp.sparse_mla_indexed_decode_cp_fwd(q, kv_one, qi, ki, k_scale, w, ks, ke, SM_SCALE, lo, hi, topk=TOPK))
     res["indexer_exchange_bytes_per_rank"] = b * TOPK * 8
+    try:
+        gi2 = cp.GraphedIndexedCpDecode(kv_one, ki, k_scale, b, HEADS, hh, SM_SCALE, lo, hi, topk=TOPK)
+        gi2(q, qi, w, ks, ke)
+        res["us_per_step_with_indexer_graph"] = timed(gi2.replay)
+        res["indexer_graph_captured"] = gi2.graph is not None
+        gi2.close()
+        del gi2
+    except Exception as e:       # noqa: BLE001
+        res["us_per_step_with_indexer_graph"] = None
+        res["indexer_graph_error"] = repr(e)
     return res
 
 

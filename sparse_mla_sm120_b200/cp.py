@@ -377,3 +377,67 @@ def sparse_mla_indexed_decode_cp_fwd(q, kv_local, qi, ki_local, k_scale_local, w
     indices = select_indices_cp(qi, ki_local, k_scale_local, weights, ks, ke, shard_lo, shard_hi, topk, group)
     out, lse = sparse_mla_decode_cp_fwd(q, kv_local, indices, sm_scale, shard_lo, shard_hi, group, attn_sink, impl)
     return out, lse, indices
+
+
+class GraphedIndexedCpDecode:
+    """``sparse_mla_indexed_decode_cp_fwd`` (indexer logits over the shard, local top-k, candidate all-gather,
+    global top-k, index partition, local decode, exchange, merge) captured into one CUDA graph, its three
+    collectives included: one graph launch per step instead of about twenty launches issued from the host.
+    Shapes are fixed at construction; the cache shard and the shard's indexer keys are bound by reference; the
+    step's inputs are copied into static buffers before a replay.  ``close()`` before the process group goes, as
+    for GraphedCpDecode.  If the capture fails the object runs the step eagerly and ``self.graph`` is None."""
+
+    def __init__(self, kv_local, ki_local, k_scale_local, num_tokens: int, num_heads: int, indexer_heads: int,
+                 sm_scale: float, shard_lo: int, shard_hi: int, topk: int = 2048, group=None, attn_sink=None,
+                 impl: int = IMPL_AUTO):
+        dev = kv_local.device
+        self.kv_local, self.ki_local, self.k_scale_local, self.attn_sink = kv_local, ki_local, k_scale_local, attn_sink
+        self.q = torch.zeros((num_tokens, num_heads, 576), dtype=torch.bfloat16, device=dev)
+        self.qi = torch.zeros((num_tokens, indexer_heads, 128), dtype=torch.float8_e4m3fn, device=dev)
+        self.weights = torch.zeros((num_tokens, indexer_heads), dtype=torch.float32, device=dev)
+        self.ks = torch.zeros(num_tokens, dtype=torch.int32, device=dev)
+        self.ke = torch.zeros(num_tokens, dtype=torch.int32, device=dev)
+
+        def step():
+            return sparse_mla_indexed_decode_cp_fwd(self.q, kv_local, self.qi, ki_local, k_scale_local, self.weights,
+                                                    self.ks, self.ke, sm_scale, shard_lo, shard_hi, topk, group,
+                                                    attn_sink, impl)
+
+        self._step = step
+        self.graph = None
+        side = torch.cuda.Stream(device=dev)
+        side.wait_stream(torch.cuda.current_stream(dev))
+        with torch.cuda.stream(side):
+            for _ in range(2):
+                self.out, self.lse, self.indices = step()   # warm-up: library load, buffers, communicator set-up
+            side.synchronize()
+            try:
+                graph = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(graph, stream=side):
+                    self.out, self.lse, self.indices = step()
+                self.graph = graph
+            except Exception:                        # noqa: BLE001 - any capture failure means: run eagerly
+                self.graph = None
+        torch.cuda.current_stream(dev).wait_stream(side)
+
+    def __call__(self, q, qi, weights, ks, ke):
+        self.q.copy_(q)
+        self.qi.copy_(qi)
+        self.weights.copy_(weights)
+        self.ks.copy_(ks)
+        self.ke.copy_(ke)
+        return self.replay()
+
+    def close(self):
+        torch.cuda.synchronize(self.q.device)
+        self.graph = None
+        self._step = None
+
+    def replay(self):
+        """(out, lse, indices): static tensors, overwritten by the next replay."""
+        if self.graph is None:
+            self.out, self.lse, self.indices = self._step()
+        else:
+            self.graph.replay()
+        return self.out, self.lse, self.indices
+

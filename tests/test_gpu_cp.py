@@ -234,6 +234,16 @@ case["indices"] = sel
 ref_out, ref_lse = H.oracle_attn(case)
 H.compare_out(out, ref_out, H.TC_ABS, H.TC_REL, H.TC_COS)
 H.compare_lse(lse, ref_lse, H.TC_LSE)
+# the same step with the indexer, captured into one CUDA graph (three collectives inside), replayed twice
+gi = cp.GraphedIndexedCpDecode(kv_local, ki[lo:hi].contiguous().to(dev), k_scale[lo:hi].contiguous().to(dev), 4, 128, 64,
+                               case["sm_scale"], lo, hi, topk=1024)
+for _ in range(2):
+    g_out, g_lse, g_sel = gi(case["q"].to(dev), qi.to(dev), w.to(dev), ks.to(dev), ke.to(dev))
+    torch.cuda.synchronize()
+    assert torch.equal(g_sel.cpu(), sel) and torch.equal(g_out, out) and torch.equal(g_lse, lse), \
+        "graph replay of the indexed step differs from the eager step"
+assert gi.graph is not None
+gi.close()
 print("rank", rank, "ok", flush=True)
 dist.barrier(); torch.cuda.synchronize()
 os._exit(0)      # every rank leaves at once; nothing here depends on an orderly shutdown of the communicator
