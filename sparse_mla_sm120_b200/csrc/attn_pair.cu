@@ -219,7 +219,11 @@ __device__ __forceinline__ int tile_entry(const AttnParams& p, const Work& w, in
     return (j < nst && pos < lim) ? __ldg(p.indices + (size_t)w.req * p.topk + pos) : -1;
 }
 
-template <int LAYOUT, bool EXTRA>
+// STAGE_Q: the Q rows of a partition's first request come in by one bulk copy (see below).  That pays when the
+// partition has one request or few (decode: 0.7 us of a 54 us step, the rows come from HBM); with many requests per
+// partition (prefill) the instances without it are 7 % faster (the waits it adds to the loops of the gather warps and
+// of the copy thread are never taken after the first tiles, but they are in the loops).
+template <int LAYOUT, bool EXTRA, bool STAGE_Q>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PAIR_THREADS, 1) attn_pair_kernel(const AttnParams p) {
     using L = Lay<LAYOUT>;
     extern __shared__ uint8_t smem_raw[];
@@ -298,7 +302,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PAIR_THREADS, 1) att
     const int last_req = min(meta.end_req, p.num_tokens - 1);
     const int live_heads = min(heads_cta, max(p.num_heads - head0, 0));
     Work w_first;
-    const bool first_work = meta.begin_req <= last_req && get_work(p, meta, meta.begin_req, w_first);   // the same in both CTAs
+    const bool first_work = STAGE_Q && meta.begin_req <= last_req && get_work(p, meta, meta.begin_req, w_first);   // the same in both CTAs
     const bool q_staged = first_work && live_heads > 0;
     if (tid == 0 && q_staged) {
         const uint32_t bytes = (uint32_t)live_heads * L::QD * 2;
@@ -341,7 +345,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PAIR_THREADS, 1) att
             // group, which is also how it loads them (16 bytes of bf16 per row and block).
             {
                 const int g = lane >> 2, c4 = lane & 3;
-                const bool from_smem = q_staged && req == meta.begin_req;
+                const bool from_smem = STAGE_Q && q_staged && req == meta.begin_req;
                 if (from_smem && !dead) dead = !mbar_wait_hot(bar(BAR_QSTAGE), 0u, abort_flag, W_QSTAGE);
                 // row (head0 + r) of the request's Q, wherever it lies
                 const __nv_bfloat16* qrows = from_smem ? reinterpret_cast<const __nv_bfloat16*>(sm + QSTAGE_OFF) - (size_t)head0 * L::QD
@@ -355,19 +359,42 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PAIR_THREADS, 1) att
                     const bool v_b = !dead && r_b < heads_cta && head0 + r_b < p.num_heads;
                     const __nv_bfloat16* src_a = qrows + (size_t)(head0 + (v_a ? r_a : 0)) * L::QD + ch * 256 + c4 * 8;
                     const __nv_bfloat16* src_b = qrows + (size_t)(head0 + (v_b ? r_b : 0)) * L::QD + ch * 256 + c4 * 8;
-                    // two passes over the rows' bytes (the second is served by L1/L2): keeping a 16-row group in
-                    // registers between the maxima and the quantisation spilled
-                    auto absmax8 = [](const uint4& a) {
-                        return fmaxf(fmaxf(fmaxf(fabsf(bf16lo(a.x)), fabsf(bf16hi(a.x))), fmaxf(fabsf(bf16lo(a.y)), fabsf(bf16hi(a.y)))),
-                                     fmaxf(fmaxf(fabsf(bf16lo(a.z)), fabsf(bf16hi(a.z))), fmaxf(fabsf(bf16lo(a.w)), fabsf(bf16hi(a.w)))));
-                    };
-                    float am_a = 0.f, am_b = 0.f;
+                    // One pass: all 16 loads of the lane are issued before the first is used (one round of latency) and the
+                    // pieces stay in registers between the maxima (packed bf16 arithmetic, exact) and the quantisation.
+                    // Two copies of the loads, so that each is a plain shared-memory or global-memory load.
+                    uint4 xa[8], xb[8];
+                    const __nv_bfloat16* gsrc_a = p.q + ((size_t)req * p.num_heads + head0 + (v_a ? r_a : 0)) * L::QD + ch * 256 + c4 * 8;
+                    const __nv_bfloat16* gsrc_b = p.q + ((size_t)req * p.num_heads + head0 + (v_b ? r_b : 0)) * L::QD + ch * 256 + c4 * 8;
+                    if (from_smem) {
+                        const uint32_t sa = smem_u32(src_a), sb = smem_u32(src_b);
 #pragma unroll
-                    for (int i = 0; i < 8; ++i) {
-                        const uint4 xa = (v_a && i < nblk32) ? *reinterpret_cast<const uint4*>(src_a + 32 * i) : make_uint4(0, 0, 0, 0);
-                        const uint4 xb = (v_b && i < nblk32) ? *reinterpret_cast<const uint4*>(src_b + 32 * i) : make_uint4(0, 0, 0, 0);
-                        am_a = fmaxf(am_a, absmax8(xa)); am_b = fmaxf(am_b, absmax8(xb));
+                        for (int i = 0; i < 8; ++i) {
+                            xa[i] = xb[i] = make_uint4(0, 0, 0, 0);
+                            if (v_a && i < nblk32)
+                                asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(xa[i].x), "=r"(xa[i].y), "=r"(xa[i].z), "=r"(xa[i].w) : "r"(sa + 64 * i));
+                            if (v_b && i < nblk32)
+                                asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(xb[i].x), "=r"(xb[i].y), "=r"(xb[i].z), "=r"(xb[i].w) : "r"(sb + 64 * i));
+                        }
+                    } else {
+#pragma unroll
+                        for (int i = 0; i < 8; ++i) {
+                            xa[i] = xb[i] = make_uint4(0, 0, 0, 0);
+                            if (v_a && i < nblk32) xa[i] = __ldg(reinterpret_cast<const uint4*>(gsrc_a + 32 * i));
+                            if (v_b && i < nblk32) xb[i] = __ldg(reinterpret_cast<const uint4*>(gsrc_b + 32 * i));
+                        }
                     }
+                    auto amax2 = [](uint32_t m, const uint4& a) {      // running |.| maximum of bf16 pairs
+                        auto mx = [](uint32_t u, uint32_t v) {
+                            const __nv_bfloat162 r = __hmax2(*reinterpret_cast<const __nv_bfloat162*>(&u),
+                                                             __habs2(*reinterpret_cast<const __nv_bfloat162*>(&v)));
+                            return *reinterpret_cast<const uint32_t*>(&r);
+                        };
+                        return mx(mx(mx(mx(m, a.x), a.y), a.z), a.w);
+                    };
+                    uint32_t ma = 0u, mb = 0u;
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) { ma = amax2(ma, xa[i]); mb = amax2(mb, xb[i]); }
+                    float am_a = fmaxf(bf16lo(ma), bf16hi(ma)), am_b = fmaxf(bf16lo(mb), bf16hi(mb));
                     am_a = fmaxf(am_a, __shfl_xor_sync(0xffffffffu, am_a, 1)); am_b = fmaxf(am_b, __shfl_xor_sync(0xffffffffu, am_b, 1));
                     am_a = fmaxf(am_a, __shfl_xor_sync(0xffffffffu, am_a, 2)); am_b = fmaxf(am_b, __shfl_xor_sync(0xffffffffu, am_b, 2));
                     // both column halves of a row agree on one scale (the repeating quarter writes the same values)
@@ -380,14 +407,12 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PAIR_THREADS, 1) att
                     const float ib = __uint_as_float(0x7f000000u - __float_as_uint(sq_b));
                     if (c4 == 0) { sqv[r_a] = sq_a; sqv[r_b] = sq_b; }
                     if (!dead) {
-#pragma unroll 1
+#pragma unroll
                         for (int h4 = 0; h4 < 2; ++h4) {
                             uint32_t wq[16];
 #pragma unroll
                             for (int kk = 0; kk < 4; ++kk) {
-                                const bool in = 4 * h4 + kk < nblk32;
-                                const uint4 a = (v_a && in) ? *reinterpret_cast<const uint4*>(src_a + 32 * (4 * h4 + kk)) : make_uint4(0, 0, 0, 0);
-                                const uint4 b4 = (v_b && in) ? *reinterpret_cast<const uint4*>(src_b + 32 * (4 * h4 + kk)) : make_uint4(0, 0, 0, 0);
+                                const uint4 a = xa[4 * h4 + kk], b4 = xb[4 * h4 + kk];
                                 wq[4 * kk + 0] = pack_e4m3x4(bf16lo(a.x) * ia, bf16hi(a.x) * ia, bf16lo(a.y) * ia, bf16hi(a.y) * ia);
                                 wq[4 * kk + 1] = pack_e4m3x4(bf16lo(a.z) * ia, bf16hi(a.z) * ia, bf16lo(a.w) * ia, bf16hi(a.w) * ia);
                                 wq[4 * kk + 2] = pack_e4m3x4(bf16lo(b4.x) * ib, bf16hi(b4.x) * ib, bf16lo(b4.y) * ib, bf16hi(b4.y) * ib);
@@ -419,7 +444,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PAIR_THREADS, 1) att
                     tc_fence_before();     // also orders the previous epilogue's TMEM reads before the next MMAs
                 }
                 __syncwarp();
-                if (first_work && req == meta.begin_req && lane == 0) {   // this warp has read the staged rows for the last time (if any): tell both CTAs
+                if (STAGE_Q && first_work && req == meta.begin_req && lane == 0) {   // this warp has read the staged rows for the last time (if any): tell both CTAs
                     mbar_arrive(bar(BAR_QFREE));
                     mbar_arrive_remote(mapa_shared(bar(BAR_QFREE), 1u - rank));
                 }
@@ -723,7 +748,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PAIR_THREADS, 1) att
                 PROF(2);
                 TRACE(62, t_it);
                 if (ok && t_it >= NK) ok = mbar_wait_hot(bar(BAR_KEMPTY + ks), ((t_it / NK) - 1) & 1u, abort_flag, W_KEMPTY);
-                if (ok && t_it < NK && ks != 0 && first_work) ok = mbar_wait_hot(bar(BAR_QFREE), 0u, abort_flag, W_QFREE);   // K stage 1 held Q until now
+                if (STAGE_Q && ok && t_it < NK && ks != 0 && first_work) ok = mbar_wait_hot(bar(BAR_QFREE), 0u, abort_flag, W_QFREE);   // K stage 1 held Q until now
                 PROF(3);
                 TRACE(63, t_it);
                 if (!ok) { stop = true; break; }
@@ -904,7 +929,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PAIR_THREADS, 1) att
                 if (it >= NV) {
                     ok = mbar_wait_thread(bar(BAR_VEMPTY + vs), ((it / NV) - 1) & 1u, abort_flag, W_VEMPTY);
                     if (!ok) break;
-                } else if (first_work) {    // the V stages of both CTAs held Q until the softmax warps had read it
+                } else if (STAGE_Q && first_work) {    // the V stages of both CTAs held Q until the softmax warps had read it
                     ok = mbar_wait_thread(bar(BAR_QFREE), 0u, abort_flag, W_QFREE);
                     if (!ok) break;
                 }
@@ -1033,8 +1058,8 @@ extern "C" int smla_prof_set(long long* buf, int block) {
 
 namespace {
 
-template <int LAYOUT, bool EXTRA>
-int launch_pair_layout(const AttnParams& p, cudaStream_t stream) {
+template <int LAYOUT, bool EXTRA, bool STAGE_Q>
+int launch_pair_instance(const AttnParams& p, cudaStream_t stream) {
     static bool attr_set[64] = {};
     static int sm_count[64] = {};
     int dev = 0;
@@ -1042,10 +1067,10 @@ int launch_pair_layout(const AttnParams& p, cudaStream_t stream) {
     if (dev < 0 || dev >= 64) return set_error(SMLA_E_SHAPE, "attn_pair_kernel: device ordinal %d not supported", dev);
     if (!attr_set[dev]) {
         cudaFuncAttributes fa;
-        if (cudaFuncGetAttributes(&fa, attn_pair_kernel<LAYOUT, EXTRA>) != cudaSuccess || fa.numRegs != REGS_LAUNCH)
+        if (cudaFuncGetAttributes(&fa, attn_pair_kernel<LAYOUT, EXTRA, STAGE_Q>) != cudaSuccess || fa.numRegs != REGS_LAUNCH)
             return set_error(SMLA_E_DEVICE, "attn_pair_kernel: compiled with %d registers per thread, the warpgroup budgets assume %d",
                              fa.numRegs, REGS_LAUNCH);
-        const cudaError_t e = cudaFuncSetAttribute(attn_pair_kernel<LAYOUT, EXTRA>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_ALLOC);
+        const cudaError_t e = cudaFuncSetAttribute(attn_pair_kernel<LAYOUT, EXTRA, STAGE_Q>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_ALLOC);
         if (e != cudaSuccess) return set_error((int)e, "attn_pair_kernel: cannot reserve %u bytes of shared memory: %s",
                                                SMEM_ALLOC, cudaGetErrorString(e));
         cudaDeviceGetAttribute(&sm_count[dev], cudaDevAttrMultiProcessorCount, dev);
@@ -1055,9 +1080,9 @@ int launch_pair_layout(const AttnParams& p, cudaStream_t stream) {
     const int max_pairs = sm_count[dev] >= 2 ? sm_count[dev] / 2 : 1;
     const int parts = p.sched ? p.num_parts : (p.num_tokens < max_pairs ? p.num_tokens : max_pairs);
     if (p.sched != nullptr)      // the scheduler kernel runs just before: start while it finishes
-        launch_dependent(attn_pair_kernel<LAYOUT, EXTRA>, dim3(2 * parts), dim3(PAIR_THREADS), SMEM_ALLOC, stream, p);
+        launch_dependent(attn_pair_kernel<LAYOUT, EXTRA, STAGE_Q>, dim3(2 * parts), dim3(PAIR_THREADS), SMEM_ALLOC, stream, p);
     else
-        attn_pair_kernel<LAYOUT, EXTRA><<<2 * parts, PAIR_THREADS, SMEM_ALLOC, stream>>>(p);
+        attn_pair_kernel<LAYOUT, EXTRA, STAGE_Q><<<2 * parts, PAIR_THREADS, SMEM_ALLOC, stream>>>(p);
     return check_launch("attn_pair_kernel");
 }
 
@@ -1073,11 +1098,24 @@ bool attn_pair_takes(const AttnParams& p) {
 
 int launch_attn_pair(const AttnParams& p, cudaStream_t stream) {
     if (p.num_tokens == 0) return 0;
-    if (p.layout == SMLA_LAYOUT_MODEL1)
-        return p.extra_topk > 0 ? launch_pair_layout<SMLA_LAYOUT_MODEL1, true>(p, stream)
-                                : launch_pair_layout<SMLA_LAYOUT_MODEL1, false>(p, stream);
-    return p.extra_topk > 0 ? launch_pair_layout<SMLA_LAYOUT_V32, true>(p, stream)
-                            : launch_pair_layout<SMLA_LAYOUT_V32, false>(p, stream);
+    // Without a scheduler a pair walks ceil(num_tokens / pairs) whole requests: from three on, no staging of the first one's Q.
+    static int sm_count[64] = {};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev < 0 || dev >= 64) return set_error(SMLA_E_SHAPE, "attn_pair_kernel: device ordinal %d not supported", dev);
+    if (sm_count[dev] == 0) cudaDeviceGetAttribute(&sm_count[dev], cudaDevAttrMultiProcessorCount, dev);
+    const int sms = sm_count[dev];
+    const bool stage = p.sched != nullptr || p.num_tokens <= 2 * (sms >= 2 ? sms / 2 : 1);
+    if (p.layout == SMLA_LAYOUT_MODEL1) {
+        if (p.extra_topk > 0) return stage ? launch_pair_instance<SMLA_LAYOUT_MODEL1, true, true>(p, stream)
+                                           : launch_pair_instance<SMLA_LAYOUT_MODEL1, true, false>(p, stream);
+        return stage ? launch_pair_instance<SMLA_LAYOUT_MODEL1, false, true>(p, stream)
+                     : launch_pair_instance<SMLA_LAYOUT_MODEL1, false, false>(p, stream);
+    }
+    if (p.extra_topk > 0) return stage ? launch_pair_instance<SMLA_LAYOUT_V32, true, true>(p, stream)
+                                       : launch_pair_instance<SMLA_LAYOUT_V32, true, false>(p, stream);
+    return stage ? launch_pair_instance<SMLA_LAYOUT_V32, false, true>(p, stream)
+                 : launch_pair_instance<SMLA_LAYOUT_V32, false, false>(p, stream);
 }
 
 }  // namespace smla
