@@ -44,7 +44,7 @@ WORKLOAD = ("V3.2-shape sparse-MLA decode: b=64/GPU, s_q=1, h_q=128, topk=2048, 
             "KV len U[4096,32768], paged block 64, packed FP8 656 B rows")
 # DRAM bytes of one launch of the attention kernel on this workload's shape, from one ncu capture
 # (dram__bytes_read.sum + dram__bytes_write.sum); the capture's summary is kept with the other profiles.
-NCU_TRAFFIC_BYTES = 88_533_504
+NCU_TRAFFIC_BYTES = 90_111_232
 CPU_SAMPLE_REQUESTS = 64   # requests of one step that the CPU legs compute: the whole step (about 0.13 s on 16 host threads)
 
 
@@ -813,7 +813,16 @@ def run_small_case(name):
     torch.cuda.set_device(0)
     g = torch.Generator(device=device).manual_seed(11)
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    if name == "prefill":
+    if name == "decode":
+        # the headline's shape over a 172 MB pool (larger than L2, small enough for a profiler's save and restore)
+        pages = 4096
+        kv = indexer.pack_kv_cache(torch.randn((pages * 64, D_QK), device=device, generator=g).to(torch.bfloat16)).view(pages, 64, 1, ROW)
+        q = (torch.randn((B_PER_GPU, HEADS, D_QK), device=device, generator=g) * 0.5).to(torch.bfloat16)
+        idx = torch.stack([torch.randperm(pages * 64, device=device, generator=g)[:TOPK] for _ in range(B_PER_GPU)]).to(torch.int32)
+        fn = lambda: flash_ops.sparse_mla_decode_fwd(q, kv, idx, SM_SCALE)
+        work = {"flop": 2.0 * B_PER_GPU * HEADS * TOPK * (D_QK + D_V)}
+        desc = f"decode b={B_PER_GPU}, h=128, topk=2048, KV pool of {pages * 64} rows (172 MB)"
+    elif name == "prefill":
         s_q, rows = 512, 8192
         kv = indexer.pack_kv_cache(torch.randn((rows, D_QK), device=device, generator=g).to(torch.bfloat16)).view(rows // 64, 64, 1, ROW)
         q = torch.randn((s_q, HEADS, D_QK), device=device, generator=g).to(torch.bfloat16)
@@ -855,7 +864,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=50)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-extras", action="store_true")
-    ap.add_argument("--case", default=None, choices=["prefill", "indexer"],
+    ap.add_argument("--case", default=None, choices=["decode", "prefill", "indexer"],
                     help="run a small instance of a secondary kernel (for profiler captures) instead of the benchmark")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
