@@ -334,10 +334,21 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PAIR_THREADS, 1) att
         uint32_t it = 0;                                  // running tile counter of this CTA
         bool dead = false;                                // a wait of this warp gave up: no more work, only barriers
         bool stop = false;
-        for (int req = meta.begin_req; req <= last_req && !stop; ++req) {
+        // A request's epilogue runs after the NEXT request's Q phase: Q and its scales are free as soon as the last
+        // scores of a request have been read, the accumulator only when its last P.V has completed, so the next
+        // request's Q is quantised while that P.V runs and its first score MMAs run while the output is written.
+        bool prev_valid = false, prev_no_split = false;
+        int prev_req = 0, prev_split = 0;
+        uint32_t prev_last = 0;
+        float prev_m = 0.f, prev_l = 0.f, prev_x = 0.f;
+        for (int req = meta.begin_req; req <= last_req + 1 && !stop; ++req) {
             Work w;
-            if (!get_work(p, meta, req, w)) continue;
-            const int nst = (w.nblk + 1) >> 1;
+            const bool have = req <= last_req && get_work(p, meta, req, w);
+            if (req <= last_req && !have) continue;
+            const int nst = have ? (w.nblk + 1) >> 1 : 0;
+            float my_sqc = 0.f;
+            if (have) {
+            if (prev_valid) named_bar_sync(1 + grp, 128);      // the group has read the last tile's row maxima: xch may be reused
             // ---- Q: warp (quarter, ch) quantises no-PE dims [256*ch, +256) of the 32 heads of its lane quarter into
             // tensor memory (the A operand of a pair MMA wants the CTA's 64 rows twice: quarters 2 and 3 repeat the
             // work of quarters 0 and 1).  The 16x256b store shape takes a row from four lanes: lane (g = lane/4,
@@ -461,10 +472,94 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PAIR_THREADS, 1) att
                 for (int i = tid; i < lines; i += N_SM_WARPS * 32)
                     asm volatile("prefetch.global.L2 [%0];" ::"l"(qn + (size_t)i * 128));
             }
-            const float my_sqc = live ? sqv[hrow] * p.sm_scale * LOG2E : 0.f;
+            my_sqc = live ? sqv[hrow] * p.sm_scale * LOG2E : 0.f;
             __syncwarp();
             if (lane == 0) mbar_arrive_remote(barp(BAR_QREADYP));
 
+            }
+            // ---- epilogue of the request before ------------------------------------------------
+            if (prev_valid) {
+                const uint32_t last = prev_last;
+                if (!dead) dead = !mbar_wait_hot(bar(BAR_PVDONE + (last & 1u)), (last >> 1) & 1u, abort_flag, W_PVDONE);
+                tc_fence_after();
+                if (named_bar_or(1 + grp, 128, dead || *abort_flag != 0)) { stop = true; break; }   // the partners have read the last tile's row maxima
+                xch[xpart * 64 + hrow] = prev_l;
+                xch[256 + xpart * 64 + hrow] = prev_x;
+                named_bar_sync(1 + grp, 128);
+                const float l_all = (xch[hrow] + xch[64 + hrow]) + (xch[128 + hrow] + xch[192 + hrow]);
+                const float xm = fmaxf(fmaxf(xch[256 + hrow], xch[320 + hrow]), fmaxf(xch[384 + hrow], xch[448 + hrow]));
+                float lse = (l_all > 0.f) ? (log2f(l_all) - (float)P_SHIFT + prev_m) : NEG_BIG;
+                float denom = l_all;
+                if (prev_no_split && p.attn_sink != nullptr && live) {
+                    const float sink2 = p.attn_sink[head] * LOG2E;
+                    denom = l_all + ((prev_m == -INFINITY) ? INFINITY : exp2f(sink2 - prev_m + (float)P_SHIFT));
+                    if (lse != NEG_BIG) lse += log2f(1.f + exp2f(sink2 - lse));
+                    else lse = sink2;
+                }
+                const float inv = (denom > 0.f) ? 1.f / denom : 0.f;
+                const int col0 = thalf * 256 + ch * 128;      // first output dim of this thread
+                if (prev_no_split) {
+                    __nv_bfloat16* dst = p.out + ((size_t)prev_req * p.num_heads + (live ? head : 0)) * D_V + col0;
+#pragma unroll 1
+                    for (int c = 0; c < 128; c += 32) {
+                        uint32_t o[32];
+                        tmem_ld32(lane_addr + TM_O + 128 * ch + c, o);
+                        tmem_wait_ld();
+                        if (live) {
+                            uint32_t pk[16];
+#pragma unroll
+                            for (int i = 0; i < 16; ++i) {
+                                __nv_bfloat162 t = __floats2bfloat162_rn(__uint_as_float(o[2 * i]) * inv, __uint_as_float(o[2 * i + 1]) * inv);
+                                pk[i] = *reinterpret_cast<uint32_t*>(&t);
+                            }
+                            if (wide_out) {
+                                const uint32_t lo8[8] = {pk[0], pk[1], pk[2], pk[3], pk[4], pk[5], pk[6], pk[7]};
+                                const uint32_t hi8[8] = {pk[8], pk[9], pk[10], pk[11], pk[12], pk[13], pk[14], pk[15]};
+                                st_global_v8(dst + c, lo8);
+                                st_global_v8(dst + c + 16, hi8);
+                            } else {
+#pragma unroll
+                                for (int i = 0; i < 4; ++i)
+                                    *reinterpret_cast<uint4*>(dst + c + 8 * i) = make_uint4(pk[4 * i], pk[4 * i + 1], pk[4 * i + 2], pk[4 * i + 3]);
+                            }
+                        }
+                    }
+                    if (live && xpart == 0) {
+                        p.out_lse[(size_t)prev_req * p.num_heads + head] = lse;
+                        if (p.out_max_logits) p.out_max_logits[(size_t)prev_req * p.num_heads + head] = (xm == -INFINITY) ? NEG_BIG : xm;
+                    }
+                } else {
+                    float* dst = p.o_accum + ((size_t)prev_split * p.num_heads + (live ? head : 0)) * D_V + col0;
+#pragma unroll 1
+                    for (int c = 0; c < 128; c += 32) {
+                        uint32_t o[32];
+                        tmem_ld32(lane_addr + TM_O + 128 * ch + c, o);
+                        tmem_wait_ld();
+                        if (live) {
+#pragma unroll
+                            for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * inv);
+                            if (wide_acc) {
+#pragma unroll
+                                for (int i = 0; i < 32; i += 8) {
+                                    const uint32_t v8[8] = {o[i], o[i + 1], o[i + 2], o[i + 3], o[i + 4], o[i + 5], o[i + 6], o[i + 7]};
+                                    st_global_v8(dst + c + i, v8);
+                                }
+                            } else {
+#pragma unroll
+                                for (int i = 0; i < 32; i += 4)
+                                    *reinterpret_cast<uint4*>(dst + c + i) = make_uint4(o[i], o[i + 1], o[i + 2], o[i + 3]);
+                            }
+                        }
+                    }
+                    if (live && xpart == 0) p.lse_accum[(size_t)prev_split * p.num_heads + head] = lse;
+                }
+                tc_fence_before();                  // the accumulator reads precede the next request's first P.V
+                named_bar_sync(1 + grp, 128);       // xch is free again
+                PROF(12);
+                TRACE(4, it);
+            }
+            prev_valid = false;
+            if (!have) break;
             float m_run = -INFINITY;   // running maximum of z (lags by at most RESCALE_TAU)
             float l_run = 0.f;         // this thread's share of the sum of P'/s (scaled by 2^P_SHIFT)
             float x_max = -INFINITY;   // this thread's share of the maximum of the scaled logits (max_logits output)
@@ -575,87 +670,8 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PAIR_THREADS, 1) att
             }
             if (stop) break;
             TRACE(3, it);
-            // ---- epilogue ---------------------------------------------------------------------
-            {
-                const uint32_t last = it - 1;
-                if (!dead) dead = !mbar_wait_hot(bar(BAR_PVDONE + (last & 1u)), (last >> 1) & 1u, abort_flag, W_PVDONE);
-                tc_fence_after();
-                if (named_bar_or(1 + grp, 128, dead || *abort_flag != 0)) { stop = true; break; }   // the partners have read the last tile's row maxima
-                xch[xpart * 64 + hrow] = l_run;
-                xch[256 + xpart * 64 + hrow] = x_max;
-                named_bar_sync(1 + grp, 128);
-                const float l_all = (xch[hrow] + xch[64 + hrow]) + (xch[128 + hrow] + xch[192 + hrow]);
-                const float xm = fmaxf(fmaxf(xch[256 + hrow], xch[320 + hrow]), fmaxf(xch[384 + hrow], xch[448 + hrow]));
-                float lse = (l_all > 0.f) ? (log2f(l_all) - (float)P_SHIFT + m_run) : NEG_BIG;
-                float denom = l_all;
-                if (w.no_split && p.attn_sink != nullptr && live) {
-                    const float sink2 = p.attn_sink[head] * LOG2E;
-                    denom = l_all + ((m_run == -INFINITY) ? INFINITY : exp2f(sink2 - m_run + (float)P_SHIFT));
-                    if (lse != NEG_BIG) lse += log2f(1.f + exp2f(sink2 - lse));
-                    else lse = sink2;
-                }
-                const float inv = (denom > 0.f) ? 1.f / denom : 0.f;
-                const int col0 = thalf * 256 + ch * 128;      // first output dim of this thread
-                if (w.no_split) {
-                    __nv_bfloat16* dst = p.out + ((size_t)req * p.num_heads + (live ? head : 0)) * D_V + col0;
-#pragma unroll 1
-                    for (int c = 0; c < 128; c += 32) {
-                        uint32_t o[32];
-                        tmem_ld32(lane_addr + TM_O + 128 * ch + c, o);
-                        tmem_wait_ld();
-                        if (live) {
-                            uint32_t pk[16];
-#pragma unroll
-                            for (int i = 0; i < 16; ++i) {
-                                __nv_bfloat162 t = __floats2bfloat162_rn(__uint_as_float(o[2 * i]) * inv, __uint_as_float(o[2 * i + 1]) * inv);
-                                pk[i] = *reinterpret_cast<uint32_t*>(&t);
-                            }
-                            if (wide_out) {
-                                const uint32_t lo8[8] = {pk[0], pk[1], pk[2], pk[3], pk[4], pk[5], pk[6], pk[7]};
-                                const uint32_t hi8[8] = {pk[8], pk[9], pk[10], pk[11], pk[12], pk[13], pk[14], pk[15]};
-                                st_global_v8(dst + c, lo8);
-                                st_global_v8(dst + c + 16, hi8);
-                            } else {
-#pragma unroll
-                                for (int i = 0; i < 4; ++i)
-                                    *reinterpret_cast<uint4*>(dst + c + 8 * i) = make_uint4(pk[4 * i], pk[4 * i + 1], pk[4 * i + 2], pk[4 * i + 3]);
-                            }
-                        }
-                    }
-                    if (live && xpart == 0) {
-                        p.out_lse[(size_t)req * p.num_heads + head] = lse;
-                        if (p.out_max_logits) p.out_max_logits[(size_t)req * p.num_heads + head] = (xm == -INFINITY) ? NEG_BIG : xm;
-                    }
-                } else {
-                    float* dst = p.o_accum + ((size_t)w.split_idx * p.num_heads + (live ? head : 0)) * D_V + col0;
-#pragma unroll 1
-                    for (int c = 0; c < 128; c += 32) {
-                        uint32_t o[32];
-                        tmem_ld32(lane_addr + TM_O + 128 * ch + c, o);
-                        tmem_wait_ld();
-                        if (live) {
-#pragma unroll
-                            for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * inv);
-                            if (wide_acc) {
-#pragma unroll
-                                for (int i = 0; i < 32; i += 8) {
-                                    const uint32_t v8[8] = {o[i], o[i + 1], o[i + 2], o[i + 3], o[i + 4], o[i + 5], o[i + 6], o[i + 7]};
-                                    st_global_v8(dst + c + i, v8);
-                                }
-                            } else {
-#pragma unroll
-                                for (int i = 0; i < 32; i += 4)
-                                    *reinterpret_cast<uint4*>(dst + c + i) = make_uint4(o[i], o[i + 1], o[i + 2], o[i + 3]);
-                            }
-                        }
-                    }
-                    if (live && xpart == 0) p.lse_accum[(size_t)w.split_idx * p.num_heads + head] = lse;
-                }
-                tc_fence_before();                  // the accumulator reads precede the next request's first P.V
-                named_bar_sync(1 + grp, 128);       // xch is free again
-                PROF(12);
-                TRACE(4, it);
-            }
+            prev_valid = true; prev_no_split = w.no_split; prev_req = req; prev_split = w.split_idx;
+            prev_last = it - 1; prev_m = m_run; prev_l = l_run; prev_x = x_max;
         }
     } else if (warp < MMA_WARP) {
         // =================================================================== gather
