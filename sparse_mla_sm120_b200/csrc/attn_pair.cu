@@ -219,10 +219,13 @@ __device__ __forceinline__ int tile_entry(const AttnParams& p, const Work& w, in
     return (j < nst && pos < lim) ? __ldg(p.indices + (size_t)w.req * p.topk + pos) : -1;
 }
 
-// STAGE_Q: the Q rows of a partition's first request come in by one bulk copy (see below).  That pays when the
-// partition has one request or few (decode: 0.7 us of a 54 us step, the rows come from HBM); with many requests per
-// partition (prefill) the instances without it are 7 % faster (the waits it adds to the loops of the gather warps and
-// of the copy thread are never taken after the first tiles, but they are in the loops).
+// STAGE_Q: the Q rows of a partition's first request come in by one bulk copy into shared memory (see below) instead
+// of being read from global memory by the softmax warps (after an L2 prefetch that the copy warps issue as soon as the
+// partition is known).  The copy wins where the kernel follows the scheduler and partitions are short (one request
+// cut into eight partitions: 28.7 against 30.7 us); without a scheduler (whole requests per partition) reading wins or
+// draws: the copy occupies K stage 1 and the V stage until Q is quantised, and the waits it adds to the loops of the
+// gather warps and of the copy thread, never taken after the first tiles, cost prefill 6 % (64 requests 53.7 = 53.9 us,
+// two query tokens per request 98.5 against 102.4, 4096 query tokens 2.24 against 2.37 ms).
 template <int LAYOUT, bool EXTRA, bool STAGE_Q>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PAIR_THREADS, 1) attn_pair_kernel(const AttnParams p) {
     using L = Lay<LAYOUT>;
@@ -311,6 +314,14 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PAIR_THREADS, 1) att
                       bytes, bar(BAR_QSTAGE));
     }
 
+    if (!STAGE_Q && warp >= PROD_WARP0 && meta.begin_req <= last_req) {
+        // no staging: ask L2 for the first request's Q rows now (the copy warps have nothing to do yet); the softmax
+        // warps read them a few thousand cycles from here
+        const uint8_t* q0 = reinterpret_cast<const uint8_t*>(p.q + ((size_t)meta.begin_req * p.num_heads + head0) * L::QD);
+        const int lines = (live_heads * L::QD * 2 + 127) >> 7;
+        for (int i = tid - PROD_WARP0 * 32; i < lines; i += N_P_WARPS * 32)
+            asm volatile("prefetch.global.L2 [%0];" ::"l"(q0 + (size_t)i * 128));
+    }
     if (warp < N_SM_WARPS) setmaxnreg_inc<REGS_SOFTMAX>();
     else if (warp < MMA_WARP) setmaxnreg_dec<REGS_GATHER>();
     else if (warp < PROD_WARP0) setmaxnreg_dec<REGS_MMA>();
@@ -1114,14 +1125,8 @@ bool attn_pair_takes(const AttnParams& p) {
 
 int launch_attn_pair(const AttnParams& p, cudaStream_t stream) {
     if (p.num_tokens == 0) return 0;
-    // Without a scheduler a pair walks ceil(num_tokens / pairs) whole requests: from three on, no staging of the first one's Q.
-    static int sm_count[64] = {};
-    int dev = 0;
-    cudaGetDevice(&dev);
-    if (dev < 0 || dev >= 64) return set_error(SMLA_E_SHAPE, "attn_pair_kernel: device ordinal %d not supported", dev);
-    if (sm_count[dev] == 0) cudaDeviceGetAttribute(&sm_count[dev], cudaDevAttrMultiProcessorCount, dev);
-    const int sms = sm_count[dev];
-    const bool stage = p.sched != nullptr || p.num_tokens <= 2 * (sms >= 2 ? sms / 2 : 1);
+    // Staging of the first request's Q only where the kernel follows the scheduler (see STAGE_Q).
+    const bool stage = p.sched != nullptr;
     if (p.layout == SMLA_LAYOUT_MODEL1) {
         if (p.extra_topk > 0) return stage ? launch_pair_instance<SMLA_LAYOUT_MODEL1, true, true>(p, stream)
                                            : launch_pair_instance<SMLA_LAYOUT_MODEL1, true, false>(p, stream);
