@@ -20,9 +20,14 @@ __device__ __forceinline__ SchedMeta load_meta(const AttnParams& p, int part) {
     } else {
         // no scheduler: the CTA pairs of the grid share the requests as contiguous, whole ranges
         // (one request each when there are at least as many pairs as requests)
-        const long long pairs = gridDim.x >> 1;
-        m.begin_req = (int)((long long)part * p.num_tokens / pairs);
-        m.end_req = (int)((long long)(part + 1) * p.num_tokens / pairs) - 1;
+        const unsigned pairs = gridDim.x >> 1;
+        if ((unsigned long long)pairs * (unsigned)p.num_tokens < 0x100000000ull) {      // 32-bit divisions: every warp of the CTA does this
+            m.begin_req = (int)((unsigned)part * (unsigned)p.num_tokens / pairs);
+            m.end_req = (int)((unsigned)(part + 1) * (unsigned)p.num_tokens / pairs) - 1;
+        } else {
+            m.begin_req = (int)((long long)part * p.num_tokens / pairs);
+            m.end_req = (int)((long long)(part + 1) * p.num_tokens / pairs) - 1;
+        }
         m.begin_block = 0; m.end_block = 0x7fffffff;
         m.begin_split = 0; m.first_split = m.last_split = 0; m.pad = 0;
     }
