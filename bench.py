@@ -44,7 +44,7 @@ WORKLOAD = ("V3.2-shape sparse-MLA decode: b=64/GPU, s_q=1, h_q=128, topk=2048, 
             "KV len U[4096,32768], paged block 64, packed FP8 656 B rows")
 # DRAM bytes of one launch of the attention kernel on this workload's shape, from one ncu capture
 # (dram__bytes_read.sum + dram__bytes_write.sum); the capture's summary is kept with the other profiles.
-NCU_TRAFFIC_BYTES = 90_111_232
+NCU_TRAFFIC_BYTES = 90_347_008
 CPU_SAMPLE_REQUESTS = 64   # requests of one step that the CPU legs compute: the whole step (about 0.13 s on 16 host threads)
 
 
@@ -651,7 +651,19 @@ def run_extras(device, hbm_peak, bf16_peak, peak_kind):
                                             "262144-token pool; CUDA graph replay of the whole step on the tensor-core kernel "
                                             "(impl=IMPL_TC; the default for this layout is the exact fp32 kernel)",
                                 "exact_fp32_kernel_us_per_step": exact_ms * 1e3, **res}
-        del pool1, epool, qm, im, ie
+        # prefill of the C3 shape over the same layout: 4096 query tokens, causal top-k over 8192 rows
+        pool_p = m1_pool(128)
+        qp = torch.randn((4096, HEADS, 512), device=device, generator=g).to(torch.bfloat16)
+        ip = torch.stack([torch.randperm(4096 + i, device=device, generator=g)[:TOPK] for i in range(4096)]).to(torch.int32)
+        ms_p = _time_cuda(lambda: flash_ops.sparse_mla_prefill_fwd(qp, pool_p, ip, 512 ** -0.5, impl=2), 5)
+        fl_p = 2.0 * 4096 * HEADS * TOPK * (512 + D_V)
+        out["prefill_model1"] = {
+            "workload": "s_q=4096, h=128, topk=2048 over a MODEL1 cache of 8192 rows, causal top-k; tensor-core kernel (impl=IMPL_TC)",
+            "ms": ms_p, "tflops": fl_p / ms_p / 1e9,
+            "roofline": {"bound": "tensor", "kernel": "attn_pair_kernel", "achieved": fl_p / ms_p / 1e9, "peak": bf16_peak,
+                         "unit": "TFLOP/s", "frac": fl_p / ms_p / 1e9 / bf16_peak, "peak_kind": f"of {peak_kind} (dense BF16)",
+                         "traffic": None}}
+        del pool1, epool, qm, im, ie, pool_p, qp, ip
     except Exception as e:           # noqa: BLE001
         out["decode_model1"] = {"error": repr(e)}
     # ---- indexer: q e4m3 [4096, 64, 128], k e4m3 [65536, 128], ke = 61440 + i, then top-2048 per row
@@ -860,13 +872,19 @@ def run_small_case(name):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=3000)
-    ap.add_argument("--warmup", type=int, default=50)
+    ap.add_argument("--steps", type=int, default=None, help="timed steps (default 3000; 20 for --impl reference)")
+    ap.add_argument("--warmup", type=int, default=None, help="untimed steps before them (default 50; 3 for --impl reference)")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-extras", action="store_true")
     ap.add_argument("--case", default=None, choices=["decode", "prefill", "indexer"],
                     help="run a small instance of a secondary kernel (for profiler captures) instead of the benchmark")
     args = ap.parse_args()
+    # a step of the reference arm is about 0.13 s of host work: its default run is 20 steps, so that both arms finish
+    # within minutes when called without flags
+    if args.steps is None:
+        args.steps = 20 if args.impl == "reference" else 3000
+    if args.warmup is None:
+        args.warmup = 3 if args.impl == "reference" else 50
     args.warmup = max(args.warmup, 3)
     if args.case is not None:
         run_small_case(args.case)
