@@ -593,7 +593,7 @@ def run_extras(device, hbm_peak, bf16_peak, peak_kind):
         # ---- small decode batches of the same shape (the split-KV path: scheduler + attention + combine as
         # dependent launches), CUDA-graph replay
         small = {}
-        for bsz in (1, 8, 32):
+        for bsz in (1, 8, 16, 32, 48):
             qs_, is_ = sets[0][0][:bsz].contiguous(), sets[0][1][:bsz].contiguous()
             runb = lambda: flash_ops.sparse_mla_decode_fwd(qs_, pool, is_, SM_SCALE)
             runb(); torch.cuda.synchronize()
@@ -606,7 +606,8 @@ def run_extras(device, hbm_peak, bf16_peak, peak_kind):
             us = _time_cuda(gb.replay, 200, warm=5) * 1e3
             small[f"b{bsz}"] = {"us_per_step": us, "gbs": algorithmic_bytes(bsz, TOPK) / us / 1e3}
             del gb
-        out["decode_small_batches"] = {"workload": "the headline's decode shape at 1, 8 and 32 requests (rows of the first input set)",
+        out["decode_small_batches"] = {"workload": "the headline's decode shape at 1, 8, 16, 32 and 48 requests (rows of the first input set); "
+                                                   "the op's own split policy: equal partitions per request up to 32 requests, unsplit from 37",
                                        **small}
         del pool, sets, q2, i2
     except Exception as e:           # noqa: BLE001 - a secondary measurement must not take the others down

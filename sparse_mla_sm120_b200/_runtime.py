@@ -119,23 +119,59 @@ BLOCKS_PER_PARTITION = 4  # a partition should be worth at least two 128-token t
 
 
 def pick_num_sm_parts(num_tokens: int, sms: int, blocks_per_token: Optional[int] = None) -> int:
-    """Partitions for the split-KV scheduler.
+    """Partitions for the split-KV scheduler when nothing is known about the requests' lengths (or they differ).
 
-    A partition is served by two CTAs, so at most sms // 2 partitions run at once.  When whole
-    requests already fill the machine to >= 80 % in full waves they are left unsplit (one
-    partition per token: no partial outputs, no combine traffic); otherwise the work is cut into
-    up to sms // 2 partitions, but not into partitions of fewer than BLOCKS_PER_PARTITION 64-token
-    blocks (every extra partition is a partial output that the combine has to read back: one
-    request of top-k 2048 is fastest in 8 partitions, 27 us, against 38 us in 74)."""
+    A partition is served by two CTAs, so at most sms // 2 partitions run at once.  When whole requests already
+    fill half of the machine in full waves they are left unsplit (one partition per token: no partial outputs, no
+    combine traffic; 40 requests of top-k 2048: 48 us unsplit, 64 us cut into 74 partitions that mostly straddle two
+    requests).  Otherwise the work is cut into up to sms // 2 partitions, but not into partitions of fewer than
+    BLOCKS_PER_PARTITION 64-token blocks (every extra partition is a partial output that the combine has to read
+    back: one request of top-k 2048 is fastest in 8 partitions, 27 us, against 38 us in 74)."""
     max_parts = max(sms // CTAS_PER_PART, 1)
     ctas = num_tokens * CTAS_PER_PART
     waves = -(-ctas // sms)
-    if ctas / (waves * sms) >= 0.8:
+    if ctas / (waves * sms) >= 0.5:
         return num_tokens
     if blocks_per_token is None:
         return max_parts
     want = -(-(num_tokens * max(blocks_per_token, 1)) // BLOCKS_PER_PARTITION)
     return max(num_tokens, min(max_parts, want))
+
+
+# Cost model of a decode step at 128 heads on a B200, microseconds (fitted to measurements of 12 to 48 requests of
+# top-k 2048 in 1, 2 and 4 partitions each; it reproduces them to about 1 us): a partition pays a fixed part (set-up,
+# Q quantisation, epilogue) and its 128-token tiles; a split step pays for every partial record, which is written and
+# read back once, and at least the latency of the scheduler and combine launches.
+_US_FIXED, _US_TILE, _US_RECORD, _US_SPLIT_MIN = 11.3, 2.3, 0.28, 9.0
+
+
+def pick_split(num_tokens: int, sms: int, blocks_per_token: Optional[int] = None, uniform: bool = False) -> Tuple[int, int]:
+    """(partitions, fixed overhead) to give the scheduler.
+
+    When every request has the same number of blocks (no ``topk_length``), the requests can be cut into k equal
+    partitions each, k a divisor of the block count, by asking the scheduler for k * tokens partitions with a fixed
+    overhead of 0: no partition then straddles two requests, i.e. none pays the fixed part of a partition twice.
+    k is chosen by the cost model above (k = 1: nothing is split, the attention kernel runs alone).  Otherwise
+    (lengths differ or are unknown) the choice is pick_num_sm_parts with the reference's fixed overhead."""
+    if not uniform or blocks_per_token is None:
+        return pick_num_sm_parts(num_tokens, sms, blocks_per_token), FIXED_OVERHEAD
+    max_parts = max(sms // CTAS_PER_PART, 1)
+    n = max(blocks_per_token, 1)
+    waves = -(-num_tokens // max_parts)
+    best = (waves * (_US_FIXED + -(-n // 2) * _US_TILE), num_tokens, FIXED_OVERHEAD)
+    cuts = 0
+    for k in range(2, n + 1):
+        if n % k or k * num_tokens > max_parts or n // k < BLOCKS_PER_PARTITION:
+            continue
+        cuts += 1
+        t = _US_FIXED + -(-(n // k) // 2) * _US_TILE + max(_US_SPLIT_MIN, _US_RECORD * k * num_tokens)
+        if t < best[0]:
+            best = (t, k * num_tokens, 0)
+    if cuts == 0 and n >= 2 * BLOCKS_PER_PARTITION:
+        # no equal cut exists although the requests are long enough to be worth cutting (a block count without a
+        # suitable divisor, or too many requests for two partitions each): the general rule
+        return pick_num_sm_parts(num_tokens, sms, blocks_per_token), FIXED_OVERHEAD
+    return best[1], best[2]
 
 
 _SCRATCH_LIMIT = 64      # cached call shapes per process before the least recently used one is dropped

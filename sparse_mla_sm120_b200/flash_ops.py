@@ -18,9 +18,8 @@ import torch
 
 from . import _lib
 from ._lib import IMPL_AUTO, IMPL_SCALAR, LAYOUT_MODEL1, LAYOUT_V32, check
-from ._runtime import (BLOCK_N, FIXED_OVERHEAD, kv_geometry, kv_layout, num_sms, pick_num_sm_parts,
-                       pick_num_sm_parts_fp32, ptr, require_cuda, resolve_impl, scratch, status_buffer, stream_ptr,
-                       tc_aligned)
+from ._runtime import (BLOCK_N, FIXED_OVERHEAD, kv_geometry, kv_layout, num_sms, pick_num_sm_parts_fp32, pick_split, ptr,
+                       require_cuda, resolve_impl, scratch, status_buffer, stream_ptr, tc_aligned)
 
 
 def _check_q(q: torch.Tensor):
@@ -179,10 +178,14 @@ def sparse_mla_decode_fwd(
     use_ext = layout != LAYOUT_V32 or ex.topk > 0
     blocks = max(-(-topk // BLOCK_N), 1) + -(-ex.topk // BLOCK_N)
 
+    fixed_overhead = FIXED_OVERHEAD
     if num_sm_parts is None:
         fp32 = use_ext and (impl == IMPL_SCALAR or not tc_aligned(kv_cache, ex.kv))
-        num_sm_parts = (pick_num_sm_parts_fp32(num_tokens, num_heads, num_sms(q.device)) if fp32
-                        else pick_num_sm_parts(num_tokens, num_sms(q.device), blocks))
+        if fp32:
+            num_sm_parts = pick_num_sm_parts_fp32(num_tokens, num_heads, num_sms(q.device))
+        else:   # requests of equal length (no topk_length, no second cache) may be cut into equal partitions
+            num_sm_parts, fixed_overhead = pick_split(num_tokens, num_sms(q.device), blocks,
+                                                      uniform=topk_length is None and ex.topk == 0)
     lib = _lib.load()
     stream = stream_ptr(q.device)
     if out is not None:
@@ -199,7 +202,7 @@ def sparse_mla_decode_fwd(
                 ex.block, ex.stride, ptr(attn_sink), ptr(topk_length), ptr(ex.length), impl, st, stream))
             return output, out_lse
         ws = scratch(q.device, num_tokens + num_sm_parts, num_heads, num_tokens, num_sm_parts)
-        check(lib.smla_sched_meta(num_tokens, topk, ex.topk, num_sm_parts, FIXED_OVERHEAD, ptr(topk_length),
+        check(lib.smla_sched_meta(num_tokens, topk, ex.topk, num_sm_parts, fixed_overhead, ptr(topk_length),
                                   ptr(ex.length), ptr(ws["sched_meta"]), ptr(ws["num_splits"]), stream))
         check(lib.smla_decode_splitkv_ext(
             ptr(q), ptr(kv_cache), ptr(indices), ptr(ex.kv), ptr(ex.indices), ptr(ws["o_accum"]),
@@ -220,7 +223,7 @@ def sparse_mla_decode_fwd(
         return output, out_lse
     total_splits = num_tokens + num_sm_parts
     ws = scratch(q.device, total_splits, num_heads, num_tokens, num_sm_parts)
-    check(lib.smla_sched_meta(num_tokens, topk, 0, num_sm_parts, FIXED_OVERHEAD, ptr(topk_length), None,
+    check(lib.smla_sched_meta(num_tokens, topk, 0, num_sm_parts, fixed_overhead, ptr(topk_length), None,
                               ptr(ws["sched_meta"]), ptr(ws["num_splits"]), stream))
     check(lib.smla_decode_splitkv(
         ptr(q), ptr(kv_cache), ptr(indices), ptr(ws["o_accum"]), ptr(ws["lse_accum"]), ptr(output), ptr(out_lse),

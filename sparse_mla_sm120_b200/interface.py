@@ -25,7 +25,7 @@ import torch
 
 from . import _lib
 from ._lib import IMPL_AUTO, IMPL_SCALAR, LAYOUT_V32, check
-from ._runtime import (BLOCK_N, FIXED_OVERHEAD, kv_geometry, num_sms, pick_num_sm_parts, pick_num_sm_parts_fp32, ptr,
+from ._runtime import (BLOCK_N, FIXED_OVERHEAD, kv_geometry, num_sms, pick_num_sm_parts_fp32, pick_split, ptr,
                        require_cuda, resolve_impl, status_buffer, stream_ptr, tc_aligned)
 from .flash_ops import _check_q, _Extra, _layout, sparse_mla_prefill_fwd
 
@@ -128,13 +128,17 @@ def flash_mla_with_kvcache(
         meta.have_initialized = True
         meta.config = cfg
         fp32 = use_ext and (impl == IMPL_SCALAR or not tc_aligned(k_cache, ex.kv))
-        meta.num_sm_parts = (pick_num_sm_parts_fp32(num_tokens, num_heads, num_sms(q.device)) if fp32
-                             else pick_num_sm_parts(num_tokens, num_sms(q.device), blocks))
+        fixed_overhead = FIXED_OVERHEAD
+        if fp32:
+            meta.num_sm_parts = pick_num_sm_parts_fp32(num_tokens, num_heads, num_sms(q.device))
+        else:
+            meta.num_sm_parts, fixed_overhead = pick_split(num_tokens, num_sms(q.device), blocks,
+                                                           uniform=topk_length is None and ex.topk == 0)
         meta.max_nsplits = min(blocks, meta.num_sm_parts)
         if meta.num_sm_parts != num_tokens:
             meta.tile_scheduler_metadata = torch.empty(meta.num_sm_parts * 8, dtype=torch.int32, device=q.device)
             meta.num_splits = torch.empty(num_tokens + 1, dtype=torch.int32, device=q.device)
-            check(lib.smla_sched_meta(num_tokens, topk, ex.topk, meta.num_sm_parts, FIXED_OVERHEAD, ptr(topk_length),
+            check(lib.smla_sched_meta(num_tokens, topk, ex.topk, meta.num_sm_parts, fixed_overhead, ptr(topk_length),
                                       ptr(ex.length), ptr(meta.tile_scheduler_metadata), ptr(meta.num_splits), stream))
             records = num_tokens + meta.num_sm_parts
             meta.o_accum = torch.empty((records, 1, num_heads, head_dim_v), dtype=torch.float32, device=q.device)

@@ -89,16 +89,29 @@ def test_model1_default_impl():
 
 
 def test_split_policy():
-    from sparse_mla_sm120_b200._runtime import pick_num_sm_parts
+    from sparse_mla_sm120_b200._runtime import FIXED_OVERHEAD, pick_num_sm_parts, pick_split
+    # lengths unknown or different: the general rule
     assert pick_num_sm_parts(64, 148) == 64      # 128 CTAs on 148 SMs: unsplit
     assert pick_num_sm_parts(128, 148) == 128    # two nearly full waves: unsplit
+    assert pick_num_sm_parts(40, 148) == 40      # more than half of the machine: unsplit
     assert pick_num_sm_parts(1, 148) == 74       # small batch, top-k unknown: cut into sms/2 partitions
-    assert pick_num_sm_parts(80, 148) == 74
+    assert pick_num_sm_parts(36, 148) == 74
     # with the top-k known, no partition gets fewer than four 64-token blocks
     assert pick_num_sm_parts(1, 148, 32) == 8
     assert pick_num_sm_parts(4, 148, 32) == 32
     assert pick_num_sm_parts(16, 148, 32) == 74
     assert pick_num_sm_parts(4, 148, 1) == 4     # nothing worth splitting: one partition per request, attention kernel alone
+    assert pick_split(16, 148, 32, uniform=False) == (74, FIXED_OVERHEAD)
+    # requests of equal length: k equal partitions each (fixed overhead 0 keeps them from straddling two requests)
+    assert pick_split(1, 148, 32, uniform=True) == (8, 0)
+    assert pick_split(8, 148, 32, uniform=True) == (32, 0)     # four partitions each: eight would double the partial records
+    assert pick_split(16, 148, 32, uniform=True) == (64, 0)
+    assert pick_split(32, 148, 32, uniform=True) == (64, 0)
+    assert pick_split(40, 148, 32, uniform=True)[0] == 40      # unsplit
+    assert pick_split(64, 148, 32, uniform=True)[0] == 64
+    assert pick_split(128, 148, 32, uniform=True)[0] == 128
+    assert pick_split(4, 148, 8, uniform=True)[0] == 4         # short requests: not worth the scheduler and combine launches
+    assert pick_split(4, 148, 31, uniform=True) == (31, FIXED_OVERHEAD)   # no divisor: the general rule
 
 
 def test_flashmla_surface_argument_checks():
