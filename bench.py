@@ -607,7 +607,7 @@ def run_extras(device, hbm_peak, bf16_peak, peak_kind):
             small[f"b{bsz}"] = {"us_per_step": us, "gbs": algorithmic_bytes(bsz, TOPK) / us / 1e3}
             del gb
         out["decode_small_batches"] = {"workload": "the headline's decode shape at 1, 8, 16, 32 and 48 requests (rows of the first input set); "
-                                                   "the op's own split policy: equal partitions per request up to 32 requests, unsplit from 37",
+                                                   "the op's own split policy: k equal partitions per request without a scheduler launch up to 37 requests, unsplit beyond",
                                        **small}
         del pool, sets, q2, i2
     except Exception as e:           # noqa: BLE001 - a secondary measurement must not take the others down

@@ -114,6 +114,20 @@ int smla_decode_splitkv(const void* q, const void* kv, const int32_t* indices,
                         int impl, int32_t* status, void* stream);
 
 /*
+ * Split-KV decode of requests that all have `topk` entries (no topk_length), every request cut into
+ * parts_per_request equal partitions (a divisor of ceil(topk / 64)): what smla_sched_meta would lay out for
+ * parts_per_request * num_tokens partitions and a fixed overhead of 0, derived inside the attention kernel, so that
+ * the step is two launches (attention, combine) instead of three.  o_accum / lse_accum hold
+ * parts_per_request * num_tokens records (partition j of request r is record j * num_tokens + r).  tcgen05 kernel
+ * only.  No counterpart in the reference (its scheduler kernel runs every step, flash_mla_sm120/ops.py:78-99).
+ */
+int smla_decode_uniform(const void* q, const void* kv, const int32_t* indices,
+                        float* o_accum, float* lse_accum, void* out, float* out_lse,
+                        int num_tokens, int num_heads, int topk, float sm_scale,
+                        int page_block_size, int64_t kv_block_stride_bytes, int parts_per_request,
+                        const float* attn_sink, int impl, int32_t* status, void* stream);
+
+/*
  * LSE-weighted merge of the split partials.  Replaces sparse_mla_combine_v2_fwd
  * (csrc/binding.cpp:166-183, kernel csrc/kernel/combine/combine_kernel.cu:39-159).
  * Requests with <= 1 split are left untouched.  max_nsplits <= 1024.

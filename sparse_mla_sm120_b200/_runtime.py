@@ -138,11 +138,11 @@ def pick_num_sm_parts(num_tokens: int, sms: int, blocks_per_token: Optional[int]
     return max(num_tokens, min(max_parts, want))
 
 
-# Cost model of a decode step at 128 heads on a B200, microseconds (fitted to measurements of 12 to 48 requests of
-# top-k 2048 in 1, 2 and 4 partitions each; it reproduces them to about 1 us): a partition pays a fixed part (set-up,
-# Q quantisation, epilogue) and its 128-token tiles; a split step pays for every partial record, which is written and
-# read back once, and at least the latency of the scheduler and combine launches.
-_US_FIXED, _US_TILE, _US_RECORD, _US_SPLIT_MIN = 11.3, 2.3, 0.28, 9.0
+# Cost model of a decode step at 128 heads on a B200, microseconds (fitted to measurements of 4 to 48 requests of
+# top-k 2048 in 1, 2, 4 and 8 equal partitions each; it reproduces them to about 1 us): a partition pays a fixed part
+# (set-up, Q quantisation, epilogue) and its 128-token tiles; a split step pays for every partial record, which is
+# written and read back once, and at least the latency of the combine launch.
+_US_FIXED, _US_TILE, _US_RECORD, _US_SPLIT_MIN = 11.3, 2.3, 0.2, 7.5
 
 
 def pick_split(num_tokens: int, sms: int, blocks_per_token: Optional[int] = None, uniform: bool = False) -> Tuple[int, int]:

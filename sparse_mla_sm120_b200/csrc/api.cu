@@ -133,6 +133,36 @@ int smla_decode_splitkv(const void* q, const void* kv, const int32_t* indices,
     return launch_attn_pair(p, (cudaStream_t)stream);
 }
 
+int smla_decode_uniform(const void* q, const void* kv, const int32_t* indices,
+                        float* o_accum, float* lse_accum, void* out, float* out_lse,
+                        int num_tokens, int num_heads, int topk, float sm_scale,
+                        int page_block_size, int64_t kv_block_stride_bytes, int parts_per_request,
+                        const float* attn_sink, int impl, int32_t* status, void* stream) {
+    if (int e = check_attn_common("smla_decode_uniform", q, kv, indices, out, out_lse, num_tokens, num_heads,
+                                  topk, page_block_size, kv_block_stride_bytes, impl)) return e;
+    if (impl == SMLA_IMPL_SCALAR)
+        return set_error(SMLA_E_SHAPE, "smla_decode_uniform: the fp32 kernel needs the scheduler's records (use smla_decode_splitkv)");
+    if (!o_accum || !lse_accum) return set_error(SMLA_E_NULL, "smla_decode_uniform: null scratch pointer");
+    if (!aligned16(o_accum)) return set_error(SMLA_E_ALIGN, "smla_decode_uniform: o_accum not 16-byte aligned");
+    const int blocks = (topk + BLOCK_N - 1) / BLOCK_N;
+    if (parts_per_request < 2 || blocks % parts_per_request != 0)
+        return set_error(SMLA_E_SHAPE, "smla_decode_uniform: %d blocks per request do not divide into %d partitions", blocks,
+                         parts_per_request);
+    if (num_tokens == 0) return SMLA_OK;
+    if ((int64_t)num_tokens * parts_per_request > (1 << 20))
+        return set_error(SMLA_E_SHAPE, "smla_decode_uniform: %d x %d partitions", num_tokens, parts_per_request);
+    AttnParams p{};
+    p.q = (const __nv_bfloat16*)q; p.kv = (const uint8_t*)kv; p.indices = indices;
+    p.o_accum = o_accum; p.lse_accum = lse_accum; p.out = (__nv_bfloat16*)out; p.out_lse = out_lse;
+    p.attn_sink = attn_sink; p.status = status;
+    p.num_tokens = num_tokens; p.num_heads = num_heads; p.topk = topk; p.num_parts = num_tokens * parts_per_request;
+    p.page_block_size = page_block_size; p.block_stride = kv_block_stride_bytes; p.sm_scale = sm_scale;
+    p.uniform_k = parts_per_request;
+    if (int e = launch_attn_pair(p, (cudaStream_t)stream)) return e;
+    return launch_combine_parts(o_accum, lse_accum, (__nv_bfloat16*)out, out_lse, parts_per_request, num_tokens, num_heads,
+                                0, 0, attn_sink, (cudaStream_t)stream);
+}
+
 int smla_combine(const float* o_accum, const float* lse_accum, void* out, float* out_lse,
                  const int32_t* num_splits, int batch, int num_heads, int max_nsplits,
                  const float* attn_sink, void* stream) {

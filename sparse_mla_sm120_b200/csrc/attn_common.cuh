@@ -17,6 +17,14 @@ __device__ __forceinline__ SchedMeta load_meta(const AttnParams& p, int part) {
     SchedMeta m;
     if (p.sched != nullptr) {
         m = p.sched[part];
+    } else if (p.uniform_k > 1) {
+        // no scheduler, requests of equal length: pair `part` owns partition part % k of request part / k, which is
+        // what the scheduler would say for k * num_tokens partitions and no fixed overhead
+        const int k = p.uniform_k, req = part / k, j = part - req * k;
+        const int per = max((p.topk + BLOCK_N - 1) / BLOCK_N, 1) / k;
+        m.begin_req = m.end_req = req;
+        m.begin_block = j * per; m.end_block = (j + 1) * per;
+        m.begin_split = j * p.num_tokens + req; m.first_split = m.last_split = 1; m.pad = 0;
     } else {
         // no scheduler: the CTA pairs of the grid share the requests as contiguous, whole ranges
         // (one request each when there are at least as many pairs as requests)
@@ -51,7 +59,7 @@ __device__ __forceinline__ bool get_work(const AttnParams& p, const SchedMeta& m
     w.req = req; w.blk0 = b0; w.nblk = b1 - b0; w.len = len;
     w.no_split = !p.force_partial &&
                  ((req == m.begin_req) ? !m.first_split : ((req == m.end_req) ? !m.last_split : true));
-    w.split_idx = p.num_splits ? p.num_splits[req] + ((req == m.begin_req) ? m.begin_split : 0) : 0;
+    w.split_idx = (p.num_splits ? p.num_splits[req] : 0) + ((req == m.begin_req) ? m.begin_split : 0);
     return w.nblk > 0;
 }
 

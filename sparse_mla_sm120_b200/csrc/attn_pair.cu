@@ -1105,7 +1105,8 @@ int launch_pair_instance(const AttnParams& p, cudaStream_t stream) {
     }
     // Without a scheduler the grid is persistent: at most one CTA per SM, each pair walks its share of the requests.
     const int max_pairs = sm_count[dev] >= 2 ? sm_count[dev] / 2 : 1;
-    const int parts = p.sched ? p.num_parts : (p.num_tokens < max_pairs ? p.num_tokens : max_pairs);
+    const int parts = p.sched ? p.num_parts : p.uniform_k > 1 ? p.uniform_k * p.num_tokens
+                                                              : (p.num_tokens < max_pairs ? p.num_tokens : max_pairs);
     if (p.sched != nullptr)      // the scheduler kernel runs just before: start while it finishes
         launch_dependent(attn_pair_kernel<LAYOUT, EXTRA, STAGE_Q>, dim3(2 * parts), dim3(PAIR_THREADS), SMEM_ALLOC, stream, p);
     else
@@ -1126,7 +1127,7 @@ bool attn_pair_takes(const AttnParams& p) {
 int launch_attn_pair(const AttnParams& p, cudaStream_t stream) {
     if (p.num_tokens == 0) return 0;
     // Staging of the first request's Q only where the kernel follows the scheduler (see STAGE_Q).
-    const bool stage = p.sched != nullptr;
+    const bool stage = p.sched != nullptr || p.uniform_k > 1;      // short partitions
     if (p.layout == SMLA_LAYOUT_MODEL1) {
         if (p.extra_topk > 0) return stage ? launch_pair_instance<SMLA_LAYOUT_MODEL1, true, true>(p, stream)
                                            : launch_pair_instance<SMLA_LAYOUT_MODEL1, true, false>(p, stream);

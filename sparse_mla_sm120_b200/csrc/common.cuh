@@ -45,6 +45,8 @@ struct AttnParams {
     int32_t* status;             // device int32[4] or null
     int num_tokens, num_heads, topk, num_parts;
     int force_partial;           // 1: every request writes an fp32 partial record, none writes `out`
+    int uniform_k;               // > 1 (no scheduler, all requests topk long): every request is cut into uniform_k equal
+                                 // partitions, partition j of request r writes partial record j * num_tokens + r
     int page_block_size;
     int64_t block_stride;        // bytes between pages
     float sm_scale;

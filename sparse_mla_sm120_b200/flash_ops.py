@@ -223,6 +223,15 @@ def sparse_mla_decode_fwd(
         return output, out_lse
     total_splits = num_tokens + num_sm_parts
     ws = scratch(q.device, total_splits, num_heads, num_tokens, num_sm_parts)
+    if (fixed_overhead == 0 and topk_length is None and impl != IMPL_SCALAR and num_sm_parts % num_tokens == 0
+            and blocks % (num_sm_parts // num_tokens) == 0):
+        # requests of equal length in equal partitions: the attention kernel derives the schedule itself, the step is
+        # two launches (attention, combine)
+        check(lib.smla_decode_uniform(
+            ptr(q), ptr(kv_cache), ptr(indices), ptr(ws["o_accum"]), ptr(ws["lse_accum"]), ptr(output), ptr(out_lse),
+            num_tokens, num_heads, topk, float(sm_scale), page_block_size, page_stride, num_sm_parts // num_tokens,
+            ptr(attn_sink), impl, ptr(status_buffer(q.device)), stream))
+        return output, out_lse
     check(lib.smla_sched_meta(num_tokens, topk, 0, num_sm_parts, fixed_overhead, ptr(topk_length), None,
                               ptr(ws["sched_meta"]), ptr(ws["num_splits"]), stream))
     check(lib.smla_decode_splitkv(

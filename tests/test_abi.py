@@ -107,6 +107,7 @@ def test_split_policy():
     assert pick_split(8, 148, 32, uniform=True) == (32, 0)     # four partitions each: eight would double the partial records
     assert pick_split(16, 148, 32, uniform=True) == (64, 0)
     assert pick_split(32, 148, 32, uniform=True) == (64, 0)
+    assert pick_split(37, 148, 32, uniform=True) == (74, 0)    # two partitions each still fit the machine
     assert pick_split(40, 148, 32, uniform=True)[0] == 40      # unsplit
     assert pick_split(64, 148, 32, uniform=True)[0] == 64
     assert pick_split(128, 148, 32, uniform=True)[0] == 128
