@@ -117,8 +117,9 @@ int smla_decode_splitkv(const void* q, const void* kv, const int32_t* indices,
  * Split-KV decode of requests that all have `topk` entries (no topk_length), every request cut into
  * parts_per_request equal partitions (a divisor of ceil(topk / 64)): what smla_sched_meta would lay out for
  * parts_per_request * num_tokens partitions and a fixed overhead of 0, derived inside the attention kernel, so that
- * the step is two launches (attention, combine) instead of three.  o_accum / lse_accum hold
- * parts_per_request * num_tokens records (partition j of request r is record j * num_tokens + r).  tcgen05 kernel
+ * the step is two launches (attention, combine) instead of three.  o_accum / lse_accum are scratch for
+ * parts_per_request * num_tokens records (partition j of request r is record j * num_tokens + r; the call keeps
+ * the partial outputs in fp16 there, so o_accum needs half of what its type says, its contents are private).  tcgen05 kernel
  * only.  No counterpart in the reference (its scheduler kernel runs every step, flash_mla_sm120/ops.py:78-99).
  */
 int smla_decode_uniform(const void* q, const void* kv, const int32_t* indices,

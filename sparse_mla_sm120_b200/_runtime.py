@@ -142,7 +142,7 @@ def pick_num_sm_parts(num_tokens: int, sms: int, blocks_per_token: Optional[int]
 # top-k 2048 in 1, 2, 4 and 8 equal partitions each; it reproduces them to about 1 us): a partition pays a fixed part
 # (set-up, Q quantisation, epilogue) and its 128-token tiles; a split step pays for every partial record, which is
 # written and read back once, and at least the latency of the combine launch.
-_US_FIXED, _US_TILE, _US_RECORD, _US_SPLIT_MIN = 11.3, 2.3, 0.2, 7.5
+_US_FIXED, _US_TILE, _US_RECORD, _US_SPLIT_MIN = 11.3, 2.3, 0.15, 8.0
 
 
 def pick_split(num_tokens: int, sms: int, blocks_per_token: Optional[int] = None, uniform: bool = False) -> Tuple[int, int]:

@@ -159,8 +159,8 @@ int smla_decode_uniform(const void* q, const void* kv, const int32_t* indices,
     p.page_block_size = page_block_size; p.block_stride = kv_block_stride_bytes; p.sm_scale = sm_scale;
     p.uniform_k = parts_per_request;
     if (int e = launch_attn_pair(p, (cudaStream_t)stream)) return e;
-    return launch_combine_parts(o_accum, lse_accum, (__nv_bfloat16*)out, out_lse, parts_per_request, num_tokens, num_heads,
-                                0, 0, attn_sink, (cudaStream_t)stream);
+    return launch_combine_parts_f16(o_accum, lse_accum, (__nv_bfloat16*)out, out_lse, parts_per_request, num_tokens,
+                                    num_heads, attn_sink, (cudaStream_t)stream);
 }
 
 int smla_combine(const float* o_accum, const float* lse_accum, void* out, float* out_lse,

@@ -539,6 +539,36 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PAIR_THREADS, 1) att
                         p.out_lse[(size_t)prev_req * p.num_heads + head] = lse;
                         if (p.out_max_logits) p.out_max_logits[(size_t)prev_req * p.num_heads + head] = (xm == -INFINITY) ? NEG_BIG : xm;
                     }
+                } else if (p.uniform_k > 1) {
+                    // partial records in fp16 (the scratch is this library's own in this mode): half the bytes to write
+                    // here and to read in the combine; a normalised partial is bounded by the largest |V|, and its
+                    // fp16 rounding (2^-11) is an eighth of the bf16 rounding of the final output
+                    __half* dst = reinterpret_cast<__half*>(p.o_accum) + ((size_t)prev_split * p.num_heads + (live ? head : 0)) * D_V + col0;
+#pragma unroll 1
+                    for (int c = 0; c < 128; c += 32) {
+                        uint32_t o[32];
+                        tmem_ld32(lane_addr + TM_O + 128 * ch + c, o);
+                        tmem_wait_ld();
+                        if (live) {
+                            uint32_t pk[16];
+#pragma unroll
+                            for (int i = 0; i < 16; ++i) {
+                                const __half2 t = __floats2half2_rn(__uint_as_float(o[2 * i]) * inv, __uint_as_float(o[2 * i + 1]) * inv);
+                                pk[i] = *reinterpret_cast<const uint32_t*>(&t);
+                            }
+                            if (wide_acc) {
+                                const uint32_t lo8[8] = {pk[0], pk[1], pk[2], pk[3], pk[4], pk[5], pk[6], pk[7]};
+                                const uint32_t hi8[8] = {pk[8], pk[9], pk[10], pk[11], pk[12], pk[13], pk[14], pk[15]};
+                                st_global_v8(dst + c, lo8);
+                                st_global_v8(dst + c + 16, hi8);
+                            } else {
+#pragma unroll
+                                for (int i = 0; i < 4; ++i)
+                                    *reinterpret_cast<uint4*>(dst + c + 8 * i) = make_uint4(pk[4 * i], pk[4 * i + 1], pk[4 * i + 2], pk[4 * i + 3]);
+                            }
+                        }
+                    }
+                    if (live && xpart == 0) p.lse_accum[(size_t)prev_split * p.num_heads + head] = lse;
                 } else {
                     float* dst = p.o_accum + ((size_t)prev_split * p.num_heads + (live ? head : 0)) * D_V + col0;
 #pragma unroll 1

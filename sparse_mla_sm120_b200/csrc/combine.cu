@@ -19,9 +19,17 @@ constexpr int WARPS = 8;
 // skipped unless OutT is float (then the single record is passed through).  Strided
 // (num_splits == null): every token has fixed_ns parts and part g of token t is record
 // g * batch + t, the layout an all-gather of per-GPU [T, H, 512] partials produces.
-template <typename OutT>
+// Four consecutive values of a partial record as fp32 (records are fp32, or fp16 where the attention kernel wrote them so).
+__device__ __forceinline__ float4 load4(const float* p) { return __ldcs(reinterpret_cast<const float4*>(p)); }
+__device__ __forceinline__ float4 load4(const __half* p) {
+    const uint2 v = __ldcs(reinterpret_cast<const uint2*>(p));
+    const float2 a = __half22float2(*reinterpret_cast<const __half2*>(&v.x)), b = __half22float2(*reinterpret_cast<const __half2*>(&v.y));
+    return make_float4(a.x, a.y, b.x, b.y);
+}
+
+template <typename OutT, typename InT = float>
 __global__ void __launch_bounds__(WARPS * 32)
-combine_kernel(const float* __restrict__ o_accum, const float* __restrict__ lse_accum,
+combine_kernel(const InT* __restrict__ o_accum, const float* __restrict__ lse_accum,
                OutT* __restrict__ out, float* __restrict__ out_lse,
                const int32_t* __restrict__ num_splits, const float* __restrict__ attn_sink,
                int batch, int num_heads, int fixed_ns, int64_t part_stride_o, int64_t part_stride_l,
@@ -48,7 +56,7 @@ combine_kernel(const float* __restrict__ o_accum, const float* __restrict__ lse_
     const size_t o_stride = (num_splits == nullptr && part_stride_o > 0) ? (size_t)part_stride_o : rec_stride * num_heads * D_V;
     const size_t l_stride = (num_splits == nullptr && part_stride_l > 0) ? (size_t)part_stride_l : rec_stride * num_heads;
     const float* lse_p = lse_accum + (size_t)s0 * num_heads + h;
-    const float* o_p = o_accum + (size_t)s0 * num_heads * D_V + (size_t)h * D_V + lane * 4;
+    const InT* o_p = o_accum + (size_t)s0 * num_heads * D_V + (size_t)h * D_V + lane * 4;
 
     float mx = NEG_BIG;
     for (int s = lane; s < ns; s += 32) mx = fmaxf(mx, lse_p[(size_t)s * l_stride]);
@@ -91,8 +99,8 @@ combine_kernel(const float* __restrict__ o_accum, const float* __restrict__ lse_
         float4 a[4], b[4];
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
-            a[i] = __ldcs(reinterpret_cast<const float4*>(o_p + (size_t)s * o_stride + i * 128));
-            b[i] = __ldcs(reinterpret_cast<const float4*>(o_p + (size_t)(s + 1) * o_stride + i * 128));
+            a[i] = load4(o_p + (size_t)s * o_stride + i * 128);
+            b[i] = load4(o_p + (size_t)(s + 1) * o_stride + i * 128);
         }
         const float wa = exp2f(lse_p[(size_t)s * l_stride] - lse_w) * sink_scale;
         const float wb = exp2f(lse_p[(size_t)(s + 1) * l_stride] - lse_w) * sink_scale;
@@ -108,7 +116,7 @@ combine_kernel(const float* __restrict__ o_accum, const float* __restrict__ lse_
         const float wa = exp2f(lse_p[(size_t)s * l_stride] - lse_w) * sink_scale;
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
-            const float4 a = __ldcs(reinterpret_cast<const float4*>(o_p + (size_t)s * o_stride + i * 128));
+            const float4 a = load4(o_p + (size_t)s * o_stride + i * 128);
             acc[i].x += wa * a.x; acc[i].y += wa * a.y; acc[i].z += wa * a.z; acc[i].w += wa * a.w;
         }
     }
@@ -170,6 +178,18 @@ int launch_combine_parts(const float* o_parts, const float* lse_parts, __nv_bflo
                                                                     attn_sink, batch, num_heads, parts, part_stride_o,
                                                                     part_stride_l, 1, 0);
     return check_launch("combine_kernel<parts>");
+}
+
+// The same merge over fp16 records (what the attention kernel writes when it derives a uniform split itself).
+int launch_combine_parts_f16(const void* o_parts, const float* lse_parts, __nv_bfloat16* out, float* out_lse,
+                             int parts, int batch, int num_heads, const float* attn_sink, cudaStream_t stream) {
+    const int64_t rows = (int64_t)batch * num_heads;
+    if (rows == 0) return 0;
+    const unsigned grid = (unsigned)((rows + WARPS - 1) / WARPS);
+    launch_dependent(combine_kernel<__nv_bfloat16, __half>, dim3(grid), dim3(WARPS * 32), 0, stream,
+                     reinterpret_cast<const __half*>(o_parts), lse_parts, out, out_lse, nullptr, attn_sink, batch, num_heads, parts,
+                     0, 0, 1, 0);
+    return check_launch("combine_kernel<parts, f16>");
 }
 
 namespace {

@@ -126,6 +126,8 @@ int launch_cp_unslice(const void* gathered, __nv_bfloat16* out, float* lse, int 
 int launch_combine_parts(const float* o_parts, const float* lse_parts, __nv_bfloat16* out, float* out_lse,
                          int parts, int batch, int num_heads, int64_t part_stride_o, int64_t part_stride_l,
                          const float* attn_sink, cudaStream_t stream);
+int launch_combine_parts_f16(const void* o_parts, const float* lse_parts, __nv_bfloat16* out, float* out_lse,
+                             int parts, int batch, int num_heads, const float* attn_sink, cudaStream_t stream);
 int launch_attn_scalar(const AttnParams& p, cudaStream_t stream);
 int launch_attn_pair(const AttnParams& p, cudaStream_t stream);
 bool attn_pair_takes(const AttnParams& p);   // alignment of the caches that the tensor-core kernel's bulk copies need

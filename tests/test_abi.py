@@ -104,7 +104,8 @@ def test_split_policy():
     assert pick_split(16, 148, 32, uniform=False) == (74, FIXED_OVERHEAD)
     # requests of equal length: k equal partitions each (fixed overhead 0 keeps them from straddling two requests)
     assert pick_split(1, 148, 32, uniform=True) == (8, 0)
-    assert pick_split(8, 148, 32, uniform=True) == (32, 0)     # four partitions each: eight would double the partial records
+    assert pick_split(8, 148, 32, uniform=True) == (64, 0)
+    assert pick_split(12, 148, 32, uniform=True) == (48, 0)    # four partitions each: eight would not fit the machine
     assert pick_split(16, 148, 32, uniform=True) == (64, 0)
     assert pick_split(32, 148, 32, uniform=True) == (64, 0)
     assert pick_split(37, 148, 32, uniform=True) == (74, 0)    # two partitions each still fit the machine
