@@ -56,6 +56,7 @@ class FlashMLASchedMeta:
     # split-KV scratch, kept with the metadata so that the layers of a step share it
     o_accum: Optional[torch.Tensor] = None
     lse_accum: Optional[torch.Tensor] = None
+    uniform_k: int = 0     # > 1: equally long requests in this many equal partitions each, no scheduler records needed
 
 
 def get_mla_metadata(*args, **kwargs) -> Tuple[FlashMLASchedMeta, None]:
@@ -135,6 +136,9 @@ def flash_mla_with_kvcache(
             meta.num_sm_parts, fixed_overhead = pick_split(num_tokens, num_sms(q.device), blocks,
                                                            uniform=topk_length is None and ex.topk == 0)
         meta.max_nsplits = min(blocks, meta.num_sm_parts)
+        if (not use_ext and fixed_overhead == 0 and impl != IMPL_SCALAR and meta.num_sm_parts > num_tokens
+                and meta.num_sm_parts % num_tokens == 0 and blocks % (meta.num_sm_parts // num_tokens) == 0):
+            meta.uniform_k = meta.num_sm_parts // num_tokens
         if meta.num_sm_parts != num_tokens:
             meta.tile_scheduler_metadata = torch.empty(meta.num_sm_parts * 8, dtype=torch.int32, device=q.device)
             meta.num_splits = torch.empty(num_tokens + 1, dtype=torch.int32, device=q.device)
@@ -169,6 +173,11 @@ def flash_mla_with_kvcache(
         check(lib.smla_prefill(ptr(q_in), ptr(k_cache), ptr(idx_in), ptr(output), ptr(out_lse), None, num_tokens,
                                num_heads, topk, float(softmax_scale), page_block_size, page_stride, ptr(attn_sink),
                                ptr(topk_length), impl, ptr(st), stream))
+    elif meta.uniform_k > 1 and impl != IMPL_SCALAR and topk_length is None:
+        check(lib.smla_decode_uniform(
+            ptr(q_in), ptr(k_cache), ptr(idx_in), ptr(meta.o_accum), ptr(meta.lse_accum), ptr(output), ptr(out_lse),
+            num_tokens, num_heads, topk, float(softmax_scale), page_block_size, page_stride, meta.uniform_k,
+            ptr(attn_sink), impl, ptr(st), stream))
     else:
         check(lib.smla_decode_splitkv(
             ptr(q_in), ptr(k_cache), ptr(idx_in), ptr(meta.o_accum), ptr(meta.lse_accum), ptr(output), ptr(out_lse),
