@@ -119,19 +119,14 @@ int smla_decode_splitkv(const void* q, const void* kv, const int32_t* indices,
  * parts_per_request * num_tokens partitions and a fixed overhead of 0, derived inside the attention kernel, so that
  * the step is two launches (attention, combine) instead of three.  o_accum / lse_accum are scratch for
  * parts_per_request * num_tokens records (partition j of request r is record j * num_tokens + r; the call keeps
- * the partial outputs in fp16 there, so o_accum needs half of what its type says, its contents are private).
- * merge_counters: NULL, or a device int32[8 * num_tokens] that is zero before the first call and left zero by every
- * call (not to be shared between streams): with it, from 8 partitions per request on and when the grid fits the
- * GPU (2 * parts_per_request * num_tokens CTAs <= SMs), the attention kernel merges the partitions itself (each partition a share of the heads,
- * after a bounded wait for the others; status code 37 if they do not all become resident) and the step is ONE
- * launch.  tcgen05 kernel
+ * the partial outputs in fp16 there, so o_accum needs half of what its type says, its contents are private).  tcgen05 kernel
  * only.  No counterpart in the reference (its scheduler kernel runs every step, flash_mla_sm120/ops.py:78-99).
  */
 int smla_decode_uniform(const void* q, const void* kv, const int32_t* indices,
                         float* o_accum, float* lse_accum, void* out, float* out_lse,
                         int num_tokens, int num_heads, int topk, float sm_scale,
                         int page_block_size, int64_t kv_block_stride_bytes, int parts_per_request,
-                        const float* attn_sink, int32_t* merge_counters, int impl, int32_t* status, void* stream);
+                        const float* attn_sink, int impl, int32_t* status, void* stream);
 
 /*
  * LSE-weighted merge of the split partials.  Replaces sparse_mla_combine_v2_fwd

@@ -39,8 +39,8 @@ _SIGS = {
                                             c_float, c_int, c_int64, c_int, c_void_p, c_void_p, c_int, c_void_p,
                                             c_void_p]),
     "smla_combine": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p]),
-    "smla_decode_uniform": (c_int, [c_void_p] * 7 + [c_int, c_int, c_int, c_float, c_int, c_int64, c_int, c_void_p, c_void_p,
-                                                 c_int, c_void_p, c_void_p]),
+    "smla_decode_uniform": (c_int, [c_void_p] * 7 + [c_int, c_int, c_int, c_float, c_int, c_int64, c_int, c_void_p, c_int,
+                                                 c_void_p, c_void_p]),
     "smla_prefill": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
                              c_float, c_int, c_int64, c_void_p, c_void_p, c_int, c_void_p, c_void_p]),
     "smla_decode_splitkv_ext": (c_int, [c_void_p] * 11 + [c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_int64,

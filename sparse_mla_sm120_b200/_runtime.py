@@ -196,8 +196,6 @@ def scratch(device: torch.device, total_splits: int, num_heads: int, num_tokens:
             "lse_accum": torch.empty((total_splits, 1, num_heads), dtype=torch.float32, device=device),
             "sched_meta": torch.empty(num_parts * 8, dtype=torch.int32, device=device),
             "num_splits": torch.empty(num_tokens + 1, dtype=torch.int32, device=device),
-            # arrival / departure counts of the attention kernel's own merge (uniform split): zero between launches
-            "merge_counters": torch.zeros(8 * num_tokens, dtype=torch.int32, device=device),
             "pinned": False,
         }
     if torch.cuda.is_current_stream_capturing():

@@ -63,7 +63,7 @@ const char* smla_status_string(int code) {
         case 27: return "attention v_full"; case 28: return "attention s_ready"; case 29: return "attention s_free";
         case 30: return "attention p_ready"; case 31: return "attention pv_done"; case 32: return "attention q_ready";
         case 33: return "attention q_staged"; case 34: return "attention q_free"; case 35: return "attention raw_empty";
-        case 36: return "attention raw_full"; case 37: return "attention merge (partitions of a request not all resident)";
+        case 36: return "attention raw_full";
         default: return "unknown";
     }
 }
@@ -137,7 +137,7 @@ int smla_decode_uniform(const void* q, const void* kv, const int32_t* indices,
                         float* o_accum, float* lse_accum, void* out, float* out_lse,
                         int num_tokens, int num_heads, int topk, float sm_scale,
                         int page_block_size, int64_t kv_block_stride_bytes, int parts_per_request,
-                        const float* attn_sink, int32_t* merge_counters, int impl, int32_t* status, void* stream) {
+                        const float* attn_sink, int impl, int32_t* status, void* stream) {
     if (int e = check_attn_common("smla_decode_uniform", q, kv, indices, out, out_lse, num_tokens, num_heads,
                                   topk, page_block_size, kv_block_stride_bytes, impl)) return e;
     if (impl == SMLA_IMPL_SCALAR)
@@ -158,14 +158,6 @@ int smla_decode_uniform(const void* q, const void* kv, const int32_t* indices,
     p.num_tokens = num_tokens; p.num_heads = num_heads; p.topk = topk; p.num_parts = num_tokens * parts_per_request;
     p.page_block_size = page_block_size; p.block_stride = kv_block_stride_bytes; p.sm_scale = sm_scale;
     p.uniform_k = parts_per_request;
-    // The kernel's own merge wants every partition of a request resident at once: a grid of one CTA per SM at most.  It
-    // pays from eight partitions per request on (a head row per warp: 1 to 8 requests 22.5-24.6 us against 24.6-26.7 with
-    // the combine launch); with two partitions per request every CTA merges sixteen rows per group after the slowest
-    // partition has arrived, and the combine kernel, which spreads them over all SMs, is 3-4 us faster.
-    if (merge_counters != nullptr && parts_per_request >= 8 && 2 * num_tokens * parts_per_request <= smla_num_sms()) {
-        p.merge_counters = merge_counters;
-        return launch_attn_pair(p, (cudaStream_t)stream);
-    }
     if (int e = launch_attn_pair(p, (cudaStream_t)stream)) return e;
     return launch_combine_parts_f16(o_accum, lse_accum, (__nv_bfloat16*)out, out_lse, parts_per_request, num_tokens,
                                     num_heads, attn_sink, (cudaStream_t)stream);

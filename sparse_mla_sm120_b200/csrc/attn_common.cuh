@@ -75,59 +75,6 @@ __device__ __forceinline__ int fetch_entry(const AttnParams& p, const Work& w, i
     return pos < w.extra_len ? __ldg(p.extra_indices + (size_t)w.req * p.extra_topk + pos) : -1;
 }
 
-// LSE-weighted merge of the k fp16 partial records of one (request, head) by one warp: record g is row
-// (g * num_tokens + req) * num_heads + head of o16 / lse_accum (the layout of the uniform split), lane l owns output
-// dims 4 l + 128 i.  The arithmetic of combine_kernel (combine.cu; csrc/kernel/combine/combine_kernel.cu:39-159 of the
-// reference).  Loads bypass L1: other SMs wrote the records.
-__device__ __forceinline__ void merge_row_f16(const AttnParams& p, const __half* o16, int k, int req, int head, int lane) {
-    const size_t H = (size_t)p.num_heads, rec = (size_t)p.num_tokens * H;
-    const float* lp = p.lse_accum + (size_t)req * H + head;
-    float mx = NEG_BIG;
-    for (int g = lane; g < k; g += 32) mx = fmaxf(mx, __ldcg(lp + g * rec));
-    mx = warp_max(mx);
-    if (mx == NEG_BIG) mx = 0.f;
-    float sum = 0.f;
-    for (int g = lane; g < k; g += 32) sum += exp2f(__ldcg(lp + g * rec) - mx);
-    sum = warp_sum(sum);
-    float lse = (sum > 0.f) ? (log2f(sum) + mx) : NEG_BIG;
-    const float lse_w = lse;            // weights against the sink-free LSE; the sink then only scales the result
-    float sink_scale = 1.f;
-    if (p.attn_sink != nullptr) {
-        const float sink2 = p.attn_sink[head] * LOG2E;
-        if (lse != NEG_BIG) {
-            const float t = exp2f(sink2 - lse);
-            sink_scale = 1.f / (1.f + t);
-            lse += log2f(1.f + t);
-        } else {
-            lse = sink2;
-        }
-    }
-    if (lane == 0) p.out_lse[(size_t)req * H + head] = lse;
-    const __half* op = o16 + ((size_t)req * H + head) * D_V + lane * 4;
-    float4 acc[4];
-#pragma unroll
-    for (int i = 0; i < 4; ++i) acc[i] = make_float4(0.f, 0.f, 0.f, 0.f);
-    for (int g = 0; g < k; ++g) {
-        const float w = exp2f(__ldcg(lp + g * rec) - lse_w) * sink_scale;
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-            const uint2 v = __ldcg(reinterpret_cast<const uint2*>(op + g * rec * D_V + i * 128));
-            const float2 a = __half22float2(*reinterpret_cast<const __half2*>(&v.x)), b = __half22float2(*reinterpret_cast<const __half2*>(&v.y));
-            acc[i].x = fmaf(w, a.x, acc[i].x); acc[i].y = fmaf(w, a.y, acc[i].y);
-            acc[i].z = fmaf(w, b.x, acc[i].z); acc[i].w = fmaf(w, b.y, acc[i].w);
-        }
-    }
-    __nv_bfloat16* dst = p.out + ((size_t)req * H + head) * D_V + lane * 4;
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-        const __nv_bfloat162 lo = __floats2bfloat162_rn(acc[i].x, acc[i].y), hi = __floats2bfloat162_rn(acc[i].z, acc[i].w);
-        uint2 v;
-        v.x = *reinterpret_cast<const uint32_t*>(&lo);
-        v.y = *reinterpret_cast<const uint32_t*>(&hi);
-        *reinterpret_cast<uint2*>(dst + i * 128) = v;
-    }
-}
-
 __device__ __forceinline__ float pow2_ceil(float x) {
     uint32_t b = __float_as_uint(x);
     if (b & 0x007fffffu) b = (b + 0x00800000u) & 0x7f800000u;

@@ -136,8 +136,7 @@ constexpr uint32_t IDESC_PV_F8 = instr_desc(FMT_E4M3, FMT_E4M3, false, true, 128
 constexpr uint32_t DESC_HI_SW128 = desc_hi(1024, (uint32_t)SWIZZLE_128B);
 
 // give-up codes reported through status[0]
-constexpr uint32_t MERGE_POLLS = 1u << 19;      // x (64 ns + a global load): a few tenths of a second
-enum { W_MERGE = 37, W_QSTAGE = 33, W_QFREE = 34, W_RAWEMPTY = 35, W_RAWFULL = 36, W_KEMPTY = 21, W_KSTORED = 22, W_KFULL = 23, W_INFO = 24, W_VEMPTY = 25, W_VFULL_CTA = 26, W_VFULL = 27,
+enum { W_QSTAGE = 33, W_QFREE = 34, W_RAWEMPTY = 35, W_RAWFULL = 36, W_KEMPTY = 21, W_KSTORED = 22, W_KFULL = 23, W_INFO = 24, W_VEMPTY = 25, W_VFULL_CTA = 26, W_VFULL = 27,
        W_SREADY = 28, W_SFREE = 29, W_PREADY = 30, W_PVDONE = 31, W_QREADY = 32 };
 
 #ifdef SMLA_TRACE
@@ -570,42 +569,6 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PAIR_THREADS, 1) att
                         }
                     }
                     if (live && xpart == 0) p.lse_accum[(size_t)prev_split * p.num_heads + head] = lse;
-                    if (p.merge_counters != nullptr) {
-                        // Merge without a combine launch.  The k pairs that share a request are all resident (the grid has
-                        // one CTA per SM at most), so each group of four warps counts itself in when its 32 head rows of
-                        // the partial are visible (fence, then an atomic), waits, bounded, until all k partitions of the
-                        // request have done so, and merges 32 / k of those rows: partition j the rows [j, j + 1) * 32 / k,
-                        // a row per warp and turn.  The group that leaves last puts both counters back to zero.
-                        const int k = p.uniform_k;
-                        int* ctr = p.merge_counters + ((((size_t)prev_req * 2 + rank) * 2 + grp) << 1);      // [arrived, left]
-                        __threadfence();
-                        named_bar_sync(1 + grp, 128);
-                        if (xpart == 0) {
-                            bool here = true;
-                            if (lane == 0) {
-                                atomicAdd(ctr, 1);
-                                uint32_t polls = 0;
-                                while (ld_acquire_gpu(ctr) < k) {
-                                    if (++polls > MERGE_POLLS || *abort_flag != 0) { here = false; break; }
-                                    __nanosleep(64);
-                                }
-                                if (!here) atomicCAS(const_cast<int*>(abort_flag), 0, (int)W_MERGE);
-                                xch[256 + hrow] = here ? 1.f : 0.f;
-                            }
-                        }
-                        named_bar_sync(1 + grp, 128);
-                        if (xch[256 + grp * 32] != 0.f) {
-                            __threadfence();
-                            const int j = prev_split / p.num_tokens, per = (32 + k - 1) / k;
-                            for (int r = j * per + xpart; r < min((j + 1) * per, 32); r += 4) {
-                                const int hr = grp * 32 + r;
-                                if (hr < heads_cta && head0 + hr < p.num_heads)
-                                    merge_row_f16(p, reinterpret_cast<const __half*>(p.o_accum), k, prev_req, head0 + hr, lane);
-                            }
-                            named_bar_sync(1 + grp, 128);       // the group has read what it needed
-                            if (xpart == 0 && lane == 0 && atomicAdd(ctr + 1, 1) == k - 1) { atomicExch(ctr, 0); atomicExch(ctr + 1, 0); }
-                        }
-                    }
                 } else {
                     float* dst = p.o_accum + ((size_t)prev_split * p.num_heads + (live ? head : 0)) * D_V + col0;
 #pragma unroll 1

@@ -43,8 +43,6 @@ struct AttnParams {
     const float* attn_sink;      // [H] or null
     const int32_t* topk_length;  // [T] or null
     int32_t* status;             // device int32[4] or null
-    int32_t* merge_counters;     // uniform split only: device int32[8 * T], zero between launches (left so), or null = a
-                                 // combine launch follows; see the merge in attn_pair.cu
     int num_tokens, num_heads, topk, num_parts;
     int force_partial;           // 1: every request writes an fp32 partial record, none writes `out`
     int uniform_k;               // > 1 (no scheduler, all requests topk long): every request is cut into uniform_k equal

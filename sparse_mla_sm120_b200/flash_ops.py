@@ -230,7 +230,7 @@ def sparse_mla_decode_fwd(
         check(lib.smla_decode_uniform(
             ptr(q), ptr(kv_cache), ptr(indices), ptr(ws["o_accum"]), ptr(ws["lse_accum"]), ptr(output), ptr(out_lse),
             num_tokens, num_heads, topk, float(sm_scale), page_block_size, page_stride, num_sm_parts // num_tokens,
-            ptr(attn_sink), ptr(ws["merge_counters"]), impl, ptr(status_buffer(q.device)), stream))
+            ptr(attn_sink), impl, ptr(status_buffer(q.device)), stream))
         return output, out_lse
     check(lib.smla_sched_meta(num_tokens, topk, 0, num_sm_parts, fixed_overhead, ptr(topk_length), None,
                               ptr(ws["sched_meta"]), ptr(ws["num_splits"]), stream))

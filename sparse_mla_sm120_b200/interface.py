@@ -57,7 +57,6 @@ class FlashMLASchedMeta:
     o_accum: Optional[torch.Tensor] = None
     lse_accum: Optional[torch.Tensor] = None
     uniform_k: int = 0     # > 1: equally long requests in this many equal partitions each, no scheduler records needed
-    merge_counters: Optional[torch.Tensor] = None   # zero between launches (the attention kernel's own merge)
 
 
 def get_mla_metadata(*args, **kwargs) -> Tuple[FlashMLASchedMeta, None]:
@@ -148,7 +147,6 @@ def flash_mla_with_kvcache(
             records = num_tokens + meta.num_sm_parts
             meta.o_accum = torch.empty((records, 1, num_heads, head_dim_v), dtype=torch.float32, device=q.device)
             meta.lse_accum = torch.empty((records, 1, num_heads), dtype=torch.float32, device=q.device)
-            meta.merge_counters = torch.zeros(8 * num_tokens, dtype=torch.int32, device=q.device)
     elif meta.config != cfg:
         raise ValueError(f"the metadata object was initialised for {meta.config}, this call has {cfg}")
 
@@ -179,7 +177,7 @@ def flash_mla_with_kvcache(
         check(lib.smla_decode_uniform(
             ptr(q_in), ptr(k_cache), ptr(idx_in), ptr(meta.o_accum), ptr(meta.lse_accum), ptr(output), ptr(out_lse),
             num_tokens, num_heads, topk, float(softmax_scale), page_block_size, page_stride, meta.uniform_k,
-            ptr(attn_sink), ptr(meta.merge_counters), impl, ptr(st), stream))
+            ptr(attn_sink), impl, ptr(st), stream))
     else:
         check(lib.smla_decode_splitkv(
             ptr(q_in), ptr(k_cache), ptr(idx_in), ptr(meta.o_accum), ptr(meta.lse_accum), ptr(output), ptr(out_lse),

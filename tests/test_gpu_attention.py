@@ -329,14 +329,11 @@ def test_topk_not_a_multiple_of_the_block(impl, topk):
 
 
 # ------------------------------------------------------------------ equal partitions without a scheduler launch
-@pytest.mark.parametrize("merged", [False, True], ids=["combine-launch", "merged-in-kernel"])
-@pytest.mark.parametrize("tokens,heads,topk,k", [(3, 128, 1024, 4), (5, 64, 512, 2), (1, 16, 2048, 8), (2, 100, 1024, 16),
-                                                  (4, 128, 2048, 8)])
-def test_uniform_split_derived_in_the_kernel(tokens, heads, topk, k, merged):
+@pytest.mark.parametrize("tokens,heads,topk,k", [(3, 128, 1024, 4), (5, 64, 512, 2), (1, 16, 2048, 8)])
+def test_uniform_split_derived_in_the_kernel(tokens, heads, topk, k):
     """Requests of equal length cut into k equal partitions each (smla_decode_uniform: the attention kernel derives the
-    schedule; the k records of a request are merged by the combine kernel or, given counters, by the attention kernel
-    itself): against the oracle, with a sink, a -1 tail and a request whose entries are all -1, and against the same
-    step through the scheduler kernel.  The merged form runs twice: its counters must be back at zero."""
+    schedule, the combine merges k records per request): against the oracle, with a sink, a -1 tail and a request
+    whose entries are all -1, and against the same step through the scheduler kernel."""
     import ctypes
     from sparse_mla_sm120_b200 import _lib, flash_ops
     from sparse_mla_sm120_b200._runtime import check_status, kv_geometry, ptr, status_buffer, stream_ptr
@@ -352,15 +349,11 @@ def test_uniform_split_derived_in_the_kernel(tokens, heads, topk, k, merged):
     lse_accum = torch.empty(k * tokens, heads, dtype=torch.float32, device=dev)
     out = torch.empty(tokens, heads, 512, dtype=torch.bfloat16, device=dev)
     lse = torch.empty(tokens, heads, dtype=torch.float32, device=dev)
-    ctr = torch.zeros(8 * tokens, dtype=torch.int32, device=dev) if merged else None
-    for _ in range(2 if merged else 1):
-        out.zero_()
-        _lib.check(_lib.load().smla_decode_uniform(ptr(q), ptr(kv), ptr(idx), ptr(o_accum), ptr(lse_accum), ptr(out), ptr(lse),
-                                                   tokens, heads, topk, ctypes.c_float(case["sm_scale"]), pbs, pstride, k,
-                                                   ptr(sink.to(dev)), ptr(ctr), TC, ptr(status_buffer(dev)), stream_ptr(dev)))
-        torch.cuda.synchronize()
-        check_status(dev)
-        assert ctr is None or not bool(ctr.any())
+    _lib.check(_lib.load().smla_decode_uniform(ptr(q), ptr(kv), ptr(idx), ptr(o_accum), ptr(lse_accum), ptr(out), ptr(lse),
+                                               tokens, heads, topk, ctypes.c_float(case["sm_scale"]), pbs, pstride, k,
+                                               ptr(sink.to(dev)), TC, ptr(status_buffer(dev)), stream_ptr(dev)))
+    torch.cuda.synchronize()
+    check_status(dev)
     _check_hard(out.cpu(), lse.cpu(), ref_out, ref_lse_sink, TC, case)
     s_out, s_lse = flash_ops.sparse_mla_decode_fwd(q, kv, idx, case["sm_scale"], attn_sink=sink.to(dev), num_sm_parts=k * tokens)
     torch.cuda.synchronize()
@@ -368,7 +361,7 @@ def test_uniform_split_derived_in_the_kernel(tokens, heads, topk, k, merged):
     # refused: a partition count that does not divide the blocks, and the fp32 kernel
     lib = _lib.load()
     assert lib.smla_decode_uniform(ptr(q), ptr(kv), ptr(idx), ptr(o_accum), ptr(lse_accum), ptr(out), ptr(lse), tokens, heads,
-                                   topk, ctypes.c_float(1.0), pbs, pstride, 3 if (topk // 64) % 3 else 5, None, None, TC, None,
+                                   topk, ctypes.c_float(1.0), pbs, pstride, 3 if (topk // 64) % 3 else 5, None, TC, None,
                                    stream_ptr(dev)) == -2
     assert lib.smla_decode_uniform(ptr(q), ptr(kv), ptr(idx), ptr(o_accum), ptr(lse_accum), ptr(out), ptr(lse), tokens, heads,
-                                   topk, ctypes.c_float(1.0), pbs, pstride, k, None, None, SCALAR, None, stream_ptr(dev)) == -2
+                                   topk, ctypes.c_float(1.0), pbs, pstride, k, None, SCALAR, None, stream_ptr(dev)) == -2
