@@ -45,3 +45,23 @@ def test_known_answer_single_request_split():
     assert [m[2:4] for m in meta] == [[0, 10], [10, 20], [20, 30], [30, 32]]
     assert ns == [0, 4]
     assert all(m[5] == 1 and m[6] == 1 for m in meta[:3])
+
+
+@pytest.mark.parametrize("b,topk,k", [(1, 2048, 8), (4, 2048, 8), (8, 2048, 4), (12, 2048, 4), (16, 1024, 4), (32, 2048, 2),
+                                      (37, 2048, 2), (3, 1000, 2), (5, 512, 2)])
+def test_equal_partitions_are_what_the_scheduler_lays_out(b, topk, k):
+    """The schedule that the attention kernel derives itself for equally long requests (pair p: partition p % k of
+    request p // k, blocks [(p % k) n/k, +n/k), every part a split) is what the scheduler gives for k * b partitions and
+    a fixed overhead of 0; the kernel numbers its partial records j * b + r instead of the scheduler's r * k + j."""
+    n = -(-topk // 64)
+    assert n % k == 0
+    meta, ns = orc.sched_meta_ref(b, topk, 0, k * b, 0)
+    assert ns == [r * k for r in range(b + 1)]
+    for p, m in enumerate(meta):
+        r, j = divmod(p, k)
+        assert m[:4] == [r, r, j * (n // k), (j + 1) * (n // k)], (p, m)
+        assert m[4] == j and (m[5], m[6]) == (1, 1)
+    # the policy only proposes such cuts
+    from sparse_mla_sm120_b200._runtime import pick_split
+    parts, overhead = pick_split(b, 148, n, uniform=True)
+    assert overhead != 0 or (parts % b == 0 and n % (parts // b) == 0)
