@@ -2,9 +2,7 @@
 decomposition run as two gloo ranks (oracle partials per shard, all-gather, LSE merge) against
 the single-rank oracle.  No GPU involved."""
 import os
-import sys
 
-import pytest
 import torch
 import torch.distributed as dist
 import torch.multiprocessing as mp

@@ -3,7 +3,6 @@ import numpy as np
 import pytest
 import torch
 
-import helpers as H
 from helpers import bf16_from_bits, orc
 
 pytestmark = pytest.mark.gpu
